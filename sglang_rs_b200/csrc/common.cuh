@@ -1,0 +1,96 @@
+// Shared helpers of the sm_100a kernels: the C ABI's status codes, element
+// conversion between the storage type and 32-bit, and fixed-order reductions.
+//
+// Every launcher is `extern "C" int srb_<name>(..., void* stream)` and returns 0 or a
+// negative status; `srb_last_error()` of the same library gives the message.  Kernels
+// never trap: an index that is out of range sets bits in a device-side error word and
+// the access is skipped, as the reference's kernels do
+// (crates/sglang-kernel/src/cuda_bf16_kernels.rs:30-35).
+#pragma once
+#include <cuda_bf16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+#include <stdio.h>
+
+#define SRB_OK 0
+#define SRB_ERR_INVALID (-1)   // a size or option this kernel does not take
+#define SRB_ERR_CUDA (-2)      // the CUDA runtime refused the launch
+
+#define SRB_DTYPE_F32 0
+#define SRB_DTYPE_BF16 1
+
+// bits of the device-side error word
+#define SRB_FLAG_BAD_TOKEN 1
+#define SRB_FLAG_BAD_SLOT 2
+#define SRB_FLAG_BAD_PAGE 4
+#define SRB_FLAG_WAIT_TIMEOUT 8
+
+static thread_local char srb_error_buffer[512] = "";
+
+#define SRB_DEFINE_LAST_ERROR() \
+  extern "C" const char* srb_last_error() { return srb_error_buffer; }
+
+#define SRB_FAIL(...)                                                   \
+  do {                                                                  \
+    snprintf(srb_error_buffer, sizeof(srb_error_buffer), __VA_ARGS__);  \
+    return SRB_ERR_INVALID;                                             \
+  } while (0)
+
+#define SRB_LAUNCH_CHECK(name)                                                              \
+  do {                                                                                      \
+    cudaError_t srb_status = cudaGetLastError();                                            \
+    if (srb_status != cudaSuccess) {                                                        \
+      snprintf(srb_error_buffer, sizeof(srb_error_buffer), "%s: %s", name,                  \
+               cudaGetErrorString(srb_status));                                             \
+      return SRB_ERR_CUDA;                                                                  \
+    }                                                                                       \
+  } while (0)
+
+#define SRB_CUDA_CALL(call)                                                                 \
+  do {                                                                                      \
+    cudaError_t srb_status = (call);                                                        \
+    if (srb_status != cudaSuccess) {                                                        \
+      snprintf(srb_error_buffer, sizeof(srb_error_buffer), "%s: %s", #call,                 \
+               cudaGetErrorString(srb_status));                                             \
+      return SRB_ERR_CUDA;                                                                  \
+    }                                                                                       \
+  } while (0)
+
+__device__ __forceinline__ float srb_to_float(float v) { return v; }
+__device__ __forceinline__ float srb_to_float(__nv_bfloat16 v) { return __bfloat162float(v); }
+
+template <typename T> __device__ __forceinline__ T srb_from_float(float v);
+template <> __device__ __forceinline__ float srb_from_float<float>(float v) { return v; }
+template <> __device__ __forceinline__ __nv_bfloat16 srb_from_float<__nv_bfloat16>(float v) {
+  return __float2bfloat16_rn(v);
+}
+
+// All lanes receive the same sum; the order of additions is fixed by the butterfly.
+__device__ __forceinline__ float srb_warp_sum(float v) {
+#pragma unroll
+  for (int offset = 16; offset > 0; offset >>= 1) v += __shfl_xor_sync(0xffffffffu, v, offset);
+  return v;
+}
+__device__ __forceinline__ float srb_warp_max(float v) {
+#pragma unroll
+  for (int offset = 16; offset > 0; offset >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, offset));
+  return v;
+}
+
+// Sum over a block of up to 1024 threads; every thread receives the result.  Warp
+// partials are added in warp order, so the result does not depend on timing.
+__device__ __forceinline__ float srb_block_sum(float v, float* scratch /* >= 33 floats */) {
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int warps = (blockDim.x + 31) >> 5;
+  v = srb_warp_sum(v);
+  __syncthreads();
+  if (lane == 0) scratch[warp] = v;
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    float total = 0.f;
+    for (int w = 0; w < warps; ++w) total += scratch[w];
+    scratch[32] = total;
+  }
+  __syncthreads();
+  return scratch[32];
+}

@@ -1,0 +1,154 @@
+// Row-wise kernels of the decoder: embedding gather, fused residual-add + RMSNorm,
+// SiLU(gate)*up, bias add.  All arithmetic is 32-bit; T is the storage type of
+// activations and weights (float or bfloat16).  The residual stream is 32-bit in both.
+//
+// Reference formulas: RMSNorm y = x / sqrt(mean(x^2) + eps) * w
+// (crates/sglang-kernel/src/cpu.rs:26-34), SiLU*mul g / (1 + exp(-g)) * u (cpu.rs:119-123),
+// embedding row copy with out-of-range ids flagged (cuda_bf16_kernels.rs:14-37).
+#include "common.cuh"
+
+SRB_DEFINE_LAST_ERROR()
+
+// residual[row, :] = float(table[ids[row], :]); a bad id writes zeros and flags.
+template <typename T>
+__global__ void embedding_kernel(const int* __restrict__ ids, const T* __restrict__ table,
+                                 float* __restrict__ residual, int width, int vocab, int* error_word) {
+  const int row = blockIdx.x;
+  const int id = ids[row];
+  const bool bad = id < 0 || id >= vocab;
+  if (bad && threadIdx.x == 0) atomicOr(error_word, SRB_FLAG_BAD_TOKEN);
+  const T* src = table + (size_t)(bad ? 0 : id) * width;
+  float* dst = residual + (size_t)row * width;
+  for (int i = threadIdx.x; i < width; i += blockDim.x) dst[i] = bad ? 0.f : srb_to_float(src[i]);
+}
+
+// x = residual[src] (+ delta[src]); optionally residual[src] = x; out[row] = T(x * rsqrt * w).
+// `row_index` (optional) picks the source rows, so the final norm touches only the rows
+// whose logits are wanted.  The row is staged in shared memory between the two passes.
+template <typename T>
+__global__ void add_rmsnorm_kernel(float* __restrict__ residual, const T* __restrict__ delta,
+                                   const float* __restrict__ weight, T* __restrict__ out,
+                                   const int* __restrict__ row_index, int width, float eps,
+                                   int write_residual) {
+  extern __shared__ float staged[];          // width floats, then 33 floats of scratch
+  float* scratch = staged + width;
+  const int row = blockIdx.x;
+  const size_t src = (size_t)(row_index ? row_index[row] : row) * width;
+  float partial = 0.f;
+  for (int i = threadIdx.x; i < width; i += blockDim.x) {
+    float x = residual[src + i];
+    if (delta) x += srb_to_float(delta[src + i]);
+    if (write_residual) residual[src + i] = x;
+    staged[i] = x;
+    partial += x * x;
+  }
+  const float total = srb_block_sum(partial, scratch);
+  const float inv = 1.0f / sqrtf(total / (float)width + eps);
+  T* dst = out + (size_t)row * width;
+  for (int i = threadIdx.x; i < width; i += blockDim.x)
+    dst[i] = srb_from_float<T>(staged[i] * inv * weight[i]);
+}
+
+// out[row, j] = silu(gate_up[row, j]) * gate_up[row, inner + j]
+template <typename T>
+__global__ void silu_mul_kernel(const T* __restrict__ gate_up, T* __restrict__ out, int rows, int inner) {
+  const size_t total = (size_t)rows * inner;
+  for (size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x; idx < total;
+       idx += (size_t)gridDim.x * blockDim.x) {
+    const size_t row = idx / inner, col = idx % inner;
+    const float g = srb_to_float(gate_up[row * 2 * inner + col]);
+    const float u = srb_to_float(gate_up[row * 2 * inner + inner + col]);
+    out[idx] = srb_from_float<T>(g / (1.0f + expf(-g)) * u);
+  }
+}
+
+template <typename T>
+__global__ void add_bias_kernel(T* __restrict__ values, const float* __restrict__ bias, int rows, int width) {
+  const size_t total = (size_t)rows * width;
+  for (size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x; idx < total;
+       idx += (size_t)gridDim.x * blockDim.x)
+    values[idx] = srb_from_float<T>(srb_to_float(values[idx]) + bias[idx % width]);
+}
+
+static int elementwise_grid(size_t total, int block) {
+  size_t blocks = (total + block - 1) / block;
+  const size_t cap = 148 * 16;
+  return (int)(blocks < 1 ? 1 : (blocks > cap ? cap : blocks));
+}
+
+extern "C" int srb_embedding(const int* ids, const void* table, float* residual, int rows, int width,
+                             int vocab, int* error_word, int dtype, void* stream) {
+  if (rows <= 0) return SRB_OK;
+  if (width <= 0 || vocab <= 0) SRB_FAIL("embedding: width %d and vocabulary %d must be positive", width, vocab);
+  cudaStream_t s = (cudaStream_t)stream;
+  if (dtype == SRB_DTYPE_F32)
+    embedding_kernel<float><<<rows, 256, 0, s>>>(ids, (const float*)table, residual, width, vocab, error_word);
+  else if (dtype == SRB_DTYPE_BF16)
+    embedding_kernel<__nv_bfloat16><<<rows, 256, 0, s>>>(ids, (const __nv_bfloat16*)table, residual, width,
+                                                         vocab, error_word);
+  else
+    SRB_FAIL("embedding: unknown dtype %d", dtype);
+  SRB_LAUNCH_CHECK("embedding");
+  return SRB_OK;
+}
+
+template <typename T>
+static int launch_add_rmsnorm(float* residual, const void* delta, const float* weight, void* out,
+                              const int* row_index, int rows, int width, float eps, int write_residual,
+                              cudaStream_t s) {
+  const size_t smem = (size_t)(width + 33) * sizeof(float);
+  if (smem > 227 * 1024) SRB_FAIL("add_rmsnorm: width %d needs %zu bytes of shared memory (limit 232448)", width, smem);
+  if (smem > 48 * 1024)
+    SRB_CUDA_CALL(cudaFuncSetAttribute(add_rmsnorm_kernel<T>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+  const int block = width >= 2048 ? 512 : (width >= 512 ? 256 : 128);
+  add_rmsnorm_kernel<T><<<rows, block, smem, s>>>(residual, (const T*)delta, weight, (T*)out, row_index, width,
+                                                  eps, write_residual);
+  SRB_LAUNCH_CHECK("add_rmsnorm");
+  return SRB_OK;
+}
+
+extern "C" int srb_add_rmsnorm(float* residual, const void* delta, const float* weight, void* out,
+                               const int* row_index, int rows, int width, float eps, int write_residual,
+                               int dtype, void* stream) {
+  if (rows <= 0) return SRB_OK;
+  if (width <= 0) SRB_FAIL("add_rmsnorm: width %d must be positive", width);
+  if (!(eps >= 0.f)) SRB_FAIL("add_rmsnorm: eps must be finite and non-negative");
+  cudaStream_t s = (cudaStream_t)stream;
+  if (dtype == SRB_DTYPE_F32)
+    return launch_add_rmsnorm<float>(residual, delta, weight, out, row_index, rows, width, eps, write_residual, s);
+  if (dtype == SRB_DTYPE_BF16)
+    return launch_add_rmsnorm<__nv_bfloat16>(residual, delta, weight, out, row_index, rows, width, eps,
+                                             write_residual, s);
+  SRB_FAIL("add_rmsnorm: unknown dtype %d", dtype);
+}
+
+extern "C" int srb_silu_mul(const void* gate_up, void* out, int rows, int inner, int dtype, void* stream) {
+  if (rows <= 0) return SRB_OK;
+  if (inner <= 0) SRB_FAIL("silu_mul: inner width %d must be positive", inner);
+  cudaStream_t s = (cudaStream_t)stream;
+  const int grid = elementwise_grid((size_t)rows * inner, 256);
+  if (dtype == SRB_DTYPE_F32)
+    silu_mul_kernel<float><<<grid, 256, 0, s>>>((const float*)gate_up, (float*)out, rows, inner);
+  else if (dtype == SRB_DTYPE_BF16)
+    silu_mul_kernel<__nv_bfloat16><<<grid, 256, 0, s>>>((const __nv_bfloat16*)gate_up, (__nv_bfloat16*)out, rows,
+                                                        inner);
+  else
+    SRB_FAIL("silu_mul: unknown dtype %d", dtype);
+  SRB_LAUNCH_CHECK("silu_mul");
+  return SRB_OK;
+}
+
+extern "C" int srb_add_bias(void* values, const float* bias, int rows, int width, int dtype, void* stream) {
+  if (rows <= 0) return SRB_OK;
+  if (width <= 0) SRB_FAIL("add_bias: width %d must be positive", width);
+  cudaStream_t s = (cudaStream_t)stream;
+  const int grid = elementwise_grid((size_t)rows * width, 256);
+  if (dtype == SRB_DTYPE_F32)
+    add_bias_kernel<float><<<grid, 256, 0, s>>>((float*)values, bias, rows, width);
+  else if (dtype == SRB_DTYPE_BF16)
+    add_bias_kernel<__nv_bfloat16><<<grid, 256, 0, s>>>((__nv_bfloat16*)values, bias, rows, width);
+  else
+    SRB_FAIL("add_bias: unknown dtype %d", dtype);
+  SRB_LAUNCH_CHECK("add_bias");
+  return SRB_OK;
+}

@@ -1,0 +1,114 @@
+// Fused per-head RMSNorm of q and k, rotary position encoding, and the write of k and v
+// into the layer's pages.  One warp handles one head vector of one row.
+//
+// Order of operations as in the reference's attention half
+// (crates/sglang-srt/src/cpu_reference.rs:485-525): project, norm each q and k head with
+// the shared [head_dim] weight, rotate q and k, then store k and v at the row's slot.
+// Rotation (crates/sglang-kernel/src/rotary.rs:216-236): half-split pairs (i, i + rot/2) or
+// interleaved pairs (2i, 2i + 1); angle = float(pos) * inv_freq[i] in 32-bit; the table
+// inv_freq[i] = theta^(-2i/rot) is computed in 64-bit on the host (rotary.rs:76-80).
+//
+// Page pool layout: [page, kv_head, slot_in_page, head_dim].
+#include "common.cuh"
+
+SRB_DEFINE_LAST_ERROR()
+
+#define ROPE_WARPS 4
+
+template <typename T>
+__global__ void qk_norm_rope_kv_kernel(const T* __restrict__ qkv, int qkv_stride, T* __restrict__ q_out,
+                                       T* __restrict__ k_pool, T* __restrict__ v_pool,
+                                       const int* __restrict__ positions, const int* __restrict__ slots,
+                                       const float* __restrict__ q_norm, const float* __restrict__ k_norm,
+                                       float eps, const float* __restrict__ inv_freq, int rotary_dim,
+                                       int interleaved, int n_q, int n_kv, int head_dim, int page_size,
+                                       int num_pages, int heads_to_do, int* error_word) {
+  extern __shared__ float staged_all[];                // ROPE_WARPS * head_dim floats
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int row = blockIdx.x;
+  const int head = blockIdx.y * ROPE_WARPS + warp;     // q heads, then k heads, then v heads
+  if (head >= heads_to_do) return;
+  float* staged = staged_all + warp * head_dim;
+  const T* src = qkv + (size_t)row * qkv_stride + (size_t)head * head_dim;
+
+  const bool is_q = head < n_q;
+  const bool is_k = !is_q && head < n_q + n_kv;
+  const float* norm_weight = is_q ? q_norm : (is_k ? k_norm : nullptr);
+
+  float partial = 0.f;
+  for (int e = lane; e < head_dim; e += 32) {
+    const float x = srb_to_float(src[e]);
+    staged[e] = x;
+    partial += x * x;
+  }
+  if (norm_weight) {
+    const float total = srb_warp_sum(partial);
+    const float inv = 1.0f / sqrtf(total / (float)head_dim + eps);
+    for (int e = lane; e < head_dim; e += 32) staged[e] = staged[e] * inv * norm_weight[e];
+  }
+  __syncwarp();
+  if ((is_q || is_k) && inv_freq) {
+    const float pos = (float)positions[row];
+    const int half = rotary_dim >> 1;
+    for (int i = lane; i < half; i += 32) {
+      const int ia = interleaved ? 2 * i : i;
+      const int ib = interleaved ? 2 * i + 1 : i + half;
+      float sn, cs;
+      sincosf(pos * inv_freq[i], &sn, &cs);
+      const float a = staged[ia], b = staged[ib];
+      staged[ia] = a * cs - b * sn;      // each element belongs to exactly one pair
+      staged[ib] = b * cs + a * sn;
+    }
+  }
+  __syncwarp();
+
+  T* dst;
+  if (is_q) {
+    dst = q_out + ((size_t)row * n_q + head) * head_dim;
+  } else {
+    const int slot = slots[row];
+    if (slot < 0 || slot >= num_pages * page_size) {
+      if (lane == 0) atomicOr(error_word, SRB_FLAG_BAD_SLOT);
+      return;
+    }
+    const int kv_head = is_k ? head - n_q : head - n_q - n_kv;
+    const size_t offset =
+        (((size_t)(slot / page_size) * n_kv + kv_head) * page_size + (slot % page_size)) * head_dim;
+    dst = (is_k ? k_pool : v_pool) + offset;
+  }
+  for (int e = lane; e < head_dim; e += 32) dst[e] = srb_from_float<T>(staged[e]);
+}
+
+// `slots` may be null: then only the q heads are processed (a layer that reads another
+// layer's cache writes nothing).
+extern "C" int srb_qk_norm_rope_kv(const void* qkv, int qkv_stride, void* q_out, void* k_pool, void* v_pool,
+                                   const int* positions, const int* slots, const float* q_norm,
+                                   const float* k_norm, float eps, const float* inv_freq, int rotary_dim,
+                                   int interleaved, int rows, int n_q, int n_kv, int head_dim, int page_size,
+                                   int num_pages, int* error_word, int dtype, void* stream) {
+  if (rows <= 0) return SRB_OK;
+  if (n_q <= 0 || n_kv <= 0 || head_dim <= 0 || page_size <= 0)
+    SRB_FAIL("qk_norm_rope_kv: head counts, head_dim and page size must be positive");
+  if (inv_freq && (rotary_dim <= 0 || rotary_dim > head_dim || (rotary_dim & 1)))
+    SRB_FAIL("qk_norm_rope_kv: rotary width %d must be even, positive and at most head_dim %d", rotary_dim,
+             head_dim);
+  if (head_dim > 2048) SRB_FAIL("qk_norm_rope_kv: head_dim %d exceeds 2048", head_dim);
+  const int heads = slots ? n_q + 2 * n_kv : n_q;
+  dim3 grid(rows, (heads + ROPE_WARPS - 1) / ROPE_WARPS);
+  const size_t smem = (size_t)ROPE_WARPS * head_dim * sizeof(float);
+  cudaStream_t s = (cudaStream_t)stream;
+  if (dtype == SRB_DTYPE_F32)
+    qk_norm_rope_kv_kernel<float><<<grid, ROPE_WARPS * 32, smem, s>>>(
+        (const float*)qkv, qkv_stride, (float*)q_out, (float*)k_pool, (float*)v_pool, positions, slots, q_norm,
+        k_norm, eps, inv_freq, rotary_dim, interleaved, n_q, n_kv, head_dim, page_size, num_pages, heads,
+        error_word);
+  else if (dtype == SRB_DTYPE_BF16)
+    qk_norm_rope_kv_kernel<__nv_bfloat16><<<grid, ROPE_WARPS * 32, smem, s>>>(
+        (const __nv_bfloat16*)qkv, qkv_stride, (__nv_bfloat16*)q_out, (__nv_bfloat16*)k_pool,
+        (__nv_bfloat16*)v_pool, positions, slots, q_norm, k_norm, eps, inv_freq, rotary_dim, interleaved, n_q,
+        n_kv, head_dim, page_size, num_pages, heads, error_word);
+  else
+    SRB_FAIL("qk_norm_rope_kv: unknown dtype %d", dtype);
+  SRB_LAUNCH_CHECK("qk_norm_rope_kv");
+  return SRB_OK;
+}

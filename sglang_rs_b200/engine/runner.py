@@ -1,0 +1,263 @@
+"""The step function: one batch of (request, its next tokens) through the model.
+
+A step runs only the tokens it is given, from the cache that earlier steps left, and
+returns 32-bit logits at the rows that were asked for.  Prompt portions and single decoded
+tokens sit side by side in the flat row arrays; nothing below the flattening knows a
+"prefill" from a "decode" (the reference's flat batch already has this shape:
+crates/sglang-srt/src/model_executor.rs:16-33, with positions that need not start at 0,
+:172-173, and causality by length, crates/sglang-srt/src/cuda_attention.rs:285-297).
+
+Both generation (the scheduler) and trace replay call :meth:`ModelRunner.step`.
+"""
+from __future__ import annotations
+
+from dataclasses import dataclass, field
+from typing import Dict, Hashable, List, Optional, Sequence
+
+import numpy as np
+import torch
+
+from .. import ops
+from ..cache.manager import CacheManager, OutOfPages, RequestCache
+
+
+class StepInputError(ValueError):
+    """A step that cannot run: bad token id, position past the model's limit, bad index."""
+
+
+@dataclass
+class StepEntry:
+    handle: RequestCache
+    tokens: Sequence[int]
+    #: indices into ``tokens`` whose logits are wanted
+    want: Sequence[int] = ()
+
+
+@dataclass
+class AttentionLaunch:
+    """Rows [begin, end) of the step run as one launch.  ``split_size`` 0: one block walks
+    all keys of a row; else the keys are cut every ``split_size`` positions."""
+    begin: int
+    end: int
+    split_size: int
+    max_splits: int
+
+
+@dataclass
+class PagedBatch:
+    """Per-step view of one cache group."""
+    block_table: torch.Tensor            # int32 [requests, stride]
+    slots: torch.Tensor                  # int32 [rows]: where each row's key and value go
+    launches: List[AttentionLaunch]
+    scratch_acc: Optional[torch.Tensor] = None
+    scratch_ml: Optional[torch.Tensor] = None
+
+
+@dataclass
+class StepContext:
+    device: torch.device
+    dtype: torch.dtype
+    num_rows: int
+    num_requests: int
+    token_ids: torch.Tensor              # int32 [rows]
+    positions: torch.Tensor              # int32 [rows]
+    row_request: torch.Tensor            # int32 [rows]: index into this step's requests
+    cu_rows: torch.Tensor                # int32 [requests + 1]: rows of request r are cu_rows[r] .. cu_rows[r+1]
+    state_slots: torch.Tensor            # int32 [requests]
+    error_word: torch.Tensor
+    paged: Dict[Hashable, PagedBatch] = field(default_factory=dict)
+    # host mirrors, for parts that plan on the host
+    host_cu_rows: Sequence[int] = ()
+    host_start_positions: Sequence[int] = ()
+    host_state_slots: Sequence[int] = ()
+
+
+class ModelRunner:
+    #: keys per split of a decode row; fixed, so a row's arithmetic depends on its own position only
+    SPLIT_SIZE = 256
+    #: a request that brings at most this many rows is run with split keys
+    SPLIT_ROWS_PER_REQUEST = 1
+    #: floats of attention scratch above which the split is made coarser
+    SCRATCH_LIMIT = 64 << 20
+
+    def __init__(self, model, cache: CacheManager):
+        if model.device is None:
+            raise RuntimeError("the model has no weights yet")
+        if model.device.type != "cuda":
+            raise RuntimeError("the engine runs on a CUDA device only; there is no host path")
+        self.model, self.cache = model, cache
+        self.device, self.dtype = model.device, model.dtype
+        self.error_word = ops.new_error_word(self.device)
+        # floats of split scratch per (row, split) that the widest mixer needs
+        widths = [layer.split_scratch() for layer in model.layers if hasattr(layer, "split_scratch")]
+        self._scratch_acc_width = max((w[0] for w in widths), default=0)
+        self._scratch_ml_width = max((w[1] for w in widths), default=0)
+        self._scratch: Dict[str, torch.Tensor] = {}
+        self.steps_run = 0
+
+    # ------------------------------------------------------------------ the step
+    def step(self, entries: Sequence[StepEntry]) -> Optional[torch.Tensor]:
+        """Runs one batch.  Returns logits [wanted rows, vocab] (float32, on the device) in
+        the order of ``entries`` and of each entry's ``want``, or None if none is wanted."""
+        entries = [entry for entry in entries]
+        if not entries:
+            return None
+        self._validate(entries)
+        reserved: List[StepEntry] = []
+        try:
+            for entry in entries:
+                self.cache.reserve(entry.handle, len(entry.tokens))
+                reserved.append(entry)
+        except OutOfPages:
+            for entry in reserved:
+                self.cache.trim_reservation(entry.handle)
+            raise
+        try:
+            ctx, logit_rows = self._flatten(entries)
+            caches = [self.cache.layer_cache(i) for i in range(len(self.model.program))]
+            logits = self.model.forward(ctx, caches, logit_rows)
+        except Exception:
+            for entry in entries:
+                self.cache.trim_reservation(entry.handle)
+            raise
+        for entry in entries:
+            self.cache.commit(entry.handle, len(entry.tokens))
+        self.steps_run += 1
+        return logits
+
+    def check_device_errors(self) -> None:
+        """Reads the device-side error word (a synchronisation) and raises if a kernel
+        skipped an access."""
+        ops.raise_on_error_word(self.error_word)
+
+    # ------------------------------------------------------------------ checks
+    def _validate(self, entries: Sequence[StepEntry]) -> None:
+        seen = set()
+        for entry in entries:
+            handle = entry.handle
+            if handle.closed:
+                raise StepInputError(f"request {handle.request_id!r} has ended")
+            if id(handle) in seen:
+                raise StepInputError(f"request {handle.request_id!r} appears twice in one step")
+            seen.add(id(handle))
+            count = len(entry.tokens)
+            if count == 0:
+                raise StepInputError(f"request {handle.request_id!r} brings no tokens")
+            if handle.length + count > self.model.max_positions:
+                raise StepInputError(
+                    f"request {handle.request_id!r}: position {handle.length + count - 1} exceeds "
+                    f"max_position_embeddings {self.model.max_positions}")
+            for token in entry.tokens:
+                if not 0 <= int(token) < self.model.vocab_size:
+                    raise StepInputError(f"request {handle.request_id!r}: token id {token} is outside the "
+                                         f"vocabulary of {self.model.vocab_size}")
+            for index in entry.want:
+                if not 0 <= int(index) < count:
+                    raise StepInputError(f"request {handle.request_id!r}: wanted row {index} is not among its "
+                                         f"{count} tokens")
+
+    # ------------------------------------------------------------------ flattening
+    def _flatten(self, entries: Sequence[StepEntry]):
+        # decoded tokens first, portions after them: each kind is one contiguous row range
+        order = sorted(range(len(entries)),
+                       key=lambda i: (len(entries[i].tokens) > self.SPLIT_ROWS_PER_REQUEST, i))
+        starts = [0] * len(entries)
+        cu_rows = [0]
+        tokens: List[int] = []
+        positions: List[int] = []
+        row_request: List[int] = []
+        start_positions: List[int] = []
+        state_slots: List[int] = []
+        split_rows = 0
+        for slot, index in enumerate(order):
+            entry = entries[index]
+            count = len(entry.tokens)
+            starts[index] = cu_rows[-1]
+            tokens.extend(int(t) for t in entry.tokens)
+            positions.extend(range(entry.handle.length, entry.handle.length + count))
+            row_request.extend([slot] * count)
+            start_positions.append(entry.handle.length)
+            state_slots.append(entry.handle.state_slot)
+            cu_rows.append(cu_rows[-1] + count)
+            if count <= self.SPLIT_ROWS_PER_REQUEST:
+                split_rows = cu_rows[-1]
+        rows = cu_rows[-1]
+        logit_rows = [starts[i] + int(w) for i, entry in enumerate(entries) for w in entry.want]
+
+        groups = list(self.cache.allocators)
+        page_size = self.cache.page_size
+        stride = 1
+        for index in order:
+            for key in groups:
+                stride = max(stride, len(entries[index].handle.tables[key]))
+        tables = {key: np.full((len(order), stride), -1, dtype=np.int32) for key in groups}
+        slots = {key: np.empty(rows, dtype=np.int32) for key in groups}
+        for slot, index in enumerate(order):
+            handle = entries[index].handle
+            begin = cu_rows[slot]
+            for key in groups:
+                table = handle.tables[key]
+                tables[key][slot, :len(table)] = table
+                pos = np.arange(handle.length, handle.length + len(entries[index].tokens))
+                pages = np.asarray(table, dtype=np.int64)[pos // page_size]
+                slots[key][begin:begin + len(pos)] = pages * page_size + pos % page_size
+
+        pieces = [np.asarray(tokens, dtype=np.int32), np.asarray(positions, dtype=np.int32),
+                  np.asarray(row_request, dtype=np.int32), np.asarray(cu_rows, dtype=np.int32),
+                  np.asarray(state_slots, dtype=np.int32), np.asarray(logit_rows, dtype=np.int32)]
+        for key in groups:
+            pieces.append(tables[key].reshape(-1))
+            pieces.append(slots[key])
+        device_pieces = self._upload(pieces)
+        token_ids, positions_d, row_request_d, cu_rows_d, state_slots_d, logit_rows_d = device_pieces[:6]
+
+        ctx = StepContext(self.device, self.dtype, rows, len(order), token_ids, positions_d, row_request_d,
+                          cu_rows_d, state_slots_d, self.error_word, host_cu_rows=cu_rows,
+                          host_start_positions=start_positions, host_state_slots=state_slots)
+        np_positions = np.asarray(positions, dtype=np.int64)
+        for g, key in enumerate(groups):
+            table_d = device_pieces[6 + 2 * g].view(len(order), stride)
+            slots_d = device_pieces[7 + 2 * g]
+            ctx.paged[key] = self._plan(key, table_d, slots_d, np_positions, split_rows, rows)
+        return ctx, (logit_rows_d if logit_rows else None)
+
+    def _upload(self, pieces: Sequence[np.ndarray]) -> List[torch.Tensor]:
+        """All of a step's index arrays in one pinned buffer and one copy."""
+        sizes = [piece.size for piece in pieces]
+        offsets = np.concatenate([[0], np.cumsum([(size + 3) // 4 * 4 for size in sizes])])
+        total = int(offsets[-1])
+        staging = torch.empty(max(total, 1), dtype=torch.int32, pin_memory=True)
+        view = staging.numpy()
+        for piece, offset, size in zip(pieces, offsets, sizes):
+            view[offset:offset + size] = piece
+        on_device = staging.to(self.device, non_blocking=True)
+        return [on_device[offset:offset + size] for offset, size in zip(offsets[:-1], sizes)]
+
+    def _plan(self, key, table_d, slots_d, positions: np.ndarray, split_rows: int, rows: int) -> PagedBatch:
+        window = self.cache.windows[key]
+        launches: List[AttentionLaunch] = []
+        scratch_acc = scratch_ml = None
+        if split_rows > 0:
+            pos = positions[:split_rows]
+            begin = np.maximum(0, pos + 1 - window) if window else np.zeros_like(pos)
+            split_size = self.SPLIT_SIZE
+            while True:
+                max_splits = int((pos // split_size - begin // split_size + 1).max())
+                need_acc = split_rows * max_splits * self._scratch_acc_width
+                need_ml = split_rows * max_splits * self._scratch_ml_width
+                if need_acc <= self.SCRATCH_LIMIT or max_splits == 1:
+                    break
+                split_size *= 2
+            launches.append(AttentionLaunch(0, split_rows, split_size, max_splits))
+            scratch_acc = self._scratch_tensor("acc", need_acc)
+            scratch_ml = self._scratch_tensor("ml", need_ml)
+        if rows > split_rows:
+            launches.append(AttentionLaunch(split_rows, rows, 0, 1))
+        return PagedBatch(table_d, slots_d, launches, scratch_acc, scratch_ml)
+
+    def _scratch_tensor(self, name: str, floats: int) -> torch.Tensor:
+        current = self._scratch.get(name)
+        if current is None or current.numel() < floats:
+            current = torch.empty(max(floats, 1), dtype=torch.float32, device=self.device)
+            self._scratch[name] = current
+        return current

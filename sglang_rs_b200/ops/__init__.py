@@ -1,0 +1,250 @@
+"""Python face of the CUDA kernels.
+
+Every function takes CUDA tensors, checks what the kernel assumes (device, dtype,
+contiguity), launches on torch's current stream and raises :class:`KernelError` with the
+library's message if the kernel refuses the sizes.  Nothing here computes on the host
+and nothing falls back to another implementation.
+"""
+from __future__ import annotations
+
+import ctypes
+from typing import Optional
+
+import torch
+
+from ..csrc.build import load_library
+
+F32, BF16 = 0, 1
+
+
+class KernelError(RuntimeError):
+    pass
+
+
+def dtype_code(dtype: torch.dtype) -> int:
+    if dtype == torch.float32:
+        return F32
+    if dtype == torch.bfloat16:
+        return BF16
+    raise KernelError(f"kernels take float32 or bfloat16, not {dtype}")
+
+
+def _ptr(tensor: Optional[torch.Tensor]):
+    return None if tensor is None else ctypes.c_void_p(tensor.data_ptr())
+
+
+def _stream():
+    return ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)
+
+
+def _need(tensor: torch.Tensor, name: str, dtype: Optional[torch.dtype] = None) -> None:
+    if not tensor.is_cuda:
+        raise KernelError(f"{name} must be a CUDA tensor; this engine has no host path")
+    if not tensor.is_contiguous():
+        raise KernelError(f"{name} must be contiguous")
+    if dtype is not None and tensor.dtype != dtype:
+        raise KernelError(f"{name} must be {dtype}, found {tensor.dtype}")
+
+
+def _check(library, status: int) -> None:
+    if status != 0:
+        raise KernelError(library.srb_last_error().decode("utf-8", "replace") or f"kernel status {status}")
+
+
+def new_error_word(device) -> torch.Tensor:
+    """Device-side word that kernels OR fault bits into (bad token, slot or page)."""
+    return torch.zeros(1, dtype=torch.int32, device=device)
+
+
+ERROR_BITS = {1: "token id outside the vocabulary", 2: "cache slot outside the pool",
+              4: "page id outside the pool", 8: "a device-side wait ran out"}
+
+
+def raise_on_error_word(word: torch.Tensor) -> None:
+    value = int(word.item())
+    if value:
+        word.zero_()
+        what = [text for bit, text in ERROR_BITS.items() if value & bit]
+        raise KernelError("device-side check failed: " + "; ".join(what))
+
+
+# --------------------------------------------------------------------------- rows
+
+def embedding(ids: torch.Tensor, table: torch.Tensor, residual: torch.Tensor, error_word: torch.Tensor) -> None:
+    """residual[r, :] = float(table[ids[r], :])"""
+    _need(ids, "ids", torch.int32); _need(table, "table"); _need(residual, "residual", torch.float32)
+    rows, width = residual.shape
+    if ids.numel() != rows or table.shape[1] != width:
+        raise KernelError("embedding: shapes of ids, table and residual do not agree")
+    lib = load_library("elementwise")
+    _check(lib, lib.srb_embedding(_ptr(ids), _ptr(table), _ptr(residual), rows, width, table.shape[0],
+                                  _ptr(error_word), dtype_code(table.dtype), _stream()))
+
+
+def add_rmsnorm(residual: torch.Tensor, delta: Optional[torch.Tensor], weight: torch.Tensor, eps: float,
+                out: torch.Tensor, row_index: Optional[torch.Tensor] = None, write_residual: bool = True) -> None:
+    """x = residual (+ delta); residual = x if asked; out = x / sqrt(mean(x^2) + eps) * weight.
+
+    With ``row_index`` the rows ``row_index[i]`` are read and ``out[i]`` is written."""
+    _need(residual, "residual", torch.float32); _need(weight, "weight", torch.float32); _need(out, "out")
+    width = residual.shape[1]
+    rows = out.shape[0]
+    if delta is not None:
+        _need(delta, "delta", out.dtype)
+        if delta.shape != residual.shape:
+            raise KernelError("add_rmsnorm: delta and residual differ in shape")
+    if row_index is not None:
+        _need(row_index, "row_index", torch.int32)
+        if row_index.numel() != rows:
+            raise KernelError("add_rmsnorm: one output row per index is needed")
+    elif rows != residual.shape[0]:
+        raise KernelError("add_rmsnorm: out and residual differ in rows")
+    if weight.numel() != width or out.shape[1] != width:
+        raise KernelError("add_rmsnorm: widths do not agree")
+    lib = load_library("elementwise")
+    _check(lib, lib.srb_add_rmsnorm(_ptr(residual), _ptr(delta), _ptr(weight), _ptr(out), _ptr(row_index), rows,
+                                    width, ctypes.c_float(eps), int(write_residual), dtype_code(out.dtype),
+                                    _stream()))
+
+
+def silu_mul(gate_up: torch.Tensor, out: torch.Tensor) -> None:
+    """out[r, j] = silu(gate_up[r, j]) * gate_up[r, inner + j]"""
+    _need(gate_up, "gate_up"); _need(out, "out", gate_up.dtype)
+    rows, inner = out.shape
+    if gate_up.shape != (rows, 2 * inner):
+        raise KernelError("silu_mul: gate_up must be [rows, 2 * inner]")
+    lib = load_library("elementwise")
+    _check(lib, lib.srb_silu_mul(_ptr(gate_up), _ptr(out), rows, inner, dtype_code(out.dtype), _stream()))
+
+
+def add_bias(values: torch.Tensor, bias: torch.Tensor) -> None:
+    _need(values, "values"); _need(bias, "bias", torch.float32)
+    rows, width = values.shape
+    if bias.numel() != width:
+        raise KernelError("add_bias: bias width differs")
+    lib = load_library("elementwise")
+    _check(lib, lib.srb_add_bias(_ptr(values), _ptr(bias), rows, width, dtype_code(values.dtype), _stream()))
+
+
+# --------------------------------------------------------------------------- attention
+
+def qk_norm_rope_kv(qkv: torch.Tensor, q_out: torch.Tensor, k_pool: Optional[torch.Tensor],
+                    v_pool: Optional[torch.Tensor], positions: torch.Tensor, slots: Optional[torch.Tensor],
+                    q_norm: Optional[torch.Tensor], k_norm: Optional[torch.Tensor], eps: float,
+                    inv_freq: Optional[torch.Tensor], rotary_dim: int, interleaved: bool, n_q: int, n_kv: int,
+                    head_dim: int, error_word: torch.Tensor) -> None:
+    """Per-head norm of q and k, rotation of q and k, q to ``q_out``, k and v into the pages.
+
+    ``qkv`` is [rows, >= (n_q + 2 n_kv) head_dim] with q heads, k heads, v heads in that order;
+    pools are [pages, n_kv, page_size, head_dim]; ``slots[r]`` = page * page_size + offset.
+    With ``slots`` None nothing is written to the pages."""
+    _need(qkv, "qkv"); _need(q_out, "q_out", qkv.dtype); _need(positions, "positions", torch.int32)
+    rows = qkv.shape[0]
+    page_size = num_pages = 1
+    if slots is not None:
+        _need(slots, "slots", torch.int32); _need(k_pool, "k_pool", qkv.dtype); _need(v_pool, "v_pool", qkv.dtype)
+        num_pages, pool_heads, page_size, pool_dim = k_pool.shape
+        if (pool_heads, pool_dim) != (n_kv, head_dim) or v_pool.shape != k_pool.shape:
+            raise KernelError("qk_norm_rope_kv: pools must be [pages, n_kv, page_size, head_dim]")
+        if qkv.shape[1] < (n_q + 2 * n_kv) * head_dim:
+            raise KernelError("qk_norm_rope_kv: qkv is narrower than q, k and v together")
+    for name, w in (("q_norm", q_norm), ("k_norm", k_norm)):
+        if w is not None:
+            _need(w, name, torch.float32)
+            if w.numel() != head_dim:
+                raise KernelError(f"qk_norm_rope_kv: {name} must have head_dim elements")
+    if inv_freq is not None:
+        _need(inv_freq, "inv_freq", torch.float32)
+        if inv_freq.numel() != rotary_dim // 2:
+            raise KernelError("qk_norm_rope_kv: inv_freq must have rotary_dim / 2 elements")
+    lib = load_library("rope_kv")
+    _check(lib, lib.srb_qk_norm_rope_kv(
+        _ptr(qkv), qkv.stride(0), _ptr(q_out), _ptr(k_pool), _ptr(v_pool), _ptr(positions), _ptr(slots),
+        _ptr(q_norm), _ptr(k_norm), ctypes.c_float(eps), _ptr(inv_freq), rotary_dim, int(interleaved), rows, n_q,
+        n_kv, head_dim, page_size, num_pages, _ptr(error_word), dtype_code(qkv.dtype), _stream()))
+
+
+def attention_scratch_sizes(rows: int, n_q: int, head_dim: int, max_splits: int) -> tuple[int, int]:
+    """Floats of scratch that a split run needs: (partial accumulators, partial max and sum)."""
+    return rows * n_q * max_splits * head_dim, rows * n_q * max_splits * 2
+
+
+def paged_attention(q: torch.Tensor, k_pool: torch.Tensor, v_pool: torch.Tensor, out: torch.Tensor,
+                    positions: torch.Tensor, row_request: torch.Tensor, block_table: torch.Tensor, *,
+                    scale: float, window: int, split_size: int, max_splits: int,
+                    scratch_acc: Optional[torch.Tensor], scratch_ml: Optional[torch.Tensor],
+                    error_word: torch.Tensor) -> None:
+    """out[r, h, :] = softmax over the keys row r may see of (q . k) * scale, times v.
+
+    q, out: [rows, n_q, head_dim]; pools [pages, n_kv, page_size, head_dim]; block_table
+    [requests, stride].  ``split_size`` 0 walks all keys in one block per (row, kv head);
+    otherwise partials go through the scratch tensors and are merged in split order."""
+    _need(q, "q"); _need(out, "out", q.dtype); _need(k_pool, "k_pool", q.dtype); _need(v_pool, "v_pool", q.dtype)
+    _need(positions, "positions", torch.int32); _need(row_request, "row_request", torch.int32)
+    _need(block_table, "block_table", torch.int32)
+    rows, n_q, head_dim = q.shape
+    num_pages, n_kv, page_size, pool_dim = k_pool.shape
+    if pool_dim != head_dim or v_pool.shape != k_pool.shape or out.shape != q.shape:
+        raise KernelError("paged_attention: shapes of q, out and the pools do not agree")
+    if split_size:
+        need_acc, need_ml = attention_scratch_sizes(rows, n_q, head_dim, max_splits)
+        if scratch_acc is None or scratch_ml is None or scratch_acc.numel() < need_acc or scratch_ml.numel() < need_ml:
+            raise KernelError("paged_attention: scratch tensors are too small for this split run")
+        _need(scratch_acc, "scratch_acc", torch.float32); _need(scratch_ml, "scratch_ml", torch.float32)
+    lib = load_library("attention")
+    _check(lib, lib.srb_paged_attention(
+        _ptr(q), _ptr(k_pool), _ptr(v_pool), _ptr(out), _ptr(scratch_acc), _ptr(scratch_ml), _ptr(positions),
+        _ptr(row_request), _ptr(block_table), block_table.stride(0), rows, n_q, n_kv, head_dim, page_size,
+        num_pages, int(window), int(split_size), int(max_splits), ctypes.c_float(scale), _ptr(error_word),
+        dtype_code(q.dtype), _stream()))
+
+
+# --------------------------------------------------------------------------- matrix products
+
+def linear(x: torch.Tensor, weight: torch.Tensor, bias: Optional[torch.Tensor] = None,
+           out_dtype: Optional[torch.dtype] = None) -> torch.Tensor:
+    """y = x @ weight^T (+ bias); weight is [out, in], row-major.
+
+    float32: the FFMA kernel of this package, true 32-bit.  bfloat16: cuBLAS through
+    torch with 32-bit accumulation, which is what the reference's engine calls for every
+    projection (crates/sglang-kernel/src/cublas.rs:383-410); ``out_dtype`` float32 keeps the
+    accumulator's precision (used for the logits)."""
+    _need(x, "x"); _need(weight, "weight", x.dtype)
+    if x.dim() != 2 or weight.dim() != 2 or x.shape[1] != weight.shape[1]:
+        raise KernelError(f"linear: x {tuple(x.shape)} and weight {tuple(weight.shape)} do not fit")
+    m, k = x.shape
+    n = weight.shape[0]
+    if x.dtype == torch.float32:
+        out = torch.empty((m, n), dtype=torch.float32, device=x.device)
+        if bias is not None:
+            _need(bias, "bias", torch.float32)
+        lib = load_library("gemm_f32")
+        _check(lib, lib.srb_gemm_f32(_ptr(x), _ptr(weight), _ptr(bias), _ptr(out), m, n, k, x.stride(0),
+                                     weight.stride(0), out.stride(0), _stream()))
+        return out
+    if out_dtype == torch.float32:
+        out = torch.mm(x, weight.t(), out_dtype=torch.float32)
+    else:
+        out = torch.mm(x, weight.t())
+    if bias is not None:
+        add_bias(out, bias)
+    return out
+
+
+# --------------------------------------------------------------------------- sampling
+
+def sample(logits: torch.Tensor, temperature: Optional[torch.Tensor], uniform: Optional[torch.Tensor],
+           out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """One token per row of 32-bit logits: argmax where temperature is None or <= 0, else
+    inverse-CDF sampling of softmax(logits / temperature) with the row's uniform number."""
+    _need(logits, "logits", torch.float32)
+    rows, vocab = logits.shape
+    if out is None:
+        out = torch.empty(rows, dtype=torch.int32, device=logits.device)
+    _need(out, "out", torch.int32)
+    if temperature is not None:
+        _need(temperature, "temperature", torch.float32); _need(uniform, "uniform", torch.float32)
+    lib = load_library("sampling")
+    _check(lib, lib.srb_sample(_ptr(logits), rows, vocab, logits.stride(0), _ptr(temperature), _ptr(uniform),
+                               _ptr(out), _stream()))
+    return out

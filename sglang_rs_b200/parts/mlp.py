@@ -1,0 +1,48 @@
+"""Gated feed-forward: down( silu(gate(x)) * up(x) ).
+
+act_j = g_j / (1 + exp(-g_j)) * u_j (reference: crates/sglang-kernel/src/cpu.rs:119-123;
+order of products crates/sglang-srt/src/cpu_reference.rs:585-603).  gate and up come from
+one product with the two matrices stacked (gate rows first), made at load time.
+"""
+from __future__ import annotations
+
+from dataclasses import dataclass
+from typing import Dict, Mapping
+
+import torch
+
+from .. import ops
+from .base import FeedForward, TensorSpec, matrix_to
+
+
+@dataclass(frozen=True)
+class GatedMlpNames:
+    gate: str
+    up: str
+    down: str
+
+
+class GatedMlp(FeedForward):
+    ACTIVATIONS = ("silu",)
+
+    def __init__(self, hidden: int, inner: int, activation: str, names: GatedMlpNames):
+        if activation not in self.ACTIVATIONS:
+            raise ValueError(f"unsupported activation {activation}; available: {self.ACTIVATIONS}")
+        self.hidden, self.inner, self.activation, self.names = int(hidden), int(inner), activation, names
+        self.w_gate_up = self.w_down = None
+
+    def tensor_specs(self) -> Dict[str, TensorSpec]:
+        n = self.names
+        return {n.gate: TensorSpec((self.inner, self.hidden)), n.up: TensorSpec((self.inner, self.hidden)),
+                n.down: TensorSpec((self.hidden, self.inner))}
+
+    def load(self, tensors: Mapping[str, torch.Tensor], device, dtype: torch.dtype) -> None:
+        n = self.names
+        self.w_gate_up = matrix_to(torch.cat([tensors[n.gate], tensors[n.up]], dim=0), device, dtype)
+        self.w_down = matrix_to(tensors[n.down], device, dtype)
+
+    def forward(self, ctx, x: torch.Tensor) -> torch.Tensor:
+        gate_up = ops.linear(x, self.w_gate_up)
+        act = torch.empty((x.shape[0], self.inner), dtype=x.dtype, device=x.device)
+        ops.silu_mul(gate_up, act)
+        return ops.linear(act, self.w_down)
