@@ -21,6 +21,48 @@ PAGE_SIZE = 16
 MAX_LIVE = 4
 
 
+class ReplaySession:
+    """A model, a cache pool for ``max_tokens`` tokens and the step function, driven by
+    step records.  Used by the command line below and by tests."""
+
+    def __init__(self, model_dir: str, dtype: str, max_tokens: int, page_size: int = PAGE_SIZE,
+                 device: str = "cuda"):
+        import torch
+        from ..cache import CacheManager
+        from ..weights import load_model, parse_dtype
+        from .runner import ModelRunner
+        if not torch.cuda.is_available():
+            raise RuntimeError("no CUDA device; this engine has no host path")
+        self.dtype = parse_dtype(dtype)
+        self.model = load_model(model_dir, device=device, dtype=self.dtype)
+        # The caller counts each live request's tokens rounded up to 64, a multiple of the page
+        # size, so ceil(max_tokens / page_size) pages hold whatever is live at any time.
+        self.cache = CacheManager(self.model.cache_needs(), page_size=page_size, max_tokens=max(max_tokens, 1),
+                                  max_requests=MAX_LIVE, device=device, dtype=self.dtype)
+        self.runner = ModelRunner(self.model, self.cache)
+        self.handles = {}
+
+    def run(self, record: dict):
+        """One step record; returns the wanted logits as a host float32 array, or None."""
+        from .runner import StepEntry
+        entries = []
+        for item in record.get("entries", []):
+            handle = self.handles.get(item["id"])
+            if handle is None:
+                handle = self.handles[item["id"]] = self.cache.open(item["id"])
+            entries.append(StepEntry(handle, item["tokens"], item.get("want", [])))
+        logits = self.runner.step(entries) if entries else None
+        host = None
+        if logits is not None:
+            host = logits.float().cpu().contiguous().numpy()
+        self.runner.check_device_errors()
+        for request_id in record.get("end", []):
+            handle = self.handles.pop(request_id, None)
+            if handle is not None:
+                self.cache.close(handle)
+        return host
+
+
 def main(argv=None) -> int:
     parser = argparse.ArgumentParser(prog="trace_run", description=__doc__.split("\n\n")[0])
     parser.add_argument("--model", required=True, help="folder with config.json and model.safetensors")
@@ -31,51 +73,22 @@ def main(argv=None) -> int:
     parser.add_argument("--page-size", type=int, default=PAGE_SIZE)
     args = parser.parse_args(argv)
 
-    import torch
-    if not torch.cuda.is_available():
-        print("trace_run: no CUDA device; this engine has no host path", file=sys.stderr)
-        return 3
-    from ..cache import CacheManager
-    from ..weights import load_model, parse_dtype
-    from .runner import ModelRunner, StepEntry
-
-    dtype = parse_dtype(args.dtype)
-    if dtype == torch.float32:
-        torch.backends.cuda.matmul.allow_tf32 = False
-        torch.backends.cudnn.allow_tf32 = False
     print(f"[trace_run] loading {args.model} as {args.dtype}", file=sys.stderr, flush=True)
-    model = load_model(args.model, device="cuda", dtype=dtype)
-    # The caller counts each live request's tokens rounded up to 64, a multiple of the page
-    # size, so ceil(max_tokens / page_size) pages hold whatever is live at any time.
-    cache = CacheManager(model.cache_needs(), page_size=args.page_size, max_tokens=max(args.max_tokens, 1),
-                         max_requests=MAX_LIVE,
-                         device="cuda", dtype=dtype)
-    runner = ModelRunner(model, cache)
+    try:
+        session = ReplaySession(args.model, args.dtype, args.max_tokens, args.page_size)
+    except RuntimeError as error:
+        print(f"trace_run: {error}", file=sys.stderr)
+        return 3
     os.makedirs(args.out, exist_ok=True)
-
-    handles = {}
     for line in sys.stdin:
         line = line.strip()
         if not line:
             continue
         record = json.loads(line)
-        step = record["step"]
-        entries = []
-        for item in record.get("entries", []):
-            handle = handles.get(item["id"])
-            if handle is None:
-                handle = handles[item["id"]] = cache.open(item["id"])
-            entries.append(StepEntry(handle, item["tokens"], item.get("want", [])))
-        logits = runner.step(entries) if entries else None
+        logits = session.run(record)
         if logits is not None:
-            host = logits.to(torch.float32).cpu().contiguous().numpy()
-            host.astype("<f4", copy=False).tofile(os.path.join(args.out, f"{step}.f32"))
-        runner.check_device_errors()
-        for request_id in record.get("end", []):
-            handle = handles.pop(request_id, None)
-            if handle is not None:
-                cache.close(handle)
-        print(f"done {step}", flush=True)
+            logits.astype("<f4", copy=False).tofile(os.path.join(args.out, f"{record['step']}.f32"))
+        print(f"done {record['step']}", flush=True)
     return 0
 
 

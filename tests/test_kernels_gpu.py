@@ -1,0 +1,304 @@
+"""Each kernel alone against the plain implementation's function for the same part, at
+sizes other than the engine's tests use, in 32-bit and in bfloat16."""
+import math
+
+import pytest
+import torch
+
+import plain_model as pm
+from sglang_rs_b200 import ops
+
+pytestmark = pytest.mark.gpu
+DEV = "cuda"
+DTYPES = [torch.float32, torch.bfloat16]
+
+
+def tol(dtype):
+    return 1e-5 if dtype == torch.float32 else 1e-2       # relative to the largest |expected|
+
+
+def close(got, want, dtype, what=""):
+    want = want.to(torch.float64).cpu()
+    got = got.to(torch.float64).cpu()
+    scale = max(float(want.abs().max()), 1e-30)
+    err = float((got - want).abs().max()) / scale
+    assert err <= tol(dtype), f"{what}: error {err:.3e} of scale (tolerance {tol(dtype)})"
+
+
+def rounded(t, dtype):
+    """What the kernel sees: the value after storage in ``dtype``, widened to 64-bit."""
+    return t.to(dtype).to(torch.float64)
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_embedding_and_bad_token(dtype):
+    g = torch.Generator().manual_seed(0)
+    table = torch.randn(331, 72, generator=g)
+    ids = torch.tensor([0, 330, 17, 17, 5], dtype=torch.int32)
+    out = torch.empty(5, 72, device=DEV)
+    word = ops.new_error_word(DEV)
+    ops.embedding(ids.to(DEV), table.to(DEV, dtype), out, word)
+    assert torch.equal(out.cpu().double(), rounded(table, dtype)[ids.long()])
+    ops.raise_on_error_word(word)
+    ops.embedding(torch.tensor([3, 331, -1], dtype=torch.int32, device=DEV), table.to(DEV, dtype), out[:3], word)
+    assert torch.equal(out[1:3].cpu(), torch.zeros(2, 72))
+    with pytest.raises(ops.KernelError, match="token id outside"):
+        ops.raise_on_error_word(word)
+    ops.raise_on_error_word(word)                         # reading it cleared it
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("width", [72, 100, 1023, 5120, 16400])
+def test_add_rmsnorm(dtype, width):
+    g = torch.Generator().manual_seed(width)
+    rows = 7
+    residual = torch.randn(rows, width, generator=g) * 3
+    delta = torch.randn(rows, width, generator=g)
+    weight = 1 + 0.1 * torch.randn(width, generator=g)
+    eps = 3e-5
+    res_d = residual.to(DEV)
+    out = torch.empty(rows, width, device=DEV, dtype=dtype)
+    ops.add_rmsnorm(res_d, delta.to(DEV, dtype), weight.to(DEV), eps, out)
+    summed = residual.double() + rounded(delta, dtype)
+    assert torch.allclose(res_d.cpu().double(), summed, atol=1e-6)        # the 32-bit sum is stored back
+    close(out, pm.plain_rms_norm(summed, weight.double(), eps), dtype, "add+norm")
+    # no delta; picked rows; the residual stays untouched
+    before = res_d.clone()
+    pick = torch.tensor([6, 0, 3], dtype=torch.int32, device=DEV)
+    out2 = torch.empty(3, width, device=DEV, dtype=dtype)
+    ops.add_rmsnorm(res_d, None, weight.to(DEV), eps, out2, row_index=pick, write_residual=False)
+    assert torch.equal(res_d, before)
+    close(out2, pm.plain_rms_norm(before.cpu().double()[pick.cpu().long()], weight.double(), eps), dtype, "picked rows")
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_silu_mul_and_bias(dtype):
+    g = torch.Generator().manual_seed(1)
+    gate_up = torch.randn(5, 2 * 200, generator=g) * 4
+    out = torch.empty(5, 200, device=DEV, dtype=dtype)
+    ops.silu_mul(gate_up.to(DEV, dtype), out)
+    seen = rounded(gate_up, dtype)
+    close(out, pm.plain_silu_mul(seen[:, :200], seen[:, 200:]), dtype, "silu*mul")
+    values = torch.randn(4, 77, generator=g)
+    bias = torch.randn(77, generator=g)
+    v = values.to(DEV, dtype)
+    ops.add_bias(v, bias.to(DEV))
+    close(v, rounded(values, dtype) + bias.double(), dtype, "bias")
+
+
+@pytest.mark.parametrize("m,n,k", [(1, 331, 72), (3, 64, 1000), (65, 130, 257), (200, 17, 48)])
+def test_gemm_f32_is_true_32_bit(m, n, k):
+    g = torch.Generator().manual_seed(m * n)
+    x, w, b = torch.randn(m, k, generator=g), torch.randn(n, k, generator=g), torch.randn(n, generator=g)
+    out = ops.linear(x.to(DEV), w.to(DEV), b.to(DEV))
+    want = pm.plain_linear(x.double(), w.double(), b.double())
+    err = float((out.cpu().double() - want).abs().max() / want.abs().max())
+    assert err < 3e-6, err                                # a TF32 product would be near 1e-3
+    # a row's result does not depend on the rows beside it
+    alone = ops.linear(x[m - 1:].contiguous().to(DEV), w.to(DEV), b.to(DEV))
+    assert torch.equal(alone[0], out[m - 1])
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("n_q,n_kv,d,rot,inter", [(4, 2, 16, 16, False), (5, 1, 48, 48, False), (3, 3, 128, 64, False),
+                                                  (2, 1, 80, 80, True), (8, 2, 256, 256, False)])
+def test_qk_norm_rope_kv(dtype, n_q, n_kv, d, rot, inter):
+    g = torch.Generator().manual_seed(d + n_q)
+    rows, page, pages = 9, 8, 6
+    qkv = torch.randn(rows, (n_q + 2 * n_kv) * d, generator=g)
+    qn, kn = 1 + 0.1 * torch.randn(d, generator=g), 1 + 0.1 * torch.randn(d, generator=g)
+    positions = torch.tensor([0, 1, 2, 50, 51, 7, 8, 1000, 3], dtype=torch.int32)
+    slots = torch.tensor([5, 6, 7, 40, 41, 16, 17, 0, 30], dtype=torch.int32)
+    theta, eps = 50000.0, 1e-5
+    inv = pm.plain_inverse_frequencies(theta, rot)
+    k_pool = torch.zeros(pages, n_kv, page, d, device=DEV, dtype=dtype)
+    v_pool = torch.zeros_like(k_pool)
+    q_out = torch.empty(rows, n_q, d, device=DEV, dtype=dtype)
+    word = ops.new_error_word(DEV)
+    ops.qk_norm_rope_kv(qkv.to(DEV, dtype), q_out, k_pool, v_pool, positions.to(DEV), slots.to(DEV), qn.to(DEV),
+                        kn.to(DEV), eps, inv.to(DEV), rot, inter, n_q, n_kv, d, word)
+    ops.raise_on_error_word(word)
+    seen = rounded(qkv, dtype)
+    q = pm.plain_rms_norm(seen[:, :n_q * d].view(rows, n_q, d), qn.double(), eps)
+    k = pm.plain_rms_norm(seen[:, n_q * d:(n_q + n_kv) * d].view(rows, n_kv, d), kn.double(), eps)
+    v = seen[:, (n_q + n_kv) * d:].view(rows, n_kv, d)
+
+    def rotate(x):
+        if not inter:
+            out = x.clone()
+            out[..., :rot] = pm.plain_rope_neox(x[..., :rot].contiguous(), positions, inv)
+            return out
+        # interleaved pairs (2i, 2i+1): the same rotation after a permutation (rotary.rs:223-226)
+        perm = torch.cat([torch.arange(0, rot, 2), torch.arange(1, rot, 2)])
+        out = x.clone()
+        out[..., perm] = pm.plain_rope_neox(x[..., perm].contiguous(), positions, inv)
+        return out
+
+    close(q_out, rotate(q), dtype, "q")
+    k_want, v_want = rotate(k), v
+    for r in range(rows):
+        pg, off = int(slots[r]) // page, int(slots[r]) % page
+        close(k_pool[pg, :, off], k_want[r], dtype, f"k row {r}")
+        close(v_pool[pg, :, off], v_want[r], dtype, f"v row {r}")
+    written = {(int(s) // page, int(s) % page) for s in slots}
+    for pg in range(pages):
+        for off in range(page):
+            if (pg, off) not in written:
+                assert float(k_pool[pg, :, off].abs().max()) == 0.0
+    # a slot outside the pool is skipped and flagged
+    ops.qk_norm_rope_kv(qkv.to(DEV, dtype), q_out, k_pool, v_pool, positions.to(DEV),
+                        torch.full((rows,), pages * page, dtype=torch.int32, device=DEV), qn.to(DEV), kn.to(DEV), eps,
+                        inv.to(DEV), rot, inter, n_q, n_kv, d, word)
+    with pytest.raises(ops.KernelError, match="cache slot"):
+        ops.raise_on_error_word(word)
+
+
+def paged_case(dtype, n_q, n_kv, d, page, lengths, rows_per_request, window, seed, boost=None):
+    """Requests with their keys scattered over shuffled pages; the last ``rows`` positions of
+    each request are the step's rows."""
+    g = torch.Generator().manual_seed(seed)
+    total_pages = sum(-(-n // page) for n in lengths) + 3
+    order = torch.randperm(total_pages, generator=g).tolist()
+    k_pool = torch.randn(total_pages, n_kv, page, d, generator=g)       # stale values everywhere
+    v_pool = torch.randn(total_pages, n_kv, page, d, generator=g)
+    stride = max(-(-n // page) for n in lengths) + 1
+    table = torch.full((len(lengths), stride), -1, dtype=torch.int32)
+    ks, vs, qs, positions, row_request = [], [], [], [], []
+    for r, (n, rows) in enumerate(zip(lengths, rows_per_request)):
+        k, v = torch.randn(n, n_kv, d, generator=g), torch.randn(n, n_kv, d, generator=g)
+        q = torch.randn(rows, n_q, d, generator=g)
+        if boost is not None and n > boost[0]:
+            # one far key stands out for the last row: its score dominates the softmax
+            k[boost[0]] = q[-1, ::n_q // n_kv] * boost[1]
+        for j in range(-(-n // page)):
+            pg = order.pop()
+            table[r, j] = pg
+            chunk = slice(j * page, min(n, (j + 1) * page))
+            k_pool[pg, :, :chunk.stop - chunk.start] = k[chunk].transpose(0, 1)
+            v_pool[pg, :, :chunk.stop - chunk.start] = v[chunk].transpose(0, 1)
+        ks.append(k); vs.append(v); qs.append(q)
+        positions += list(range(n - rows, n))
+        row_request += [r] * rows
+    return dict(k_pool=k_pool.to(DEV, dtype), v_pool=v_pool.to(DEV, dtype), table=table.to(DEV),
+                q=torch.cat(qs).to(DEV, dtype), positions=torch.tensor(positions, dtype=torch.int32, device=DEV),
+                row_request=torch.tensor(row_request, dtype=torch.int32, device=DEV), ks=ks, vs=vs, qs=qs,
+                lengths=lengths, rows=rows_per_request, window=window, dtype=dtype)
+
+
+def expected_attention(case, scale):
+    outs = []
+    for k, v, q, n, rows in zip(case["ks"], case["vs"], case["qs"], case["lengths"], case["rows"]):
+        outs.append(pm.plain_attention(rounded(q, case["dtype"]), rounded(k, case["dtype"]), rounded(v, case["dtype"]),
+                                       scale, window=case["window"], first_position=n - rows))
+    return torch.cat(outs)
+
+
+def run_attention(case, scale, split_size):
+    q = case["q"]
+    rows, n_q, d = q.shape
+    out = torch.full_like(q, float("nan"))
+    word = ops.new_error_word(DEV)
+    max_splits, acc, ml = 1, None, None
+    if split_size:
+        pos = case["positions"].cpu()
+        begin = torch.clamp(pos + 1 - case["window"], min=0) if case["window"] else torch.zeros_like(pos)
+        max_splits = int((pos // split_size - begin // split_size + 1).max())
+        a, m = ops.attention_scratch_sizes(rows, n_q, d, max_splits)
+        acc = torch.full((a,), float("nan"), device=DEV)
+        ml = torch.full((m,), float("nan"), device=DEV)
+    ops.paged_attention(q, case["k_pool"], case["v_pool"], out, case["positions"], case["row_request"], case["table"],
+                        scale=scale, window=case["window"] or 0, split_size=split_size, max_splits=max_splits,
+                        scratch_acc=acc, scratch_ml=ml, error_word=word)
+    ops.raise_on_error_word(word)
+    return out
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("n_q,n_kv,d,page,window", [(4, 2, 16, 16, None), (6, 3, 32, 8, None), (5, 1, 48, 16, 37),
+                                                    (8, 8, 64, 4, None), (16, 2, 128, 32, 100), (3, 1, 272, 16, None)])
+@pytest.mark.parametrize("split", [0, 32, 256])
+def test_paged_attention(dtype, n_q, n_kv, d, page, window, split):
+    lengths, rows = (1, 33, 300, 64, 257), (1, 5, 2, 64, 1)
+    case = paged_case(dtype, n_q, n_kv, d, page, lengths, rows, window, seed=d + page)
+    scale = 0.7 / math.sqrt(d)
+    close(run_attention(case, scale, split), expected_attention(case, scale), dtype, "attention")
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("split", [0, 256])
+def test_a_far_key_among_hundreds_is_found(dtype, split):
+    """One key far back gets a score that dominates; leaving it out, or reading a stale page
+    in its place, would change the output completely."""
+    n_q, n_kv, d, page = 4, 2, 64, 16
+    case = paged_case(dtype, n_q, n_kv, d, page, (700, 530), (1, 3), None, seed=9, boost=(17, 3.0))
+    scale = 1.0 / math.sqrt(d)
+    out = run_attention(case, scale, split)
+    close(out, expected_attention(case, scale), dtype, "far key")
+    # the last row of the first request is, within rounding, the boosted key's value
+    v_far = rounded(case["vs"][0][17], dtype)               # [n_kv, d]
+    got = out[0].double().cpu()                             # row 0 = request 0's only row, [n_q, d]
+    for h in (0, 2):                                        # the query heads the key was aligned with
+        assert float((got[h] - v_far[h // 2]).abs().max()) < 0.05
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_window_edge(dtype):
+    """The key just outside the window is boosted: it must not be seen; the one just inside is."""
+    n_q, n_kv, d, page, window = 2, 1, 32, 8, 24
+    n = 100
+    for which, visible in ((n - window - 1, False), (n - window, True)):
+        case = paged_case(dtype, n_q, n_kv, d, page, (n,), (1,), window, seed=4, boost=(which, 4.0))
+        out = run_attention(case, 1.0 / math.sqrt(d), 0)
+        close(out, expected_attention(case, 1.0 / math.sqrt(d)), dtype, f"window edge key {which}")
+        near = float((out[0, 0].double().cpu() - rounded(case["vs"][0][which, 0], dtype)).abs().max()) < 0.05
+        assert near == visible
+
+
+def test_attention_refuses_sizes_it_cannot_take():
+    case = paged_case(torch.float32, 4, 2, 16, 16, (5,), (1,), None, seed=0)
+    bad_q = torch.zeros(1, 4, 24, device=DEV)
+    with pytest.raises(ops.KernelError):
+        ops.paged_attention(bad_q, case["k_pool"], case["v_pool"], torch.empty_like(bad_q), case["positions"],
+                            case["row_request"], case["table"], scale=1.0, window=0, split_size=0, max_splits=1,
+                            scratch_acc=None, scratch_ml=None, error_word=ops.new_error_word(DEV))
+    pool = torch.zeros(4, 1, 16, 40, device=DEV)
+    q = torch.zeros(1, 2, 40, device=DEV)
+    with pytest.raises(ops.KernelError, match="multiple of 16"):
+        ops.paged_attention(q, pool, pool, torch.empty_like(q), case["positions"], case["row_request"], case["table"],
+                            scale=1.0, window=0, split_size=0, max_splits=1, scratch_acc=None, scratch_ml=None,
+                            error_word=ops.new_error_word(DEV))
+    pool = torch.zeros(4, 1, 16, 16, device=DEV)
+    q = torch.zeros(1, 40, 16, device=DEV)
+    with pytest.raises(ops.KernelError, match="exceed 32"):
+        ops.paged_attention(q, pool, pool, torch.empty_like(q), case["positions"], case["row_request"], case["table"],
+                            scale=1.0, window=0, split_size=0, max_splits=1, scratch_acc=None, scratch_ml=None,
+                            error_word=ops.new_error_word(DEV))
+
+
+def test_sampling_kernel():
+    g = torch.Generator().manual_seed(3)
+    vocab = 1531
+    logits = torch.randn(6, vocab, generator=g) * 3
+    logits[2, 100] = logits[2, 900] = 50.0                 # equal maxima: the lowest index wins
+    picked = ops.sample(logits.to(DEV), None, None).cpu()
+    assert picked.tolist() == [pm.plain_argmax(row) for row in logits]
+    assert picked[2] == 100
+    temperature = torch.tensor([0.7, 1.0, 0.0, 1.5, 0.3, 1.0])
+    for trial in range(20):
+        u = torch.rand(6, generator=g)
+        got = ops.sample(logits.to(DEV), temperature.to(DEV), u.to(DEV)).cpu().tolist()
+        for r in range(6):
+            if temperature[r] <= 0:
+                assert got[r] == pm.plain_argmax(logits[r])
+                continue
+            want = pm.plain_temperature_sample(logits[r], float(temperature[r]), float(u[r]))
+            if got[r] != want:
+                # only a tie of the running sum at 32-bit rounding may move the pick by one place
+                p = torch.softmax(logits[r].double() / float(temperature[r]), 0)
+                edge = float(torch.cumsum(p, 0)[min(got[r], want)])
+                assert abs(got[r] - want) == 1 and abs(edge - float(u[r])) < 1e-5, (r, got[r], want)
+    # u at the ends
+    ends = ops.sample(logits[:1].to(DEV), torch.tensor([1.0], device=DEV), torch.tensor([0.0], device=DEV))
+    assert int(ends[0]) == 0
+    last = ops.sample(logits[:1].to(DEV), torch.tensor([1.0], device=DEV), torch.tensor([0.99999994], device=DEV))
+    assert int(last[0]) >= vocab - 50

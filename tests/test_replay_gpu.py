@@ -1,0 +1,103 @@
+"""Replay of the same requests cut in different ways, in 32-bit and in bfloat16, against the
+plain implementation: whole; most in one step and the last 32 one by one; in portions of
+changing size; mixed with other requests on so few pages that they are used again."""
+import json
+import os
+import subprocess
+import sys
+
+import numpy as np
+import pytest
+import torch
+
+import plain_model as pm
+import replay_helpers as rh
+
+pytestmark = pytest.mark.gpu
+
+CASES = {
+    # config, request lengths, page size
+    "A": (pm.TINY_A, (5, 17, 33, 64, 200, 131), 16),
+    "B": (pm.TINY_B, (7, 40, 90, 128, 65, 33), 8),
+    "C": (pm.TINY_C, (3, 300, 47, 600, 258, 513), 16),
+}
+DTYPES = {"float32": (torch.float32, rh.FP32_TOLERANCE), "bfloat16": (torch.bfloat16, rh.BF16_TOLERANCE)}
+
+
+@pytest.fixture(scope="module")
+def prepared(tmp_path_factory):
+    cache = {}
+
+    def get(case, dtype_name):
+        key = (case, dtype_name)
+        if key not in cache:
+            config, lengths, page = CASES[case]
+            folder = rh.make_folder(tmp_path_factory.mktemp(f"{case}_{dtype_name}"), "model", config, seed=7,
+                                    dtype=DTYPES[dtype_name][0])
+            requests = rh.random_requests(config, lengths, seed=3)
+            cache[key] = (folder, requests, rh.oracle(folder, requests), page)
+        return cache[key]
+    return get
+
+
+def check(rows, expected, tolerance, requests, what):
+    assert {rid: len(v) for rid, v in rows.items()} == {rid: len(t) for rid, t in requests.items()}
+    bad = rh.first_bad(rows, expected, tolerance)
+    worst, where = rh.worst_error(rows, expected)
+    print(f"{what}: worst error {worst:.3e} of scale at {where}")
+    assert bad is None, f"{what}: first wrong row: request {bad[0]} position {bad[1]} error {bad[2]:.3e} (tolerance {tolerance})"
+
+
+@pytest.mark.parametrize("dtype_name", list(DTYPES))
+@pytest.mark.parametrize("case", list(CASES))
+@pytest.mark.parametrize("mode", ["whole", "tail", "portions", "mixed"])
+def test_cut_does_not_matter(prepared, case, dtype_name, mode):
+    folder, requests, expected, page = prepared(case, dtype_name)
+    trace = {"whole": rh.trace_whole, "tail": rh.trace_tail_by_one, "portions": rh.trace_portions,
+             "mixed": lambda r: rh.trace_mixed(r, seed=11)}[mode](requests)
+    rows, session = rh.run_in_process(folder, dtype_name, trace, page_size=page)
+    check(rows, expected, DTYPES[dtype_name][1], requests, f"{case}/{dtype_name}/{mode}")
+    if mode == "mixed":
+        # pages that one request gave back were handed to another
+        shared = [owners for owners in session.page_owners.values() if len(owners) > 1]
+        assert len(shared) >= 3, "no page was used again; the trace does not test stale contents"
+
+
+@pytest.mark.parametrize("dtype_name", list(DTYPES))
+def test_bfloat16_and_float32_cuts_agree_with_each_other(prepared, dtype_name):
+    """Between two cuts of the same engine the difference is rounding only, far below the
+    distance to the oracle in bfloat16."""
+    folder, requests, expected, page = prepared("C", dtype_name)
+    whole, _ = rh.run_in_process(folder, dtype_name, rh.trace_whole(requests), page_size=page)
+    mixed, _ = rh.run_in_process(folder, dtype_name, rh.trace_mixed(requests, seed=5), page_size=page)
+    as_expected = {rid: np.stack([whole[rid][p] for p in range(len(t))]).astype(np.float64) for rid, t in requests.items()}
+    worst, where = rh.worst_error(mixed, as_expected)
+    print(f"C/{dtype_name}: mixed against whole: {worst:.3e} at {where}")
+    assert worst <= (2e-5 if dtype_name == "float32" else 2e-2)
+
+
+def test_trace_run_program(prepared, tmp_path):
+    """The program itself, as a user calls it: steps on standard input, files out."""
+    folder, requests, expected, page = prepared("A", "float32")
+    trace = rh.trace_mixed(requests, seed=2)
+    out = tmp_path / "out"
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    process = subprocess.run(
+        [sys.executable, os.path.join(root, "bin", "trace_run"), "--model", folder, "--dtype", "float32",
+         "--out", str(out), "--max-tokens", str(rh.max_tokens_of(trace))],
+        input="\n".join(json.dumps(s) for s in trace) + "\n", capture_output=True, text=True, timeout=600)
+    assert process.returncode == 0, process.stderr[-2000:]
+    assert process.stdout.split() == [x for s in trace for x in ("done", str(s["step"]))]
+    vocab = pm.TINY_A["vocab_size"]
+    outputs = []
+    for s in trace:
+        wanted = sum(len(e["want"]) for e in s["entries"])
+        path = out / f"{s['step']}.f32"
+        if wanted:
+            data = np.fromfile(path, dtype="<f4")
+            assert data.size == wanted * vocab
+            outputs.append(data.reshape(wanted, vocab))
+        else:
+            assert not path.exists()
+            outputs.append(None)
+    check(rh.collect(trace, outputs), expected, rh.FP32_TOLERANCE, requests, "trace_run A/float32/mixed")
