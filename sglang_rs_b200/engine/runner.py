@@ -72,7 +72,10 @@ class StepContext:
     host_state_slots: Sequence[int] = ()
 
 
-class ModelRunner:
+class StepPlanner:
+    """Turns a step's entries into the flat device arrays and the per-group plans that the
+    parts read.  It needs the cache manager and the scratch widths of the mixers, not the
+    model, so a single part can be stepped with it."""
     #: keys per split of a decode row; fixed, so a row's arithmetic depends on its own position only
     SPLIT_SIZE = 256
     #: a request that brings at most this many rows is run with split keys
@@ -80,84 +83,17 @@ class ModelRunner:
     #: floats of attention scratch above which the split is made coarser
     SCRATCH_LIMIT = 64 << 20
 
-    def __init__(self, model, cache: CacheManager):
-        if model.device is None:
-            raise RuntimeError("the model has no weights yet")
-        if model.device.type != "cuda":
-            raise RuntimeError("the engine runs on a CUDA device only; there is no host path")
-        self.model, self.cache = model, cache
-        self.device, self.dtype = model.device, model.dtype
+    def __init__(self, cache: CacheManager, device, dtype: torch.dtype, scratch_widths: Sequence = ()):
+        self.cache, self.device, self.dtype = cache, torch.device(device), dtype
         self.error_word = ops.new_error_word(self.device)
         # floats of split scratch per (row, split) that the widest mixer needs
-        widths = [layer.split_scratch() for layer in model.layers if hasattr(layer, "split_scratch")]
-        self._scratch_acc_width = max((w[0] for w in widths), default=0)
-        self._scratch_ml_width = max((w[1] for w in widths), default=0)
+        self._scratch_acc_width = max((w[0] for w in scratch_widths), default=0)
+        self._scratch_ml_width = max((w[1] for w in scratch_widths), default=0)
         self._scratch: Dict[str, torch.Tensor] = {}
-        self.steps_run = 0
-
-    # ------------------------------------------------------------------ the step
-    def step(self, entries: Sequence[StepEntry]) -> Optional[torch.Tensor]:
-        """Runs one batch.  Returns logits [wanted rows, vocab] (float32, on the device) in
-        the order of ``entries`` and of each entry's ``want``, or None if none is wanted."""
-        entries = [entry for entry in entries]
-        if not entries:
-            return None
-        self._validate(entries)
-        reserved: List[StepEntry] = []
-        try:
-            for entry in entries:
-                self.cache.reserve(entry.handle, len(entry.tokens))
-                reserved.append(entry)
-        except OutOfPages:
-            for entry in reserved:
-                self.cache.trim_reservation(entry.handle)
-            raise
-        try:
-            ctx, logit_rows = self._flatten(entries)
-            caches = [self.cache.layer_cache(i) for i in range(len(self.model.program))]
-            logits = self.model.forward(ctx, caches, logit_rows)
-        except Exception:
-            for entry in entries:
-                self.cache.trim_reservation(entry.handle)
-            raise
-        for entry in entries:
-            self.cache.commit(entry.handle, len(entry.tokens))
-        self.steps_run += 1
-        return logits
-
-    def check_device_errors(self) -> None:
-        """Reads the device-side error word (a synchronisation) and raises if a kernel
-        skipped an access."""
-        ops.raise_on_error_word(self.error_word)
-
-    # ------------------------------------------------------------------ checks
-    def _validate(self, entries: Sequence[StepEntry]) -> None:
-        seen = set()
-        for entry in entries:
-            handle = entry.handle
-            if handle.closed:
-                raise StepInputError(f"request {handle.request_id!r} has ended")
-            if id(handle) in seen:
-                raise StepInputError(f"request {handle.request_id!r} appears twice in one step")
-            seen.add(id(handle))
-            count = len(entry.tokens)
-            if count == 0:
-                raise StepInputError(f"request {handle.request_id!r} brings no tokens")
-            if handle.length + count > self.model.max_positions:
-                raise StepInputError(
-                    f"request {handle.request_id!r}: position {handle.length + count - 1} exceeds "
-                    f"max_position_embeddings {self.model.max_positions}")
-            for token in entry.tokens:
-                if not 0 <= int(token) < self.model.vocab_size:
-                    raise StepInputError(f"request {handle.request_id!r}: token id {token} is outside the "
-                                         f"vocabulary of {self.model.vocab_size}")
-            for index in entry.want:
-                if not 0 <= int(index) < count:
-                    raise StepInputError(f"request {handle.request_id!r}: wanted row {index} is not among its "
-                                         f"{count} tokens")
+        self.last_upload_bytes = 0
 
     # ------------------------------------------------------------------ flattening
-    def _flatten(self, entries: Sequence[StepEntry]):
+    def flatten(self, entries: Sequence[StepEntry]):
         # decoded tokens first, portions after them: each kind is one contiguous row range
         order = sorted(range(len(entries)),
                        key=lambda i: (len(entries[i].tokens) > self.SPLIT_ROWS_PER_REQUEST, i))
@@ -230,6 +166,7 @@ class ModelRunner:
         view = staging.numpy()
         for piece, offset, size in zip(pieces, offsets, sizes):
             view[offset:offset + size] = piece
+        self.last_upload_bytes = total * 4
         on_device = staging.to(self.device, non_blocking=True)
         return [on_device[offset:offset + size] for offset, size in zip(offsets[:-1], sizes)]
 
@@ -261,3 +198,79 @@ class ModelRunner:
             current = torch.empty(max(floats, 1), dtype=torch.float32, device=self.device)
             self._scratch[name] = current
         return current
+
+
+class ModelRunner:
+    def __init__(self, model, cache: CacheManager):
+        if model.device is None:
+            raise RuntimeError("the model has no weights yet")
+        if model.device.type != "cuda":
+            raise RuntimeError("the engine runs on a CUDA device only; there is no host path")
+        self.model, self.cache = model, cache
+        self.device, self.dtype = model.device, model.dtype
+        widths = [layer.split_scratch() for layer in model.layers if hasattr(layer, "split_scratch")]
+        self.planner = StepPlanner(cache, self.device, self.dtype, widths)
+        self.error_word = self.planner.error_word
+        self.steps_run = 0
+
+    # ------------------------------------------------------------------ the step
+    def step(self, entries: Sequence[StepEntry]) -> Optional[torch.Tensor]:
+        """Runs one batch.  Returns logits [wanted rows, vocab] (float32, on the device) in
+        the order of ``entries`` and of each entry's ``want``, or None if none is wanted."""
+        entries = [entry for entry in entries]
+        if not entries:
+            return None
+        self._validate(entries)
+        reserved: List[StepEntry] = []
+        try:
+            for entry in entries:
+                self.cache.reserve(entry.handle, len(entry.tokens))
+                reserved.append(entry)
+        except OutOfPages:
+            for entry in reserved:
+                self.cache.trim_reservation(entry.handle)
+            raise
+        try:
+            ctx, logit_rows = self.planner.flatten(entries)
+            caches = [self.cache.layer_cache(i) for i in range(len(self.model.program))]
+            logits = self.model.forward(ctx, caches, logit_rows)
+        except Exception:
+            for entry in entries:
+                self.cache.trim_reservation(entry.handle)
+            raise
+        for entry in entries:
+            self.cache.commit(entry.handle, len(entry.tokens))
+        self.steps_run += 1
+        return logits
+
+    def check_device_errors(self) -> None:
+        """Reads the device-side error word (a synchronisation) and raises if a kernel
+        skipped an access."""
+        ops.raise_on_error_word(self.error_word)
+
+    # ------------------------------------------------------------------ checks
+    def _validate(self, entries: Sequence[StepEntry]) -> None:
+        seen = set()
+        for entry in entries:
+            handle = entry.handle
+            if handle.closed:
+                raise StepInputError(f"request {handle.request_id!r} has ended")
+            if id(handle) in seen:
+                raise StepInputError(f"request {handle.request_id!r} appears twice in one step")
+            seen.add(id(handle))
+            count = len(entry.tokens)
+            if count == 0:
+                raise StepInputError(f"request {handle.request_id!r} brings no tokens")
+            if handle.length + count > self.model.max_positions:
+                raise StepInputError(
+                    f"request {handle.request_id!r}: position {handle.length + count - 1} exceeds "
+                    f"max_position_embeddings {self.model.max_positions}")
+            for token in entry.tokens:
+                if not 0 <= int(token) < self.model.vocab_size:
+                    raise StepInputError(f"request {handle.request_id!r}: token id {token} is outside the "
+                                         f"vocabulary of {self.model.vocab_size}")
+            for index in entry.want:
+                if not 0 <= int(index) < count:
+                    raise StepInputError(f"request {handle.request_id!r}: wanted row {index} is not among its "
+                                         f"{count} tokens")
+

@@ -46,7 +46,13 @@ def _need(tensor: torch.Tensor, name: str, dtype: Optional[torch.dtype] = None) 
         raise KernelError(f"{name} must be {dtype}, found {tensor.dtype}")
 
 
-def _check(library, status: int) -> None:
+#: kernels of this package launched so far (the bench reports the count of a timed region)
+launch_count = 0
+
+
+def _check(library, status: int, launches: int = 1) -> None:
+    global launch_count
+    launch_count += launches
     if status != 0:
         raise KernelError(library.srb_last_error().decode("utf-8", "replace") or f"kernel status {status}")
 
@@ -196,7 +202,7 @@ def paged_attention(q: torch.Tensor, k_pool: torch.Tensor, v_pool: torch.Tensor,
         _ptr(q), _ptr(k_pool), _ptr(v_pool), _ptr(out), _ptr(scratch_acc), _ptr(scratch_ml), _ptr(positions),
         _ptr(row_request), _ptr(block_table), block_table.stride(0), rows, n_q, n_kv, head_dim, page_size,
         num_pages, int(window), int(split_size), int(max_splits), ctypes.c_float(scale), _ptr(error_word),
-        dtype_code(q.dtype), _stream()))
+        dtype_code(q.dtype), _stream()), launches=2 if split_size else 1)
 
 
 # --------------------------------------------------------------------------- matrix products

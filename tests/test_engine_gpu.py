@@ -1,0 +1,430 @@
+"""Generation through the entry point, long decoding, the first tokens of a sequence, each
+part alone, and an architecture defined here (a mixer with state of its own, layers of
+different kinds, a layer called twice, a layer that reads another layer's cache) that is
+registered, built and stepped without a change to the framework's files."""
+import json
+import math
+import os
+import subprocess
+import sys
+
+import numpy as np
+import pytest
+import torch
+
+import plain_model as pm
+import replay_helpers as rh
+
+pytestmark = pytest.mark.gpu
+DEV = "cuda"
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+def plain_greedy_margin(config, weights, prompt, got, limit):
+    """Every generated token is the plain argmax, or (bfloat16) within ``limit`` of it."""
+    tokens = list(prompt)
+    for token in got:
+        logits = pm.plain_forward(config, weights, tokens)[-1]
+        best = int(torch.argmax(logits))
+        assert float(logits[best] - logits[token]) <= limit * float(logits.abs().max()), (prompt[:4], got, token, best)
+        tokens.append(token)
+
+
+# ------------------------------------------------------------------------------ generation
+@pytest.mark.parametrize("dtype_name,stored,limit", [("float32", torch.float32, 0.0), ("bfloat16", torch.bfloat16, 3e-2)])
+@pytest.mark.parametrize("config,page,chunk,pool", [(pm.TINY_A, 16, 16, 512), (pm.TINY_B, 8, 16, 160), (pm.TINY_C, 16, 50, 400)])
+def test_greedy_generation_through_the_entry_point(tmp_path, config, page, chunk, pool, dtype_name, stored, limit):
+    from sglang_rs_b200 import Engine
+    folder = rh.make_folder(tmp_path, "m", config, seed=21, dtype=stored)
+    cfg, weights = pm.load_folder(folder)
+    lengths = (5, 17, 33, 64) if config is not pm.TINY_B else (7, 40, 90)
+    prompts = list(rh.random_requests(config, lengths, seed=8).values())
+    engine = Engine(model_path=folder, dtype=dtype_name, page_size=page, max_total_tokens=pool,
+                    max_running_requests=3, chunked_prefill_size=chunk)
+    results = engine.generate(prompts, {"max_new_tokens": 16})
+    for prompt, result in zip(prompts, results):
+        assert result["finished"] and result["finish_reason"] == "length" and len(result["output_ids"]) == 16
+        plain_greedy_margin(cfg, weights, prompt, result["output_ids"], limit)
+    if dtype_name == "float32":
+        assert [r["output_ids"] for r in results] == [pm.plain_greedy(cfg, weights, p, 16) for p in prompts]
+    # the same prompts one at a time, with another budget: the same tokens
+    again = Engine(model_path=folder, dtype=dtype_name, page_size=page, max_total_tokens=pool,
+                   max_running_requests=1, chunked_prefill_size=7)
+    if dtype_name == "float32":
+        assert [again.generate(p, {"max_new_tokens": 16})["output_ids"] for p in prompts] == [r["output_ids"] for r in results]
+    engine.cache.check_invariants()
+    assert all(a.free_count == a.num_pages for a in engine.cache.allocators.values())
+
+
+def test_preemption_on_a_small_pool_gives_the_same_tokens(tmp_path):
+    from sglang_rs_b200 import Engine
+    folder = rh.make_folder(tmp_path, "m", pm.TINY_A, seed=4, dtype=torch.float32)
+    cfg, weights = pm.load_folder(folder)
+    prompts = list(rh.random_requests(pm.TINY_A, (40, 35, 50), seed=2).values())
+    engine = Engine(model_path=folder, dtype="float32", page_size=16, max_total_tokens=160, max_running_requests=3,
+                    chunked_prefill_size=64)
+    results = engine.generate(prompts, {"max_new_tokens": 40})
+    assert engine.scheduler.stats["preemptions"] >= 1
+    assert [r["output_ids"] for r in results] == [pm.plain_greedy(cfg, weights, p, 40) for p in prompts]
+
+
+def test_temperature_sampling_is_seeded_and_independent_of_the_batch(tmp_path):
+    from sglang_rs_b200 import Engine
+    folder = rh.make_folder(tmp_path, "m", pm.TINY_B, seed=6, dtype=torch.float32)
+    prompts = list(rh.random_requests(pm.TINY_B, (7, 40, 24), seed=5).values())
+    params = [{"max_new_tokens": 20, "temperature": 0.7, "seed": 100 + i} for i in range(3)]
+    engine = Engine(model_path=folder, dtype="float32", page_size=8, max_total_tokens=400, chunked_prefill_size=16)
+    together = [r["output_ids"] for r in engine.generate(prompts, params)]
+    alone = [engine.generate(p, q)["output_ids"] for p, q in zip(prompts, params)]
+    assert together == alone
+    other = engine.generate(prompts[0], dict(params[0], seed=999))["output_ids"]
+    assert other != together[0]
+    # every sampled token is what the plain sampler picks from the plain logits with the same uniform number
+    from sglang_rs_b200.sampling import RequestRandom
+    cfg, weights = pm.load_folder(folder)
+    rng = RequestRandom("x", 100)
+    tokens = list(prompts[0])
+    for token in together[0]:
+        logits = pm.plain_forward(cfg, weights, tokens)[-1]
+        u = rng.next_unit()
+        want = pm.plain_temperature_sample(logits, 0.7, float(np.float32(u)))
+        if token != want:       # only a tie of the running sum at rounding may move the pick by one place
+            p = torch.softmax(logits / 0.7, 0)
+            assert abs(token - want) == 1 and abs(float(torch.cumsum(p, 0)[min(token, want)]) - u) < 1e-4
+        tokens.append(token)
+
+
+def test_stop_tokens_top_k_and_penalties(tmp_path):
+    from sglang_rs_b200 import Engine
+    folder = rh.make_folder(tmp_path, "m", pm.TINY_A, seed=9, dtype=torch.float32)
+    cfg, weights = pm.load_folder(folder)
+    prompt = list(rh.random_requests(pm.TINY_A, (12,), seed=1).values())[0]
+    greedy = pm.plain_greedy(cfg, weights, prompt, 8)
+    engine = Engine(model_path=folder, dtype="float32", max_total_tokens=256)
+    stopped = engine.generate(prompt, {"max_new_tokens": 8, "stop_token_ids": [greedy[3]]})
+    first = greedy.index(greedy[3])
+    assert stopped["output_ids"] == greedy[:first + 1] and stopped["finish_reason"] == "stop"
+    ignored = engine.generate(prompt, {"max_new_tokens": 8, "stop_token_ids": [greedy[3]], "ignore_eos": True})
+    assert ignored["output_ids"] == greedy
+    assert engine.generate(prompt, {"max_new_tokens": 8, "temperature": 1.0, "top_k": 1})["output_ids"] == greedy
+    # top-k 3: every token is among the three best of the plain logits
+    out = engine.generate(prompt, {"max_new_tokens": 12, "temperature": 1.5, "top_k": 3, "seed": 5})["output_ids"]
+    tokens = list(prompt)
+    for token in out:
+        logits = pm.plain_forward(cfg, weights, tokens)[-1]
+        assert token in torch.topk(logits, 3).indices.tolist()
+        tokens.append(token)
+    # a strong repetition penalty: the penalised greedy path of the plain implementation
+    out = engine.generate(prompt, {"max_new_tokens": 10, "repetition_penalty": 1.8, "presence_penalty": 0.5,
+                                   "frequency_penalty": 0.3})["output_ids"]
+    tokens = list(prompt)
+    for token in out:
+        logits = pm.plain_apply_penalties(pm.plain_forward(cfg, weights, tokens)[-1], tokens, 0.3, 0.5, 1.8)
+        assert token == int(torch.argmax(logits))
+        tokens.append(token)
+    with pytest.raises(ValueError, match="outside the vocabulary"):
+        engine.generate([1, 2, 99999], {"max_new_tokens": 2})
+
+
+def test_command_line(tmp_path):
+    folder = rh.make_folder(tmp_path, "m", pm.TINY_A, seed=3, dtype=torch.float32)
+    cfg, weights = pm.load_folder(folder)
+    process = subprocess.run(
+        [sys.executable, os.path.join(ROOT, "bin", "sglang-rs"), "generate", f"--model-path={folder}", "--device", "cuda",
+         "--dtype", "float32", "--input-ids", "5,17,3", "--input-ids", "9 8 7 6", "--max-new-tokens", "5",
+         "--max-total-tokens", "256", "--some-unknown-flag"],
+        capture_output=True, text=True, timeout=600)
+    assert process.returncode == 0, process.stderr[-2000:]
+    lines = [json.loads(line) for line in process.stdout.strip().splitlines()]
+    assert [l["input_ids"] for l in lines] == [[5, 17, 3], [9, 8, 7, 6]]
+    assert [l["output_ids"] for l in lines] == [pm.plain_greedy(cfg, weights, p, 5) for p in ([5, 17, 3], [9, 8, 7, 6])]
+    refused = subprocess.run([sys.executable, os.path.join(ROOT, "bin", "sglang-rs"), "generate", "--model-path", folder,
+                              "--device", "cpu", "--input-ids", "1"], capture_output=True, text=True, timeout=600)
+    assert refused.returncode != 0 and "CUDA only" in refused.stderr
+
+
+# ------------------------------------------------------------------------------ long decoding, first tokens
+@pytest.mark.parametrize("dtype_name,stored,tolerance", [("float32", torch.float32, rh.FP32_TOLERANCE),
+                                                         ("bfloat16", torch.bfloat16, rh.BF16_TOLERANCE)])
+def test_long_decoding_and_first_tokens(tmp_path, dtype_name, stored, tolerance):
+    """A prompt of two tokens, then 600 tokens decoded one by one (three key splits, many
+    pages); beside it a request whose every position from the very first is checked."""
+    folder = rh.make_folder(tmp_path, "m", pm.TINY_C, seed=13, dtype=stored)
+    requests = rh.random_requests(pm.TINY_C, (602, 9), seed=17)
+    expected = rh.oracle(folder, requests)
+    long, short = requests["r0"], requests["r1"]
+    trace = [{"entries": [{"id": "r0", "tokens": long[:2], "want": [0, 1]}], "end": []}]
+    for p in range(2, len(long)):
+        entries = [{"id": "r0", "tokens": [long[p]], "want": [0]}]
+        if p - 2 < len(short):
+            entries.append({"id": "r1", "tokens": [short[p - 2]], "want": [0]})     # token by token from position 0
+        trace.append({"entries": entries, "end": ["r1"] if p - 2 == len(short) - 1 else []})
+    trace[-1]["end"] = ["r0"]
+    for i, step in enumerate(trace):
+        step["step"] = i
+    rows, _ = rh.run_in_process(folder, dtype_name, trace)
+    bad = rh.first_bad(rows, expected, tolerance)
+    print("long decoding:", rh.worst_error(rows, expected))
+    assert bad is None, bad
+    assert len(rows["r0"]) == 602 and len(rows["r1"]) == 9
+
+
+# ------------------------------------------------------------------------------ parts alone
+def part_context(needs, entries_tokens, dtype, page_size=8, scratch=()):
+    """A cache manager and a flattened step for single parts: ``entries_tokens`` is a list of
+    (request id, start length, token count)."""
+    from sglang_rs_b200.cache import CacheManager
+    from sglang_rs_b200.engine import StepEntry, StepPlanner
+    cache = CacheManager(needs, page_size=page_size, max_tokens=1024, max_requests=8, device=DEV, dtype=dtype)
+    planner = StepPlanner(cache, DEV, dtype, scratch)
+    return cache, planner
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_parts_alone(dtype):
+    from sglang_rs_b200.engine import StepEntry
+    from sglang_rs_b200.parts import (AttentionNames, GatedMlp, GatedMlpNames, GroupedQueryAttention, OutputHead,
+                                      PreNormBlock, RmsNorm, RotaryEncoding, TokenEmbedding)
+    g = torch.Generator().manual_seed(0)
+    tol = 1e-5 if dtype == torch.float32 else 2e-2
+    hidden, inner, n_q, n_kv, d, vocab, eps, theta = 40, 56, 6, 2, 16, 77, 1e-5, 777.0
+
+    def seen(t):
+        return t.to(dtype).double()
+
+    def close(got, want, what):
+        err = float((got.double().cpu() - want).abs().max() / want.abs().max())
+        assert err <= tol, f"{what}: {err:.3e}"
+
+    w = {"n1": 1 + 0.1 * torch.randn(hidden, generator=g), "n2": 1 + 0.1 * torch.randn(hidden, generator=g),
+         "q": torch.randn(n_q * d, hidden, generator=g) * 0.2, "k": torch.randn(n_kv * d, hidden, generator=g) * 0.2,
+         "v": torch.randn(n_kv * d, hidden, generator=g) * 0.2, "o": torch.randn(hidden, n_q * d, generator=g) * 0.2,
+         "qn": 1 + 0.1 * torch.randn(d, generator=g), "kn": 1 + 0.1 * torch.randn(d, generator=g),
+         "gate": torch.randn(inner, hidden, generator=g) * 0.2, "up": torch.randn(inner, hidden, generator=g) * 0.2,
+         "down": torch.randn(hidden, inner, generator=g) * 0.2, "emb": torch.randn(vocab, hidden, generator=g),
+         "head": torch.randn(vocab, hidden, generator=g) * 0.2}
+    norm1, norm2 = RmsNorm(hidden, eps, "n1"), RmsNorm(hidden, eps, "n2")
+    rope = RotaryEncoding(d, theta)
+    attention = GroupedQueryAttention(hidden, n_q, n_kv, d, 1 / math.sqrt(d), rope,
+                                      AttentionNames("q", "k", "v", "o", "qn", "kn"), qk_norm_eps=eps)
+    mlp = GatedMlp(hidden, inner, "silu", GatedMlpNames("gate", "up", "down"))
+    block = PreNormBlock(norm1, attention, norm2, mlp)
+    embedding = TokenEmbedding(vocab, hidden, "emb")
+    head, tied = OutputHead(vocab, hidden, "head"), OutputHead(vocab, hidden, None, embedding)
+    assert set(block.tensor_specs()) == {"n1", "n2", "q", "k", "v", "o", "qn", "kn", "gate", "up", "down"}
+    for part in (block, embedding, head, tied):
+        part.load(w, DEV, dtype)
+
+    # rotary table: theta^(-2i/d) in 64-bit
+    assert torch.equal(rope.fused_rotary().inv_freq.cpu(), pm.plain_inverse_frequencies(theta, d))
+
+    # norm alone, with the pending sum
+    residual, delta = torch.randn(5, hidden, generator=g), torch.randn(5, hidden, generator=g)
+    res_d = residual.to(DEV)
+    out = norm1.add_norm(res_d, delta.to(DEV, dtype), dtype)
+    close(out, pm.plain_rms_norm(residual.double() + seen(delta), w["n1"].double(), eps), "norm")
+
+    # feed-forward alone
+    x = torch.randn(7, hidden, generator=g)
+    mw = {k: seen(v) for k, v in w.items()}
+    want = pm.plain_linear(pm.plain_silu_mul(pm.plain_linear(seen(x), mw["gate"]), pm.plain_linear(seen(x), mw["up"])), mw["down"])
+    close(mlp.forward(None, x.to(DEV, dtype)), want, "mlp")
+
+    # embedding and heads alone
+    cache, planner = part_context([attention.cache_need()], None, dtype, scratch=[attention.split_scratch()])
+    handle = cache.open("a")
+    tokens = [3, 76, 0, 3, 19, 54, 8, 8, 41, 2, 33]
+    cache.reserve(handle, len(tokens))
+    ctx, _ = planner.flatten([StepEntry(handle, tokens, [])])
+    emb = embedding.forward(ctx, ctx.token_ids)
+    assert torch.equal(emb.cpu().double(), mw["emb"][tokens])
+    close(head.forward(ctx, x.to(DEV, dtype)), pm.plain_linear(seen(x), mw["head"]), "head")
+    close(tied.forward(ctx, x.to(DEV, dtype)), pm.plain_linear(seen(x), mw["emb"]), "tied head")
+    assert head.forward(ctx, x.to(DEV, dtype)).dtype == torch.float32
+
+    # attention alone: 11 tokens in one step, then 2 and 1 more, against the whole sequence
+    def plain_attn(xs):
+        pos = torch.arange(len(xs))
+        q = pm.plain_rms_norm(pm.plain_linear(xs, mw["q"]).view(-1, n_q, d), w["qn"].double(), eps)
+        k = pm.plain_rms_norm(pm.plain_linear(xs, mw["k"]).view(-1, n_kv, d), w["kn"].double(), eps)
+        v = pm.plain_linear(xs, mw["v"]).view(-1, n_kv, d)
+        inv = pm.plain_inverse_frequencies(theta, d)
+        a = pm.plain_attention(pm.plain_rope_neox(q, pos, inv), pm.plain_rope_neox(k, pos, inv), v, 1 / math.sqrt(d))
+        return pm.plain_linear(a.reshape(len(xs), -1), mw["o"])
+
+    xs = torch.randn(14, hidden, generator=g)
+    want = plain_attn(seen(xs))
+    layer_cache = cache.layer_cache(0)
+    got = [attention.forward(ctx, layer_cache, xs[:11].to(DEV, dtype))]
+    cache.commit(handle, 11)
+    for begin, end in ((11, 13), (13, 14)):
+        cache.reserve(handle, end - begin)
+        ctx, _ = planner.flatten([StepEntry(handle, [1] * (end - begin), [])])
+        got.append(attention.forward(ctx, layer_cache, xs[begin:end].to(DEV, dtype)))
+        cache.commit(handle, end - begin)
+    close(torch.cat(got), want, "attention")
+
+    # the block alone: (residual, delta) in, (residual, delta) out
+    other = cache.open("b")
+    cache.reserve(other, 6)
+    ctx, _ = planner.flatten([StepEntry(other, [1] * 6, [])])
+    h = torch.randn(6, hidden, generator=g)
+    res, dlt = block.forward(ctx, layer_cache, h.to(DEV).clone(), None)
+    a = plain_attn(pm.plain_rms_norm(h.double(), w["n1"].double(), eps).to(dtype).double())
+    mid = h.double() + a
+    normed = pm.plain_rms_norm(mid, w["n2"].double(), eps)
+    ff = pm.plain_linear(pm.plain_silu_mul(pm.plain_linear(normed, mw["gate"]), pm.plain_linear(normed, mw["up"])), mw["down"])
+    close(res.double() + dlt.double(), mid + ff, "block")
+    planner_error = planner.error_word
+    from sglang_rs_b200 import ops
+    ops.raise_on_error_word(planner_error)
+
+
+# ------------------------------------------------------------------------------ an architecture defined here
+TOY = {"architectures": ["ToyHybridForTests"], "hidden": 48, "vocab": 90, "heads": 4, "kv_heads": 2, "head_dim": 16,
+       "inner": 64, "eps": 1e-5, "theta": 3000.0, "window": 11, "decay": 0.8, "max_positions": 400}
+
+
+def register_toy():
+    """Everything the toy needs is defined here; the framework's files are not touched."""
+    from sglang_rs_b200 import ops
+    from sglang_rs_b200.config import register_architecture
+    from sglang_rs_b200.models import DecoderModel, LayerCall
+    from sglang_rs_b200.parts import (AttentionNames, GatedMlp, GatedMlpNames, GroupedQueryAttention, Mixer,
+                                      NoPositionEncoding, OutputHead, PreNormBlock, RequestState, RmsNorm,
+                                      RotaryEncoding, TensorSpec, TokenEmbedding, matrix_to)
+
+    class DecayingSumMixer(Mixer):
+        """s_t = decay * s_{t-1} + W x_t; y_t = s_t.  The state s lives in the request's slot."""
+
+        def __init__(self, hidden, decay, weight_name):
+            self.hidden, self.decay, self.weight_name = hidden, decay, weight_name
+
+        def cache_need(self):
+            return RequestState((self.hidden,), torch.float32)
+
+        def tensor_specs(self):
+            return {self.weight_name: TensorSpec((self.hidden, self.hidden))}
+
+        def load(self, tensors, device, dtype):
+            self.w = matrix_to(tensors[self.weight_name], device, dtype)
+
+        def forward(self, ctx, cache, x):
+            v = ops.linear(x, self.w).float()
+            out = torch.empty_like(v)
+            for r in range(ctx.num_requests):
+                slot = ctx.host_state_slots[r]
+                s = cache.state[slot].clone()
+                for t in range(ctx.host_cu_rows[r], ctx.host_cu_rows[r + 1]):
+                    s = self.decay * s + v[t]
+                    out[t] = s
+                cache.state[slot] = s
+            return out.to(x.dtype)
+
+    def build(cfg):
+        h = cfg["hidden"]
+
+        def attn(i, window, position):
+            p = f"layers.{i}"
+            return GroupedQueryAttention(h, cfg["heads"], cfg["kv_heads"], cfg["head_dim"], 1 / math.sqrt(cfg["head_dim"]),
+                                         position, AttentionNames(f"{p}.q", f"{p}.k", f"{p}.v", f"{p}.o", f"{p}.qn", f"{p}.kn"),
+                                         qk_norm_eps=cfg["eps"], window=window)
+
+        def block(i, mixer):
+            p = f"layers.{i}"
+            return PreNormBlock(RmsNorm(h, cfg["eps"], f"{p}.n1"), mixer, RmsNorm(h, cfg["eps"], f"{p}.n2"),
+                                GatedMlp(h, cfg["inner"], "silu", GatedMlpNames(f"{p}.gate", f"{p}.up", f"{p}.down")))
+
+        rope = lambda: RotaryEncoding(cfg["head_dim"], cfg["theta"])  # noqa: E731
+        layers = [block(0, DecayingSumMixer(h, cfg["decay"], "layers.0.mix")), block(1, attn(1, None, rope())),
+                  block(2, attn(2, cfg["window"], NoPositionEncoding())), block(3, attn(3, None, rope()))]
+        # layer 1 runs twice (two caches, one set of weights); layer 3 reads the cache of the first call of layer 1
+        program = [LayerCall(0), LayerCall(1), LayerCall(2), LayerCall(1), LayerCall(3, cache_from=1)]
+        embedding = TokenEmbedding(cfg["vocab"], h, "embed")
+        return DecoderModel(embedding, layers, RmsNorm(h, cfg["eps"], "norm"), OutputHead(cfg["vocab"], h, "head"),
+                            vocab_size=cfg["vocab"], max_positions=cfg["max_positions"], program=program)
+
+    register_architecture("ToyHybridForTests", lambda raw: dict(raw.document), build, replace=True)
+
+
+def plain_toy_forward(cfg, weights, tokens):
+    """The toy's whole-sequence reference, from the plain implementation's functions."""
+    w = {k: v.double() for k, v in weights.items()}
+    n_q, n_kv, d, eps = cfg["heads"], cfg["kv_heads"], cfg["head_dim"], cfg["eps"]
+    pos = torch.arange(len(tokens))
+    inv = pm.plain_inverse_frequencies(cfg["theta"], d)
+    h = w["embed"][torch.tensor(tokens)]
+    kept = {}
+
+    def attn(i, x, window, rotate, call, reuse=None):
+        p = f"layers.{i}"
+        q = pm.plain_rms_norm(pm.plain_linear(x, w[f"{p}.q"]).view(-1, n_q, d), w[f"{p}.qn"], eps)
+        if rotate:
+            q = pm.plain_rope_neox(q, pos, inv)
+        if reuse is None:
+            k = pm.plain_rms_norm(pm.plain_linear(x, w[f"{p}.k"]).view(-1, n_kv, d), w[f"{p}.kn"], eps)
+            if rotate:
+                k = pm.plain_rope_neox(k, pos, inv)
+            v = pm.plain_linear(x, w[f"{p}.v"]).view(-1, n_kv, d)
+            kept[call] = (k, v)
+        else:
+            k, v = kept[reuse]
+        a = pm.plain_attention(q, k, v, 1 / math.sqrt(d), window=window)
+        return pm.plain_linear(a.reshape(len(x), -1), w[f"{p}.o"])
+
+    def mixer0(x):
+        v = pm.plain_linear(x, w["layers.0.mix"])
+        out, s = [], torch.zeros(cfg["hidden"], dtype=torch.float64)
+        for t in range(len(x)):
+            s = cfg["decay"] * s + v[t]
+            out.append(s)
+        return torch.stack(out)
+
+    calls = [(0, lambda x: mixer0(x)), (1, lambda x: attn(1, x, None, True, 1)),
+             (2, lambda x: attn(2, x, cfg["window"], False, 2)), (1, lambda x: attn(1, x, None, True, 3)),
+             (3, lambda x: attn(3, x, None, True, 4, reuse=1))]
+    for layer, mix in calls:
+        p = f"layers.{layer}"
+        h = h + mix(pm.plain_rms_norm(h, w[f"{p}.n1"], eps))
+        n = pm.plain_rms_norm(h, w[f"{p}.n2"], eps)
+        h = h + pm.plain_linear(pm.plain_silu_mul(pm.plain_linear(n, w[f"{p}.gate"]), pm.plain_linear(n, w[f"{p}.up"])), w[f"{p}.down"])
+    return pm.plain_linear(pm.plain_rms_norm(h, w["norm"], eps), w["head"])
+
+
+@pytest.mark.parametrize("dtype_name,stored,tolerance", [("float32", torch.float32, rh.FP32_TOLERANCE),
+                                                         ("bfloat16", torch.bfloat16, rh.BF16_TOLERANCE)])
+def test_an_architecture_defined_in_the_test(tmp_path, dtype_name, stored, tolerance):
+    from sglang_rs_b200.cache import CacheManager
+    from sglang_rs_b200.config import unregister_architecture
+    from sglang_rs_b200.parts import PagedKV, RequestState
+    from sglang_rs_b200.weights import read_model_dir, write_model_folder
+    register_toy()
+    try:
+        folder = write_model_folder(str(tmp_path / "toy"), TOY, seed=5, dtype=stored)      # the random-weights mode knows it too
+        weights = {k: v.float() for k, v in read_model_dir(folder).items()}
+        requests = rh.random_requests({"vocab_size": TOY["vocab"]}, (70, 33, 150, 9, 41), seed=4)
+        expected = {rid: plain_toy_forward(TOY, weights, toks).numpy() for rid, toks in requests.items()}
+        for make_trace in (rh.trace_whole, rh.trace_portions, lambda r: rh.trace_mixed(r, seed=3)):
+            trace = make_trace(requests)
+            rows, session = rh.run_in_process(folder, dtype_name, trace)
+            bad = rh.first_bad(rows, expected, tolerance)
+            print("toy:", rh.worst_error(rows, expected))
+            assert bad is None, bad
+        needs = session.model.cache_needs()
+        assert isinstance(needs[0], RequestState) and needs[4] is None and needs[2] == PagedKV(2, 16, 11)
+        assert set(session.cache.allocators) == {("kv", None), ("kv", 11)}
+        # generation through the scheduler works for it as well
+        from sglang_rs_b200 import Engine
+        engine = Engine(model_path=folder, dtype=dtype_name, max_total_tokens=512, chunked_prefill_size=16,
+                        max_running_requests=4)
+        prompts = [requests["r1"], requests["r3"]]
+        results = engine.generate(prompts, {"max_new_tokens": 6})
+        for prompt, result in zip(prompts, results):
+            tokens = list(prompt)
+            for token in result["output_ids"]:
+                logits = torch.from_numpy(plain_toy_forward(TOY, weights, tokens).numpy()[-1])
+                limit = (0.0 if dtype_name == "float32" else 3e-2) * float(logits.abs().max())
+                assert float(logits.max() - logits[token]) <= limit
+                tokens.append(token)
+    finally:
+        unregister_architecture("ToyHybridForTests")
