@@ -137,7 +137,8 @@ def main() -> int:
     torch.manual_seed(0)
 
     def make_engine(batch: int, steps: int) -> Engine:
-        tokens = batch * (args.context + steps + warmup + 8 + 64)
+        # while later prompts are still computed, earlier requests already decode: leave room for that
+        tokens = batch * (args.context + 2 * (steps + warmup) + batch + 64)
         return Engine(config=config, random_weights=True, seed=0, dtype="bfloat16", page_size=16,
                       max_total_tokens=max(tokens, PREFILL_TOKENS + 64), max_running_requests=max(batch, 1),
                       chunked_prefill_size=2048)
@@ -192,9 +193,11 @@ def main() -> int:
         clocks = sampler.stop() if sample_clocks else None
         step_ms = begin.elapsed_time(end) / steps
         launches = ops.launch_count - launches_before
-        context_mid = handles[0].length - steps / 2
+        context_mid = sum(h.length for h in handles) / len(handles) - steps / 2
         for h in handles:
             engine.cache.close(h)
+        print(f"[bench] batch {batch}: step {step_ms:.3f} ms, entry point {e2e_ms:.3f} ms, context {context_mid:.0f}",
+              file=sys.stderr, flush=True)
         return {"step_ms": step_ms, "e2e_ms": e2e_ms, "h2d": h2d, "d2h": 4 * batch, "launches": launches,
                 "context": context_mid, "clocks": clocks}
 
@@ -237,6 +240,7 @@ def main() -> int:
             if i >= warmup:
                 times.append(begin.elapsed_time(end))
         ms = min(times)
+        print(f"[bench] prefill {PREFILL_TOKENS} tokens: {ms:.2f} ms", file=sys.stderr, flush=True)
         flops = prefill_flops(config, PREFILL_TOKENS)
         record["prefill"] = {"value": round(PREFILL_TOKENS * 1e3 / ms, 1), "tokens": PREFILL_TOKENS, "ms": round(ms, 3),
                              "frac": round(flops / (ms * 1e-3) / (peak["bf16_tflops"] * 1e12), 4),
