@@ -127,6 +127,12 @@ def compile_library(name: str) -> str:
                     os.remove(partial)
                 raise KernelBuildError(f"nvcc failed for {name}.cu:\n{' '.join(command)}\n{output}")
             os.replace(partial, target)
+            for stale in os.listdir(os.path.dirname(target)):        # builds of older sources of this library
+                if stale.startswith(f"{name}-") and stale.endswith(".so") and stale != os.path.basename(target):
+                    try:
+                        os.remove(os.path.join(os.path.dirname(target), stale))
+                    except OSError:
+                        pass
             _say(f"compiled {name}.cu in {time.time() - started:.1f} s")
         finally:
             fcntl.flock(lock, fcntl.LOCK_UN)
