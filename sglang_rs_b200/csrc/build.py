@@ -30,7 +30,7 @@ NVCC_FLAGS: Sequence[str] = (
 )
 
 #: every library of the package; ``build_all`` compiles each of them
-LIBRARIES: Sequence[str] = ("elementwise", "rope_kv", "attention", "gemm_f32", "sampling")
+LIBRARIES: Sequence[str] = ("elementwise", "rope_kv", "attention", "gemm_f32", "sampling", "attention_noalloc")
 
 _loaded: Dict[str, ctypes.CDLL] = {}
 
