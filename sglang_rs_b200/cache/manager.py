@@ -173,7 +173,8 @@ class CacheManager:
                 key = group_key(need)
                 pools = (None, None)
                 if device is not None:
-                    shape = (self.allocators[key].num_pages, need.num_kv_heads, self.page_size, need.head_dim)
+                    # one page more than the allocator owns: rows that pad a captured step write there
+                    shape = (self.allocators[key].num_pages + 1, need.num_kv_heads, self.page_size, need.head_dim)
                     pools = (torch.zeros(shape, dtype=dtype, device=device),
                              torch.zeros(shape, dtype=dtype, device=device))
                 self.layer_caches.append(PagedLayerCache(key, *pools))

@@ -31,11 +31,12 @@ class Engine:
                  dtype: str = "bfloat16", device: str = "cuda", page_size: int = 16,
                  max_total_tokens: Optional[int] = None, mem_fraction_static: float = 0.85,
                  max_running_requests: int = 256, chunked_prefill_size: int = 2048,
-                 config: Optional[Mapping[str, Any]] = None, stop_token_ids: Optional[Sequence[int]] = None):
+                 config: Optional[Mapping[str, Any]] = None, stop_token_ids: Optional[Sequence[int]] = None,
+                 disable_cuda_graph: bool = False):
         """Option names follow the reference's server arguments where it has them
         (crates/sglang-srt/src/cli.rs:15-79: ``model_path``, ``device``, ``page_size``,
         ``max_total_tokens``, ``mem_fraction_static``, ``max_running_requests``,
-        ``chunked_prefill_size``).  ``config`` may stand in for the folder's config.json
+        ``chunked_prefill_size``, ``disable_cuda_graph``).  ``config`` may stand in for the folder's config.json
         together with ``random_weights``."""
         if not str(device).startswith("cuda"):
             raise ValueError(f"device {device!r}: this engine runs on CUDA only and never falls back to the host")
@@ -52,7 +53,7 @@ class Engine:
             max_total_tokens = max(page_size, min(max_total_tokens, max_running_requests * self.model.max_positions))
         self.cache = CacheManager(self.model.cache_needs(), page_size=page_size, max_tokens=max_total_tokens,
                                   max_requests=max_running_requests, device=self.device, dtype=self.dtype)
-        self.runner = ModelRunner(self.model, self.cache)
+        self.runner = ModelRunner(self.model, self.cache, use_cuda_graphs=not disable_cuda_graph)
         stops = tuple(stop_token_ids) if stop_token_ids is not None else tuple(self.model.eos_token_ids)
         self.scheduler = Scheduler(self.cache, SchedulerConfig(
             max_running_requests=max_running_requests, chunked_prefill_size=chunked_prefill_size,

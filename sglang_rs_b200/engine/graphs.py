@@ -1,0 +1,181 @@
+"""CUDA graphs for steps that hold decoded tokens only.
+
+A decode step is a few hundred small launches; replayed from a graph it costs one launch
+on the host.  A graph is captured per (row bucket, block-table width, key-split count per
+group) with every index array in one static device buffer that is refilled by one copy
+before each replay.  Rows beyond the live ones are padding: token 0 at position 0 whose
+key and value go to the pool's spare page (the page after the last one the allocator
+owns), so they touch nothing that lives.
+
+The kernels, their arithmetic and the split of the keys are those of the eager path.
+"""
+from __future__ import annotations
+
+from dataclasses import dataclass
+from typing import Dict, Hashable, List, Optional, Sequence, Tuple
+
+import numpy as np
+import torch
+
+from .. import ops
+from .runner import AttentionLaunch, PagedBatch, StepContext, StepEntry, StepPlanner
+
+
+def bucket_of(value: int, smallest: int = 1) -> int:
+    bucket = smallest
+    while bucket < value:
+        bucket *= 2
+    return bucket
+
+
+@dataclass
+class CapturedStep:
+    graph: torch.cuda.CUDAGraph
+    staging: torch.Tensor            # pinned int32, same layout as ``static``
+    static: torch.Tensor             # device int32
+    layout: Dict[str, Tuple[int, int]]
+    logits: torch.Tensor             # [bucket, vocab] float32, rewritten by every replay
+    keep: tuple                      # tensors the graph's kernels point at
+    copied: Optional[torch.cuda.Event] = None   # the last copy out of ``staging``
+
+
+class DecodeGraphs:
+    MAX_ROWS = 256
+
+    def __init__(self, model, cache, planner: StepPlanner):
+        self.model, self.cache, self.planner = model, cache, planner
+        self.device, self.dtype = planner.device, planner.dtype
+        self.captured: Dict[Hashable, CapturedStep] = {}
+        self.pool = None
+        self.replays = 0
+        self.kernels_per_replay: Dict[Hashable, int] = {}
+
+    def eligible(self, entries: Sequence[StepEntry]) -> bool:
+        return (0 < len(entries) <= self.MAX_ROWS
+                and all(len(e.tokens) == 1 and list(e.want) in ([], [0]) for e in entries))
+
+    # ------------------------------------------------------------------ one step
+    def run(self, entries: Sequence[StepEntry]) -> Optional[torch.Tensor]:
+        """Entries are validated and their pages reserved.  Returns logits of the entries
+        that want them, in order."""
+        rows = len(entries)
+        bucket = bucket_of(rows)
+        groups = list(self.cache.allocators)
+        page_size = self.cache.page_size
+        stride = bucket_of(max([len(e.handle.tables[key]) for e in entries for key in groups] + [1]), 8)
+        positions = np.fromiter((e.handle.length for e in entries), dtype=np.int64, count=rows)
+        splits = []
+        for key in groups:
+            window = self.cache.windows[key]
+            begin = np.maximum(0, positions + 1 - window) if window else np.zeros_like(positions)
+            size = StepPlanner.SPLIT_SIZE
+            splits.append(bucket_of(int((positions // size - begin // size + 1).max())))
+        key = (bucket, stride, tuple(splits))
+        step = self.captured.get(key)
+        if step is None:
+            step = self._prepare(key, groups)
+        if step.copied is not None:
+            step.copied.synchronize()        # the staging buffer is free again once its last copy has run
+        self._fill(step, entries, groups, bucket, stride, positions, page_size)
+        step.static.copy_(step.staging, non_blocking=True)
+        if step.copied is None:
+            step.copied = torch.cuda.Event()
+        step.copied.record()
+        if step.graph is None:
+            self._capture(key, step, groups, bucket, stride, splits)
+        step.graph.replay()
+        self.replays += 1
+        ops.launch_count += self.kernels_per_replay[key]
+        wanted = [i for i, e in enumerate(entries) if len(e.want)]
+        if not wanted:
+            return None
+        if len(wanted) == rows:
+            return step.logits[:rows]
+        return step.logits[torch.tensor(wanted, device=self.device)]
+
+    # ------------------------------------------------------------------ buffers
+    def _prepare(self, key, groups) -> CapturedStep:
+        bucket, stride, _ = key
+        layout, offset = {}, 0
+        for name, size in (("tokens", bucket), ("positions", bucket), ("row_request", bucket), ("cu_rows", bucket + 1),
+                           ("state_slots", bucket), ("logit_rows", bucket)):
+            layout[name] = (offset, size)
+            offset += (size + 3) // 4 * 4
+        for g in range(len(groups)):
+            layout[f"table{g}"] = (offset, bucket * stride)
+            offset += bucket * stride
+            layout[f"slots{g}"] = (offset, bucket)
+            offset += (bucket + 3) // 4 * 4
+        staging = torch.zeros(offset, dtype=torch.int32, pin_memory=True)
+        static = torch.zeros(offset, dtype=torch.int32, device=self.device)
+        step = CapturedStep(None, staging, static, layout, None, ())
+        self.captured[key] = step
+        return step
+
+    def _fill(self, step: CapturedStep, entries, groups, bucket, stride, positions, page_size) -> None:
+        rows = len(entries)
+        view = step.staging.numpy()
+
+        def part(name):
+            begin, size = step.layout[name]
+            return view[begin:begin + size]
+        tokens = part("tokens"); tokens[:] = 0
+        tokens[:rows] = [int(e.tokens[0]) for e in entries]
+        pos = part("positions"); pos[:] = 0
+        pos[:rows] = positions
+        part("row_request")[:] = np.arange(bucket)
+        part("cu_rows")[:] = np.arange(bucket + 1)
+        slots_of_state = part("state_slots"); slots_of_state[:] = 0
+        slots_of_state[:rows] = [e.handle.state_slot for e in entries]
+        part("logit_rows")[:] = np.arange(bucket)
+        for g, key in enumerate(groups):
+            spare = self.cache.allocators[key].num_pages          # the pool's page that no request owns
+            table = part(f"table{g}").reshape(bucket, stride)
+            table[:] = -1
+            table[rows:, 0] = spare
+            slots = part(f"slots{g}")
+            slots[:] = spare * page_size
+            for r, entry in enumerate(entries):
+                pages = entry.handle.tables[key]
+                table[r, :len(pages)] = pages
+                slots[r] = pages[positions[r] // page_size] * page_size + positions[r] % page_size
+
+    # ------------------------------------------------------------------ capture
+    def _context(self, step: CapturedStep, groups, bucket, stride, splits) -> Tuple[StepContext, torch.Tensor, list]:
+        def part(name):
+            begin, size = step.layout[name]
+            return step.static[begin:begin + size]
+        ctx = StepContext(self.device, self.dtype, bucket, bucket, part("tokens"), part("positions"),
+                          part("row_request"), part("cu_rows"), part("state_slots"), self.planner.error_word,
+                          host_cu_rows=list(range(bucket + 1)), host_start_positions=[0] * bucket,
+                          host_state_slots=[0] * bucket)
+        keep = []
+        for g, key in enumerate(groups):
+            acc = torch.empty(max(bucket * splits[g] * self.planner._scratch_acc_width, 1), dtype=torch.float32,
+                              device=self.device)
+            ml = torch.empty(max(bucket * splits[g] * self.planner._scratch_ml_width, 1), dtype=torch.float32,
+                             device=self.device)
+            keep += [acc, ml]
+            ctx.paged[key] = PagedBatch(part(f"table{g}").view(bucket, stride), part(f"slots{g}"),
+                                        [AttentionLaunch(0, bucket, StepPlanner.SPLIT_SIZE, splits[g])], acc, ml)
+        return ctx, part("logit_rows"), keep
+
+    def _capture(self, key, step: CapturedStep, groups, bucket, stride, splits) -> None:
+        ctx, logit_rows, keep = self._context(step, groups, bucket, stride, splits)
+        caches = [self.cache.layer_cache(i) for i in range(len(self.model.program))]
+        current = torch.cuda.current_stream()
+        side = torch.cuda.Stream()
+        side.wait_stream(current)
+        with torch.cuda.stream(side):        # the same rows twice: libraries settle their workspaces
+            for _ in range(2):
+                self.model.forward(ctx, caches, logit_rows)
+        current.wait_stream(side)
+        torch.cuda.synchronize()
+        graph = torch.cuda.CUDAGraph()
+        before = ops.launch_count
+        with torch.cuda.graph(graph, pool=self.pool):
+            logits = self.model.forward(ctx, caches, logit_rows)
+        self.kernels_per_replay[key] = ops.launch_count - before
+        if self.pool is None:
+            self.pool = graph.pool()
+        step.graph, step.logits, step.keep = graph, logits, (ctx, keep)

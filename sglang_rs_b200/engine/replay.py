@@ -26,7 +26,7 @@ class ReplaySession:
     step records.  Used by the command line below and by tests."""
 
     def __init__(self, model_dir: str, dtype: str, max_tokens: int, page_size: int = PAGE_SIZE,
-                 device: str = "cuda"):
+                 device: str = "cuda", use_cuda_graphs: bool = True):
         import torch
         from ..cache import CacheManager
         from ..weights import load_model, parse_dtype
@@ -39,7 +39,7 @@ class ReplaySession:
         # size, so ceil(max_tokens / page_size) pages hold whatever is live at any time.
         self.cache = CacheManager(self.model.cache_needs(), page_size=page_size, max_tokens=max(max_tokens, 1),
                                   max_requests=MAX_LIVE, device=device, dtype=self.dtype)
-        self.runner = ModelRunner(self.model, self.cache)
+        self.runner = ModelRunner(self.model, self.cache, use_cuda_graphs=use_cuda_graphs)
         self.handles = {}
 
     def run(self, record: dict):

@@ -201,7 +201,7 @@ class StepPlanner:
 
 
 class ModelRunner:
-    def __init__(self, model, cache: CacheManager):
+    def __init__(self, model, cache: CacheManager, use_cuda_graphs: bool = True):
         if model.device is None:
             raise RuntimeError("the model has no weights yet")
         if model.device.type != "cuda":
@@ -212,6 +212,10 @@ class ModelRunner:
         self.planner = StepPlanner(cache, self.device, self.dtype, widths)
         self.error_word = self.planner.error_word
         self.steps_run = 0
+        self.graphs = None
+        if use_cuda_graphs and all(getattr(layer, "graph_safe", False) for layer in model.layers):
+            from .graphs import DecodeGraphs
+            self.graphs = DecodeGraphs(model, cache, self.planner)
 
     # ------------------------------------------------------------------ the step
     def step(self, entries: Sequence[StepEntry]) -> Optional[torch.Tensor]:
@@ -231,9 +235,12 @@ class ModelRunner:
                 self.cache.trim_reservation(entry.handle)
             raise
         try:
-            ctx, logit_rows = self.planner.flatten(entries)
-            caches = [self.cache.layer_cache(i) for i in range(len(self.model.program))]
-            logits = self.model.forward(ctx, caches, logit_rows)
+            if self.graphs is not None and self.graphs.eligible(entries):
+                logits = self.graphs.run(entries)
+            else:
+                ctx, logit_rows = self.planner.flatten(entries)
+                caches = [self.cache.layer_cache(i) for i in range(len(self.model.program))]
+                logits = self.model.forward(ctx, caches, logit_rows)
         except Exception:
             for entry in entries:
                 self.cache.trim_reservation(entry.handle)

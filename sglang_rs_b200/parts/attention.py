@@ -34,6 +34,8 @@ class AttentionNames:
 
 
 class GroupedQueryAttention(Mixer):
+    graph_safe = True
+
     def __init__(self, hidden: int, num_heads: int, num_kv_heads: int, head_dim: int, scale: float,
                  position: PositionEncoding, names: AttentionNames, *, qk_norm_eps: Optional[float] = None,
                  window: Optional[int] = None):

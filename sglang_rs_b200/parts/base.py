@@ -54,6 +54,10 @@ CacheNeed = Union[PagedKV, RequestState, None]
 
 
 class Part:
+    #: True if ``forward`` only launches kernels that read the step's device arrays: nothing is
+    #: decided on the host from the step's values, so the call may be captured in a CUDA graph
+    graph_safe = False
+
     def tensor_specs(self) -> Dict[str, TensorSpec]:
         return {}
 

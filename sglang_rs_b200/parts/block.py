@@ -18,6 +18,10 @@ class PreNormBlock(Part):
     def __init__(self, input_norm: Norm, mixer: Mixer, post_norm: Norm, feed_forward: FeedForward):
         self.input_norm, self.mixer, self.post_norm, self.feed_forward = input_norm, mixer, post_norm, feed_forward
 
+    @property
+    def graph_safe(self) -> bool:
+        return all(part.graph_safe for part in self.parts())
+
     def parts(self):
         return (self.input_norm, self.mixer, self.post_norm, self.feed_forward)
 

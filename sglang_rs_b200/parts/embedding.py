@@ -15,6 +15,8 @@ from .base import Part, TensorSpec, matrix_to
 
 
 class TokenEmbedding(Part):
+    graph_safe = True
+
     def __init__(self, vocab: int, width: int, weight_name: str):
         self.vocab, self.width, self.weight_name = int(vocab), int(width), weight_name
         self.table: Optional[torch.Tensor] = None
@@ -33,6 +35,8 @@ class TokenEmbedding(Part):
 
 class OutputHead(Part):
     """``weight_name`` None ties the head to ``embedding``'s table."""
+    graph_safe = True
+
 
     def __init__(self, vocab: int, width: int, weight_name: Optional[str], embedding: Optional[TokenEmbedding] = None):
         if weight_name is None and embedding is None:

@@ -23,6 +23,8 @@ class GatedMlpNames:
 
 
 class GatedMlp(FeedForward):
+    graph_safe = True
+
     ACTIVATIONS = ("silu",)
 
     def __init__(self, hidden: int, inner: int, activation: str, names: GatedMlpNames):

@@ -16,6 +16,8 @@ from .base import Norm, TensorSpec, scale_to
 
 
 class RmsNorm(Norm):
+    graph_safe = True
+
     def __init__(self, width: int, eps: float, weight_name: str):
         self.width, self.eps, self.weight_name = int(width), float(eps), weight_name
         self.weight: Optional[torch.Tensor] = None

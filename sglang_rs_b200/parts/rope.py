@@ -25,6 +25,8 @@ class FusedRotary:
 
 
 class RotaryEncoding(PositionEncoding):
+    graph_safe = True
+
     fused = True
 
     def __init__(self, head_dim: int, theta: float, rotary_dim: Optional[int] = None, interleaved: bool = False):
@@ -51,6 +53,8 @@ class RotaryEncoding(PositionEncoding):
 
 class NoPositionEncoding(PositionEncoding):
     """Leaves q and k as they are."""
+    graph_safe = True
+
     fused = True
 
     def fused_rotary(self):

@@ -135,9 +135,10 @@ def collect(trace, outputs) -> Dict[str, Dict[int, np.ndarray]]:
     return rows
 
 
-def run_in_process(folder: str, dtype: str, trace, max_tokens=None, page_size: int = 16):
+def run_in_process(folder: str, dtype: str, trace, max_tokens=None, page_size: int = 16, graphs: bool = True):
     from sglang_rs_b200.engine.replay import ReplaySession
-    session = ReplaySession(folder, dtype, max_tokens if max_tokens is not None else max_tokens_of(trace), page_size)
+    session = ReplaySession(folder, dtype, max_tokens if max_tokens is not None else max_tokens_of(trace), page_size,
+                            use_cuda_graphs=graphs)
     outputs = []
     session.page_owners = {}                 # (group, page id) -> requests that held it at some time
     for step in trace:

@@ -76,6 +76,24 @@ def test_bfloat16_and_float32_cuts_agree_with_each_other(prepared, dtype_name):
     assert worst <= (2e-5 if dtype_name == "float32" else 2e-2)
 
 
+@pytest.mark.parametrize("dtype_name", list(DTYPES))
+@pytest.mark.parametrize("case", ["A", "C"])
+def test_captured_decode_steps_equal_eager_ones(prepared, case, dtype_name):
+    """Decoded tokens replayed from CUDA graphs (padded to a bucket of rows) against the same
+    steps launched one kernel at a time."""
+    folder, requests, expected, page = prepared(case, dtype_name)
+    for trace in (rh.trace_tail_by_one(requests), rh.trace_mixed(requests, seed=21)):
+        eager, _ = rh.run_in_process(folder, dtype_name, trace, page_size=page, graphs=False)
+        captured, session = rh.run_in_process(folder, dtype_name, trace, page_size=page, graphs=True)
+        assert session.runner.graphs is not None and session.runner.graphs.replays > 30
+        as_expected = {rid: np.stack([eager[rid][p] for p in range(len(t))]).astype(np.float64)
+                       for rid, t in requests.items()}
+        worst, where = rh.worst_error(captured, as_expected)
+        print(f"{case}/{dtype_name}: captured against eager: {worst:.3e} at {where}")
+        assert worst <= (0.0 if dtype_name == "float32" else 1e-2)
+        check(captured, expected, DTYPES[dtype_name][1], requests, f"{case}/{dtype_name}/captured")
+
+
 def test_trace_run_program(prepared, tmp_path):
     """The program itself, as a user calls it: steps on standard input, files out."""
     folder, requests, expected, page = prepared("A", "float32")
