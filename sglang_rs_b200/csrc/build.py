@@ -30,7 +30,8 @@ NVCC_FLAGS: Sequence[str] = (
 )
 
 #: every library of the package; ``build_all`` compiles each of them
-LIBRARIES: Sequence[str] = ("elementwise", "rope_kv", "attention", "gemm_f32", "sampling", "attention_noalloc")
+LIBRARIES: Sequence[str] = ("elementwise", "rope_kv", "attention", "gemm_f32", "sampling", "attention_noalloc",
+                            "attention_decode")
 
 _loaded: Dict[str, ctypes.CDLL] = {}
 

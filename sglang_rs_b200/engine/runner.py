@@ -77,7 +77,7 @@ class StepPlanner:
     parts read.  It needs the cache manager and the scratch widths of the mixers, not the
     model, so a single part can be stepped with it."""
     #: keys per split of a decode row; fixed, so a row's arithmetic depends on its own position only
-    SPLIT_SIZE = 256
+    SPLIT_SIZE = 128
     #: a request that brings at most this many rows is run with split keys
     SPLIT_ROWS_PER_REQUEST = 1
     #: floats of attention scratch above which the split is made coarser

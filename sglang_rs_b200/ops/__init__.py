@@ -197,12 +197,22 @@ def paged_attention(q: torch.Tensor, k_pool: torch.Tensor, v_pool: torch.Tensor,
         if scratch_acc is None or scratch_ml is None or scratch_acc.numel() < need_acc or scratch_ml.numel() < need_ml:
             raise KernelError("paged_attention: scratch tensors are too small for this split run")
         _need(scratch_acc, "scratch_acc", torch.float32); _need(scratch_ml, "scratch_ml", torch.float32)
+    if split_size and q.dtype == torch.bfloat16:
+        fast = load_library("attention_decode")
+        if fast.srb_decode_attention_supports(n_q, n_kv, head_dim, int(split_size), BF16):
+            _check(fast, fast.srb_decode_attention(
+                _ptr(q), _ptr(k_pool), _ptr(v_pool), _ptr(out), _ptr(scratch_acc), _ptr(scratch_ml), _ptr(positions),
+                _ptr(row_request), _ptr(block_table), block_table.stride(0), rows, n_q, n_kv, head_dim, page_size,
+                num_pages, int(window), int(split_size), int(max_splits), ctypes.c_float(scale), _ptr(error_word),
+                _stream()), launches=2)
+            return
     lib = load_library("attention")
     _check(lib, lib.srb_paged_attention(
         _ptr(q), _ptr(k_pool), _ptr(v_pool), _ptr(out), _ptr(scratch_acc), _ptr(scratch_ml), _ptr(positions),
         _ptr(row_request), _ptr(block_table), block_table.stride(0), rows, n_q, n_kv, head_dim, page_size,
         num_pages, int(window), int(split_size), int(max_splits), ctypes.c_float(scale), _ptr(error_word),
         dtype_code(q.dtype), _stream()), launches=2 if split_size else 1)
+
 
 
 # --------------------------------------------------------------------------- matrix products

@@ -216,7 +216,7 @@ def run_attention(case, scale, split_size):
 @pytest.mark.parametrize("dtype", DTYPES)
 @pytest.mark.parametrize("n_q,n_kv,d,page,window", [(4, 2, 16, 16, None), (6, 3, 32, 8, None), (5, 1, 48, 16, 37),
                                                     (8, 8, 64, 4, None), (16, 2, 128, 32, 100), (3, 1, 272, 16, None)])
-@pytest.mark.parametrize("split", [0, 32, 256])
+@pytest.mark.parametrize("split", [0, 32, 128, 256])
 def test_paged_attention(dtype, n_q, n_kv, d, page, window, split):
     lengths, rows = (1, 33, 300, 64, 257), (1, 5, 2, 64, 1)
     case = paged_case(dtype, n_q, n_kv, d, page, lengths, rows, window, seed=d + page)
@@ -225,7 +225,7 @@ def test_paged_attention(dtype, n_q, n_kv, d, page, window, split):
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
-@pytest.mark.parametrize("split", [0, 256])
+@pytest.mark.parametrize("split", [0, 128])
 def test_a_far_key_among_hundreds_is_found(dtype, split):
     """One key far back gets a score that dominates; leaving it out, or reading a stale page
     in its place, would change the output completely."""
