@@ -41,6 +41,9 @@ class AttentionLaunch:
     end: int
     split_size: int
     max_splits: int
+    #: for an unsplit launch: int32 [tiles, 4] = (first row, rows, request, first position), rows in tiles
+    #: of at most ``StepPlanner.TILE_ROWS`` consecutive rows of one request
+    tiles: Optional[torch.Tensor] = None
 
 
 @dataclass
@@ -80,6 +83,8 @@ class StepPlanner:
     SPLIT_SIZE = 128
     #: a request that brings at most this many rows is run with split keys
     SPLIT_ROWS_PER_REQUEST = 1
+    #: rows of one request that the tiled attention kernel takes per block
+    TILE_ROWS = 64
     #: floats of attention scratch above which the split is made coarser
     SCRATCH_LIMIT = 64 << 20
 
@@ -138,23 +143,32 @@ class StepPlanner:
                 pages = np.asarray(table, dtype=np.int64)[pos // page_size]
                 slots[key][begin:begin + len(pos)] = pages * page_size + pos % page_size
 
+        tiles: List[int] = []
+        for slot in range(len(order)):
+            if cu_rows[slot] < split_rows:
+                continue
+            for first in range(cu_rows[slot], cu_rows[slot + 1], self.TILE_ROWS):
+                tiles += [first, min(self.TILE_ROWS, cu_rows[slot + 1] - first), slot,
+                          start_positions[slot] + first - cu_rows[slot]]
         pieces = [np.asarray(tokens, dtype=np.int32), np.asarray(positions, dtype=np.int32),
                   np.asarray(row_request, dtype=np.int32), np.asarray(cu_rows, dtype=np.int32),
-                  np.asarray(state_slots, dtype=np.int32), np.asarray(logit_rows, dtype=np.int32)]
+                  np.asarray(state_slots, dtype=np.int32), np.asarray(logit_rows, dtype=np.int32),
+                  np.asarray(tiles, dtype=np.int32)]
         for key in groups:
             pieces.append(tables[key].reshape(-1))
             pieces.append(slots[key])
         device_pieces = self._upload(pieces)
-        token_ids, positions_d, row_request_d, cu_rows_d, state_slots_d, logit_rows_d = device_pieces[:6]
+        token_ids, positions_d, row_request_d, cu_rows_d, state_slots_d, logit_rows_d, tiles_d = device_pieces[:7]
+        tiles_d = tiles_d.view(-1, 4)
 
         ctx = StepContext(self.device, self.dtype, rows, len(order), token_ids, positions_d, row_request_d,
                           cu_rows_d, state_slots_d, self.error_word, host_cu_rows=cu_rows,
                           host_start_positions=start_positions, host_state_slots=state_slots)
         np_positions = np.asarray(positions, dtype=np.int64)
         for g, key in enumerate(groups):
-            table_d = device_pieces[6 + 2 * g].view(len(order), stride)
-            slots_d = device_pieces[7 + 2 * g]
-            ctx.paged[key] = self._plan(key, table_d, slots_d, np_positions, split_rows, rows)
+            table_d = device_pieces[7 + 2 * g].view(len(order), stride)
+            slots_d = device_pieces[8 + 2 * g]
+            ctx.paged[key] = self._plan(key, table_d, slots_d, np_positions, split_rows, rows, tiles_d)
         return ctx, (logit_rows_d if logit_rows else None)
 
     def _upload(self, pieces: Sequence[np.ndarray]) -> List[torch.Tensor]:
@@ -170,7 +184,8 @@ class StepPlanner:
         on_device = staging.to(self.device, non_blocking=True)
         return [on_device[offset:offset + size] for offset, size in zip(offsets[:-1], sizes)]
 
-    def _plan(self, key, table_d, slots_d, positions: np.ndarray, split_rows: int, rows: int) -> PagedBatch:
+    def _plan(self, key, table_d, slots_d, positions: np.ndarray, split_rows: int, rows: int,
+              tiles_d: Optional[torch.Tensor] = None) -> PagedBatch:
         window = self.cache.windows[key]
         launches: List[AttentionLaunch] = []
         scratch_acc = scratch_ml = None
@@ -189,7 +204,7 @@ class StepPlanner:
             scratch_acc = self._scratch_tensor("acc", need_acc)
             scratch_ml = self._scratch_tensor("ml", need_ml)
         if rows > split_rows:
-            launches.append(AttentionLaunch(split_rows, rows, 0, 1))
+            launches.append(AttentionLaunch(split_rows, rows, 0, 1, tiles_d))
         return PagedBatch(table_d, slots_d, launches, scratch_acc, scratch_ml)
 
     def _scratch_tensor(self, name: str, floats: int) -> torch.Tensor:

@@ -215,6 +215,33 @@ def paged_attention(q: torch.Tensor, k_pool: torch.Tensor, v_pool: torch.Tensor,
 
 
 
+def tiled_attention_takes(dtype: torch.dtype, n_q: int, n_kv: int, head_dim: int) -> bool:
+    """True if the tensor-core kernel for prompt portions takes these sizes."""
+    if dtype != torch.bfloat16:
+        return False
+    return bool(load_library("attention_prefill").srb_prefill_attention_supports(n_q, n_kv, head_dim, BF16))
+
+
+def tiled_attention(q: torch.Tensor, k_pool: torch.Tensor, v_pool: torch.Tensor, out: torch.Tensor,
+                    tiles: torch.Tensor, block_table: torch.Tensor, *, scale: float, window: int,
+                    error_word: torch.Tensor) -> None:
+    """Attention of prompt portions, bfloat16.  ``tiles`` is int32 [n, 4]: first row of the
+    step, rows (at most 64, consecutive rows of one request), request index, first position.
+    Rows outside the tiles are left untouched."""
+    _need(q, "q", torch.bfloat16); _need(out, "out", torch.bfloat16); _need(k_pool, "k_pool", torch.bfloat16)
+    _need(v_pool, "v_pool", torch.bfloat16); _need(tiles, "tiles", torch.int32)
+    _need(block_table, "block_table", torch.int32)
+    rows, n_q, head_dim = q.shape
+    num_pages, n_kv, page_size, pool_dim = k_pool.shape
+    if pool_dim != head_dim or v_pool.shape != k_pool.shape or out.shape != q.shape or tiles.shape[-1] != 4:
+        raise KernelError("tiled_attention: shapes of q, out, the pools and the tiles do not agree")
+    lib = load_library("attention_prefill")
+    _check(lib, lib.srb_prefill_attention(
+        _ptr(q), _ptr(k_pool), _ptr(v_pool), _ptr(out), _ptr(tiles), tiles.shape[0], _ptr(block_table),
+        block_table.stride(0), n_q, n_kv, head_dim, page_size, num_pages, int(window), ctypes.c_float(scale),
+        _ptr(error_word), _stream()))
+
+
 # --------------------------------------------------------------------------- matrix products
 
 def linear(x: torch.Tensor, weight: torch.Tensor, bias: Optional[torch.Tensor] = None,

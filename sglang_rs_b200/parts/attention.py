@@ -103,6 +103,10 @@ class GroupedQueryAttention(Mixer):
         out = torch.empty_like(q)
         for launch in batch.launches:
             b, e = launch.begin, launch.end
+            if launch.tiles is not None and ops.tiled_attention_takes(q.dtype, self.n_q, self.n_kv, self.d):
+                ops.tiled_attention(q, cache.k_pool, cache.v_pool, out, launch.tiles, batch.block_table,
+                                    scale=self.scale, window=self.window or 0, error_word=ctx.error_word)
+                continue
             ops.paged_attention(q[b:e], cache.k_pool, cache.v_pool, out[b:e], ctx.positions[b:e],
                                 ctx.row_request[b:e], batch.block_table, scale=self.scale,
                                 window=self.window or 0, split_size=launch.split_size,
