@@ -1,0 +1,409 @@
+// Y = X W^T in bfloat16 with 32-bit accumulation on the 5th-generation tensor cores:
+// tcgen05.mma with the accumulator in tensor memory, operands brought into shared memory
+// by TMA (cp.async.bulk.tensor, 128-byte swizzle), mbarrier pipelines between a copy warp,
+// an issue warp and four epilogue warps.
+//
+// The weight is the M side of the instruction ("swap-AB"): a block owns 128 rows of W
+// [features, K] and up to 256 tokens of X [tokens, K]; both are K-major, so no transpose is
+// needed anywhere, and a step with few tokens (decode) still fills the 128-wide M side of
+// the unit while it streams W exactly once.  The accumulator tile is [128 features (TMEM
+// lanes) x tokens (TMEM columns)]; the epilogue reads it with tcgen05.ld and stores
+// out[token][feature], 32 consecutive features per warp store.
+//
+// Modes of the epilogue: bfloat16 store; float store (logits); SiLU(gate) * up, where the
+// block multiplies two row blocks of the stacked gate/up matrix into two accumulators and
+// writes only the product; and float partials per K split, [split][token][feature], which
+// the consumer adds in split order (few tokens cannot fill 148 SMs with 128-row blocks alone,
+// so K is cut; the cut depends on the shape only).
+//
+// Weight layout and meaning as the reference's projection: row-major [out, in],
+// y[o] = sum_i x[i] W[o, i] (crates/sglang-kernel/src/cpu.rs:73-108), bfloat16 inputs with
+// 32-bit accumulation as its cuBLAS call (crates/sglang-kernel/src/cublas.rs:383-410).
+//
+// Every wait on an mbarrier is bounded (about a second of spinning); a wait that runs out
+// sets SRB_FLAG_WAIT_TIMEOUT in the error word, every role leaves its loop, outstanding
+// copies are waited for with the same bound, tensor memory is freed and the block returns.
+// No TMA load uses cluster multicast.
+#include "common.cuh"
+#include <cuda.h>
+#include <mutex>
+#include <unordered_map>
+
+SRB_DEFINE_LAST_ERROR()
+
+#define GEMM_BLOCK_F 128      // weight rows (features) per block = M of the instruction
+#define GEMM_BLOCK_K 64       // bfloat16 elements per 128-byte swizzle row
+#define GEMM_UMMA_K 16
+#define GEMM_THREADS 192      // warp 0: TMA, warp 1: MMA + TMEM, warps 2-5: epilogue
+#define GEMM_SPIN_LIMIT 2000000000ll   // clock cycles before a wait gives up
+
+#define EPI_BF16 0
+#define EPI_F32 1
+#define EPI_SILU 2
+#define EPI_PARTIAL 3
+
+// ------------------------------------------------------------------------------- PTX helpers
+__device__ __forceinline__ unsigned smem_u32(const void* p) { return (unsigned)__cvta_generic_to_shared(p); }
+
+__device__ __forceinline__ void mbar_init(unsigned bar, unsigned count) {
+  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count));
+}
+__device__ __forceinline__ void mbar_expect_tx(unsigned bar, unsigned bytes) {
+  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ bool mbar_try_wait(unsigned bar, unsigned parity) {
+  unsigned ok;
+  asm volatile(
+      "{\n.reg .pred p;\nmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\nselp.u32 %0, 1, 0, p;\n}\n"
+      : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
+  return ok != 0;
+}
+// Bounded wait: false if the phase did not complete in time (or another role gave up).
+__device__ __forceinline__ bool mbar_wait(unsigned bar, unsigned parity, volatile int* abort_flag) {
+  if (mbar_try_wait(bar, parity)) return true;
+  const long long start = clock64();
+  for (unsigned spins = 0;; ++spins) {
+    if (mbar_try_wait(bar, parity)) return true;
+    if ((spins & 255u) == 255u) {
+      if (*abort_flag) return false;
+      if (clock64() - start > GEMM_SPIN_LIMIT) {
+        *abort_flag = 1;
+        return false;
+      }
+    }
+  }
+}
+// The same bound without the shared give-up flag: used to drain copies after a role gave up.
+__device__ __forceinline__ bool mbar_wait_timed(unsigned bar, unsigned parity) {
+  const long long start = clock64();
+  for (unsigned spins = 0;; ++spins) {
+    if (mbar_try_wait(bar, parity)) return true;
+    if ((spins & 255u) == 255u && clock64() - start > GEMM_SPIN_LIMIT) return false;
+  }
+}
+__device__ __forceinline__ void tma_load_2d(unsigned dst, const CUtensorMap* map, unsigned bar, int x, int y) {
+  asm volatile(
+      "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
+      ::"r"(dst), "l"(map), "r"(bar), "r"(x), "r"(y) : "memory");
+}
+__device__ __forceinline__ void tmem_alloc(unsigned holder, unsigned columns) {
+  asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(holder), "r"(columns)
+               : "memory");
+  asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void tmem_dealloc(unsigned address, unsigned columns) {
+  asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(address), "r"(columns) : "memory");
+}
+__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void umma_bf16(unsigned tmem_d, unsigned long long a_desc, unsigned long long b_desc,
+                                          unsigned idesc, unsigned accumulate) {
+  asm volatile(
+      "{\n.reg .pred p;\nsetp.ne.b32 p, %4, 0;\ntcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n}\n"
+      ::"r"(tmem_d), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate) : "memory");
+}
+__device__ __forceinline__ void umma_commit(unsigned bar) {
+  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ void tmem_load_16(unsigned address, float (&v)[16]) {
+  unsigned r[16];
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15}, [%16];"
+      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
+        "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
+      : "r"(address) : "memory");
+  asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+#pragma unroll
+  for (int i = 0; i < 16; ++i) v[i] = __uint_as_float(r[i]);
+}
+
+// Shared-memory matrix descriptor of a K-major tile written by TMA with 128-byte swizzle:
+// rows of 128 bytes, groups of 8 rows 1024 bytes apart.
+__device__ __forceinline__ unsigned long long smem_descriptor(unsigned address) {
+  unsigned long long d = 0;
+  d |= (unsigned long long)((address & 0x3ffffu) >> 4);        // start address, 16-byte units
+  d |= (unsigned long long)(1024u >> 4) << 32;                 // stride between 8-row groups
+  d |= 1ull << 46;                                             // descriptor version of sm_100
+  d |= 2ull << 61;                                             // layout: 128-byte swizzle
+  return d;
+}
+
+// Instruction descriptor: D float, A and B bfloat16, both K-major, M = 128, N = tokens.
+__host__ __device__ constexpr unsigned instruction_descriptor(int n) {
+  return (1u << 4) | (1u << 7) | (1u << 10) | ((unsigned)(n >> 3) << 17) | ((unsigned)(GEMM_BLOCK_F >> 4) << 24);
+}
+
+struct GemmArgs {
+  void* out;                 // bf16 / float [tokens, ldo] or float partials [splits, tokens, ldo]
+  int tokens, features, k;   // problem
+  int ldo;                   // row pitch of out, in elements
+  int up_row_offset;         // EPI_SILU: rows of the up matrix start here in W
+  int k_blocks_per_split;
+  int* error_word;
+};
+
+template <int BLOCK_T, int EPI, int STAGES>
+__global__ void __launch_bounds__(GEMM_THREADS, 1)
+gemm_bf16_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_x,
+                 GemmArgs args) {
+  constexpr int A_TILES = EPI == EPI_SILU ? 2 : 1;
+  constexpr int A_BYTES = GEMM_BLOCK_F * GEMM_BLOCK_K * 2;
+  constexpr int B_BYTES = BLOCK_T * GEMM_BLOCK_K * 2;
+  constexpr int STAGE_BYTES = A_TILES * A_BYTES + B_BYTES;
+  constexpr int ACC_COLUMNS = A_TILES * BLOCK_T;
+  constexpr unsigned TMEM_COLUMNS = ACC_COLUMNS <= 32 ? 32 : ACC_COLUMNS <= 64 ? 64 : ACC_COLUMNS <= 128 ? 128
+                                                                               : ACC_COLUMNS <= 256 ? 256 : 512;
+  extern __shared__ unsigned char smem_unaligned[];
+  unsigned char* smem = reinterpret_cast<unsigned char*>(((uintptr_t)smem_unaligned + 1023) & ~(uintptr_t)1023);
+  __shared__ __align__(8) unsigned long long full_bar[STAGES], empty_bar[STAGES], acc_bar;
+  __shared__ unsigned tmem_holder;
+  __shared__ int abort_flag;
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  // token tiles are the fastest grid dimension: blocks that share a weight tile run together
+  const int token0 = blockIdx.x * BLOCK_T;
+  const int feature0 = blockIdx.y * GEMM_BLOCK_F;
+  const int total_k_blocks = (args.k + GEMM_BLOCK_K - 1) / GEMM_BLOCK_K;
+  const int kb_begin = blockIdx.z * args.k_blocks_per_split;
+  const int kb_end = min(total_k_blocks, kb_begin + args.k_blocks_per_split);
+  const int num_kb = max(kb_end - kb_begin, 0);
+
+  if (threadIdx.x == 0) {
+    abort_flag = 0;
+    for (int s = 0; s < STAGES; ++s) {
+      mbar_init(smem_u32(&full_bar[s]), 1);
+      mbar_init(smem_u32(&empty_bar[s]), 1);
+    }
+    mbar_init(smem_u32(&acc_bar), 1);
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  if (warp == 1) tmem_alloc(smem_u32(&tmem_holder), TMEM_COLUMNS);
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const unsigned tmem_base = tmem_holder;
+
+  if (warp == 0) {
+    if (lane == 0) {
+      int issued = 0;
+      for (int i = 0; i < num_kb; ++i) {
+        const int s = i % STAGES;
+        const unsigned phase = (unsigned)(i / STAGES) & 1u;
+        if (!mbar_wait(smem_u32(&empty_bar[s]), phase ^ 1u, &abort_flag)) break;
+        const unsigned bar = smem_u32(&full_bar[s]);
+        unsigned char* stage = smem + (size_t)s * STAGE_BYTES;
+        mbar_expect_tx(bar, STAGE_BYTES);
+        const int kx = (kb_begin + i) * GEMM_BLOCK_K;
+        tma_load_2d(smem_u32(stage), &map_w, bar, kx, feature0);
+        if (A_TILES == 2) tma_load_2d(smem_u32(stage + A_BYTES), &map_w, bar, kx, args.up_row_offset + feature0);
+        tma_load_2d(smem_u32(stage + A_TILES * A_BYTES), &map_x, bar, kx, token0);
+        issued = i + 1;
+      }
+      // copies still in flight write into this block's shared memory: wait for them before leaving
+      if (abort_flag) {
+        for (int i = max(0, issued - STAGES); i < issued; ++i)
+          mbar_wait_timed(smem_u32(&full_bar[i % STAGES]), (unsigned)(i / STAGES) & 1u);
+      }
+    }
+  } else if (warp == 1) {
+    if (lane == 0) {
+      constexpr unsigned idesc = instruction_descriptor(BLOCK_T);
+      bool ok = true;
+      for (int i = 0; i < num_kb && ok; ++i) {
+        const int s = i % STAGES;
+        const unsigned phase = (unsigned)(i / STAGES) & 1u;
+        ok = mbar_wait(smem_u32(&full_bar[s]), phase, &abort_flag);
+        if (!ok) break;
+        tc_fence_after();
+        const unsigned stage = smem_u32(smem + (size_t)s * STAGE_BYTES);
+        const unsigned long long a_desc = smem_descriptor(stage);
+        const unsigned long long b_desc = smem_descriptor(stage + A_TILES * A_BYTES);
+#pragma unroll
+        for (int k = 0; k < GEMM_BLOCK_K / GEMM_UMMA_K; ++k) {
+          const unsigned accumulate = (i > 0 || k > 0) ? 1u : 0u;
+          const unsigned long long step = (unsigned long long)((k * GEMM_UMMA_K * 2) >> 4);
+          umma_bf16(tmem_base, a_desc + step, b_desc + step, idesc, accumulate);
+          if (A_TILES == 2) {
+            const unsigned long long up_desc = smem_descriptor(stage + A_BYTES);
+            umma_bf16(tmem_base + BLOCK_T, up_desc + step, b_desc + step, idesc, accumulate);
+          }
+        }
+        umma_commit(smem_u32(&empty_bar[s]));        // frees the stage when these products have read it
+      }
+      if (ok) umma_commit(smem_u32(&acc_bar));       // the accumulator is complete
+    }
+  } else {
+    // epilogue: warp w may read TMEM lanes 32 * (w % 4) .. + 32
+    const int quarter = warp & 3;
+    const int feature = feature0 + quarter * 32 + lane;
+    bool ok = true;
+    if (num_kb > 0) {
+      ok = mbar_wait(smem_u32(&acc_bar), 0, &abort_flag);
+      tc_fence_after();
+    }
+    if (ok) {
+      const unsigned lane_address = tmem_base + ((unsigned)(quarter * 32) << 16);
+#pragma unroll 1
+      for (int c = 0; c < BLOCK_T; c += 16) {
+        if (token0 + c >= args.tokens) break;          // warp-uniform
+        float acc[16], up[16];
+        if (num_kb > 0) {
+          tmem_load_16(lane_address + c, acc);
+          if (EPI == EPI_SILU) tmem_load_16(lane_address + BLOCK_T + c, up);
+        } else {
+#pragma unroll
+          for (int j = 0; j < 16; ++j) acc[j] = up[j] = 0.f;
+        }
+        if (feature < args.features) {
+#pragma unroll
+          for (int j = 0; j < 16; ++j) {
+            const int token = token0 + c + j;
+            if (token >= args.tokens) break;
+            if (EPI == EPI_BF16) {
+              reinterpret_cast<__nv_bfloat16*>(args.out)[(size_t)token * args.ldo + feature] =
+                  __float2bfloat16_rn(acc[j]);
+            } else if (EPI == EPI_F32) {
+              reinterpret_cast<float*>(args.out)[(size_t)token * args.ldo + feature] = acc[j];
+            } else if (EPI == EPI_SILU) {
+              const float g = acc[j];
+              reinterpret_cast<__nv_bfloat16*>(args.out)[(size_t)token * args.ldo + feature] =
+                  __float2bfloat16_rn(g / (1.0f + expf(-g)) * up[j]);
+            } else {
+              reinterpret_cast<float*>(args.out)[((size_t)blockIdx.z * args.tokens + token) * args.ldo + feature] =
+                  acc[j];
+            }
+          }
+        }
+      }
+    }
+    tc_fence_before();
+  }
+  __syncthreads();
+  if (threadIdx.x == 0 && abort_flag) atomicOr(args.error_word, SRB_FLAG_WAIT_TIMEOUT);
+  if (warp == 1) {
+    tc_fence_after();
+    tmem_dealloc(tmem_base, TMEM_COLUMNS);
+  }
+}
+
+// ------------------------------------------------------------------------------- host side
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+static EncodeTiledFn encode_tiled() {
+  static EncodeTiledFn fn = nullptr;
+  static std::once_flag once;
+  std::call_once(once, [] {
+    void* entry = nullptr;
+    cudaDriverEntryPointQueryResult result;
+    if (cudaGetDriverEntryPointByVersion("cuTensorMapEncodeTiled", &entry, 12000, cudaEnableDefault, &result) ==
+            cudaSuccess && result == cudaDriverEntryPointSuccess)
+      fn = reinterpret_cast<EncodeTiledFn>(entry);
+  });
+  return fn;
+}
+
+// A [rows, k] bfloat16 row-major matrix cut into boxes of [box_rows, 64] with 128-byte swizzle.
+static int make_map(CUtensorMap* map, const void* base, long long rows, long long k, long long pitch, int box_rows) {
+  EncodeTiledFn fn = encode_tiled();
+  if (!fn) SRB_FAIL("gemm_bf16: the driver does not offer cuTensorMapEncodeTiled");
+  const cuuint64_t dims[2] = {(cuuint64_t)k, (cuuint64_t)rows};
+  const cuuint64_t strides[1] = {(cuuint64_t)pitch * 2};
+  const cuuint32_t box[2] = {GEMM_BLOCK_K, (cuuint32_t)box_rows};
+  const cuuint32_t elem[2] = {1, 1};
+  const CUresult status = fn(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(base), dims, strides, box,
+                             elem, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                             CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (status != CUDA_SUCCESS) SRB_FAIL("gemm_bf16: cuTensorMapEncodeTiled failed with %d", (int)status);
+  return SRB_OK;
+}
+
+template <int BLOCK_T, int EPI>
+static int launch_gemm(const CUtensorMap& map_w, const CUtensorMap& map_x, const GemmArgs& args, int splits,
+                       cudaStream_t s) {
+  constexpr int A_TILES = EPI == EPI_SILU ? 2 : 1;
+  constexpr int STAGE_BYTES = A_TILES * GEMM_BLOCK_F * GEMM_BLOCK_K * 2 + BLOCK_T * GEMM_BLOCK_K * 2;
+  constexpr int STAGES = (200 * 1024) / STAGE_BYTES >= 8 ? 8 : (200 * 1024) / STAGE_BYTES;
+  static_assert(STAGES >= 3, "a pipeline needs at least three stages");
+  const size_t smem = (size_t)STAGES * STAGE_BYTES + 1024;
+  auto kernel = gemm_bf16_kernel<BLOCK_T, EPI, STAGES>;
+  SRB_CUDA_CALL(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+  dim3 grid((args.tokens + BLOCK_T - 1) / BLOCK_T, (args.features + GEMM_BLOCK_F - 1) / GEMM_BLOCK_F, splits);
+  if (grid.y > 65535) SRB_FAIL("gemm_bf16: %d features exceed one launch", args.features);
+  kernel<<<grid, GEMM_THREADS, smem, s>>>(map_w, map_x, args);
+  SRB_LAUNCH_CHECK("gemm_bf16");
+  return SRB_OK;
+}
+
+template <int EPI>
+static int dispatch_tokens(int block_t, const CUtensorMap& map_w, const CUtensorMap& map_x, const GemmArgs& args,
+                           int splits, cudaStream_t s) {
+  switch (block_t) {
+    case 16: return launch_gemm<16, EPI>(map_w, map_x, args, splits, s);
+    case 32: return launch_gemm<32, EPI>(map_w, map_x, args, splits, s);
+    case 64: return launch_gemm<64, EPI>(map_w, map_x, args, splits, s);
+    case 128: return launch_gemm<128, EPI>(map_w, map_x, args, splits, s);
+    default: return launch_gemm<256, EPI>(map_w, map_x, args, splits, s);
+  }
+}
+
+// Tokens per block for a step of `tokens` rows: the smallest tile that holds them, 256 at most
+// (the SiLU mode keeps two accumulators and stops at 128).
+extern "C" int srb_gemm_bf16_block_tokens(int tokens, int mode) {
+  const int cap = mode == EPI_SILU ? 128 : 256;
+  int block = 16;
+  while (block < tokens && block < cap) block *= 2;
+  return block;
+}
+
+// x [tokens, k] (row pitch ldx), w [rows_of_w, k] (row pitch ldw), both bfloat16, k a multiple of 8.
+// mode 0: out bf16 [tokens, ldo] = x w^T over `features` rows of w.
+// mode 1: the same as float.
+// mode 2: w stacks gate rows [0, features) and up rows [up_row_offset, up_row_offset + features);
+//         out bf16 [tokens, ldo] = silu(x gate^T) * (x up^T).
+// mode 3: `splits` partial sums over K as float [splits, tokens, ldo]; the caller adds them in order.
+extern "C" int srb_gemm_bf16(const void* x, const void* w, void* out, int tokens, int features, int k, int ldx,
+                             int ldw, int ldo, int rows_of_w, int up_row_offset, int mode, int splits,
+                             int* error_word, void* stream) {
+  if (tokens <= 0 || features <= 0) return SRB_OK;
+  if (k <= 0 || k % 8 != 0 || ldx % 8 != 0 || ldw % 8 != 0)
+    SRB_FAIL("gemm_bf16: inner size %d and the row pitches %d, %d must be positive multiples of 8 (16-byte rows "
+             "for TMA)", k, ldx, ldw);
+  if (((uintptr_t)x | (uintptr_t)w) & 15) SRB_FAIL("gemm_bf16: operands must be 16-byte aligned");
+  if (mode < 0 || mode > 3) SRB_FAIL("gemm_bf16: unknown mode %d", mode);
+  if (ldo < features) SRB_FAIL("gemm_bf16: output pitch %d is smaller than %d features", ldo, features);
+  if (mode == EPI_SILU && up_row_offset + features > rows_of_w)
+    SRB_FAIL("gemm_bf16: the up rows %d..%d lie outside the %d rows of w", up_row_offset, up_row_offset + features,
+             rows_of_w);
+  if (mode != EPI_SILU && features > rows_of_w) SRB_FAIL("gemm_bf16: %d features exceed %d rows of w", features, rows_of_w);
+  const int total_k_blocks = (k + GEMM_BLOCK_K - 1) / GEMM_BLOCK_K;
+  if (mode != EPI_PARTIAL) splits = 1;
+  if (splits < 1 || splits > total_k_blocks) SRB_FAIL("gemm_bf16: %d splits do not fit %d blocks of K", splits, total_k_blocks);
+  const int block_t = srb_gemm_bf16_block_tokens(tokens, mode);
+
+  CUtensorMap map_w, map_x;
+  // rows beyond `features` (or beyond the matrix) are never stored; the map covers all rows of w
+  if (make_map(&map_w, w, rows_of_w, k, ldw, GEMM_BLOCK_F) != SRB_OK) return SRB_ERR_INVALID;
+  if (make_map(&map_x, x, tokens, k, ldx, block_t) != SRB_OK) return SRB_ERR_INVALID;
+
+  GemmArgs args;
+  args.out = out; args.tokens = tokens; args.features = features; args.k = k; args.ldo = ldo;
+  args.up_row_offset = up_row_offset; args.error_word = error_word;
+  args.k_blocks_per_split = (total_k_blocks + splits - 1) / splits;
+  const int used_splits = (total_k_blocks + args.k_blocks_per_split - 1) / args.k_blocks_per_split;
+  if (used_splits != splits) SRB_FAIL("gemm_bf16: %d splits leave one without work for %d blocks of K", splits, total_k_blocks);
+  cudaStream_t s = (cudaStream_t)stream;
+  switch (mode) {
+    case EPI_BF16: return dispatch_tokens<EPI_BF16>(block_t, map_w, map_x, args, splits, s);
+    case EPI_F32: return dispatch_tokens<EPI_F32>(block_t, map_w, map_x, args, splits, s);
+    case EPI_SILU:
+      switch (block_t) {
+        case 16: return launch_gemm<16, EPI_SILU>(map_w, map_x, args, 1, s);
+        case 32: return launch_gemm<32, EPI_SILU>(map_w, map_x, args, 1, s);
+        case 64: return launch_gemm<64, EPI_SILU>(map_w, map_x, args, 1, s);
+        default: return launch_gemm<128, EPI_SILU>(map_w, map_x, args, 1, s);
+      }
+    default: return dispatch_tokens<EPI_PARTIAL>(block_t, map_w, map_x, args, splits, s);
+  }
+}

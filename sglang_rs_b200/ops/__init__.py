@@ -197,15 +197,15 @@ def paged_attention(q: torch.Tensor, k_pool: torch.Tensor, v_pool: torch.Tensor,
         if scratch_acc is None or scratch_ml is None or scratch_acc.numel() < need_acc or scratch_ml.numel() < need_ml:
             raise KernelError("paged_attention: scratch tensors are too small for this split run")
         _need(scratch_acc, "scratch_acc", torch.float32); _need(scratch_ml, "scratch_ml", torch.float32)
-    if split_size and q.dtype == torch.bfloat16:
+    if split_size == 128 and q.dtype == torch.bfloat16 and head_dim in (64, 128) and n_q // n_kv <= 16:
+        # sizes the tensor-core kernel takes (srb_decode_attention_supports states the same rule)
         fast = load_library("attention_decode")
-        if fast.srb_decode_attention_supports(n_q, n_kv, head_dim, int(split_size), BF16):
-            _check(fast, fast.srb_decode_attention(
-                _ptr(q), _ptr(k_pool), _ptr(v_pool), _ptr(out), _ptr(scratch_acc), _ptr(scratch_ml), _ptr(positions),
-                _ptr(row_request), _ptr(block_table), block_table.stride(0), rows, n_q, n_kv, head_dim, page_size,
-                num_pages, int(window), int(split_size), int(max_splits), ctypes.c_float(scale), _ptr(error_word),
-                _stream()), launches=2)
-            return
+        _check(fast, fast.srb_decode_attention(
+            _ptr(q), _ptr(k_pool), _ptr(v_pool), _ptr(out), _ptr(scratch_acc), _ptr(scratch_ml), _ptr(positions),
+            _ptr(row_request), _ptr(block_table), block_table.stride(0), rows, n_q, n_kv, head_dim, page_size,
+            num_pages, int(window), int(split_size), int(max_splits), ctypes.c_float(scale), _ptr(error_word),
+            _stream()), launches=2)
+        return
     lib = load_library("attention")
     _check(lib, lib.srb_paged_attention(
         _ptr(q), _ptr(k_pool), _ptr(v_pool), _ptr(out), _ptr(scratch_acc), _ptr(scratch_ml), _ptr(positions),
@@ -217,9 +217,9 @@ def paged_attention(q: torch.Tensor, k_pool: torch.Tensor, v_pool: torch.Tensor,
 
 def tiled_attention_takes(dtype: torch.dtype, n_q: int, n_kv: int, head_dim: int) -> bool:
     """True if the tensor-core kernel for prompt portions takes these sizes."""
-    if dtype != torch.bfloat16:
-        return False
-    return bool(load_library("attention_prefill").srb_prefill_attention_supports(n_q, n_kv, head_dim, BF16))
+    # the same rule as srb_prefill_attention_supports, asked here so that a model the kernel
+    # does not take never compiles it
+    return dtype == torch.bfloat16 and head_dim in (64, 128) and n_kv > 0 and n_q % n_kv == 0
 
 
 def tiled_attention(q: torch.Tensor, k_pool: torch.Tensor, v_pool: torch.Tensor, out: torch.Tensor,
@@ -272,6 +272,41 @@ def linear(x: torch.Tensor, weight: torch.Tensor, bias: Optional[torch.Tensor] =
     if bias is not None:
         add_bias(out, bias)
     return out
+
+
+GEMM_MODES = {"bf16": 0, "f32": 1, "silu": 2, "partial": 3}
+
+
+def gemm_bf16(x: torch.Tensor, w: torch.Tensor, error_word: torch.Tensor, *, mode: str = "bf16",
+              features: Optional[int] = None, up_row_offset: int = 0, splits: int = 1) -> torch.Tensor:
+    """y = x @ w^T on tcgen05 tensor cores (bfloat16 in, 32-bit accumulation).
+
+    x [tokens, k], w [rows, k], k a multiple of 8.  ``mode``: ``bf16`` / ``f32`` store
+    [tokens, features]; ``silu`` treats w as gate rows [0, features) stacked over up rows
+    [up_row_offset, up_row_offset + features) and stores silu(gate) * up; ``partial`` stores
+    ``splits`` float partial sums [splits, tokens, features] that the consumer adds in order."""
+    _need(x, "x", torch.bfloat16); _need(w, "w", torch.bfloat16)
+    tokens, k = x.shape
+    rows = w.shape[0]
+    if w.shape[1] != k:
+        raise KernelError(f"gemm_bf16: x {tuple(x.shape)} and w {tuple(w.shape)} do not fit")
+    if features is None:
+        features = rows
+    code = GEMM_MODES[mode]
+    if mode == "partial":
+        out = torch.empty((splits, tokens, features), dtype=torch.float32, device=x.device)
+    else:
+        splits = 1
+        out = torch.empty((tokens, features), dtype=torch.float32 if mode == "f32" else torch.bfloat16, device=x.device)
+    lib = load_library("gemm_bf16")
+    _check(lib, lib.srb_gemm_bf16(_ptr(x), _ptr(w), _ptr(out), tokens, features, k, x.stride(0), w.stride(0), features,
+                                  rows, int(up_row_offset), code, int(splits), _ptr(error_word), _stream()))
+    return out
+
+
+def gemm_bf16_takes(k: int) -> bool:
+    """TMA needs 16-byte rows: the inner size must be a multiple of 8 bfloat16 values."""
+    return k % 8 == 0
 
 
 # --------------------------------------------------------------------------- sampling

@@ -1,0 +1,73 @@
+"""The tcgen05 / TMEM / TMA matrix product alone, against a 64-bit product of the same
+bfloat16 values, at sizes that are no multiple of any tile."""
+import pytest
+import torch
+
+import plain_model as pm
+from sglang_rs_b200 import ops
+
+pytestmark = pytest.mark.gpu
+DEV = "cuda"
+
+
+def operands(tokens, features, k, seed, rows=None):
+    g = torch.Generator().manual_seed(seed)
+    x = torch.randn(tokens, k, generator=g).to(torch.bfloat16)
+    w = (torch.randn(rows or features, k, generator=g) * 0.5).to(torch.bfloat16)
+    return x, w
+
+
+def relative_error(got, want):
+    return float((got.double().cpu() - want).abs().max() / want.abs().max())
+
+
+@pytest.mark.parametrize("tokens,features,k", [(1, 128, 64), (8, 256, 128), (3, 331, 72), (17, 130, 200), (64, 512, 4096),
+                                               (100, 96, 1000), (300, 640, 328), (1, 6144, 4096), (513, 257, 136)])
+def test_plain_product(tokens, features, k):
+    x, w = operands(tokens, features, k, seed=tokens + k)
+    word = ops.new_error_word(DEV)
+    want = pm.plain_linear(x.double(), w.double())
+    got = ops.gemm_bf16(x.to(DEV), w.to(DEV), word, mode="f32")
+    ops.raise_on_error_word(word)
+    assert relative_error(got, want) < 1e-5           # 32-bit accumulation of exact bfloat16 products
+    rounded = ops.gemm_bf16(x.to(DEV), w.to(DEV), word, mode="bf16")
+    assert rounded.dtype == torch.bfloat16 and relative_error(rounded, want) < 5e-3
+    ops.raise_on_error_word(word)
+
+
+@pytest.mark.parametrize("tokens,features,k,splits", [(2, 128, 256, 2), (8, 200, 4096, 5), (33, 384, 1000, 16), (64, 64, 328, 3)])
+def test_partial_sums_over_k(tokens, features, k, splits):
+    x, w = operands(tokens, features, k, seed=7)
+    word = ops.new_error_word(DEV)
+    parts = ops.gemm_bf16(x.to(DEV), w.to(DEV), word, mode="partial", splits=splits)
+    ops.raise_on_error_word(word)
+    assert parts.shape == (splits, tokens, features)
+    want = pm.plain_linear(x.double(), w.double())
+    assert relative_error(parts.double().sum(0), want) < 1e-5
+    assert float(parts[-1].abs().max()) > 0        # the last split did its share
+
+
+@pytest.mark.parametrize("tokens,inner,k", [(1, 128, 64), (8, 200, 72), (70, 256, 512), (129, 130, 200)])
+def test_gate_up_with_silu_epilogue(tokens, inner, k):
+    x, w = operands(tokens, inner, k, seed=11, rows=2 * inner)
+    word = ops.new_error_word(DEV)
+    got = ops.gemm_bf16(x.to(DEV), w.to(DEV), word, mode="silu", features=inner, up_row_offset=inner)
+    ops.raise_on_error_word(word)
+    both = pm.plain_linear(x.double(), w.double())
+    want = pm.plain_silu_mul(both[:, :inner], both[:, inner:])
+    assert got.shape == (tokens, inner) and relative_error(got, want) < 5e-3
+
+
+def test_a_rows_result_does_not_depend_on_the_rows_beside_it():
+    x, w = operands(40, 256, 512, seed=5)
+    word = ops.new_error_word(DEV)
+    together = ops.gemm_bf16(x.to(DEV), w.to(DEV), word, mode="f32")
+    alone = ops.gemm_bf16(x[17:18].contiguous().to(DEV), w.to(DEV), word, mode="f32")
+    assert torch.equal(together[17], alone[0])
+
+
+def test_sizes_tma_cannot_take_are_refused():
+    x, w = operands(4, 128, 68, seed=1)
+    with pytest.raises(ops.KernelError, match="multiples of 8"):
+        ops.gemm_bf16(x.to(DEV), w.to(DEV), ops.new_error_word(DEV))
+    assert not ops.gemm_bf16_takes(68) and ops.gemm_bf16_takes(72)
