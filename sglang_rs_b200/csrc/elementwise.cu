@@ -25,8 +25,11 @@ __global__ void embedding_kernel(const int* __restrict__ ids, const T* __restric
 // x = residual[src] (+ delta[src]); optionally residual[src] = x; out[row] = T(x * rsqrt * w).
 // `row_index` (optional) picks the source rows, so the final norm touches only the rows
 // whose logits are wanted.  The row is staged in shared memory between the two passes.
+// The pending sum may also arrive as `num_parts` float partial sums (a matrix product cut
+// along K), `part_stride` elements apart; they are added in part order.
 template <typename T>
 __global__ void add_rmsnorm_kernel(float* __restrict__ residual, const T* __restrict__ delta,
+                                   const float* __restrict__ delta_parts, int num_parts, size_t part_stride,
                                    const float* __restrict__ weight, T* __restrict__ out,
                                    const int* __restrict__ row_index, int width, float eps,
                                    int write_residual) {
@@ -38,6 +41,7 @@ __global__ void add_rmsnorm_kernel(float* __restrict__ residual, const T* __rest
   for (int i = threadIdx.x; i < width; i += blockDim.x) {
     float x = residual[src + i];
     if (delta) x += srb_to_float(delta[src + i]);
+    for (int part = 0; part < num_parts; ++part) x += delta_parts[part * part_stride + src + i];
     if (write_residual) residual[src + i] = x;
     staged[i] = x;
     partial += x * x;
@@ -93,32 +97,36 @@ extern "C" int srb_embedding(const int* ids, const void* table, float* residual,
 }
 
 template <typename T>
-static int launch_add_rmsnorm(float* residual, const void* delta, const float* weight, void* out,
-                              const int* row_index, int rows, int width, float eps, int write_residual,
-                              cudaStream_t s) {
+static int launch_add_rmsnorm(float* residual, const void* delta, const float* delta_parts, int num_parts,
+                              size_t part_stride, const float* weight, void* out, const int* row_index, int rows,
+                              int width, float eps, int write_residual, cudaStream_t s) {
   const size_t smem = (size_t)(width + 33) * sizeof(float);
   if (smem > 227 * 1024) SRB_FAIL("add_rmsnorm: width %d needs %zu bytes of shared memory (limit 232448)", width, smem);
   if (smem > 48 * 1024)
     SRB_CUDA_CALL(cudaFuncSetAttribute(add_rmsnorm_kernel<T>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
   const int block = width >= 2048 ? 512 : (width >= 512 ? 256 : 128);
-  add_rmsnorm_kernel<T><<<rows, block, smem, s>>>(residual, (const T*)delta, weight, (T*)out, row_index, width,
-                                                  eps, write_residual);
+  add_rmsnorm_kernel<T><<<rows, block, smem, s>>>(residual, (const T*)delta, delta_parts, num_parts, part_stride,
+                                                  weight, (T*)out, row_index, width, eps, write_residual);
   SRB_LAUNCH_CHECK("add_rmsnorm");
   return SRB_OK;
 }
 
-extern "C" int srb_add_rmsnorm(float* residual, const void* delta, const float* weight, void* out,
-                               const int* row_index, int rows, int width, float eps, int write_residual,
-                               int dtype, void* stream) {
+// delta: [rows_of_residual, width] of the output's type, or null; delta_parts: `num_parts` float
+// tensors of that shape, `part_stride` elements apart, or null.
+extern "C" int srb_add_rmsnorm(float* residual, const void* delta, const float* delta_parts, int num_parts,
+                               long long part_stride, const float* weight, void* out, const int* row_index,
+                               int rows, int width, float eps, int write_residual, int dtype, void* stream) {
   if (rows <= 0) return SRB_OK;
   if (width <= 0) SRB_FAIL("add_rmsnorm: width %d must be positive", width);
   if (!(eps >= 0.f)) SRB_FAIL("add_rmsnorm: eps must be finite and non-negative");
+  if (num_parts < 0 || (num_parts > 0 && !delta_parts)) SRB_FAIL("add_rmsnorm: partial sums are missing");
   cudaStream_t s = (cudaStream_t)stream;
   if (dtype == SRB_DTYPE_F32)
-    return launch_add_rmsnorm<float>(residual, delta, weight, out, row_index, rows, width, eps, write_residual, s);
+    return launch_add_rmsnorm<float>(residual, delta, delta_parts, num_parts, (size_t)part_stride, weight, out,
+                                     row_index, rows, width, eps, write_residual, s);
   if (dtype == SRB_DTYPE_BF16)
-    return launch_add_rmsnorm<__nv_bfloat16>(residual, delta, weight, out, row_index, rows, width, eps,
-                                             write_residual, s);
+    return launch_add_rmsnorm<__nv_bfloat16>(residual, delta, delta_parts, num_parts, (size_t)part_stride, weight,
+                                             out, row_index, rows, width, eps, write_residual, s);
   SRB_FAIL("add_rmsnorm: unknown dtype %d", dtype);
 }
 

@@ -15,8 +15,11 @@ SRB_DEFINE_LAST_ERROR()
 
 #define ROPE_WARPS 4
 
+// The projection may arrive as `num_parts` float partial sums (a product cut along K),
+// `part_stride` elements apart, instead of one tensor of type T; they are added in part order.
 template <typename T>
-__global__ void qk_norm_rope_kv_kernel(const T* __restrict__ qkv, int qkv_stride, T* __restrict__ q_out,
+__global__ void qk_norm_rope_kv_kernel(const T* __restrict__ qkv, const float* __restrict__ qkv_parts, int num_parts,
+                                       size_t part_stride, int qkv_stride, T* __restrict__ q_out,
                                        T* __restrict__ k_pool, T* __restrict__ v_pool,
                                        const int* __restrict__ positions, const int* __restrict__ slots,
                                        const float* __restrict__ q_norm, const float* __restrict__ k_norm,
@@ -29,7 +32,7 @@ __global__ void qk_norm_rope_kv_kernel(const T* __restrict__ qkv, int qkv_stride
   const int head = blockIdx.y * ROPE_WARPS + warp;     // q heads, then k heads, then v heads
   if (head >= heads_to_do) return;
   float* staged = staged_all + warp * head_dim;
-  const T* src = qkv + (size_t)row * qkv_stride + (size_t)head * head_dim;
+  const size_t src_offset = (size_t)row * qkv_stride + (size_t)head * head_dim;
 
   const bool is_q = head < n_q;
   const bool is_k = !is_q && head < n_q + n_kv;
@@ -37,7 +40,12 @@ __global__ void qk_norm_rope_kv_kernel(const T* __restrict__ qkv, int qkv_stride
 
   float partial = 0.f;
   for (int e = lane; e < head_dim; e += 32) {
-    const float x = srb_to_float(src[e]);
+    float x = 0.f;
+    if (num_parts == 0) {
+      x = srb_to_float(qkv[src_offset + e]);
+    } else {
+      for (int part = 0; part < num_parts; ++part) x += qkv_parts[part * part_stride + src_offset + e];
+    }
     staged[e] = x;
     partial += x * x;
   }
@@ -81,7 +89,8 @@ __global__ void qk_norm_rope_kv_kernel(const T* __restrict__ qkv, int qkv_stride
 
 // `slots` may be null: then only the q heads are processed (a layer that reads another
 // layer's cache writes nothing).
-extern "C" int srb_qk_norm_rope_kv(const void* qkv, int qkv_stride, void* q_out, void* k_pool, void* v_pool,
+extern "C" int srb_qk_norm_rope_kv(const void* qkv, const float* qkv_parts, int num_parts, long long part_stride,
+                                   int qkv_stride, void* q_out, void* k_pool, void* v_pool,
                                    const int* positions, const int* slots, const float* q_norm,
                                    const float* k_norm, float eps, const float* inv_freq, int rotary_dim,
                                    int interleaved, int rows, int n_q, int n_kv, int head_dim, int page_size,
@@ -93,18 +102,20 @@ extern "C" int srb_qk_norm_rope_kv(const void* qkv, int qkv_stride, void* q_out,
     SRB_FAIL("qk_norm_rope_kv: rotary width %d must be even, positive and at most head_dim %d", rotary_dim,
              head_dim);
   if (head_dim > 2048) SRB_FAIL("qk_norm_rope_kv: head_dim %d exceeds 2048", head_dim);
+  if (num_parts < 0 || (num_parts > 0 && !qkv_parts) || (num_parts == 0 && !qkv))
+    SRB_FAIL("qk_norm_rope_kv: the projection is missing");
   const int heads = slots ? n_q + 2 * n_kv : n_q;
   dim3 grid(rows, (heads + ROPE_WARPS - 1) / ROPE_WARPS);
   const size_t smem = (size_t)ROPE_WARPS * head_dim * sizeof(float);
   cudaStream_t s = (cudaStream_t)stream;
   if (dtype == SRB_DTYPE_F32)
     qk_norm_rope_kv_kernel<float><<<grid, ROPE_WARPS * 32, smem, s>>>(
-        (const float*)qkv, qkv_stride, (float*)q_out, (float*)k_pool, (float*)v_pool, positions, slots, q_norm,
+        (const float*)qkv, qkv_parts, num_parts, (size_t)part_stride, qkv_stride, (float*)q_out, (float*)k_pool, (float*)v_pool, positions, slots, q_norm,
         k_norm, eps, inv_freq, rotary_dim, interleaved, n_q, n_kv, head_dim, page_size, num_pages, heads,
         error_word);
   else if (dtype == SRB_DTYPE_BF16)
     qk_norm_rope_kv_kernel<__nv_bfloat16><<<grid, ROPE_WARPS * 32, smem, s>>>(
-        (const __nv_bfloat16*)qkv, qkv_stride, (__nv_bfloat16*)q_out, (__nv_bfloat16*)k_pool,
+        (const __nv_bfloat16*)qkv, qkv_parts, num_parts, (size_t)part_stride, qkv_stride, (__nv_bfloat16*)q_out, (__nv_bfloat16*)k_pool,
         (__nv_bfloat16*)v_pool, positions, slots, q_norm, k_norm, eps, inv_freq, rotary_dim, interleaved, n_q,
         n_kv, head_dim, page_size, num_pages, heads, error_word);
   else

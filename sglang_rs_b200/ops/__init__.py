@@ -91,14 +91,24 @@ def add_rmsnorm(residual: torch.Tensor, delta: Optional[torch.Tensor], weight: t
                 out: torch.Tensor, row_index: Optional[torch.Tensor] = None, write_residual: bool = True) -> None:
     """x = residual (+ delta); residual = x if asked; out = x / sqrt(mean(x^2) + eps) * weight.
 
-    With ``row_index`` the rows ``row_index[i]`` are read and ``out[i]`` is written."""
+    ``delta`` is [rows, width] of ``out``'s dtype, or float32 [parts, rows, width]: partial sums
+    of a product cut along K, added in order.  With ``row_index`` the rows ``row_index[i]`` are
+    read and ``out[i]`` is written."""
     _need(residual, "residual", torch.float32); _need(weight, "weight", torch.float32); _need(out, "out")
     width = residual.shape[1]
     rows = out.shape[0]
-    if delta is not None:
+    whole = parts = None
+    num_parts = part_stride = 0
+    if delta is not None and delta.dim() == 3:
+        _need(delta, "delta", torch.float32)
+        if delta.shape[1:] != residual.shape:
+            raise KernelError("add_rmsnorm: partial sums and residual differ in shape")
+        parts, num_parts, part_stride = delta, delta.shape[0], delta.stride(0)
+    elif delta is not None:
         _need(delta, "delta", out.dtype)
         if delta.shape != residual.shape:
             raise KernelError("add_rmsnorm: delta and residual differ in shape")
+        whole = delta
     if row_index is not None:
         _need(row_index, "row_index", torch.int32)
         if row_index.numel() != rows:
@@ -108,9 +118,9 @@ def add_rmsnorm(residual: torch.Tensor, delta: Optional[torch.Tensor], weight: t
     if weight.numel() != width or out.shape[1] != width:
         raise KernelError("add_rmsnorm: widths do not agree")
     lib = load_library("elementwise")
-    _check(lib, lib.srb_add_rmsnorm(_ptr(residual), _ptr(delta), _ptr(weight), _ptr(out), _ptr(row_index), rows,
-                                    width, ctypes.c_float(eps), int(write_residual), dtype_code(out.dtype),
-                                    _stream()))
+    _check(lib, lib.srb_add_rmsnorm(_ptr(residual), _ptr(whole), _ptr(parts), num_parts, ctypes.c_longlong(part_stride),
+                                    _ptr(weight), _ptr(out), _ptr(row_index), rows, width, ctypes.c_float(eps),
+                                    int(write_residual), dtype_code(out.dtype), _stream()))
 
 
 def silu_mul(gate_up: torch.Tensor, out: torch.Tensor) -> None:
@@ -141,18 +151,27 @@ def qk_norm_rope_kv(qkv: torch.Tensor, q_out: torch.Tensor, k_pool: Optional[tor
                     head_dim: int, error_word: torch.Tensor) -> None:
     """Per-head norm of q and k, rotation of q and k, q to ``q_out``, k and v into the pages.
 
-    ``qkv`` is [rows, >= (n_q + 2 n_kv) head_dim] with q heads, k heads, v heads in that order;
+    ``qkv`` is [rows, >= (n_q + 2 n_kv) head_dim] with q heads, k heads, v heads in that order,
+    of ``q_out``'s dtype, or float32 [parts, rows, width] partial sums that are added in order;
     pools are [pages, n_kv, page_size, head_dim]; ``slots[r]`` = page * page_size + offset.
     With ``slots`` None nothing is written to the pages."""
-    _need(qkv, "qkv"); _need(q_out, "q_out", qkv.dtype); _need(positions, "positions", torch.int32)
-    rows = qkv.shape[0]
+    _need(qkv, "qkv"); _need(q_out, "q_out"); _need(positions, "positions", torch.int32)
+    whole = parts = None
+    num_parts = part_stride = 0
+    if qkv.dim() == 3:
+        _need(qkv, "qkv", torch.float32)
+        parts, num_parts, part_stride = qkv, qkv.shape[0], qkv.stride(0)
+    else:
+        _need(qkv, "qkv", q_out.dtype)
+        whole = qkv
+    rows = qkv.shape[-2]
     page_size = num_pages = 1
     if slots is not None:
-        _need(slots, "slots", torch.int32); _need(k_pool, "k_pool", qkv.dtype); _need(v_pool, "v_pool", qkv.dtype)
+        _need(slots, "slots", torch.int32); _need(k_pool, "k_pool", q_out.dtype); _need(v_pool, "v_pool", q_out.dtype)
         num_pages, pool_heads, page_size, pool_dim = k_pool.shape
         if (pool_heads, pool_dim) != (n_kv, head_dim) or v_pool.shape != k_pool.shape:
             raise KernelError("qk_norm_rope_kv: pools must be [pages, n_kv, page_size, head_dim]")
-        if qkv.shape[1] < (n_q + 2 * n_kv) * head_dim:
+        if qkv.shape[-1] < (n_q + 2 * n_kv) * head_dim:
             raise KernelError("qk_norm_rope_kv: qkv is narrower than q, k and v together")
     for name, w in (("q_norm", q_norm), ("k_norm", k_norm)):
         if w is not None:
@@ -165,9 +184,10 @@ def qk_norm_rope_kv(qkv: torch.Tensor, q_out: torch.Tensor, k_pool: Optional[tor
             raise KernelError("qk_norm_rope_kv: inv_freq must have rotary_dim / 2 elements")
     lib = load_library("rope_kv")
     _check(lib, lib.srb_qk_norm_rope_kv(
-        _ptr(qkv), qkv.stride(0), _ptr(q_out), _ptr(k_pool), _ptr(v_pool), _ptr(positions), _ptr(slots),
-        _ptr(q_norm), _ptr(k_norm), ctypes.c_float(eps), _ptr(inv_freq), rotary_dim, int(interleaved), rows, n_q,
-        n_kv, head_dim, page_size, num_pages, _ptr(error_word), dtype_code(qkv.dtype), _stream()))
+        _ptr(whole), _ptr(parts), num_parts, ctypes.c_longlong(part_stride), qkv.stride(-2), _ptr(q_out), _ptr(k_pool),
+        _ptr(v_pool), _ptr(positions), _ptr(slots), _ptr(q_norm), _ptr(k_norm), ctypes.c_float(eps), _ptr(inv_freq),
+        rotary_dim, int(interleaved), rows, n_q, n_kv, head_dim, page_size, num_pages, _ptr(error_word),
+        dtype_code(q_out.dtype), _stream()))
 
 
 def attention_scratch_sizes(rows: int, n_q: int, head_dim: int, max_splits: int) -> tuple[int, int]:
@@ -244,14 +264,39 @@ def tiled_attention(q: torch.Tensor, k_pool: torch.Tensor, v_pool: torch.Tensor,
 
 # --------------------------------------------------------------------------- matrix products
 
+#: up to this many rows a bfloat16 product runs on this package's tcgen05 kernel; above it on cuBLAS
+OWN_GEMM_MAX_TOKENS = 128
+#: the SMs a product cut along K should fill
+SM_COUNT = 148
+
+
+def gemm_splits(tokens: int, features: int, k: int) -> int:
+    """Into how many partial sums a small-batch product is cut along K.  A function of the
+    shape only: blocks of 128 weight rows alone cannot occupy the SMs when there are few of
+    them, so K is cut until about one block per SM exists, each with at least 8 K blocks."""
+    if tokens > 64:
+        return 1
+    tiles = -(-features // 128)
+    k_blocks = -(-k // 64)
+    splits = max(1, min(SM_COUNT // tiles, k_blocks // 8))
+    if splits <= 1:
+        return 1
+    per_split = -(-k_blocks // splits)
+    return -(-k_blocks // per_split)
+
+
 def linear(x: torch.Tensor, weight: torch.Tensor, bias: Optional[torch.Tensor] = None,
-           out_dtype: Optional[torch.dtype] = None) -> torch.Tensor:
+           out_dtype: Optional[torch.dtype] = None, error_word: Optional[torch.Tensor] = None,
+           partial_ok: bool = False) -> torch.Tensor:
     """y = x @ weight^T (+ bias); weight is [out, in], row-major.
 
-    float32: the FFMA kernel of this package, true 32-bit.  bfloat16: cuBLAS through
-    torch with 32-bit accumulation, which is what the reference's engine calls for every
-    projection (crates/sglang-kernel/src/cublas.rs:383-410); ``out_dtype`` float32 keeps the
-    accumulator's precision (used for the logits)."""
+    float32: the FFMA kernel of this package, true 32-bit.  bfloat16: up to
+    ``OWN_GEMM_MAX_TOKENS`` rows the tcgen05 kernel of this package, above that cuBLAS through
+    torch (what the reference's engine calls for every projection,
+    crates/sglang-kernel/src/cublas.rs:383-410); both accumulate in 32-bit.  ``out_dtype``
+    float32 keeps the accumulator's precision (used for the logits).  With ``partial_ok`` the
+    result may be float32 [parts, rows, out]: partial sums over K that the consumer adds in
+    order (``add_rmsnorm`` and ``qk_norm_rope_kv`` do)."""
     _need(x, "x"); _need(weight, "weight", x.dtype)
     if x.dim() != 2 or weight.dim() != 2 or x.shape[1] != weight.shape[1]:
         raise KernelError(f"linear: x {tuple(x.shape)} and weight {tuple(weight.shape)} do not fit")
@@ -265,13 +310,37 @@ def linear(x: torch.Tensor, weight: torch.Tensor, bias: Optional[torch.Tensor] =
         _check(lib, lib.srb_gemm_f32(_ptr(x), _ptr(weight), _ptr(bias), _ptr(out), m, n, k, x.stride(0),
                                      weight.stride(0), out.stride(0), _stream()))
         return out
-    if out_dtype == torch.float32:
+    if m <= OWN_GEMM_MAX_TOKENS and error_word is not None and gemm_bf16_takes(k):
+        splits = gemm_splits(m, n, k) if partial_ok else 1
+        if splits > 1:
+            out = gemm_bf16(x, weight, error_word, mode="partial", splits=splits)
+            if bias is not None:
+                add_bias(out[0], bias)
+            return out
+        out = gemm_bf16(x, weight, error_word, mode="f32" if out_dtype == torch.float32 else "bf16")
+    elif out_dtype == torch.float32:
         out = torch.mm(x, weight.t(), out_dtype=torch.float32)
     else:
         out = torch.mm(x, weight.t())
     if bias is not None:
         add_bias(out, bias)
     return out
+
+
+def gate_up_silu(x: torch.Tensor, weight: torch.Tensor, inner: int,
+                 error_word: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """silu(x gate^T) * (x up^T) for ``weight`` = gate rows stacked over up rows [2 inner, in].
+
+    bfloat16 with few rows: one tcgen05 kernel whose epilogue takes the product of its two
+    accumulators, so the [rows, 2 inner] intermediate never exists.  Otherwise the product
+    (``linear``) followed by the SiLU kernel."""
+    if (x.dtype == torch.bfloat16 and x.shape[0] <= OWN_GEMM_MAX_TOKENS and error_word is not None
+            and gemm_bf16_takes(x.shape[1])):
+        return gemm_bf16(x, weight, error_word, mode="silu", features=inner, up_row_offset=inner)
+    gate_up = linear(x, weight, error_word=error_word)
+    act = torch.empty((x.shape[0], inner), dtype=x.dtype, device=x.device)
+    silu_mul(gate_up, act)
+    return act
 
 
 GEMM_MODES = {"bf16": 0, "f32": 1, "silu": 2, "partial": 3}

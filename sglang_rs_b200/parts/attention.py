@@ -89,7 +89,7 @@ class GroupedQueryAttention(Mixer):
     def forward(self, ctx, cache, x: torch.Tensor) -> torch.Tensor:
         batch = ctx.paged[cache.group]
         rows = x.shape[0]
-        qkv = ops.linear(x, self.w_qkv, self.b_qkv)
+        qkv = ops.linear(x, self.w_qkv, self.b_qkv, error_word=ctx.error_word, partial_ok=True)
         q = torch.empty((rows, self.n_q, self.d), dtype=x.dtype, device=x.device)
         rotary = self.position.fused_rotary() if self.position.fused else None
         if not self.position.fused:
@@ -112,4 +112,5 @@ class GroupedQueryAttention(Mixer):
                                 window=self.window or 0, split_size=launch.split_size,
                                 max_splits=launch.max_splits, scratch_acc=batch.scratch_acc,
                                 scratch_ml=batch.scratch_ml, error_word=ctx.error_word)
-        return ops.linear(out.view(rows, self.n_q * self.d), self.w_o, self.b_o)
+        return ops.linear(out.view(rows, self.n_q * self.d), self.w_o, self.b_o, error_word=ctx.error_word,
+                          partial_ok=True)

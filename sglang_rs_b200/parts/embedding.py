@@ -53,4 +53,4 @@ class OutputHead(Part):
 
     def forward(self, ctx, normed: torch.Tensor) -> torch.Tensor:
         weight = self.weight if self.weight_name else self.embedding.table
-        return ops.linear(normed, weight, out_dtype=torch.float32)
+        return ops.linear(normed, weight, out_dtype=torch.float32, error_word=ctx.error_word)

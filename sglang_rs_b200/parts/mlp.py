@@ -44,7 +44,6 @@ class GatedMlp(FeedForward):
         self.w_down = matrix_to(tensors[n.down], device, dtype)
 
     def forward(self, ctx, x: torch.Tensor) -> torch.Tensor:
-        gate_up = ops.linear(x, self.w_gate_up)
-        act = torch.empty((x.shape[0], self.inner), dtype=x.dtype, device=x.device)
-        ops.silu_mul(gate_up, act)
-        return ops.linear(act, self.w_down)
+        error_word = ctx.error_word if ctx is not None else None
+        act = ops.gate_up_silu(x, self.w_gate_up, self.inner, error_word)
+        return ops.linear(act, self.w_down, error_word=error_word, partial_ok=True)

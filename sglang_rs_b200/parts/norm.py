@@ -30,7 +30,8 @@ class RmsNorm(Norm):
 
     def add_norm(self, residual: torch.Tensor, delta: Optional[torch.Tensor], out_dtype: torch.dtype,
                  row_index: Optional[torch.Tensor] = None) -> torch.Tensor:
-        """residual += delta (in place, unless rows are picked); returns norm(residual)."""
+        """residual += delta (in place, unless rows are picked); returns norm(residual).
+        ``delta`` may be float32 [parts, rows, width]: partial sums, added in order."""
         rows = residual.shape[0] if row_index is None else row_index.numel()
         out = torch.empty((rows, self.width), dtype=out_dtype, device=residual.device)
         ops.add_rmsnorm(residual, delta, self.weight, self.eps, out, row_index=row_index,

@@ -72,6 +72,35 @@ def test_add_rmsnorm(dtype, width):
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
+def test_norm_and_rope_take_partial_sums(dtype):
+    """A product cut along K hands its consumer float partial sums; they are added in order."""
+    g = torch.Generator().manual_seed(2)
+    rows, width, parts = 5, 200, 3
+    residual, weight = torch.randn(rows, width, generator=g), 1 + 0.1 * torch.randn(width, generator=g)
+    pieces = torch.randn(parts, rows, width, generator=g)
+    res_d = residual.to(DEV)
+    out = torch.empty(rows, width, device=DEV, dtype=dtype)
+    ops.add_rmsnorm(res_d, pieces.to(DEV), weight.to(DEV), 1e-6, out)
+    summed = residual.double() + pieces.double().sum(0)
+    assert torch.allclose(res_d.cpu().double(), summed, atol=1e-5)
+    close(out, pm.plain_rms_norm(summed, weight.double(), 1e-6), dtype, "norm of partial sums")
+    n_q, n_kv, d = 3, 1, 32
+    qkv = torch.randn(parts, rows, (n_q + 2 * n_kv) * d, generator=g)
+    positions = torch.arange(rows, dtype=torch.int32)
+    inv = pm.plain_inverse_frequencies(1e4, d)
+    k_pool = torch.zeros(2, n_kv, 8, d, device=DEV, dtype=dtype)
+    v_pool = torch.zeros_like(k_pool)
+    q_out = torch.empty(rows, n_q, d, device=DEV, dtype=dtype)
+    word = ops.new_error_word(DEV)
+    ops.qk_norm_rope_kv(qkv.to(DEV), q_out, k_pool, v_pool, positions.to(DEV), positions.to(DEV), None, None, 0.0,
+                        inv.to(DEV), d, False, n_q, n_kv, d, word)
+    ops.raise_on_error_word(word)
+    total = qkv.double().sum(0)
+    close(q_out, pm.plain_rope_neox(total[:, :n_q * d].view(rows, n_q, d), positions, inv), dtype, "q of partial sums")
+    close(v_pool[0, 0, :rows], total[:, (n_q + n_kv) * d:], dtype, "v of partial sums")
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
 def test_silu_mul_and_bias(dtype):
     g = torch.Generator().manual_seed(1)
     gate_up = torch.randn(5, 2 * 200, generator=g) * 4
