@@ -28,7 +28,8 @@ template <int D>
 __global__ void __launch_bounds__(DEC_WARPS * 32)
 decode_attention_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __restrict__ k_pool,
                         const __nv_bfloat16* __restrict__ v_pool, float* __restrict__ part_acc,
-                        float* __restrict__ part_ml, AttnParams p) {
+                        float* __restrict__ part_ml, __nv_bfloat16* __restrict__ out, int* __restrict__ counters,
+                        AttnParams p) {
   constexpr int CHUNKS = D / 8;            // 16-byte chunks per key row
   constexpr int KSTEPS = D / 16;           // k16 steps of Q K^T
   constexpr int NT_S = DEC_KEYS / 8;       // n8 tiles of S
@@ -51,25 +52,29 @@ decode_attention_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16
   __nv_bfloat16* vs = ks + DEC_KEYS * D;
 
   if (has_keys) {
+    // lane i looks up the page of key i once; the copies below fetch the row offset by shuffle
+    long long my_offset = -1;
+    {
+      const int abs_key = warp_base + lane;
+      if (abs_key >= k_lo && abs_key < k_hi) {
+        const int page = p.block_table[(size_t)request * p.table_stride + abs_key / p.page_size];
+        if (page < 0 || page >= p.num_pages)
+          atomicOr(p.error_word, SRB_FLAG_BAD_PAGE);
+        else
+          my_offset = (((long long)page * p.n_kv + kv_head) * p.page_size + abs_key % p.page_size) * D;
+      }
+    }
 #pragma unroll 1
     for (int pass = 0; pass < 2; ++pass) {
       const __nv_bfloat16* pool = pass == 0 ? k_pool : v_pool;
       __nv_bfloat16* dst_base = pass == 0 ? ks : vs;
-      for (int i = lane; i < DEC_KEYS * CHUNKS; i += 32) {
+#pragma unroll
+      for (int j = 0; j < DEC_KEYS * CHUNKS / 32; ++j) {
+        const int i = lane + 32 * j;
         const int key = i / CHUNKS, c = i % CHUNKS;
-        const int abs_key = warp_base + key;
-        bool valid = abs_key >= k_lo && abs_key < k_hi;
-        long long offset = 0;
-        if (valid) {
-          const int page = p.block_table[(size_t)request * p.table_stride + abs_key / p.page_size];
-          if (page < 0 || page >= p.num_pages) {
-            atomicOr(p.error_word, SRB_FLAG_BAD_PAGE);
-            valid = false;
-          } else {
-            offset = (((long long)page * p.n_kv + kv_head) * p.page_size + abs_key % p.page_size) * D + c * 8;
-          }
-        }
-        cp_async_16(dst_base + key * D + ((c ^ (key & 7)) * 8), pool + offset, valid ? 16 : 0);
+        const long long offset = __shfl_sync(0xffffffffu, my_offset, key);
+        const bool valid = offset >= 0;
+        cp_async_16(dst_base + key * D + ((c ^ (key & 7)) * 8), pool + (valid ? offset + c * 8 : 0), valid ? 16 : 0);
       }
       cp_async_commit();
     }
@@ -215,18 +220,65 @@ decode_attention_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16
       part_ml[slot * 2 + 1] = l;
     }
   }
+  if (!counters) return;                 // a separate kernel merges the splits
+
+  // The block that arrives last at this (row, kv head) merges all splits, in split order, so
+  // the result does not depend on which block that is.  The counter returns to zero.
+  __shared__ int is_last;
+  const int count = min(row_split_count(p, pos), p.max_splits);
+  __threadfence();
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    int* counter = counters + (size_t)row * p.n_kv + kv_head;
+    const int ticket = atomicAdd(counter, 1);
+    is_last = ticket == count - 1;
+    if (is_last) *counter = 0;
+  }
+  __syncthreads();
+  if (!is_last) return;
+  __threadfence();
+  float* weights = stage;                // [groups][count + 1]: e^(m_s - M) per split, then 1 / sum
+  for (int head = warp; head < groups; head += DEC_WARPS) {
+    const size_t first = ((size_t)row * p.n_q + (size_t)kv_head * groups + head) * p.max_splits;
+    float m = -INFINITY;
+    for (int sp = lane; sp < count; sp += 32) m = fmaxf(m, __ldcg(part_ml + (first + sp) * 2));
+    m = srb_warp_max(m);
+    float l = 0.f;
+    for (int base = 0; base < count; base += 32) {      // sums in split order: lane order inside, chunks outside
+      const int sp = base + lane;
+      float w = 0.f, lw = 0.f;
+      if (sp < count) {
+        w = expf(__ldcg(part_ml + (first + sp) * 2) - m);
+        lw = __ldcg(part_ml + (first + sp) * 2 + 1) * w;
+        weights[head * (count + 1) + sp] = w;
+      }
+      for (int k = 0; k < 32; ++k) l += __shfl_sync(0xffffffffu, lw, k);
+    }
+    if (lane == 0) weights[head * (count + 1) + count] = 1.0f / l;
+  }
+  __syncthreads();
+  for (int i = threadIdx.x; i < groups * D; i += blockDim.x) {
+    const int head = i / D, e = i % D;
+    const size_t first = ((size_t)row * p.n_q + (size_t)kv_head * groups + head) * p.max_splits;
+    const float* w = weights + head * (count + 1);
+    float acc = 0.f;
+    for (int sp = 0; sp < count; ++sp) acc += __ldcg(part_acc + (first + sp) * D + e) * w[sp];
+    out[((size_t)row * p.n_q + (size_t)kv_head * groups + head) * D + e] = __float2bfloat16_rn(acc * w[count]);
+  }
 }
 
 template <int D>
 static int launch_decode(const void* q, const void* k_pool, const void* v_pool, void* out, float* part_acc,
-                         float* part_ml, const AttnParams& p, int rows, cudaStream_t s) {
+                         float* part_ml, int* counters, const AttnParams& p, int rows, cudaStream_t s) {
   const size_t smem = (size_t)DEC_WARPS * 2 * DEC_KEYS * D * sizeof(__nv_bfloat16);
   SRB_CUDA_CALL(cudaFuncSetAttribute(decode_attention_kernel<D>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                      (int)smem));
   dim3 grid(p.max_splits, p.n_kv, rows);
   decode_attention_kernel<D><<<grid, DEC_WARPS * 32, smem, s>>>(
-      (const __nv_bfloat16*)q, (const __nv_bfloat16*)k_pool, (const __nv_bfloat16*)v_pool, part_acc, part_ml, p);
+      (const __nv_bfloat16*)q, (const __nv_bfloat16*)k_pool, (const __nv_bfloat16*)v_pool, part_acc, part_ml,
+      (__nv_bfloat16*)out, counters, p);
   SRB_LAUNCH_CHECK("decode_attention");
+  if (counters) return SRB_OK;
   dim3 cgrid(rows, p.n_q);
   attention_combine_kernel<__nv_bfloat16><<<cgrid, 64, 0, s>>>(part_acc, part_ml, (__nv_bfloat16*)out, p);
   SRB_LAUNCH_CHECK("attention_combine");
@@ -239,9 +291,11 @@ extern "C" int srb_decode_attention_supports(int n_q, int n_kv, int head_dim, in
          n_q / n_kv <= 16 && split_size == DEC_SPLIT;
 }
 
-// Arguments as srb_paged_attention; bfloat16 only; split_size must be 128.
+// Arguments as srb_paged_attention; bfloat16 only; split_size must be 128.  `counters` (optional)
+// holds rows * n_kv ints that are zero before the call and zero again after it: with it the
+// last block of each (row, kv head) merges the splits and no second kernel runs.
 extern "C" int srb_decode_attention(const void* q, const void* k_pool, const void* v_pool, void* out,
-                                    float* part_acc, float* part_ml, const int* positions,
+                                    float* part_acc, float* part_ml, int* counters, const int* positions,
                                     const int* row_request, const int* block_table, int table_stride, int rows,
                                     int n_q, int n_kv, int head_dim, int page_size, int num_pages, int window,
                                     int split_size, int max_splits, float scale, int* error_word, void* stream) {
@@ -259,6 +313,6 @@ extern "C" int srb_decode_attention(const void* q, const void* k_pool, const voi
   p.page_size = page_size; p.num_pages = num_pages; p.window = window; p.split_size = split_size;
   p.max_splits = max_splits; p.scale = scale; p.error_word = error_word;
   cudaStream_t s = (cudaStream_t)stream;
-  if (head_dim == 64) return launch_decode<64>(q, k_pool, v_pool, out, part_acc, part_ml, p, rows, s);
-  return launch_decode<128>(q, k_pool, v_pool, out, part_acc, part_ml, p, rows, s);
+  if (head_dim == 64) return launch_decode<64>(q, k_pool, v_pool, out, part_acc, part_ml, counters, p, rows, s);
+  return launch_decode<128>(q, k_pool, v_pool, out, part_acc, part_ml, counters, p, rows, s);
 }

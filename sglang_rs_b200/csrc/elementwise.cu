@@ -53,6 +53,57 @@ __global__ void add_rmsnorm_kernel(float* __restrict__ residual, const T* __rest
     dst[i] = srb_from_float<T>(staged[i] * inv * weight[i]);
 }
 
+// The same for widths that are a multiple of 4 and fit 4 * ITER values per thread: the row
+// stays in registers, every load of a thread is issued before the first use (the row is
+// small and the kernel is bound by latency, not by bandwidth), and the additions keep the
+// order residual, delta, part 0, part 1, ...
+template <typename T, int ITER>
+__global__ void __launch_bounds__(1024)
+add_rmsnorm_vec_kernel(float* __restrict__ residual, const T* __restrict__ delta,
+                       const float* __restrict__ delta_parts, int num_parts, size_t part_stride,
+                       const float* __restrict__ weight, T* __restrict__ out, const int* __restrict__ row_index,
+                       int width, float eps, int write_residual) {
+  __shared__ float scratch[33];
+  const int row = blockIdx.x;
+  const size_t src = (size_t)(row_index ? row_index[row] : row) * width;
+  float4 x[ITER];
+  float partial = 0.f;
+#pragma unroll
+  for (int it = 0; it < ITER; ++it) {
+    const int i = (it * blockDim.x + threadIdx.x) * 4;
+    x[it] = make_float4(0.f, 0.f, 0.f, 0.f);
+    if (i < width) {
+      x[it] = *reinterpret_cast<const float4*>(residual + src + i);
+      if (delta) {
+        x[it].x += srb_to_float(delta[src + i]);
+        x[it].y += srb_to_float(delta[src + i + 1]);
+        x[it].z += srb_to_float(delta[src + i + 2]);
+        x[it].w += srb_to_float(delta[src + i + 3]);
+      }
+      for (int part = 0; part < num_parts; ++part) {
+        const float4 d = *reinterpret_cast<const float4*>(delta_parts + part * part_stride + src + i);
+        x[it].x += d.x; x[it].y += d.y; x[it].z += d.z; x[it].w += d.w;
+      }
+      if (write_residual) *reinterpret_cast<float4*>(residual + src + i) = x[it];
+      partial += x[it].x * x[it].x + x[it].y * x[it].y + x[it].z * x[it].z + x[it].w * x[it].w;
+    }
+  }
+  const float total = srb_block_sum(partial, scratch);
+  const float inv = 1.0f / sqrtf(total / (float)width + eps);
+  T* dst = out + (size_t)row * width;
+#pragma unroll
+  for (int it = 0; it < ITER; ++it) {
+    const int i = (it * blockDim.x + threadIdx.x) * 4;
+    if (i < width) {
+      const float4 w = *reinterpret_cast<const float4*>(weight + i);
+      dst[i] = srb_from_float<T>(x[it].x * inv * w.x);
+      dst[i + 1] = srb_from_float<T>(x[it].y * inv * w.y);
+      dst[i + 2] = srb_from_float<T>(x[it].z * inv * w.z);
+      dst[i + 3] = srb_from_float<T>(x[it].w * inv * w.w);
+    }
+  }
+}
+
 // out[row, j] = silu(gate_up[row, j]) * gate_up[row, inner + j]
 template <typename T>
 __global__ void silu_mul_kernel(const T* __restrict__ gate_up, T* __restrict__ out, int rows, int inner) {
@@ -100,6 +151,23 @@ template <typename T>
 static int launch_add_rmsnorm(float* residual, const void* delta, const float* delta_parts, int num_parts,
                               size_t part_stride, const float* weight, void* out, const int* row_index, int rows,
                               int width, float eps, int write_residual, cudaStream_t s) {
+  // widths that are a multiple of 4 (so float4 accesses stay aligned) and fit the registers
+  const bool aligned = width % 4 == 0 && (((uintptr_t)residual | (uintptr_t)delta_parts | (uintptr_t)weight) & 15) == 0 &&
+                       part_stride % 4 == 0;
+  if (aligned && width <= 4 * 1024 * 2) {
+    int threads = ((width / 4 + 31) / 32) * 32;
+    if (threads > 1024) threads = 1024;
+    if (width <= 4 * threads)
+      add_rmsnorm_vec_kernel<T, 1><<<rows, threads, 0, s>>>(residual, (const T*)delta, delta_parts, num_parts,
+                                                            part_stride, weight, (T*)out, row_index, width, eps,
+                                                            write_residual);
+    else
+      add_rmsnorm_vec_kernel<T, 2><<<rows, threads, 0, s>>>(residual, (const T*)delta, delta_parts, num_parts,
+                                                            part_stride, weight, (T*)out, row_index, width, eps,
+                                                            write_residual);
+    SRB_LAUNCH_CHECK("add_rmsnorm");
+    return SRB_OK;
+  }
   const size_t smem = (size_t)(width + 33) * sizeof(float);
   if (smem > 227 * 1024) SRB_FAIL("add_rmsnorm: width %d needs %zu bytes of shared memory (limit 232448)", width, smem);
   if (smem > 48 * 1024)

@@ -25,8 +25,8 @@ __global__ void qk_norm_rope_kv_kernel(const T* __restrict__ qkv, const float* _
                                        const float* __restrict__ q_norm, const float* __restrict__ k_norm,
                                        float eps, const float* __restrict__ inv_freq, int rotary_dim,
                                        int interleaved, int n_q, int n_kv, int head_dim, int page_size,
-                                       int num_pages, int heads_to_do, int* error_word) {
-  extern __shared__ float staged_all[];                // ROPE_WARPS * head_dim floats
+                                       int num_pages, int heads_to_do, int vector_ok, int* error_word) {
+  extern __shared__ __align__(16) float staged_all[];  // ROPE_WARPS * head_dim floats
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int row = blockIdx.x;
   const int head = blockIdx.y * ROPE_WARPS + warp;     // q heads, then k heads, then v heads
@@ -39,15 +39,28 @@ __global__ void qk_norm_rope_kv_kernel(const T* __restrict__ qkv, const float* _
   const float* norm_weight = is_q ? q_norm : (is_k ? k_norm : nullptr);
 
   float partial = 0.f;
-  for (int e = lane; e < head_dim; e += 32) {
-    float x = 0.f;
-    if (num_parts == 0) {
-      x = srb_to_float(qkv[src_offset + e]);
-    } else {
-      for (int part = 0; part < num_parts; ++part) x += qkv_parts[part * part_stride + src_offset + e];
+  if (num_parts > 0 && vector_ok) {
+    // four consecutive values per lane and part: all loads of a lane are in flight together
+    for (int e = lane * 4; e < head_dim; e += 128) {
+      float4 x = make_float4(0.f, 0.f, 0.f, 0.f);
+      for (int part = 0; part < num_parts; ++part) {
+        const float4 d = *reinterpret_cast<const float4*>(qkv_parts + part * part_stride + src_offset + e);
+        x.x += d.x; x.y += d.y; x.z += d.z; x.w += d.w;
+      }
+      *reinterpret_cast<float4*>(staged + e) = x;
+      partial += x.x * x.x + x.y * x.y + x.z * x.z + x.w * x.w;
     }
-    staged[e] = x;
-    partial += x * x;
+  } else {
+    for (int e = lane; e < head_dim; e += 32) {
+      float x = 0.f;
+      if (num_parts == 0) {
+        x = srb_to_float(qkv[src_offset + e]);
+      } else {
+        for (int part = 0; part < num_parts; ++part) x += qkv_parts[part * part_stride + src_offset + e];
+      }
+      staged[e] = x;
+      partial += x * x;
+    }
   }
   if (norm_weight) {
     const float total = srb_warp_sum(partial);
@@ -105,6 +118,9 @@ extern "C" int srb_qk_norm_rope_kv(const void* qkv, const float* qkv_parts, int 
   if (num_parts < 0 || (num_parts > 0 && !qkv_parts) || (num_parts == 0 && !qkv))
     SRB_FAIL("qk_norm_rope_kv: the projection is missing");
   const int heads = slots ? n_q + 2 * n_kv : n_q;
+  // float4 loads of the partial sums need 16-byte rows
+  const int vector_ok = num_parts > 0 && head_dim % 4 == 0 && qkv_stride % 4 == 0 && part_stride % 4 == 0 &&
+                        ((uintptr_t)qkv_parts & 15) == 0;
   dim3 grid(rows, (heads + ROPE_WARPS - 1) / ROPE_WARPS);
   const size_t smem = (size_t)ROPE_WARPS * head_dim * sizeof(float);
   cudaStream_t s = (cudaStream_t)stream;
@@ -112,12 +128,12 @@ extern "C" int srb_qk_norm_rope_kv(const void* qkv, const float* qkv_parts, int 
     qk_norm_rope_kv_kernel<float><<<grid, ROPE_WARPS * 32, smem, s>>>(
         (const float*)qkv, qkv_parts, num_parts, (size_t)part_stride, qkv_stride, (float*)q_out, (float*)k_pool, (float*)v_pool, positions, slots, q_norm,
         k_norm, eps, inv_freq, rotary_dim, interleaved, n_q, n_kv, head_dim, page_size, num_pages, heads,
-        error_word);
+        vector_ok, error_word);
   else if (dtype == SRB_DTYPE_BF16)
     qk_norm_rope_kv_kernel<__nv_bfloat16><<<grid, ROPE_WARPS * 32, smem, s>>>(
         (const __nv_bfloat16*)qkv, qkv_parts, num_parts, (size_t)part_stride, qkv_stride, (__nv_bfloat16*)q_out, (__nv_bfloat16*)k_pool,
         (__nv_bfloat16*)v_pool, positions, slots, q_norm, k_norm, eps, inv_freq, rotary_dim, interleaved, n_q,
-        n_kv, head_dim, page_size, num_pages, heads, error_word);
+        n_kv, head_dim, page_size, num_pages, heads, vector_ok, error_word);
   else
     SRB_FAIL("qk_norm_rope_kv: unknown dtype %d", dtype);
   SRB_LAUNCH_CHECK("qk_norm_rope_kv");

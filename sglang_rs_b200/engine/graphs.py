@@ -157,7 +157,8 @@ class DecodeGraphs:
                              device=self.device)
             keep += [acc, ml]
             ctx.paged[key] = PagedBatch(part(f"table{g}").view(bucket, stride), part(f"slots{g}"),
-                                        [AttentionLaunch(0, bucket, StepPlanner.SPLIT_SIZE, splits[g])], acc, ml)
+                                        [AttentionLaunch(0, bucket, StepPlanner.SPLIT_SIZE, splits[g])], acc, ml,
+                                        self.planner.counters)
         return ctx, part("logit_rows"), keep
 
     def _capture(self, key, step: CapturedStep, groups, bucket, stride, splits) -> None:

@@ -54,6 +54,8 @@ class PagedBatch:
     launches: List[AttentionLaunch]
     scratch_acc: Optional[torch.Tensor] = None
     scratch_ml: Optional[torch.Tensor] = None
+    #: zeroed ints with which the blocks of a split run find out which of them merges the splits
+    counters: Optional[torch.Tensor] = None
 
 
 @dataclass
@@ -95,6 +97,7 @@ class StepPlanner:
         self._scratch_acc_width = max((w[0] for w in scratch_widths), default=0)
         self._scratch_ml_width = max((w[1] for w in scratch_widths), default=0)
         self._scratch: Dict[str, torch.Tensor] = {}
+        self.counters = torch.zeros(1 << 16, dtype=torch.int32, device=self.device)
         self.last_upload_bytes = 0
 
     # ------------------------------------------------------------------ flattening
@@ -205,7 +208,7 @@ class StepPlanner:
             scratch_ml = self._scratch_tensor("ml", need_ml)
         if rows > split_rows:
             launches.append(AttentionLaunch(split_rows, rows, 0, 1, tiles_d))
-        return PagedBatch(table_d, slots_d, launches, scratch_acc, scratch_ml)
+        return PagedBatch(table_d, slots_d, launches, scratch_acc, scratch_ml, self.counters)
 
     def _scratch_tensor(self, name: str, floats: int) -> torch.Tensor:
         current = self._scratch.get(name)

@@ -199,12 +199,14 @@ def paged_attention(q: torch.Tensor, k_pool: torch.Tensor, v_pool: torch.Tensor,
                     positions: torch.Tensor, row_request: torch.Tensor, block_table: torch.Tensor, *,
                     scale: float, window: int, split_size: int, max_splits: int,
                     scratch_acc: Optional[torch.Tensor], scratch_ml: Optional[torch.Tensor],
-                    error_word: torch.Tensor) -> None:
+                    error_word: torch.Tensor, counters: Optional[torch.Tensor] = None) -> None:
     """out[r, h, :] = softmax over the keys row r may see of (q . k) * scale, times v.
 
     q, out: [rows, n_q, head_dim]; pools [pages, n_kv, page_size, head_dim]; block_table
     [requests, stride].  ``split_size`` 0 walks all keys in one block per (row, kv head);
-    otherwise partials go through the scratch tensors and are merged in split order."""
+    otherwise partials go through the scratch tensors and are merged in split order.
+    ``counters`` (int32, zero, at least rows * n_kv entries; left zero) lets the tensor-core
+    kernel merge the splits itself instead of launching a second kernel."""
     _need(q, "q"); _need(out, "out", q.dtype); _need(k_pool, "k_pool", q.dtype); _need(v_pool, "v_pool", q.dtype)
     _need(positions, "positions", torch.int32); _need(row_request, "row_request", torch.int32)
     _need(block_table, "block_table", torch.int32)
@@ -220,11 +222,15 @@ def paged_attention(q: torch.Tensor, k_pool: torch.Tensor, v_pool: torch.Tensor,
     if split_size == 128 and q.dtype == torch.bfloat16 and head_dim in (64, 128) and n_q // n_kv <= 16:
         # sizes the tensor-core kernel takes (srb_decode_attention_supports states the same rule)
         fast = load_library("attention_decode")
+        if counters is not None:
+            _need(counters, "counters", torch.int32)
+            if counters.numel() < rows * n_kv:
+                counters = None
         _check(fast, fast.srb_decode_attention(
-            _ptr(q), _ptr(k_pool), _ptr(v_pool), _ptr(out), _ptr(scratch_acc), _ptr(scratch_ml), _ptr(positions),
-            _ptr(row_request), _ptr(block_table), block_table.stride(0), rows, n_q, n_kv, head_dim, page_size,
-            num_pages, int(window), int(split_size), int(max_splits), ctypes.c_float(scale), _ptr(error_word),
-            _stream()), launches=2)
+            _ptr(q), _ptr(k_pool), _ptr(v_pool), _ptr(out), _ptr(scratch_acc), _ptr(scratch_ml), _ptr(counters),
+            _ptr(positions), _ptr(row_request), _ptr(block_table), block_table.stride(0), rows, n_q, n_kv, head_dim,
+            page_size, num_pages, int(window), int(split_size), int(max_splits), ctypes.c_float(scale),
+            _ptr(error_word), _stream()), launches=1 if counters is not None else 2)
         return
     lib = load_library("attention")
     _check(lib, lib.srb_paged_attention(

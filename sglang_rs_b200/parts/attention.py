@@ -111,6 +111,7 @@ class GroupedQueryAttention(Mixer):
                                 ctx.row_request[b:e], batch.block_table, scale=self.scale,
                                 window=self.window or 0, split_size=launch.split_size,
                                 max_splits=launch.max_splits, scratch_acc=batch.scratch_acc,
-                                scratch_ml=batch.scratch_ml, error_word=ctx.error_word)
+                                scratch_ml=batch.scratch_ml, error_word=ctx.error_word,
+                                counters=batch.counters)
         return ops.linear(out.view(rows, self.n_q * self.d), self.w_o, self.b_o, error_word=ctx.error_word,
                           partial_ok=True)

@@ -222,7 +222,7 @@ def expected_attention(case, scale):
     return torch.cat(outs)
 
 
-def run_attention(case, scale, split_size):
+def run_attention(case, scale, split_size, counters=None):
     q = case["q"]
     rows, n_q, d = q.shape
     out = torch.full_like(q, float("nan"))
@@ -237,9 +237,25 @@ def run_attention(case, scale, split_size):
         ml = torch.full((m,), float("nan"), device=DEV)
     ops.paged_attention(q, case["k_pool"], case["v_pool"], out, case["positions"], case["row_request"], case["table"],
                         scale=scale, window=case["window"] or 0, split_size=split_size, max_splits=max_splits,
-                        scratch_acc=acc, scratch_ml=ml, error_word=word)
+                        scratch_acc=acc, scratch_ml=ml, error_word=word, counters=counters)
     ops.raise_on_error_word(word)
     return out
+
+
+@pytest.mark.parametrize("n_q,n_kv,d,page,window", [(8, 2, 64, 16, None), (16, 1, 128, 8, 300), (6, 3, 128, 32, None)])
+def test_last_block_merges_the_splits(n_q, n_kv, d, page, window):
+    """With counters the tensor-core kernel merges its own splits: the same numbers as with the
+    separate merge kernel, and the counters are zero again afterwards, twice in a row."""
+    lengths, rows = (1, 129, 700, 64, 257, 1000), (1, 1, 1, 1, 1, 1)
+    case = paged_case(torch.bfloat16, n_q, n_kv, d, page, lengths, rows, window, seed=d)
+    scale = 1.0 / math.sqrt(d)
+    separate = run_attention(case, scale, 128)
+    counters = torch.zeros(64, dtype=torch.int32, device=DEV)
+    for _ in range(2):
+        fused = run_attention(case, scale, 128, counters)
+        assert torch.equal(fused, separate)
+        assert int(counters.abs().sum()) == 0
+    close(fused, expected_attention(case, scale), torch.bfloat16, "fused merge")
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
