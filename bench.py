@@ -116,6 +116,8 @@ def main() -> int:
     parser.add_argument("--batch", type=int, default=8)
     parser.add_argument("--context", type=int, default=2048, help="tokens each request holds when decoding starts")
     parser.add_argument("--skip-points", action="store_true", help="leave out batch 1 / 64 and the prefill")
+    parser.add_argument("--only-prefill", action="store_true",
+                        help="run only the 2,048-token prefill (for profiling); prints its own short line")
     args = parser.parse_args()
 
     if args.impl == "reference":
@@ -202,6 +204,21 @@ def main() -> int:
                 "context": context_mid, "clocks": clocks}
 
     engine = make_engine(max(args.batch, 1), args.steps)
+    if args.only_prefill:
+        from sglang_rs_b200.engine.runner import StepEntry
+        times = []
+        for i in range(warmup + args.steps):
+            handle = engine.cache.open(f"prefill-{i}")
+            torch.cuda.synchronize()
+            begin, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            begin.record()
+            engine.runner.step([StepEntry(handle, prompts(1, PREFILL_TOKENS)[0], [PREFILL_TOKENS - 1])])
+            end.record()
+            torch.cuda.synchronize()
+            engine.cache.close(handle)
+            times.append(begin.elapsed_time(end))
+        print(json.dumps({"prefill_ms": round(min(times[warmup:]), 3), "tokens": PREFILL_TOKENS, "layers": args.layers}))
+        return 0
     main_run = decode_run(engine, args.batch, args.steps, sample_clocks=True)
     value = args.batch * 1e3 / main_run["step_ms"]
     need = decode_bytes(config, args.batch, main_run["context"])

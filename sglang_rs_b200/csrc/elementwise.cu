@@ -19,6 +19,20 @@ __global__ void embedding_kernel(const int* __restrict__ ids, const T* __restric
   if (bad && threadIdx.x == 0) atomicOr(error_word, SRB_FLAG_BAD_TOKEN);
   const T* src = table + (size_t)(bad ? 0 : id) * width;
   float* dst = residual + (size_t)row * width;
+  if (sizeof(T) == 2 && width % 8 == 0 && (((uintptr_t)table | (uintptr_t)residual) & 15) == 0) {
+    for (int i = threadIdx.x * 8; i < width; i += blockDim.x * 8) {
+      const uint4 raw = *reinterpret_cast<const uint4*>(src + i);
+      const __nv_bfloat162* pair = reinterpret_cast<const __nv_bfloat162*>(&raw);
+      float4 lo, hi;
+      const float2 a = __bfloat1622float2(pair[0]), b = __bfloat1622float2(pair[1]);
+      const float2 c = __bfloat1622float2(pair[2]), d = __bfloat1622float2(pair[3]);
+      lo = bad ? make_float4(0.f, 0.f, 0.f, 0.f) : make_float4(a.x, a.y, b.x, b.y);
+      hi = bad ? make_float4(0.f, 0.f, 0.f, 0.f) : make_float4(c.x, c.y, d.x, d.y);
+      *reinterpret_cast<float4*>(dst + i) = lo;
+      *reinterpret_cast<float4*>(dst + i + 4) = hi;
+    }
+    return;
+  }
   for (int i = threadIdx.x; i < width; i += blockDim.x) dst[i] = bad ? 0.f : srb_to_float(src[i]);
 }
 
@@ -117,6 +131,29 @@ __global__ void silu_mul_kernel(const T* __restrict__ gate_up, T* __restrict__ o
   }
 }
 
+// The same with eight bfloat16 values (16 bytes) per thread and access; `inner` a multiple of 8.
+__global__ void silu_mul_bf16x8_kernel(const __nv_bfloat16* __restrict__ gate_up, __nv_bfloat16* __restrict__ out,
+                                       int rows, int inner) {
+  const int per_row = inner / 8;
+  const size_t total = (size_t)rows * per_row;
+  for (size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x; idx < total;
+       idx += (size_t)gridDim.x * blockDim.x) {
+    const size_t row = idx / per_row, col = (idx % per_row) * 8;
+    const uint4 g4 = *reinterpret_cast<const uint4*>(gate_up + row * 2 * inner + col);
+    const uint4 u4 = *reinterpret_cast<const uint4*>(gate_up + row * 2 * inner + inner + col);
+    const __nv_bfloat162* g2 = reinterpret_cast<const __nv_bfloat162*>(&g4);
+    const __nv_bfloat162* u2 = reinterpret_cast<const __nv_bfloat162*>(&u4);
+    uint4 o4;
+    __nv_bfloat162* o2 = reinterpret_cast<__nv_bfloat162*>(&o4);
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      const float2 g = __bfloat1622float2(g2[j]), u = __bfloat1622float2(u2[j]);
+      o2[j] = __floats2bfloat162_rn(g.x / (1.0f + expf(-g.x)) * u.x, g.y / (1.0f + expf(-g.y)) * u.y);
+    }
+    *reinterpret_cast<uint4*>(out + row * inner + col) = o4;
+  }
+}
+
 template <typename T>
 __global__ void add_bias_kernel(T* __restrict__ values, const float* __restrict__ bias, int rows, int width) {
   const size_t total = (size_t)rows * width;
@@ -205,7 +242,11 @@ extern "C" int srb_silu_mul(const void* gate_up, void* out, int rows, int inner,
   const int grid = elementwise_grid((size_t)rows * inner, 256);
   if (dtype == SRB_DTYPE_F32)
     silu_mul_kernel<float><<<grid, 256, 0, s>>>((const float*)gate_up, (float*)out, rows, inner);
-  else if (dtype == SRB_DTYPE_BF16)
+  else if (dtype == SRB_DTYPE_BF16 && inner % 8 == 0 && (((uintptr_t)gate_up | (uintptr_t)out) & 15) == 0) {
+    size_t blocks = ((size_t)rows * (inner / 8) + 255) / 256;
+    if (blocks > 148 * 64) blocks = 148 * 64;
+    silu_mul_bf16x8_kernel<<<(int)blocks, 256, 0, s>>>((const __nv_bfloat16*)gate_up, (__nv_bfloat16*)out, rows, inner);
+  } else if (dtype == SRB_DTYPE_BF16)
     silu_mul_kernel<__nv_bfloat16><<<grid, 256, 0, s>>>((const __nv_bfloat16*)gate_up, (__nv_bfloat16*)out, rows,
                                                         inner);
   else

@@ -50,6 +50,20 @@ __global__ void qk_norm_rope_kv_kernel(const T* __restrict__ qkv, const float* _
       *reinterpret_cast<float4*>(staged + e) = x;
       partial += x.x * x.x + x.y * x.y + x.z * x.z + x.w * x.w;
     }
+  } else if (vector_ok) {
+    for (int e = lane * 4; e < head_dim; e += 128) {
+      float4 x;
+      if (sizeof(T) == 2) {
+        const uint2 raw = *reinterpret_cast<const uint2*>(qkv + src_offset + e);
+        const float2 a = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&raw.x));
+        const float2 b = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&raw.y));
+        x = make_float4(a.x, a.y, b.x, b.y);
+      } else {
+        x = *reinterpret_cast<const float4*>(qkv + src_offset + e);
+      }
+      *reinterpret_cast<float4*>(staged + e) = x;
+      partial += x.x * x.x + x.y * x.y + x.z * x.z + x.w * x.w;
+    }
   } else {
     for (int e = lane; e < head_dim; e += 32) {
       float x = 0.f;
@@ -97,6 +111,20 @@ __global__ void qk_norm_rope_kv_kernel(const T* __restrict__ qkv, const float* _
         (((size_t)(slot / page_size) * n_kv + kv_head) * page_size + (slot % page_size)) * head_dim;
     dst = (is_k ? k_pool : v_pool) + offset;
   }
+  if (vector_ok) {
+    for (int e = lane * 4; e < head_dim; e += 128) {
+      const float4 x = *reinterpret_cast<const float4*>(staged + e);
+      if (sizeof(T) == 2) {
+        uint2 raw;
+        *reinterpret_cast<__nv_bfloat162*>(&raw.x) = __floats2bfloat162_rn(x.x, x.y);
+        *reinterpret_cast<__nv_bfloat162*>(&raw.y) = __floats2bfloat162_rn(x.z, x.w);
+        *reinterpret_cast<uint2*>(dst + e) = raw;
+      } else {
+        *reinterpret_cast<float4*>(dst + e) = x;
+      }
+    }
+    return;
+  }
   for (int e = lane; e < head_dim; e += 32) dst[e] = srb_from_float<T>(staged[e]);
 }
 
@@ -118,9 +146,10 @@ extern "C" int srb_qk_norm_rope_kv(const void* qkv, const float* qkv_parts, int 
   if (num_parts < 0 || (num_parts > 0 && !qkv_parts) || (num_parts == 0 && !qkv))
     SRB_FAIL("qk_norm_rope_kv: the projection is missing");
   const int heads = slots ? n_q + 2 * n_kv : n_q;
-  // float4 loads of the partial sums need 16-byte rows
-  const int vector_ok = num_parts > 0 && head_dim % 4 == 0 && qkv_stride % 4 == 0 && part_stride % 4 == 0 &&
-                        ((uintptr_t)qkv_parts & 15) == 0;
+  // four values per lane and access need 16-byte rows
+  const int vector_ok = head_dim % 4 == 0 && qkv_stride % 4 == 0 && part_stride % 4 == 0 &&
+                        (((uintptr_t)qkv_parts | (uintptr_t)qkv | (uintptr_t)q_out | (uintptr_t)k_pool |
+                          (uintptr_t)v_pool) & 15) == 0;
   dim3 grid(rows, (heads + ROPE_WARPS - 1) / ROPE_WARPS);
   const size_t smem = (size_t)ROPE_WARPS * head_dim * sizeof(float);
   cudaStream_t s = (cudaStream_t)stream;

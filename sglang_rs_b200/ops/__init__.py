@@ -398,6 +398,7 @@ def sample(logits: torch.Tensor, temperature: Optional[torch.Tensor], uniform: O
     if temperature is not None:
         _need(temperature, "temperature", torch.float32); _need(uniform, "uniform", torch.float32)
     lib = load_library("sampling")
+    scratch = torch.empty(lib.srb_sample_scratch_floats(rows), dtype=torch.float32, device=logits.device)
     _check(lib, lib.srb_sample(_ptr(logits), rows, vocab, logits.stride(0), _ptr(temperature), _ptr(uniform),
-                               _ptr(out), _stream()))
+                               _ptr(out), _ptr(scratch), _stream()), launches=2)
     return out
