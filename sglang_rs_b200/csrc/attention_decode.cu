@@ -19,6 +19,7 @@
 #include "mma_helpers.cuh"
 
 SRB_DEFINE_LAST_ERROR()
+SRB_DEFINE_PDL_SWITCH()
 
 #define DEC_WARPS 4
 #define DEC_KEYS 32                       // keys per warp
@@ -37,6 +38,8 @@ decode_attention_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16
   extern __shared__ __align__(128) unsigned char smem_raw[];
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int row = blockIdx.z, kv_head = blockIdx.y, split = blockIdx.x;
+  srb_launch_dependents();
+  srb_grid_dependency_wait();
   const int pos = p.positions[row];
   int lo, hi;
   row_key_range(p, pos, split, lo, hi);
@@ -274,10 +277,9 @@ static int launch_decode(const void* q, const void* k_pool, const void* v_pool, 
   SRB_CUDA_CALL(cudaFuncSetAttribute(decode_attention_kernel<D>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                      (int)smem));
   dim3 grid(p.max_splits, p.n_kv, rows);
-  decode_attention_kernel<D><<<grid, DEC_WARPS * 32, smem, s>>>(
-      (const __nv_bfloat16*)q, (const __nv_bfloat16*)k_pool, (const __nv_bfloat16*)v_pool, part_acc, part_ml,
-      (__nv_bfloat16*)out, counters, p);
-  SRB_LAUNCH_CHECK("decode_attention");
+  SRB_CUDA_CALL(srb_launch(decode_attention_kernel<D>, grid, dim3(DEC_WARPS * 32), smem, s, (const __nv_bfloat16*)q,
+                           (const __nv_bfloat16*)k_pool, (const __nv_bfloat16*)v_pool, part_acc, part_ml,
+                           (__nv_bfloat16*)out, counters, p));
   if (counters) return SRB_OK;
   dim3 cgrid(rows, p.n_q);
   attention_combine_kernel<__nv_bfloat16><<<cgrid, 64, 0, s>>>(part_acc, part_ml, (__nv_bfloat16*)out, p);

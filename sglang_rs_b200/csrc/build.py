@@ -144,11 +144,27 @@ def compile_library(name: str) -> str:
     return target
 
 
+#: whether kernels that support it are launched with programmatic dependent launch
+_pdl = os.environ.get("SRB_PDL", "1") not in ("0", "", "off", "false")
+
+
+def set_pdl(on: bool) -> None:
+    """Switches programmatic dependent launch (a kernel's set-up overlaps the tail of the
+    kernel before it) for the libraries that are loaded and for those loaded later."""
+    global _pdl
+    _pdl = bool(on)
+    for library in _loaded.values():
+        if hasattr(library, "srb_set_pdl"):
+            library.srb_set_pdl(int(_pdl))
+
+
 def load_library(name: str) -> ctypes.CDLL:
     library = _loaded.get(name)
     if library is None:
         library = ctypes.CDLL(compile_library(name))
         library.srb_last_error.restype = ctypes.c_char_p
+        if hasattr(library, "srb_set_pdl"):
+            library.srb_set_pdl(int(_pdl))
         _loaded[name] = library
     return library
 

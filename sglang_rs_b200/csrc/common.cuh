@@ -94,3 +94,34 @@ __device__ __forceinline__ float srb_block_sum(float v, float* scratch /* >= 33 
   __syncthreads();
   return scratch[32];
 }
+
+// ---- programmatic dependent launch ------------------------------------------------------
+// A kernel launched through srb_launch with the switch on may become resident while the
+// kernel before it in the stream is still running: its set-up (barriers, tensor memory,
+// loads of weights that no earlier kernel writes) overlaps that kernel's tail.  Such a
+// kernel calls srb_grid_dependency_wait() before it reads or writes anything an earlier
+// kernel may touch; the call returns once every earlier kernel has completed and its writes
+// are visible.  srb_launch_dependents() tells the device that the next kernel may be brought
+// in.  Without the launch attribute both calls do nothing.
+static int srb_pdl_enabled = 0;
+#define SRB_DEFINE_PDL_SWITCH() \
+  extern "C" void srb_set_pdl(int on) { srb_pdl_enabled = on; }
+
+__device__ __forceinline__ void srb_grid_dependency_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void srb_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+
+template <typename... KernelArgs, typename... Args>
+static cudaError_t srb_launch(void (*kernel)(KernelArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream,
+                              Args... args) {
+  cudaLaunchConfig_t config = {};
+  config.gridDim = grid;
+  config.blockDim = block;
+  config.dynamicSmemBytes = smem;
+  config.stream = stream;
+  cudaLaunchAttribute attribute[1];
+  attribute[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attribute[0].val.programmaticStreamSerializationAllowed = 1;
+  config.attrs = attribute;
+  config.numAttrs = srb_pdl_enabled ? 1 : 0;
+  return cudaLaunchKernelEx(&config, kernel, KernelArgs(args)...);
+}

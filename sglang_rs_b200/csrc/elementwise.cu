@@ -8,11 +8,14 @@
 #include "common.cuh"
 
 SRB_DEFINE_LAST_ERROR()
+SRB_DEFINE_PDL_SWITCH()
 
 // residual[row, :] = float(table[ids[row], :]); a bad id writes zeros and flags.
 template <typename T>
 __global__ void embedding_kernel(const int* __restrict__ ids, const T* __restrict__ table,
                                  float* __restrict__ residual, int width, int vocab, int* error_word) {
+  srb_launch_dependents();
+  srb_grid_dependency_wait();
   const int row = blockIdx.x;
   const int id = ids[row];
   const bool bad = id < 0 || id >= vocab;
@@ -49,6 +52,8 @@ __global__ void add_rmsnorm_kernel(float* __restrict__ residual, const T* __rest
                                    int write_residual) {
   extern __shared__ float staged[];          // width floats, then 33 floats of scratch
   float* scratch = staged + width;
+  srb_launch_dependents();
+  srb_grid_dependency_wait();
   const int row = blockIdx.x;
   const size_t src = (size_t)(row_index ? row_index[row] : row) * width;
   float partial = 0.f;
@@ -78,6 +83,8 @@ add_rmsnorm_vec_kernel(float* __restrict__ residual, const T* __restrict__ delta
                        const float* __restrict__ weight, T* __restrict__ out, const int* __restrict__ row_index,
                        int width, float eps, int write_residual) {
   __shared__ float scratch[33];
+  srb_launch_dependents();
+  srb_grid_dependency_wait();
   const int row = blockIdx.x;
   const size_t src = (size_t)(row_index ? row_index[row] : row) * width;
   float4 x[ITER];
@@ -174,10 +181,11 @@ extern "C" int srb_embedding(const int* ids, const void* table, float* residual,
   if (width <= 0 || vocab <= 0) SRB_FAIL("embedding: width %d and vocabulary %d must be positive", width, vocab);
   cudaStream_t s = (cudaStream_t)stream;
   if (dtype == SRB_DTYPE_F32)
-    embedding_kernel<float><<<rows, 256, 0, s>>>(ids, (const float*)table, residual, width, vocab, error_word);
+    SRB_CUDA_CALL(srb_launch(embedding_kernel<float>, dim3(rows), dim3(256), 0, s, ids, (const float*)table, residual,
+                             width, vocab, error_word));
   else if (dtype == SRB_DTYPE_BF16)
-    embedding_kernel<__nv_bfloat16><<<rows, 256, 0, s>>>(ids, (const __nv_bfloat16*)table, residual, width,
-                                                         vocab, error_word);
+    SRB_CUDA_CALL(srb_launch(embedding_kernel<__nv_bfloat16>, dim3(rows), dim3(256), 0, s, ids,
+                             (const __nv_bfloat16*)table, residual, width, vocab, error_word));
   else
     SRB_FAIL("embedding: unknown dtype %d", dtype);
   SRB_LAUNCH_CHECK("embedding");
@@ -195,13 +203,13 @@ static int launch_add_rmsnorm(float* residual, const void* delta, const float* d
     int threads = ((width / 4 + 31) / 32) * 32;
     if (threads > 1024) threads = 1024;
     if (width <= 4 * threads)
-      add_rmsnorm_vec_kernel<T, 1><<<rows, threads, 0, s>>>(residual, (const T*)delta, delta_parts, num_parts,
-                                                            part_stride, weight, (T*)out, row_index, width, eps,
-                                                            write_residual);
+      SRB_CUDA_CALL(srb_launch(add_rmsnorm_vec_kernel<T, 1>, dim3(rows), dim3(threads), 0, s, residual, (const T*)delta,
+                               delta_parts, num_parts, part_stride, weight, (T*)out, row_index, width, eps,
+                               write_residual));
     else
-      add_rmsnorm_vec_kernel<T, 2><<<rows, threads, 0, s>>>(residual, (const T*)delta, delta_parts, num_parts,
-                                                            part_stride, weight, (T*)out, row_index, width, eps,
-                                                            write_residual);
+      SRB_CUDA_CALL(srb_launch(add_rmsnorm_vec_kernel<T, 2>, dim3(rows), dim3(threads), 0, s, residual, (const T*)delta,
+                               delta_parts, num_parts, part_stride, weight, (T*)out, row_index, width, eps,
+                               write_residual));
     SRB_LAUNCH_CHECK("add_rmsnorm");
     return SRB_OK;
   }
@@ -210,8 +218,9 @@ static int launch_add_rmsnorm(float* residual, const void* delta, const float* d
   if (smem > 48 * 1024)
     SRB_CUDA_CALL(cudaFuncSetAttribute(add_rmsnorm_kernel<T>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
   const int block = width >= 2048 ? 512 : (width >= 512 ? 256 : 128);
-  add_rmsnorm_kernel<T><<<rows, block, smem, s>>>(residual, (const T*)delta, delta_parts, num_parts, part_stride,
-                                                  weight, (T*)out, row_index, width, eps, write_residual);
+  SRB_CUDA_CALL(srb_launch(add_rmsnorm_kernel<T>, dim3(rows), dim3(block), smem, s, residual, (const T*)delta,
+                           delta_parts, num_parts, part_stride, weight, (T*)out, row_index, width, eps,
+                           write_residual));
   SRB_LAUNCH_CHECK("add_rmsnorm");
   return SRB_OK;
 }

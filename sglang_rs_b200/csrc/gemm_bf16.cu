@@ -30,6 +30,7 @@
 #include <unordered_map>
 
 SRB_DEFINE_LAST_ERROR()
+SRB_DEFINE_PDL_SWITCH()
 
 #define GEMM_BLOCK_F 128      // weight rows (features) per block = M of the instruction
 #define GEMM_BLOCK_K 64       // bfloat16 elements per 128-byte swizzle row
@@ -183,10 +184,32 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constan
   tc_fence_after();
   const unsigned tmem_base = tmem_holder;
 
+  srb_launch_dependents();
   if (warp == 0) {
     if (lane == 0) {
       int issued = 0;
-      for (int i = 0; i < num_kb; ++i) {
+      // The weights are written by no kernel of the step, so the first stages of W are
+      // requested before the wait for the kernels ahead; X follows once they have completed.
+      const int early = min(num_kb, STAGES);
+      bool ok = true;
+      for (int i = 0; i < early && ok; ++i) {
+        ok = mbar_wait(smem_u32(&empty_bar[i]), 1u, &abort_flag);      // first use of a stage: free
+        if (!ok) break;
+        const unsigned bar = smem_u32(&full_bar[i]);
+        unsigned char* stage = smem + (size_t)i * STAGE_BYTES;
+        mbar_expect_tx(bar, STAGE_BYTES);
+        const int kx = (kb_begin + i) * GEMM_BLOCK_K;
+        tma_load_2d(smem_u32(stage), &map_w, bar, kx, feature0);
+        if (A_TILES == 2) tma_load_2d(smem_u32(stage + A_BYTES), &map_w, bar, kx, args.up_row_offset + feature0);
+        issued = i + 1;
+      }
+      srb_grid_dependency_wait();
+      for (int i = 0; i < issued; ++i) {
+        unsigned char* stage = smem + (size_t)i * STAGE_BYTES;
+        tma_load_2d(smem_u32(stage + A_TILES * A_BYTES), &map_x, smem_u32(&full_bar[i]), (kb_begin + i) * GEMM_BLOCK_K,
+                    token0);
+      }
+      for (int i = issued; i < num_kb && ok; ++i) {
         const int s = i % STAGES;
         const unsigned phase = (unsigned)(i / STAGES) & 1u;
         if (!mbar_wait(smem_u32(&empty_bar[s]), phase ^ 1u, &abort_flag)) break;
@@ -234,6 +257,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constan
     }
   } else {
     // epilogue: warp w may read TMEM lanes 32 * (w % 4) .. + 32
+    srb_grid_dependency_wait();             // the output buffer may still be read by a kernel ahead
     const int quarter = warp & 3;
     const int feature = feature0 + quarter * 32 + lane;
     bool ok = true;
@@ -331,8 +355,7 @@ static int launch_gemm(const CUtensorMap& map_w, const CUtensorMap& map_x, const
   SRB_CUDA_CALL(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
   dim3 grid((args.tokens + BLOCK_T - 1) / BLOCK_T, (args.features + GEMM_BLOCK_F - 1) / GEMM_BLOCK_F, splits);
   if (grid.y > 65535) SRB_FAIL("gemm_bf16: %d features exceed one launch", args.features);
-  kernel<<<grid, GEMM_THREADS, smem, s>>>(map_w, map_x, args);
-  SRB_LAUNCH_CHECK("gemm_bf16");
+  SRB_CUDA_CALL(srb_launch(kernel, grid, dim3(GEMM_THREADS), smem, s, map_w, map_x, args));
   return SRB_OK;
 }
 

@@ -12,6 +12,7 @@
 #include "common.cuh"
 
 SRB_DEFINE_LAST_ERROR()
+SRB_DEFINE_PDL_SWITCH()
 
 #define ROPE_WARPS 4
 
@@ -27,6 +28,8 @@ __global__ void qk_norm_rope_kv_kernel(const T* __restrict__ qkv, const float* _
                                        int interleaved, int n_q, int n_kv, int head_dim, int page_size,
                                        int num_pages, int heads_to_do, int vector_ok, int* error_word) {
   extern __shared__ __align__(16) float staged_all[];  // ROPE_WARPS * head_dim floats
+  srb_launch_dependents();
+  srb_grid_dependency_wait();
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int row = blockIdx.x;
   const int head = blockIdx.y * ROPE_WARPS + warp;     // q heads, then k heads, then v heads
@@ -154,15 +157,16 @@ extern "C" int srb_qk_norm_rope_kv(const void* qkv, const float* qkv_parts, int 
   const size_t smem = (size_t)ROPE_WARPS * head_dim * sizeof(float);
   cudaStream_t s = (cudaStream_t)stream;
   if (dtype == SRB_DTYPE_F32)
-    qk_norm_rope_kv_kernel<float><<<grid, ROPE_WARPS * 32, smem, s>>>(
-        (const float*)qkv, qkv_parts, num_parts, (size_t)part_stride, qkv_stride, (float*)q_out, (float*)k_pool, (float*)v_pool, positions, slots, q_norm,
-        k_norm, eps, inv_freq, rotary_dim, interleaved, n_q, n_kv, head_dim, page_size, num_pages, heads,
-        vector_ok, error_word);
+    SRB_CUDA_CALL(srb_launch(qk_norm_rope_kv_kernel<float>, grid, dim3(ROPE_WARPS * 32), smem, s, (const float*)qkv,
+                             qkv_parts, num_parts, (size_t)part_stride, qkv_stride, (float*)q_out, (float*)k_pool,
+                             (float*)v_pool, positions, slots, q_norm, k_norm, eps, inv_freq, rotary_dim, interleaved,
+                             n_q, n_kv, head_dim, page_size, num_pages, heads, vector_ok, error_word));
   else if (dtype == SRB_DTYPE_BF16)
-    qk_norm_rope_kv_kernel<__nv_bfloat16><<<grid, ROPE_WARPS * 32, smem, s>>>(
-        (const __nv_bfloat16*)qkv, qkv_parts, num_parts, (size_t)part_stride, qkv_stride, (__nv_bfloat16*)q_out, (__nv_bfloat16*)k_pool,
-        (__nv_bfloat16*)v_pool, positions, slots, q_norm, k_norm, eps, inv_freq, rotary_dim, interleaved, n_q,
-        n_kv, head_dim, page_size, num_pages, heads, vector_ok, error_word);
+    SRB_CUDA_CALL(srb_launch(qk_norm_rope_kv_kernel<__nv_bfloat16>, grid, dim3(ROPE_WARPS * 32), smem, s,
+                             (const __nv_bfloat16*)qkv, qkv_parts, num_parts, (size_t)part_stride, qkv_stride,
+                             (__nv_bfloat16*)q_out, (__nv_bfloat16*)k_pool, (__nv_bfloat16*)v_pool, positions, slots,
+                             q_norm, k_norm, eps, inv_freq, rotary_dim, interleaved, n_q, n_kv, head_dim, page_size,
+                             num_pages, heads, vector_ok, error_word));
   else
     SRB_FAIL("qk_norm_rope_kv: unknown dtype %d", dtype);
   SRB_LAUNCH_CHECK("qk_norm_rope_kv");
