@@ -101,6 +101,7 @@ add_rmsnorm_vec_kernel(float* __restrict__ residual, const T* __restrict__ delta
         x[it].z += srb_to_float(delta[src + i + 2]);
         x[it].w += srb_to_float(delta[src + i + 3]);
       }
+#pragma unroll 4
       for (int part = 0; part < num_parts; ++part) {
         const float4 d = *reinterpret_cast<const float4*>(delta_parts + part * part_stride + src + i);
         x[it].x += d.x; x[it].y += d.y; x[it].z += d.z; x[it].w += d.w;

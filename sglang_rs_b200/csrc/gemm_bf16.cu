@@ -11,8 +11,9 @@
 // out[token][feature], 32 consecutive features per warp store.
 //
 // Modes of the epilogue: bfloat16 store; float store (logits); SiLU(gate) * up, where the
-// block multiplies two row blocks of the stacked gate/up matrix into two accumulators and
-// writes only the product; and float partials per K split, [split][token][feature], which
+// block's 128 weight rows are 64 gate rows over the 64 up rows of the same features, the two
+// halves of the accumulator meet through shared memory and only the product is written; and
+// float partials per K split, [split][token][feature], which
 // the consumer adds in split order (few tokens cannot fill 148 SMs with 128-row blocks alone,
 // so K is cut; the cut depends on the shape only).
 //
@@ -144,14 +145,15 @@ struct GemmArgs {
 };
 
 template <int BLOCK_T, int EPI, int STAGES>
-__global__ void __launch_bounds__(GEMM_THREADS, 1)
+__global__ void __launch_bounds__(GEMM_THREADS, BLOCK_T <= 64 ? 2 : 1)
 gemm_bf16_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_x,
                  GemmArgs args) {
-  constexpr int A_TILES = EPI == EPI_SILU ? 2 : 1;
+  // SiLU mode: the 128 rows of the A tile are 64 gate rows over the 64 up rows of the same features
   constexpr int A_BYTES = GEMM_BLOCK_F * GEMM_BLOCK_K * 2;
   constexpr int B_BYTES = BLOCK_T * GEMM_BLOCK_K * 2;
-  constexpr int STAGE_BYTES = A_TILES * A_BYTES + B_BYTES;
-  constexpr int ACC_COLUMNS = A_TILES * BLOCK_T;
+  constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
+  constexpr int ACC_COLUMNS = BLOCK_T;
+  constexpr int FEATURES_PER_BLOCK = EPI == EPI_SILU ? GEMM_BLOCK_F / 2 : GEMM_BLOCK_F;
   constexpr unsigned TMEM_COLUMNS = ACC_COLUMNS <= 32 ? 32 : ACC_COLUMNS <= 64 ? 64 : ACC_COLUMNS <= 128 ? 128
                                                                                : ACC_COLUMNS <= 256 ? 256 : 512;
   extern __shared__ unsigned char smem_unaligned[];
@@ -163,7 +165,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constan
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   // token tiles are the fastest grid dimension: blocks that share a weight tile run together
   const int token0 = blockIdx.x * BLOCK_T;
-  const int feature0 = blockIdx.y * GEMM_BLOCK_F;
+  const int feature0 = blockIdx.y * FEATURES_PER_BLOCK;
   const int total_k_blocks = (args.k + GEMM_BLOCK_K - 1) / GEMM_BLOCK_K;
   const int kb_begin = blockIdx.z * args.k_blocks_per_split;
   const int kb_end = min(total_k_blocks, kb_begin + args.k_blocks_per_split);
@@ -200,14 +202,13 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constan
         mbar_expect_tx(bar, STAGE_BYTES);
         const int kx = (kb_begin + i) * GEMM_BLOCK_K;
         tma_load_2d(smem_u32(stage), &map_w, bar, kx, feature0);
-        if (A_TILES == 2) tma_load_2d(smem_u32(stage + A_BYTES), &map_w, bar, kx, args.up_row_offset + feature0);
+        if (EPI == EPI_SILU) tma_load_2d(smem_u32(stage + A_BYTES / 2), &map_w, bar, kx, args.up_row_offset + feature0);
         issued = i + 1;
       }
       srb_grid_dependency_wait();
       for (int i = 0; i < issued; ++i) {
         unsigned char* stage = smem + (size_t)i * STAGE_BYTES;
-        tma_load_2d(smem_u32(stage + A_TILES * A_BYTES), &map_x, smem_u32(&full_bar[i]), (kb_begin + i) * GEMM_BLOCK_K,
-                    token0);
+        tma_load_2d(smem_u32(stage + A_BYTES), &map_x, smem_u32(&full_bar[i]), (kb_begin + i) * GEMM_BLOCK_K, token0);
       }
       for (int i = issued; i < num_kb && ok; ++i) {
         const int s = i % STAGES;
@@ -218,8 +219,8 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constan
         mbar_expect_tx(bar, STAGE_BYTES);
         const int kx = (kb_begin + i) * GEMM_BLOCK_K;
         tma_load_2d(smem_u32(stage), &map_w, bar, kx, feature0);
-        if (A_TILES == 2) tma_load_2d(smem_u32(stage + A_BYTES), &map_w, bar, kx, args.up_row_offset + feature0);
-        tma_load_2d(smem_u32(stage + A_TILES * A_BYTES), &map_x, bar, kx, token0);
+        if (EPI == EPI_SILU) tma_load_2d(smem_u32(stage + A_BYTES / 2), &map_w, bar, kx, args.up_row_offset + feature0);
+        tma_load_2d(smem_u32(stage + A_BYTES), &map_x, bar, kx, token0);
         issued = i + 1;
       }
       // copies still in flight write into this block's shared memory: wait for them before leaving
@@ -240,16 +241,12 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constan
         tc_fence_after();
         const unsigned stage = smem_u32(smem + (size_t)s * STAGE_BYTES);
         const unsigned long long a_desc = smem_descriptor(stage);
-        const unsigned long long b_desc = smem_descriptor(stage + A_TILES * A_BYTES);
+        const unsigned long long b_desc = smem_descriptor(stage + A_BYTES);
 #pragma unroll
         for (int k = 0; k < GEMM_BLOCK_K / GEMM_UMMA_K; ++k) {
           const unsigned accumulate = (i > 0 || k > 0) ? 1u : 0u;
           const unsigned long long step = (unsigned long long)((k * GEMM_UMMA_K * 2) >> 4);
           umma_bf16(tmem_base, a_desc + step, b_desc + step, idesc, accumulate);
-          if (A_TILES == 2) {
-            const unsigned long long up_desc = smem_descriptor(stage + A_BYTES);
-            umma_bf16(tmem_base + BLOCK_T, up_desc + step, b_desc + step, idesc, accumulate);
-          }
         }
         umma_commit(smem_u32(&empty_bar[s]));        // frees the stage when these products have read it
       }
@@ -259,43 +256,55 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constan
     // epilogue: warp w may read TMEM lanes 32 * (w % 4) .. + 32
     srb_grid_dependency_wait();             // the output buffer may still be read by a kernel ahead
     const int quarter = warp & 3;
-    const int feature = feature0 + quarter * 32 + lane;
+    // SiLU mode: lanes 0..63 hold gate, lanes 64..127 up of the same 64 features
+    const int feature = EPI == EPI_SILU ? feature0 + (quarter & 1) * 32 + lane : feature0 + quarter * 32 + lane;
     bool ok = true;
     if (num_kb > 0) {
       ok = mbar_wait(smem_u32(&acc_bar), 0, &abort_flag);
       tc_fence_after();
     }
-    if (ok) {
-      const unsigned lane_address = tmem_base + ((unsigned)(quarter * 32) << 16);
+    // The pipeline's stages are idle once the accumulator is complete: in SiLU mode the up half
+    // passes through them to the warps that hold the gate half ([64 features][16 tokens] floats).
+    float* exchange = reinterpret_cast<float*>(smem);
+    const unsigned lane_address = tmem_base + ((unsigned)(quarter * 32) << 16);
 #pragma unroll 1
-      for (int c = 0; c < BLOCK_T; c += 16) {
-        if (token0 + c >= args.tokens) break;          // warp-uniform
-        float acc[16], up[16];
-        if (num_kb > 0) {
-          tmem_load_16(lane_address + c, acc);
-          if (EPI == EPI_SILU) tmem_load_16(lane_address + BLOCK_T + c, up);
-        } else {
+    for (int c = 0; c < BLOCK_T; c += 16) {
+      if (token0 + c >= args.tokens) break;            // the same for all epilogue warps
+      float acc[16];
+      if (ok && num_kb > 0) {
+        tmem_load_16(lane_address + c, acc);
+      } else {
 #pragma unroll
-          for (int j = 0; j < 16; ++j) acc[j] = up[j] = 0.f;
+        for (int j = 0; j < 16; ++j) acc[j] = 0.f;
+      }
+      if (EPI == EPI_SILU) {
+        if (quarter >= 2) {
+#pragma unroll
+          for (int j = 0; j < 16; ++j) exchange[((quarter & 1) * 32 + lane) * 16 + j] = acc[j];
         }
-        if (feature < args.features) {
+        asm volatile("bar.sync 1, 128;" ::: "memory");       // the four epilogue warps only
+        if (quarter < 2 && ok && feature < args.features) {
 #pragma unroll
           for (int j = 0; j < 16; ++j) {
             const int token = token0 + c + j;
             if (token >= args.tokens) break;
-            if (EPI == EPI_BF16) {
-              reinterpret_cast<__nv_bfloat16*>(args.out)[(size_t)token * args.ldo + feature] =
-                  __float2bfloat16_rn(acc[j]);
-            } else if (EPI == EPI_F32) {
-              reinterpret_cast<float*>(args.out)[(size_t)token * args.ldo + feature] = acc[j];
-            } else if (EPI == EPI_SILU) {
-              const float g = acc[j];
-              reinterpret_cast<__nv_bfloat16*>(args.out)[(size_t)token * args.ldo + feature] =
-                  __float2bfloat16_rn(g / (1.0f + expf(-g)) * up[j]);
-            } else {
-              reinterpret_cast<float*>(args.out)[((size_t)blockIdx.z * args.tokens + token) * args.ldo + feature] =
-                  acc[j];
-            }
+            const float g = acc[j], u = exchange[((quarter & 1) * 32 + lane) * 16 + j];
+            reinterpret_cast<__nv_bfloat16*>(args.out)[(size_t)token * args.ldo + feature] =
+                __float2bfloat16_rn(g / (1.0f + expf(-g)) * u);
+          }
+        }
+        asm volatile("bar.sync 1, 128;" ::: "memory");       // the buffer is reused by the next 16 tokens
+      } else if (ok && feature < args.features) {
+#pragma unroll
+        for (int j = 0; j < 16; ++j) {
+          const int token = token0 + c + j;
+          if (token >= args.tokens) break;
+          if (EPI == EPI_BF16) {
+            reinterpret_cast<__nv_bfloat16*>(args.out)[(size_t)token * args.ldo + feature] = __float2bfloat16_rn(acc[j]);
+          } else if (EPI == EPI_F32) {
+            reinterpret_cast<float*>(args.out)[(size_t)token * args.ldo + feature] = acc[j];
+          } else {
+            reinterpret_cast<float*>(args.out)[((size_t)blockIdx.z * args.tokens + token) * args.ldo + feature] = acc[j];
           }
         }
       }
@@ -346,14 +355,17 @@ static int make_map(CUtensorMap* map, const void* base, long long rows, long lon
 template <int BLOCK_T, int EPI>
 static int launch_gemm(const CUtensorMap& map_w, const CUtensorMap& map_x, const GemmArgs& args, int splits,
                        cudaStream_t s) {
-  constexpr int A_TILES = EPI == EPI_SILU ? 2 : 1;
-  constexpr int STAGE_BYTES = A_TILES * GEMM_BLOCK_F * GEMM_BLOCK_K * 2 + BLOCK_T * GEMM_BLOCK_K * 2;
-  constexpr int STAGES = (200 * 1024) / STAGE_BYTES >= 8 ? 8 : (200 * 1024) / STAGE_BYTES;
+  constexpr int STAGE_BYTES = GEMM_BLOCK_F * GEMM_BLOCK_K * 2 + BLOCK_T * GEMM_BLOCK_K * 2;
+  // Few tokens (decode): about 100 KB of stages, so that two blocks share an SM and one block's
+  // set-up and epilogue hide behind the other's stream of weights.  Many tokens: one block per SM.
+  constexpr int BUDGET = BLOCK_T <= 64 ? 108 * 1024 : 200 * 1024;
+  constexpr int STAGES = BUDGET / STAGE_BYTES >= 8 ? 8 : BUDGET / STAGE_BYTES;
   static_assert(STAGES >= 3, "a pipeline needs at least three stages");
+  constexpr int FEATURES_PER_BLOCK = EPI == EPI_SILU ? GEMM_BLOCK_F / 2 : GEMM_BLOCK_F;
   const size_t smem = (size_t)STAGES * STAGE_BYTES + 1024;
   auto kernel = gemm_bf16_kernel<BLOCK_T, EPI, STAGES>;
   SRB_CUDA_CALL(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-  dim3 grid((args.tokens + BLOCK_T - 1) / BLOCK_T, (args.features + GEMM_BLOCK_F - 1) / GEMM_BLOCK_F, splits);
+  dim3 grid((args.tokens + BLOCK_T - 1) / BLOCK_T, (args.features + FEATURES_PER_BLOCK - 1) / FEATURES_PER_BLOCK, splits);
   if (grid.y > 65535) SRB_FAIL("gemm_bf16: %d features exceed one launch", args.features);
   SRB_CUDA_CALL(srb_launch(kernel, grid, dim3(GEMM_THREADS), smem, s, map_w, map_x, args));
   return SRB_OK;
@@ -371,10 +383,9 @@ static int dispatch_tokens(int block_t, const CUtensorMap& map_w, const CUtensor
   }
 }
 
-// Tokens per block for a step of `tokens` rows: the smallest tile that holds them, 256 at most
-// (the SiLU mode keeps two accumulators and stops at 128).
+// Tokens per block for a step of `tokens` rows: the smallest tile that holds them, 256 at most.
 extern "C" int srb_gemm_bf16_block_tokens(int tokens, int mode) {
-  const int cap = mode == EPI_SILU ? 128 : 256;
+  const int cap = 256;
   int block = 16;
   while (block < tokens && block < cap) block *= 2;
   return block;
@@ -407,7 +418,8 @@ extern "C" int srb_gemm_bf16(const void* x, const void* w, void* out, int tokens
 
   CUtensorMap map_w, map_x;
   // rows beyond `features` (or beyond the matrix) are never stored; the map covers all rows of w
-  if (make_map(&map_w, w, rows_of_w, k, ldw, GEMM_BLOCK_F) != SRB_OK) return SRB_ERR_INVALID;
+  if (make_map(&map_w, w, rows_of_w, k, ldw, mode == EPI_SILU ? GEMM_BLOCK_F / 2 : GEMM_BLOCK_F) != SRB_OK)
+    return SRB_ERR_INVALID;
   if (make_map(&map_x, x, tokens, k, ldx, block_t) != SRB_OK) return SRB_ERR_INVALID;
 
   GemmArgs args;
@@ -420,13 +432,7 @@ extern "C" int srb_gemm_bf16(const void* x, const void* w, void* out, int tokens
   switch (mode) {
     case EPI_BF16: return dispatch_tokens<EPI_BF16>(block_t, map_w, map_x, args, splits, s);
     case EPI_F32: return dispatch_tokens<EPI_F32>(block_t, map_w, map_x, args, splits, s);
-    case EPI_SILU:
-      switch (block_t) {
-        case 16: return launch_gemm<16, EPI_SILU>(map_w, map_x, args, 1, s);
-        case 32: return launch_gemm<32, EPI_SILU>(map_w, map_x, args, 1, s);
-        case 64: return launch_gemm<64, EPI_SILU>(map_w, map_x, args, 1, s);
-        default: return launch_gemm<128, EPI_SILU>(map_w, map_x, args, 1, s);
-      }
+    case EPI_SILU: return dispatch_tokens<EPI_SILU>(block_t, map_w, map_x, args, 1, s);
     default: return dispatch_tokens<EPI_PARTIAL>(block_t, map_w, map_x, args, splits, s);
   }
 }

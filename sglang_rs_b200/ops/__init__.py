@@ -279,12 +279,13 @@ SM_COUNT = 148
 def gemm_splits(tokens: int, features: int, k: int) -> int:
     """Into how many partial sums a small-batch product is cut along K.  A function of the
     shape only: blocks of 128 weight rows alone cannot occupy the SMs when there are few of
-    them, so K is cut until about one block per SM exists, each with at least 8 K blocks."""
+    them, so K is cut until about two blocks per SM exist (two fit), each with at least 8 K
+    blocks."""
     if tokens > 64:
         return 1
     tiles = -(-features // 128)
     k_blocks = -(-k // 64)
-    splits = max(1, min(SM_COUNT // tiles, k_blocks // 8))
+    splits = max(1, min(2 * SM_COUNT // tiles, k_blocks // 8))
     if splits <= 1:
         return 1
     per_split = -(-k_blocks // splits)
