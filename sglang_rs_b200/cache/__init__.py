@@ -1,5 +1,7 @@
 from .manager import (CacheManager, OutOfPages, OutOfStateSlots, PageAllocator, PagedLayerCache, RequestCache,
                       StateLayerCache, StateSlotPool, group_key)
 
-__all__ = ["CacheManager", "OutOfPages", "OutOfStateSlots", "PageAllocator", "PagedLayerCache", "RequestCache",
+from .radix import PrefixTree
+
+__all__ = ["PrefixTree", "CacheManager", "OutOfPages", "OutOfStateSlots", "PageAllocator", "PagedLayerCache", "RequestCache",
            "StateLayerCache", "StateSlotPool", "group_key"]

@@ -143,6 +143,9 @@ def group_key(need: PagedKV) -> GroupKey:
 
 
 class CacheManager:
+    #: pages freed at once when cached prefixes have to make room
+    EVICT_AHEAD = 32
+
     def __init__(self, needs: Sequence[CacheNeed], *, page_size: int, max_tokens: int, max_requests: int,
                  device=None, dtype: torch.dtype = torch.bfloat16,
                  pages_per_group: Optional[Dict[GroupKey, int]] = None):
@@ -188,6 +191,31 @@ class CacheManager:
             else:
                 raise TypeError(f"unknown cache need {need!r}")
         self.live: Dict[Hashable, RequestCache] = {}
+        self.prefix_tree = None
+
+    # ------------------------------------------------------------------ prefix reuse
+    def prefix_reuse_possible(self) -> bool:
+        """Full pages can be shared only if every layer keeps all its keys in pages: a window
+        gives pages back, and state of fixed size cannot be rebuilt from shared pages (the
+        reference switches its prefix cache off for such models,
+        crates/sglang-srt/src/models/mod.rs:508-516)."""
+        return (not self.has_state and list(self.allocators) == [("kv", None)])
+
+    def enable_prefix_reuse(self):
+        from .radix import PrefixTree
+        if not self.prefix_reuse_possible():
+            raise ValueError("this model's cache cannot share prefixes")
+        key = ("kv", None)
+        self.prefix_tree = PrefixTree(self.page_size, self.allocators[key])
+        return self.prefix_tree
+
+    def _reclaim(self, key: GroupKey, shortfall: int) -> None:
+        if self.prefix_tree is not None and key == ("kv", None) and shortfall > 0:
+            # a search of the tree costs as much for one page as for many: take some ahead
+            self.prefix_tree.evict(max(shortfall, self.EVICT_AHEAD))
+
+    def _reclaimable(self, key: GroupKey) -> int:
+        return self.prefix_tree.evictable() if self.prefix_tree is not None and key == ("kv", None) else 0
 
     # ------------------------------------------------------------------ requests
     def open(self, request_id: Hashable) -> RequestCache:
@@ -215,8 +243,11 @@ class CacheManager:
 
     def can_reserve(self, handle: RequestCache, tokens: int, spare: Optional[Dict[GroupKey, int]] = None) -> bool:
         spare = spare or {}
-        return all(count <= self.allocators[key].free_count - spare.get(key, 0)
-                   for key, count in self.pages_needed(handle, tokens).items())
+        for key, count in self.pages_needed(handle, tokens).items():
+            free = self.allocators[key].free_count - spare.get(key, 0)
+            if count > free and count > free + self._reclaimable(key):
+                return False
+        return True
 
     def reserve(self, handle: RequestCache, tokens: int) -> None:
         """Makes room for ``tokens`` more tokens in every group, or changes nothing and
@@ -225,6 +256,8 @@ class CacheManager:
             raise RuntimeError(f"request {handle.request_id!r} has ended")
         needed = self.pages_needed(handle, tokens)
         for key, count in needed.items():
+            if count > self.allocators[key].free_count:
+                self._reclaim(key, count - self.allocators[key].free_count)     # pages only the prefix tree holds
             if count > self.allocators[key].free_count:
                 raise OutOfPages(key, count, self.allocators[key].free_count)
         for key, count in needed.items():
@@ -286,7 +319,8 @@ class CacheManager:
         return page * self.page_size + position % self.page_size
 
     def free_pages(self) -> Dict[GroupKey, int]:
-        return {key: allocator.free_count for key, allocator in self.allocators.items()}
+        """Pages that can be had now: free ones and those only the prefix tree holds."""
+        return {key: allocator.free_count + self._reclaimable(key) for key, allocator in self.allocators.items()}
 
     def layer_cache(self, call_index: int):
         return self.layer_caches[call_index]
@@ -302,6 +336,9 @@ class CacheManager:
                         held[page] = held.get(page, 0) + 1
             for page in (extra_holders or {}).get(key, ()):
                 held[page] = held.get(page, 0) + 1
+            if self.prefix_tree is not None and key == ("kv", None):
+                for page in self.prefix_tree.pages():
+                    held[page] = held.get(page, 0) + 1
             free = list(allocator._free)
             if len(set(free)) != len(free):
                 raise AssertionError(f"group {key}: a page is on the free list twice")

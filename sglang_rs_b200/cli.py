@@ -36,6 +36,7 @@ def build_parser() -> argparse.ArgumentParser:
     gen.add_argument("--max-running-requests", type=int, default=256)
     gen.add_argument("--chunked-prefill-size", type=int, default=2048)
     gen.add_argument("--disable-cuda-graph", action="store_true")
+    gen.add_argument("--disable-radix-cache", action="store_true")
     source = gen.add_mutually_exclusive_group(required=True)
     source.add_argument("--input-ids", action="append", help="comma-separated token ids; repeat for more prompts")
     source.add_argument("--input-ids-file", help="JSON file: a list of token-id lists")
@@ -83,7 +84,8 @@ def main(argv: Optional[List[str]] = None) -> int:
     engine = Engine(model_path=args.model_path, random_weights=args.random_weights, seed=args.seed, dtype=args.dtype,
                     device=args.device, page_size=args.page_size, max_total_tokens=args.max_total_tokens,
                     mem_fraction_static=args.mem_fraction_static, max_running_requests=args.max_running_requests,
-                    chunked_prefill_size=args.chunked_prefill_size, disable_cuda_graph=args.disable_cuda_graph)
+                    chunked_prefill_size=args.chunked_prefill_size, disable_cuda_graph=args.disable_cuda_graph,
+                    disable_radix_cache=args.disable_radix_cache)
     if args.input_ids:
         prompts = [_ids(text) for text in args.input_ids]
     elif args.input_ids_file:

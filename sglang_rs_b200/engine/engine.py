@@ -32,11 +32,11 @@ class Engine:
                  max_total_tokens: Optional[int] = None, mem_fraction_static: float = 0.85,
                  max_running_requests: int = 256, chunked_prefill_size: int = 2048,
                  config: Optional[Mapping[str, Any]] = None, stop_token_ids: Optional[Sequence[int]] = None,
-                 disable_cuda_graph: bool = False):
+                 disable_cuda_graph: bool = False, disable_radix_cache: bool = False):
         """Option names follow the reference's server arguments where it has them
         (crates/sglang-srt/src/cli.rs:15-79: ``model_path``, ``device``, ``page_size``,
         ``max_total_tokens``, ``mem_fraction_static``, ``max_running_requests``,
-        ``chunked_prefill_size``, ``disable_cuda_graph``).  ``config`` may stand in for the folder's config.json
+        ``chunked_prefill_size``, ``disable_cuda_graph``, ``disable_radix_cache``).  ``config`` may stand in for the folder's config.json
         together with ``random_weights``."""
         if not str(device).startswith("cuda"):
             raise ValueError(f"device {device!r}: this engine runs on CUDA only and never falls back to the host")
@@ -53,6 +53,8 @@ class Engine:
             max_total_tokens = max(page_size, min(max_total_tokens, max_running_requests * self.model.max_positions))
         self.cache = CacheManager(self.model.cache_needs(), page_size=page_size, max_tokens=max_total_tokens,
                                   max_requests=max_running_requests, device=self.device, dtype=self.dtype)
+        if not disable_radix_cache and self.cache.prefix_reuse_possible():
+            self.cache.enable_prefix_reuse()
         self.runner = ModelRunner(self.model, self.cache, use_cuda_graphs=not disable_cuda_graph)
         stops = tuple(stop_token_ids) if stop_token_ids is not None else tuple(self.model.eos_token_ids)
         self.scheduler = Scheduler(self.cache, SchedulerConfig(
@@ -114,7 +116,11 @@ class Engine:
     def flush_cache(self) -> bool:
         """Possible only while nothing is queued or running, as in the reference
         (crates/sglang-srt/src/scheduler.rs:442-454)."""
-        return not self.scheduler.has_work
+        if self.scheduler.has_work:
+            return False
+        if self.cache.prefix_tree is not None:
+            self.cache.prefix_tree.clear()
+        return True
 
     # ------------------------------------------------------------------ the call a user makes
     def generate(self, input_ids: Union[Sequence[int], Sequence[Sequence[int]]],

@@ -290,10 +290,9 @@ class ModelRunner:
                 raise StepInputError(
                     f"request {handle.request_id!r}: position {handle.length + count - 1} exceeds "
                     f"max_position_embeddings {self.model.max_positions}")
-            for token in entry.tokens:
-                if not 0 <= int(token) < self.model.vocab_size:
-                    raise StepInputError(f"request {handle.request_id!r}: token id {token} is outside the "
-                                         f"vocabulary of {self.model.vocab_size}")
+            if min(entry.tokens) < 0 or max(entry.tokens) >= self.model.vocab_size:
+                raise StepInputError(f"request {handle.request_id!r}: a token id among {list(entry.tokens)[:8]}... is "
+                                     f"outside the vocabulary of {self.model.vocab_size}")
             for index in entry.want:
                 if not 0 <= int(index) < count:
                     raise StepInputError(f"request {handle.request_id!r}: wanted row {index} is not among its "

@@ -45,10 +45,28 @@ class Request:
     cached_tokens: int = 0                   # prompt tokens that were not computed again (prefix reuse)
     preemptions: int = 0
     admitted_at: int = -1
+    published_pages: int = 0                 # prompt pages already handed to the prefix tree
 
     @property
     def tokens(self) -> List[int]:
         return self.prompt + self.output_ids
+
+    @property
+    def num_tokens(self) -> int:
+        return len(self.prompt) + len(self.output_ids)
+
+    @property
+    def last_token(self) -> int:
+        return self.output_ids[-1] if self.output_ids else self.prompt[-1]
+
+    def tokens_from(self, start: int, count: int) -> List[int]:
+        """``tokens[start:start + count]`` without building the whole list."""
+        n = len(self.prompt)
+        if start >= n:
+            return self.output_ids[start - n:start - n + count]
+        if start + count <= n:
+            return self.prompt[start:start + count]
+        return self.prompt[start:] + self.output_ids[:start + count - n]
 
     @property
     def computed(self) -> int:
@@ -156,7 +174,7 @@ class Scheduler:
                     if victim is request:
                         break
             if request in self.running and not request.finished:
-                entries.append(ScheduledEntry(request, [request.tokens[-1]], True))
+                entries.append(ScheduledEntry(request, [request.last_token], True))
                 budget -= 1
 
         # 2. prompts in progress go on, oldest first; 3. then new requests are admitted
@@ -179,6 +197,14 @@ class Scheduler:
                 request.handle = self.cache.open(request.request_id)
             except OutOfStateSlots:
                 break
+            tree = self.cache.prefix_tree
+            if tree is not None:
+                shared = tree.match(request.tokens)
+                if shared:
+                    self.cache.adopt_prefix(request.handle, ("kv", None), shared)
+                    request.published_pages = len(shared)
+                    if not request.preemptions:
+                        request.cached_tokens = min(request.handle.length, len(request.prompt))
             taken = self._schedule_portion(request, budget, entries)
             if taken == 0:
                 self.cache.close(request.handle)             # no page free: it stays at the head
@@ -191,12 +217,12 @@ class Scheduler:
         return entries
 
     def _is_decoding(self, request: Request) -> bool:
-        return request.handle is not None and request.computed == len(request.tokens) - 1 and bool(request.output_ids)
+        return request.handle is not None and bool(request.output_ids) and request.computed == request.num_tokens - 1
 
     def _schedule_portion(self, request: Request, budget: int, entries: List[ScheduledEntry]) -> int:
-        tokens = request.tokens
+        total = request.num_tokens
         start = request.computed
-        count = min(budget, len(tokens) - start)
+        count = min(budget, total - start)
         # cut the portion down to the pages that are free
         while count > 0 and not self.cache.can_reserve(request.handle, count):
             free = min(self.cache.free_pages().values(), default=0)
@@ -205,12 +231,12 @@ class Scheduler:
         if count <= 0:
             return 0
         self.cache.reserve(request.handle, count)
-        entries.append(ScheduledEntry(request, tokens[start:start + count], start + count == len(tokens)))
+        entries.append(ScheduledEntry(request, request.tokens_from(start, count), start + count == total))
         return count
 
     def _can_never_fit(self, request: Request) -> bool:
         # prompt (and what was generated before a preemption) plus the token to be sampled next
-        need = -(-(len(request.tokens) + 1) // self.cache.page_size)
+        need = -(-(request.num_tokens + 1) // self.cache.page_size)
         return any(need > allocator.num_pages for key, allocator in self.cache.allocators.items()
                    if self.cache.windows[key] is None)
 
@@ -222,6 +248,7 @@ class Scheduler:
         self.running.remove(victim)
         self.cache.close(victim.handle)
         victim.handle = None
+        victim.published_pages = 0
         victim.preemptions += 1
         self.stats["preemptions"] += 1
         self.waiting.appendleft(victim)
@@ -233,8 +260,15 @@ class Scheduler:
         outputs: List[StepOutput] = list(self.finished_unreported)
         self.finished_unreported.clear()
         picks = iter(sampled)
+        tree = self.cache.prefix_tree
         for entry in entries:
             request = entry.request
+            if tree is not None and request.handle is not None:
+                # full pages of prompt tokens become known as soon as they are computed
+                full = min(request.handle.length, len(request.prompt)) // self.cache.page_size
+                if full > request.published_pages:
+                    tree.insert(request.prompt[:full * self.cache.page_size], request.handle.tables[("kv", None)][:full])
+                    request.published_pages = full
             if not entry.samples:
                 continue
             token = int(next(picks))
@@ -245,7 +279,7 @@ class Scheduler:
                 reason = "stop"
             elif len(request.output_ids) >= request.sampling.max_new_tokens:
                 reason = "length"
-            elif len(request.tokens) >= self.config.max_positions:
+            elif request.num_tokens >= self.config.max_positions:
                 reason = "context"
             if reason:
                 self.running.remove(request)

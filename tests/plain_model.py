@@ -262,6 +262,21 @@ TINY_C = {
 }
 
 
+# head_dim 128 and 64: the sizes the tensor-core attention kernels take (A, B and C run the generic one)
+TINY_D = {
+    "architectures": ["Qwen3ForCausalLM"], "model_type": "qwen3", "num_hidden_layers": 2, "hidden_size": 256,
+    "num_attention_heads": 8, "num_key_value_heads": 2, "head_dim": 128, "intermediate_size": 640,
+    "vocab_size": 1000, "rope_theta": 1000000.0, "rms_norm_eps": 1e-6, "tie_word_embeddings": False,
+    "max_position_embeddings": 1024, "hidden_act": "silu", "attention_bias": False,
+}
+TINY_E = {
+    "architectures": ["Qwen3ForCausalLM"], "model_type": "qwen3", "num_hidden_layers": 1, "hidden_size": 192,
+    "num_attention_heads": 6, "num_key_value_heads": 6, "head_dim": 64, "intermediate_size": 320,
+    "vocab_size": 777, "rope_theta": 20000.0, "rms_norm_eps": 2e-5, "tie_word_embeddings": True,
+    "max_position_embeddings": 512, "hidden_act": "silu", "attention_bias": True,
+}
+
+
 def plain_random_weights(config: dict, seed: int) -> Dict[str, torch.Tensor]:
     """Own initialiser (not the engine's): N(0, 0.02) matrices, norms 1 + U(-0.1, 0.1)."""
     gen = torch.Generator().manual_seed(seed)

@@ -53,6 +53,7 @@ def test_greedy_generation_through_the_entry_point(tmp_path, config, page, chunk
     if dtype_name == "float32":
         assert [again.generate(p, {"max_new_tokens": 16})["output_ids"] for p in prompts] == [r["output_ids"] for r in results]
     engine.cache.check_invariants()
+    assert engine.flush_cache()                          # cached prompt pages are the only ones still held
     assert all(a.free_count == a.num_pages for a in engine.cache.allocators.values())
 
 
@@ -66,6 +67,37 @@ def test_preemption_on_a_small_pool_gives_the_same_tokens(tmp_path):
     results = engine.generate(prompts, {"max_new_tokens": 40})
     assert engine.scheduler.stats["preemptions"] >= 1
     assert [r["output_ids"] for r in results] == [pm.plain_greedy(cfg, weights, p, 40) for p in prompts]
+
+
+@pytest.mark.parametrize("dtype_name,stored,limit", [("float32", torch.float32, 0.0), ("bfloat16", torch.bfloat16, 3e-2)])
+def test_shared_prefix_is_reused_and_changes_nothing(tmp_path, dtype_name, stored, limit):
+    """Two prompts share 24 tokens (3 pages of 8); the second starts from the first one's pages.
+    A prompt that is cached entirely still computes its last page's tokens."""
+    from sglang_rs_b200 import Engine
+    folder = rh.make_folder(tmp_path, "m", pm.TINY_B, seed=31, dtype=stored)
+    cfg, weights = pm.load_folder(folder)
+    base = list(rh.random_requests(pm.TINY_B, (90,), seed=12).values())[0]
+    other = base[:24] + list(rh.random_requests(pm.TINY_B, (16,), seed=13).values())[0]
+    engine = Engine(model_path=folder, dtype=dtype_name, page_size=8, max_total_tokens=400, chunked_prefill_size=16)
+    first = engine.generate(base[:40], {"max_new_tokens": 6})
+    assert first["cached_tokens"] == 0
+    second = engine.generate(other, {"max_new_tokens": 6})
+    assert second["cached_tokens"] == 24
+    third = engine.generate(base[:40], {"max_new_tokens": 6})
+    assert third["cached_tokens"] == 32                   # 40 tokens known; (40 - 1) // 8 pages are taken
+    for prompt, result in ((base[:40], first), (other, second), (base[:40], third)):
+        plain_greedy_margin(cfg, weights, prompt, result["output_ids"], limit)
+    assert third["output_ids"] == first["output_ids"]
+    fresh = Engine(model_path=folder, dtype=dtype_name, page_size=8, max_total_tokens=400, chunked_prefill_size=16,
+                   disable_radix_cache=True)
+    assert fresh.cache.prefix_tree is None
+    if dtype_name == "float32":
+        assert fresh.generate(other, {"max_new_tokens": 6})["output_ids"] == second["output_ids"]
+    # cached pages make room when the pool is needed: a long request evicts them
+    long = list(rh.random_requests(pm.TINY_B, (100,), seed=14).values())
+    many = engine.generate(long * 3, {"max_new_tokens": 20})
+    assert all(r["finished"] for r in many)
+    engine.cache.check_invariants()
 
 
 def test_temperature_sampling_is_seeded_and_independent_of_the_batch(tmp_path):

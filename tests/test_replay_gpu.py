@@ -20,6 +20,9 @@ CASES = {
     "A": (pm.TINY_A, (5, 17, 33, 64, 200, 131), 16),
     "B": (pm.TINY_B, (7, 40, 90, 128, 65, 33), 8),
     "C": (pm.TINY_C, (3, 300, 47, 600, 258, 513), 16),
+    # head_dim 128 / 64: in bfloat16 these run the tensor-core attention kernels and the tcgen05 product
+    "D": (pm.TINY_D, (2, 129, 700, 64, 385, 257), 16),
+    "E": (pm.TINY_E, (65, 130, 31, 400, 5), 32),
 }
 DTYPES = {"float32": (torch.float32, rh.FP32_TOLERANCE), "bfloat16": (torch.bfloat16, rh.BF16_TOLERANCE)}
 
