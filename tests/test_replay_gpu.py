@@ -22,7 +22,7 @@ CASES = {
     "C": (pm.TINY_C, (3, 300, 47, 600, 258, 513), 16),
     # head_dim 128 / 64: in bfloat16 these run the tensor-core attention kernels and the tcgen05 product
     "D": (pm.TINY_D, (2, 129, 700, 64, 385, 257), 16),
-    "E": (pm.TINY_E, (65, 130, 31, 400, 5), 32),
+    "E": (pm.TINY_E, (65, 130, 31, 400, 5, 90, 200, 33), 32),
 }
 DTYPES = {"float32": (torch.float32, rh.FP32_TOLERANCE), "bfloat16": (torch.bfloat16, rh.BF16_TOLERANCE)}
 
