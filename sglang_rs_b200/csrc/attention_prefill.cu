@@ -6,7 +6,8 @@
 // positions, brought from the pages into shared memory by 16-byte asynchronous copies, two
 // blocks in flight; S = Q K^T and O += P V run on mma.sync m16n8k16 with the running
 // maximum and sum of the online softmax in 32-bit (crates/sglang-kernel/src/cuda_attention.rs:
-// 137-151 is the reference's per-key form of the same recurrence).  A row's arithmetic
+// 137-151 is the reference's per-key form of the same recurrence); exponentials are taken as
+// 2^(s log2 e - m), one ex2 instruction each.  A row's arithmetic
 // depends only on its own position: blocks are absolute, and a block that lies wholly
 // outside a warp's rows is skipped without changing anything.
 //
@@ -24,7 +25,7 @@ SRB_DEFINE_LAST_ERROR()
 #define PF_WARPS 4
 
 template <int D>
-__global__ void __launch_bounds__(PF_WARPS * 32)
+__global__ void __launch_bounds__(PF_WARPS * 32, 3)
 prefill_attention_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __restrict__ k_pool,
                          const __nv_bfloat16* __restrict__ v_pool, __nv_bfloat16* __restrict__ out,
                          const int* __restrict__ tiles, AttnParams p) {
@@ -33,8 +34,10 @@ prefill_attention_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat1
   constexpr int NT_S = PF_KEYS / 8;
   constexpr int NT_O = D / 8;
   extern __shared__ __align__(128) unsigned char smem_raw[];
-  __nv_bfloat16* qs = reinterpret_cast<__nv_bfloat16*>(smem_raw);        // [64][D]
-  __nv_bfloat16* kv = qs + PF_ROWS * D;                                  // [2 stages][K, V][64][D]
+  __nv_bfloat16* kv = reinterpret_cast<__nv_bfloat16*>(smem_raw);        // [2 stages][K, V][64][D]
+  // Q passes through the second stage before the first copy into it is issued; it then lives in
+  // registers, so a block needs 64 KB at head_dim 128 and three blocks share an SM.
+  __nv_bfloat16* qs = kv + 2 * PF_KEYS * D;                              // [64][D]
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int tile = blockIdx.x, head = blockIdx.y;
@@ -54,6 +57,7 @@ prefill_attention_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat1
   }
   cp_async_commit();
 
+  const int page_shift = (p.page_size & (p.page_size - 1)) == 0 ? __ffs(p.page_size) - 1 : -1;
   auto load_block = [&](int block, int stage) {
     __nv_bfloat16* ks = kv + (size_t)stage * 2 * PF_KEYS * D;
     __nv_bfloat16* vs = ks + PF_KEYS * D;
@@ -63,12 +67,14 @@ prefill_attention_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat1
       bool valid = abs_key >= kv_lo && abs_key < kv_hi;
       long long offset = 0;
       if (valid) {
-        const int page = p.block_table[(size_t)request * p.table_stride + abs_key / p.page_size];
+        const int logical = page_shift >= 0 ? abs_key >> page_shift : abs_key / p.page_size;
+        const int within = page_shift >= 0 ? abs_key & (p.page_size - 1) : abs_key % p.page_size;
+        const int page = p.block_table[(size_t)request * p.table_stride + logical];
         if (page < 0 || page >= p.num_pages) {
           atomicOr(p.error_word, SRB_FLAG_BAD_PAGE);
           valid = false;
         } else {
-          offset = (((long long)page * p.n_kv + kv_head) * p.page_size + abs_key % p.page_size) * D + c * 8;
+          offset = (((long long)page * p.n_kv + kv_head) * p.page_size + within) * D + c * 8;
         }
       }
       const int where = key * D + ((c ^ (key & 7)) * 8);
@@ -84,11 +90,23 @@ prefill_attention_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat1
   // rows of this thread inside the tile and their positions
   const int r_in[2] = {warp * 16 + g, warp * 16 + g + 8};
   const int pos_r[2] = {pos_begin + r_in[0], pos_begin + r_in[1]};
+  const int lowest_r[2] = {(p.window > 0 && pos_r[0] + 1 > p.window) ? pos_r[0] + 1 - p.window : 0,
+                           (p.window > 0 && pos_r[1] + 1 > p.window) ? pos_r[1] + 1 - p.window : 0};
+  const float scale_log2 = p.scale * 1.4426950408889634f;
   const int warp_first_pos = pos_begin + warp * 16;
   const int warp_last_pos = pos_begin + min(warp * 16 + 15, n_rows - 1);
   const bool warp_has_rows = warp * 16 < n_rows;
 
   unsigned qa[KSTEPS][4];
+  cp_async_wait<0>();
+  __syncthreads();
+#pragma unroll
+  for (int kk = 0; kk < KSTEPS; ++kk) {
+    const int r = warp * 16 + (mat & 1) * 8 + mrow;
+    const int chunk = kk * 2 + (mat >> 1);
+    ldmatrix_x4(qa[kk][0], qa[kk][1], qa[kk][2], qa[kk][3], qs + r * D + ((chunk ^ (r & 7)) * 8));
+  }
+  __syncthreads();                                      // the second stage may be overwritten from here on
   float m_row[2] = {-INFINITY, -INFINITY}, l_row[2] = {0.f, 0.f};
   float o[NT_O][4];
 #pragma unroll
@@ -103,14 +121,6 @@ prefill_attention_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat1
       cp_async_wait<0>();
     }
     __syncthreads();
-    if (block == first_block) {
-#pragma unroll
-      for (int kk = 0; kk < KSTEPS; ++kk) {
-        const int r = warp * 16 + (mat & 1) * 8 + mrow;
-        const int chunk = kk * 2 + (mat >> 1);
-        ldmatrix_x4(qa[kk][0], qa[kk][1], qa[kk][2], qa[kk][3], qs + r * D + ((chunk ^ (r & 7)) * 8));
-      }
-    }
     const int block_lo = block * PF_KEYS, block_hi = block_lo + PF_KEYS;
     // the block matters to this warp if some key in it is visible to one of the warp's rows
     const int warp_window_lo = (p.window > 0 && warp_first_pos + 1 > p.window) ? warp_first_pos + 1 - p.window : 0;
@@ -132,18 +142,34 @@ prefill_attention_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat1
           mma_bf16(s[t + 1], qa[kk], b2, b3);
         }
       }
+      // Scores are kept in units of log2: s * scale * log2(e), so that the exponentials are
+      // single ex2 instructions; the maximum and the sum are 32-bit as before.  A block whose
+      // keys are visible to every row of the warp (the common case below the diagonal) skips
+      // the comparisons.
       float mx[2] = {-INFINITY, -INFINITY};
+      const bool all_visible = warp * 16 + 15 < n_rows && block_hi - 1 <= warp_first_pos &&
+                               (p.window == 0 || block_lo >= pos_begin + warp * 16 + 15 + 1 - p.window);
+      if (all_visible) {
 #pragma unroll
-      for (int t = 0; t < NT_S; ++t) {
+        for (int t = 0; t < NT_S; ++t) {
 #pragma unroll
-        for (int e = 0; e < 4; ++e) {
-          const int h = e >> 1;
-          const int key = block_lo + t * 8 + col + (e & 1);
-          const int lowest = (p.window > 0 && pos_r[h] + 1 > p.window) ? pos_r[h] + 1 - p.window : 0;
-          const bool visible = r_in[h] < n_rows && key <= pos_r[h] && key >= lowest;
-          const float v = visible ? s[t][e] * p.scale : -INFINITY;
-          s[t][e] = v;
-          mx[h] = fmaxf(mx[h], v);
+          for (int e = 0; e < 4; ++e) {
+            s[t][e] *= scale_log2;
+            mx[e >> 1] = fmaxf(mx[e >> 1], s[t][e]);
+          }
+        }
+      } else {
+#pragma unroll
+        for (int t = 0; t < NT_S; ++t) {
+#pragma unroll
+          for (int e = 0; e < 4; ++e) {
+            const int h = e >> 1;
+            const int key = block_lo + t * 8 + col + (e & 1);
+            const bool visible = r_in[h] < n_rows && key <= pos_r[h] && key >= lowest_r[h];
+            const float v = visible ? s[t][e] * scale_log2 : -INFINITY;
+            s[t][e] = v;
+            mx[h] = fmaxf(mx[h], v);
+          }
         }
       }
       float corr[2], safe[2], sum[2] = {0.f, 0.f};
@@ -153,14 +179,14 @@ prefill_attention_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat1
         mx[h] = fmaxf(mx[h], __shfl_xor_sync(0xffffffffu, mx[h], 2));
         const float m_new = fmaxf(m_row[h], mx[h]);
         safe[h] = m_new == -INFINITY ? 0.f : m_new;       // a row that has seen no key yet
-        corr[h] = expf(m_row[h] - safe[h]);               // exp(-inf) = 0 the first time
+        corr[h] = exp2f(m_row[h] - safe[h]);              // 2^(-inf) = 0 the first time
         m_row[h] = m_new;
       }
 #pragma unroll
       for (int t = 0; t < NT_S; ++t) {
 #pragma unroll
         for (int e = 0; e < 4; ++e) {
-          const float pv = expf(s[t][e] - safe[e >> 1]);
+          const float pv = exp2f(s[t][e] - safe[e >> 1]);
           s[t][e] = pv;
           sum[e >> 1] += pv;
         }
@@ -211,7 +237,7 @@ prefill_attention_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat1
 template <int D>
 static int launch_prefill(const void* q, const void* k_pool, const void* v_pool, void* out, const int* tiles,
                           int num_tiles, const AttnParams& p, cudaStream_t s) {
-  const size_t smem = (size_t)(PF_ROWS + 4 * PF_KEYS) * D * sizeof(__nv_bfloat16);
+  const size_t smem = (size_t)(4 * PF_KEYS) * D * sizeof(__nv_bfloat16);
   SRB_CUDA_CALL(cudaFuncSetAttribute(prefill_attention_kernel<D>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                      (int)smem));
   dim3 grid(num_tiles, p.n_q);
