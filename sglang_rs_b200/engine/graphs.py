@@ -78,6 +78,7 @@ class DecodeGraphs:
             step.copied.synchronize()        # the staging buffer is free again once its last copy has run
         self._fill(step, entries, groups, bucket, stride, positions, page_size)
         step.static.copy_(step.staging, non_blocking=True)
+        self.planner.last_upload_bytes = step.staging.numel() * 4
         if step.copied is None:
             step.copied = torch.cuda.Event()
         step.copied.record()

@@ -33,7 +33,7 @@ from ..cache.manager import CacheManager, OutOfPages, OutOfStateSlots, RequestCa
 from ..sampling.params import SamplingParams
 
 
-@dataclass
+@dataclass(eq=False)            # requests are compared by identity: membership tests must not walk token lists
 class Request:
     request_id: Hashable
     prompt: List[int]
