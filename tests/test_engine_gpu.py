@@ -317,7 +317,7 @@ TOY = {"architectures": ["ToyHybridForTests"], "hidden": 48, "vocab": 90, "heads
        "inner": 64, "eps": 1e-5, "theta": 3000.0, "window": 11, "decay": 0.8, "max_positions": 400}
 
 
-def register_toy():
+def register_toy(stateless=False):
     """Everything the toy needs is defined here; the framework's files are not touched."""
     from sglang_rs_b200 import ops
     from sglang_rs_b200.config import register_architecture
@@ -368,7 +368,8 @@ def register_toy():
                                 GatedMlp(h, cfg["inner"], "silu", GatedMlpNames(f"{p}.gate", f"{p}.up", f"{p}.down")))
 
         rope = lambda: RotaryEncoding(cfg["head_dim"], cfg["theta"])  # noqa: E731
-        layers = [block(0, DecayingSumMixer(h, cfg["decay"], "layers.0.mix")), block(1, attn(1, None, rope())),
+        first = attn(0, cfg["window"] + 6, rope()) if cfg.get("stateless") else DecayingSumMixer(h, cfg["decay"], "layers.0.mix")
+        layers = [block(0, first), block(1, attn(1, None, rope())),
                   block(2, attn(2, cfg["window"], NoPositionEncoding())), block(3, attn(3, None, rope()))]
         # layer 1 runs twice (two caches, one set of weights); layer 3 reads the cache of the first call of layer 1
         program = [LayerCall(0), LayerCall(1), LayerCall(2), LayerCall(1), LayerCall(3, cache_from=1)]
@@ -412,7 +413,8 @@ def plain_toy_forward(cfg, weights, tokens):
             out.append(s)
         return torch.stack(out)
 
-    calls = [(0, lambda x: mixer0(x)), (1, lambda x: attn(1, x, None, True, 1)),
+    first = (lambda x: attn(0, x, cfg["window"] + 6, True, 0)) if cfg.get("stateless") else (lambda x: mixer0(x))
+    calls = [(0, first), (1, lambda x: attn(1, x, None, True, 1)),
              (2, lambda x: attn(2, x, cfg["window"], False, 2)), (1, lambda x: attn(1, x, None, True, 3)),
              (3, lambda x: attn(3, x, None, True, 4, reuse=1))]
     for layer, mix in calls:
@@ -458,5 +460,33 @@ def test_an_architecture_defined_in_the_test(tmp_path, dtype_name, stored, toler
                 limit = (0.0 if dtype_name == "float32" else 3e-2) * float(logits.abs().max())
                 assert float(logits.max() - logits[token]) <= limit
                 tokens.append(token)
+    finally:
+        unregister_architecture("ToyHybridForTests")
+
+
+@pytest.mark.parametrize("dtype_name,stored,tolerance", [("float32", torch.float32, rh.FP32_TOLERANCE),
+                                                         ("bfloat16", torch.bfloat16, rh.BF16_TOLERANCE)])
+def test_captured_steps_with_window_groups(tmp_path, dtype_name, stored, tolerance):
+    """The toy without its stateful mixer is safe to capture: three cache groups (all keys, windows
+    of 11 and 17), a layer called twice, a layer that reads another's cache, decoded from CUDA graphs
+    and from single launches, with pages of the window groups handed back on the way."""
+    from sglang_rs_b200.config import unregister_architecture
+    from sglang_rs_b200.weights import read_model_dir, write_model_folder
+    toy = dict(TOY, stateless=True)
+    register_toy()
+    try:
+        folder = write_model_folder(str(tmp_path / "toy2"), toy, seed=8, dtype=stored)
+        weights = {k: v.float() for k, v in read_model_dir(folder).items()}
+        requests = rh.random_requests({"vocab_size": toy["vocab"]}, (90, 45, 200, 33), seed=6)
+        expected = {rid: plain_toy_forward(toy, weights, toks).numpy() for rid, toks in requests.items()}
+        for trace in (rh.trace_tail_by_one(requests, tail=40), rh.trace_mixed(requests, seed=9, decode_tail=40)):
+            for graphs in (False, True):
+                rows, session = rh.run_in_process(folder, dtype_name, trace, graphs=graphs)
+                assert (session.runner.graphs is not None) == graphs
+                if graphs:
+                    assert session.runner.graphs.replays > 40
+                bad = rh.first_bad(rows, expected, tolerance)
+                assert bad is None, (graphs, bad)
+        assert set(session.cache.allocators) == {("kv", None), ("kv", 11), ("kv", 17)}
     finally:
         unregister_architecture("ToyHybridForTests")

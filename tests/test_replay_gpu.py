@@ -122,3 +122,23 @@ def test_trace_run_program(prepared, tmp_path):
             assert not path.exists()
             outputs.append(None)
     check(rh.collect(trace, outputs), expected, rh.FP32_TOLERANCE, requests, "trace_run A/float32/mixed")
+
+
+@pytest.mark.parametrize("dtype_name", ["bfloat16", "float32"])
+def test_layer_sizes_of_the_8b_shape(tmp_path, dtype_name):
+    """One layer with the benchmark's layer sizes (hidden 4096, 32/8 heads of 128, inner 12288) and a
+    vocabulary of 32,000: the products are cut along K as in the benchmark and the attention kernels
+    see 4 query heads per kv head.  Prompt in one step, then tokens one by one across a key split."""
+    config = dict(pm.TINY_D, num_hidden_layers=1, hidden_size=4096, num_attention_heads=32, num_key_value_heads=8,
+                  head_dim=128, intermediate_size=12288, vocab_size=32000, max_position_embeddings=512)
+    stored = DTYPES[dtype_name][0]
+    folder = rh.make_folder(tmp_path, "big", config, seed=5, dtype=stored)
+    requests = rh.random_requests(config, (150, 40), seed=9)
+    cfg, weights = pm.load_folder(folder)
+    expected = {rid: pm.plain_forward(cfg, weights, toks, dtype=torch.float32).double().numpy()
+                for rid, toks in requests.items()}
+    trace = rh.trace_tail_by_one(requests, tail=30) if dtype_name == "bfloat16" else rh.trace_portions(requests)
+    rows, _ = rh.run_in_process(folder, dtype_name, trace)
+    # the oracle itself is 32-bit here (64-bit weights of this size would not fit the test's time)
+    tolerance = DTYPES[dtype_name][1] if dtype_name == "bfloat16" else 5e-4
+    check(rows, expected, tolerance, requests, f"8B layer sizes/{dtype_name}")
