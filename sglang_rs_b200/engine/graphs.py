@@ -152,9 +152,10 @@ class DecodeGraphs:
                           host_state_slots=[0] * bucket)
         keep = []
         for g, key in enumerate(groups):
-            acc = torch.empty(max(bucket * splits[g] * self.planner._scratch_acc_width, 1), dtype=torch.float32,
+            widest = max(splits[g], ops.decode_splits(bucket, 1))
+            acc = torch.empty(max(bucket * widest * self.planner._scratch_acc_width, 1), dtype=torch.float32,
                               device=self.device)
-            ml = torch.empty(max(bucket * splits[g] * self.planner._scratch_ml_width, 1), dtype=torch.float32,
+            ml = torch.empty(max(bucket * widest * self.planner._scratch_ml_width, 1), dtype=torch.float32,
                              device=self.device)
             keep += [acc, ml]
             ctx.paged[key] = PagedBatch(part(f"table{g}").view(bucket, stride), part(f"slots{g}"),

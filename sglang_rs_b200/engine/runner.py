@@ -198,8 +198,10 @@ class StepPlanner:
             split_size = self.SPLIT_SIZE
             while True:
                 max_splits = int((pos // split_size - begin // split_size + 1).max())
-                need_acc = split_rows * max_splits * self._scratch_acc_width
-                need_ml = split_rows * max_splits * self._scratch_ml_width
+                # the split count of the generic kernel, or that of the tensor-core decode kernel if larger
+                widest = max(max_splits, ops.decode_splits(split_rows, 1))
+                need_acc = split_rows * widest * self._scratch_acc_width
+                need_ml = split_rows * widest * self._scratch_ml_width
                 if need_acc <= self.SCRATCH_LIMIT or max_splits == 1:
                     break
                 split_size *= 2

@@ -199,14 +199,13 @@ def paged_attention(q: torch.Tensor, k_pool: torch.Tensor, v_pool: torch.Tensor,
                     positions: torch.Tensor, row_request: torch.Tensor, block_table: torch.Tensor, *,
                     scale: float, window: int, split_size: int, max_splits: int,
                     scratch_acc: Optional[torch.Tensor], scratch_ml: Optional[torch.Tensor],
-                    error_word: torch.Tensor, counters: Optional[torch.Tensor] = None) -> None:
+                    error_word: torch.Tensor) -> None:
     """out[r, h, :] = softmax over the keys row r may see of (q . k) * scale, times v.
 
     q, out: [rows, n_q, head_dim]; pools [pages, n_kv, page_size, head_dim]; block_table
     [requests, stride].  ``split_size`` 0 walks all keys in one block per (row, kv head);
     otherwise partials go through the scratch tensors and are merged in split order.
-    ``counters`` (int32, zero, at least rows * n_kv entries; left zero) lets the tensor-core
-    kernel merge the splits itself instead of launching a second kernel."""
+    This is the generic kernel (any head_dim that is a multiple of 16, float32 or bfloat16)."""
     _need(q, "q"); _need(out, "out", q.dtype); _need(k_pool, "k_pool", q.dtype); _need(v_pool, "v_pool", q.dtype)
     _need(positions, "positions", torch.int32); _need(row_request, "row_request", torch.int32)
     _need(block_table, "block_table", torch.int32)
@@ -219,19 +218,6 @@ def paged_attention(q: torch.Tensor, k_pool: torch.Tensor, v_pool: torch.Tensor,
         if scratch_acc is None or scratch_ml is None or scratch_acc.numel() < need_acc or scratch_ml.numel() < need_ml:
             raise KernelError("paged_attention: scratch tensors are too small for this split run")
         _need(scratch_acc, "scratch_acc", torch.float32); _need(scratch_ml, "scratch_ml", torch.float32)
-    if split_size == 128 and q.dtype == torch.bfloat16 and head_dim in (64, 128) and n_q // n_kv <= 16:
-        # sizes the tensor-core kernel takes (srb_decode_attention_supports states the same rule)
-        fast = load_library("attention_decode")
-        if counters is not None:
-            _need(counters, "counters", torch.int32)
-            if counters.numel() < rows * n_kv:
-                counters = None
-        _check(fast, fast.srb_decode_attention(
-            _ptr(q), _ptr(k_pool), _ptr(v_pool), _ptr(out), _ptr(scratch_acc), _ptr(scratch_ml), _ptr(counters),
-            _ptr(positions), _ptr(row_request), _ptr(block_table), block_table.stride(0), rows, n_q, n_kv, head_dim,
-            page_size, num_pages, int(window), int(split_size), int(max_splits), ctypes.c_float(scale),
-            _ptr(error_word), _stream()), launches=1 if counters is not None else 2)
-        return
     lib = load_library("attention")
     _check(lib, lib.srb_paged_attention(
         _ptr(q), _ptr(k_pool), _ptr(v_pool), _ptr(out), _ptr(scratch_acc), _ptr(scratch_ml), _ptr(positions),
@@ -239,6 +225,53 @@ def paged_attention(q: torch.Tensor, k_pool: torch.Tensor, v_pool: torch.Tensor,
         num_pages, int(window), int(split_size), int(max_splits), ctypes.c_float(scale), _ptr(error_word),
         dtype_code(q.dtype), _stream()), launches=2 if split_size else 1)
 
+
+
+#: blocks the decode attention aims at: three per SM
+DECODE_TARGET_BLOCKS = 3 * 148
+DECODE_MAX_SPLITS = 64
+
+
+def decode_attention_takes(dtype: torch.dtype, n_q: int, n_kv: int, head_dim: int) -> bool:
+    """True if the tensor-core kernel for decoded tokens takes these sizes (the rule of
+    srb_decode_attention_supports, asked here so that other models never compile it)."""
+    return dtype == torch.bfloat16 and head_dim in (64, 128) and n_kv > 0 and n_q % n_kv == 0 and n_q // n_kv <= 16
+
+
+def decode_splits(rows: int, n_kv: int) -> int:
+    """Blocks per (row, kv head): enough that about three blocks per SM exist."""
+    return max(1, min(DECODE_MAX_SPLITS, DECODE_TARGET_BLOCKS // max(rows * n_kv, 1)))
+
+
+def decode_attention(q: torch.Tensor, k_pool: torch.Tensor, v_pool: torch.Tensor, out: torch.Tensor,
+                     positions: torch.Tensor, row_request: torch.Tensor, block_table: torch.Tensor, *,
+                     scale: float, window: int, scratch_acc: torch.Tensor, scratch_ml: torch.Tensor,
+                     counters: torch.Tensor, error_word: torch.Tensor) -> None:
+    """Attention of decoded tokens (one row each), bfloat16, head_dim 64 or 128.
+
+    The keys of a (row, kv head) are shared by ``decode_splits(rows, n_kv)`` blocks; the block
+    that finishes last merges them.  ``counters``: int32, zero, at least rows * n_kv entries; they
+    are zero again afterwards.  Scratch: rows * n_q * splits * head_dim and rows * n_q * splits * 2
+    floats."""
+    _need(q, "q", torch.bfloat16); _need(out, "out", torch.bfloat16); _need(k_pool, "k_pool", torch.bfloat16)
+    _need(v_pool, "v_pool", torch.bfloat16); _need(positions, "positions", torch.int32)
+    _need(row_request, "row_request", torch.int32); _need(block_table, "block_table", torch.int32)
+    _need(scratch_acc, "scratch_acc", torch.float32); _need(scratch_ml, "scratch_ml", torch.float32)
+    _need(counters, "counters", torch.int32)
+    rows, n_q, head_dim = q.shape
+    num_pages, n_kv, page_size, pool_dim = k_pool.shape
+    if pool_dim != head_dim or v_pool.shape != k_pool.shape or out.shape != q.shape:
+        raise KernelError("decode_attention: shapes of q, out and the pools do not agree")
+    splits = decode_splits(rows, n_kv)
+    if scratch_acc.numel() < rows * n_q * splits * head_dim or scratch_ml.numel() < rows * n_q * splits * 2:
+        raise KernelError("decode_attention: scratch tensors are too small")
+    if counters.numel() < rows * n_kv:
+        raise KernelError("decode_attention: too few counters")
+    lib = load_library("attention_decode")
+    _check(lib, lib.srb_decode_attention(
+        _ptr(q), _ptr(k_pool), _ptr(v_pool), _ptr(out), _ptr(scratch_acc), _ptr(scratch_ml), _ptr(counters),
+        _ptr(positions), _ptr(row_request), _ptr(block_table), block_table.stride(0), rows, n_q, n_kv, head_dim,
+        page_size, num_pages, int(window), splits, ctypes.c_float(scale), _ptr(error_word), _stream()))
 
 
 def tiled_attention_takes(dtype: torch.dtype, n_q: int, n_kv: int, head_dim: int) -> bool:

@@ -107,11 +107,19 @@ class GroupedQueryAttention(Mixer):
                 ops.tiled_attention(q, cache.k_pool, cache.v_pool, out, launch.tiles, batch.block_table,
                                     scale=self.scale, window=self.window or 0, error_word=ctx.error_word)
                 continue
+            if (launch.tiles is None and launch.split_size and batch.counters is not None
+                    and batch.counters.numel() >= (e - b) * self.n_kv
+                    and ops.decode_attention_takes(q.dtype, self.n_q, self.n_kv, self.d)):
+                ops.decode_attention(q[b:e], cache.k_pool, cache.v_pool, out[b:e], ctx.positions[b:e],
+                                     ctx.row_request[b:e], batch.block_table, scale=self.scale,
+                                     window=self.window or 0, scratch_acc=batch.scratch_acc,
+                                     scratch_ml=batch.scratch_ml, counters=batch.counters,
+                                     error_word=ctx.error_word)
+                continue
             ops.paged_attention(q[b:e], cache.k_pool, cache.v_pool, out[b:e], ctx.positions[b:e],
                                 ctx.row_request[b:e], batch.block_table, scale=self.scale,
                                 window=self.window or 0, split_size=launch.split_size,
                                 max_splits=launch.max_splits, scratch_acc=batch.scratch_acc,
-                                scratch_ml=batch.scratch_ml, error_word=ctx.error_word,
-                                counters=batch.counters)
+                                scratch_ml=batch.scratch_ml, error_word=ctx.error_word)
         return ops.linear(out.view(rows, self.n_q * self.d), self.w_o, self.b_o, error_word=ctx.error_word,
                           partial_ok=True)

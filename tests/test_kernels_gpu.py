@@ -222,7 +222,7 @@ def expected_attention(case, scale):
     return torch.cat(outs)
 
 
-def run_attention(case, scale, split_size, counters=None):
+def run_attention(case, scale, split_size):
     q = case["q"]
     rows, n_q, d = q.shape
     out = torch.full_like(q, float("nan"))
@@ -237,25 +237,65 @@ def run_attention(case, scale, split_size, counters=None):
         ml = torch.full((m,), float("nan"), device=DEV)
     ops.paged_attention(q, case["k_pool"], case["v_pool"], out, case["positions"], case["row_request"], case["table"],
                         scale=scale, window=case["window"] or 0, split_size=split_size, max_splits=max_splits,
-                        scratch_acc=acc, scratch_ml=ml, error_word=word, counters=counters)
+                        scratch_acc=acc, scratch_ml=ml, error_word=word)
     ops.raise_on_error_word(word)
     return out
 
 
-@pytest.mark.parametrize("n_q,n_kv,d,page,window", [(8, 2, 64, 16, None), (16, 1, 128, 8, 300), (6, 3, 128, 32, None)])
-def test_last_block_merges_the_splits(n_q, n_kv, d, page, window):
-    """With counters the tensor-core kernel merges its own splits: the same numbers as with the
-    separate merge kernel, and the counters are zero again afterwards, twice in a row."""
-    lengths, rows = (1, 129, 700, 64, 257, 1000), (1, 1, 1, 1, 1, 1)
-    case = paged_case(torch.bfloat16, n_q, n_kv, d, page, lengths, rows, window, seed=d)
+def run_decode(case, scale, counters):
+    q = case["q"]
+    rows, n_q, d = q.shape
+    n_kv = case["k_pool"].shape[1]
+    splits = ops.decode_splits(rows, n_kv)
+    out = torch.full_like(q, float("nan"))
+    word = ops.new_error_word(DEV)
+    acc = torch.full((rows * n_q * splits * d,), float("nan"), device=DEV)
+    ml = torch.full((rows * n_q * splits * 2,), float("nan"), device=DEV)
+    ops.decode_attention(q, case["k_pool"], case["v_pool"], out, case["positions"], case["row_request"], case["table"],
+                         scale=scale, window=case["window"] or 0, scratch_acc=acc, scratch_ml=ml, counters=counters,
+                         error_word=word)
+    ops.raise_on_error_word(word)
+    return out
+
+
+@pytest.mark.parametrize("n_q,n_kv,d,page,window", [(8, 2, 64, 16, None), (16, 1, 128, 8, 300), (6, 3, 128, 32, None),
+                                                    (4, 4, 128, 16, 70), (32, 8, 128, 16, None)])
+@pytest.mark.parametrize("lengths", [(1, 129, 700, 64, 257, 1000), (3000,), tuple(range(60, 100))])
+def test_decode_attention_of_single_tokens(n_q, n_kv, d, page, window, lengths):
+    """The tensor-core kernel for decoded tokens: one row per request, contexts from 1 to 3,000
+    keys, 1 to 40 rows (so from 55 blocks per (row, kv head) down to one), twice in a row with
+    the same counters, which are zero again afterwards."""
+    assert ops.decode_attention_takes(torch.bfloat16, n_q, n_kv, d)
+    assert not ops.decode_attention_takes(torch.float32, n_q, n_kv, d)
+    assert not ops.decode_attention_takes(torch.bfloat16, n_q, n_kv, 48)
+    case = paged_case(torch.bfloat16, n_q, n_kv, d, page, lengths, (1,) * len(lengths), window, seed=d + len(lengths))
     scale = 1.0 / math.sqrt(d)
-    separate = run_attention(case, scale, 128)
-    counters = torch.zeros(64, dtype=torch.int32, device=DEV)
-    for _ in range(2):
-        fused = run_attention(case, scale, 128, counters)
-        assert torch.equal(fused, separate)
-        assert int(counters.abs().sum()) == 0
-    close(fused, expected_attention(case, scale), torch.bfloat16, "fused merge")
+    want = expected_attention(case, scale)
+    counters = torch.zeros(len(lengths) * n_kv, dtype=torch.int32, device=DEV)
+    first = run_decode(case, scale, counters)
+    assert int(counters.abs().sum()) == 0
+    second = run_decode(case, scale, counters)
+    assert int(counters.abs().sum()) == 0
+    assert torch.equal(first, second)
+    close(first, want, torch.bfloat16, "decode attention")
+
+
+def test_decode_attention_finds_a_far_key_and_respects_the_window_edge():
+    case = paged_case(torch.bfloat16, 4, 2, 64, 16, (700, 530), (1, 1), None, seed=9, boost=(17, 3.0))
+    scale = 1.0 / 8.0
+    counters = torch.zeros(16, dtype=torch.int32, device=DEV)
+    out = run_decode(case, scale, counters)
+    close(out, expected_attention(case, scale), torch.bfloat16, "far key")
+    v_far = rounded(case["vs"][0][17], torch.bfloat16)
+    for h in (0, 2):
+        assert float((out[0, h].double().cpu() - v_far[h // 2]).abs().max()) < 0.05
+    window, n = 24, 100
+    for which, visible in ((n - window - 1, False), (n - window, True)):
+        case = paged_case(torch.bfloat16, 2, 1, 64, 8, (n,), (1,), window, seed=4, boost=(which, 4.0))
+        out = run_decode(case, scale, counters)
+        close(out, expected_attention(case, scale), torch.bfloat16, f"window edge key {which}")
+        near = float((out[0, 0].double().cpu() - rounded(case["vs"][0][which, 0], torch.bfloat16)).abs().max()) < 0.05
+        assert near == visible
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
