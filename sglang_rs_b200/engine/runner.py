@@ -44,6 +44,8 @@ class AttentionLaunch:
     #: for an unsplit launch: int32 [tiles, 4] = (first row, rows, request, first position), rows in tiles
     #: of at most ``StepPlanner.TILE_ROWS`` consecutive rows of one request
     tiles: Optional[torch.Tensor] = None
+    #: for a split launch: the most keys any of its rows sees (a bound is enough)
+    max_keys: Optional[int] = None
 
 
 @dataclass
@@ -205,7 +207,8 @@ class StepPlanner:
                 if need_acc <= self.SCRATCH_LIMIT or max_splits == 1:
                     break
                 split_size *= 2
-            launches.append(AttentionLaunch(0, split_rows, split_size, max_splits))
+            visible = int((pos + 1 - begin).max())
+            launches.append(AttentionLaunch(0, split_rows, split_size, max_splits, None, visible))
             scratch_acc = self._scratch_tensor("acc", need_acc)
             scratch_ml = self._scratch_tensor("ml", need_ml)
         if rows > split_rows:

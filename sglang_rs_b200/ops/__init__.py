@@ -238,19 +238,27 @@ def decode_attention_takes(dtype: torch.dtype, n_q: int, n_kv: int, head_dim: in
     return dtype == torch.bfloat16 and head_dim in (64, 128) and n_kv > 0 and n_q % n_kv == 0 and n_q // n_kv <= 16
 
 
-def decode_splits(rows: int, n_kv: int) -> int:
-    """Blocks per (row, kv head): enough that about three blocks per SM exist."""
-    return max(1, min(DECODE_MAX_SPLITS, DECODE_TARGET_BLOCKS // max(rows * n_kv, 1)))
+#: a block of the decode attention should walk at least this many 64-key units
+DECODE_MIN_UNITS = 2
+
+
+def decode_splits(rows: int, n_kv: int, max_keys: Optional[int] = None) -> int:
+    """Blocks per (row, kv head): enough that about three blocks per SM exist, but no more than
+    the longest row (``max_keys`` visible keys) can feed with ``DECODE_MIN_UNITS`` units each."""
+    splits = max(1, min(DECODE_MAX_SPLITS, DECODE_TARGET_BLOCKS // max(rows * n_kv, 1)))
+    if max_keys is not None:
+        splits = max(1, min(splits, -(-max_keys // 64) // DECODE_MIN_UNITS))
+    return splits
 
 
 def decode_attention(q: torch.Tensor, k_pool: torch.Tensor, v_pool: torch.Tensor, out: torch.Tensor,
                      positions: torch.Tensor, row_request: torch.Tensor, block_table: torch.Tensor, *,
                      scale: float, window: int, scratch_acc: torch.Tensor, scratch_ml: torch.Tensor,
-                     counters: torch.Tensor, error_word: torch.Tensor) -> None:
+                     counters: torch.Tensor, error_word: torch.Tensor, max_keys: Optional[int] = None) -> None:
     """Attention of decoded tokens (one row each), bfloat16, head_dim 64 or 128.
 
-    The keys of a (row, kv head) are shared by ``decode_splits(rows, n_kv)`` blocks; the block
-    that finishes last merges them.  ``counters``: int32, zero, at least rows * n_kv entries; they
+    The keys of a (row, kv head) are shared by ``decode_splits(rows, n_kv, max_keys)`` blocks
+    (``max_keys``: the most keys any row sees, if known); the block that finishes last merges them.  ``counters``: int32, zero, at least rows * n_kv entries; they
     are zero again afterwards.  Scratch: rows * n_q * splits * head_dim and rows * n_q * splits * 2
     floats."""
     _need(q, "q", torch.bfloat16); _need(out, "out", torch.bfloat16); _need(k_pool, "k_pool", torch.bfloat16)
@@ -262,7 +270,7 @@ def decode_attention(q: torch.Tensor, k_pool: torch.Tensor, v_pool: torch.Tensor
     num_pages, n_kv, page_size, pool_dim = k_pool.shape
     if pool_dim != head_dim or v_pool.shape != k_pool.shape or out.shape != q.shape:
         raise KernelError("decode_attention: shapes of q, out and the pools do not agree")
-    splits = decode_splits(rows, n_kv)
+    splits = decode_splits(rows, n_kv, max_keys)
     if scratch_acc.numel() < rows * n_q * splits * head_dim or scratch_ml.numel() < rows * n_q * splits * 2:
         raise KernelError("decode_attention: scratch tensors are too small")
     if counters.numel() < rows * n_kv:

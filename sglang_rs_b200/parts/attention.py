@@ -114,7 +114,7 @@ class GroupedQueryAttention(Mixer):
                                      ctx.row_request[b:e], batch.block_table, scale=self.scale,
                                      window=self.window or 0, scratch_acc=batch.scratch_acc,
                                      scratch_ml=batch.scratch_ml, counters=batch.counters,
-                                     error_word=ctx.error_word)
+                                     error_word=ctx.error_word, max_keys=launch.max_keys)
                 continue
             ops.paged_attention(q[b:e], cache.k_pool, cache.v_pool, out[b:e], ctx.positions[b:e],
                                 ctx.row_request[b:e], batch.block_table, scale=self.scale,
