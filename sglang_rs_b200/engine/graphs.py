@@ -170,14 +170,14 @@ class DecodeGraphs:
         current = torch.cuda.current_stream()
         side = torch.cuda.Stream()
         side.wait_stream(current)
-        with torch.cuda.stream(side):        # the same rows twice: libraries settle their workspaces
+        with torch.cuda.stream(side), ops.stream_scope():   # the same rows twice: libraries settle their workspaces
             for _ in range(2):
                 self.model.forward(ctx, caches, logit_rows)
         current.wait_stream(side)
         torch.cuda.synchronize()
         graph = torch.cuda.CUDAGraph()
         before = ops.launch_count
-        with torch.cuda.graph(graph, pool=self.pool):
+        with torch.cuda.graph(graph, pool=self.pool), ops.stream_scope():
             logits = self.model.forward(ctx, caches, logit_rows)
         self.kernels_per_replay[key] = ops.launch_count - before
         if self.pool is None:

@@ -263,7 +263,8 @@ class ModelRunner:
             else:
                 ctx, logit_rows = self.planner.flatten(entries)
                 caches = [self.cache.layer_cache(i) for i in range(len(self.model.program))]
-                logits = self.model.forward(ctx, caches, logit_rows)
+                with ops.stream_scope():
+                    logits = self.model.forward(ctx, caches, logit_rows)
         except Exception:
             for entry in entries:
                 self.cache.trim_reservation(entry.handle)

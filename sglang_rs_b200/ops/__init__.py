@@ -33,8 +33,29 @@ def _ptr(tensor: Optional[torch.Tensor]):
     return None if tensor is None else ctypes.c_void_p(tensor.data_ptr())
 
 
+_scoped_stream = None
+
+
 def _stream():
+    if _scoped_stream is not None:
+        return _scoped_stream
     return ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)
+
+
+class stream_scope:
+    """Looks up torch's current stream once for all kernel launches inside the ``with`` block
+    (the look-up costs as much as a small launch).  The current stream must not change inside."""
+
+    def __enter__(self):
+        global _scoped_stream
+        self._previous = _scoped_stream
+        _scoped_stream = ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)
+        return self
+
+    def __exit__(self, *exc):
+        global _scoped_stream
+        _scoped_stream = self._previous
+        return False
 
 
 def _need(tensor: torch.Tensor, name: str, dtype: Optional[torch.dtype] = None) -> None:
