@@ -1,0 +1,393 @@
+// Attention of prompt portions over the paged cache in bfloat16 on the 5th-generation tensor
+// cores: S = Q K^T and O += P V are tcgen05.mma with S, P and O in tensor memory; Q, K and V
+// come into shared memory by TMA (128-byte swizzle), K and V page by page through the block
+// table.
+//
+// Same formula and key ranges as the generic kernel (attention_kernels.cuh).  One block per
+// (tile of up to 128 consecutive rows of one request, query head), 192 threads:
+//   warp 0    copies: Q once, then for every block of 128 keys the pages of K and of V;
+//   warp 1    issues the products and owns the tensor memory;
+//   warps 2-5 softmax: thread t owns row t of the tile (one TMEM lane), so a row's maximum and
+//             sum need no exchange between threads.  Scores are kept in units of log2; the
+//             running maximum only moves (and O is only rescaled) when it grows by more than
+//             2^8, which bounds P by 2^8 and keeps the result exact up to 32-bit rounding.
+// Key blocks are aligned to absolute multiples of 128, so a row's arithmetic depends on its
+// own position only.  `tiles` holds four ints per tile: first row of the step, number of rows,
+// index of the request in the block table, position of the first row.
+//
+// Sizes: head_dim 64 or 128; page size a multiple of 8 and at most 128 that divides 128.
+// Every mbarrier wait is bounded; a wait that runs out flags SRB_FLAG_WAIT_TIMEOUT, every role
+// leaves its loop, tensor memory is freed and the block returns.  No TMA load uses multicast.
+#include "attention_kernels.cuh"
+#include "tcgen05_helpers.cuh"
+
+SRB_DEFINE_LAST_ERROR()
+
+#define TC_ROWS 128
+#define TC_KEYS 128
+#define TC_THREADS 192
+#define TC_STAGES 2
+#define TC_RESCALE_STEP 8.0f      // in units of log2
+
+struct TcArgs {
+  const int* tiles;
+  const int* block_table;
+  __nv_bfloat16* out;
+  int table_stride, n_q, n_kv, page_size, pool_rows, window;
+  float scale_log2;
+  int* error_word;
+};
+
+// M = 128, N = n, A and B bfloat16, D float; b_mn_major: B is [K rows][N contiguous] (V), else K-major
+__host__ __device__ constexpr unsigned tc_idesc(int n, bool b_mn_major) {
+  return (1u << 4) | (1u << 7) | (1u << 10) | ((b_mn_major ? 1u : 0u) << 16) | ((unsigned)(n >> 3) << 17) |
+         ((unsigned)(TC_ROWS >> 4) << 24);
+}
+
+// descriptor of a tile read as [K rows of 128 bytes][N]: 8-row groups 1024 bytes apart (stride), blocks
+// of 64 N-elements `lbo` bytes apart (leading)
+__device__ __forceinline__ unsigned long long smem_descriptor_mn(unsigned address, unsigned lbo) {
+  unsigned long long d = 0;
+  d |= (unsigned long long)((address & 0x3ffffu) >> 4);
+  d |= (unsigned long long)((lbo >> 4) & 0x3fffu) << 16;
+  d |= (unsigned long long)(1024u >> 4) << 32;
+  d |= 1ull << 46;
+  d |= 2ull << 61;
+  return d;
+}
+
+template <int D>
+__global__ void __launch_bounds__(TC_THREADS, 1)
+prefill_attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
+                            const __grid_constant__ CUtensorMap map_v, TcArgs args) {
+  constexpr int HALVES = D / 64;                           // 64-element (128-byte) column blocks of a head
+  constexpr int HALF_BYTES = TC_KEYS * 128;                // [128 rows][64] bfloat16
+  constexpr int Q_BYTES = HALVES * HALF_BYTES;
+  constexpr int KV_BYTES = HALVES * HALF_BYTES;
+  constexpr int STAGE_BYTES = 2 * KV_BYTES;                // K then V
+  constexpr unsigned S_COL = 0, O_COL = 128, P_COL = 256;  // tensor-memory columns
+  extern __shared__ unsigned char smem_unaligned[];
+  unsigned char* smem = reinterpret_cast<unsigned char*>(((uintptr_t)smem_unaligned + 1023) & ~(uintptr_t)1023);
+  unsigned char* q_smem = smem;
+  unsigned char* kv_smem = smem + Q_BYTES;
+  __shared__ __align__(8) unsigned long long q_full, k_full[TC_STAGES], v_full[TC_STAGES], kv_empty[TC_STAGES],
+      s_ready, p_ready, o_ready;
+  __shared__ unsigned tmem_holder;
+  __shared__ int abort_flag;
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int tile = blockIdx.x, head = blockIdx.y;
+  const int groups = args.n_q / args.n_kv;
+  const int kv_head = head / groups;
+  const int row_begin = args.tiles[4 * tile], n_rows = args.tiles[4 * tile + 1];
+  const int request = args.tiles[4 * tile + 2], pos_begin = args.tiles[4 * tile + 3];
+  const int kv_lo = (args.window > 0 && pos_begin + 1 > args.window) ? pos_begin + 1 - args.window : 0;
+  const int kv_hi = pos_begin + n_rows;
+  const int first_block = kv_lo / TC_KEYS, last_block = (kv_hi - 1) / TC_KEYS;
+  const int num_blocks = last_block - first_block + 1;
+
+  if (threadIdx.x == 0) {
+    abort_flag = 0;
+    mbar_init(smem_u32(&q_full), 1);
+    for (int s = 0; s < TC_STAGES; ++s) {
+      mbar_init(smem_u32(&k_full[s]), 1);
+      mbar_init(smem_u32(&v_full[s]), 1);
+      mbar_init(smem_u32(&kv_empty[s]), 1);
+    }
+    mbar_init(smem_u32(&s_ready), 1);
+    mbar_init(smem_u32(&p_ready), 128);
+    mbar_init(smem_u32(&o_ready), 1);
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  if (warp == 1) tmem_alloc(smem_u32(&tmem_holder), 512);
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const unsigned tmem_base = tmem_holder;
+
+  if (warp == 0) {
+    if (lane == 0) {
+      // Q: [128 rows][D] of this head, as HALVES tiles of [128][64]
+      mbar_expect_tx(smem_u32(&q_full), Q_BYTES);
+      for (int h = 0; h < HALVES; ++h)
+        tma_load_3d(smem_u32(q_smem + h * HALF_BYTES), &map_q, smem_u32(&q_full), h * 64, head, row_begin);
+      const int pages_per_block = TC_KEYS / args.page_size;
+      int issued = 0;
+      for (int i = 0; i < num_blocks; ++i) {
+        const int s = i % TC_STAGES;
+        const unsigned phase = (unsigned)(i / TC_STAGES) & 1u;
+        if (!mbar_wait(smem_u32(&kv_empty[s]), phase ^ 1u, &abort_flag)) break;
+        issued = i + 1;
+        unsigned char* k_stage = kv_smem + (size_t)s * STAGE_BYTES;
+        unsigned char* v_stage = k_stage + KV_BYTES;
+        const int key0 = (first_block + i) * TC_KEYS;
+        mbar_expect_tx(smem_u32(&k_full[s]), KV_BYTES);
+        mbar_expect_tx(smem_u32(&v_full[s]), KV_BYTES);
+#pragma unroll 1
+        for (int pass = 0; pass < 2; ++pass) {
+          const CUtensorMap* map = pass == 0 ? &map_k : &map_v;
+          unsigned char* stage = pass == 0 ? k_stage : v_stage;
+          const unsigned bar = smem_u32(pass == 0 ? &k_full[s] : &v_full[s]);
+          for (int pg = 0; pg < pages_per_block; ++pg) {
+            const int key = key0 + pg * args.page_size;
+            int row = args.pool_rows;                       // outside the pool: TMA fills zeros
+            if (key < kv_hi && key + args.page_size > kv_lo) {
+              const int page = args.block_table[(size_t)request * args.table_stride + key / args.page_size];
+              if (page < 0 || (long long)(page + 1) * args.n_kv * args.page_size > args.pool_rows)
+                atomicOr(args.error_word, SRB_FLAG_BAD_PAGE);
+              else
+                row = (page * args.n_kv + kv_head) * args.page_size;
+            }
+            for (int h = 0; h < HALVES; ++h)
+              tma_load_2d(smem_u32(stage + h * HALF_BYTES + pg * args.page_size * 128), map, bar, h * 64, row);
+          }
+        }
+      }
+      // copies still in flight write into this block's shared memory: wait for them before leaving
+      if (abort_flag) {
+        mbar_wait_timed(smem_u32(&q_full), 0);
+        for (int i = max(0, issued - TC_STAGES); i < issued; ++i) {
+          mbar_wait_timed(smem_u32(&k_full[i % TC_STAGES]), (unsigned)(i / TC_STAGES) & 1u);
+          mbar_wait_timed(smem_u32(&v_full[i % TC_STAGES]), (unsigned)(i / TC_STAGES) & 1u);
+        }
+      }
+    }
+  } else if (warp == 1) {
+    if (lane == 0) {
+      constexpr unsigned idesc_s = tc_idesc(TC_KEYS, false);
+      constexpr unsigned idesc_o = tc_idesc(D, true);
+      bool ok = mbar_wait(smem_u32(&q_full), 0, &abort_flag);
+      for (int i = 0; i < num_blocks && ok; ++i) {
+        const int s = i % TC_STAGES;
+        const unsigned phase = (unsigned)(i / TC_STAGES) & 1u;
+        const unsigned k_stage = smem_u32(kv_smem + (size_t)s * STAGE_BYTES);
+        const unsigned v_stage = k_stage + KV_BYTES;
+        ok = mbar_wait(smem_u32(&k_full[s]), phase, &abort_flag);
+        if (!ok) break;
+        tc_fence_after();
+        // S = Q K^T over D in steps of 16
+#pragma unroll
+        for (int k = 0; k < D / 16; ++k) {
+          const unsigned half = (k / 4) * HALF_BYTES, step = (k % 4) * 32;
+          umma_bf16(tmem_base + S_COL, smem_descriptor(smem_u32(q_smem) + half + step),
+                    smem_descriptor(k_stage + half + step), idesc_s, k > 0 ? 1u : 0u);
+        }
+        umma_commit(smem_u32(&s_ready));
+        // O += P V over the 128 keys in steps of 16 once the softmax warps have written P
+        ok = mbar_wait(smem_u32(&p_ready), (unsigned)i & 1u, &abort_flag) &&
+             mbar_wait(smem_u32(&v_full[s]), phase, &abort_flag);
+        if (!ok) break;
+        tc_fence_after();
+#pragma unroll
+        for (int k = 0; k < TC_KEYS / 16; ++k)
+          umma_bf16_tmem_a(tmem_base + O_COL, tmem_base + P_COL + k * 8,
+                           smem_descriptor_mn(v_stage + k * 16 * 128, HALF_BYTES), idesc_o, (i > 0 || k > 0) ? 1u : 0u);
+        umma_commit(smem_u32(&kv_empty[s]));
+        if (i == num_blocks - 1) umma_commit(smem_u32(&o_ready));
+      }
+    }
+  } else {
+    // softmax: thread = row
+    const int quarter = warp & 3;
+    const int r = quarter * 32 + lane;
+    const int pos_r = pos_begin + r;
+    const int lowest_r = (args.window > 0 && pos_r + 1 > args.window) ? pos_r + 1 - args.window : 0;
+    const bool row_live = r < n_rows;
+    const unsigned lane_address = tmem_base + ((unsigned)(quarter * 32) << 16);
+    float m_run = -INFINITY, l_run = 0.f;
+    bool ok = true;
+    for (int i = 0; i < num_blocks && ok; ++i) {
+      ok = mbar_wait(smem_u32(&s_ready), (unsigned)i & 1u, &abort_flag);
+      if (!ok) break;
+      tc_fence_after();
+      const int key0 = (first_block + i) * TC_KEYS;
+      const bool all_visible = n_rows == TC_ROWS && key0 + TC_KEYS - 1 <= pos_begin &&
+                               (args.window == 0 || key0 >= pos_begin + TC_ROWS - args.window);
+      // pass 1: the row's maximum over this block
+      float m_block = -INFINITY;
+#pragma unroll 1
+      for (int c = 0; c < TC_KEYS; c += 32) {
+        float sv[32];
+        tmem_load_32(lane_address + S_COL + c, sv);
+#pragma unroll
+        for (int j = 0; j < 32; ++j) {
+          const int key = key0 + c + j;
+          const bool visible = all_visible || (row_live && key <= pos_r && key >= lowest_r);
+          if (visible) m_block = fmaxf(m_block, sv[j] * args.scale_log2);
+        }
+      }
+      // the running maximum moves only when it must: P stays below 2^8
+      float corr = 1.f;
+      bool rescale = false;
+      if (m_block > m_run + TC_RESCALE_STEP || m_run == -INFINITY) {
+        const float m_new = fmaxf(m_run, m_block);
+        if (m_new > -INFINITY) {
+          corr = exp2f(m_run - m_new);                     // 0 the first time
+          rescale = m_run > -INFINITY;
+          m_run = m_new;
+        }
+      }
+      const float m_use = m_run == -INFINITY ? 0.f : m_run;
+      if (__any_sync(0xffffffffu, rescale)) {
+#pragma unroll 1
+        for (int c = 0; c < D; c += 32) {
+          float ov[32];
+          tmem_load_32(lane_address + O_COL + c, ov);
+#pragma unroll
+          for (int j = 0; j < 32; ++j) ov[j] *= corr;
+          tmem_store_32(lane_address + O_COL + c, ov);
+        }
+        tmem_store_wait();
+      }
+      l_run *= corr;
+      // pass 2: P = 2^(s - m), rounded to bfloat16 pairs, into tensor memory; the row's sum
+      float sum = 0.f;
+#pragma unroll 1
+      for (int c = 0; c < TC_KEYS; c += 32) {
+        float sv[32];
+        tmem_load_32(lane_address + S_COL + c, sv);
+        unsigned packed[16];
+#pragma unroll
+        for (int j = 0; j < 32; j += 2) {
+          float p0, p1;
+          {
+            const int key = key0 + c + j;
+            const bool visible = all_visible || (row_live && key <= pos_r && key >= lowest_r);
+            p0 = visible ? exp2f(sv[j] * args.scale_log2 - m_use) : 0.f;
+          }
+          {
+            const int key = key0 + c + j + 1;
+            const bool visible = all_visible || (row_live && key <= pos_r && key >= lowest_r);
+            p1 = visible ? exp2f(sv[j + 1] * args.scale_log2 - m_use) : 0.f;
+          }
+          sum += p0 + p1;
+          __nv_bfloat162 pair = __floats2bfloat162_rn(p0, p1);
+          packed[j / 2] = *reinterpret_cast<unsigned*>(&pair);
+        }
+        tmem_store_16(lane_address + P_COL + c / 2, packed);
+      }
+      tmem_store_wait();
+      l_run += sum;
+      tc_fence_before();
+      mbar_arrive(smem_u32(&p_ready));
+    }
+    if (ok) ok = mbar_wait(smem_u32(&o_ready), 0, &abort_flag);
+    if (ok) {
+      tc_fence_after();
+      const float inv = row_live && l_run > 0.f ? 1.0f / l_run : 0.f;
+      __nv_bfloat16* dst = args.out + ((size_t)(row_begin + r) * args.n_q + head) * D;
+#pragma unroll 1
+      for (int c = 0; c < D; c += 32) {
+        float ov[32];
+        tmem_load_32(lane_address + O_COL + c, ov);
+        if (row_live) {
+#pragma unroll
+          for (int j = 0; j < 32; j += 8) {
+            uint4 packed;
+            __nv_bfloat162* pair = reinterpret_cast<__nv_bfloat162*>(&packed);
+            pair[0] = __floats2bfloat162_rn(ov[j] * inv, ov[j + 1] * inv);
+            pair[1] = __floats2bfloat162_rn(ov[j + 2] * inv, ov[j + 3] * inv);
+            pair[2] = __floats2bfloat162_rn(ov[j + 4] * inv, ov[j + 5] * inv);
+            pair[3] = __floats2bfloat162_rn(ov[j + 6] * inv, ov[j + 7] * inv);
+            *reinterpret_cast<uint4*>(dst + c + j) = packed;
+          }
+        }
+      }
+    }
+    tc_fence_before();
+  }
+  __syncthreads();
+  if (threadIdx.x == 0 && abort_flag) atomicOr(args.error_word, SRB_FLAG_WAIT_TIMEOUT);
+  if (warp == 1) {
+    tc_fence_after();
+    tmem_dealloc(tmem_base, 512);
+  }
+}
+
+// ------------------------------------------------------------------------------- host side
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+static EncodeTiledFn encode_tiled() {
+  static EncodeTiledFn fn = nullptr;
+  static bool looked = false;
+  if (!looked) {
+    looked = true;
+    void* entry = nullptr;
+    cudaDriverEntryPointQueryResult result;
+    if (cudaGetDriverEntryPointByVersion("cuTensorMapEncodeTiled", &entry, 12000, cudaEnableDefault, &result) ==
+            cudaSuccess && result == cudaDriverEntryPointSuccess)
+      fn = reinterpret_cast<EncodeTiledFn>(entry);
+  }
+  return fn;
+}
+
+extern "C" int srb_prefill_tc_supports(int n_q, int n_kv, int head_dim, int page_size, int dtype) {
+  return dtype == SRB_DTYPE_BF16 && (head_dim == 64 || head_dim == 128) && n_kv > 0 && n_q % n_kv == 0 &&
+         page_size >= 8 && page_size % 8 == 0 && TC_KEYS % page_size == 0;
+}
+
+extern "C" int srb_prefill_tc_tile_rows() { return TC_ROWS; }
+
+template <int D>
+static int launch_tc(const CUtensorMap& map_q, const CUtensorMap& map_k, const CUtensorMap& map_v, const TcArgs& args,
+                     int num_tiles, cudaStream_t s) {
+  const size_t smem = (size_t)(D / 64) * TC_KEYS * 128 * (1 + 2 * TC_STAGES) + 1024;
+  auto kernel = prefill_attention_tc_kernel<D>;
+  SRB_CUDA_CALL(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+  dim3 grid(num_tiles, args.n_q);
+  kernel<<<grid, TC_THREADS, smem, s>>>(map_q, map_k, map_v, args);
+  SRB_LAUNCH_CHECK("prefill_attention_tc");
+  return SRB_OK;
+}
+
+// q, out: [rows, n_q, head_dim] bfloat16 of the whole step; pools [pages, n_kv, page_size, head_dim];
+// tiles: [num_tiles, 4] ints with at most 128 rows each.
+extern "C" int srb_prefill_attention_tc(const void* q, const void* k_pool, const void* v_pool, void* out,
+                                        const int* tiles, int num_tiles, int rows, const int* block_table,
+                                        int table_stride, int n_q, int n_kv, int head_dim, int page_size,
+                                        int num_pages, int window, float scale, int* error_word, void* stream) {
+  if (num_tiles <= 0) return SRB_OK;
+  if (!srb_prefill_tc_supports(n_q, n_kv, head_dim, page_size, SRB_DTYPE_BF16))
+    SRB_FAIL("prefill_attention_tc: head_dim %d (64 or 128), page size %d (a multiple of 8 dividing 128) or the "
+             "head counts are not taken by this kernel", head_dim, page_size);
+  if (num_pages <= 0 || table_stride <= 0 || window < 0 || rows <= 0)
+    SRB_FAIL("prefill_attention_tc: page count, table stride and rows must be positive");
+  if (n_q > 65535) SRB_FAIL("prefill_attention_tc: %d query heads exceed one launch", n_q);
+  if ((((uintptr_t)q | (uintptr_t)k_pool | (uintptr_t)v_pool) & 15) != 0)
+    SRB_FAIL("prefill_attention_tc: operands must be 16-byte aligned");
+  EncodeTiledFn encode = encode_tiled();
+  if (!encode) SRB_FAIL("prefill_attention_tc: the driver does not offer cuTensorMapEncodeTiled");
+  CUtensorMap map_q, map_k, map_v;
+  {
+    const cuuint64_t dims[3] = {(cuuint64_t)head_dim, (cuuint64_t)n_q, (cuuint64_t)rows};
+    const cuuint64_t strides[2] = {(cuuint64_t)head_dim * 2, (cuuint64_t)n_q * head_dim * 2};
+    const cuuint32_t box[3] = {64, 1, TC_ROWS};
+    const cuuint32_t elem[3] = {1, 1, 1};
+    const CUresult status = encode(&map_q, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3, const_cast<void*>(q), dims, strides,
+                                   box, elem, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                                   CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (status != CUDA_SUCCESS) SRB_FAIL("prefill_attention_tc: tensor map of q failed with %d", (int)status);
+  }
+  const long long pool_rows = (long long)num_pages * n_kv * page_size;
+  if (pool_rows > 0x7fffffffll) SRB_FAIL("prefill_attention_tc: the pool has too many rows for one tensor map");
+  for (int pass = 0; pass < 2; ++pass) {
+    const cuuint64_t dims[2] = {(cuuint64_t)head_dim, (cuuint64_t)pool_rows};
+    const cuuint64_t strides[1] = {(cuuint64_t)head_dim * 2};
+    const cuuint32_t box[2] = {64, (cuuint32_t)page_size};
+    const cuuint32_t elem[2] = {1, 1};
+    const CUresult status = encode(pass == 0 ? &map_k : &map_v, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2,
+                                   const_cast<void*>(pass == 0 ? k_pool : v_pool), dims, strides, box, elem,
+                                   CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                                   CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (status != CUDA_SUCCESS) SRB_FAIL("prefill_attention_tc: tensor map of a pool failed with %d", (int)status);
+  }
+  TcArgs args;
+  args.tiles = tiles; args.block_table = block_table; args.out = (__nv_bfloat16*)out; args.table_stride = table_stride;
+  args.n_q = n_q; args.n_kv = n_kv; args.page_size = page_size; args.pool_rows = (int)pool_rows; args.window = window;
+  args.scale_log2 = scale * 1.4426950408889634f; args.error_word = error_word;
+  cudaStream_t s = (cudaStream_t)stream;
+  if (head_dim == 64) return launch_tc<64>(map_q, map_k, map_v, args, num_tiles, s);
+  return launch_tc<128>(map_q, map_k, map_v, args, num_tiles, s);
+}

@@ -330,6 +330,35 @@ def tiled_attention(q: torch.Tensor, k_pool: torch.Tensor, v_pool: torch.Tensor,
         _ptr(error_word), _stream()))
 
 
+TC_TILE_ROWS = 128
+
+
+def tiled_attention_tc_takes(dtype: torch.dtype, n_q: int, n_kv: int, head_dim: int, page_size: int) -> bool:
+    """True if the tcgen05 kernel for prompt portions takes these sizes (the rule of
+    srb_prefill_tc_supports)."""
+    return (dtype == torch.bfloat16 and head_dim in (64, 128) and n_kv > 0 and n_q % n_kv == 0
+            and page_size >= 8 and page_size % 8 == 0 and 128 % page_size == 0)
+
+
+def tiled_attention_tc(q: torch.Tensor, k_pool: torch.Tensor, v_pool: torch.Tensor, out: torch.Tensor,
+                       tiles: torch.Tensor, block_table: torch.Tensor, *, scale: float, window: int,
+                       error_word: torch.Tensor) -> None:
+    """Attention of prompt portions on tcgen05 tensor cores (S, P and O in tensor memory, operands
+    by TMA).  ``tiles`` as for :func:`tiled_attention`, with at most 128 rows per tile."""
+    _need(q, "q", torch.bfloat16); _need(out, "out", torch.bfloat16); _need(k_pool, "k_pool", torch.bfloat16)
+    _need(v_pool, "v_pool", torch.bfloat16); _need(tiles, "tiles", torch.int32)
+    _need(block_table, "block_table", torch.int32)
+    rows, n_q, head_dim = q.shape
+    num_pages, n_kv, page_size, pool_dim = k_pool.shape
+    if pool_dim != head_dim or v_pool.shape != k_pool.shape or out.shape != q.shape or tiles.shape[-1] != 4:
+        raise KernelError("tiled_attention_tc: shapes of q, out, the pools and the tiles do not agree")
+    lib = load_library("attention_prefill_tc")
+    _check(lib, lib.srb_prefill_attention_tc(
+        _ptr(q), _ptr(k_pool), _ptr(v_pool), _ptr(out), _ptr(tiles), tiles.shape[0], rows, _ptr(block_table),
+        block_table.stride(0), n_q, n_kv, head_dim, page_size, num_pages, int(window), ctypes.c_float(scale),
+        _ptr(error_word), _stream()))
+
+
 # --------------------------------------------------------------------------- matrix products
 
 #: up to this many rows a bfloat16 product runs on this package's tcgen05 kernel; above it on cuBLAS

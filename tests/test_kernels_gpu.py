@@ -318,13 +318,47 @@ def tiles_of(case, tile_rows=64):
     return torch.tensor(tiles, dtype=torch.int32, device=DEV)
 
 
-def run_tiled(case, scale):
+def run_tiled(case, scale, tensor_memory=False):
     out = torch.full_like(case["q"], float("nan"))
     word = ops.new_error_word(DEV)
-    ops.tiled_attention(case["q"], case["k_pool"], case["v_pool"], out, tiles_of(case), case["table"], scale=scale,
-                        window=case["window"] or 0, error_word=word)
+    if tensor_memory:
+        ops.tiled_attention_tc(case["q"], case["k_pool"], case["v_pool"], out, tiles_of(case, 128), case["table"],
+                               scale=scale, window=case["window"] or 0, error_word=word)
+    else:
+        ops.tiled_attention(case["q"], case["k_pool"], case["v_pool"], out, tiles_of(case), case["table"], scale=scale,
+                            window=case["window"] or 0, error_word=word)
     ops.raise_on_error_word(word)
     return out
+
+
+@pytest.mark.parametrize("n_q,n_kv,d,page,window", [(4, 2, 64, 16, None), (6, 3, 128, 8, None), (16, 2, 128, 32, 100),
+                                                    (5, 1, 64, 16, 37), (3, 3, 128, 128, 64), (32, 8, 128, 16, None)])
+def test_tcgen05_attention_of_prompt_portions(n_q, n_kv, d, page, window):
+    """The tensor-memory kernel: portions of 1 to 300 rows at the end of sequences of up to 700 keys."""
+    assert ops.tiled_attention_tc_takes(torch.bfloat16, n_q, n_kv, d, page)
+    assert not ops.tiled_attention_tc_takes(torch.bfloat16, n_q, n_kv, d, 4)
+    assert not ops.tiled_attention_tc_takes(torch.float32, n_q, n_kv, d, page)
+    lengths, rows = (1, 33, 300, 64, 257, 191, 700), (1, 5, 130, 64, 70, 191, 300)
+    case = paged_case(torch.bfloat16, n_q, n_kv, d, page, lengths, rows, window, seed=3 * d + page)
+    scale = 0.9 / math.sqrt(d)
+    close(run_tiled(case, scale, tensor_memory=True), expected_attention(case, scale), torch.bfloat16, "tcgen05 attention")
+
+
+def test_tcgen05_attention_finds_a_far_key_and_respects_the_window_edge():
+    case = paged_case(torch.bfloat16, 4, 2, 64, 16, (700, 530), (70, 3), None, seed=9, boost=(17, 3.0))
+    scale = 1.0 / 8.0
+    out = run_tiled(case, scale, tensor_memory=True)
+    close(out, expected_attention(case, scale), torch.bfloat16, "far key")
+    v_far = rounded(case["vs"][0][17], torch.bfloat16)
+    for h in (0, 2):
+        assert float((out[69, h].double().cpu() - v_far[h // 2]).abs().max()) < 0.05
+    window, n = 24, 100
+    for which, visible in ((n - window - 1, False), (n - window, True)):
+        case = paged_case(torch.bfloat16, 2, 1, 64, 8, (n,), (5,), window, seed=4, boost=(which, 4.0))
+        out = run_tiled(case, scale, tensor_memory=True)
+        close(out, expected_attention(case, scale), torch.bfloat16, f"window edge key {which}")
+        near = float((out[4, 0].double().cpu() - rounded(case["vs"][0][which, 0], torch.bfloat16)).abs().max()) < 0.05
+        assert near == visible
 
 
 @pytest.mark.parametrize("n_q,n_kv,d,page,window", [(4, 2, 64, 16, None), (6, 3, 128, 8, None), (16, 2, 128, 32, 100),
