@@ -40,7 +40,8 @@ prefill_attention_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat1
   __nv_bfloat16* qs = kv + 2 * PF_KEYS * D;                              // [64][D]
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int tile = blockIdx.x, head = blockIdx.y;
+  // heads are the fast grid dimension: tiles arrive sorted by falling work, so the long ones start first
+  const int tile = blockIdx.y, head = blockIdx.x;
   const int groups = p.n_q / p.n_kv;
   const int kv_head = head / groups;
   const int row_begin = tiles[4 * tile], n_rows = tiles[4 * tile + 1];
@@ -240,7 +241,8 @@ static int launch_prefill(const void* q, const void* k_pool, const void* v_pool,
   const size_t smem = (size_t)(4 * PF_KEYS) * D * sizeof(__nv_bfloat16);
   SRB_CUDA_CALL(cudaFuncSetAttribute(prefill_attention_kernel<D>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                      (int)smem));
-  dim3 grid(num_tiles, p.n_q);
+  dim3 grid(p.n_q, num_tiles);
+  if (num_tiles > 65535) SRB_FAIL("prefill_attention: %d tiles exceed one launch", num_tiles);
   prefill_attention_kernel<D><<<grid, PF_WARPS * 32, smem, s>>>(
       (const __nv_bfloat16*)q, (const __nv_bfloat16*)k_pool, (const __nv_bfloat16*)v_pool, (__nv_bfloat16*)out,
       tiles, p);
@@ -265,7 +267,6 @@ extern "C" int srb_prefill_attention(const void* q, const void* k_pool, const vo
              head_dim, n_q, n_kv);
   if (page_size <= 0 || num_pages <= 0 || table_stride <= 0 || window < 0)
     SRB_FAIL("prefill_attention: page size, page count and table stride must be positive");
-  if (n_q > 65535) SRB_FAIL("prefill_attention: %d query heads exceed one launch", n_q);
   AttnParams p;
   p.positions = nullptr; p.row_request = nullptr; p.block_table = block_table;
   p.table_stride = table_stride; p.n_q = n_q; p.n_kv = n_kv; p.head_dim = head_dim;

@@ -5,17 +5,19 @@
 //
 // Same formula and key ranges as the generic kernel (attention_kernels.cuh).  One block per
 // (tile of up to 128 consecutive rows of one request, query head), 192 threads:
-//   warp 0    copies: Q once, then for every block of 128 keys the pages of K and of V;
+//   warp 0    copies: Q once, then for every block of 64 keys the pages of K and of V;
 //   warp 1    issues the products and owns the tensor memory;
 //   warps 2-5 softmax: thread t owns row t of the tile (one TMEM lane), so a row's maximum and
 //             sum need no exchange between threads.  Scores are kept in units of log2; the
 //             running maximum only moves (and O is only rescaled) when it grows by more than
 //             2^8, which bounds P by 2^8 and keeps the result exact up to 32-bit rounding.
-// Key blocks are aligned to absolute multiples of 128, so a row's arithmetic depends on its
+// Key blocks are aligned to absolute multiples of 64, so a row's arithmetic depends on its
 // own position only.  `tiles` holds four ints per tile: first row of the step, number of rows,
 // index of the request in the block table, position of the first row.
 //
-// Sizes: head_dim 64 or 128; page size a multiple of 8 and at most 128 that divides 128.
+// Sizes: head_dim 64 or 128; page size a multiple of 8 that divides 64.  A block needs 96 KB of
+// shared memory and 256 columns of tensor memory, so two blocks share an SM and one block's
+// softmax runs while the other's products do.
 // Every mbarrier wait is bounded; a wait that runs out flags SRB_FLAG_WAIT_TIMEOUT, every role
 // leaves its loop, tensor memory is freed and the block returns.  No TMA load uses multicast.
 #include "attention_kernels.cuh"
@@ -24,7 +26,7 @@
 SRB_DEFINE_LAST_ERROR()
 
 #define TC_ROWS 128
-#define TC_KEYS 128
+#define TC_KEYS 64
 #define TC_THREADS 192
 #define TC_STAGES 2
 #define TC_RESCALE_STEP 8.0f      // in units of log2
@@ -57,15 +59,17 @@ __device__ __forceinline__ unsigned long long smem_descriptor_mn(unsigned addres
 }
 
 template <int D>
-__global__ void __launch_bounds__(TC_THREADS, 1)
+__global__ void __launch_bounds__(TC_THREADS, 2)
 prefill_attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
                             const __grid_constant__ CUtensorMap map_v, TcArgs args) {
   constexpr int HALVES = D / 64;                           // 64-element (128-byte) column blocks of a head
-  constexpr int HALF_BYTES = TC_KEYS * 128;                // [128 rows][64] bfloat16
-  constexpr int Q_BYTES = HALVES * HALF_BYTES;
+  constexpr int Q_HALF_BYTES = TC_ROWS * 128;              // [128 rows][64] bfloat16
+  constexpr int HALF_BYTES = TC_KEYS * 128;                // [64 keys][64] bfloat16
+  constexpr int Q_BYTES = HALVES * Q_HALF_BYTES;
   constexpr int KV_BYTES = HALVES * HALF_BYTES;
   constexpr int STAGE_BYTES = 2 * KV_BYTES;                // K then V
-  constexpr unsigned S_COL = 0, O_COL = 128, P_COL = 256;  // tensor-memory columns
+  constexpr unsigned S_COL = 0, P_COL = 64, O_COL = 128;   // tensor-memory columns (256 allocated)
+  constexpr unsigned TMEM_COLUMNS = 256;                   // two blocks share an SM's 512
   extern __shared__ unsigned char smem_unaligned[];
   unsigned char* smem = reinterpret_cast<unsigned char*>(((uintptr_t)smem_unaligned + 1023) & ~(uintptr_t)1023);
   unsigned char* q_smem = smem;
@@ -76,7 +80,8 @@ prefill_attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
   __shared__ int abort_flag;
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int tile = blockIdx.x, head = blockIdx.y;
+  // heads are the fast grid dimension: tiles arrive sorted by falling work, so the long ones start first
+  const int tile = blockIdx.y, head = blockIdx.x;
   const int groups = args.n_q / args.n_kv;
   const int kv_head = head / groups;
   const int row_begin = args.tiles[4 * tile], n_rows = args.tiles[4 * tile + 1];
@@ -99,7 +104,7 @@ prefill_attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
     mbar_init(smem_u32(&o_ready), 1);
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
-  if (warp == 1) tmem_alloc(smem_u32(&tmem_holder), 512);
+  if (warp == 1) tmem_alloc(smem_u32(&tmem_holder), TMEM_COLUMNS);
   tc_fence_before();
   __syncthreads();
   tc_fence_after();
@@ -110,7 +115,7 @@ prefill_attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
       // Q: [128 rows][D] of this head, as HALVES tiles of [128][64]
       mbar_expect_tx(smem_u32(&q_full), Q_BYTES);
       for (int h = 0; h < HALVES; ++h)
-        tma_load_3d(smem_u32(q_smem + h * HALF_BYTES), &map_q, smem_u32(&q_full), h * 64, head, row_begin);
+        tma_load_3d(smem_u32(q_smem + h * Q_HALF_BYTES), &map_q, smem_u32(&q_full), h * 64, head, row_begin);
       const int pages_per_block = TC_KEYS / args.page_size;
       int issued = 0;
       for (int i = 0; i < num_blocks; ++i) {
@@ -168,9 +173,9 @@ prefill_attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
         // S = Q K^T over D in steps of 16
 #pragma unroll
         for (int k = 0; k < D / 16; ++k) {
-          const unsigned half = (k / 4) * HALF_BYTES, step = (k % 4) * 32;
-          umma_bf16(tmem_base + S_COL, smem_descriptor(smem_u32(q_smem) + half + step),
-                    smem_descriptor(k_stage + half + step), idesc_s, k > 0 ? 1u : 0u);
+          const unsigned step = (k % 4) * 32;
+          umma_bf16(tmem_base + S_COL, smem_descriptor(smem_u32(q_smem) + (k / 4) * Q_HALF_BYTES + step),
+                    smem_descriptor(k_stage + (k / 4) * HALF_BYTES + step), idesc_s, k > 0 ? 1u : 0u);
         }
         umma_commit(smem_u32(&s_ready));
         // O += P V over the 128 keys in steps of 16 once the softmax warps have written P
@@ -203,19 +208,24 @@ prefill_attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
       const int key0 = (first_block + i) * TC_KEYS;
       const bool all_visible = n_rows == TC_ROWS && key0 + TC_KEYS - 1 <= pos_begin &&
                                (args.window == 0 || key0 >= pos_begin + TC_ROWS - args.window);
-      // pass 1: the row's maximum over this block
-      float m_block = -INFINITY;
-#pragma unroll 1
-      for (int c = 0; c < TC_KEYS; c += 32) {
-        float sv[32];
-        tmem_load_32(lane_address + S_COL + c, sv);
+      // the row's 64 scores, once, in units of log2; masked keys are -inf
+      float sv[TC_KEYS];
+      {
+        float part[32];
 #pragma unroll
-        for (int j = 0; j < 32; ++j) {
-          const int key = key0 + c + j;
-          const bool visible = all_visible || (row_live && key <= pos_r && key >= lowest_r);
-          if (visible) m_block = fmaxf(m_block, sv[j] * args.scale_log2);
+        for (int c = 0; c < TC_KEYS; c += 32) {
+          tmem_load_32(lane_address + S_COL + c, part);
+#pragma unroll
+          for (int j = 0; j < 32; ++j) {
+            const int key = key0 + c + j;
+            const bool visible = all_visible || (row_live && key <= pos_r && key >= lowest_r);
+            sv[c + j] = visible ? part[j] * args.scale_log2 : -INFINITY;
+          }
         }
       }
+      float m_block = -INFINITY;
+#pragma unroll
+      for (int j = 0; j < TC_KEYS; ++j) m_block = fmaxf(m_block, sv[j]);
       // the running maximum moves only when it must: P stays below 2^8
       float corr = 1.f;
       bool rescale = false;
@@ -237,29 +247,16 @@ prefill_attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
           for (int j = 0; j < 32; ++j) ov[j] *= corr;
           tmem_store_32(lane_address + O_COL + c, ov);
         }
-        tmem_store_wait();
       }
       l_run *= corr;
-      // pass 2: P = 2^(s - m), rounded to bfloat16 pairs, into tensor memory; the row's sum
+      // P = 2^(s - m), rounded to bfloat16 pairs, into tensor memory; the row's sum
       float sum = 0.f;
-#pragma unroll 1
+#pragma unroll
       for (int c = 0; c < TC_KEYS; c += 32) {
-        float sv[32];
-        tmem_load_32(lane_address + S_COL + c, sv);
         unsigned packed[16];
 #pragma unroll
         for (int j = 0; j < 32; j += 2) {
-          float p0, p1;
-          {
-            const int key = key0 + c + j;
-            const bool visible = all_visible || (row_live && key <= pos_r && key >= lowest_r);
-            p0 = visible ? exp2f(sv[j] * args.scale_log2 - m_use) : 0.f;
-          }
-          {
-            const int key = key0 + c + j + 1;
-            const bool visible = all_visible || (row_live && key <= pos_r && key >= lowest_r);
-            p1 = visible ? exp2f(sv[j + 1] * args.scale_log2 - m_use) : 0.f;
-          }
+          const float p0 = exp2f(sv[c + j] - m_use), p1 = exp2f(sv[c + j + 1] - m_use);    // 2^(-inf) = 0
           sum += p0 + p1;
           __nv_bfloat162 pair = __floats2bfloat162_rn(p0, p1);
           packed[j / 2] = *reinterpret_cast<unsigned*>(&pair);
@@ -300,7 +297,7 @@ prefill_attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
   if (threadIdx.x == 0 && abort_flag) atomicOr(args.error_word, SRB_FLAG_WAIT_TIMEOUT);
   if (warp == 1) {
     tc_fence_after();
-    tmem_dealloc(tmem_base, 512);
+    tmem_dealloc(tmem_base, TMEM_COLUMNS);
   }
 }
 
@@ -333,10 +330,11 @@ extern "C" int srb_prefill_tc_tile_rows() { return TC_ROWS; }
 template <int D>
 static int launch_tc(const CUtensorMap& map_q, const CUtensorMap& map_k, const CUtensorMap& map_v, const TcArgs& args,
                      int num_tiles, cudaStream_t s) {
-  const size_t smem = (size_t)(D / 64) * TC_KEYS * 128 * (1 + 2 * TC_STAGES) + 1024;
+  const size_t smem = (size_t)(D / 64) * 128 * (TC_ROWS + 2 * TC_STAGES * TC_KEYS) + 1024;
   auto kernel = prefill_attention_tc_kernel<D>;
   SRB_CUDA_CALL(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-  dim3 grid(num_tiles, args.n_q);
+  dim3 grid(args.n_q, num_tiles);
+  if (num_tiles > 65535) SRB_FAIL("prefill_attention_tc: %d tiles exceed one launch", num_tiles);
   kernel<<<grid, TC_THREADS, smem, s>>>(map_q, map_k, map_v, args);
   SRB_LAUNCH_CHECK("prefill_attention_tc");
   return SRB_OK;
@@ -350,11 +348,10 @@ extern "C" int srb_prefill_attention_tc(const void* q, const void* k_pool, const
                                         int num_pages, int window, float scale, int* error_word, void* stream) {
   if (num_tiles <= 0) return SRB_OK;
   if (!srb_prefill_tc_supports(n_q, n_kv, head_dim, page_size, SRB_DTYPE_BF16))
-    SRB_FAIL("prefill_attention_tc: head_dim %d (64 or 128), page size %d (a multiple of 8 dividing 128) or the "
+    SRB_FAIL("prefill_attention_tc: head_dim %d (64 or 128), page size %d (a multiple of 8 dividing 64) or the "
              "head counts are not taken by this kernel", head_dim, page_size);
   if (num_pages <= 0 || table_stride <= 0 || window < 0 || rows <= 0)
     SRB_FAIL("prefill_attention_tc: page count, table stride and rows must be positive");
-  if (n_q > 65535) SRB_FAIL("prefill_attention_tc: %d query heads exceed one launch", n_q);
   if ((((uintptr_t)q | (uintptr_t)k_pool | (uintptr_t)v_pool) & 15) != 0)
     SRB_FAIL("prefill_attention_tc: operands must be 16-byte aligned");
   EncodeTiledFn encode = encode_tiled();

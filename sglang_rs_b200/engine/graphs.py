@@ -159,7 +159,7 @@ class DecodeGraphs:
                              device=self.device)
             keep += [acc, ml]
             ctx.paged[key] = PagedBatch(part(f"table{g}").view(bucket, stride), part(f"slots{g}"),
-                                        [AttentionLaunch(0, bucket, StepPlanner.SPLIT_SIZE, splits[g], None,
+                                        [AttentionLaunch(0, bucket, StepPlanner.SPLIT_SIZE, splits[g], None, None,
                                                          splits[g] * StepPlanner.SPLIT_SIZE)], acc, ml,
                                         self.planner.counters)
         return ctx, part("logit_rows"), keep

@@ -44,6 +44,8 @@ class AttentionLaunch:
     #: for an unsplit launch: int32 [tiles, 4] = (first row, rows, request, first position), rows in tiles
     #: of at most ``StepPlanner.TILE_ROWS`` consecutive rows of one request
     tiles: Optional[torch.Tensor] = None
+    #: the same rows cut into tiles of at most ``StepPlanner.WIDE_TILE_ROWS`` (for the tcgen05 kernel)
+    wide_tiles: Optional[torch.Tensor] = None
     #: for a split launch: the most keys any of its rows sees (a bound is enough)
     max_keys: Optional[int] = None
 
@@ -89,6 +91,7 @@ class StepPlanner:
     SPLIT_ROWS_PER_REQUEST = 1
     #: rows of one request that the tiled attention kernel takes per block
     TILE_ROWS = 64
+    WIDE_TILE_ROWS = 128
     #: floats of attention scratch above which the split is made coarser
     SCRATCH_LIMIT = 64 << 20
 
@@ -149,31 +152,39 @@ class StepPlanner:
                 slots[key][begin:begin + len(pos)] = pages * page_size + pos % page_size
 
         tiles: List[int] = []
+        wide_tiles: List[int] = []
         for slot in range(len(order)):
             if cu_rows[slot] < split_rows:
                 continue
-            for first in range(cu_rows[slot], cu_rows[slot + 1], self.TILE_ROWS):
-                tiles += [first, min(self.TILE_ROWS, cu_rows[slot + 1] - first), slot,
-                          start_positions[slot] + first - cu_rows[slot]]
+            for size, into in ((self.TILE_ROWS, tiles), (self.WIDE_TILE_ROWS, wide_tiles)):
+                for first in range(cu_rows[slot], cu_rows[slot + 1], size):
+                    into += [first, min(size, cu_rows[slot + 1] - first), slot,
+                             start_positions[slot] + first - cu_rows[slot]]
+        # tiles with the most keys first: the blocks that work longest start first
+        def by_falling_work(flat: List[int]) -> np.ndarray:
+            table = np.asarray(flat, dtype=np.int32).reshape(-1, 4)
+            return table[np.argsort(-(table[:, 1] + table[:, 3]), kind="stable")].reshape(-1)
+        tiles, wide_tiles = by_falling_work(tiles), by_falling_work(wide_tiles)
         pieces = [np.asarray(tokens, dtype=np.int32), np.asarray(positions, dtype=np.int32),
                   np.asarray(row_request, dtype=np.int32), np.asarray(cu_rows, dtype=np.int32),
                   np.asarray(state_slots, dtype=np.int32), np.asarray(logit_rows, dtype=np.int32),
-                  np.asarray(tiles, dtype=np.int32)]
+                  np.asarray(tiles, dtype=np.int32), np.asarray(wide_tiles, dtype=np.int32)]
         for key in groups:
             pieces.append(tables[key].reshape(-1))
             pieces.append(slots[key])
         device_pieces = self._upload(pieces)
-        token_ids, positions_d, row_request_d, cu_rows_d, state_slots_d, logit_rows_d, tiles_d = device_pieces[:7]
-        tiles_d = tiles_d.view(-1, 4)
+        (token_ids, positions_d, row_request_d, cu_rows_d, state_slots_d, logit_rows_d, tiles_d,
+         wide_tiles_d) = device_pieces[:8]
+        tiles_d, wide_tiles_d = tiles_d.view(-1, 4), wide_tiles_d.view(-1, 4)
 
         ctx = StepContext(self.device, self.dtype, rows, len(order), token_ids, positions_d, row_request_d,
                           cu_rows_d, state_slots_d, self.error_word, host_cu_rows=cu_rows,
                           host_start_positions=start_positions, host_state_slots=state_slots)
         np_positions = np.asarray(positions, dtype=np.int64)
         for g, key in enumerate(groups):
-            table_d = device_pieces[7 + 2 * g].view(len(order), stride)
-            slots_d = device_pieces[8 + 2 * g]
-            ctx.paged[key] = self._plan(key, table_d, slots_d, np_positions, split_rows, rows, tiles_d)
+            table_d = device_pieces[8 + 2 * g].view(len(order), stride)
+            slots_d = device_pieces[9 + 2 * g]
+            ctx.paged[key] = self._plan(key, table_d, slots_d, np_positions, split_rows, rows, tiles_d, wide_tiles_d)
         return ctx, (logit_rows_d if logit_rows else None)
 
     def _upload(self, pieces: Sequence[np.ndarray]) -> List[torch.Tensor]:
@@ -190,7 +201,7 @@ class StepPlanner:
         return [on_device[offset:offset + size] for offset, size in zip(offsets[:-1], sizes)]
 
     def _plan(self, key, table_d, slots_d, positions: np.ndarray, split_rows: int, rows: int,
-              tiles_d: Optional[torch.Tensor] = None) -> PagedBatch:
+              tiles_d: Optional[torch.Tensor] = None, wide_tiles_d: Optional[torch.Tensor] = None) -> PagedBatch:
         window = self.cache.windows[key]
         launches: List[AttentionLaunch] = []
         scratch_acc = scratch_ml = None
@@ -208,11 +219,11 @@ class StepPlanner:
                     break
                 split_size *= 2
             visible = int((pos + 1 - begin).max())
-            launches.append(AttentionLaunch(0, split_rows, split_size, max_splits, None, visible))
+            launches.append(AttentionLaunch(0, split_rows, split_size, max_splits, None, None, visible))
             scratch_acc = self._scratch_tensor("acc", need_acc)
             scratch_ml = self._scratch_tensor("ml", need_ml)
         if rows > split_rows:
-            launches.append(AttentionLaunch(split_rows, rows, 0, 1, tiles_d))
+            launches.append(AttentionLaunch(split_rows, rows, 0, 1, tiles_d, wide_tiles_d))
         return PagedBatch(table_d, slots_d, launches, scratch_acc, scratch_ml, self.counters)
 
     def _scratch_tensor(self, name: str, floats: int) -> torch.Tensor:

@@ -337,7 +337,7 @@ def tiled_attention_tc_takes(dtype: torch.dtype, n_q: int, n_kv: int, head_dim: 
     """True if the tcgen05 kernel for prompt portions takes these sizes (the rule of
     srb_prefill_tc_supports)."""
     return (dtype == torch.bfloat16 and head_dim in (64, 128) and n_kv > 0 and n_q % n_kv == 0
-            and page_size >= 8 and page_size % 8 == 0 and 128 % page_size == 0)
+            and page_size >= 8 and page_size % 8 == 0 and 64 % page_size == 0)
 
 
 def tiled_attention_tc(q: torch.Tensor, k_pool: torch.Tensor, v_pool: torch.Tensor, out: torch.Tensor,

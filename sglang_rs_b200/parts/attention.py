@@ -103,6 +103,11 @@ class GroupedQueryAttention(Mixer):
         out = torch.empty_like(q)
         for launch in batch.launches:
             b, e = launch.begin, launch.end
+            if launch.wide_tiles is not None and ops.tiled_attention_tc_takes(q.dtype, self.n_q, self.n_kv, self.d,
+                                                                              cache.k_pool.shape[2]):
+                ops.tiled_attention_tc(q, cache.k_pool, cache.v_pool, out, launch.wide_tiles, batch.block_table,
+                                       scale=self.scale, window=self.window or 0, error_word=ctx.error_word)
+                continue
             if launch.tiles is not None and ops.tiled_attention_takes(q.dtype, self.n_q, self.n_kv, self.d):
                 ops.tiled_attention(q, cache.k_pool, cache.v_pool, out, launch.tiles, batch.block_table,
                                     scale=self.scale, window=self.window or 0, error_word=ctx.error_word)

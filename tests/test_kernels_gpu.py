@@ -332,7 +332,7 @@ def run_tiled(case, scale, tensor_memory=False):
 
 
 @pytest.mark.parametrize("n_q,n_kv,d,page,window", [(4, 2, 64, 16, None), (6, 3, 128, 8, None), (16, 2, 128, 32, 100),
-                                                    (5, 1, 64, 16, 37), (3, 3, 128, 128, 64), (32, 8, 128, 16, None)])
+                                                    (5, 1, 64, 16, 37), (3, 3, 128, 64, 64), (32, 8, 128, 16, None)])
 def test_tcgen05_attention_of_prompt_portions(n_q, n_kv, d, page, window):
     """The tensor-memory kernel: portions of 1 to 300 rows at the end of sequences of up to 700 keys."""
     assert ops.tiled_attention_tc_takes(torch.bfloat16, n_q, n_kv, d, page)
