@@ -208,24 +208,24 @@ prefill_attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
       const int key0 = (first_block + i) * TC_KEYS;
       const bool all_visible = n_rows == TC_ROWS && key0 + TC_KEYS - 1 <= pos_begin &&
                                (args.window == 0 || key0 >= pos_begin + TC_ROWS - args.window);
-      // the row's 64 scores, once, in units of log2; masked keys are -inf
+      // the row's 64 raw scores, once; masked keys become -inf.  Four running maxima keep the
+      // chain of dependent instructions short.
       float sv[TC_KEYS];
-      {
-        float part[32];
+      tmem_load_64(lane_address + S_COL, sv);
+      if (!all_visible) {
 #pragma unroll
-        for (int c = 0; c < TC_KEYS; c += 32) {
-          tmem_load_32(lane_address + S_COL + c, part);
-#pragma unroll
-          for (int j = 0; j < 32; ++j) {
-            const int key = key0 + c + j;
-            const bool visible = all_visible || (row_live && key <= pos_r && key >= lowest_r);
-            sv[c + j] = visible ? part[j] * args.scale_log2 : -INFINITY;
-          }
+        for (int j = 0; j < TC_KEYS; ++j) {
+          const int key = key0 + j;
+          if (!(row_live && key <= pos_r && key >= lowest_r)) sv[j] = -INFINITY;
         }
       }
-      float m_block = -INFINITY;
+      float mx[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
 #pragma unroll
-      for (int j = 0; j < TC_KEYS; ++j) m_block = fmaxf(m_block, sv[j]);
+      for (int j = 0; j < TC_KEYS; j += 4) {
+        mx[0] = fmaxf(mx[0], sv[j]); mx[1] = fmaxf(mx[1], sv[j + 1]);
+        mx[2] = fmaxf(mx[2], sv[j + 2]); mx[3] = fmaxf(mx[3], sv[j + 3]);
+      }
+      const float m_block = fmaxf(fmaxf(mx[0], mx[1]), fmaxf(mx[2], mx[3])) * args.scale_log2;   // in units of log2
       // the running maximum moves only when it must: P stays below 2^8
       float corr = 1.f;
       bool rescale = false;
@@ -249,20 +249,26 @@ prefill_attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
         }
       }
       l_run *= corr;
-      // P = 2^(s - m), rounded to bfloat16 pairs, into tensor memory; the row's sum
-      float sum = 0.f;
+      // P = 2^(s * scale * log2 e - m), rounded to bfloat16 pairs, into tensor memory; the row's sum
+      const float neg_m = -m_use;
+      float sums[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
       for (int c = 0; c < TC_KEYS; c += 32) {
         unsigned packed[16];
 #pragma unroll
-        for (int j = 0; j < 32; j += 2) {
-          const float p0 = exp2f(sv[c + j] - m_use), p1 = exp2f(sv[c + j + 1] - m_use);    // 2^(-inf) = 0
-          sum += p0 + p1;
-          __nv_bfloat162 pair = __floats2bfloat162_rn(p0, p1);
-          packed[j / 2] = *reinterpret_cast<unsigned*>(&pair);
+        for (int j = 0; j < 32; j += 4) {
+          const float p0 = exp2f(fmaf(sv[c + j], args.scale_log2, neg_m));          // 2^(-inf) = 0 for masked keys
+          const float p1 = exp2f(fmaf(sv[c + j + 1], args.scale_log2, neg_m));
+          const float p2 = exp2f(fmaf(sv[c + j + 2], args.scale_log2, neg_m));
+          const float p3 = exp2f(fmaf(sv[c + j + 3], args.scale_log2, neg_m));
+          sums[0] += p0; sums[1] += p1; sums[2] += p2; sums[3] += p3;
+          __nv_bfloat162 lo = __floats2bfloat162_rn(p0, p1), hi = __floats2bfloat162_rn(p2, p3);
+          packed[j / 2] = *reinterpret_cast<unsigned*>(&lo);
+          packed[j / 2 + 1] = *reinterpret_cast<unsigned*>(&hi);
         }
         tmem_store_16(lane_address + P_COL + c / 2, packed);
       }
+      const float sum = (sums[0] + sums[1]) + (sums[2] + sums[3]);
       tmem_store_wait();
       l_run += sum;
       tc_fence_before();
