@@ -15,6 +15,7 @@ SRB_DEFINE_LAST_ERROR()
 SRB_DEFINE_PDL_SWITCH()
 
 #define ROPE_WARPS 4
+#define ROPE_MAX_ROUNDS 3             // many rows: a block handles 12 head vectors of one row with one table of angles
 
 // The projection may arrive as `num_parts` float partial sums (a product cut along K),
 // `part_stride` elements apart, instead of one tensor of type T; they are added in part order.
@@ -26,15 +27,25 @@ __global__ void qk_norm_rope_kv_kernel(const T* __restrict__ qkv, const float* _
                                        const float* __restrict__ q_norm, const float* __restrict__ k_norm,
                                        float eps, const float* __restrict__ inv_freq, int rotary_dim,
                                        int interleaved, int n_q, int n_kv, int head_dim, int page_size,
-                                       int num_pages, int heads_to_do, int vector_ok, int* error_word) {
+                                       int num_pages, int heads_to_do, int vector_ok, int rounds, int* error_word) {
   extern __shared__ __align__(16) float staged_all[];  // ROPE_WARPS * head_dim floats
   srb_launch_dependents();
   srb_grid_dependency_wait();
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int row = blockIdx.x;
-  const int head = blockIdx.y * ROPE_WARPS + warp;     // q heads, then k heads, then v heads
-  if (head >= heads_to_do) return;
   float* staged = staged_all + warp * head_dim;
+  // cos and sin of the row's angles, once per block: every q and k head of the row turns by the same angles
+  float* cos_table = staged_all + ROPE_WARPS * head_dim;
+  float* sin_table = cos_table + (rotary_dim >> 1);
+  if (inv_freq) {
+    const float pos = (float)positions[row];
+    for (int i = threadIdx.x; i < (rotary_dim >> 1); i += blockDim.x) sincosf(pos * inv_freq[i], &sin_table[i], &cos_table[i]);
+  }
+  __syncthreads();
+#pragma unroll 1
+  for (int round = 0; round < rounds; ++round) {
+  const int head = (blockIdx.y * rounds + round) * ROPE_WARPS + warp;     // q heads, then k heads, then v heads
+  if (head >= heads_to_do) break;
   const size_t src_offset = (size_t)row * qkv_stride + (size_t)head * head_dim;
 
   const bool is_q = head < n_q;
@@ -86,13 +97,11 @@ __global__ void qk_norm_rope_kv_kernel(const T* __restrict__ qkv, const float* _
   }
   __syncwarp();
   if ((is_q || is_k) && inv_freq) {
-    const float pos = (float)positions[row];
     const int half = rotary_dim >> 1;
     for (int i = lane; i < half; i += 32) {
       const int ia = interleaved ? 2 * i : i;
       const int ib = interleaved ? 2 * i + 1 : i + half;
-      float sn, cs;
-      sincosf(pos * inv_freq[i], &sn, &cs);
+      const float sn = sin_table[i], cs = cos_table[i];
       const float a = staged[ia], b = staged[ib];
       staged[ia] = a * cs - b * sn;      // each element belongs to exactly one pair
       staged[ib] = b * cs + a * sn;
@@ -107,7 +116,8 @@ __global__ void qk_norm_rope_kv_kernel(const T* __restrict__ qkv, const float* _
     const int slot = slots[row];
     if (slot < 0 || slot >= num_pages * page_size) {
       if (lane == 0) atomicOr(error_word, SRB_FLAG_BAD_SLOT);
-      return;
+      __syncwarp();
+      continue;
     }
     const int kv_head = is_k ? head - n_q : head - n_q - n_kv;
     const size_t offset =
@@ -126,9 +136,11 @@ __global__ void qk_norm_rope_kv_kernel(const T* __restrict__ qkv, const float* _
         *reinterpret_cast<float4*>(dst + e) = x;
       }
     }
-    return;
+  } else {
+    for (int e = lane; e < head_dim; e += 32) dst[e] = srb_from_float<T>(staged[e]);
   }
-  for (int e = lane; e < head_dim; e += 32) dst[e] = srb_from_float<T>(staged[e]);
+  __syncwarp();                            // the staging row is reused by the warp's next head
+  }
 }
 
 // `slots` may be null: then only the q heads are processed (a layer that reads another
@@ -153,20 +165,23 @@ extern "C" int srb_qk_norm_rope_kv(const void* qkv, const float* qkv_parts, int 
   const int vector_ok = head_dim % 4 == 0 && qkv_stride % 4 == 0 && part_stride % 4 == 0 &&
                         (((uintptr_t)qkv_parts | (uintptr_t)qkv | (uintptr_t)q_out | (uintptr_t)k_pool |
                           (uintptr_t)v_pool) & 15) == 0;
-  dim3 grid(rows, (heads + ROPE_WARPS - 1) / ROPE_WARPS);
-  const size_t smem = (size_t)ROPE_WARPS * head_dim * sizeof(float);
+  // few rows (decode): one head per warp, so that the row is finished soonest; many rows: fewer tables of angles
+  const int rounds = rows >= 64 ? ROPE_MAX_ROUNDS : 1;
+  const int heads_per_block = ROPE_WARPS * rounds;
+  dim3 grid(rows, (heads + heads_per_block - 1) / heads_per_block);
+  const size_t smem = ((size_t)ROPE_WARPS * head_dim + (inv_freq ? rotary_dim : 0)) * sizeof(float);
   cudaStream_t s = (cudaStream_t)stream;
   if (dtype == SRB_DTYPE_F32)
     SRB_CUDA_CALL(srb_launch(qk_norm_rope_kv_kernel<float>, grid, dim3(ROPE_WARPS * 32), smem, s, (const float*)qkv,
                              qkv_parts, num_parts, (size_t)part_stride, qkv_stride, (float*)q_out, (float*)k_pool,
                              (float*)v_pool, positions, slots, q_norm, k_norm, eps, inv_freq, rotary_dim, interleaved,
-                             n_q, n_kv, head_dim, page_size, num_pages, heads, vector_ok, error_word));
+                             n_q, n_kv, head_dim, page_size, num_pages, heads, vector_ok, rounds, error_word));
   else if (dtype == SRB_DTYPE_BF16)
     SRB_CUDA_CALL(srb_launch(qk_norm_rope_kv_kernel<__nv_bfloat16>, grid, dim3(ROPE_WARPS * 32), smem, s,
                              (const __nv_bfloat16*)qkv, qkv_parts, num_parts, (size_t)part_stride, qkv_stride,
                              (__nv_bfloat16*)q_out, (__nv_bfloat16*)k_pool, (__nv_bfloat16*)v_pool, positions, slots,
                              q_norm, k_norm, eps, inv_freq, rotary_dim, interleaved, n_q, n_kv, head_dim, page_size,
-                             num_pages, heads, vector_ok, error_word));
+                             num_pages, heads, vector_ok, rounds, error_word));
   else
     SRB_FAIL("qk_norm_rope_kv: unknown dtype %d", dtype);
   SRB_LAUNCH_CHECK("qk_norm_rope_kv");
