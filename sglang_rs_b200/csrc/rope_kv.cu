@@ -6,7 +6,9 @@
 // the shared [head_dim] weight, rotate q and k, then store k and v at the row's slot.
 // Rotation (crates/sglang-kernel/src/rotary.rs:216-236): half-split pairs (i, i + rot/2) or
 // interleaved pairs (2i, 2i + 1); angle = float(pos) * inv_freq[i] in 32-bit; the table
-// inv_freq[i] = theta^(-2i/rot) is computed in 64-bit on the host (rotary.rs:76-80).
+// inv_freq[i] = theta^(-2i/rot) is computed in 64-bit on the host (rotary.rs:76-80).  Instead of
+// the table the caller may give the angle of every (row, pair) itself (`angles` [rows, rot/2]):
+// that covers every encoding of the rotary family without a change here.
 //
 // Page pool layout: [page, kv_head, slot_in_page, head_dim].
 #include "common.cuh"
@@ -25,7 +27,8 @@ __global__ void qk_norm_rope_kv_kernel(const T* __restrict__ qkv, const float* _
                                        T* __restrict__ k_pool, T* __restrict__ v_pool,
                                        const int* __restrict__ positions, const int* __restrict__ slots,
                                        const float* __restrict__ q_norm, const float* __restrict__ k_norm,
-                                       float eps, const float* __restrict__ inv_freq, int rotary_dim,
+                                       float eps, const float* __restrict__ inv_freq,
+                                       const float* __restrict__ angles, int rotary_dim,
                                        int interleaved, int n_q, int n_kv, int head_dim, int page_size,
                                        int num_pages, int heads_to_do, int vector_ok, int rounds, int* error_word) {
   extern __shared__ __align__(16) float staged_all[];  // ROPE_WARPS * head_dim floats
@@ -37,7 +40,11 @@ __global__ void qk_norm_rope_kv_kernel(const T* __restrict__ qkv, const float* _
   // cos and sin of the row's angles, once per block: every q and k head of the row turns by the same angles
   float* cos_table = staged_all + ROPE_WARPS * head_dim;
   float* sin_table = cos_table + (rotary_dim >> 1);
-  if (inv_freq) {
+  const bool rotate = inv_freq || angles;
+  if (angles) {            // the angles of every row and pair are given: any encoding of the rotary family
+    for (int i = threadIdx.x; i < (rotary_dim >> 1); i += blockDim.x)
+      sincosf(angles[(size_t)row * (rotary_dim >> 1) + i], &sin_table[i], &cos_table[i]);
+  } else if (inv_freq) {
     const float pos = (float)positions[row];
     for (int i = threadIdx.x; i < (rotary_dim >> 1); i += blockDim.x) sincosf(pos * inv_freq[i], &sin_table[i], &cos_table[i]);
   }
@@ -96,7 +103,7 @@ __global__ void qk_norm_rope_kv_kernel(const T* __restrict__ qkv, const float* _
     for (int e = lane; e < head_dim; e += 32) staged[e] = staged[e] * inv * norm_weight[e];
   }
   __syncwarp();
-  if ((is_q || is_k) && inv_freq) {
+  if ((is_q || is_k) && rotate) {
     const int half = rotary_dim >> 1;
     for (int i = lane; i < half; i += 32) {
       const int ia = interleaved ? 2 * i : i;
@@ -148,13 +155,14 @@ __global__ void qk_norm_rope_kv_kernel(const T* __restrict__ qkv, const float* _
 extern "C" int srb_qk_norm_rope_kv(const void* qkv, const float* qkv_parts, int num_parts, long long part_stride,
                                    int qkv_stride, void* q_out, void* k_pool, void* v_pool,
                                    const int* positions, const int* slots, const float* q_norm,
-                                   const float* k_norm, float eps, const float* inv_freq, int rotary_dim,
+                                   const float* k_norm, float eps, const float* inv_freq, const float* angles,
+                                   int rotary_dim,
                                    int interleaved, int rows, int n_q, int n_kv, int head_dim, int page_size,
                                    int num_pages, int* error_word, int dtype, void* stream) {
   if (rows <= 0) return SRB_OK;
   if (n_q <= 0 || n_kv <= 0 || head_dim <= 0 || page_size <= 0)
     SRB_FAIL("qk_norm_rope_kv: head counts, head_dim and page size must be positive");
-  if (inv_freq && (rotary_dim <= 0 || rotary_dim > head_dim || (rotary_dim & 1)))
+  if ((inv_freq || angles) && (rotary_dim <= 0 || rotary_dim > head_dim || (rotary_dim & 1)))
     SRB_FAIL("qk_norm_rope_kv: rotary width %d must be even, positive and at most head_dim %d", rotary_dim,
              head_dim);
   if (head_dim > 2048) SRB_FAIL("qk_norm_rope_kv: head_dim %d exceeds 2048", head_dim);
@@ -169,19 +177,19 @@ extern "C" int srb_qk_norm_rope_kv(const void* qkv, const float* qkv_parts, int 
   const int rounds = rows >= 64 ? ROPE_MAX_ROUNDS : 1;
   const int heads_per_block = ROPE_WARPS * rounds;
   dim3 grid(rows, (heads + heads_per_block - 1) / heads_per_block);
-  const size_t smem = ((size_t)ROPE_WARPS * head_dim + (inv_freq ? rotary_dim : 0)) * sizeof(float);
+  const size_t smem = ((size_t)ROPE_WARPS * head_dim + ((inv_freq || angles) ? rotary_dim : 0)) * sizeof(float);
   cudaStream_t s = (cudaStream_t)stream;
   if (dtype == SRB_DTYPE_F32)
     SRB_CUDA_CALL(srb_launch(qk_norm_rope_kv_kernel<float>, grid, dim3(ROPE_WARPS * 32), smem, s, (const float*)qkv,
                              qkv_parts, num_parts, (size_t)part_stride, qkv_stride, (float*)q_out, (float*)k_pool,
-                             (float*)v_pool, positions, slots, q_norm, k_norm, eps, inv_freq, rotary_dim, interleaved,
-                             n_q, n_kv, head_dim, page_size, num_pages, heads, vector_ok, rounds, error_word));
+                             (float*)v_pool, positions, slots, q_norm, k_norm, eps, inv_freq, angles, rotary_dim,
+                             interleaved, n_q, n_kv, head_dim, page_size, num_pages, heads, vector_ok, rounds, error_word));
   else if (dtype == SRB_DTYPE_BF16)
     SRB_CUDA_CALL(srb_launch(qk_norm_rope_kv_kernel<__nv_bfloat16>, grid, dim3(ROPE_WARPS * 32), smem, s,
                              (const __nv_bfloat16*)qkv, qkv_parts, num_parts, (size_t)part_stride, qkv_stride,
                              (__nv_bfloat16*)q_out, (__nv_bfloat16*)k_pool, (__nv_bfloat16*)v_pool, positions, slots,
-                             q_norm, k_norm, eps, inv_freq, rotary_dim, interleaved, n_q, n_kv, head_dim, page_size,
-                             num_pages, heads, vector_ok, rounds, error_word));
+                             q_norm, k_norm, eps, inv_freq, angles, rotary_dim, interleaved, n_q, n_kv, head_dim,
+                             page_size, num_pages, heads, vector_ok, rounds, error_word));
   else
     SRB_FAIL("qk_norm_rope_kv: unknown dtype %d", dtype);
   SRB_LAUNCH_CHECK("qk_norm_rope_kv");

@@ -169,14 +169,20 @@ def qk_norm_rope_kv(qkv: torch.Tensor, q_out: torch.Tensor, k_pool: Optional[tor
                     v_pool: Optional[torch.Tensor], positions: torch.Tensor, slots: Optional[torch.Tensor],
                     q_norm: Optional[torch.Tensor], k_norm: Optional[torch.Tensor], eps: float,
                     inv_freq: Optional[torch.Tensor], rotary_dim: int, interleaved: bool, n_q: int, n_kv: int,
-                    head_dim: int, error_word: torch.Tensor) -> None:
+                    head_dim: int, error_word: torch.Tensor, angles: Optional[torch.Tensor] = None) -> None:
     """Per-head norm of q and k, rotation of q and k, q to ``q_out``, k and v into the pages.
 
     ``qkv`` is [rows, >= (n_q + 2 n_kv) head_dim] with q heads, k heads, v heads in that order,
     of ``q_out``'s dtype, or float32 [parts, rows, width] partial sums that are added in order;
     pools are [pages, n_kv, page_size, head_dim]; ``slots[r]`` = page * page_size + offset.
-    With ``slots`` None nothing is written to the pages."""
+    With ``slots`` None nothing is written to the pages.  The rotation takes its angles as
+    ``positions[r] * inv_freq[i]`` or, if ``angles`` (float32 [rows, rotary_dim / 2]) is given,
+    from there."""
     _need(qkv, "qkv"); _need(q_out, "q_out"); _need(positions, "positions", torch.int32)
+    if angles is not None:
+        _need(angles, "angles", torch.float32)
+        if angles.shape != (qkv.shape[-2], rotary_dim // 2):
+            raise KernelError("qk_norm_rope_kv: angles must be [rows, rotary_dim / 2]")
     whole = parts = None
     num_parts = part_stride = 0
     if qkv.dim() == 3:
@@ -207,7 +213,7 @@ def qk_norm_rope_kv(qkv: torch.Tensor, q_out: torch.Tensor, k_pool: Optional[tor
     _check(lib, lib.srb_qk_norm_rope_kv(
         _ptr(whole), _ptr(parts), num_parts, ctypes.c_longlong(part_stride), qkv.stride(-2), _ptr(q_out), _ptr(k_pool),
         _ptr(v_pool), _ptr(positions), _ptr(slots), _ptr(q_norm), _ptr(k_norm), ctypes.c_float(eps), _ptr(inv_freq),
-        rotary_dim, int(interleaved), rows, n_q, n_kv, head_dim, page_size, num_pages, _ptr(error_word),
+        _ptr(angles), rotary_dim, int(interleaved), rows, n_q, n_kv, head_dim, page_size, num_pages, _ptr(error_word),
         dtype_code(q_out.dtype), _stream()))
 
 

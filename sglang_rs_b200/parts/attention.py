@@ -99,7 +99,8 @@ class GroupedQueryAttention(Mixer):
             ctx.positions, batch.slots if cache.writable else None, self.q_norm, self.k_norm,
             self.qk_norm_eps if self.qk_norm_eps is not None else 0.0,
             rotary.inv_freq if rotary else None, rotary.rotary_dim if rotary else 0,
-            rotary.interleaved if rotary else False, self.n_q, self.n_kv, self.d, ctx.error_word)
+            rotary.interleaved if rotary else False, self.n_q, self.n_kv, self.d, ctx.error_word,
+            angles=rotary.angles(ctx.positions) if rotary is not None and rotary.angles is not None else None)
         out = torch.empty_like(q)
         for launch in batch.launches:
             b, e = launch.begin, launch.end

@@ -10,8 +10,9 @@ What each kind must offer:
 * every part: ``tensor_specs()`` (checkpoint name -> :class:`TensorSpec`) and
   ``load(tensors, device, dtype)``;
 * :class:`Norm`: ``add_norm(residual, delta, out_dtype, row_index=None)``;
-* :class:`PositionEncoding`: either ``fused_rotary()`` (parameters the fused q/k kernel
-  applies) or ``apply(q, k, positions)`` (its own kernels), chosen by ``fused``;
+* :class:`PositionEncoding`: ``fused_rotary()``: what the fused q/k kernel rotates with: a
+  frequency table, or a function from the step's positions to the angle of every (row, pair),
+  which covers any encoding of the rotary family; None leaves q and k alone;
 * :class:`Mixer`: ``cache_need()`` and ``forward(ctx, cache, x) -> y``;
 * :class:`FeedForward`: ``forward(ctx, x) -> y``;
 * a block: ``forward(ctx, cache, residual, delta) -> (residual, delta)`` where the hidden

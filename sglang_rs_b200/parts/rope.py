@@ -10,7 +10,7 @@ kernel.
 from __future__ import annotations
 
 from dataclasses import dataclass
-from typing import Optional
+from typing import Callable, Optional
 
 import torch
 
@@ -19,9 +19,13 @@ from .base import PositionEncoding
 
 @dataclass(frozen=True)
 class FusedRotary:
-    inv_freq: torch.Tensor
+    """What the fused q/k kernel needs to rotate: either a table ``inv_freq`` (angle = position *
+    inv_freq[i]) or ``angles(positions) -> float32 [rows, rotary_dim / 2]`` for encodings whose angles
+    are not a product of position and frequency."""
+    inv_freq: Optional[torch.Tensor]
     rotary_dim: int
     interleaved: bool
+    angles: Optional[Callable[[torch.Tensor], torch.Tensor]] = None
 
 
 class RotaryEncoding(PositionEncoding):

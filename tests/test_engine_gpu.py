@@ -490,3 +490,157 @@ def test_captured_steps_with_window_groups(tmp_path, dtype_name, stored, toleran
         assert set(session.cache.allocators) == {("kv", None), ("kv", 11), ("kv", 17)}
     finally:
         unregister_architecture("ToyHybridForTests")
+
+
+# ------------------------------------------------------------------------------ more parts defined here
+TOY2 = {"architectures": ["ToyPartsForTests"], "hidden": 64, "vocab": 120, "heads": 4, "kv_heads": 4, "head_dim": 16,
+        "inner": 48, "eps": 1e-6, "experts": 3, "top_k": 2, "max_positions": 300}
+
+
+def register_toy_parts():
+    """A position encoding whose angles are not position * frequency, and a feed-forward with
+    routing, both defined here and used through the framework's interfaces."""
+    from sglang_rs_b200 import ops
+    from sglang_rs_b200.config import register_architecture
+    from sglang_rs_b200.models import DecoderModel
+    from sglang_rs_b200.parts import (AttentionNames, FeedForward, GatedMlp, GatedMlpNames, GroupedQueryAttention,
+                                      OutputHead, PositionEncoding, PreNormBlock, RmsNorm, TensorSpec, TokenEmbedding,
+                                      scale_to)
+    from sglang_rs_b200.parts.rope import FusedRotary
+
+    class LogRotary(PositionEncoding):
+        """angle(pos, i) = log(1 + pos) * rate[i] + phase[i]; rate and phase are checkpoint tensors."""
+        fused = True
+        graph_safe = True
+
+        def __init__(self, head_dim, prefix):
+            self.head_dim, self.prefix = head_dim, prefix
+
+        def tensor_specs(self):
+            return {f"{self.prefix}.rate": TensorSpec((self.head_dim // 2,), "scale"),
+                    f"{self.prefix}.phase": TensorSpec((self.head_dim // 2,), "normal")}
+
+        def load(self, tensors, device, dtype):
+            self.rate = scale_to(tensors[f"{self.prefix}.rate"], device)
+            self.phase = scale_to(tensors[f"{self.prefix}.phase"], device)
+
+        def fused_rotary(self):
+            return FusedRotary(None, self.head_dim, False,
+                               angles=lambda positions: (torch.log1p(positions.float())[:, None] * self.rate[None, :]
+                                                         + self.phase[None, :]).contiguous())
+
+    class RoutedMlp(FeedForward):
+        """Router logits in 32-bit, top-k experts, weights = softmax over the chosen logits."""
+
+        def __init__(self, hidden, inner, experts, top_k, prefix):
+            self.hidden, self.top_k, self.prefix = hidden, top_k, prefix
+            self.experts = [GatedMlp(hidden, inner, "silu", GatedMlpNames(f"{prefix}.e{e}.gate", f"{prefix}.e{e}.up",
+                                                                         f"{prefix}.e{e}.down")) for e in range(experts)]
+
+        def tensor_specs(self):
+            specs = {f"{self.prefix}.router": TensorSpec((len(self.experts), self.hidden))}
+            for expert in self.experts:
+                specs.update(expert.tensor_specs())
+            return specs
+
+        def load(self, tensors, device, dtype):
+            self.router = scale_to(tensors[f"{self.prefix}.router"], device) * 50.0     # clear-cut choices
+            for expert in self.experts:
+                expert.load(tensors, device, dtype)
+
+        def forward(self, ctx, x):
+            logits = x.float() @ self.router.t()
+            top, chosen = torch.topk(logits, self.top_k, dim=-1)
+            weights = torch.softmax(top, dim=-1)
+            out = torch.zeros(x.shape, dtype=torch.float32, device=x.device)
+            for e, expert in enumerate(self.experts):
+                rows, slot = torch.nonzero(chosen == e, as_tuple=True)
+                if rows.numel():
+                    y = expert.forward(ctx, x[rows].contiguous())
+                    y = y.sum(0) if y.dim() == 3 else y
+                    out.index_add_(0, rows, y.float() * weights[rows, slot][:, None])
+            return out.to(x.dtype)
+
+    def build(cfg):
+        h, d = cfg["hidden"], cfg["head_dim"]
+        layers = []
+        for i in range(2):
+            p = f"layers.{i}"
+            mixer = GroupedQueryAttention(h, cfg["heads"], cfg["kv_heads"], d, 1 / math.sqrt(d), LogRotary(d, f"{p}.pos"),
+                                          AttentionNames(f"{p}.q", f"{p}.k", f"{p}.v", f"{p}.o", f"{p}.qn", f"{p}.kn"),
+                                          qk_norm_eps=cfg["eps"])
+            ffn = RoutedMlp(h, cfg["inner"], cfg["experts"], cfg["top_k"], f"{p}.moe") if cfg["experts"] else \
+                GatedMlp(h, cfg["inner"], "silu", GatedMlpNames(f"{p}.gate", f"{p}.up", f"{p}.down"))
+            layers.append(PreNormBlock(RmsNorm(h, cfg["eps"], f"{p}.n1"), mixer, RmsNorm(h, cfg["eps"], f"{p}.n2"), ffn))
+        embedding = TokenEmbedding(cfg["vocab"], h, "embed")
+        return DecoderModel(embedding, layers, RmsNorm(h, cfg["eps"], "norm"), OutputHead(cfg["vocab"], h, None, embedding),
+                            vocab_size=cfg["vocab"], max_positions=cfg["max_positions"])
+
+    register_architecture("ToyPartsForTests", lambda raw: dict(raw.document), build, replace=True)
+
+
+def plain_toy_parts_forward(cfg, weights, tokens):
+    w = {k: v.double() for k, v in weights.items()}
+    n_q, d, eps = cfg["heads"], cfg["head_dim"], cfg["eps"]
+    pos = torch.arange(len(tokens))
+    h = w["embed"][torch.tensor(tokens)]
+
+    def rotate(x, p):
+        angle = (torch.log1p(pos.float())[:, None] * w[f"{p}.pos.rate"].float()[None, :]
+                 + w[f"{p}.pos.phase"].float()[None, :]).double()      # the engine forms the angle in 32-bit
+        cos, sin = torch.cos(angle)[:, None, :], torch.sin(angle)[:, None, :]
+        a, b = x[..., :d // 2], x[..., d // 2:]
+        return torch.cat([a * cos - b * sin, b * cos + a * sin], dim=-1)
+
+    def gated(x, gate, up, down):
+        return pm.plain_linear(pm.plain_silu_mul(pm.plain_linear(x, w[gate]), pm.plain_linear(x, w[up])), w[down])
+
+    for i in range(2):
+        p = f"layers.{i}"
+        n = pm.plain_rms_norm(h, w[f"{p}.n1"], eps)
+        q = rotate(pm.plain_rms_norm(pm.plain_linear(n, w[f"{p}.q"]).view(-1, n_q, d), w[f"{p}.qn"], eps), p)
+        k = rotate(pm.plain_rms_norm(pm.plain_linear(n, w[f"{p}.k"]).view(-1, n_q, d), w[f"{p}.kn"], eps), p)
+        v = pm.plain_linear(n, w[f"{p}.v"]).view(-1, n_q, d)
+        a = pm.plain_attention(q, k, v, 1 / math.sqrt(d))
+        h = h + pm.plain_linear(a.reshape(len(tokens), -1), w[f"{p}.o"])
+        n = pm.plain_rms_norm(h, w[f"{p}.n2"], eps)
+        if cfg["experts"]:
+            logits = n @ (w[f"{p}.moe.router"] * 50.0).t()
+            top, chosen = torch.topk(logits, cfg["top_k"], dim=-1)
+            weights_ = torch.softmax(top, dim=-1)
+            out = torch.zeros_like(n)
+            for t in range(len(tokens)):
+                for j in range(cfg["top_k"]):
+                    e = int(chosen[t, j])
+                    out[t] += weights_[t, j] * gated(n[t:t + 1], f"{p}.moe.e{e}.gate", f"{p}.moe.e{e}.up", f"{p}.moe.e{e}.down")[0]
+            h = h + out
+        else:
+            h = h + gated(n, f"{p}.gate", f"{p}.up", f"{p}.down")
+    return pm.plain_linear(pm.plain_rms_norm(h, w["norm"], eps), w["embed"])
+
+
+@pytest.mark.parametrize("experts,dtype_name,stored,tolerance", [
+    (0, "float32", torch.float32, rh.FP32_TOLERANCE), (0, "bfloat16", torch.bfloat16, rh.BF16_TOLERANCE),
+    (3, "float32", torch.float32, rh.FP32_TOLERANCE)])
+def test_another_position_encoding_and_a_routed_feed_forward(tmp_path, experts, dtype_name, stored, tolerance):
+    """Parts defined in this file: a rotary encoding with logarithmic angles and tensors of its
+    own (it hands the fused kernel an angle per row and pair), and a feed-forward that routes each
+    row to 2 of 3 experts (32-bit router; tested in 32-bit, where a close call cannot fall the
+    other way).  Decoded steps of the first run from CUDA graphs."""
+    from sglang_rs_b200.config import unregister_architecture
+    from sglang_rs_b200.weights import read_model_dir, write_model_folder
+    toy = dict(TOY2, experts=experts)
+    register_toy_parts()
+    try:
+        folder = write_model_folder(str(tmp_path / "parts"), toy, seed=3, dtype=stored)
+        weights = {k: v.float() for k, v in read_model_dir(folder).items()}
+        requests = rh.random_requests({"vocab_size": toy["vocab"]}, (70, 33, 150, 9), seed=2)
+        expected = {rid: plain_toy_parts_forward(toy, weights, toks).numpy() for rid, toks in requests.items()}
+        for trace in (rh.trace_whole(requests), rh.trace_tail_by_one(requests), rh.trace_mixed(requests, seed=6)):
+            rows, session = rh.run_in_process(folder, dtype_name, trace)
+            bad = rh.first_bad(rows, expected, tolerance)
+            print("toy parts:", rh.worst_error(rows, expected))
+            assert bad is None, bad
+        assert (session.runner.graphs is not None) == (experts == 0)
+    finally:
+        unregister_architecture("ToyPartsForTests")

@@ -182,6 +182,43 @@ def test_qk_norm_rope_kv(dtype, n_q, n_kv, d, rot, inter):
         ops.raise_on_error_word(word)
 
 
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("rows,n_q,n_kv,d,rot", [(5, 3, 1, 32, 32), (150, 6, 2, 64, 48)])
+def test_rope_from_a_table_of_angles(dtype, rows, n_q, n_kv, d, rot):
+    """The kernel may be given an angle per (row, pair) instead of frequencies: another
+    position encoding needs no kernel of its own.  Few rows and many rows take different
+    ways through the kernel."""
+    g = torch.Generator().manual_seed(rows + d)
+    page = 8
+    pages = -(-rows // page) + 1
+    qkv = torch.randn(rows, (n_q + 2 * n_kv) * d, generator=g)
+    qn, kn = 1 + 0.1 * torch.randn(d, generator=g), 1 + 0.1 * torch.randn(d, generator=g)
+    angles = (torch.rand(rows, rot // 2, generator=g) * 12 - 6).float()
+    slots = torch.randperm(pages * page, generator=g)[:rows].to(torch.int32)
+    positions = torch.arange(rows, dtype=torch.int32)
+    k_pool = torch.zeros(pages, n_kv, page, d, device=DEV, dtype=dtype)
+    v_pool = torch.zeros_like(k_pool)
+    q_out = torch.empty(rows, n_q, d, device=DEV, dtype=dtype)
+    word = ops.new_error_word(DEV)
+    ops.qk_norm_rope_kv(qkv.to(DEV, dtype), q_out, k_pool, v_pool, positions.to(DEV), slots.to(DEV), qn.to(DEV),
+                        kn.to(DEV), 1e-6, None, rot, False, n_q, n_kv, d, word, angles=angles.to(DEV))
+    ops.raise_on_error_word(word)
+    seen = rounded(qkv, dtype)
+    cos, sin = torch.cos(angles.double())[:, None, :], torch.sin(angles.double())[:, None, :]
+
+    def rotate(x):
+        out = x.clone()
+        a, b = x[..., :rot // 2], x[..., rot // 2:rot]
+        out[..., :rot // 2], out[..., rot // 2:rot] = a * cos - b * sin, b * cos + a * sin
+        return out
+
+    q = rotate(pm.plain_rms_norm(seen[:, :n_q * d].view(rows, n_q, d), qn.double(), 1e-6))
+    k = rotate(pm.plain_rms_norm(seen[:, n_q * d:(n_q + n_kv) * d].view(rows, n_kv, d), kn.double(), 1e-6))
+    close(q_out, q, dtype, "q from angles")
+    got_k = k_pool.cpu()[slots.long() // page, :, slots.long() % page]
+    close(got_k, k, dtype, "k from angles")
+
+
 def paged_case(dtype, n_q, n_kv, d, page, lengths, rows_per_request, window, seed, boost=None):
     """Requests with their keys scattered over shuffled pages; the last ``rows`` positions of
     each request are the step's rows."""
