@@ -100,70 +100,80 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constan
 
   srb_launch_dependents();
   if (warp == 0) {
-    if (lane == 0) {
-      int issued = 0;
-      // The weights are written by no kernel of the step, so the first stages of W are
-      // requested before the wait for the kernels ahead; X follows once they have completed.
-      const int early = min(num_kb, STAGES);
-      bool ok = true;
-      for (int i = 0; i < early && ok; ++i) {
-        ok = mbar_wait(smem_u32(&empty_bar[i]), 1u, &abort_flag);      // first use of a stage: free
-        if (!ok) break;
-        const unsigned bar = smem_u32(&full_bar[i]);
-        unsigned char* stage = smem + (size_t)i * STAGE_BYTES;
+    // Copies, by the whole warp with one elected lane issuing: addresses and coordinates stay in
+    // uniform registers, which the copy instruction takes its operands from.
+    int issued = 0;
+    // The weights are written by no kernel of the step, so the first stages of W are
+    // requested before the wait for the kernels ahead; X follows once they have completed.
+    const int early = min(num_kb, STAGES);
+    const unsigned smem_base = smem_u32(smem);
+    bool ok = true;
+    for (int i = 0; i < early && ok; ++i) {
+      ok = mbar_wait_warp(smem_u32(&empty_bar[i]), 1u, &abort_flag);      // first use of a stage: free
+      if (!ok) break;
+      const unsigned bar = smem_u32(&full_bar[i]);
+      const unsigned stage = smem_base + i * STAGE_BYTES;
+      const int kx = (kb_begin + i) * GEMM_BLOCK_K;
+      if (elect_one()) {
         mbar_expect_tx(bar, STAGE_BYTES);
-        const int kx = (kb_begin + i) * GEMM_BLOCK_K;
-        tma_load_2d(smem_u32(stage), &map_w, bar, kx, feature0);
-        if (EPI == EPI_SILU) tma_load_2d(smem_u32(stage + A_BYTES / 2), &map_w, bar, kx, args.up_row_offset + feature0);
-        issued = i + 1;
+        tma_load_2d(stage, &map_w, bar, kx, feature0);
+        if (EPI == EPI_SILU) tma_load_2d(stage + A_BYTES / 2, &map_w, bar, kx, args.up_row_offset + feature0);
       }
-      srb_grid_dependency_wait();
-      for (int i = 0; i < issued; ++i) {
-        unsigned char* stage = smem + (size_t)i * STAGE_BYTES;
-        tma_load_2d(smem_u32(stage + A_BYTES), &map_x, smem_u32(&full_bar[i]), (kb_begin + i) * GEMM_BLOCK_K, token0);
-      }
-      for (int i = issued; i < num_kb && ok; ++i) {
-        const int s = i % STAGES;
-        const unsigned phase = (unsigned)(i / STAGES) & 1u;
-        if (!mbar_wait(smem_u32(&empty_bar[s]), phase ^ 1u, &abort_flag)) break;
-        const unsigned bar = smem_u32(&full_bar[s]);
-        unsigned char* stage = smem + (size_t)s * STAGE_BYTES;
+      issued = i + 1;
+    }
+    srb_grid_dependency_wait();
+    for (int i = 0; i < issued; ++i) {
+      if (elect_one())
+        tma_load_2d(smem_base + i * STAGE_BYTES + A_BYTES, &map_x, smem_u32(&full_bar[i]), (kb_begin + i) * GEMM_BLOCK_K,
+                    token0);
+    }
+    for (int i = issued; i < num_kb && ok; ++i) {
+      const int s = i % STAGES;
+      const unsigned phase = (unsigned)(i / STAGES) & 1u;
+      if (!mbar_wait_warp(smem_u32(&empty_bar[s]), phase ^ 1u, &abort_flag)) break;
+      const unsigned bar = smem_u32(&full_bar[s]);
+      const unsigned stage = smem_base + s * STAGE_BYTES;
+      const int kx = (kb_begin + i) * GEMM_BLOCK_K;
+      if (elect_one()) {
         mbar_expect_tx(bar, STAGE_BYTES);
-        const int kx = (kb_begin + i) * GEMM_BLOCK_K;
-        tma_load_2d(smem_u32(stage), &map_w, bar, kx, feature0);
-        if (EPI == EPI_SILU) tma_load_2d(smem_u32(stage + A_BYTES / 2), &map_w, bar, kx, args.up_row_offset + feature0);
-        tma_load_2d(smem_u32(stage + A_BYTES), &map_x, bar, kx, token0);
-        issued = i + 1;
+        tma_load_2d(stage, &map_w, bar, kx, feature0);
+        if (EPI == EPI_SILU) tma_load_2d(stage + A_BYTES / 2, &map_w, bar, kx, args.up_row_offset + feature0);
+        tma_load_2d(stage + A_BYTES, &map_x, bar, kx, token0);
       }
-      // copies still in flight write into this block's shared memory: wait for them before leaving
-      if (abort_flag) {
-        for (int i = max(0, issued - STAGES); i < issued; ++i)
-          mbar_wait_timed(smem_u32(&full_bar[i % STAGES]), (unsigned)(i / STAGES) & 1u);
-      }
+      issued = i + 1;
+    }
+    // copies still in flight write into this block's shared memory: wait for them before leaving
+    __syncwarp();
+    if (lane == 0 && abort_flag) {
+      for (int i = max(0, issued - STAGES); i < issued; ++i)
+        mbar_wait_timed(smem_u32(&full_bar[i % STAGES]), (unsigned)(i / STAGES) & 1u);
     }
   } else if (warp == 1) {
-    if (lane == 0) {
-      constexpr unsigned idesc = instruction_descriptor(BLOCK_T);
-      bool ok = true;
-      for (int i = 0; i < num_kb && ok; ++i) {
-        const int s = i % STAGES;
-        const unsigned phase = (unsigned)(i / STAGES) & 1u;
-        ok = mbar_wait(smem_u32(&full_bar[s]), phase, &abort_flag);
-        if (!ok) break;
-        tc_fence_after();
-        const unsigned stage = smem_u32(smem + (size_t)s * STAGE_BYTES);
-        const unsigned long long a_desc = smem_descriptor(stage);
-        const unsigned long long b_desc = smem_descriptor(stage + A_BYTES);
+    // Products, by the whole warp with one elected lane issuing.
+    constexpr unsigned idesc = instruction_descriptor(BLOCK_T);
+    const unsigned long long a_desc0 = smem_descriptor(smem_u32(smem));
+    const unsigned long long b_desc0 = smem_descriptor(smem_u32(smem) + A_BYTES);
+    bool ok = true;
+    for (int i = 0; i < num_kb && ok; ++i) {
+      const int s = i % STAGES;
+      const unsigned phase = (unsigned)(i / STAGES) & 1u;
+      ok = mbar_wait_warp(smem_u32(&full_bar[s]), phase, &abort_flag);
+      if (!ok) break;
+      tc_fence_after();
+      const unsigned long long stage_step = (unsigned long long)((s * STAGE_BYTES) >> 4);
+      if (elect_one()) {
 #pragma unroll
         for (int k = 0; k < GEMM_BLOCK_K / GEMM_UMMA_K; ++k) {
           const unsigned accumulate = (i > 0 || k > 0) ? 1u : 0u;
-          const unsigned long long step = (unsigned long long)((k * GEMM_UMMA_K * 2) >> 4);
-          umma_bf16(tmem_base, a_desc + step, b_desc + step, idesc, accumulate);
+          const unsigned long long step = stage_step + (unsigned long long)((k * GEMM_UMMA_K * 2) >> 4);
+          umma_bf16(tmem_base, a_desc0 + step, b_desc0 + step, idesc, accumulate);
         }
         umma_commit(smem_u32(&empty_bar[s]));        // frees the stage when these products have read it
       }
-      if (ok) umma_commit(smem_u32(&acc_bar));       // the accumulator is complete
+      __syncwarp();
     }
+    if (ok && elect_one()) umma_commit(smem_u32(&acc_bar));       // the accumulator is complete
+    __syncwarp();
   } else {
     // epilogue: warp w may read TMEM lanes 32 * (w % 4) .. + 32
     srb_grid_dependency_wait();             // the output buffer may still be read by a kernel ahead

@@ -170,3 +170,18 @@ __device__ __forceinline__ void tmem_store_16(unsigned address, const unsigned (
       : "memory");
 }
 __device__ __forceinline__ void tmem_store_wait() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
+
+// ---- issue by one elected lane of a converged warp ---------------------------------------
+// The copy and product instructions take their operands from uniform registers.  A warp that
+// runs its loop converged and lets one elected lane issue keeps addresses and descriptors in
+// uniform registers; a loop inside `if (lane == 0)` moves every operand there again for every
+// instruction, which costs about 60 cycles per instruction.
+__device__ __forceinline__ bool elect_one() {
+  unsigned chosen;
+  asm volatile("{\n.reg .pred p;\nelect.sync _|p, 0xffffffff;\nselp.u32 %0, 1, 0, p;\n}\n" : "=r"(chosen));
+  return chosen != 0;
+}
+// Bounded wait by every lane of a converged warp; the same answer in every lane.
+__device__ __forceinline__ bool mbar_wait_warp(unsigned bar, unsigned parity, volatile int* abort_flag) {
+  return __all_sync(0xffffffffu, mbar_wait(bar, parity, abort_flag));
+}
