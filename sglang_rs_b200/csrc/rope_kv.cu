@@ -19,6 +19,20 @@ SRB_DEFINE_PDL_SWITCH()
 #define ROPE_WARPS 4
 #define ROPE_MAX_ROUNDS 3             // many rows: a block handles 12 head vectors of one row with one table of angles
 
+
+// The arithmetic that both kernels below share, written with explicit roundings so that a value
+// does not depend on which kernel computed it.
+__device__ __forceinline__ float sum_squares4(float4 x) {
+  return __fmaf_rn(x.w, x.w, __fmaf_rn(x.z, x.z, __fmaf_rn(x.y, x.y, __fmul_rn(x.x, x.x))));
+}
+__device__ __forceinline__ float rotate_first(float a, float b, float cs, float sn) {    // a cos - b sin
+  return __fmaf_rn(a, cs, -__fmul_rn(b, sn));
+}
+__device__ __forceinline__ float rotate_second(float a, float b, float cs, float sn) {   // b cos + a sin
+  return __fmaf_rn(b, cs, __fmul_rn(a, sn));
+}
+__device__ __forceinline__ float normed(float x, float inv, float w) { return __fmul_rn(__fmul_rn(x, inv), w); }
+
 // The projection may arrive as `num_parts` float partial sums (a product cut along K),
 // `part_stride` elements apart, instead of one tensor of type T; they are added in part order.
 template <typename T>
@@ -69,7 +83,7 @@ __global__ void qk_norm_rope_kv_kernel(const T* __restrict__ qkv, const float* _
         x.x += d.x; x.y += d.y; x.z += d.z; x.w += d.w;
       }
       *reinterpret_cast<float4*>(staged + e) = x;
-      partial += x.x * x.x + x.y * x.y + x.z * x.z + x.w * x.w;
+      partial += sum_squares4(x);
     }
   } else if (vector_ok) {
     for (int e = lane * 4; e < head_dim; e += 128) {
@@ -83,7 +97,7 @@ __global__ void qk_norm_rope_kv_kernel(const T* __restrict__ qkv, const float* _
         x = *reinterpret_cast<const float4*>(qkv + src_offset + e);
       }
       *reinterpret_cast<float4*>(staged + e) = x;
-      partial += x.x * x.x + x.y * x.y + x.z * x.z + x.w * x.w;
+      partial += sum_squares4(x);
     }
   } else {
     for (int e = lane; e < head_dim; e += 32) {
@@ -99,8 +113,8 @@ __global__ void qk_norm_rope_kv_kernel(const T* __restrict__ qkv, const float* _
   }
   if (norm_weight) {
     const float total = srb_warp_sum(partial);
-    const float inv = 1.0f / sqrtf(total / (float)head_dim + eps);
-    for (int e = lane; e < head_dim; e += 32) staged[e] = staged[e] * inv * norm_weight[e];
+    const float inv = __frsqrt_rn(total / (float)head_dim + eps);
+    for (int e = lane; e < head_dim; e += 32) staged[e] = normed(staged[e], inv, norm_weight[e]);
   }
   __syncwarp();
   if ((is_q || is_k) && rotate) {
@@ -110,8 +124,8 @@ __global__ void qk_norm_rope_kv_kernel(const T* __restrict__ qkv, const float* _
       const int ib = interleaved ? 2 * i + 1 : i + half;
       const float sn = sin_table[i], cs = cos_table[i];
       const float a = staged[ia], b = staged[ib];
-      staged[ia] = a * cs - b * sn;      // each element belongs to exactly one pair
-      staged[ib] = b * cs + a * sn;
+      staged[ia] = rotate_first(a, b, cs, sn);      // each element belongs to exactly one pair
+      staged[ib] = rotate_second(a, b, cs, sn);
     }
   }
   __syncwarp();
@@ -150,6 +164,118 @@ __global__ void qk_norm_rope_kv_kernel(const T* __restrict__ qkv, const float* _
   }
 }
 
+
+// Many rows, head_dim 128, rotation of the whole head in half-split pairs: one block per row, every
+// warp takes several heads of the row and keeps a head in registers (lane l holds elements 4l..4l+3,
+// its rotation partner sits in lane l ^ 16), so a head costs one load, two shuffles' worth of
+// exchange and one store.  Same arithmetic as the kernel above.
+#define ROW_WARPS 8
+template <typename T>
+__global__ void __launch_bounds__(ROW_WARPS * 32)
+qk_norm_rope_kv_row_kernel(const T* __restrict__ qkv, const float* __restrict__ qkv_parts, int num_parts,
+                           size_t part_stride, int qkv_stride, T* __restrict__ q_out, T* __restrict__ k_pool,
+                           T* __restrict__ v_pool, const int* __restrict__ positions, const int* __restrict__ slots,
+                           const float* __restrict__ q_norm, const float* __restrict__ k_norm, float eps,
+                           const float* __restrict__ inv_freq, const float* __restrict__ angles, int n_q, int n_kv,
+                           int page_size, int num_pages, int heads_to_do, int* error_word) {
+  constexpr int D = 128, HALF = 64;
+  __shared__ __align__(16) float cos_table[HALF], sin_table[HALF];
+  srb_launch_dependents();
+  srb_grid_dependency_wait();
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int row = blockIdx.x;
+  const bool rotate = inv_freq || angles;
+  // a head's values, four per lane; the loads of the warp's next two heads are in flight while this one is worked on
+  auto load_head = [&](int head) {
+    const size_t src_offset = (size_t)row * qkv_stride + (size_t)head * D + lane * 4;
+    float4 x = make_float4(0.f, 0.f, 0.f, 0.f);
+    if (head >= heads_to_do) return x;
+    if (num_parts > 0) {
+      for (int part = 0; part < num_parts; ++part) {
+        const float4 d = *reinterpret_cast<const float4*>(qkv_parts + part * part_stride + src_offset);
+        x.x += d.x; x.y += d.y; x.z += d.z; x.w += d.w;
+      }
+    } else if (sizeof(T) == 2) {
+      const uint2 raw = *reinterpret_cast<const uint2*>(qkv + src_offset);
+      const float2 a = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&raw.x));
+      const float2 b = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&raw.y));
+      x = make_float4(a.x, a.y, b.x, b.y);
+    } else {
+      x = *reinterpret_cast<const float4*>(qkv + src_offset);
+    }
+    return x;
+  };
+  float4 next = load_head(warp), after_next = load_head(warp + ROW_WARPS);
+  if (threadIdx.x < HALF) {
+    if (angles) {
+      sincosf(angles[(size_t)row * HALF + threadIdx.x], &sin_table[threadIdx.x], &cos_table[threadIdx.x]);
+    } else if (inv_freq) {
+      sincosf((float)positions[row] * inv_freq[threadIdx.x], &sin_table[threadIdx.x], &cos_table[threadIdx.x]);
+    }
+  }
+  __syncthreads();
+  const int pair0 = (lane & 15) * 4;                      // the four pairs this lane takes part in
+  float4 cs = make_float4(1.f, 1.f, 1.f, 1.f), sn = make_float4(0.f, 0.f, 0.f, 0.f);
+  if (rotate) {
+    cs = *reinterpret_cast<const float4*>(cos_table + pair0);
+    sn = *reinterpret_cast<const float4*>(sin_table + pair0);
+  }
+  const bool first_half = lane < 16;
+  int slot = 0;
+  bool slot_ok = true;
+  if (slots) {
+    slot = slots[row];
+    slot_ok = slot >= 0 && slot < num_pages * page_size;
+    if (!slot_ok && threadIdx.x == 0) atomicOr(error_word, SRB_FLAG_BAD_SLOT);
+  }
+  // where the row's k and v go: element offset of kv head 0, and the step from one kv head to the next
+  const size_t kv_base = ((size_t)(slot / page_size) * n_kv * page_size + (slot % page_size)) * D + lane * 4;
+  const size_t kv_step = (size_t)page_size * D;
+  T* const q_dst = q_out + (size_t)row * n_q * D + lane * 4;
+  const float4 wq = q_norm ? *reinterpret_cast<const float4*>(q_norm + lane * 4) : make_float4(1.f, 1.f, 1.f, 1.f);
+  const float4 wk = k_norm ? *reinterpret_cast<const float4*>(k_norm + lane * 4) : make_float4(1.f, 1.f, 1.f, 1.f);
+#pragma unroll 1
+  for (int head = warp; head < heads_to_do; head += ROW_WARPS) {   // q heads, then k heads, then v heads
+    const bool is_q = head < n_q;
+    const bool is_k = !is_q && head < n_q + n_kv;
+    float4 x = next;
+    next = after_next;
+    after_next = load_head(head + 2 * ROW_WARPS);
+    if (is_q ? q_norm != nullptr : (is_k && k_norm != nullptr)) {
+      const float total = srb_warp_sum(sum_squares4(x));
+      const float inv = __frsqrt_rn(total * (1.0f / (float)D) + eps);
+      const float4 w = is_q ? wq : wk;
+      x = make_float4(normed(x.x, inv, w.x), normed(x.y, inv, w.y), normed(x.z, inv, w.z), normed(x.w, inv, w.w));
+    }
+    if ((is_q || is_k) && rotate) {
+      float4 other;
+      other.x = __shfl_xor_sync(0xffffffffu, x.x, 16); other.y = __shfl_xor_sync(0xffffffffu, x.y, 16);
+      other.z = __shfl_xor_sync(0xffffffffu, x.z, 16); other.w = __shfl_xor_sync(0xffffffffu, x.w, 16);
+      if (first_half)
+        x = make_float4(rotate_first(x.x, other.x, cs.x, sn.x), rotate_first(x.y, other.y, cs.y, sn.y),
+                        rotate_first(x.z, other.z, cs.z, sn.z), rotate_first(x.w, other.w, cs.w, sn.w));
+      else
+        x = make_float4(rotate_second(other.x, x.x, cs.x, sn.x), rotate_second(other.y, x.y, cs.y, sn.y),
+                        rotate_second(other.z, x.z, cs.z, sn.z), rotate_second(other.w, x.w, cs.w, sn.w));
+    }
+    T* dst;
+    if (is_q) {
+      dst = q_dst + head * D;
+    } else {
+      if (!slot_ok) continue;
+      dst = is_k ? k_pool + kv_base + (head - n_q) * kv_step : v_pool + kv_base + (head - n_q - n_kv) * kv_step;
+    }
+    if (sizeof(T) == 2) {
+      uint2 raw;
+      *reinterpret_cast<__nv_bfloat162*>(&raw.x) = __floats2bfloat162_rn(x.x, x.y);
+      *reinterpret_cast<__nv_bfloat162*>(&raw.y) = __floats2bfloat162_rn(x.z, x.w);
+      *reinterpret_cast<uint2*>(dst) = raw;
+    } else {
+      *reinterpret_cast<float4*>(dst) = x;
+    }
+  }
+}
+
 // `slots` may be null: then only the q heads are processed (a layer that reads another
 // layer's cache writes nothing).
 extern "C" int srb_qk_norm_rope_kv(const void* qkv, const float* qkv_parts, int num_parts, long long part_stride,
@@ -173,12 +299,31 @@ extern "C" int srb_qk_norm_rope_kv(const void* qkv, const float* qkv_parts, int 
   const int vector_ok = head_dim % 4 == 0 && qkv_stride % 4 == 0 && part_stride % 4 == 0 &&
                         (((uintptr_t)qkv_parts | (uintptr_t)qkv | (uintptr_t)q_out | (uintptr_t)k_pool |
                           (uintptr_t)v_pool) & 15) == 0;
+  cudaStream_t s = (cudaStream_t)stream;
+  const bool whole_head_pairs = !(inv_freq || angles) || (rotary_dim == head_dim && !interleaved);
+  if (rows >= 64 && head_dim == 128 && vector_ok && whole_head_pairs &&
+      (((uintptr_t)q_norm | (uintptr_t)k_norm) & 15) == 0) {
+    if (dtype == SRB_DTYPE_F32)
+      SRB_CUDA_CALL(srb_launch(qk_norm_rope_kv_row_kernel<float>, dim3(rows), dim3(ROW_WARPS * 32), 0, s,
+                               (const float*)qkv, qkv_parts, num_parts, (size_t)part_stride, qkv_stride, (float*)q_out,
+                               (float*)k_pool, (float*)v_pool, positions, slots, q_norm, k_norm, eps, inv_freq, angles,
+                               n_q, n_kv, page_size, num_pages, heads, error_word));
+    else if (dtype == SRB_DTYPE_BF16)
+      SRB_CUDA_CALL(srb_launch(qk_norm_rope_kv_row_kernel<__nv_bfloat16>, dim3(rows), dim3(ROW_WARPS * 32), 0, s,
+                               (const __nv_bfloat16*)qkv, qkv_parts, num_parts, (size_t)part_stride, qkv_stride,
+                               (__nv_bfloat16*)q_out, (__nv_bfloat16*)k_pool, (__nv_bfloat16*)v_pool, positions, slots,
+                               q_norm, k_norm, eps, inv_freq, angles, n_q, n_kv, page_size, num_pages, heads,
+                               error_word));
+    else
+      SRB_FAIL("qk_norm_rope_kv: unknown dtype %d", dtype);
+    SRB_LAUNCH_CHECK("qk_norm_rope_kv_row");
+    return SRB_OK;
+  }
   // few rows (decode): one head per warp, so that the row is finished soonest; many rows: fewer tables of angles
   const int rounds = rows >= 64 ? ROPE_MAX_ROUNDS : 1;
   const int heads_per_block = ROPE_WARPS * rounds;
   dim3 grid(rows, (heads + heads_per_block - 1) / heads_per_block);
   const size_t smem = ((size_t)ROPE_WARPS * head_dim + ((inv_freq || angles) ? rotary_dim : 0)) * sizeof(float);
-  cudaStream_t s = (cudaStream_t)stream;
   if (dtype == SRB_DTYPE_F32)
     SRB_CUDA_CALL(srb_launch(qk_norm_rope_kv_kernel<float>, grid, dim3(ROPE_WARPS * 32), smem, s, (const float*)qkv,
                              qkv_parts, num_parts, (size_t)part_stride, qkv_stride, (float*)q_out, (float*)k_pool,

@@ -183,6 +183,57 @@ def test_qk_norm_rope_kv(dtype, n_q, n_kv, d, rot, inter):
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("use_parts", [False, True])
+def test_qk_norm_rope_kv_many_rows_of_128(dtype, use_parts):
+    """Portions of 64 rows and more with head_dim 128 take a kernel that keeps a head in
+    registers: against the plain formulas, and bit for bit against the kernel that the same rows
+    take when they come a few at a time (a token's cache entry must not depend on the step it
+    came in)."""
+    g = torch.Generator().manual_seed(5)
+    rows, n_q, n_kv, d, page = 131, 6, 2, 128, 16
+    pages = -(-rows // page) + 2
+    width = (n_q + 2 * n_kv) * d
+    qkv = torch.randn(rows, width, generator=g)
+    qn, kn = 1 + 0.1 * torch.randn(d, generator=g), 1 + 0.1 * torch.randn(d, generator=g)
+    positions = torch.randint(0, 5000, (rows,), generator=g).to(torch.int32)
+    slots = torch.randperm(pages * page, generator=g)[:rows].to(torch.int32)
+    inv = pm.plain_inverse_frequencies(1e6, d)
+    word = ops.new_error_word(DEV)
+    if use_parts:
+        parts = torch.randn(3, rows, width, generator=g)
+        source, seen = parts.to(DEV), parts.double().sum(0)
+    else:
+        source, seen = qkv.to(DEV, dtype), rounded(qkv, dtype)
+
+    def run(lo, hi):
+        k_pool = torch.zeros(pages, n_kv, page, d, device=DEV, dtype=dtype)
+        v_pool = torch.zeros_like(k_pool)
+        q_out = torch.zeros(hi - lo, n_q, d, device=DEV, dtype=dtype)
+        src = source[:, lo:hi].contiguous() if use_parts else source[lo:hi]
+        ops.qk_norm_rope_kv(src, q_out, k_pool, v_pool, positions[lo:hi].to(DEV), slots[lo:hi].to(DEV), qn.to(DEV),
+                            kn.to(DEV), 1e-6, inv.to(DEV), d, False, n_q, n_kv, d, word)
+        return q_out, k_pool, v_pool
+
+    q_out, k_pool, v_pool = run(0, rows)
+    ops.raise_on_error_word(word)
+    q = pm.plain_rope_neox(pm.plain_rms_norm(seen[:, :n_q * d].view(rows, n_q, d), qn.double(), 1e-6), positions, inv)
+    k = pm.plain_rope_neox(pm.plain_rms_norm(seen[:, n_q * d:(n_q + n_kv) * d].view(rows, n_kv, d), kn.double(), 1e-6),
+                           positions, inv)
+    v = seen[:, (n_q + n_kv) * d:].view(rows, n_kv, d)
+    close(q_out, q, dtype, "q")
+    close(k_pool.cpu()[slots.long() // page, :, slots.long() % page], k, dtype, "k")
+    close(v_pool.cpu()[slots.long() // page, :, slots.long() % page], v, dtype, "v")
+    # the same rows, seven at a time, through the kernel for few rows
+    for lo in range(0, rows, 7):
+        hi = min(rows, lo + 7)
+        q_few, k_few, v_few = run(lo, hi)
+        assert torch.equal(q_few, q_out[lo:hi])
+        idx = slots[lo:hi].long()
+        assert torch.equal(k_few[idx // page, :, idx % page], k_pool[idx // page, :, idx % page])
+        assert torch.equal(v_few[idx // page, :, idx % page], v_pool[idx // page, :, idx % page])
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
 @pytest.mark.parametrize("rows,n_q,n_kv,d,rot", [(5, 3, 1, 32, 32), (150, 6, 2, 64, 48)])
 def test_rope_from_a_table_of_angles(dtype, rows, n_q, n_kv, d, rot):
     """The kernel may be given an angle per (row, pair) instead of frequencies: another
