@@ -26,12 +26,12 @@ FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustain
 PREFILL_TOKENS = 2048
 
 
-def qwen3_8b_config(layers: int) -> dict:
+def qwen3_8b_config(layers: int, max_positions: int = 4096) -> dict:
     """Layer sizes of BASELINE.json configs[2] (Qwen3-8B shape)."""
     return {"architectures": ["Qwen3ForCausalLM"], "model_type": "qwen3", "num_hidden_layers": layers,
             "hidden_size": 4096, "num_attention_heads": 32, "num_key_value_heads": 8, "head_dim": 128,
             "intermediate_size": 12288, "vocab_size": 151936, "rope_theta": 1000000.0, "rms_norm_eps": 1e-6,
-            "tie_word_embeddings": False, "max_position_embeddings": 4096, "hidden_act": "silu",
+            "tie_word_embeddings": False, "max_position_embeddings": max_positions, "hidden_act": "silu",
             "attention_bias": False}
 
 
@@ -117,7 +117,9 @@ def main() -> int:
     parser.add_argument("--context", type=int, default=2048, help="tokens each request holds when decoding starts")
     parser.add_argument("--skip-points", action="store_true", help="leave out batch 1 / 64 and the prefill")
     parser.add_argument("--only-prefill", action="store_true",
-                        help="run only the 2,048-token prefill (for profiling); prints its own short line")
+                        help="run only the prefill of one prompt (for profiling); prints its own short line")
+    parser.add_argument("--prefill-tokens", type=int, default=PREFILL_TOKENS,
+                        help="length of the prompt of --only-prefill (the bench line always uses 2,048)")
     args = parser.parse_args()
 
     if args.impl == "reference":
@@ -135,14 +137,15 @@ def main() -> int:
     from sglang_rs_b200.engine.engine import Engine
 
     peak, peak_source = peaks()
-    config = qwen3_8b_config(args.layers)
+    config = qwen3_8b_config(args.layers, max(4096, args.context + 2048, args.prefill_tokens + 64))
     torch.manual_seed(0)
 
     def make_engine(batch: int, steps: int) -> Engine:
         # while later prompts are still computed, earlier requests already decode: leave room for that
         tokens = batch * (args.context + 2 * (steps + warmup) + batch + 64)
         return Engine(config=config, random_weights=True, seed=0, dtype="bfloat16", page_size=16,
-                      max_total_tokens=max(tokens, PREFILL_TOKENS + 64), max_running_requests=max(batch, 1),
+                      max_total_tokens=max(tokens, PREFILL_TOKENS + 64, args.prefill_tokens + 64),
+                      max_running_requests=max(batch, 1),
                       chunked_prefill_size=2048)
 
     def prompts(batch: int, length: int):
@@ -207,17 +210,22 @@ def main() -> int:
     if args.only_prefill:
         from sglang_rs_b200.engine.runner import StepEntry
         times = []
+        length = args.prefill_tokens
+        tokens = prompts(1, length)[0]
         for i in range(warmup + args.steps):
             handle = engine.cache.open(f"prefill-{i}")
             torch.cuda.synchronize()
             begin, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
             begin.record()
-            engine.runner.step([StepEntry(handle, prompts(1, PREFILL_TOKENS)[0], [PREFILL_TOKENS - 1])])
+            engine.runner.step([StepEntry(handle, tokens, [length - 1])])
             end.record()
             torch.cuda.synchronize()
             engine.cache.close(handle)
             times.append(begin.elapsed_time(end))
-        print(json.dumps({"prefill_ms": round(min(times[warmup:]), 3), "tokens": PREFILL_TOKENS, "layers": args.layers}))
+        flops = prefill_flops(config, length)
+        ms = min(times[warmup:])
+        print(json.dumps({"prefill_ms": round(ms, 3), "tokens": length, "layers": args.layers,
+                          "frac_of_bf16_peak": round(flops / (ms * 1e-3) / (peak["bf16_tflops"] * 1e12), 4)}))
         return 0
     main_run = decode_run(engine, args.batch, args.steps, sample_clocks=True)
     value = args.batch * 1e3 / main_run["step_ms"]
@@ -231,7 +239,7 @@ def main() -> int:
         "config": {"model": "Qwen3-8B shape", "layers": args.layers, "layers_of_config": 36, "hidden_size": 4096,
                    "num_attention_heads": 32, "num_key_value_heads": 8, "head_dim": 128, "intermediate_size": 12288,
                    "vocab_size": 151936, "global_batch": args.batch, "seq_len": args.context,
-                   "context_limit": 4096, "page_size": 16, "parallelism": "single GPU",
+                   "context_limit": config["max_position_embeddings"], "page_size": 16, "parallelism": "single GPU",
                    "l2": "inputs larger than L2: a step reads all weights"},
         "gpu_launches": main_run["launches"], "clocks": main_run["clocks"],
         "e2e": {"value": round(args.batch * 1e3 / main_run["e2e_ms"], 2), "unit": "tokens/s",
