@@ -152,7 +152,7 @@ class DecodeGraphs:
                           host_state_slots=[0] * bucket)
         keep = []
         for g, key in enumerate(groups):
-            widest = max(splits[g], ops.decode_splits(bucket, 1))
+            widest = max(splits[g], ops.decode_splits_bound(splits[g] * StepPlanner.SPLIT_SIZE))
             acc = torch.empty(max(bucket * widest * self.planner._scratch_acc_width, 1), dtype=torch.float32,
                               device=self.device)
             ml = torch.empty(max(bucket * widest * self.planner._scratch_ml_width, 1), dtype=torch.float32,

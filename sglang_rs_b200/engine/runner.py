@@ -209,16 +209,18 @@ class StepPlanner:
             pos = positions[:split_rows]
             begin = np.maximum(0, pos + 1 - window) if window else np.zeros_like(pos)
             split_size = self.SPLIT_SIZE
+            visible = int((pos + 1 - begin).max())
             while True:
                 max_splits = int((pos // split_size - begin // split_size + 1).max())
                 # the split count of the generic kernel, or that of the tensor-core decode kernel if larger
-                widest = max(max_splits, ops.decode_splits(split_rows, 1))
+                # (as far as the scratch limit lets it go)
+                fit = max(1, self.SCRATCH_LIMIT // max(split_rows * self._scratch_acc_width, 1))
+                widest = max(max_splits, min(ops.decode_splits_bound(visible), fit))
                 need_acc = split_rows * widest * self._scratch_acc_width
                 need_ml = split_rows * widest * self._scratch_ml_width
                 if need_acc <= self.SCRATCH_LIMIT or max_splits == 1:
                     break
                 split_size *= 2
-            visible = int((pos + 1 - begin).max())
             launches.append(AttentionLaunch(0, split_rows, split_size, max_splits, None, None, visible))
             scratch_acc = self._scratch_tensor("acc", need_acc)
             scratch_ml = self._scratch_tensor("ml", need_ml)

@@ -269,13 +269,35 @@ def decode_attention_takes(dtype: torch.dtype, n_q: int, n_kv: int, head_dim: in
 DECODE_MIN_UNITS = 2
 
 
+#: what a block costs beside its keys (set-up, the load of q, the merge), in 64-key units
+DECODE_BLOCK_OVERHEAD_UNITS = 3
+
+
 def decode_splits(rows: int, n_kv: int, max_keys: Optional[int] = None) -> int:
-    """Blocks per (row, kv head): enough that about three blocks per SM exist, but no more than
-    the longest row (``max_keys`` visible keys) can feed with ``DECODE_MIN_UNITS`` units each."""
-    splits = max(1, min(DECODE_MAX_SPLITS, DECODE_TARGET_BLOCKS // max(rows * n_kv, 1)))
-    if max_keys is not None:
-        splits = max(1, min(splits, -(-max_keys // 64) // DECODE_MIN_UNITS))
-    return splits
+    """Blocks per (row, kv head).  A function of the shape only.
+
+    Without ``max_keys`` (the most keys any row sees): as many as make about three blocks per SM.
+    With it, the count that makes the step shortest under a simple model: the blocks run in waves
+    of three per SM, and a wave lasts as long as one block's share of the keys plus a fixed cost.
+    Many rows then still get their keys cut (512 blocks are 1.15 waves: nearly half the second
+    wave's time is lost), and no block walks fewer than ``DECODE_MIN_UNITS`` units."""
+    base = max(rows * n_kv, 1)
+    if max_keys is None:
+        return max(1, min(DECODE_MAX_SPLITS, DECODE_TARGET_BLOCKS // base))
+    units = max(1, -(-max_keys // 64))
+    cap = max(1, min(DECODE_MAX_SPLITS, units // DECODE_MIN_UNITS))
+    best, best_cost = 1, None
+    for splits in range(1, cap + 1):
+        waves = -(-base * splits // DECODE_TARGET_BLOCKS)
+        cost = waves * (-(-units // splits) + DECODE_BLOCK_OVERHEAD_UNITS)
+        if best_cost is None or cost < best_cost:
+            best, best_cost = splits, cost
+    return best
+
+
+def decode_splits_bound(max_keys: int) -> int:
+    """No call of :func:`decode_splits` with this ``max_keys`` returns more, whatever the rows and heads."""
+    return max(1, min(DECODE_MAX_SPLITS, -(-max_keys // 64) // DECODE_MIN_UNITS))
 
 
 def decode_attention(q: torch.Tensor, k_pool: torch.Tensor, v_pool: torch.Tensor, out: torch.Tensor,
@@ -297,7 +319,9 @@ def decode_attention(q: torch.Tensor, k_pool: torch.Tensor, v_pool: torch.Tensor
     num_pages, n_kv, page_size, pool_dim = k_pool.shape
     if pool_dim != head_dim or v_pool.shape != k_pool.shape or out.shape != q.shape:
         raise KernelError("decode_attention: shapes of q, out and the pools do not agree")
-    splits = decode_splits(rows, n_kv, max_keys)
+    # never more blocks than the scratch memory holds partial results for
+    splits = max(1, min(decode_splits(rows, n_kv, max_keys), scratch_acc.numel() // (rows * n_q * head_dim),
+                        scratch_ml.numel() // (rows * n_q * 2)))
     if scratch_acc.numel() < rows * n_q * splits * head_dim or scratch_ml.numel() < rows * n_q * splits * 2:
         raise KernelError("decode_attention: scratch tensors are too small")
     if counters.numel() < rows * n_kv:
