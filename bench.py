@@ -160,9 +160,11 @@ def main() -> int:
         while any(not engine.scheduler._is_decoding(engine._requests[i]) for i in ids):
             engine.step()                                     # portions of prompts until every request decodes
         requests = [engine._requests[i] for i in ids]
-        # --- entry point, end to end
+        # --- entry point, end to end: every step takes its rows' index arrays from pinned host memory and
+        # hands the tokens of the step before back to the host (steps overlap the host's work)
         for _ in range(warmup):
-            engine.step()
+            engine.step(overlap=True)
+        engine.drain()
         torch.cuda.synchronize()
         sampler = ClockSampler()
         if sample_clocks:
@@ -170,11 +172,14 @@ def main() -> int:
         begin, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         t0 = time.perf_counter()
         begin.record()
+        produced = 0
         for _ in range(steps):
-            engine.step()
+            produced += sum(len(o.token_ids) for o in engine.step(overlap=True))
+        produced += sum(len(o.token_ids) for o in engine.drain())
         end.record()
         torch.cuda.synchronize()
         wall = time.perf_counter() - t0
+        assert produced == steps * batch, (produced, steps, batch)
         e2e_ms = max(begin.elapsed_time(end), wall * 1e3) / steps
         h2d = engine.runner.planner.last_upload_bytes + (8 * batch if False else 0)
         # --- the step function alone: fixed token ids, logits stay on the device, greedy pick on the device
@@ -203,7 +208,7 @@ def main() -> int:
             engine.cache.close(h)
         print(f"[bench] batch {batch}: step {step_ms:.3f} ms, entry point {e2e_ms:.3f} ms, context {context_mid:.0f}",
               file=sys.stderr, flush=True)
-        return {"step_ms": step_ms, "e2e_ms": e2e_ms, "h2d": h2d, "d2h": 4 * batch, "launches": launches,
+        return {"step_ms": step_ms, "e2e_ms": e2e_ms, "h2d": h2d, "d2h": 4 * batch + 4, "launches": launches,
                 "context": context_mid, "clocks": clocks}
 
     engine = make_engine(max(args.batch, 1), args.steps)

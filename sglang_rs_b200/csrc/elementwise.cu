@@ -279,3 +279,28 @@ extern "C" int srb_add_bias(void* values, const float* bias, int rows, int width
   SRB_LAUNCH_CHECK("add_bias");
   return SRB_OK;
 }
+
+// tokens[i] = source[index[i]] where index[i] >= 0: rows whose token was chosen on the device by
+// the step before and has not been to the host yet.  An index outside the source flags a bad token.
+__global__ void take_tokens_kernel(int* __restrict__ tokens, const int* __restrict__ source,
+                                   const int* __restrict__ index, int rows, int source_rows, int* error_word) {
+  const int i = blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= rows) return;
+  const int from = index[i];
+  if (from < 0) return;
+  if (from >= source_rows) {
+    atomicOr(error_word, SRB_FLAG_BAD_TOKEN);
+    return;
+  }
+  tokens[i] = source[from];
+}
+
+extern "C" int srb_take_tokens(int* tokens, const int* source, const int* index, int rows, int source_rows,
+                               int* error_word, void* stream) {
+  if (rows <= 0) return SRB_OK;
+  if (source_rows <= 0) SRB_FAIL("take_tokens: the source has no rows");
+  take_tokens_kernel<<<(rows + 127) / 128, 128, 0, (cudaStream_t)stream>>>(tokens, source, index, rows, source_rows,
+                                                                          error_word);
+  SRB_LAUNCH_CHECK("take_tokens");
+  return SRB_OK;
+}

@@ -165,7 +165,7 @@ __global__ void qk_norm_rope_kv_kernel(const T* __restrict__ qkv, const float* _
 }
 
 
-// Many rows, head_dim 128, rotation of the whole head in half-split pairs: one block per row, every
+// Many rows (256 and more), head_dim 128, rotation of the whole head in half-split pairs: one block per row, every
 // warp takes several heads of the row and keeps a head in registers (lane l holds elements 4l..4l+3,
 // its rotation partner sits in lane l ^ 16), so a head costs one load, two shuffles' worth of
 // exchange and one store.  Same arithmetic as the kernel above.
@@ -301,7 +301,8 @@ extern "C" int srb_qk_norm_rope_kv(const void* qkv, const float* qkv_parts, int 
                           (uintptr_t)v_pool) & 15) == 0;
   cudaStream_t s = (cudaStream_t)stream;
   const bool whole_head_pairs = !(inv_freq || angles) || (rotary_dim == head_dim && !interleaved);
-  if (rows >= 64 && head_dim == 128 && vector_ok && whole_head_pairs &&
+  // (with fewer rows than about two per SM the kernel below, which spreads a row over blocks, is quicker)
+  if (rows >= 256 && head_dim == 128 && vector_ok && whole_head_pairs &&
       (((uintptr_t)q_norm | (uintptr_t)k_norm) & 15) == 0) {
     if (dtype == SRB_DTYPE_F32)
       SRB_CUDA_CALL(srb_launch(qk_norm_rope_kv_row_kernel<float>, dim3(rows), dim3(ROW_WARPS * 32), 0, s,

@@ -9,6 +9,7 @@ join between any two steps (``add_request`` + ``step``).
 from __future__ import annotations
 
 import itertools
+from dataclasses import dataclass
 from typing import Any, Dict, Hashable, List, Mapping, Optional, Sequence, Union
 
 import torch
@@ -26,17 +27,29 @@ def kv_bytes_per_token(model, dtype: torch.dtype) -> int:
     return width * (4 if dtype == torch.float32 else 2)
 
 
+@dataclass
+class _StepInFlight:
+    """A step that runs on the GPU while the host goes on: its rows, the ids it chose (on the
+    device), and the pinned copy of ids and error word that the event says is complete."""
+    entries: list
+    picked: torch.Tensor
+    host: torch.Tensor                       # pinned int32: picked ids, then the error word
+    done: torch.cuda.Event
+
+
 class Engine:
     def __init__(self, model_path: Optional[str] = None, *, random_weights: bool = False, seed: int = 0,
                  dtype: str = "bfloat16", device: str = "cuda", page_size: int = 16,
                  max_total_tokens: Optional[int] = None, mem_fraction_static: float = 0.85,
                  max_running_requests: int = 256, chunked_prefill_size: int = 2048,
                  config: Optional[Mapping[str, Any]] = None, stop_token_ids: Optional[Sequence[int]] = None,
-                 disable_cuda_graph: bool = False, disable_radix_cache: bool = False):
+                 disable_cuda_graph: bool = False, disable_radix_cache: bool = False,
+                 disable_overlap_schedule: bool = False):
         """Option names follow the reference's server arguments where it has them
         (crates/sglang-srt/src/cli.rs:15-79: ``model_path``, ``device``, ``page_size``,
         ``max_total_tokens``, ``mem_fraction_static``, ``max_running_requests``,
-        ``chunked_prefill_size``, ``disable_cuda_graph``, ``disable_radix_cache``).  ``config`` may stand in for the folder's config.json
+        ``chunked_prefill_size``, ``disable_cuda_graph``, ``disable_radix_cache``; ``disable_overlap_schedule``
+        has the name that SGLang gives it).  ``config`` may stand in for the folder's config.json
         together with ``random_weights``."""
         if not str(device).startswith("cuda"):
             raise ValueError(f"device {device!r}: this engine runs on CUDA only and never falls back to the host")
@@ -44,6 +57,7 @@ class Engine:
             raise RuntimeError("no CUDA device is visible; this engine has no host path")
         self.dtype = parse_dtype(dtype)
         self.device = torch.device(device)
+        self.disable_overlap_schedule = disable_overlap_schedule
         self.model = load_model(model_path, device=self.device, dtype=self.dtype, random_weights=random_weights,
                                 seed=seed, config=config)
         if max_total_tokens is None:
@@ -64,6 +78,8 @@ class Engine:
         self._randoms: Dict[Hashable, RequestRandom] = {}
         self._requests: Dict[Hashable, Request] = {}
         self._ids = itertools.count()
+        self._in_flight: Optional[_StepInFlight] = None
+        self._host_only_sampling = 0            # live requests whose sampling needs their tokens on the host
 
     # ------------------------------------------------------------------ low level
     def add_request(self, input_ids: Sequence[int], sampling_params: Union[SamplingParams, Mapping, None] = None,
@@ -82,14 +98,25 @@ class Engine:
         self.scheduler.add_request(request)
         self._requests[request_id] = request
         self._randoms[request_id] = RequestRandom(request_id, params.seed)
+        if not Sampler.stays_on_device(params):
+            self._host_only_sampling += 1
         return request_id
 
-    def step(self) -> List[StepOutput]:
+    def step(self, overlap: bool = False) -> List[StepOutput]:
         """One scheduling decision, one model step, one token for every request whose
-        portion reached its last token."""
+        portion reached its last token.
+
+        ``overlap``: the step is launched and the call returns what the step *before* produced;
+        the host's work for the next step (scheduling, flattening, reading the tokens) then runs
+        while the GPU computes.  Tokens of requests that decode go from one step to the next on the
+        device.  A request that ends on a stop token has then one more row computed in vain, which
+        is dropped.  Call :meth:`drain` (or keep stepping) for the last step's outputs."""
+        if overlap:
+            return self._step_overlapped()
+        outputs = self.drain()
         entries = self.scheduler.schedule()
         if not entries:
-            return self.scheduler.process_outputs([], [])
+            return outputs + self.scheduler.process_outputs([], [])
         step_entries = [StepEntry(e.request.handle, e.tokens, [len(e.tokens) - 1] if e.samples else [])
                         for e in entries]
         try:
@@ -104,10 +131,94 @@ class Engine:
         except Exception:
             self.scheduler.step_failed(entries)
             raise
-        outputs = self.scheduler.process_outputs(entries, sampled)
+        outputs += self.scheduler.process_outputs(entries, sampled)
+        self._forget_finished(outputs)
+        return outputs
+
+    def _forget_finished(self, outputs: Sequence[StepOutput]) -> None:
         for output in outputs:
-            if output.finished:
-                self._randoms.pop(output.request_id, None)
+            if output.finished and self._randoms.pop(output.request_id, None) is not None:
+                request = self._requests.get(output.request_id)
+                if request is not None and not Sampler.stays_on_device(request.sampling):
+                    self._host_only_sampling -= 1
+
+    # ------------------------------------------------------------------ steps that overlap the host's work
+    def _step_overlapped(self) -> List[StepOutput]:
+        before = self._in_flight
+        launched = None
+        if before is not None and self._may_run_ahead():
+            launched = self._launch(before)                  # the GPU has its next step before this one is read
+        outputs = self.drain()
+        if launched is None:
+            launched = self._launch(None)
+        self._in_flight = launched
+        return outputs
+
+    def _may_run_ahead(self) -> bool:
+        """The next step can be chosen before the tokens of the one in flight are known: sampling
+        needs no token history, and every running request can get a page without preemption."""
+        if self._host_only_sampling:
+            return False
+        running = len(self.scheduler.running)
+        return all(free >= running for free in self.cache.free_pages().values())
+
+    def _launch(self, before: Optional[_StepInFlight]) -> Optional[_StepInFlight]:
+        entries = self.scheduler.schedule(ahead=before is not None)
+        if not entries:
+            return None
+        sampling = [e.request for e in entries if e.samples]
+        on_device = all(Sampler.stays_on_device(r.sampling) for r in sampling)
+        source_row = {}
+        if before is not None:
+            rows = [e.request for e in before.entries if e.samples]
+            source_row = {id(r): i for i, r in enumerate(rows)}
+        step_entries = [StepEntry(e.request.handle, [0] if e.from_device else e.tokens,
+                                  [len(e.tokens) - 1] if e.samples else [],
+                                  token_from=source_row[id(e.request)] if e.from_device else -1) for e in entries]
+        try:
+            logits = self.runner.step(step_entries, before.picked if before is not None else None)
+            if logits is None or not on_device:
+                # nothing to sample, or sampling that needs the host: finish the step here
+                sampled: List[int] = []
+                if logits is not None:
+                    sampled = self.sampler.sample(
+                        logits, [r.sampling for r in sampling], [self._randoms[r.request_id] for r in sampling],
+                        [r.tokens if r.sampling.has_penalties else () for r in sampling])
+                self.runner.check_device_errors()
+                picked = torch.tensor(sampled + [0], dtype=torch.int32).pin_memory()
+                done = torch.cuda.Event()
+                done.record()
+                for request in sampling:
+                    request.pending += 1
+                return _StepInFlight(entries, picked[:len(sampled)].to(self.device, non_blocking=True), picked, done)
+            picked = self.sampler.pick_on_device(logits, [r.sampling for r in sampling],
+                                                 [self._randoms[r.request_id] for r in sampling])
+            host = torch.empty(picked.numel() + 1, dtype=torch.int32, pin_memory=True)
+            host[:-1].copy_(picked, non_blocking=True)
+            host[-1:].copy_(self.runner.error_word, non_blocking=True)
+            done = torch.cuda.Event()
+            done.record()
+        except Exception:
+            self.scheduler.step_failed(entries)
+            raise
+        for request in sampling:
+            request.pending += 1
+        return _StepInFlight(entries, picked, host, done)
+
+    def drain(self) -> List[StepOutput]:
+        """Outputs of the step in flight, if there is one (waits for it)."""
+        flight, self._in_flight = self._in_flight, None
+        if flight is None:
+            return []
+        flight.done.synchronize()
+        values = flight.host.tolist()
+        try:
+            self.runner.raise_on_error_bits(values[-1])
+        except Exception:
+            self.scheduler.step_failed(flight.entries)
+            raise
+        outputs = self.scheduler.process_outputs(flight.entries, values[:-1])
+        self._forget_finished(outputs)
         return outputs
 
     def abort(self, request_id: Hashable) -> bool:
@@ -136,8 +247,8 @@ class Engine:
         else:
             params = [sampling_params] * len(prompts)
         ids = [self.add_request(prompt, p) for prompt, p in zip(prompts, params)]
-        while self.scheduler.has_work:
-            self.step()
+        while self.scheduler.has_work or self._in_flight is not None:
+            self.step(overlap=not self.disable_overlap_schedule)
         results = []
         for request_id in ids:
             request = self._requests.pop(request_id)

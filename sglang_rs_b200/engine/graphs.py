@@ -55,7 +55,7 @@ class DecodeGraphs:
                 and all(len(e.tokens) == 1 and list(e.want) in ([], [0]) for e in entries))
 
     # ------------------------------------------------------------------ one step
-    def run(self, entries: Sequence[StepEntry]) -> Optional[torch.Tensor]:
+    def run(self, entries: Sequence[StepEntry], token_source: Optional[torch.Tensor] = None) -> Optional[torch.Tensor]:
         """Entries are validated and their pages reserved.  Returns logits of the entries
         that want them, in order."""
         rows = len(entries)
@@ -78,6 +78,10 @@ class DecodeGraphs:
             step.copied.synchronize()        # the staging buffer is free again once its last copy has run
         self._fill(step, entries, groups, bucket, stride, positions, page_size)
         step.static.copy_(step.staging, non_blocking=True)
+        if any(e.token_from >= 0 for e in entries):
+            # tokens that the step before chose and that never went to the host
+            (t0, _), (f0, _) = step.layout["tokens"], step.layout["token_from"]
+            ops.take_tokens(step.static[t0:t0 + rows], token_source, step.static[f0:f0 + rows], self.planner.error_word)
         self.planner.last_upload_bytes = step.staging.numel() * 4
         if step.copied is None:
             step.copied = torch.cuda.Event()
@@ -99,7 +103,7 @@ class DecodeGraphs:
         bucket, stride, _ = key
         layout, offset = {}, 0
         for name, size in (("tokens", bucket), ("positions", bucket), ("row_request", bucket), ("cu_rows", bucket + 1),
-                           ("state_slots", bucket), ("logit_rows", bucket)):
+                           ("state_slots", bucket), ("logit_rows", bucket), ("token_from", bucket)):
             layout[name] = (offset, size)
             offset += (size + 3) // 4 * 4
         for g in range(len(groups)):
@@ -122,6 +126,8 @@ class DecodeGraphs:
             return view[begin:begin + size]
         tokens = part("tokens"); tokens[:] = 0
         tokens[:rows] = [int(e.tokens[0]) for e in entries]
+        token_from = part("token_from"); token_from[:] = -1
+        token_from[:rows] = [e.token_from for e in entries]
         pos = part("positions"); pos[:] = 0
         pos[:rows] = positions
         part("row_request")[:] = np.arange(bucket)

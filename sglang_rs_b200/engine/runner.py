@@ -31,6 +31,9 @@ class StepEntry:
     tokens: Sequence[int]
     #: indices into ``tokens`` whose logits are wanted
     want: Sequence[int] = ()
+    #: >= 0: the entry's single token is not known on the host; it is row ``token_from`` of the
+    #: ``token_source`` tensor given to the step (what the step before chose, still on the device)
+    token_from: int = -1
 
 
 @dataclass
@@ -106,13 +109,14 @@ class StepPlanner:
         self.last_upload_bytes = 0
 
     # ------------------------------------------------------------------ flattening
-    def flatten(self, entries: Sequence[StepEntry]):
+    def flatten(self, entries: Sequence[StepEntry], token_source: Optional[torch.Tensor] = None):
         # decoded tokens first, portions after them: each kind is one contiguous row range
         order = sorted(range(len(entries)),
                        key=lambda i: (len(entries[i].tokens) > self.SPLIT_ROWS_PER_REQUEST, i))
         starts = [0] * len(entries)
         cu_rows = [0]
         tokens: List[int] = []
+        token_from: List[int] = []
         positions: List[int] = []
         row_request: List[int] = []
         start_positions: List[int] = []
@@ -123,6 +127,7 @@ class StepPlanner:
             count = len(entry.tokens)
             starts[index] = cu_rows[-1]
             tokens.extend(int(t) for t in entry.tokens)
+            token_from.extend([entry.token_from] * count)
             positions.extend(range(entry.handle.length, entry.handle.length + count))
             row_request.extend([slot] * count)
             start_positions.append(entry.handle.length)
@@ -172,7 +177,12 @@ class StepPlanner:
         for key in groups:
             pieces.append(tables[key].reshape(-1))
             pieces.append(slots[key])
+        from_device = any(f >= 0 for f in token_from)
+        if from_device:
+            pieces.append(np.asarray(token_from, dtype=np.int32))
         device_pieces = self._upload(pieces)
+        if from_device:
+            ops.take_tokens(device_pieces[0], token_source, device_pieces[-1], self.error_word)
         (token_ids, positions_d, row_request_d, cu_rows_d, state_slots_d, logit_rows_d, tiles_d,
          wide_tiles_d) = device_pieces[:8]
         tiles_d, wide_tiles_d = tiles_d.view(-1, 4), wide_tiles_d.view(-1, 4)
@@ -254,13 +264,14 @@ class ModelRunner:
             self.graphs = DecodeGraphs(model, cache, self.planner)
 
     # ------------------------------------------------------------------ the step
-    def step(self, entries: Sequence[StepEntry]) -> Optional[torch.Tensor]:
+    def step(self, entries: Sequence[StepEntry], token_source: Optional[torch.Tensor] = None) -> Optional[torch.Tensor]:
         """Runs one batch.  Returns logits [wanted rows, vocab] (float32, on the device) in
-        the order of ``entries`` and of each entry's ``want``, or None if none is wanted."""
+        the order of ``entries`` and of each entry's ``want``, or None if none is wanted.
+        ``token_source``: int32 on the device, read by entries with ``token_from`` set."""
         entries = [entry for entry in entries]
         if not entries:
             return None
-        self._validate(entries)
+        self._validate(entries, token_source)
         reserved: List[StepEntry] = []
         try:
             for entry in entries:
@@ -272,9 +283,9 @@ class ModelRunner:
             raise
         try:
             if self.graphs is not None and self.graphs.eligible(entries):
-                logits = self.graphs.run(entries)
+                logits = self.graphs.run(entries, token_source)
             else:
-                ctx, logit_rows = self.planner.flatten(entries)
+                ctx, logit_rows = self.planner.flatten(entries, token_source)
                 caches = [self.cache.layer_cache(i) for i in range(len(self.model.program))]
                 with ops.stream_scope():
                     logits = self.model.forward(ctx, caches, logit_rows)
@@ -292,8 +303,12 @@ class ModelRunner:
         skipped an access."""
         ops.raise_on_error_word(self.error_word)
 
+    def raise_on_error_bits(self, value: int) -> None:
+        """The same check for a copy of the error word that is on the host already."""
+        ops.raise_on_error_value(int(value), self.error_word)
+
     # ------------------------------------------------------------------ checks
-    def _validate(self, entries: Sequence[StepEntry]) -> None:
+    def _validate(self, entries: Sequence[StepEntry], token_source: Optional[torch.Tensor] = None) -> None:
         seen = set()
         for entry in entries:
             handle = entry.handle
@@ -309,7 +324,11 @@ class ModelRunner:
                 raise StepInputError(
                     f"request {handle.request_id!r}: position {handle.length + count - 1} exceeds "
                     f"max_position_embeddings {self.model.max_positions}")
-            if min(entry.tokens) < 0 or max(entry.tokens) >= self.model.vocab_size:
+            if entry.token_from >= 0:
+                if count != 1 or token_source is None or entry.token_from >= token_source.numel():
+                    raise StepInputError(f"request {handle.request_id!r}: a token taken from the device must be the "
+                                         f"entry's only one and lie inside the source")
+            elif min(entry.tokens) < 0 or max(entry.tokens) >= self.model.vocab_size:
                 raise StepInputError(f"request {handle.request_id!r}: a token id among {list(entry.tokens)[:8]}... is "
                                      f"outside the vocabulary of {self.model.vocab_size}")
             for index in entry.want:

@@ -46,6 +46,9 @@ class Request:
     preemptions: int = 0
     admitted_at: int = -1
     published_pages: int = 0                 # prompt pages already handed to the prefix tree
+    #: tokens that a step has chosen for this request but that have not reached the host yet (0 or 1):
+    #: they count as tokens of the request, their values are on the device
+    pending: int = 0
 
     @property
     def tokens(self) -> List[int]:
@@ -53,10 +56,13 @@ class Request:
 
     @property
     def num_tokens(self) -> int:
-        return len(self.prompt) + len(self.output_ids)
+        return len(self.prompt) + len(self.output_ids) + self.pending
 
     @property
     def last_token(self) -> int:
+        """The last token, or -1 while it is still on the device."""
+        if self.pending:
+            return -1
         return self.output_ids[-1] if self.output_ids else self.prompt[-1]
 
     def tokens_from(self, start: int, count: int) -> List[int]:
@@ -79,6 +85,8 @@ class ScheduledEntry:
     tokens: List[int]
     #: True if this portion ends with the request's last known token, so a token is sampled
     samples: bool
+    #: True if the entry's one token (-1 here) was chosen by the step before and is still on the device
+    from_device: bool = False
 
 
 @dataclass
@@ -135,11 +143,15 @@ class Scheduler:
         return bool(self.waiting or self.running)
 
     # ------------------------------------------------------------------ one step's decisions
-    def schedule(self) -> List[ScheduledEntry]:
-        """Chooses the rows of the next step and reserves their pages."""
+    def schedule(self, ahead: bool = False) -> List[ScheduledEntry]:
+        """Chooses the rows of the next step and reserves their pages.
+
+        ``ahead``: the step before has not reported its tokens yet (requests have ``pending``
+        tokens).  The caller has made sure that every running request can get a page, so nothing
+        is preempted; a step with nothing to do is then no deadlock, only a wait for those tokens."""
         while True:
             entries = self._schedule_once()
-            if entries or not self.running:
+            if entries or not self.running or ahead:
                 break
             # Nothing could move although requests are running: prompts in progress hold all
             # pages between them.  The one admitted last gives its pages up.
@@ -158,6 +170,8 @@ class Scheduler:
         for request in decoding:
             if request not in self.running:
                 continue                                     # preempted below, earlier in this loop
+            if self._ends_whatever_comes(request):
+                continue                                     # it finishes when its token arrives
             while True:
                 try:
                     self.cache.reserve(request.handle, 1)
@@ -174,13 +188,15 @@ class Scheduler:
                     if victim is request:
                         break
             if request in self.running and not request.finished:
-                entries.append(ScheduledEntry(request, [request.last_token], True))
+                entries.append(ScheduledEntry(request, [request.last_token], True, from_device=request.pending > 0))
                 budget -= 1
 
         # 2. prompts in progress go on, oldest first; 3. then new requests are admitted
         for request in [r for r in self.running if not self._is_decoding(r)]:
             if budget <= 0:
                 break
+            if request.pending:
+                continue
             if any(e.request is request for e in entries):
                 continue
             budget -= self._schedule_portion(request, budget, entries)
@@ -217,7 +233,14 @@ class Scheduler:
         return entries
 
     def _is_decoding(self, request: Request) -> bool:
-        return request.handle is not None and bool(request.output_ids) and request.computed == request.num_tokens - 1
+        return (request.handle is not None and bool(request.output_ids or request.pending)
+                and request.computed == request.num_tokens - 1)
+
+    def _ends_whatever_comes(self, request: Request) -> bool:
+        """True if the token still on the device is the request's last, whichever it is."""
+        return request.pending > 0 and (
+            len(request.output_ids) + request.pending >= request.sampling.max_new_tokens
+            or request.num_tokens >= self.config.max_positions)
 
     def _schedule_portion(self, request: Request, budget: int, entries: List[ScheduledEntry]) -> int:
         total = request.num_tokens
@@ -272,6 +295,9 @@ class Scheduler:
             if not entry.samples:
                 continue
             token = int(next(picks))
+            if request.finished:
+                continue                     # it ended (stop token, abort) while this step was already running
+            request.pending = max(0, request.pending - 1)
             request.output_ids.append(token)
             stops = set(request.sampling.stop_token_ids) | set(self.config.default_stop_token_ids)
             reason = None

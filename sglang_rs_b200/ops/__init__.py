@@ -88,7 +88,11 @@ ERROR_BITS = {1: "token id outside the vocabulary", 2: "cache slot outside the p
 
 
 def raise_on_error_word(word: torch.Tensor) -> None:
-    value = int(word.item())
+    raise_on_error_value(int(word.item()), word)
+
+
+def raise_on_error_value(value: int, word: torch.Tensor) -> None:
+    """``value``: what ``word`` held when it was last copied to the host."""
     if value:
         word.zero_()
         what = [text for bit, text in ERROR_BITS.items() if value & bit]
@@ -106,6 +110,17 @@ def embedding(ids: torch.Tensor, table: torch.Tensor, residual: torch.Tensor, er
     lib = load_library("elementwise")
     _check(lib, lib.srb_embedding(_ptr(ids), _ptr(table), _ptr(residual), rows, width, table.shape[0],
                                   _ptr(error_word), dtype_code(table.dtype), _stream()))
+
+
+def take_tokens(tokens: torch.Tensor, source: torch.Tensor, index: torch.Tensor, error_word: torch.Tensor) -> None:
+    """tokens[i] = source[index[i]] where index[i] >= 0 (int32, on the device): the token ids that the
+    step before chose and that have not been to the host yet."""
+    _need(tokens, "tokens", torch.int32); _need(source, "source", torch.int32); _need(index, "index", torch.int32)
+    if index.numel() < tokens.numel():
+        raise KernelError("take_tokens: one index per token is needed")
+    lib = load_library("elementwise")
+    _check(lib, lib.srb_take_tokens(_ptr(tokens), _ptr(source), _ptr(index), tokens.numel(), source.numel(),
+                                    _ptr(error_word), _stream()))
 
 
 def add_rmsnorm(residual: torch.Tensor, delta: Optional[torch.Tensor], weight: torch.Tensor, eps: float,

@@ -74,6 +74,27 @@ class Sampler:
     def __init__(self, device):
         self.device = device
 
+    def pick_on_device(self, logits: torch.Tensor, params: Sequence[SamplingParams],
+                       randoms: Sequence[RequestRandom]) -> torch.Tensor:
+        """Greedy and plain temperature rows only (no penalties, no top-k / top-p / min-p): the
+        chosen ids stay on the device (int32 [rows]); nothing waits for the GPU."""
+        rows = logits.shape[0]
+        temperature = [0.0] * rows
+        uniform = [0.0] * rows
+        for r, p in enumerate(params):
+            if not p.is_greedy:
+                uniform[r] = randoms[r].next_unit()
+                temperature[r] = p.effective_temperature
+        if any(t > 0 for t in temperature):
+            staged = torch.tensor([temperature, uniform], dtype=torch.float32).pin_memory().to(self.device, non_blocking=True)
+            return ops.sample(logits, staged[0].contiguous(), staged[1].contiguous())
+        return ops.sample(logits, None, None)
+
+    @staticmethod
+    def stays_on_device(params: SamplingParams) -> bool:
+        """True if :meth:`pick_on_device` samples this request exactly as :meth:`sample` does."""
+        return not params.has_penalties and (params.is_greedy or not params.filters)
+
     def sample(self, logits: torch.Tensor, params: Sequence[SamplingParams], randoms: Sequence[RequestRandom],
                seen_tokens: Sequence[Sequence[int]]) -> List[int]:
         """``logits`` [rows, vocab] float32 on the device; one entry of the other arguments

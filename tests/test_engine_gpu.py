@@ -126,6 +126,64 @@ def test_temperature_sampling_is_seeded_and_independent_of_the_batch(tmp_path):
         tokens.append(token)
 
 
+@pytest.mark.parametrize("use_graphs", [True, False])
+def test_overlapped_steps_give_the_same_tokens(tmp_path, use_graphs):
+    """With ``overlap`` a step is launched before the tokens of the step before are read: decoded
+    tokens travel on the device, finished requests get one row in vain.  Requests that stop at
+    different times (stop tokens, lengths), requests that join later, temperature sampling, a
+    request whose sampling needs the host, and a pool so small that requests are preempted: the
+    tokens are those of the plain loop."""
+    from sglang_rs_b200 import Engine
+    folder = rh.make_folder(tmp_path, "m", pm.TINY_B, seed=14, dtype=torch.float32)
+    cfg, weights = pm.load_folder(folder)
+    prompts = list(rh.random_requests(pm.TINY_B, (9, 30, 17, 41, 5, 26), seed=3).values())
+    greedy = [pm.plain_greedy(cfg, weights, p, 24) for p in prompts]
+    params = [{"max_new_tokens": 24},
+              {"max_new_tokens": 24, "stop_token_ids": [greedy[1][6]]},
+              {"max_new_tokens": 11},
+              {"max_new_tokens": 20, "temperature": 0.8, "seed": 4},
+              {"max_new_tokens": 1},
+              {"max_new_tokens": 24, "stop_token_ids": [greedy[5][15]]}]
+
+    def run(overlap, pool, late=(), extra=None):
+        engine = Engine(model_path=folder, dtype="float32", page_size=8, max_total_tokens=pool, max_running_requests=4,
+                        chunked_prefill_size=24, disable_cuda_graph=not use_graphs)
+        chosen = dict(enumerate(params))
+        if extra:
+            chosen.update(extra)
+        ids = {}
+        for i, prompt in enumerate(prompts):
+            if i not in late:
+                ids[i] = engine.add_request(prompt, chosen[i])
+        got = {i: [] for i in range(len(prompts))}
+        by_id = lambda rid: next(i for i, v in ids.items() if v == rid)
+        steps = 0
+        while engine.scheduler.has_work or engine._in_flight is not None or len(ids) < len(prompts):
+            if steps == 5:
+                for i in late:
+                    ids[i] = engine.add_request(prompts[i], chosen[i])
+            for output in engine.step(overlap=overlap):
+                got[by_id(output.request_id)] += output.token_ids
+            steps += 1
+            assert steps < 500
+        engine.cache.check_invariants()
+        assert engine.flush_cache()
+        assert all(a.free_count == a.num_pages for a in engine.cache.allocators.values())
+        return [got[i] for i in range(len(prompts))], engine.scheduler.stats["preemptions"]
+
+    plain, _ = run(False, 600)
+    assert plain[0] == greedy[0] and plain[2] == greedy[2][:11] and plain[4] == greedy[4][:1]
+    assert plain[1] == greedy[1][:greedy[1].index(greedy[1][6]) + 1]
+    assert run(True, 600) == (plain, 0)
+    assert run(True, 600, late=(2, 5))[0] == plain
+    # a request with top-k among them: its steps wait for the host, the tokens stay the same
+    top = {0: {"max_new_tokens": 24, "temperature": 1.0, "top_k": 1}}
+    assert run(True, 600, extra=top)[0] == plain
+    # so few pages that requests are preempted and recomputed
+    tight, preemptions = run(True, 104)
+    assert tight == plain and preemptions > 0
+
+
 def test_stop_tokens_top_k_and_penalties(tmp_path):
     from sglang_rs_b200 import Engine
     folder = rh.make_folder(tmp_path, "m", pm.TINY_A, seed=9, dtype=torch.float32)

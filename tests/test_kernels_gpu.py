@@ -185,12 +185,12 @@ def test_qk_norm_rope_kv(dtype, n_q, n_kv, d, rot, inter):
 @pytest.mark.parametrize("dtype", DTYPES)
 @pytest.mark.parametrize("use_parts", [False, True])
 def test_qk_norm_rope_kv_many_rows_of_128(dtype, use_parts):
-    """Portions of 64 rows and more with head_dim 128 take a kernel that keeps a head in
+    """Portions of 256 rows and more with head_dim 128 take a kernel that keeps a head in
     registers: against the plain formulas, and bit for bit against the kernel that the same rows
     take when they come a few at a time (a token's cache entry must not depend on the step it
     came in)."""
     g = torch.Generator().manual_seed(5)
-    rows, n_q, n_kv, d, page = 131, 6, 2, 128, 16
+    rows, n_q, n_kv, d, page = 291, 6, 2, 128, 16
     pages = -(-rows // page) + 2
     width = (n_q + 2 * n_kv) * d
     qkv = torch.randn(rows, width, generator=g)
@@ -223,9 +223,9 @@ def test_qk_norm_rope_kv_many_rows_of_128(dtype, use_parts):
     close(q_out, q, dtype, "q")
     close(k_pool.cpu()[slots.long() // page, :, slots.long() % page], k, dtype, "k")
     close(v_pool.cpu()[slots.long() // page, :, slots.long() % page], v, dtype, "v")
-    # the same rows, seven at a time, through the kernel for few rows
-    for lo in range(0, rows, 7):
-        hi = min(rows, lo + 7)
+    # the same rows, 37 at a time, through the kernel for few rows
+    for lo in range(0, rows, 37):
+        hi = min(rows, lo + 37)
         q_few, k_few, v_few = run(lo, hi)
         assert torch.equal(q_few, q_out[lo:hi])
         idx = slots[lo:hi].long()
