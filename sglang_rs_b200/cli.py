@@ -37,6 +37,8 @@ def build_parser() -> argparse.ArgumentParser:
     gen.add_argument("--chunked-prefill-size", type=int, default=2048)
     gen.add_argument("--disable-cuda-graph", action="store_true")
     gen.add_argument("--disable-radix-cache", action="store_true")
+    gen.add_argument("--disable-overlap-schedule", action="store_true",
+                     help="read every step's tokens before the next step is launched")
     source = gen.add_mutually_exclusive_group(required=True)
     source.add_argument("--input-ids", action="append", help="comma-separated token ids; repeat for more prompts")
     source.add_argument("--input-ids-file", help="JSON file: a list of token-id lists")
@@ -85,7 +87,8 @@ def main(argv: Optional[List[str]] = None) -> int:
                     device=args.device, page_size=args.page_size, max_total_tokens=args.max_total_tokens,
                     mem_fraction_static=args.mem_fraction_static, max_running_requests=args.max_running_requests,
                     chunked_prefill_size=args.chunked_prefill_size, disable_cuda_graph=args.disable_cuda_graph,
-                    disable_radix_cache=args.disable_radix_cache)
+                    disable_radix_cache=args.disable_radix_cache,
+                    disable_overlap_schedule=args.disable_overlap_schedule)
     if args.input_ids:
         prompts = [_ids(text) for text in args.input_ids]
     elif args.input_ids_file:

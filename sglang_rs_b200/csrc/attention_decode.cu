@@ -59,14 +59,21 @@ decode_attention_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16
   const AttnParams& p = dp.a;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int row = blockIdx.z, kv_head = blockIdx.y, split = blockIdx.x;
+  // The step's index arrays were copied in before its first kernel, so they may be read at once.
+  // q and the key and value at the row's own position come from the kernel ahead: they are read
+  // after the dependency wait.  Keys before that position are from earlier steps (a row of this
+  // launch is the only row of its request in the step), so a block whose first unit ends before
+  // the row's position asks for it before the wait and overlaps the kernel ahead.
   srb_launch_dependents();
-  srb_grid_dependency_wait();
   const int pos = p.positions[row];
   int first_unit, units, lo, hi;
   decode_units(p, pos, first_unit, units, lo, hi);
   const int per_split = (units + p.max_splits - 1) / p.max_splits;
   const int count = (units + per_split - 1) / per_split;           // splits that have work
-  if (split >= count) return;
+  if (split >= count) {
+    srb_grid_dependency_wait();
+    return;
+  }
   const int unit_begin = first_unit + split * per_split;
   const int unit_end = min(first_unit + units, unit_begin + per_split);
   const int groups = p.n_q / p.n_kv;
@@ -103,7 +110,10 @@ decode_attention_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16
     }
     cp_async_commit();
   };
-  issue(unit_begin, 0);
+  const bool first_unit_is_old = (unit_begin + 1) * DEC_UNIT <= pos;
+  if (first_unit_is_old) issue(unit_begin, 0);
+  srb_grid_dependency_wait();
+  if (!first_unit_is_old) issue(unit_begin, 0);
 
   // Q fragments: rows of the tile are the query heads of this kv head; rows >= groups are zero
   unsigned qa[KSTEPS][4];

@@ -46,8 +46,9 @@ __global__ void qk_norm_rope_kv_kernel(const T* __restrict__ qkv, const float* _
                                        int interleaved, int n_q, int n_kv, int head_dim, int page_size,
                                        int num_pages, int heads_to_do, int vector_ok, int rounds, int* error_word) {
   extern __shared__ __align__(16) float staged_all[];  // ROPE_WARPS * head_dim floats
+  // The table of angles needs only the step's index arrays and constants: it is computed before
+  // the wait for the kernel ahead (whose product this kernel reads) and overlaps that kernel's end.
   srb_launch_dependents();
-  srb_grid_dependency_wait();
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int row = blockIdx.x;
   float* staged = staged_all + warp * head_dim;
@@ -62,6 +63,7 @@ __global__ void qk_norm_rope_kv_kernel(const T* __restrict__ qkv, const float* _
     const float pos = (float)positions[row];
     for (int i = threadIdx.x; i < (rotary_dim >> 1); i += blockDim.x) sincosf(pos * inv_freq[i], &sin_table[i], &cos_table[i]);
   }
+  srb_grid_dependency_wait();
   __syncthreads();
 #pragma unroll 1
   for (int round = 0; round < rounds; ++round) {
