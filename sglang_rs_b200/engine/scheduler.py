@@ -295,9 +295,9 @@ class Scheduler:
             if not entry.samples:
                 continue
             token = int(next(picks))
+            request.pending = max(0, request.pending - 1)
             if request.finished:
                 continue                     # it ended (stop token, abort) while this step was already running
-            request.pending = max(0, request.pending - 1)
             request.output_ids.append(token)
             stops = set(request.sampling.stop_token_ids) | set(self.config.default_stop_token_ids)
             reason = None

@@ -236,3 +236,124 @@ def test_random_workloads_finish_with_the_right_tokens(seed):
         assert r.finished and r.finish_reason == "length"
         assert r.output_ids == expected_output(r.prompt, r.sampling.max_new_tokens)
     assert all(a.free_count == a.num_pages for a in cache.allocators.values())
+
+
+# ------------------------------------------------------------------------------ steps that run ahead
+class FakeOverlappedEngine:
+    """The engine's overlapped loop with the model faked: a step is 'launched' (pages reserved and
+    committed, tokens computed but withheld), and its tokens reach the scheduler one call later."""
+
+    def __init__(self, scheduler, cache):
+        self.scheduler, self.cache = scheduler, cache
+        self.in_flight = None
+        self.ran_ahead = 0
+        self.rows_in_vain = 0
+
+    def launch(self, ahead):
+        entries = self.scheduler.schedule(ahead=ahead)
+        if not entries:
+            return None
+        before = {id(e.request): t for e, t in self.in_flight} if ahead else {}
+        tokens = []
+        for entry in entries:
+            handle = entry.request.handle
+            if entry.from_device:
+                assert ahead and entry.tokens == [-1] and entry.request.pending == 1
+                known = entry.request.tokens + [before[id(entry.request)]]      # what the device holds
+            else:
+                assert -1 not in entry.tokens
+                known = entry.request.tokens[:handle.length + len(entry.tokens)]
+            self.cache.reserve(handle, len(entry.tokens))
+            self.cache.commit(handle, len(entry.tokens))
+            tokens.append(next_token(known) if entry.samples else None)
+        for entry in entries:
+            if entry.samples:
+                entry.request.pending += 1
+        return list(zip(entries, tokens))
+
+    def step(self):
+        launched = None
+        if self.in_flight is not None:
+            running = len(self.scheduler.running)
+            if all(free >= running for free in self.cache.free_pages().values()):
+                launched = self.launch(ahead=True)
+                self.ran_ahead += launched is not None
+        outputs = []
+        if self.in_flight is not None:
+            entries = [e for e, _ in self.in_flight]
+            outputs = self.scheduler.process_outputs(entries, [t for _, t in self.in_flight if t is not None])
+            self.in_flight = None
+        if launched is None:
+            launched = self.launch(ahead=False)
+        else:
+            self.rows_in_vain += sum(e.request.finished for e, _ in launched)
+        self.in_flight = launched
+        self.cache.check_invariants()
+        return outputs
+
+
+@pytest.mark.parametrize("seed", range(6))
+def test_steps_that_run_ahead_give_the_same_tokens(seed):
+    """Requests of random lengths arrive over time; some stop on a stop token, so the step that ran
+    ahead computed a row in vain; pools are small, so some steps cannot run ahead and some requests
+    are preempted.  Every request ends with the tokens of the plain loop, and no page is lost."""
+    rng = random.Random(100 + seed)
+    stops = (5, 17, 60)
+    scheduler, cache = make(max_tokens=rng.choice([64, 96, 200]), page_size=rng.choice([2, 4, 8]),
+                            budget=rng.choice([7, 16, 33]), max_running=rng.choice([2, 4, 6]), stops=stops)
+    engine = FakeOverlappedEngine(scheduler, cache)
+    requests, got = [], {}
+    arrivals = sorted(rng.randrange(50) for _ in range(16))
+    step = 0
+    while arrivals or scheduler.has_work or engine.in_flight is not None:
+        while arrivals and arrivals[0] <= step:
+            arrivals.pop(0)
+            r = request(len(requests), [rng.randrange(97) for _ in range(rng.randrange(1, 28))],
+                        max_new_tokens=rng.randrange(1, 14), ignore_eos=rng.random() < 0.3)
+            requests.append(r)
+            scheduler.add_request(r)
+        for output in engine.step():
+            got.setdefault(output.request_id, []).extend(output.token_ids)
+        step += 1
+        assert step < 5000
+    for r in requests:
+        want = expected_output(r.prompt, r.sampling.max_new_tokens, () if r.sampling.ignore_eos else stops)
+        assert r.finished and r.output_ids == want and got.get(r.request_id, []) == want and r.pending == 0
+        assert r.finish_reason == ("stop" if want[-1] in stops and not r.sampling.ignore_eos else "length")
+    assert engine.ran_ahead > 0
+    assert all(a.free_count == a.num_pages for a in cache.allocators.values())
+
+
+def test_a_request_whose_pending_token_is_its_last_is_not_scheduled_ahead():
+    scheduler, cache = make(max_tokens=128)
+    engine = FakeOverlappedEngine(scheduler, cache)
+    a, b = request("a", range(6), max_new_tokens=2), request("b", range(9), max_new_tokens=4)
+    scheduler.add_request(a)
+    scheduler.add_request(b)
+    engine.step()                                            # both prompts; first tokens pending
+    assert a.pending == b.pending == 1 and not a.output_ids
+    engine.step()                                            # runs ahead: second token of each, the first arrives
+    assert [e.request.request_id for e, _ in engine.in_flight] == ["a", "b"]
+    assert len(a.output_ids) == 1 and a.pending == 1
+    engine.step()                                            # a's pending token is its last whatever it is: only b
+    assert [e.request.request_id for e, _ in engine.in_flight] == ["b"]
+    while scheduler.has_work or engine.in_flight is not None:
+        engine.step()
+    assert a.output_ids == expected_output(a.prompt, 2) and b.output_ids == expected_output(b.prompt, 4)
+    assert engine.rows_in_vain == 0
+
+
+def test_decode_split_counts_follow_the_shape_only():
+    """How many blocks share the keys of a (row, kv head) in the decode attention: a function of
+    rows, kv heads and the longest row; within the bound that sizes the scratch memory."""
+    from sglang_rs_b200 import ops
+    assert ops.decode_splits(64, 8, 2100) == 3           # 512 blocks would be 1.15 waves of 444
+    assert ops.decode_splits(8, 8, 2100) == 6            # 384 blocks: one wave
+    assert ops.decode_splits(1, 8, 2100) == 16           # as many as have two 64-key units each
+    assert ops.decode_splits(1, 8, 40) == 1
+    for rows in (1, 3, 8, 64, 200):
+        for n_kv in (1, 2, 8, 32):
+            for keys in (1, 64, 65, 1000, 5000, 40000):
+                splits = ops.decode_splits(rows, n_kv, keys)
+                assert 1 <= splits <= ops.decode_splits_bound(keys) <= ops.DECODE_MAX_SPLITS
+                assert splits == ops.decode_splits(rows, n_kv, keys)
