@@ -227,7 +227,7 @@ class Engine:
     def flush_cache(self) -> bool:
         """Possible only while nothing is queued or running, as in the reference
         (crates/sglang-srt/src/scheduler.rs:442-454)."""
-        if self.scheduler.has_work:
+        if self.scheduler.has_work or self._in_flight is not None:
             return False
         if self.cache.prefix_tree is not None:
             self.cache.prefix_tree.clear()
