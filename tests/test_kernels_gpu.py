@@ -432,6 +432,18 @@ def test_tcgen05_attention_of_prompt_portions(n_q, n_kv, d, page, window):
     close(run_tiled(case, scale, tensor_memory=True), expected_attention(case, scale), torch.bfloat16, "tcgen05 attention")
 
 
+@pytest.mark.parametrize("n_q,n_kv,d,page", [(4, 2, 128, 16), (3, 1, 64, 8)])
+def test_tcgen05_attention_with_maxima_that_keep_jumping(n_q, n_kv, d, page):
+    """Scores thirty times as wide as usual: a row's maximum jumps by far more than 2^8 from one
+    64-key block to the next, so the output in tensor memory is rescaled in many blocks, each time
+    after the product of the block before has landed (the kernel computes S of the next block
+    while it waits)."""
+    lengths, rows = (900, 260, 1500), (300, 260, 129)
+    case = paged_case(torch.bfloat16, n_q, n_kv, d, page, lengths, rows, None, seed=d + page)
+    scale = 30.0 / math.sqrt(d)
+    close(run_tiled(case, scale, tensor_memory=True), expected_attention(case, scale), torch.bfloat16, "jumping maxima")
+
+
 def test_tcgen05_attention_finds_a_far_key_and_respects_the_window_edge():
     case = paged_case(torch.bfloat16, 4, 2, 64, 16, (700, 530), (70, 3), None, seed=9, boost=(17, 3.0))
     scale = 1.0 / 8.0
