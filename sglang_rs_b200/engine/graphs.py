@@ -1,8 +1,8 @@
 """CUDA graphs for steps that hold decoded tokens only.
 
 A decode step is a few hundred small launches; replayed from a graph it costs one launch
-on the host.  A graph is captured per (row bucket, block-table width, key-split count per
-group) with every index array in one static device buffer that is refilled by one copy
+on the host.  A graph is captured per (row bucket, block-table width, key-split count and
+split length per group) with every index array in one static device buffer that is refilled by one copy
 before each replay.  Rows beyond the live ones are padding: token 0 at position 0 whose
 key and value go to the pool's spare page (the page after the last one the allocator
 owns), so they touch nothing that lives.
@@ -11,6 +11,7 @@ The kernels, their arithmetic and the split of the keys are those of the eager p
 """
 from __future__ import annotations
 
+from collections import OrderedDict
 from dataclasses import dataclass
 from typing import Dict, Hashable, List, Optional, Sequence, Tuple
 
@@ -41,12 +42,18 @@ class CapturedStep:
 
 class DecodeGraphs:
     MAX_ROWS = 256
+    #: floats of split scratch that all captured steps share (they replay one after another); keys are cut
+    #: into longer pieces, or into fewer blocks, until a step's partial results fit
+    SCRATCH_FLOATS = 16 << 20
+    #: captured steps kept; the one unused for longest goes first
+    MAX_CAPTURED = 48
 
     def __init__(self, model, cache, planner: StepPlanner):
         self.model, self.cache, self.planner = model, cache, planner
         self.device, self.dtype = planner.device, planner.dtype
-        self.captured: Dict[Hashable, CapturedStep] = {}
+        self.captured: "OrderedDict[Hashable, CapturedStep]" = OrderedDict()
         self.pool = None
+        self._scratch: Optional[Tuple[torch.Tensor, torch.Tensor]] = None
         self.replays = 0
         self.kernels_per_replay: Dict[Hashable, int] = {}
 
@@ -64,16 +71,25 @@ class DecodeGraphs:
         page_size = self.cache.page_size
         stride = bucket_of(max([len(e.handle.tables[key]) for e in entries for key in groups] + [1]), 8)
         positions = np.fromiter((e.handle.length for e in entries), dtype=np.int64, count=rows)
-        splits = []
+        splits, sizes = [], []
         for key in groups:
             window = self.cache.windows[key]
             begin = np.maximum(0, positions + 1 - window) if window else np.zeros_like(positions)
             size = StepPlanner.SPLIT_SIZE
-            splits.append(bucket_of(int((positions // size - begin // size + 1).max())))
-        key = (bucket, stride, tuple(splits))
+            while True:
+                count = bucket_of(int((positions // size - begin // size + 1).max()))
+                if count == 1 or bucket * count * max(self.planner._scratch_acc_width, 1) <= self.SCRATCH_FLOATS:
+                    break
+                size *= 2
+            splits.append(count)
+            sizes.append(size)
+        key = (bucket, stride, tuple(splits), tuple(sizes))
         step = self.captured.get(key)
         if step is None:
             step = self._prepare(key, groups)
+            while len(self.captured) > self.MAX_CAPTURED:
+                self.captured.popitem(last=False)
+        self.captured.move_to_end(key)
         if step.copied is not None:
             step.copied.synchronize()        # the staging buffer is free again once its last copy has run
         self._fill(step, entries, groups, bucket, stride, positions, page_size)
@@ -87,7 +103,7 @@ class DecodeGraphs:
             step.copied = torch.cuda.Event()
         step.copied.record()
         if step.graph is None:
-            self._capture(key, step, groups, bucket, stride, splits)
+            self._capture(key, step, groups, bucket, stride, splits, sizes)
         step.graph.replay()
         self.replays += 1
         ops.launch_count += self.kernels_per_replay[key]
@@ -100,7 +116,7 @@ class DecodeGraphs:
 
     # ------------------------------------------------------------------ buffers
     def _prepare(self, key, groups) -> CapturedStep:
-        bucket, stride, _ = key
+        bucket, stride = key[0], key[1]
         layout, offset = {}, 0
         for name, size in (("tokens", bucket), ("positions", bucket), ("row_request", bucket), ("cu_rows", bucket + 1),
                            ("state_slots", bucket), ("logit_rows", bucket), ("token_from", bucket)):
@@ -148,7 +164,7 @@ class DecodeGraphs:
                 slots[r] = pages[positions[r] // page_size] * page_size + positions[r] % page_size
 
     # ------------------------------------------------------------------ capture
-    def _context(self, step: CapturedStep, groups, bucket, stride, splits) -> Tuple[StepContext, torch.Tensor, list]:
+    def _context(self, step: CapturedStep, groups, bucket, stride, splits, sizes) -> Tuple[StepContext, torch.Tensor, list]:
         def part(name):
             begin, size = step.layout[name]
             return step.static[begin:begin + size]
@@ -156,22 +172,21 @@ class DecodeGraphs:
                           part("row_request"), part("cu_rows"), part("state_slots"), self.planner.error_word,
                           host_cu_rows=list(range(bucket + 1)), host_start_positions=[0] * bucket,
                           host_state_slots=[0] * bucket)
-        keep = []
+        if self._scratch is None:
+            width = max(self.planner._scratch_acc_width, 1)
+            ml = max(self.SCRATCH_FLOATS // width * max(self.planner._scratch_ml_width, 1), 1)
+            self._scratch = (torch.empty(self.SCRATCH_FLOATS, dtype=torch.float32, device=self.device),
+                             torch.empty(ml, dtype=torch.float32, device=self.device))
+        acc, ml = self._scratch
+        keep = [acc, ml]
         for g, key in enumerate(groups):
-            widest = max(splits[g], ops.decode_splits_bound(splits[g] * StepPlanner.SPLIT_SIZE))
-            acc = torch.empty(max(bucket * widest * self.planner._scratch_acc_width, 1), dtype=torch.float32,
-                              device=self.device)
-            ml = torch.empty(max(bucket * widest * self.planner._scratch_ml_width, 1), dtype=torch.float32,
-                             device=self.device)
-            keep += [acc, ml]
             ctx.paged[key] = PagedBatch(part(f"table{g}").view(bucket, stride), part(f"slots{g}"),
-                                        [AttentionLaunch(0, bucket, StepPlanner.SPLIT_SIZE, splits[g], None, None,
-                                                         splits[g] * StepPlanner.SPLIT_SIZE)], acc, ml,
-                                        self.planner.counters)
+                                        [AttentionLaunch(0, bucket, sizes[g], splits[g], None, None,
+                                                         splits[g] * sizes[g])], acc, ml, self.planner.counters)
         return ctx, part("logit_rows"), keep
 
-    def _capture(self, key, step: CapturedStep, groups, bucket, stride, splits) -> None:
-        ctx, logit_rows, keep = self._context(step, groups, bucket, stride, splits)
+    def _capture(self, key, step: CapturedStep, groups, bucket, stride, splits, sizes) -> None:
+        ctx, logit_rows, keep = self._context(step, groups, bucket, stride, splits, sizes)
         caches = [self.cache.layer_cache(i) for i in range(len(self.model.program))]
         current = torch.cuda.current_stream()
         side = torch.cuda.Stream()
