@@ -278,20 +278,18 @@ decode_attention_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16
   float* weights = stage_f;              // [groups][count + 1]: 2^(m_s - M) per split, then 1 / sum
   for (int head = warp; head < groups; head += DEC_WARPS) {
     const size_t first = ((size_t)row * p.n_q + (size_t)kv_head * groups + head) * p.max_splits;
+    // lane s holds split s (and s + 32, ...): maxima and sums go through the fixed butterfly of the warp,
+    // so their order does not depend on which block merges
     float m = -INFINITY;
     for (int sp = lane; sp < count; sp += 32) m = fmaxf(m, __ldcg(part_ml + (first + sp) * 2));
     m = srb_warp_max(m);
-    float l = 0.f;
-    for (int base = 0; base < count; base += 32) {      // sums in split order: lane order inside, chunks outside
-      const int sp = base + lane;
-      float w = 0.f, lw = 0.f;
-      if (sp < count) {
-        w = exp2f(__ldcg(part_ml + (first + sp) * 2) - m);
-        lw = __ldcg(part_ml + (first + sp) * 2 + 1) * w;
-        weights[head * (count + 1) + sp] = w;
-      }
-      for (int k = 0; k < 32; ++k) l += __shfl_sync(0xffffffffu, lw, k);
+    float lw = 0.f;
+    for (int sp = lane; sp < count; sp += 32) {
+      const float w = exp2f(__ldcg(part_ml + (first + sp) * 2) - m);
+      lw += __ldcg(part_ml + (first + sp) * 2 + 1) * w;
+      weights[head * (count + 1) + sp] = w;
     }
+    const float l = srb_warp_sum(lw);
     if (lane == 0) weights[head * (count + 1) + count] = 1.0f / l;
   }
   __syncthreads();
@@ -300,7 +298,14 @@ decode_attention_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16
     const size_t first = ((size_t)row * p.n_q + (size_t)kv_head * groups + head) * p.max_splits;
     const float* w = weights + head * (count + 1);
     float acc = 0.f;
-    for (int sp = 0; sp < count; ++sp) acc += __ldcg(part_acc + (first + sp) * D + e) * w[sp];
+    for (int base = 0; base < count; base += 8) {          // eight loads in flight, added in split order
+      float v[8];
+#pragma unroll
+      for (int j = 0; j < 8; ++j) v[j] = base + j < count ? __ldcg(part_acc + (first + base + j) * D + e) : 0.f;
+#pragma unroll
+      for (int j = 0; j < 8; ++j)
+        if (base + j < count) acc += v[j] * w[base + j];
+    }
     out[((size_t)row * p.n_q + (size_t)kv_head * groups + head) * D + e] = __float2bfloat16_rn(acc * w[count]);
   }
 }
