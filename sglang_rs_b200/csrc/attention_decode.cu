@@ -45,7 +45,10 @@ __device__ __forceinline__ void decode_units(const AttnParams& p, int pos, int& 
   units = (hi - 1) / DEC_UNIT - first_unit + 1;
 }
 
-template <int D>
+// CLUSTER: the blocks of a (row, kv head) form a thread-block cluster (at most 8 of them) and merge
+// their partial results through each other's shared memory; otherwise through global memory, where
+// the block that arrives last merges.
+template <int D, bool CLUSTER>
 __global__ void __launch_bounds__(DEC_WARPS * 32, 3)
 decode_attention_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __restrict__ k_pool,
                         const __nv_bfloat16* __restrict__ v_pool, float* __restrict__ part_acc,
@@ -70,12 +73,12 @@ decode_attention_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16
   decode_units(p, pos, first_unit, units, lo, hi);
   const int per_split = (units + p.max_splits - 1) / p.max_splits;
   const int count = (units + per_split - 1) / per_split;           // splits that have work
-  if (split >= count) {
+  if (!CLUSTER && split >= count) {
     srb_grid_dependency_wait();
     return;
   }
   const int unit_begin = first_unit + split * per_split;
-  const int unit_end = min(first_unit + units, unit_begin + per_split);
+  const int unit_end = min(first_unit + units, unit_begin + per_split);     // a block without work: begin >= end
   const int groups = p.n_q / p.n_kv;
   const int request = p.row_request[row];
   const int page_shift = (p.page_size & (p.page_size - 1)) == 0 ? __ffs(p.page_size) - 1 : -1;
@@ -110,10 +113,11 @@ decode_attention_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16
     }
     cp_async_commit();
   };
+  const bool has_work = unit_begin < unit_end;
   const bool first_unit_is_old = (unit_begin + 1) * DEC_UNIT <= pos;
-  if (first_unit_is_old) issue(unit_begin, 0);
+  if (has_work && first_unit_is_old) issue(unit_begin, 0);
   srb_grid_dependency_wait();
-  if (!first_unit_is_old) issue(unit_begin, 0);
+  if (has_work && !first_unit_is_old) issue(unit_begin, 0);
 
   // Q fragments: rows of the tile are the query heads of this kv head; rows >= groups are zero
   unsigned qa[KSTEPS][4];
@@ -240,6 +244,7 @@ decode_attention_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16
     }
   }
   __syncthreads();
+  float* mine = stage_f + (size_t)DEC_WARPS * groups * (D + 2);          // CLUSTER: this block's [head][D + 2]
   for (int i = threadIdx.x; i < groups * D; i += blockDim.x) {
     const int head = i / D, e = i % D;
     float m = -INFINITY;
@@ -253,12 +258,57 @@ decode_attention_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16
       acc += src[e] * weight;
       l += src[D + 1] * weight;
     }
+    if (CLUSTER) {
+      mine[head * (D + 2) + e] = acc;
+      if (e == 0) {
+        mine[head * (D + 2) + D] = m;      // in units of log2
+        mine[head * (D + 2) + D + 1] = l;
+      }
+      continue;
+    }
     const size_t slot = ((size_t)row * p.n_q + (size_t)kv_head * groups + head) * p.max_splits + split;
     part_acc[slot * D + e] = acc;
     if (e == 0) {
       part_ml[slot * 2] = m;             // in units of log2
       part_ml[slot * 2 + 1] = l;
     }
+  }
+  if (CLUSTER) {
+    // Every block of the cluster takes a slice of the (head, element) pairs and merges the blocks'
+    // results for it, in block order, reading the others' shared memory.
+    srb_cluster_sync();
+    const int blocks = p.max_splits;                       // = cluster size
+    const int total = groups * D;
+    const int per_block = (total + blocks - 1) / blocks;
+    const int begin = min(total, (int)srb_cluster_rank() * per_block), end = min(total, begin + per_block);
+    for (int i = begin + threadIdx.x; i < end; i += blockDim.x) {
+      const int head = i / D, e = i % D;
+      const float* base = mine + head * (D + 2);
+      float ms[8], ls[8], as[8];
+      float m = -INFINITY;
+#pragma unroll
+      for (int b = 0; b < 8; ++b) {
+        if (b < blocks) {
+          ms[b] = srb_load_peer_shared(base + D, b);
+          ls[b] = srb_load_peer_shared(base + D + 1, b);
+          as[b] = srb_load_peer_shared(base + e, b);
+          m = fmaxf(m, ms[b]);
+        }
+      }
+      float acc = 0.f, l = 0.f;
+#pragma unroll
+      for (int b = 0; b < 8; ++b) {
+        if (b < blocks) {
+          const float weight = ls[b] > 0.f ? exp2f(ms[b] - m) : 0.f;      // a block without keys adds nothing
+          acc += as[b] * weight;
+          l += ls[b] * weight;
+        }
+      }
+      out[((size_t)row * p.n_q + (size_t)kv_head * groups + head) * D + e] =
+          __float2bfloat16_rn(l > 0.f ? acc / l : 0.f);
+    }
+    srb_cluster_sync();                                    // nobody leaves while its memory may still be read
+    return;
   }
 
   // The block that arrives last at this (row, kv head) merges all splits, in split order, so
@@ -313,14 +363,22 @@ decode_attention_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16
 template <int D>
 static int launch_decode(const void* q, const void* k_pool, const void* v_pool, void* out, float* part_acc,
                          float* part_ml, int* counters, const DecodeParams& dp, int rows, cudaStream_t s) {
-  const size_t smem = (size_t)DEC_WARPS * DEC_STAGES * 2 * DEC_KEYS * D * sizeof(__nv_bfloat16);
+  const int groups = dp.a.n_q / dp.a.n_kv;
+  const size_t keys = (size_t)DEC_WARPS * DEC_STAGES * 2 * DEC_KEYS * D * sizeof(__nv_bfloat16);
+  // up to 8 blocks per (row, kv head) merge inside a cluster, when all blocks run at once (then the
+  // merge is the tail of the kernel; with several waves of blocks the placement of whole clusters costs
+  // more than it saves); the merge needs room for one more [head][D + 2]
+  const bool cluster = dp.a.max_splits > 1 && dp.a.max_splits <= 8 &&
+                       (long long)rows * dp.a.n_kv * dp.a.max_splits <= 3 * 148;
+  const size_t merge = (size_t)(DEC_WARPS + 1) * groups * (D + 2) * sizeof(float);
+  const size_t smem = cluster && merge > keys ? merge : keys;
+  auto kernel = cluster ? decode_attention_kernel<D, true> : decode_attention_kernel<D, false>;
   if (smem > 48 * 1024)
-    SRB_CUDA_CALL(cudaFuncSetAttribute(decode_attention_kernel<D>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                       (int)smem));
+    SRB_CUDA_CALL(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
   dim3 grid(dp.a.max_splits, dp.a.n_kv, rows);
-  SRB_CUDA_CALL(srb_launch(decode_attention_kernel<D>, grid, dim3(DEC_WARPS * 32), smem, s, (const __nv_bfloat16*)q,
-                           (const __nv_bfloat16*)k_pool, (const __nv_bfloat16*)v_pool, part_acc, part_ml,
-                           (__nv_bfloat16*)out, counters, dp));
+  SRB_CUDA_CALL(srb_launch_clustered(kernel, grid, dim3(DEC_WARPS * 32), smem, s, cluster ? (unsigned)dp.a.max_splits : 1u,
+                                     (const __nv_bfloat16*)q, (const __nv_bfloat16*)k_pool, (const __nv_bfloat16*)v_pool,
+                                     part_acc, part_ml, (__nv_bfloat16*)out, counters, dp));
   return SRB_OK;
 }
 

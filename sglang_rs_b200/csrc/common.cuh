@@ -110,18 +110,54 @@ static int srb_pdl_enabled = 0;
 __device__ __forceinline__ void srb_grid_dependency_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
 __device__ __forceinline__ void srb_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
 
+// `cluster_x` > 1 launches thread-block clusters of that many blocks along x (the grid's x is a multiple).
 template <typename... KernelArgs, typename... Args>
-static cudaError_t srb_launch(void (*kernel)(KernelArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream,
-                              Args... args) {
+static cudaError_t srb_launch_clustered(void (*kernel)(KernelArgs...), dim3 grid, dim3 block, size_t smem,
+                                        cudaStream_t stream, unsigned cluster_x, Args... args) {
   cudaLaunchConfig_t config = {};
   config.gridDim = grid;
   config.blockDim = block;
   config.dynamicSmemBytes = smem;
   config.stream = stream;
-  cudaLaunchAttribute attribute[1];
-  attribute[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
-  attribute[0].val.programmaticStreamSerializationAllowed = 1;
+  cudaLaunchAttribute attribute[2];
+  unsigned count = 0;
+  if (srb_pdl_enabled) {
+    attribute[count].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attribute[count].val.programmaticStreamSerializationAllowed = 1;
+    ++count;
+  }
+  if (cluster_x > 1) {
+    attribute[count].id = cudaLaunchAttributeClusterDimension;
+    attribute[count].val.clusterDim.x = cluster_x;
+    attribute[count].val.clusterDim.y = 1;
+    attribute[count].val.clusterDim.z = 1;
+    ++count;
+  }
   config.attrs = attribute;
-  config.numAttrs = srb_pdl_enabled ? 1 : 0;
+  config.numAttrs = count;
   return cudaLaunchKernelEx(&config, kernel, KernelArgs(args)...);
+}
+
+template <typename... KernelArgs, typename... Args>
+static cudaError_t srb_launch(void (*kernel)(KernelArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream,
+                              Args... args) {
+  return srb_launch_clustered(kernel, grid, block, smem, stream, 1u, args...);
+}
+
+// ---- thread-block clusters: rank, barrier, and loads from another block's shared memory ------------
+__device__ __forceinline__ unsigned srb_cluster_rank() {
+  unsigned r;
+  asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+  return r;
+}
+// every thread of every block of the cluster arrives; writes to shared memory before it are visible after it
+__device__ __forceinline__ void srb_cluster_sync() {
+  asm volatile("barrier.cluster.arrive.release.aligned;\nbarrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+__device__ __forceinline__ float srb_load_peer_shared(const float* mine, unsigned rank) {
+  unsigned local = (unsigned)__cvta_generic_to_shared(mine), remote;
+  float v;
+  asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(remote) : "r"(local), "r"(rank));
+  asm volatile("ld.shared::cluster.f32 %0, [%1];" : "=f"(v) : "r"(remote) : "memory");
+  return v;
 }

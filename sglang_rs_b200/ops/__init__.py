@@ -284,8 +284,11 @@ def decode_attention_takes(dtype: torch.dtype, n_q: int, n_kv: int, head_dim: in
 DECODE_MIN_UNITS = 2
 
 
-#: what a block costs beside its keys (set-up, the load of q, the merge), in 64-key units
+#: what a block costs beside its keys (set-up, the load of q, the merge), in 64-key units: up to
+#: DECODE_CLUSTER_SPLITS blocks merge inside a thread-block cluster, more go through global memory
 DECODE_BLOCK_OVERHEAD_UNITS = 3
+DECODE_GLOBAL_MERGE_UNITS = 3
+DECODE_CLUSTER_SPLITS = 8
 
 
 def decode_splits(rows: int, n_kv: int, max_keys: Optional[int] = None) -> int:
@@ -304,7 +307,8 @@ def decode_splits(rows: int, n_kv: int, max_keys: Optional[int] = None) -> int:
     best, best_cost = 1, None
     for splits in range(1, cap + 1):
         waves = -(-base * splits // DECODE_TARGET_BLOCKS)
-        cost = waves * (-(-units // splits) + DECODE_BLOCK_OVERHEAD_UNITS)
+        cost = waves * (-(-units // splits) + DECODE_BLOCK_OVERHEAD_UNITS) + (
+            DECODE_GLOBAL_MERGE_UNITS if splits > DECODE_CLUSTER_SPLITS else 0)
         if best_cost is None or cost < best_cost:
             best, best_cost = splits, cost
     return best

@@ -349,7 +349,7 @@ def test_decode_split_counts_follow_the_shape_only():
     from sglang_rs_b200 import ops
     assert ops.decode_splits(64, 8, 2100) == 3           # 512 blocks would be 1.15 waves of 444
     assert ops.decode_splits(8, 8, 2100) == 6            # 384 blocks: one wave
-    assert ops.decode_splits(1, 8, 2100) == 11           # three units each; more blocks would not shorten them
+    assert ops.decode_splits(1, 8, 2100) == 7            # five units each, merged inside a cluster
     assert ops.decode_splits(1, 8, 40) == 1
     for rows in (1, 3, 8, 64, 200):
         for n_kv in (1, 2, 8, 32):
