@@ -376,7 +376,7 @@ static int launch_decode(const void* q, const void* k_pool, const void* v_pool, 
   if (smem > 48 * 1024)
     SRB_CUDA_CALL(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
   dim3 grid(dp.a.max_splits, dp.a.n_kv, rows);
-  SRB_CUDA_CALL(srb_launch_clustered(kernel, grid, dim3(DEC_WARPS * 32), smem, s, cluster ? (unsigned)dp.a.max_splits : 1u,
+  SRB_CUDA_CALL(srb_launch_clustered(kernel, grid, dim3(DEC_WARPS * 32), smem, s, dim3(cluster ? dp.a.max_splits : 1, 1, 1),
                                      (const __nv_bfloat16*)q, (const __nv_bfloat16*)k_pool, (const __nv_bfloat16*)v_pool,
                                      part_acc, part_ml, (__nv_bfloat16*)out, counters, dp));
   return SRB_OK;

@@ -110,10 +110,10 @@ static int srb_pdl_enabled = 0;
 __device__ __forceinline__ void srb_grid_dependency_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
 __device__ __forceinline__ void srb_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
 
-// `cluster_x` > 1 launches thread-block clusters of that many blocks along x (the grid's x is a multiple).
+// A cluster dimension > 1 launches thread-block clusters of that shape (the grid is a multiple of it).
 template <typename... KernelArgs, typename... Args>
 static cudaError_t srb_launch_clustered(void (*kernel)(KernelArgs...), dim3 grid, dim3 block, size_t smem,
-                                        cudaStream_t stream, unsigned cluster_x, Args... args) {
+                                        cudaStream_t stream, dim3 cluster, Args... args) {
   cudaLaunchConfig_t config = {};
   config.gridDim = grid;
   config.blockDim = block;
@@ -126,11 +126,11 @@ static cudaError_t srb_launch_clustered(void (*kernel)(KernelArgs...), dim3 grid
     attribute[count].val.programmaticStreamSerializationAllowed = 1;
     ++count;
   }
-  if (cluster_x > 1) {
+  if (cluster.x * cluster.y * cluster.z > 1) {
     attribute[count].id = cudaLaunchAttributeClusterDimension;
-    attribute[count].val.clusterDim.x = cluster_x;
-    attribute[count].val.clusterDim.y = 1;
-    attribute[count].val.clusterDim.z = 1;
+    attribute[count].val.clusterDim.x = cluster.x;
+    attribute[count].val.clusterDim.y = cluster.y;
+    attribute[count].val.clusterDim.z = cluster.z;
     ++count;
   }
   config.attrs = attribute;
@@ -141,7 +141,7 @@ static cudaError_t srb_launch_clustered(void (*kernel)(KernelArgs...), dim3 grid
 template <typename... KernelArgs, typename... Args>
 static cudaError_t srb_launch(void (*kernel)(KernelArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream,
                               Args... args) {
-  return srb_launch_clustered(kernel, grid, block, smem, stream, 1u, args...);
+  return srb_launch_clustered(kernel, grid, block, smem, stream, dim3(1, 1, 1), args...);
 }
 
 // ---- thread-block clusters: rank, barrier, and loads from another block's shared memory ------------

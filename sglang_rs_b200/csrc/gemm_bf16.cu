@@ -15,7 +15,10 @@
 // halves of the accumulator meet through shared memory and only the product is written; and
 // float partials per K split, [split][token][feature], which
 // the consumer adds in split order (few tokens cannot fill 148 SMs with 128-row blocks alone,
-// so K is cut; the cut depends on the shape only).
+// so K is cut; the cut depends on the shape only); and the sum of the K splits added to a float
+// tensor in place (the residual stream): the up to 8 blocks of a tile form a thread-block cluster,
+// leave their partial tiles in shared memory and each adds a slice of the tile, over all blocks in
+// block order, to the tensor.
 //
 // Weight layout and meaning as the reference's projection: row-major [out, in],
 // y[o] = sum_i x[i] W[o, i] (crates/sglang-kernel/src/cpu.rs:73-108), bfloat16 inputs with
@@ -41,6 +44,7 @@ SRB_DEFINE_PDL_SWITCH()
 #define EPI_F32 1
 #define EPI_SILU 2
 #define EPI_PARTIAL 3
+#define EPI_ADD 4          // out (float) += sum over the K splits, reduced inside a cluster
 
 // Instruction descriptor: D float, A and B bfloat16, both K-major, M = 128, N = tokens.
 __host__ __device__ constexpr unsigned instruction_descriptor(int n) {
@@ -216,6 +220,10 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constan
           }
         }
         asm volatile("bar.sync 1, 128;" ::: "memory");       // the buffer is reused by the next 16 tokens
+      } else if (EPI == EPI_ADD) {
+        // this block's partial tile as [token][128 features] floats over the idle pipeline stages
+#pragma unroll
+        for (int j = 0; j < 16; ++j) exchange[(c + j) * GEMM_BLOCK_F + quarter * 32 + lane] = acc[j];
       } else if (ok && feature < args.features) {
 #pragma unroll
         for (int j = 0; j < 16; ++j) {
@@ -232,6 +240,28 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constan
       }
     }
     tc_fence_before();
+  }
+  if (EPI == EPI_ADD) {
+    // The blocks of the cluster hold the K splits of one tile.  Block r adds slice r of the tile:
+    // the sum over all blocks, in block order, goes onto the float tensor (each element once).
+    const float* tile = reinterpret_cast<const float*>(smem);
+    srb_cluster_sync();
+    if (warp >= 2) {
+      const int blocks = gridDim.z;                          // = cluster size
+      const int live_tokens = min(BLOCK_T, args.tokens - token0);
+      const int total = max(live_tokens, 0) * GEMM_BLOCK_F;
+      const int per_block = (total + blocks - 1) / blocks;
+      const int begin = min(total, (int)srb_cluster_rank() * per_block), end = min(total, begin + per_block);
+      for (int i = begin + (int)threadIdx.x - 64; i < end; i += GEMM_THREADS - 64) {
+        const int token = i / GEMM_BLOCK_F, f = i % GEMM_BLOCK_F;
+        if (feature0 + f >= args.features) continue;
+        float sum = 0.f;
+        for (int b = 0; b < blocks; ++b) sum += srb_load_peer_shared(tile + i, b);
+        float* dst = reinterpret_cast<float*>(args.out) + (size_t)(token0 + token) * args.ldo + feature0 + f;
+        *dst += sum;
+      }
+    }
+    srb_cluster_sync();                                      // nobody leaves while its tile may still be read
   }
   __syncthreads();
   if (threadIdx.x == 0 && abort_flag) atomicOr(args.error_word, SRB_FLAG_WAIT_TIMEOUT);
@@ -289,7 +319,8 @@ static int launch_gemm(const CUtensorMap& map_w, const CUtensorMap& map_x, const
   SRB_CUDA_CALL(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
   dim3 grid((args.tokens + BLOCK_T - 1) / BLOCK_T, (args.features + FEATURES_PER_BLOCK - 1) / FEATURES_PER_BLOCK, splits);
   if (grid.y > 65535) SRB_FAIL("gemm_bf16: %d features exceed one launch", args.features);
-  SRB_CUDA_CALL(srb_launch(kernel, grid, dim3(GEMM_THREADS), smem, s, map_w, map_x, args));
+  SRB_CUDA_CALL(srb_launch_clustered(kernel, grid, dim3(GEMM_THREADS), smem, s,
+                                     dim3(1, 1, EPI == EPI_ADD ? splits : 1), map_w, map_x, args));
   return SRB_OK;
 }
 
@@ -319,6 +350,8 @@ extern "C" int srb_gemm_bf16_block_tokens(int tokens, int mode) {
 // mode 2: w stacks gate rows [0, features) and up rows [up_row_offset, up_row_offset + features);
 //         out bf16 [tokens, ldo] = silu(x gate^T) * (x up^T).
 // mode 3: `splits` partial sums over K as float [splits, tokens, ldo]; the caller adds them in order.
+// mode 4: out float [tokens, ldo] += x w^T, K cut into `splits` (at most 8) blocks that form a cluster and add
+//         their sums in block order.
 extern "C" int srb_gemm_bf16(const void* x, const void* w, void* out, int tokens, int features, int k, int ldx,
                              int ldw, int ldo, int rows_of_w, int up_row_offset, int mode, int splits,
                              int* error_word, void* stream) {
@@ -327,14 +360,15 @@ extern "C" int srb_gemm_bf16(const void* x, const void* w, void* out, int tokens
     SRB_FAIL("gemm_bf16: inner size %d and the row pitches %d, %d must be positive multiples of 8 (16-byte rows "
              "for TMA)", k, ldx, ldw);
   if (((uintptr_t)x | (uintptr_t)w) & 15) SRB_FAIL("gemm_bf16: operands must be 16-byte aligned");
-  if (mode < 0 || mode > 3) SRB_FAIL("gemm_bf16: unknown mode %d", mode);
+  if (mode < 0 || mode > 4) SRB_FAIL("gemm_bf16: unknown mode %d", mode);
   if (ldo < features) SRB_FAIL("gemm_bf16: output pitch %d is smaller than %d features", ldo, features);
   if (mode == EPI_SILU && up_row_offset + features > rows_of_w)
     SRB_FAIL("gemm_bf16: the up rows %d..%d lie outside the %d rows of w", up_row_offset, up_row_offset + features,
              rows_of_w);
   if (mode != EPI_SILU && features > rows_of_w) SRB_FAIL("gemm_bf16: %d features exceed %d rows of w", features, rows_of_w);
   const int total_k_blocks = (k + GEMM_BLOCK_K - 1) / GEMM_BLOCK_K;
-  if (mode != EPI_PARTIAL) splits = 1;
+  if (mode != EPI_PARTIAL && mode != EPI_ADD) splits = 1;
+  if (mode == EPI_ADD && splits > 8) SRB_FAIL("gemm_bf16: %d splits exceed a cluster of 8 blocks", splits);
   if (splits < 1 || splits > total_k_blocks) SRB_FAIL("gemm_bf16: %d splits do not fit %d blocks of K", splits, total_k_blocks);
   const int block_t = srb_gemm_bf16_block_tokens(tokens, mode);
 
@@ -355,6 +389,7 @@ extern "C" int srb_gemm_bf16(const void* x, const void* w, void* out, int tokens
     case EPI_BF16: return dispatch_tokens<EPI_BF16>(block_t, map_w, map_x, args, splits, s);
     case EPI_F32: return dispatch_tokens<EPI_F32>(block_t, map_w, map_x, args, splits, s);
     case EPI_SILU: return dispatch_tokens<EPI_SILU>(block_t, map_w, map_x, args, 1, s);
+    case EPI_ADD: return dispatch_tokens<EPI_ADD>(block_t, map_w, map_x, args, splits, s);
     default: return dispatch_tokens<EPI_PARTIAL>(block_t, map_w, map_x, args, splits, s);
   }
 }

@@ -490,17 +490,25 @@ def gate_up_silu(x: torch.Tensor, weight: torch.Tensor, inner: int,
     return act
 
 
-GEMM_MODES = {"bf16": 0, "f32": 1, "silu": 2, "partial": 3}
+GEMM_MODES = {"bf16": 0, "f32": 1, "silu": 2, "partial": 3, "add": 4}
+#: the blocks of a thread-block cluster: at most this many K splits add their sums inside the kernel
+GEMM_CLUSTER_SPLITS = 8
 
 
 def gemm_bf16(x: torch.Tensor, w: torch.Tensor, error_word: torch.Tensor, *, mode: str = "bf16",
-              features: Optional[int] = None, up_row_offset: int = 0, splits: int = 1) -> torch.Tensor:
+              features: Optional[int] = None, up_row_offset: int = 0, splits: int = 1,
+              out: Optional[torch.Tensor] = None) -> torch.Tensor:
     """y = x @ w^T on tcgen05 tensor cores (bfloat16 in, 32-bit accumulation).
 
     x [tokens, k], w [rows, k], k a multiple of 8.  ``mode``: ``bf16`` / ``f32`` store
     [tokens, features]; ``silu`` treats w as gate rows [0, features) stacked over up rows
     [up_row_offset, up_row_offset + features) and stores silu(gate) * up; ``partial`` stores
-    ``splits`` float partial sums [splits, tokens, features] that the consumer adds in order."""
+    ``splits`` float partial sums [splits, tokens, features] that the consumer adds in order;
+    ``add`` adds the product to ``out`` (float32 [tokens, features], e.g. the residual stream) in
+    place, K cut into at most ``GEMM_CLUSTER_SPLITS`` blocks that sum inside the kernel in block order.
+    (The engine's decode steps do not use ``add``: measured at Qwen3-8B sizes, partial sums that the
+    next norm kernel adds are quicker, 3.22 / 3.48 / 7.21 ms per step at batch 1 / 8 / 64 against
+    3.37 / 3.52 / 7.69 ms, because clusters of 8 blocks start later and end with two cluster barriers.)"""
     _need(x, "x", torch.bfloat16); _need(w, "w", torch.bfloat16)
     tokens, k = x.shape
     rows = w.shape[0]
@@ -509,13 +517,21 @@ def gemm_bf16(x: torch.Tensor, w: torch.Tensor, error_word: torch.Tensor, *, mod
     if features is None:
         features = rows
     code = GEMM_MODES[mode]
+    pitch = features
     if mode == "partial":
         out = torch.empty((splits, tokens, features), dtype=torch.float32, device=x.device)
+    elif mode == "add":
+        if out is None or not out.is_cuda or out.dtype != torch.float32 or out.dim() != 2 or out.stride(1) != 1:
+            raise KernelError("gemm_bf16: the tensor added to must be a float32 CUDA matrix with dense rows")
+        if out.shape[0] != tokens or out.shape[1] != features or not 1 <= splits <= GEMM_CLUSTER_SPLITS:
+            raise KernelError("gemm_bf16: the tensor added to must be [tokens, features], the splits at most "
+                              f"{GEMM_CLUSTER_SPLITS}")
+        pitch = out.stride(0)
     else:
         splits = 1
         out = torch.empty((tokens, features), dtype=torch.float32 if mode == "f32" else torch.bfloat16, device=x.device)
     lib = load_library("gemm_bf16")
-    _check(lib, lib.srb_gemm_bf16(_ptr(x), _ptr(w), _ptr(out), tokens, features, k, x.stride(0), w.stride(0), features,
+    _check(lib, lib.srb_gemm_bf16(_ptr(x), _ptr(w), _ptr(out), tokens, features, k, x.stride(0), w.stride(0), pitch,
                                   rows, int(up_row_offset), code, int(splits), _ptr(error_word), _stream()))
     return out
 

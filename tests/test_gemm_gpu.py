@@ -47,6 +47,38 @@ def test_partial_sums_over_k(tokens, features, k, splits):
     assert float(parts[-1].abs().max()) > 0        # the last split did its share
 
 
+@pytest.mark.parametrize("tokens,features,k,splits", [(1, 128, 64, 1), (8, 4096, 4096, 8), (5, 200, 1000, 3), (33, 384, 1000, 8),
+                                                      (64, 70, 328, 2), (128, 257, 520, 5), (100, 300, 200, 4)])
+def test_product_added_to_a_float_tensor_inside_a_cluster(tokens, features, k, splits):
+    """The K splits of a tile form a thread-block cluster and add their sum, in block order, onto a
+    float tensor in place (the residual stream): against the 64-bit product, twice in a row (the
+    second call adds again), and the same bits every time."""
+    x, w = operands(tokens, features, k, seed=11 + tokens)
+    g = torch.Generator().manual_seed(3)
+    start = torch.randn(tokens, features, generator=g)
+    word = ops.new_error_word(DEV)
+    want = pm.plain_linear(x.double(), w.double())
+    into = start.to(DEV)
+    ops.gemm_bf16(x.to(DEV), w.to(DEV), word, mode="add", splits=splits, out=into)
+    ops.raise_on_error_word(word)
+    scale = float(want.abs().max())
+    assert float((into.double().cpu() - (start.double() + want)).abs().max()) < 1e-5 * scale
+    first = into.clone()
+    ops.gemm_bf16(x.to(DEV), w.to(DEV), word, mode="add", splits=splits, out=into)
+    assert float((into.double().cpu() - (start.double() + 2 * want)).abs().max()) < 2e-5 * scale
+    again = start.to(DEV)
+    ops.gemm_bf16(x.to(DEV), w.to(DEV), word, mode="add", splits=splits, out=again)
+    assert torch.equal(again, first)
+    # a tensor with a wider row pitch (a view of a larger buffer) is taken; other columns stay
+    wide = torch.zeros(tokens, features + 24, device=DEV)
+    ops.gemm_bf16(x.to(DEV), w.to(DEV), word, mode="add", splits=splits, out=wide[:, :features])
+    ops.raise_on_error_word(word)
+    assert float(wide[:, features:].abs().max()) == 0.0
+    assert float((wide[:, :features].double().cpu() - want).abs().max()) < 1e-5 * scale
+    with pytest.raises(ops.KernelError, match="at most"):
+        ops.gemm_bf16(x.to(DEV), w.to(DEV), word, mode="add", splits=9, out=into)
+
+
 @pytest.mark.parametrize("tokens,inner,k", [(1, 128, 64), (8, 200, 72), (70, 256, 512), (129, 130, 200)])
 def test_gate_up_with_silu_epilogue(tokens, inner, k):
     x, w = operands(tokens, inner, k, seed=11, rows=2 * inner)
