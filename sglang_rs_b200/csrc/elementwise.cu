@@ -72,6 +72,23 @@ __global__ void add_rmsnorm_kernel(float* __restrict__ residual, const T* __rest
     dst[i] = srb_from_float<T>(staged[i] * inv * weight[i]);
 }
 
+
+// four consecutive values in one access (the address is a multiple of 4 elements)
+__device__ __forceinline__ float4 load4(const float* p) { return *reinterpret_cast<const float4*>(p); }
+__device__ __forceinline__ float4 load4(const __nv_bfloat16* p) {
+  const uint2 raw = *reinterpret_cast<const uint2*>(p);
+  const float2 a = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&raw.x));
+  const float2 b = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&raw.y));
+  return make_float4(a.x, a.y, b.x, b.y);
+}
+__device__ __forceinline__ void store4(float* p, float4 v) { *reinterpret_cast<float4*>(p) = v; }
+__device__ __forceinline__ void store4(__nv_bfloat16* p, float4 v) {
+  uint2 raw;
+  *reinterpret_cast<__nv_bfloat162*>(&raw.x) = __floats2bfloat162_rn(v.x, v.y);
+  *reinterpret_cast<__nv_bfloat162*>(&raw.y) = __floats2bfloat162_rn(v.z, v.w);
+  *reinterpret_cast<uint2*>(p) = raw;
+}
+
 // The same for widths that are a multiple of 4 and fit 4 * ITER values per thread: the row
 // stays in registers, every load of a thread is issued before the first use (the row is
 // small and the kernel is bound by latency, not by bandwidth), and the additions keep the
@@ -96,10 +113,8 @@ add_rmsnorm_vec_kernel(float* __restrict__ residual, const T* __restrict__ delta
     if (i < width) {
       x[it] = *reinterpret_cast<const float4*>(residual + src + i);
       if (delta) {
-        x[it].x += srb_to_float(delta[src + i]);
-        x[it].y += srb_to_float(delta[src + i + 1]);
-        x[it].z += srb_to_float(delta[src + i + 2]);
-        x[it].w += srb_to_float(delta[src + i + 3]);
+        const float4 d = load4(delta + src + i);
+        x[it].x += d.x; x[it].y += d.y; x[it].z += d.z; x[it].w += d.w;
       }
 #pragma unroll 4
       for (int part = 0; part < num_parts; ++part) {
@@ -118,10 +133,7 @@ add_rmsnorm_vec_kernel(float* __restrict__ residual, const T* __restrict__ delta
     const int i = (it * blockDim.x + threadIdx.x) * 4;
     if (i < width) {
       const float4 w = *reinterpret_cast<const float4*>(weight + i);
-      dst[i] = srb_from_float<T>(x[it].x * inv * w.x);
-      dst[i + 1] = srb_from_float<T>(x[it].y * inv * w.y);
-      dst[i + 2] = srb_from_float<T>(x[it].z * inv * w.z);
-      dst[i + 3] = srb_from_float<T>(x[it].w * inv * w.w);
+      store4(dst + i, make_float4(x[it].x * inv * w.x, x[it].y * inv * w.y, x[it].z * inv * w.z, x[it].w * inv * w.w));
     }
   }
 }
@@ -156,7 +168,8 @@ __global__ void silu_mul_bf16x8_kernel(const __nv_bfloat16* __restrict__ gate_up
 #pragma unroll
     for (int j = 0; j < 4; ++j) {
       const float2 g = __bfloat1622float2(g2[j]), u = __bfloat1622float2(u2[j]);
-      o2[j] = __floats2bfloat162_rn(g.x / (1.0f + expf(-g.x)) * u.x, g.y / (1.0f + expf(-g.y)) * u.y);
+      // the result is rounded to bfloat16 (8 bits): the hardware's exponential and division are exact enough
+      o2[j] = __floats2bfloat162_rn(__fdividef(g.x, 1.0f + __expf(-g.x)) * u.x, __fdividef(g.y, 1.0f + __expf(-g.y)) * u.y);
     }
     *reinterpret_cast<uint4*>(out + row * inner + col) = o4;
   }
@@ -199,7 +212,7 @@ static int launch_add_rmsnorm(float* residual, const void* delta, const float* d
                               int width, float eps, int write_residual, cudaStream_t s) {
   // widths that are a multiple of 4 (so float4 accesses stay aligned) and fit the registers
   const bool aligned = width % 4 == 0 && (((uintptr_t)residual | (uintptr_t)delta_parts | (uintptr_t)weight) & 15) == 0 &&
-                       part_stride % 4 == 0;
+                       (((uintptr_t)delta | (uintptr_t)out) & (4 * sizeof(T) - 1)) == 0 && part_stride % 4 == 0;
   if (aligned && width <= 4 * 1024 * 2) {
     int threads = ((width / 4 + 31) / 32) * 32;
     if (threads > 1024) threads = 1024;

@@ -167,47 +167,68 @@ __global__ void qk_norm_rope_kv_kernel(const T* __restrict__ qkv, const float* _
 }
 
 
-// Many rows (256 and more), head_dim 128, rotation of the whole head in half-split pairs: one block per row, every
-// warp takes several heads of the row and keeps a head in registers (lane l holds elements 4l..4l+3,
-// its rotation partner sits in lane l ^ 16), so a head costs one load, two shuffles' worth of
-// exchange and one store.  Same arithmetic as the kernel above.
+// Many rows (256 and more), head_dim 128, rotation of the whole head in half-split pairs, the
+// projection in one tensor: one block per row, every warp takes several heads of the row and keeps a
+// head in registers (lane l holds elements 4l..4l+3, its rotation partner sits in lane l ^ 16), so a
+// head costs one load, one exchange and one store; v heads are copied as they are.  Same arithmetic
+// as the kernel above.
 #define ROW_WARPS 8
 template <typename T>
+__device__ __forceinline__ float4 load_head4(const T* p) {
+  if (sizeof(T) == 2) {
+    const uint2 raw = *reinterpret_cast<const uint2*>(p);
+    const float2 a = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&raw.x));
+    const float2 b = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&raw.y));
+    return make_float4(a.x, a.y, b.x, b.y);
+  }
+  return *reinterpret_cast<const float4*>(p);
+}
+template <typename T>
+__device__ __forceinline__ void store_head4(T* p, float4 x) {
+  if (sizeof(T) == 2) {
+    uint2 raw;
+    *reinterpret_cast<__nv_bfloat162*>(&raw.x) = __floats2bfloat162_rn(x.x, x.y);
+    *reinterpret_cast<__nv_bfloat162*>(&raw.y) = __floats2bfloat162_rn(x.z, x.w);
+    *reinterpret_cast<uint2*>(p) = raw;
+  } else {
+    *reinterpret_cast<float4*>(p) = x;
+  }
+}
+// norm (if a weight is given) and rotation of the four values this lane holds of one head
+__device__ __forceinline__ float4 norm_and_rotate(float4 x, bool has_norm, float4 w, float eps, bool rotate, float4 cs,
+                                                  float4 sn, bool first_half) {
+  if (has_norm) {
+    const float total = srb_warp_sum(sum_squares4(x));
+    const float inv = __frsqrt_rn(total * (1.0f / 128.0f) + eps);
+    x = make_float4(normed(x.x, inv, w.x), normed(x.y, inv, w.y), normed(x.z, inv, w.z), normed(x.w, inv, w.w));
+  }
+  if (rotate) {
+    float4 other;
+    other.x = __shfl_xor_sync(0xffffffffu, x.x, 16); other.y = __shfl_xor_sync(0xffffffffu, x.y, 16);
+    other.z = __shfl_xor_sync(0xffffffffu, x.z, 16); other.w = __shfl_xor_sync(0xffffffffu, x.w, 16);
+    if (first_half)
+      x = make_float4(rotate_first(x.x, other.x, cs.x, sn.x), rotate_first(x.y, other.y, cs.y, sn.y),
+                      rotate_first(x.z, other.z, cs.z, sn.z), rotate_first(x.w, other.w, cs.w, sn.w));
+    else
+      x = make_float4(rotate_second(other.x, x.x, cs.x, sn.x), rotate_second(other.y, x.y, cs.y, sn.y),
+                      rotate_second(other.z, x.z, cs.z, sn.z), rotate_second(other.w, x.w, cs.w, sn.w));
+  }
+  return x;
+}
+
+template <typename T>
 __global__ void __launch_bounds__(ROW_WARPS * 32)
-qk_norm_rope_kv_row_kernel(const T* __restrict__ qkv, const float* __restrict__ qkv_parts, int num_parts,
-                           size_t part_stride, int qkv_stride, T* __restrict__ q_out, T* __restrict__ k_pool,
+qk_norm_rope_kv_row_kernel(const T* __restrict__ qkv, int qkv_stride, T* __restrict__ q_out, T* __restrict__ k_pool,
                            T* __restrict__ v_pool, const int* __restrict__ positions, const int* __restrict__ slots,
                            const float* __restrict__ q_norm, const float* __restrict__ k_norm, float eps,
                            const float* __restrict__ inv_freq, const float* __restrict__ angles, int n_q, int n_kv,
-                           int page_size, int num_pages, int heads_to_do, int* error_word) {
+                           int page_size, int num_pages, int* error_word) {
   constexpr int D = 128, HALF = 64;
   __shared__ __align__(16) float cos_table[HALF], sin_table[HALF];
   srb_launch_dependents();
-  srb_grid_dependency_wait();
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int row = blockIdx.x;
   const bool rotate = inv_freq || angles;
-  // a head's values, four per lane; the loads of the warp's next two heads are in flight while this one is worked on
-  auto load_head = [&](int head) {
-    const size_t src_offset = (size_t)row * qkv_stride + (size_t)head * D + lane * 4;
-    float4 x = make_float4(0.f, 0.f, 0.f, 0.f);
-    if (head >= heads_to_do) return x;
-    if (num_parts > 0) {
-      for (int part = 0; part < num_parts; ++part) {
-        const float4 d = *reinterpret_cast<const float4*>(qkv_parts + part * part_stride + src_offset);
-        x.x += d.x; x.y += d.y; x.z += d.z; x.w += d.w;
-      }
-    } else if (sizeof(T) == 2) {
-      const uint2 raw = *reinterpret_cast<const uint2*>(qkv + src_offset);
-      const float2 a = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&raw.x));
-      const float2 b = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&raw.y));
-      x = make_float4(a.x, a.y, b.x, b.y);
-    } else {
-      x = *reinterpret_cast<const float4*>(qkv + src_offset);
-    }
-    return x;
-  };
-  float4 next = load_head(warp), after_next = load_head(warp + ROW_WARPS);
   if (threadIdx.x < HALF) {
     if (angles) {
       sincosf(angles[(size_t)row * HALF + threadIdx.x], &sin_table[threadIdx.x], &cos_table[threadIdx.x]);
@@ -215,6 +236,14 @@ qk_norm_rope_kv_row_kernel(const T* __restrict__ qkv, const float* __restrict__ 
       sincosf((float)positions[row] * inv_freq[threadIdx.x], &sin_table[threadIdx.x], &cos_table[threadIdx.x]);
     }
   }
+  int slot = 0;
+  bool slot_ok = true;
+  if (slots) {
+    slot = slots[row];
+    slot_ok = slot >= 0 && slot < num_pages * page_size;
+    if (!slot_ok && threadIdx.x == 0) atomicOr(error_word, SRB_FLAG_BAD_SLOT);
+  }
+  srb_grid_dependency_wait();
   __syncthreads();
   const int pair0 = (lane & 15) * 4;                      // the four pairs this lane takes part in
   float4 cs = make_float4(1.f, 1.f, 1.f, 1.f), sn = make_float4(0.f, 0.f, 0.f, 0.f);
@@ -223,58 +252,37 @@ qk_norm_rope_kv_row_kernel(const T* __restrict__ qkv, const float* __restrict__ 
     sn = *reinterpret_cast<const float4*>(sin_table + pair0);
   }
   const bool first_half = lane < 16;
-  int slot = 0;
-  bool slot_ok = true;
-  if (slots) {
-    slot = slots[row];
-    slot_ok = slot >= 0 && slot < num_pages * page_size;
-    if (!slot_ok && threadIdx.x == 0) atomicOr(error_word, SRB_FLAG_BAD_SLOT);
+  const float4 one = make_float4(1.f, 1.f, 1.f, 1.f);
+  const T* src = qkv + (size_t)row * qkv_stride + lane * 4;
+  // q heads
+  {
+    const float4 w = q_norm ? *reinterpret_cast<const float4*>(q_norm + lane * 4) : one;
+    T* dst = q_out + (size_t)row * n_q * D + lane * 4;
+#pragma unroll 2
+    for (int head = warp; head < n_q; head += ROW_WARPS)
+      store_head4(dst + head * D, norm_and_rotate(load_head4(src + head * D), q_norm != nullptr, w, eps, rotate, cs, sn,
+                                                  first_half));
   }
+  if (!slots || !slot_ok) return;
   // where the row's k and v go: element offset of kv head 0, and the step from one kv head to the next
   const size_t kv_base = ((size_t)(slot / page_size) * n_kv * page_size + (slot % page_size)) * D + lane * 4;
   const size_t kv_step = (size_t)page_size * D;
-  T* const q_dst = q_out + (size_t)row * n_q * D + lane * 4;
-  const float4 wq = q_norm ? *reinterpret_cast<const float4*>(q_norm + lane * 4) : make_float4(1.f, 1.f, 1.f, 1.f);
-  const float4 wk = k_norm ? *reinterpret_cast<const float4*>(k_norm + lane * 4) : make_float4(1.f, 1.f, 1.f, 1.f);
-#pragma unroll 1
-  for (int head = warp; head < heads_to_do; head += ROW_WARPS) {   // q heads, then k heads, then v heads
-    const bool is_q = head < n_q;
-    const bool is_k = !is_q && head < n_q + n_kv;
-    float4 x = next;
-    next = after_next;
-    after_next = load_head(head + 2 * ROW_WARPS);
-    if (is_q ? q_norm != nullptr : (is_k && k_norm != nullptr)) {
-      const float total = srb_warp_sum(sum_squares4(x));
-      const float inv = __frsqrt_rn(total * (1.0f / (float)D) + eps);
-      const float4 w = is_q ? wq : wk;
-      x = make_float4(normed(x.x, inv, w.x), normed(x.y, inv, w.y), normed(x.z, inv, w.z), normed(x.w, inv, w.w));
-    }
-    if ((is_q || is_k) && rotate) {
-      float4 other;
-      other.x = __shfl_xor_sync(0xffffffffu, x.x, 16); other.y = __shfl_xor_sync(0xffffffffu, x.y, 16);
-      other.z = __shfl_xor_sync(0xffffffffu, x.z, 16); other.w = __shfl_xor_sync(0xffffffffu, x.w, 16);
-      if (first_half)
-        x = make_float4(rotate_first(x.x, other.x, cs.x, sn.x), rotate_first(x.y, other.y, cs.y, sn.y),
-                        rotate_first(x.z, other.z, cs.z, sn.z), rotate_first(x.w, other.w, cs.w, sn.w));
-      else
-        x = make_float4(rotate_second(other.x, x.x, cs.x, sn.x), rotate_second(other.y, x.y, cs.y, sn.y),
-                        rotate_second(other.z, x.z, cs.z, sn.z), rotate_second(other.w, x.w, cs.w, sn.w));
-    }
-    T* dst;
-    if (is_q) {
-      dst = q_dst + head * D;
-    } else {
-      if (!slot_ok) continue;
-      dst = is_k ? k_pool + kv_base + (head - n_q) * kv_step : v_pool + kv_base + (head - n_q - n_kv) * kv_step;
-    }
-    if (sizeof(T) == 2) {
-      uint2 raw;
-      *reinterpret_cast<__nv_bfloat162*>(&raw.x) = __floats2bfloat162_rn(x.x, x.y);
-      *reinterpret_cast<__nv_bfloat162*>(&raw.y) = __floats2bfloat162_rn(x.z, x.w);
-      *reinterpret_cast<uint2*>(dst) = raw;
-    } else {
-      *reinterpret_cast<float4*>(dst) = x;
-    }
+  {
+    const float4 w = k_norm ? *reinterpret_cast<const float4*>(k_norm + lane * 4) : one;
+#pragma unroll 2
+    for (int head = warp; head < n_kv; head += ROW_WARPS)
+      store_head4(k_pool + kv_base + head * kv_step,
+                  norm_and_rotate(load_head4(src + (n_q + head) * D), k_norm != nullptr, w, eps, rotate, cs, sn,
+                                  first_half));
+  }
+  // v heads: no arithmetic, the values go to the pages as they are
+  for (int head = warp; head < n_kv; head += ROW_WARPS) {
+    const T* from = src + (n_q + n_kv + head) * D;
+    T* to = v_pool + kv_base + head * kv_step;
+    if (sizeof(T) == 2)
+      *reinterpret_cast<uint2*>(to) = *reinterpret_cast<const uint2*>(from);
+    else
+      *reinterpret_cast<float4*>(to) = *reinterpret_cast<const float4*>(from);
   }
 }
 
@@ -304,19 +312,18 @@ extern "C" int srb_qk_norm_rope_kv(const void* qkv, const float* qkv_parts, int 
   cudaStream_t s = (cudaStream_t)stream;
   const bool whole_head_pairs = !(inv_freq || angles) || (rotary_dim == head_dim && !interleaved);
   // (with fewer rows than about two per SM the kernel below, which spreads a row over blocks, is quicker)
-  if (rows >= 256 && head_dim == 128 && vector_ok && whole_head_pairs &&
+  if (rows >= 256 && head_dim == 128 && vector_ok && whole_head_pairs && num_parts == 0 &&
       (((uintptr_t)q_norm | (uintptr_t)k_norm) & 15) == 0) {
     if (dtype == SRB_DTYPE_F32)
       SRB_CUDA_CALL(srb_launch(qk_norm_rope_kv_row_kernel<float>, dim3(rows), dim3(ROW_WARPS * 32), 0, s,
-                               (const float*)qkv, qkv_parts, num_parts, (size_t)part_stride, qkv_stride, (float*)q_out,
-                               (float*)k_pool, (float*)v_pool, positions, slots, q_norm, k_norm, eps, inv_freq, angles,
-                               n_q, n_kv, page_size, num_pages, heads, error_word));
+                               (const float*)qkv, qkv_stride, (float*)q_out, (float*)k_pool, (float*)v_pool, positions,
+                               slots, q_norm, k_norm, eps, inv_freq, angles, n_q, n_kv, page_size, num_pages,
+                               error_word));
     else if (dtype == SRB_DTYPE_BF16)
       SRB_CUDA_CALL(srb_launch(qk_norm_rope_kv_row_kernel<__nv_bfloat16>, dim3(rows), dim3(ROW_WARPS * 32), 0, s,
-                               (const __nv_bfloat16*)qkv, qkv_parts, num_parts, (size_t)part_stride, qkv_stride,
-                               (__nv_bfloat16*)q_out, (__nv_bfloat16*)k_pool, (__nv_bfloat16*)v_pool, positions, slots,
-                               q_norm, k_norm, eps, inv_freq, angles, n_q, n_kv, page_size, num_pages, heads,
-                               error_word));
+                               (const __nv_bfloat16*)qkv, qkv_stride, (__nv_bfloat16*)q_out, (__nv_bfloat16*)k_pool,
+                               (__nv_bfloat16*)v_pool, positions, slots, q_norm, k_norm, eps, inv_freq, angles, n_q, n_kv,
+                               page_size, num_pages, error_word));
     else
       SRB_FAIL("qk_norm_rope_kv: unknown dtype %d", dtype);
     SRB_LAUNCH_CHECK("qk_norm_rope_kv_row");
