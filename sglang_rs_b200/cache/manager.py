@@ -16,9 +16,11 @@ share another, whose pages are given back as soon as the window has passed them.
 """
 from __future__ import annotations
 
-from dataclasses import dataclass, field
+import ctypes
+from dataclasses import dataclass
 from typing import Dict, Hashable, List, Optional, Sequence, Tuple
 
+import numpy as np
 import torch
 
 from ..parts.base import CacheNeed, PagedKV, RequestState
@@ -36,50 +38,106 @@ class OutOfStateSlots(RuntimeError):
     pass
 
 
-class PageAllocator:
-    """Reference-counted pages of one group.  The free list is a stack: a page that was
-    just given back is the next one handed out."""
+def _core_library():
+    """The C++ books (csrc/host_core.cu), built at first use like the kernels."""
+    global _library
+    if _library is None:
+        from ..csrc.build import load_library
+        lib = load_library("host_core")
+        lib.hc_create.restype = ctypes.c_void_p
+        lib.hc_create.argtypes = [ctypes.c_int, ctypes.c_int, ctypes.c_void_p, ctypes.c_void_p, ctypes.c_int]
+        lib.hc_destroy.argtypes = [ctypes.c_void_p]
+        for name in ("hc_free_count", "hc_allocate", "hc_retain", "hc_release", "hc_refcount", "hc_free_list", "hc_open",
+                     "hc_close", "hc_live_count", "hc_free_state_count", "hc_length", "hc_state_slot", "hc_table_length",
+                     "hc_table", "hc_pages_needed", "hc_reserve", "hc_trim", "hc_capacity", "hc_commit",
+                     "hc_adopt_prefix", "hc_check", "hc_fill_group", "hc_fill_decode"):
+            getattr(lib, name).restype = ctypes.c_int
+        _library = lib
+    return _library
 
-    def __init__(self, num_pages: int):
+
+_library = None
+
+
+def _ints(values) -> np.ndarray:
+    return np.ascontiguousarray(values, dtype=np.int32)
+
+
+def _pointer(array: np.ndarray) -> ctypes.c_void_p:
+    return ctypes.c_void_p(array.ctypes.data)
+
+
+def _message(lib) -> str:
+    return lib.srb_last_error().decode("utf-8", "replace")
+
+
+class _Core:
+    """Owner of one set of C++ books."""
+
+    def __init__(self, page_size: int, windows: Sequence[int], num_pages: Sequence[int], max_requests: int):
+        self.lib = _core_library()
+        w, n = _ints(windows), _ints(num_pages)
+        self.pointer = self.lib.hc_create(int(page_size), len(w), _pointer(w), _pointer(n), int(max_requests))
+        if not self.pointer:
+            raise ValueError("a page pool needs at least one page, a positive page size and room for a request")
+        self.pointer = ctypes.c_void_p(self.pointer)
+
+    def __del__(self):
+        try:
+            if getattr(self, "pointer", None):
+                self.lib.hc_destroy(self.pointer)
+        except Exception:
+            pass
+
+
+class PageAllocator:
+    """Reference-counted pages of one group (kept by the C++ books).  The free list is a stack:
+    a page that was just given back is the next one handed out."""
+
+    def __init__(self, num_pages: int, core: Optional[_Core] = None, group: int = 0, key: GroupKey = None):
         if num_pages <= 0:
             raise ValueError("a page pool needs at least one page")
         self.num_pages = int(num_pages)
-        self._free: List[int] = list(range(self.num_pages - 1, -1, -1))   # pop() yields 0, 1, 2, ...
-        self._refs: List[int] = [0] * self.num_pages
+        self._core = core if core is not None else _Core(1, [0], [self.num_pages], 1)
+        self._group, self._key = int(group), key
+        self._lib, self._pointer = self._core.lib, self._core.pointer
 
     @property
     def free_count(self) -> int:
-        return len(self._free)
+        return self._lib.hc_free_count(self._pointer, self._group)
 
     def allocate(self, count: int, group: GroupKey = None) -> List[int]:
-        if count > len(self._free):
-            raise OutOfPages(group, count, len(self._free))
-        pages = [self._free.pop() for _ in range(count)]
-        for page in pages:
-            self._refs[page] = 1
-        return pages
+        out = np.empty(max(int(count), 1), dtype=np.int32)
+        status = self._lib.hc_allocate(self._pointer, self._group, int(count), _pointer(out))
+        if status == -2:
+            raise OutOfPages(group if group is not None else self._key, count, self.free_count)
+        if status < 0:
+            raise RuntimeError(_message(self._lib))
+        return out[:count].tolist()
 
     def retain(self, page: int) -> None:
-        if self._refs[page] <= 0:
-            raise RuntimeError(f"page {page} is free and cannot be shared")
-        self._refs[page] += 1
+        if self._lib.hc_retain(self._pointer, self._group, int(page)) < 0:
+            raise RuntimeError(_message(self._lib))
 
     def release(self, page: int) -> bool:
         """Drops one reference; True if the page went back to the free list."""
-        if not 0 <= page < self.num_pages or self._refs[page] <= 0:
-            raise RuntimeError(f"page {page} is freed twice or was never handed out")
-        self._refs[page] -= 1
-        if self._refs[page] == 0:
-            self._free.append(page)
-            return True
-        return False
+        status = self._lib.hc_release(self._pointer, self._group, int(page))
+        if status < 0:
+            raise RuntimeError(_message(self._lib))
+        return status == 1
 
     def refcount(self, page: int) -> int:
-        return self._refs[page]
+        return self._lib.hc_refcount(self._pointer, self._group, int(page))
+
+    def free_list(self) -> List[int]:
+        out = np.empty(self.num_pages, dtype=np.int32)
+        count = self._lib.hc_free_list(self._pointer, self._group, _pointer(out), self.num_pages)
+        return out[:count].tolist()
 
 
 class StateSlotPool:
-    """Slots for per-request state of fixed size; capacity = the most requests that run."""
+    """Slots for per-request state of fixed size; capacity = the most requests that run.
+    (A cache manager's slots live in its C++ books; this class stands alone.)"""
 
     def __init__(self, capacity: int):
         self.capacity = int(capacity)
@@ -102,6 +160,17 @@ class StateSlotPool:
             raise RuntimeError(f"state slot {slot} is freed twice or was never assigned")
         self._used.remove(slot)
         self._free.append(slot)
+
+
+class _StateSlots:
+    """What ``CacheManager.state_pool`` shows of the slots in the C++ books."""
+
+    def __init__(self, core: _Core, capacity: int):
+        self._core, self.capacity = core, int(capacity)
+
+    @property
+    def free_count(self) -> int:
+        return self._core.lib.hc_free_state_count(self._core.pointer)
 
 
 @dataclass
@@ -127,15 +196,34 @@ class StateLayerCache:
         return StateLayerCache(self.state, False)
 
 
-@dataclass
 class RequestCache:
-    """A live request's hold on the cache."""
-    request_id: Hashable
-    length: int = 0                                   # tokens whose keys and values are stored
-    tables: Dict[GroupKey, List[int]] = field(default_factory=dict)   # logical page -> page id, -1 = given back
-    state_slot: int = -1
-    shared_prefix_pages: int = 0                      # leading pages that came from the prefix tree
-    closed: bool = False
+    """A live request's hold on the cache.  Length, state slot and block tables live in the C++
+    books; ``tables`` copies them out (logical page -> page id, -1 = given back)."""
+
+    def __init__(self, request_id: Hashable, manager: "CacheManager", index: int):
+        self.request_id, self._manager, self.index = request_id, manager, index
+        self.length = 0                                  # tokens whose keys and values are stored
+        self.state_slot = manager._lib.hc_state_slot(manager._pointer, index)
+        self.shared_prefix_pages = 0                     # leading pages that came from the prefix tree
+        self.closed = False
+
+    def table(self, key: GroupKey) -> List[int]:
+        manager = self._manager
+        if self.closed:
+            return []
+        g = manager._group_index[key]
+        count = manager._lib.hc_table_length(manager._pointer, self.index, g)
+        out = np.empty(max(count, 1), dtype=np.int32)
+        manager._lib.hc_table(manager._pointer, self.index, g, _pointer(out), count)
+        return out[:count].tolist()
+
+    def table_length(self, key: GroupKey) -> int:
+        manager = self._manager
+        return 0 if self.closed else manager._lib.hc_table_length(manager._pointer, self.index, manager._group_index[key])
+
+    @property
+    def tables(self) -> Dict[GroupKey, List[int]]:
+        return {key: self.table(key) for key in self._manager.allocators}
 
 
 def group_key(need: PagedKV) -> GroupKey:
@@ -159,16 +247,27 @@ class CacheManager:
         self.device, self.dtype = device, dtype
         self.needs = list(needs)
         default_pages = max(1, -(-int(max_tokens) // self.page_size))
-        self.allocators: Dict[GroupKey, PageAllocator] = {}
         self.windows: Dict[GroupKey, Optional[int]] = {}
+        counts: Dict[GroupKey, int] = {}
         for need in self.needs:
             if isinstance(need, PagedKV):
                 key = group_key(need)
-                if key not in self.allocators:
-                    count = (pages_per_group or {}).get(key, default_pages)
-                    self.allocators[key] = PageAllocator(count)
+                if key not in counts:
+                    counts[key] = (pages_per_group or {}).get(key, default_pages)
                     self.windows[key] = need.window
-        self.state_pool = StateSlotPool(self.max_requests)
+        for key, count in counts.items():
+            if count <= 0:
+                raise ValueError("a page pool needs at least one page")
+        self._core = _Core(self.page_size, [self.windows[key] or 0 for key in counts], list(counts.values()),
+                           self.max_requests)
+        self._lib, self._pointer = self._core.lib, self._core.pointer
+        self._group_index: Dict[GroupKey, int] = {key: g for g, key in enumerate(counts)}
+        self._group_keys: List[GroupKey] = list(counts)
+        self.allocators: Dict[GroupKey, PageAllocator] = {
+            key: PageAllocator(count, self._core, g, key) for g, (key, count) in enumerate(counts.items())}
+        self._needed = np.zeros(max(len(counts), 1), dtype=np.int32)
+        self._short_group, self._shortfall = ctypes.c_int(0), ctypes.c_int(0)
+        self.state_pool = _StateSlots(self._core, self.max_requests)
         self.has_state = any(isinstance(need, RequestState) for need in self.needs)
         self.layer_caches: List[object] = []
         for need in self.needs:
@@ -221,10 +320,10 @@ class CacheManager:
     def open(self, request_id: Hashable) -> RequestCache:
         if request_id in self.live:
             raise ValueError(f"request {request_id!r} is already live")
-        if len(self.live) >= self.max_requests:
+        index = self._lib.hc_open(self._pointer)
+        if index < 0:
             raise OutOfStateSlots(f"{self.max_requests} requests are live already")
-        handle = RequestCache(request_id, tables={key: [] for key in self.allocators})
-        handle.state_slot = self.state_pool.assign()
+        handle = RequestCache(request_id, self, index)
         if self.has_state and self.device is not None:
             for cache in self.layer_caches:
                 if isinstance(cache, StateLayerCache):
@@ -237,9 +336,14 @@ class CacheManager:
         window = self.windows[key]
         return 0 if window is None else max(0, length - window + 1)
 
+    def _live(self, handle: RequestCache) -> None:
+        if handle.closed:
+            raise RuntimeError(f"request {handle.request_id!r} has ended")
+
     def pages_needed(self, handle: RequestCache, tokens: int) -> Dict[GroupKey, int]:
-        need = -(-(handle.length + tokens) // self.page_size)
-        return {key: max(0, need - len(table)) for key, table in handle.tables.items()}
+        self._live(handle)
+        self._lib.hc_pages_needed(self._pointer, handle.index, int(tokens), _pointer(self._needed))
+        return {key: int(self._needed[g]) for g, key in enumerate(self._group_keys)}
 
     def can_reserve(self, handle: RequestCache, tokens: int, spare: Optional[Dict[GroupKey, int]] = None) -> bool:
         spare = spare or {}
@@ -252,68 +356,63 @@ class CacheManager:
     def reserve(self, handle: RequestCache, tokens: int) -> None:
         """Makes room for ``tokens`` more tokens in every group, or changes nothing and
         raises :class:`OutOfPages`."""
-        if handle.closed:
-            raise RuntimeError(f"request {handle.request_id!r} has ended")
-        needed = self.pages_needed(handle, tokens)
-        for key, count in needed.items():
-            if count > self.allocators[key].free_count:
-                self._reclaim(key, count - self.allocators[key].free_count)     # pages only the prefix tree holds
-            if count > self.allocators[key].free_count:
-                raise OutOfPages(key, count, self.allocators[key].free_count)
-        for key, count in needed.items():
-            handle.tables[key].extend(self.allocators[key].allocate(count, key))
+        self._live(handle)
+        status = self._lib.hc_reserve(self._pointer, handle.index, int(tokens), ctypes.byref(self._short_group),
+                                      ctypes.byref(self._shortfall))
+        if status == -2:
+            key = self._group_keys[self._short_group.value]
+            self._reclaim(key, self._shortfall.value)            # pages only the prefix tree holds
+            status = self._lib.hc_reserve(self._pointer, handle.index, int(tokens), ctypes.byref(self._short_group),
+                                          ctypes.byref(self._shortfall))
+            if status == -2:
+                key = self._group_keys[self._short_group.value]
+                free = self.allocators[key].free_count
+                raise OutOfPages(key, free + self._shortfall.value, free)
+        if status < 0:
+            raise RuntimeError(_message(self._lib))
 
     def trim_reservation(self, handle: RequestCache) -> None:
         """Gives back pages that were reserved beyond what the stored tokens need (a step
         that did not run)."""
-        keep = -(-handle.length // self.page_size)
-        for key, table in handle.tables.items():
-            while len(table) > keep:
-                page = table.pop()
-                if page >= 0:
-                    self.allocators[key].release(page)
+        if handle.closed:
+            return
+        if self._lib.hc_trim(self._pointer, handle.index) < 0:
+            raise RuntimeError(_message(self._lib))
 
     def commit(self, handle: RequestCache, tokens: int) -> None:
         """``tokens`` more tokens are stored; pages a window has passed are given back."""
-        handle.length += tokens
-        if handle.length > self.capacity(handle):
-            raise RuntimeError("more tokens were stored than pages were reserved for")
-        for key, table in handle.tables.items():
-            first = self.first_kept_position(key, handle.length)
-            for logical in range(min(len(table), first // self.page_size)):
-                if table[logical] >= 0:
-                    self.allocators[key].release(table[logical])
-                    table[logical] = -1
+        self._live(handle)
+        length = self._lib.hc_commit(self._pointer, handle.index, int(tokens))
+        if length < 0:
+            raise RuntimeError(_message(self._lib))
+        handle.length = length
 
     def capacity(self, handle: RequestCache) -> int:
-        return min((len(table) * self.page_size for table in handle.tables.values()), default=1 << 62)
+        self._live(handle)
+        return self._lib.hc_capacity(self._pointer, handle.index)
 
     def close(self, handle: RequestCache) -> None:
         if handle.closed:
             raise RuntimeError(f"request {handle.request_id!r} is ended twice")
-        for key, table in handle.tables.items():
-            for page in table:
-                if page >= 0:
-                    self.allocators[key].release(page)
-            table.clear()
-        self.state_pool.release(handle.state_slot)
+        if self._lib.hc_close(self._pointer, handle.index) < 0:
+            raise RuntimeError(_message(self._lib))
         handle.closed = True
         del self.live[handle.request_id]
 
     # ------------------------------------------------------------------ sharing (prefix tree)
     def adopt_prefix(self, handle: RequestCache, key: GroupKey, pages: Sequence[int]) -> None:
         """Starts a new request on full pages that another owner already holds."""
-        if handle.length or handle.tables[key]:
-            raise RuntimeError("a prefix can only be adopted by a request that holds nothing yet")
-        for page in pages:
-            self.allocators[key].retain(page)
-        handle.tables[key].extend(pages)
-        handle.shared_prefix_pages = len(pages)
-        handle.length = len(pages) * self.page_size
+        self._live(handle)
+        array = _ints(list(pages))
+        length = self._lib.hc_adopt_prefix(self._pointer, handle.index, self._group_index[key], _pointer(array), len(array))
+        if length < 0:
+            raise RuntimeError(_message(self._lib))
+        handle.shared_prefix_pages = len(array)
+        handle.length = length
 
     # ------------------------------------------------------------------ step support
     def slot_of(self, handle: RequestCache, key: GroupKey, position: int) -> int:
-        page = handle.tables[key][position // self.page_size]
+        page = handle.table(key)[position // self.page_size]
         if page < 0:
             raise RuntimeError(f"position {position} lies in a page that was given back")
         return page * self.page_size + position % self.page_size
@@ -328,32 +427,42 @@ class CacheManager:
     # ------------------------------------------------------------------ checks
     def check_invariants(self, extra_holders: Optional[Dict[GroupKey, Sequence[int]]] = None) -> None:
         """No page lost, none held more often than counted, none both free and held."""
-        for key, allocator in self.allocators.items():
-            held: Dict[int, int] = {}
-            for handle in self.live.values():
-                for page in handle.tables[key]:
-                    if page >= 0:
-                        held[page] = held.get(page, 0) + 1
-            for page in (extra_holders or {}).get(key, ()):
-                held[page] = held.get(page, 0) + 1
-            if self.prefix_tree is not None and key == ("kv", None):
-                for page in self.prefix_tree.pages():
-                    held[page] = held.get(page, 0) + 1
-            free = list(allocator._free)
-            if len(set(free)) != len(free):
-                raise AssertionError(f"group {key}: a page is on the free list twice")
-            for page in free:
-                if page in held:
-                    raise AssertionError(f"group {key}: page {page} is free and held")
-                if allocator.refcount(page) != 0:
-                    raise AssertionError(f"group {key}: free page {page} has references")
-            for page, count in held.items():
-                if allocator.refcount(page) != count:
-                    raise AssertionError(f"group {key}: page {page} held {count} times, counted {allocator.refcount(page)}")
-            if len(free) + len(held) != allocator.num_pages:
-                raise AssertionError(f"group {key}: {allocator.num_pages - len(free) - len(held)} pages are lost")
-        slots = [handle.state_slot for handle in self.live.values()]
-        if len(set(slots)) != len(slots):
-            raise AssertionError("a state slot is held by two requests")
-        if len(slots) + self.state_pool.free_count != self.state_pool.capacity:
-            raise AssertionError("a state slot is lost")
+        pairs: List[int] = []
+        for key, pages in (extra_holders or {}).items():
+            for page in pages:
+                pairs += [self._group_index[key], int(page)]
+        if self.prefix_tree is not None:
+            for page in self.prefix_tree.pages():
+                pairs += [self._group_index[("kv", None)], int(page)]
+        array = _ints(pairs if pairs else [0])
+        if self._lib.hc_check(self._pointer, _pointer(array), len(pairs) // 2) < 0:
+            raise AssertionError(_message(self._lib))
+        if len(self.live) != self._lib.hc_live_count(self._pointer):
+            raise AssertionError("the live requests of the books and of the manager differ")
+
+    # ------------------------------------------------------------------ index arrays of a step
+    def fill_group(self, key: GroupKey, handles: Sequence[RequestCache], counts: Sequence[int], stride: int):
+        """Block tables [requests, stride] and write slots [rows] of one group for a step whose
+        request i brings ``counts[i]`` rows at its next positions."""
+        requests, rows = _ints([h.index for h in handles]), _ints(list(counts))
+        table = np.empty((len(requests), stride), dtype=np.int32)
+        slots = np.empty(max(int(rows.sum()), 1), dtype=np.int32)
+        status = self._lib.hc_fill_group(self._pointer, self._group_index[key], _pointer(requests), _pointer(rows),
+                                         len(requests), int(stride), _pointer(table), _pointer(slots))
+        if status < 0:
+            raise RuntimeError(_message(self._lib))
+        return table, slots[:status]
+
+    def fill_decode(self, handles: Sequence[RequestCache], tokens: Sequence[int], token_from: Sequence[int], bucket: int,
+                    stride: int, offsets: Sequence[int], buffer: np.ndarray) -> None:
+        """The static buffer of a captured decode step (one row per request, padded to
+        ``bucket`` rows whose writes go to each pool's spare page)."""
+        # the arrays stay referenced until the call has returned
+        requests = _ints([h.index for h in handles])
+        spare = _ints([self.allocators[key].num_pages for key in self._group_keys] or [0])
+        token_ids, sources, starts = _ints(list(tokens)), _ints(list(token_from)), _ints(list(offsets))
+        status = self._lib.hc_fill_decode(self._pointer, _pointer(requests), _pointer(token_ids), _pointer(sources),
+                                          len(requests), int(bucket), int(stride), _pointer(spare), _pointer(starts),
+                                          ctypes.c_void_p(buffer.ctypes.data))
+        if status < 0:
+            raise RuntimeError(_message(self._lib))

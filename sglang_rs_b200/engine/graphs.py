@@ -69,7 +69,7 @@ class DecodeGraphs:
         bucket = bucket_of(rows)
         groups = list(self.cache.allocators)
         page_size = self.cache.page_size
-        stride = bucket_of(max([len(e.handle.tables[key]) for e in entries for key in groups] + [1]), 8)
+        stride = bucket_of(max([e.handle.table_length(key) for e in entries for key in groups] + [1]), 8)
         positions = np.fromiter((e.handle.length for e in entries), dtype=np.int64, count=rows)
         splits, sizes = [], []
         for key in groups:
@@ -134,34 +134,13 @@ class DecodeGraphs:
         return step
 
     def _fill(self, step: CapturedStep, entries, groups, bucket, stride, positions, page_size) -> None:
-        rows = len(entries)
-        view = step.staging.numpy()
-
-        def part(name):
-            begin, size = step.layout[name]
-            return view[begin:begin + size]
-        tokens = part("tokens"); tokens[:] = 0
-        tokens[:rows] = [int(e.tokens[0]) for e in entries]
-        token_from = part("token_from"); token_from[:] = -1
-        token_from[:rows] = [e.token_from for e in entries]
-        pos = part("positions"); pos[:] = 0
-        pos[:rows] = positions
-        part("row_request")[:] = np.arange(bucket)
-        part("cu_rows")[:] = np.arange(bucket + 1)
-        slots_of_state = part("state_slots"); slots_of_state[:] = 0
-        slots_of_state[:rows] = [e.handle.state_slot for e in entries]
-        part("logit_rows")[:] = np.arange(bucket)
-        for g, key in enumerate(groups):
-            spare = self.cache.allocators[key].num_pages          # the pool's page that no request owns
-            table = part(f"table{g}").reshape(bucket, stride)
-            table[:] = -1
-            table[rows:, 0] = spare
-            slots = part(f"slots{g}")
-            slots[:] = spare * page_size
-            for r, entry in enumerate(entries):
-                pages = entry.handle.tables[key]
-                table[r, :len(pages)] = pages
-                slots[r] = pages[positions[r] // page_size] * page_size + positions[r] % page_size
+        """The pinned copy of the step's index arrays, written by the C++ books."""
+        names = ["tokens", "positions", "row_request", "cu_rows", "state_slots", "logit_rows", "token_from"]
+        for g in range(len(groups)):
+            names += [f"table{g}", f"slots{g}"]
+        offsets = [step.layout[name][0] for name in names]
+        self.cache.fill_decode([e.handle for e in entries], [int(e.tokens[0]) for e in entries],
+                               [e.token_from for e in entries], bucket, stride, offsets, step.staging.numpy())
 
     # ------------------------------------------------------------------ capture
     def _context(self, step: CapturedStep, groups, bucket, stride, splits, sizes) -> Tuple[StepContext, torch.Tensor, list]:

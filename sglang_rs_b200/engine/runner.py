@@ -139,22 +139,15 @@ class StepPlanner:
         logit_rows = [starts[i] + int(w) for i, entry in enumerate(entries) for w in entry.want]
 
         groups = list(self.cache.allocators)
-        page_size = self.cache.page_size
+        ordered = [entries[index].handle for index in order]
+        counts = [len(entries[index].tokens) for index in order]
         stride = 1
-        for index in order:
+        for handle in ordered:
             for key in groups:
-                stride = max(stride, len(entries[index].handle.tables[key]))
-        tables = {key: np.full((len(order), stride), -1, dtype=np.int32) for key in groups}
-        slots = {key: np.empty(rows, dtype=np.int32) for key in groups}
-        for slot, index in enumerate(order):
-            handle = entries[index].handle
-            begin = cu_rows[slot]
-            for key in groups:
-                table = handle.tables[key]
-                tables[key][slot, :len(table)] = table
-                pos = np.arange(handle.length, handle.length + len(entries[index].tokens))
-                pages = np.asarray(table, dtype=np.int64)[pos // page_size]
-                slots[key][begin:begin + len(pos)] = pages * page_size + pos % page_size
+                stride = max(stride, handle.table_length(key))
+        tables, slots = {}, {}
+        for key in groups:
+            tables[key], slots[key] = self.cache.fill_group(key, ordered, counts, stride)   # from the C++ books
 
         tiles: List[int] = []
         wide_tiles: List[int] = []

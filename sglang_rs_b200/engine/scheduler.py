@@ -290,7 +290,7 @@ class Scheduler:
                 # full pages of prompt tokens become known as soon as they are computed
                 full = min(request.handle.length, len(request.prompt)) // self.cache.page_size
                 if full > request.published_pages:
-                    tree.insert(request.prompt[:full * self.cache.page_size], request.handle.tables[("kv", None)][:full])
+                    tree.insert(request.prompt[:full * self.cache.page_size], request.handle.table(("kv", None))[:full])
                     request.published_pages = full
             if not entry.samples:
                 continue
