@@ -76,6 +76,7 @@ class _Core:
 
     def __init__(self, page_size: int, windows: Sequence[int], num_pages: Sequence[int], max_requests: int):
         self.lib = _core_library()
+        self.page_size = int(page_size)
         w, n = _ints(windows), _ints(num_pages)
         self.pointer = self.lib.hc_create(int(page_size), len(w), _pointer(w), _pointer(n), int(max_requests))
         if not self.pointer:

@@ -11,122 +11,87 @@ used leaves first, when the pool runs short.
 
 A match never covers the whole sequence: at most ``(len - 1) // page_size`` pages, so at
 least one token is computed, into a page of the request's own.
+
+The tree itself lives in the C++ books beside the pages it refers to (csrc/host_core.cu);
+this class is its Python face.
 """
 from __future__ import annotations
 
-import itertools
-from typing import Dict, List, Optional, Sequence, Tuple
+import ctypes
+from typing import List, Sequence
 
-from .manager import PageAllocator
+import numpy as np
 
-
-class _Node:
-    __slots__ = ("key", "page", "parent", "children", "stamp")
-
-    def __init__(self, key, page, parent):
-        self.key, self.page, self.parent = key, page, parent
-        self.children: Dict[Tuple[int, ...], "_Node"] = {}
-        self.stamp = 0
+from .manager import PageAllocator, _core_library, _message, _pointer
 
 
 class PrefixTree:
     def __init__(self, page_size: int, allocator: PageAllocator):
         self.page_size, self.allocator = int(page_size), allocator
-        self.root = _Node((), -1, None)
-        self._clock = itertools.count(1)
-        self.pages_held = 0
+        self._lib = _core_library()
+        for name in ("hc_tree_match", "hc_tree_insert", "hc_tree_evictable", "hc_tree_evict", "hc_tree_pages_held",
+                     "hc_tree_pages", "hc_tree_clear"):
+            getattr(self._lib, name).restype = ctypes.c_int
+        self._lib.hc_tree_create.restype = ctypes.c_void_p
+        self._lib.hc_tree_create.argtypes = [ctypes.c_void_p, ctypes.c_int, ctypes.c_int]
+        self._lib.hc_tree_destroy.argtypes = [ctypes.c_void_p]
+        self._core = allocator._core                     # the books outlive the tree
+        pointer = self._lib.hc_tree_create(self._core.pointer, allocator._group, self.page_size)
+        if not pointer:
+            raise ValueError("the prefix tree could not be made for this group of pages")
+        self._pointer = ctypes.c_void_p(pointer)
         self.hits = self.lookups = 0
 
-    def _walk(self, tokens: Sequence[int], max_pages: int) -> List[_Node]:
-        path, node = [], self.root
-        for i in range(max_pages):
-            child = node.children.get(tuple(tokens[i * self.page_size:(i + 1) * self.page_size]))
-            if child is None:
-                break
-            path.append(child)
-            node = child
-        return path
+    def __del__(self):
+        try:
+            if getattr(self, "_pointer", None):
+                self._lib.hc_tree_destroy(self._pointer)
+        except Exception:
+            pass
+
+    @property
+    def pages_held(self) -> int:
+        return self._lib.hc_tree_pages_held(self._pointer)
 
     def match(self, tokens: Sequence[int]) -> List[int]:
         """Page ids of the longest known prefix of ``tokens``, leaving at least one token out."""
         self.lookups += 1
-        path = self._walk(tokens, (len(tokens) - 1) // self.page_size)
-        stamp = next(self._clock)
-        for node in path:
-            node.stamp = stamp
-        self.hits += bool(path)
-        return [node.page for node in path]
+        array = np.ascontiguousarray(tokens, dtype=np.int32)
+        out = np.empty(max(len(array) // self.page_size, 1), dtype=np.int32)
+        found = self._lib.hc_tree_match(self._pointer, _pointer(array), len(array), _pointer(out))
+        if found < 0:
+            raise RuntimeError(_message(self._lib))
+        self.hits += bool(found)
+        return out[:found].tolist()
 
     def insert(self, tokens: Sequence[int], pages: Sequence[int]) -> int:
         """Makes the full pages ``pages[i]`` holding ``tokens[i*P:(i+1)*P]`` known.  Pages that are
         new to the tree get one more reference; a page whose tokens are known already under
         another page id is left to its request.  Returns the number of pages adopted."""
-        count = min(len(pages), len(tokens) // self.page_size)
-        node, adopted, stamp = self.root, 0, next(self._clock)
-        for i in range(count):
-            key = tuple(tokens[i * self.page_size:(i + 1) * self.page_size])
-            child = node.children.get(key)
-            if child is None:
-                if pages[i] < 0:
-                    break
-                child = _Node(key, pages[i], node)
-                node.children[key] = child
-                self.allocator.retain(pages[i])
-                self.pages_held += 1
-                adopted += 1
-            child.stamp = stamp
-            node = child
+        token_array = np.ascontiguousarray(tokens, dtype=np.int32)
+        page_array = np.ascontiguousarray(list(pages) or [0], dtype=np.int32)
+        adopted = self._lib.hc_tree_insert(self._pointer, _pointer(token_array), len(token_array), _pointer(page_array),
+                                           len(pages))
+        if adopted < 0:
+            raise RuntimeError(_message(self._lib))
         return adopted
 
     def evictable(self) -> int:
         """Pages that only the tree holds and that could be freed (leaves first, then their parents)."""
-        def count(node) -> Tuple[int, bool]:
-            total, all_free = 0, True
-            for child in node.children.values():
-                sub, free = count(child)
-                total += sub
-                all_free &= free
-            if node is self.root:
-                return total, False
-            mine = all_free and self.allocator.refcount(node.page) == 1
-            return total + int(mine), mine
-        return count(self.root)[0]
+        return self._lib.hc_tree_evictable(self._pointer)
 
     def evict(self, pages: int) -> int:
         """Frees up to ``pages`` pages that nobody but the tree holds, least recently used leaves first."""
-        freed = 0
-        while freed < pages:
-            leaves = [n for n in self._leaves() if self.allocator.refcount(n.page) == 1]
-            if not leaves:
-                break
-            for node in sorted(leaves, key=lambda n: n.stamp):
-                del node.parent.children[node.key]
-                self.allocator.release(node.page)
-                self.pages_held -= 1
-                freed += 1
-                if freed >= pages:
-                    break
+        freed = self._lib.hc_tree_evict(self._pointer, int(pages))
+        if freed < 0:
+            raise RuntimeError(_message(self._lib))
         return freed
 
-    def _leaves(self):
-        stack = list(self.root.children.values())
-        while stack:
-            node = stack.pop()
-            if node.children:
-                stack.extend(node.children.values())
-            else:
-                yield node
-
     def pages(self) -> List[int]:
-        out, stack = [], list(self.root.children.values())
-        while stack:
-            node = stack.pop()
-            out.append(node.page)
-            stack.extend(node.children.values())
-        return out
+        out = np.empty(max(self.pages_held, 1), dtype=np.int32)
+        count = self._lib.hc_tree_pages(self._pointer, _pointer(out), len(out))
+        return out[:count].tolist()
 
     def clear(self) -> None:
-        for page in self.pages():
-            self.allocator.release(page)
-        self.root.children.clear()
-        self.pages_held = 0
+        if self._lib.hc_tree_clear(self._pointer) < 0:
+            raise RuntimeError(_message(self._lib))

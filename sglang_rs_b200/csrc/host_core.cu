@@ -16,6 +16,8 @@
 #include <stdio.h>
 #include <string.h>
 #include <algorithm>
+#include <map>
+#include <memory>
 #include <vector>
 
 namespace {
@@ -445,6 +447,195 @@ int hc_fill_decode(void* handle, const int* requests, const int* tokens, const i
     }
   }
   return 0;
+}
+
+}  // extern "C"
+
+// ---- prefix tree over full pages of tokens -------------------------------------------------------
+// An edge is one page of tokens, a node holds the page id; the tree holds one reference on every page
+// it knows, so a finished request's prompt pages stay until they are evicted: least recently used
+// leaves that nobody else holds go first (the reference keeps a per-token trie, floors a match to whole
+// pages and never evicts, crates/sglang-srt/src/cache.rs:475-547).  A match never covers the whole
+// sequence: at most (len - 1) / page_size pages, so at least one token is computed.
+namespace {
+
+struct TreeNode {
+  std::vector<int> key;
+  int page = -1;
+  TreeNode* parent = nullptr;
+  long long stamp = 0;
+  std::map<std::vector<int>, std::unique_ptr<TreeNode>> children;
+};
+
+struct Tree {
+  Core* core = nullptr;
+  int group = 0;
+  int page_size = 1;
+  TreeNode root;
+  long long clock = 0;
+  int pages_held = 0;
+};
+
+void collect_leaves(TreeNode* node, std::vector<TreeNode*>& out) {
+  for (auto& entry : node->children) {
+    if (entry.second->children.empty()) out.push_back(entry.second.get());
+    else collect_leaves(entry.second.get(), out);
+  }
+}
+
+// pages below `node` that only the tree holds and that eviction could reach; `free_out`: the node itself is one
+int count_evictable(const Tree* tree, const TreeNode* node, bool is_root, bool* free_out) {
+  int total = 0;
+  bool all_free = true;
+  for (const auto& entry : node->children) {
+    bool child_free = false;
+    total += count_evictable(tree, entry.second.get(), false, &child_free);
+    all_free = all_free && child_free;
+  }
+  if (is_root) {
+    *free_out = false;
+    return total;
+  }
+  const bool mine = all_free && tree->core->groups[tree->group].refs[node->page] == 1;
+  *free_out = mine;
+  return total + (mine ? 1 : 0);
+}
+
+void collect_pages(const TreeNode* node, std::vector<int>& out) {
+  for (const auto& entry : node->children) {
+    out.push_back(entry.second->page);
+    collect_pages(entry.second.get(), out);
+  }
+}
+
+}  // namespace
+
+extern "C" {
+
+void* hc_tree_create(void* handle, int g, int page_size) {
+  Core* core = static_cast<Core*>(handle);
+  if (!good_group(core, g) || page_size <= 0) return nullptr;
+  Tree* tree = new Tree();
+  tree->core = core;
+  tree->group = g;
+  tree->page_size = page_size;
+  return tree;
+}
+
+void hc_tree_destroy(void* handle) { delete static_cast<Tree*>(handle); }
+
+// page ids of the longest known prefix of tokens[0..count), leaving at least one token out
+int hc_tree_match(void* handle, const int* tokens, int count, int* pages_out) {
+  Tree* tree = static_cast<Tree*>(handle);
+  if (!tree || count < 0) return fail(-1, "no tree");
+  const int page_size = tree->page_size;
+  const int most = count > 0 ? (count - 1) / page_size : 0;
+  TreeNode* node = &tree->root;
+  const long long stamp = ++tree->clock;
+  int found = 0;
+  std::vector<int> key(page_size);
+  for (int i = 0; i < most; ++i) {
+    key.assign(tokens + (size_t)i * page_size, tokens + (size_t)(i + 1) * page_size);
+    auto it = node->children.find(key);
+    if (it == node->children.end()) break;
+    node = it->second.get();
+    node->stamp = stamp;
+    pages_out[found++] = node->page;
+  }
+  return found;
+}
+
+// Makes the full pages pages[i] holding tokens[i*P..(i+1)*P) known.  Pages new to the tree get one more
+// reference; a page whose tokens are known already under another page id is left to its request.
+int hc_tree_insert(void* handle, const int* tokens, int token_count, const int* pages, int page_count) {
+  Tree* tree = static_cast<Tree*>(handle);
+  if (!tree) return fail(-1, "no tree");
+  const int page_size = tree->page_size;
+  Group& group = tree->core->groups[tree->group];
+  const int count = std::min(page_count, token_count / page_size);
+  TreeNode* node = &tree->root;
+  const long long stamp = ++tree->clock;
+  int adopted = 0;
+  std::vector<int> key(page_size);
+  for (int i = 0; i < count; ++i) {
+    key.assign(tokens + (size_t)i * page_size, tokens + (size_t)(i + 1) * page_size);
+    auto it = node->children.find(key);
+    TreeNode* child;
+    if (it == node->children.end()) {
+      if (pages[i] < 0) break;
+      if (pages[i] >= group.num_pages || group.refs[pages[i]] <= 0)
+        return fail(-4, "page %d is free and cannot be shared", pages[i]);
+      std::unique_ptr<TreeNode> fresh(new TreeNode());
+      fresh->key = key;
+      fresh->page = pages[i];
+      fresh->parent = node;
+      child = fresh.get();
+      node->children.emplace(key, std::move(fresh));
+      ++group.refs[pages[i]];
+      ++tree->pages_held;
+      ++adopted;
+    } else {
+      child = it->second.get();
+    }
+    child->stamp = stamp;
+    node = child;
+  }
+  return adopted;
+}
+
+int hc_tree_evictable(void* handle) {
+  Tree* tree = static_cast<Tree*>(handle);
+  if (!tree) return fail(-1, "no tree");
+  bool unused = false;
+  return count_evictable(tree, &tree->root, true, &unused);
+}
+
+// frees up to `pages` pages that nobody but the tree holds, least recently used leaves first
+int hc_tree_evict(void* handle, int pages) {
+  Tree* tree = static_cast<Tree*>(handle);
+  if (!tree) return fail(-1, "no tree");
+  Group& group = tree->core->groups[tree->group];
+  int freed = 0;
+  while (freed < pages) {
+    std::vector<TreeNode*> leaves;
+    collect_leaves(&tree->root, leaves);
+    leaves.erase(std::remove_if(leaves.begin(), leaves.end(), [&](TreeNode* n) { return group.refs[n->page] != 1; }),
+                 leaves.end());
+    if (leaves.empty()) break;
+    std::stable_sort(leaves.begin(), leaves.end(), [](TreeNode* a, TreeNode* b) { return a->stamp < b->stamp; });
+    for (TreeNode* leaf : leaves) {
+      if (release_page(group, leaf->page) < 0) return -4;
+      --tree->pages_held;
+      ++freed;
+      const std::vector<int> key = leaf->key;        // the node, and its key with it, goes with the erase
+      leaf->parent->children.erase(key);
+      if (freed >= pages) break;
+    }
+  }
+  return freed;
+}
+
+int hc_tree_pages_held(void* handle) { return handle ? static_cast<Tree*>(handle)->pages_held : fail(-1, "no tree"); }
+
+int hc_tree_pages(void* handle, int* out, int capacity) {
+  Tree* tree = static_cast<Tree*>(handle);
+  if (!tree) return fail(-1, "no tree");
+  std::vector<int> pages;
+  collect_pages(&tree->root, pages);
+  for (int i = 0; i < (int)pages.size() && i < capacity; ++i) out[i] = pages[i];
+  return (int)pages.size();
+}
+
+int hc_tree_clear(void* handle) {
+  Tree* tree = static_cast<Tree*>(handle);
+  if (!tree) return fail(-1, "no tree");
+  std::vector<int> pages;
+  collect_pages(&tree->root, pages);
+  for (int page : pages)
+    if (release_page(tree->core->groups[tree->group], page) < 0) return -4;
+  tree->root.children.clear();
+  tree->pages_held = 0;
+  return (int)pages.size();
 }
 
 }  // extern "C"
