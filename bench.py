@@ -186,7 +186,7 @@ def main() -> int:
         handles = [r.handle for r in requests]
         tokens = [[r.tokens[-1]] for r in requests]
         for r, h in zip(requests, handles):                   # the scheduler must not touch them meanwhile
-            engine.scheduler.running.remove(r)
+            engine.scheduler.release(r)
 
         def one_step():
             logits = engine.runner.step([StepEntry(h, t, [0]) for h, t in zip(handles, tokens)])

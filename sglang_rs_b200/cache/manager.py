@@ -332,6 +332,24 @@ class CacheManager:
         self.live[request_id] = handle
         return handle
 
+    def attach(self, request_id: Hashable, index: int) -> RequestCache:
+        """The handle of a request that the C++ scheduler has opened in the books already."""
+        if request_id in self.live:
+            raise ValueError(f"request {request_id!r} is already live")
+        handle = RequestCache(request_id, self, index)
+        handle.length = self._lib.hc_length(self._pointer, index)
+        if self.has_state and self.device is not None:
+            for cache in self.layer_caches:
+                if isinstance(cache, StateLayerCache):
+                    cache.state[handle.state_slot].zero_()       # a new request starts from zero state
+        self.live[request_id] = handle
+        return handle
+
+    def detach(self, handle: RequestCache) -> None:
+        """The C++ scheduler has closed the request in the books: the handle ends too."""
+        handle.closed = True
+        self.live.pop(handle.request_id, None)
+
     def first_kept_position(self, key: GroupKey, length: int) -> int:
         """The first position whose key a query at position >= ``length`` can still see."""
         window = self.windows[key]

@@ -639,3 +639,537 @@ int hc_tree_clear(void* handle) {
 }
 
 }  // extern "C"
+
+// ---- the scheduler -------------------------------------------------------------------------------
+// Decisions only: which rows the next step holds.  First come, first served admission under a limit
+// of running requests and a token budget per step that counts only tokens still to be computed (the
+// reference: crates/sglang-srt/src/scheduler.rs:463-525); a request finishes on a stop token, which
+// stays in its output, unless it ignores them (crates/sglang-srt/src/model_executor.rs:763-769), or
+// when its new tokens are out (scheduler.rs:195-197).  Beyond the reference: every step gives each
+// decoding request its one row first and fills the rest of the budget with prompt portions, the last
+// one cut to fit; when pages run out a portion is cut to the free pages, then the request admitted
+// last is preempted (pages freed, tokens kept, recomputed later), and a request that could not fit
+// even alone finishes with "cache_full".  A request may have one token that is still on the device
+// (`pending`): it counts as a token, its value is not known here.
+#include <deque>
+
+namespace {
+
+enum Reason { REASON_NONE = 0, REASON_STOP = 1, REASON_LENGTH = 2, REASON_CONTEXT = 3, REASON_CACHE_FULL = 4, REASON_ABORT = 5 };
+
+struct SchedRequest {
+  bool used = false;
+  std::vector<int> prompt, output, stops;
+  int max_new_tokens = 0;
+  bool ignore_eos = false;
+  int handle = -1;                 // request of the cache books, -1 while it holds nothing
+  bool finished = false;
+  int reason = REASON_NONE;
+  int cached_tokens = 0, preemptions = 0, published_pages = 0, pending = 0;
+  long long admitted_at = -1;
+};
+
+struct Entry {
+  int request, start, count, samples, from_device;
+};
+
+struct Output {
+  int request, token, cached_tokens, finished, reason;
+};
+
+struct Sched {
+  Core* core = nullptr;
+  Tree* tree = nullptr;
+  int max_running = 1, budget = 1, max_positions = 1, evict_ahead = 32;
+  std::vector<int> default_stops;
+  std::vector<SchedRequest> requests;
+  std::vector<int> free_slots;
+  std::deque<int> waiting;
+  std::vector<int> running;
+  std::vector<Output> unreported;
+  std::vector<int> events;                  // cache requests opened (1, handle, request) and closed (0, handle, -1), in order
+  std::vector<int> touched;                 // requests whose record changed in a way their entries do not show
+  long long clock = 0;
+  long long steps = 0, preemptions = 0, failed_cache_full = 0, scheduled_tokens = 0;
+  std::vector<Entry> entries;               // of the last schedule call
+};
+
+int num_tokens(const SchedRequest& r) { return (int)r.prompt.size() + (int)r.output.size() + r.pending; }
+int computed(const Sched* s, const SchedRequest& r) { return r.handle >= 0 ? s->core->requests[r.handle].length : 0; }
+
+bool is_decoding(const Sched* s, const SchedRequest& r) {
+  return r.handle >= 0 && (!r.output.empty() || r.pending > 0) && computed(s, r) == num_tokens(r) - 1;
+}
+
+bool ends_whatever_comes(const Sched* s, const SchedRequest& r) {
+  return r.pending > 0 && ((int)r.output.size() + r.pending >= r.max_new_tokens || num_tokens(r) >= s->max_positions);
+}
+
+int token_at(const SchedRequest& r, int position) {
+  const int n = (int)r.prompt.size();
+  if (position < n) return r.prompt[position];
+  if (position - n < (int)r.output.size()) return r.output[position - n];
+  return -1;                                   // still on the device
+}
+
+int reclaimable(const Sched* s, int g) {
+  if (!s->tree || s->tree->group != g) return 0;
+  bool unused = false;
+  return count_evictable(s->tree, &s->tree->root, true, &unused);
+}
+
+int evict(Sched* s, int pages) {
+  Group& group = s->core->groups[s->tree->group];
+  int freed = 0;
+  while (freed < pages) {
+    std::vector<TreeNode*> leaves;
+    collect_leaves(&s->tree->root, leaves);
+    leaves.erase(std::remove_if(leaves.begin(), leaves.end(), [&](TreeNode* n) { return group.refs[n->page] != 1; }),
+                 leaves.end());
+    if (leaves.empty()) break;
+    std::stable_sort(leaves.begin(), leaves.end(), [](TreeNode* a, TreeNode* b) { return a->stamp < b->stamp; });
+    for (TreeNode* leaf : leaves) {
+      release_page(group, leaf->page);
+      --s->tree->pages_held;
+      ++freed;
+      const std::vector<int> key = leaf->key;
+      leaf->parent->children.erase(key);
+      if (freed >= pages) break;
+    }
+  }
+  return freed;
+}
+
+// room for `tokens` more tokens, evicting cached prefixes if that helps; false: nothing changed
+bool reserve(Sched* s, int handle, int tokens) {
+  int short_group = 0, shortfall = 0;
+  int status = hc_reserve(s->core, handle, tokens, &short_group, &shortfall);
+  if (status == -2 && s->tree && s->tree->group == short_group) {
+    evict(s, std::max(shortfall, s->evict_ahead));
+    status = hc_reserve(s->core, handle, tokens, &short_group, &shortfall);
+  }
+  return status == 0;
+}
+
+bool can_reserve(const Sched* s, int handle, int tokens) {
+  const Request& request = s->core->requests[handle];
+  const int need = pages_for(s->core, request.length + tokens);
+  for (size_t g = 0; g < s->core->groups.size(); ++g) {
+    const int count = std::max(0, need - (int)request.tables[g].size());
+    const int free_pages = (int)s->core->groups[g].free_stack.size();
+    if (count > free_pages && count > free_pages + reclaimable(s, (int)g)) return false;
+  }
+  return true;
+}
+
+void close_handle(Sched* s, SchedRequest& r) {
+  if (r.handle >= 0) {
+    hc_close(s->core, r.handle);
+    s->events.insert(s->events.end(), {0, r.handle, -1});
+    r.handle = -1;
+  }
+}
+
+void finish(Sched* s, int slot, int reason, bool report) {
+  SchedRequest& r = s->requests[slot];
+  s->touched.push_back(slot);
+  close_handle(s, r);
+  r.finished = true;
+  r.reason = reason;
+  if (report) s->unreported.push_back(Output{slot, -1, r.cached_tokens, 1, reason});
+}
+
+void remove_running(Sched* s, int slot) {
+  s->running.erase(std::remove(s->running.begin(), s->running.end(), slot), s->running.end());
+}
+
+bool is_running(const Sched* s, int slot) { return std::find(s->running.begin(), s->running.end(), slot) != s->running.end(); }
+
+int youngest_running(const Sched* s) {
+  int best = s->running.front();
+  for (int slot : s->running)
+    if (s->requests[slot].admitted_at > s->requests[best].admitted_at) best = slot;
+  return best;
+}
+
+void preempt(Sched* s, int victim) {
+  s->entries.erase(std::remove_if(s->entries.begin(), s->entries.end(), [&](const Entry& e) { return e.request == victim; }),
+                   s->entries.end());
+  remove_running(s, victim);
+  SchedRequest& r = s->requests[victim];
+  s->touched.push_back(victim);
+  close_handle(s, r);
+  r.published_pages = 0;
+  ++r.preemptions;
+  ++s->preemptions;
+  s->waiting.push_front(victim);
+}
+
+int schedule_portion(Sched* s, int slot, int budget) {
+  SchedRequest& r = s->requests[slot];
+  const int total = num_tokens(r);
+  const int start = computed(s, r);
+  int count = std::min(budget, total - start);
+  // cut the portion down to the pages that are free
+  while (count > 0 && !can_reserve(s, r.handle, count)) {
+    int free_pages = 1 << 30;
+    for (size_t g = 0; g < s->core->groups.size(); ++g)
+      free_pages = std::min(free_pages, (int)s->core->groups[g].free_stack.size() + reclaimable(s, (int)g));
+    if (s->core->groups.empty()) free_pages = 0;
+    const int room = hc_capacity(s->core, r.handle) - start + free_pages * s->core->page_size;
+    count = std::min(count - 1, std::max(room, 0));
+  }
+  if (count <= 0) return 0;
+  if (!reserve(s, r.handle, count)) return 0;
+  s->entries.push_back(Entry{slot, start, count, start + count == total ? 1 : 0, 0});
+  return count;
+}
+
+bool can_never_fit(const Sched* s, const SchedRequest& r) {
+  // prompt (and what was generated before a preemption) plus the token to be sampled next
+  const int need = pages_for(s->core, num_tokens(r) + 1);
+  for (const Group& group : s->core->groups)
+    if (group.window <= 0 && need > group.num_pages) return true;
+  return false;
+}
+
+void schedule_once(Sched* s) {
+  int budget = s->budget;
+  s->entries.clear();
+  const long long preempted_before = s->preemptions;
+  // 1. every decoding request gets its one row; make room by preemption if needed
+  std::vector<int> decoding;
+  for (int slot : s->running)
+    if (is_decoding(s, s->requests[slot])) decoding.push_back(slot);
+  for (int slot : decoding) {
+    if (!is_running(s, slot)) continue;                       // preempted below, earlier in this loop
+    SchedRequest& r = s->requests[slot];
+    if (ends_whatever_comes(s, r)) continue;                  // it finishes when its token arrives
+    while (true) {
+      if (reserve(s, r.handle, 1)) break;
+      const int victim = youngest_running(s);
+      if (victim == slot && s->running.size() == 1) {
+        // alone and the pool is full of its own tokens: it can never go on
+        remove_running(s, slot);
+        finish(s, slot, REASON_CACHE_FULL, true);
+        ++s->failed_cache_full;
+        break;
+      }
+      preempt(s, victim);
+      if (victim == slot) break;
+    }
+    if (is_running(s, slot) && !r.finished) {
+      s->entries.push_back(Entry{slot, computed(s, r), 1, 1, r.pending > 0 ? 1 : 0});
+      --budget;
+    }
+  }
+  // 2. prompts in progress go on, oldest first; 3. then new requests are admitted
+  std::vector<int> in_progress;
+  for (int slot : s->running)
+    if (!is_decoding(s, s->requests[slot])) in_progress.push_back(slot);
+  for (int slot : in_progress) {
+    if (budget <= 0) break;
+    if (s->requests[slot].pending) continue;
+    bool scheduled = false;
+    for (const Entry& e : s->entries) scheduled = scheduled || e.request == slot;
+    if (scheduled) continue;
+    budget -= schedule_portion(s, slot, budget);
+  }
+  while (!s->waiting.empty() && budget > 0 && (int)s->running.size() < s->max_running) {
+    if (s->preemptions != preempted_before && !s->running.empty()) break;   // pages were just taken away: admit nobody
+    const int slot = s->waiting.front();
+    SchedRequest& r = s->requests[slot];
+    if (can_never_fit(s, r)) {
+      s->waiting.pop_front();
+      finish(s, slot, REASON_CACHE_FULL, true);
+      ++s->failed_cache_full;
+      continue;
+    }
+    const int handle = hc_open(s->core);
+    if (handle < 0) break;
+    r.handle = handle;
+    s->touched.push_back(slot);
+    s->events.insert(s->events.end(), {1, handle, slot});
+    if (s->tree) {
+      std::vector<int> tokens(r.prompt);
+      tokens.insert(tokens.end(), r.output.begin(), r.output.end());
+      std::vector<int> shared(tokens.size() / s->tree->page_size + 1);
+      const int found = hc_tree_match(s->tree, tokens.data(), (int)tokens.size(), shared.data());
+      if (found > 0) {
+        hc_adopt_prefix(s->core, handle, s->tree->group, shared.data(), found);
+        r.published_pages = found;
+        if (!r.preemptions) r.cached_tokens = std::min(s->core->requests[handle].length, (int)r.prompt.size());
+      }
+    }
+    const int taken = schedule_portion(s, slot, budget);
+    if (taken == 0) {
+      close_handle(s, r);                                     // no page free: it stays at the head
+      break;
+    }
+    s->waiting.pop_front();
+    r.admitted_at = s->clock++;
+    s->running.push_back(slot);
+    budget -= taken;
+  }
+}
+
+}  // namespace
+
+extern "C" {
+
+void* hs_create(void* core, void* tree, int max_running, int budget, int max_positions, const int* stops, int num_stops) {
+  if (!core || max_running <= 0 || budget <= 0) return nullptr;
+  Sched* s = new Sched();
+  s->core = static_cast<Core*>(core);
+  s->tree = static_cast<Tree*>(tree);
+  s->max_running = max_running;
+  s->budget = budget;
+  s->max_positions = max_positions;
+  s->default_stops.assign(stops, stops + num_stops);
+  return s;
+}
+
+void hs_destroy(void* handle) { delete static_cast<Sched*>(handle); }
+
+void hs_set_tree(void* handle, void* tree) { static_cast<Sched*>(handle)->tree = static_cast<Tree*>(tree); }
+
+int hs_add(void* handle, const int* prompt, int prompt_len, int max_new_tokens, const int* stops, int num_stops,
+           int ignore_eos) {
+  Sched* s = static_cast<Sched*>(handle);
+  if (!s || prompt_len <= 0) return fail(-1, "a request needs a prompt");
+  int slot;
+  if (!s->free_slots.empty()) {
+    slot = s->free_slots.back();
+    s->free_slots.pop_back();
+  } else {
+    slot = (int)s->requests.size();
+    s->requests.emplace_back();
+  }
+  SchedRequest& r = s->requests[slot];
+  r = SchedRequest();
+  r.used = true;
+  r.prompt.assign(prompt, prompt + prompt_len);
+  r.max_new_tokens = max_new_tokens;
+  r.stops.assign(stops, stops + num_stops);
+  r.ignore_eos = ignore_eos != 0;
+  s->waiting.push_back(slot);
+  return slot;
+}
+
+// a finished request's record may be used again
+int hs_forget(void* handle, int slot) {
+  Sched* s = static_cast<Sched*>(handle);
+  if (!s || slot < 0 || slot >= (int)s->requests.size() || !s->requests[slot].used) return fail(-1, "no such request");
+  if (!s->requests[slot].finished) return fail(-4, "the request is not finished");
+  s->requests[slot] = SchedRequest();
+  s->free_slots.push_back(slot);
+  return 0;
+}
+
+int hs_has_work(void* handle) {
+  Sched* s = static_cast<Sched*>(handle);
+  return s && (!s->waiting.empty() || !s->running.empty());
+}
+
+// Chooses the rows of the next step and reserves their pages.  Returns the number of entries; the entries
+// are read with hs_entries, the tokens of all entries, one after another, with hs_entry_tokens.
+int hs_schedule(void* handle, int ahead) {
+  Sched* s = static_cast<Sched*>(handle);
+  if (!s) return fail(-1, "no scheduler");
+  while (true) {
+    schedule_once(s);
+    if (!s->entries.empty() || s->running.empty() || ahead) break;
+    // Nothing could move although requests are running: prompts in progress hold all pages between
+    // them.  The one admitted last gives its pages up.
+    preempt(s, youngest_running(s));
+  }
+  ++s->steps;
+  for (const Entry& e : s->entries) s->scheduled_tokens += e.count;
+  return (int)s->entries.size();
+}
+
+int hs_entries(void* handle, int* out /* [n][5]: request, start, count, samples, from_device */) {
+  Sched* s = static_cast<Sched*>(handle);
+  for (size_t i = 0; i < s->entries.size(); ++i) {
+    const Entry& e = s->entries[i];
+    out[5 * i] = e.request; out[5 * i + 1] = e.start; out[5 * i + 2] = e.count; out[5 * i + 3] = e.samples;
+    out[5 * i + 4] = e.from_device;
+  }
+  return (int)s->entries.size();
+}
+
+int hs_entry_tokens(void* handle, int* out, int capacity) {
+  Sched* s = static_cast<Sched*>(handle);
+  int written = 0;
+  for (const Entry& e : s->entries)
+    for (int j = 0; j < e.count; ++j) {
+      if (written >= capacity) return fail(-1, "the token buffer is too small");
+      out[written++] = token_at(s->requests[e.request], e.start + j);
+    }
+  return written;
+}
+
+// After the step: entries [n][5] as given by hs_entries, one sampled token per entry with `samples` set, in
+// order.  Outputs [m][5]: request, token (-1: none), cached tokens, finished, reason; returns m.
+int hs_process(void* handle, const int* entries, int num_entries, const int* sampled, int num_sampled, int* out,
+               int capacity) {
+  Sched* s = static_cast<Sched*>(handle);
+  if (!s) return fail(-1, "no scheduler");
+  std::vector<Output> outputs(s->unreported);
+  s->unreported.clear();
+  int next_pick = 0;
+  for (int i = 0; i < num_entries; ++i) {
+    const int slot = entries[5 * i];
+    const bool samples = entries[5 * i + 3] != 0;
+    SchedRequest& r = s->requests[slot];
+    if (s->tree && r.handle >= 0) {
+      // full pages of prompt tokens become known as soon as they are computed
+      const int full = std::min(s->core->requests[r.handle].length, (int)r.prompt.size()) / s->core->page_size;
+      if (full > r.published_pages) {
+        const std::vector<int>& table = s->core->requests[r.handle].tables[s->tree->group];
+        hc_tree_insert(s->tree, r.prompt.data(), full * s->core->page_size, table.data(), std::min(full, (int)table.size()));
+        r.published_pages = full;
+      }
+    }
+    if (!samples) continue;
+    if (next_pick >= num_sampled) return fail(-1, "fewer tokens than entries that sample");
+    const int token = sampled[next_pick++];
+    r.pending = std::max(0, r.pending - 1);
+    if (r.finished) continue;                  // it ended (stop token, abort) while this step was already running
+    r.output.push_back(token);
+    bool is_stop = std::find(r.stops.begin(), r.stops.end(), token) != r.stops.end() ||
+                   std::find(s->default_stops.begin(), s->default_stops.end(), token) != s->default_stops.end();
+    int reason = REASON_NONE;
+    if (is_stop && !r.ignore_eos) reason = REASON_STOP;
+    else if ((int)r.output.size() >= r.max_new_tokens) reason = REASON_LENGTH;
+    else if (num_tokens(r) >= s->max_positions) reason = REASON_CONTEXT;
+    if (reason != REASON_NONE) {
+      remove_running(s, slot);
+      finish(s, slot, reason, false);
+    }
+    outputs.push_back(Output{slot, token, r.cached_tokens, r.finished ? 1 : 0, reason});
+  }
+  if ((int)outputs.size() > capacity) return fail(-1, "the output buffer is too small");
+  for (size_t i = 0; i < outputs.size(); ++i) {
+    out[5 * i] = outputs[i].request; out[5 * i + 1] = outputs[i].token; out[5 * i + 2] = outputs[i].cached_tokens;
+    out[5 * i + 3] = outputs[i].finished; out[5 * i + 4] = outputs[i].reason;
+  }
+  return (int)outputs.size();
+}
+
+// the step raised: every request of the batch is failed and gives its pages back
+int hs_step_failed(void* handle, const int* entries, int num_entries) {
+  Sched* s = static_cast<Sched*>(handle);
+  for (int i = 0; i < num_entries; ++i) {
+    const int slot = entries[5 * i];
+    if (is_running(s, slot)) {
+      remove_running(s, slot);
+      finish(s, slot, REASON_ABORT, true);
+    }
+  }
+  return 0;
+}
+
+int hs_abort(void* handle, int slot) {
+  Sched* s = static_cast<Sched*>(handle);
+  if (!s || slot < 0 || slot >= (int)s->requests.size() || !s->requests[slot].used) return 0;
+  auto in_waiting = std::find(s->waiting.begin(), s->waiting.end(), slot);
+  if (in_waiting != s->waiting.end()) {
+    s->waiting.erase(in_waiting);
+  } else if (is_running(s, slot)) {
+    remove_running(s, slot);
+  } else {
+    return 0;
+  }
+  finish(s, slot, REASON_ABORT, true);
+  return 1;
+}
+
+// the caller takes a running request out of the scheduler's hands (it keeps its pages)
+int hs_release(void* handle, int slot) {
+  Sched* s = static_cast<Sched*>(handle);
+  if (!s || !is_running(s, slot)) return fail(-4, "the request is not running");
+  remove_running(s, slot);
+  return 0;
+}
+
+int hs_mark_pending(void* handle, int slot, int delta) {
+  Sched* s = static_cast<Sched*>(handle);
+  s->requests[slot].pending += delta;
+  return s->requests[slot].pending;
+}
+
+// what a request's record holds: out[0..8] = handle, finished, reason, cached tokens, preemptions, published pages,
+// pending, outputs so far, decoding; out[9] admitted_at (low 31 bits)
+int hs_state(void* handle, int slot, int* out) {
+  Sched* s = static_cast<Sched*>(handle);
+  if (!s || slot < 0 || slot >= (int)s->requests.size() || !s->requests[slot].used) return fail(-1, "no such request");
+  const SchedRequest& r = s->requests[slot];
+  out[0] = r.handle; out[1] = r.finished; out[2] = r.reason; out[3] = r.cached_tokens; out[4] = r.preemptions;
+  out[5] = r.published_pages; out[6] = r.pending; out[7] = (int)r.output.size(); out[8] = is_decoding(s, r) ? 1 : 0;
+  out[9] = (int)(r.admitted_at & 0x7fffffff) * (r.admitted_at < 0 ? -1 : 1);
+  return 0;
+}
+
+int hs_outputs(void* handle, int slot, int from, int* out, int capacity) {
+  Sched* s = static_cast<Sched*>(handle);
+  const SchedRequest& r = s->requests[slot];
+  int written = 0;
+  for (int i = from; i < (int)r.output.size() && written < capacity; ++i) out[written++] = r.output[i];
+  return written;
+}
+
+int hs_queue(void* handle, int which /* 0 waiting, 1 running */, int* out, int capacity) {
+  Sched* s = static_cast<Sched*>(handle);
+  int written = 0;
+  if (which == 0) {
+    for (int slot : s->waiting)
+      if (written < capacity) out[written++] = slot;
+    return (int)s->waiting.size();
+  }
+  for (int slot : s->running)
+    if (written < capacity) out[written++] = slot;
+  return (int)s->running.size();
+}
+
+// cache requests opened (1, handle, request) and closed (0, handle, -1) since the last call, in order
+int hs_handle_events(void* handle, int* out, int capacity) {
+  Sched* s = static_cast<Sched*>(handle);
+  const int count = (int)s->events.size();
+  if (count > capacity) return fail(-1, "the event buffer is too small");
+  std::copy(s->events.begin(), s->events.end(), out);
+  s->events.clear();
+  return count / 3;
+}
+
+// requests that were admitted, preempted or finished since the last call
+int hs_touched(void* handle, int* out, int capacity) {
+  Sched* s = static_cast<Sched*>(handle);
+  std::sort(s->touched.begin(), s->touched.end());
+  s->touched.erase(std::unique(s->touched.begin(), s->touched.end()), s->touched.end());
+  const int count = (int)s->touched.size();
+  if (count > capacity) return fail(-1, "the buffer is too small");
+  std::copy(s->touched.begin(), s->touched.end(), out);
+  s->touched.clear();
+  return count;
+}
+
+// for tests that build a state by hand: a waiting request becomes a running one on a cache request
+int hs_force_running(void* handle, int slot, int cache_request, int admitted_at) {
+  Sched* s = static_cast<Sched*>(handle);
+  auto in_waiting = std::find(s->waiting.begin(), s->waiting.end(), slot);
+  if (in_waiting == s->waiting.end()) return fail(-4, "the request is not waiting");
+  s->waiting.erase(in_waiting);
+  s->requests[slot].handle = cache_request;
+  s->requests[slot].admitted_at = admitted_at;
+  s->running.push_back(slot);
+  return 0;
+}
+
+int hs_stats(void* handle, long long* out /* steps, preemptions, failed_cache_full, scheduled_tokens */) {
+  Sched* s = static_cast<Sched*>(handle);
+  out[0] = s->steps; out[1] = s->preemptions; out[2] = s->failed_cache_full; out[3] = s->scheduled_tokens;
+  return 0;
+}
+
+}  // extern "C"

@@ -189,7 +189,7 @@ class Engine:
                 done = torch.cuda.Event()
                 done.record()
                 for request in sampling:
-                    request.pending += 1
+                    self.scheduler.mark_pending(request)
                 return _StepInFlight(entries, picked[:len(sampled)].to(self.device, non_blocking=True), picked, done)
             picked = self.sampler.pick_on_device(logits, [r.sampling for r in sampling],
                                                  [self._randoms[r.request_id] for r in sampling])
@@ -202,7 +202,7 @@ class Engine:
             self.scheduler.step_failed(entries)
             raise
         for request in sampling:
-            request.pending += 1
+            self.scheduler.mark_pending(request)
         return _StepInFlight(entries, picked, host, done)
 
     def drain(self) -> List[StepOutput]:

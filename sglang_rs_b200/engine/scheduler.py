@@ -21,15 +21,20 @@ share a step.  When pages run out:
    are kept, and it goes back to the head of the waiting queue to be recomputed;
 3. a request that could not fit even with the whole pool to itself is finished with the
    reason ``"cache_full"``; nothing else is disturbed.
+
+The decisions themselves are taken in C++ (the scheduler section of csrc/host_core.cu, which
+works on the cache's books directly); this module holds the request and entry types and the
+class that keeps the Python ``Request`` objects in step with the records there.
 """
 from __future__ import annotations
 
-import itertools
-from collections import deque
+import ctypes
 from dataclasses import dataclass, field
-from typing import Deque, Dict, Hashable, List, Optional, Sequence
+from typing import Dict, Hashable, List, Optional, Sequence
 
-from ..cache.manager import CacheManager, OutOfPages, OutOfStateSlots, RequestCache
+import numpy as np
+
+from ..cache.manager import CacheManager, RequestCache
 from ..sampling.params import SamplingParams
 
 
@@ -49,6 +54,9 @@ class Request:
     #: tokens that a step has chosen for this request but that have not reached the host yet (0 or 1):
     #: they count as tokens of the request, their values are on the device
     pending: int = 0
+    #: the request's record in the C++ scheduler (-1: none), and whether its end has been reported
+    slot: int = field(default=-1, repr=False)
+    reported: bool = field(default=False, repr=False)
 
     @property
     def tokens(self) -> List[int]:
@@ -87,6 +95,8 @@ class ScheduledEntry:
     samples: bool
     #: True if the entry's one token (-1 here) was chosen by the step before and is still on the device
     from_device: bool = False
+    #: the entry as the C++ scheduler gave it: request record, first position, rows, samples, from_device
+    record: tuple = (0, 0, 0, 0, 0)
 
 
 @dataclass
@@ -106,41 +116,173 @@ class SchedulerConfig:
     default_stop_token_ids: Sequence[int] = ()
 
 
+REASONS = {0: None, 1: "stop", 2: "length", 3: "context", 4: "cache_full", 5: "abort"}
+
+
 class Scheduler:
+    """The decisions are taken in C++ (csrc/host_core.cu, beside the cache's books); this class keeps
+    the Python ``Request`` objects in step with the records there."""
+
     def __init__(self, cache: CacheManager, config: SchedulerConfig):
         if config.chunked_prefill_size <= 0 or config.max_running_requests <= 0:
             raise ValueError("the token budget and the running limit must be positive")
         self.cache, self.config = cache, config
-        self.waiting: Deque[Request] = deque()
-        self.running: List[Request] = []
-        self.finished_unreported: List[StepOutput] = []
-        self._clock = itertools.count()
-        self.stats = {"steps": 0, "preemptions": 0, "failed_cache_full": 0, "scheduled_tokens": 0}
+        lib = self._lib = cache._lib
+        lib.hs_create.restype = ctypes.c_void_p
+        lib.hs_create.argtypes = [ctypes.c_void_p, ctypes.c_void_p, ctypes.c_int, ctypes.c_int, ctypes.c_int,
+                                  ctypes.c_void_p, ctypes.c_int]
+        lib.hs_destroy.argtypes = [ctypes.c_void_p]
+        lib.hs_set_tree.argtypes = [ctypes.c_void_p, ctypes.c_void_p]
+        for name in ("hs_add", "hs_forget", "hs_has_work", "hs_schedule", "hs_entries", "hs_entry_tokens", "hs_process",
+                     "hs_step_failed", "hs_abort", "hs_release", "hs_mark_pending", "hs_state", "hs_outputs", "hs_queue",
+                     "hs_handle_events", "hs_stats", "hs_force_running", "hs_touched"):
+            getattr(lib, name).restype = ctypes.c_int
+        stops = np.ascontiguousarray(list(config.default_stop_token_ids) or [0], dtype=np.int32)
+        pointer = lib.hs_create(cache._pointer, None, int(config.max_running_requests), int(config.chunked_prefill_size),
+                                int(config.max_positions), ctypes.c_void_p(stops.ctypes.data),
+                                len(config.default_stop_token_ids))
+        if not pointer:
+            raise ValueError("the scheduler could not be made")
+        self._pointer = ctypes.c_void_p(pointer)
+        self._requests: Dict[int, Request] = {}             # record in the C++ scheduler -> request
+        self._by_handle: Dict[int, Request] = {}            # request of the cache books -> request
+        self._state = np.zeros(16, dtype=np.int32)
+        self._ended: set = set()                            # finished and reported, record not yet given back
+        self._tree = None
+
+    def __del__(self):
+        try:
+            if getattr(self, "_pointer", None):
+                self._lib.hs_destroy(self._pointer)
+        except Exception:
+            pass
+
+    # ------------------------------------------------------------------ keeping both sides in step
+    def _use_tree(self) -> None:
+        tree = self.cache.prefix_tree
+        if tree is not self._tree:
+            self._lib.hs_set_tree(self._pointer, tree._pointer if tree is not None else None)
+            self._tree = tree
+
+    def _sync(self, request: Request) -> None:
+        state = self._state
+        self._lib.hs_state(self._pointer, request.slot, ctypes.c_void_p(state.ctypes.data))
+        request.finished = bool(state[1])
+        request.finish_reason = REASONS[int(state[2])]
+        request.cached_tokens, request.preemptions = int(state[3]), int(state[4])
+        request.published_pages, request.pending = int(state[5]), int(state[6])
+        request.admitted_at = int(state[9])
+        have, total = len(request.output_ids), int(state[7])
+        if total > have:
+            fresh = np.empty(total - have, dtype=np.int32)
+            self._lib.hs_outputs(self._pointer, request.slot, have, ctypes.c_void_p(fresh.ctypes.data), len(fresh))
+            request.output_ids.extend(fresh.tolist())
+
+    def _handle_events(self) -> None:
+        """Cache requests that the C++ side opened or closed get (or lose) their Python handles."""
+        capacity = 3 * 64
+        while True:
+            out = np.empty(capacity, dtype=np.int32)
+            count = self._lib.hs_handle_events(self._pointer, ctypes.c_void_p(out.ctypes.data), capacity)
+            if count >= 0:
+                break
+            capacity *= 4
+        for kind, handle_index, slot in out[:3 * count].reshape(-1, 3).tolist():
+            if kind == 1:
+                request = self._requests[slot]
+                request.handle = self.cache.attach(request.request_id, handle_index)
+                self._by_handle[handle_index] = request
+            else:
+                request = self._by_handle.pop(handle_index, None)
+                if request is not None and request.handle is not None:
+                    self.cache.detach(request.handle)
+                    request.handle = None
 
     # ------------------------------------------------------------------ requests
     def add_request(self, request: Request) -> None:
         if not request.prompt:
             raise ValueError(f"request {request.request_id!r} has an empty prompt")
-        if any(r.request_id == request.request_id for r in itertools.chain(self.waiting, self.running)):
+        if any(r.request_id == request.request_id and not r.finished for r in self._requests.values()):
             raise ValueError(f"request {request.request_id!r} is queued already")
-        self.waiting.append(request)
+        prompt = np.ascontiguousarray(request.prompt, dtype=np.int32)
+        stops = np.ascontiguousarray(list(request.sampling.stop_token_ids) or [0], dtype=np.int32)
+        slot = self._lib.hs_add(self._pointer, ctypes.c_void_p(prompt.ctypes.data), len(prompt),
+                                int(min(request.sampling.max_new_tokens, 1 << 30)), ctypes.c_void_p(stops.ctypes.data),
+                                len(request.sampling.stop_token_ids), int(bool(request.sampling.ignore_eos)))
+        if slot < 0:
+            raise ValueError(self._lib.srb_last_error().decode())
+        stale = self._requests.get(slot)
+        if stale is not None:
+            stale.slot = -1
+        request.slot = slot
+        self._requests[slot] = request
+
+    def _forget_finished(self) -> None:
+        """Records of finished requests may be used again (their Python objects keep what they hold)."""
+        for slot in list(self._ended):
+            request = self._requests[slot]
+            self._sync(request)
+            if request.reported and request.pending == 0:    # no step in flight still names the record
+                self._lib.hs_forget(self._pointer, slot)
+                del self._requests[slot]
+                self._ended.discard(slot)
+                request.slot = -1
 
     def abort(self, request_id: Hashable) -> bool:
-        for queue in (self.waiting, self.running):
-            for request in list(queue):
-                if request.request_id == request_id:
-                    queue.remove(request)
-                    self._finish(request, "abort")
-                    return True
+        for request in list(self._requests.values()):
+            if request.request_id == request_id and not request.finished:
+                done = self._lib.hs_abort(self._pointer, request.slot) == 1
+                self._handle_events()
+                self._sync_touched()
+                self._sync(request)
+                return done
         return False
 
     def abort_all(self) -> int:
-        ids = [r.request_id for r in itertools.chain(self.waiting, self.running)]
+        ids = [r.request_id for r in self._requests.values() if not r.finished]
         return sum(self.abort(i) for i in ids)
 
     @property
     def has_work(self) -> bool:
-        return bool(self.waiting or self.running)
+        return bool(self._lib.hs_has_work(self._pointer))
+
+    def _queue(self, which: int) -> List[Request]:
+        out = np.empty(len(self._requests) + 1, dtype=np.int32)
+        count = self._lib.hs_queue(self._pointer, which, ctypes.c_void_p(out.ctypes.data), len(out))
+        return [self._requests[slot] for slot in out[:count].tolist()]
+
+    @property
+    def waiting(self) -> List[Request]:
+        return self._queue(0)
+
+    @property
+    def running(self) -> List[Request]:
+        return self._queue(1)
+
+    @property
+    def stats(self) -> Dict[str, int]:
+        out = np.zeros(4, dtype=np.int64)
+        self._lib.hs_stats(self._pointer, ctypes.c_void_p(out.ctypes.data))
+        return {"steps": int(out[0]), "preemptions": int(out[1]), "failed_cache_full": int(out[2]),
+                "scheduled_tokens": int(out[3])}
+
+    def release(self, request: Request) -> None:
+        """Takes a running request out of the scheduler's hands; the caller now owns its cache handle."""
+        if self._lib.hs_release(self._pointer, request.slot) < 0:
+            raise RuntimeError(self._lib.srb_last_error().decode())
+        self._by_handle.pop(request.handle.index, None)
+
+    def mark_pending(self, request: Request, delta: int = 1) -> None:
+        """A token was chosen for the request on the device and has not reached the host yet (+1), or
+        it has (-1, which ``process_outputs`` does by itself)."""
+        request.pending = self._lib.hs_mark_pending(self._pointer, request.slot, int(delta))
+
+    def _force_running(self, request: Request, handle: RequestCache, admitted_at: int) -> None:
+        """For tests that build a state by hand: a waiting request becomes a running one on ``handle``."""
+        if self._lib.hs_force_running(self._pointer, request.slot, handle.index, int(admitted_at)) < 0:
+            raise RuntimeError(self._lib.srb_last_error().decode())
+        request.handle, request.admitted_at = handle, admitted_at
+        self._by_handle[handle.index] = request
 
     # ------------------------------------------------------------------ one step's decisions
     def schedule(self, ahead: bool = False) -> List[ScheduledEntry]:
@@ -149,182 +291,78 @@ class Scheduler:
         ``ahead``: the step before has not reported its tokens yet (requests have ``pending``
         tokens).  The caller has made sure that every running request can get a page, so nothing
         is preempted; a step with nothing to do is then no deadlock, only a wait for those tokens."""
-        while True:
-            entries = self._schedule_once()
-            if entries or not self.running or ahead:
-                break
-            # Nothing could move although requests are running: prompts in progress hold all
-            # pages between them.  The one admitted last gives its pages up.
-            self._preempt(self._youngest_running(), entries)
-        self.stats["steps"] += 1
-        self.stats["scheduled_tokens"] += sum(len(e.tokens) for e in entries)
-        return entries
-
-    def _schedule_once(self) -> List[ScheduledEntry]:
-        budget = self.config.chunked_prefill_size
+        self._use_tree()
+        count = self._lib.hs_schedule(self._pointer, int(ahead))
+        if count < 0:
+            raise RuntimeError(self._lib.srb_last_error().decode())
+        self._handle_events()
+        table = np.empty((max(count, 1), 5), dtype=np.int32)
+        self._lib.hs_entries(self._pointer, ctypes.c_void_p(table.ctypes.data))
+        total = int(table[:count, 2].sum()) if count else 0
+        tokens = np.empty(max(total, 1), dtype=np.int32)
+        if self._lib.hs_entry_tokens(self._pointer, ctypes.c_void_p(tokens.ctypes.data), len(tokens)) < 0:
+            raise RuntimeError(self._lib.srb_last_error().decode())
         entries: List[ScheduledEntry] = []
-        preempted_before = self.stats["preemptions"]
-
-        # 1. every decoding request gets its one row; make room by preemption if needed
-        decoding = [r for r in self.running if self._is_decoding(r)]
-        for request in decoding:
-            if request not in self.running:
-                continue                                     # preempted below, earlier in this loop
-            if self._ends_whatever_comes(request):
-                continue                                     # it finishes when its token arrives
-            while True:
-                try:
-                    self.cache.reserve(request.handle, 1)
-                    break
-                except OutOfPages:
-                    victim = self._youngest_running()
-                    if victim is request and len(self.running) == 1:
-                        # alone and the pool is full of its own tokens: it can never go on
-                        self.running.remove(request)
-                        self._finish(request, "cache_full")
-                        self.stats["failed_cache_full"] += 1
-                        break
-                    self._preempt(victim, entries)
-                    if victim is request:
-                        break
-            if request in self.running and not request.finished:
-                entries.append(ScheduledEntry(request, [request.last_token], True, from_device=request.pending > 0))
-                budget -= 1
-
-        # 2. prompts in progress go on, oldest first; 3. then new requests are admitted
-        for request in [r for r in self.running if not self._is_decoding(r)]:
-            if budget <= 0:
-                break
-            if request.pending:
-                continue
-            if any(e.request is request for e in entries):
-                continue
-            budget -= self._schedule_portion(request, budget, entries)
-        while self.waiting and budget > 0 and len(self.running) < self.config.max_running_requests:
-            if self.stats["preemptions"] != preempted_before and self.running:
-                break                                        # pages were just taken away: admit nobody this step
-            request = self.waiting[0]
-            if self._can_never_fit(request):
-                self.waiting.popleft()
-                self._finish(request, "cache_full")
-                self.stats["failed_cache_full"] += 1
-                continue
-            try:
-                request.handle = self.cache.open(request.request_id)
-            except OutOfStateSlots:
-                break
-            tree = self.cache.prefix_tree
-            if tree is not None:
-                shared = tree.match(request.tokens)
-                if shared:
-                    self.cache.adopt_prefix(request.handle, ("kv", None), shared)
-                    request.published_pages = len(shared)
-                    if not request.preemptions:
-                        request.cached_tokens = min(request.handle.length, len(request.prompt))
-            taken = self._schedule_portion(request, budget, entries)
-            if taken == 0:
-                self.cache.close(request.handle)             # no page free: it stays at the head
-                request.handle = None
-                break
-            self.waiting.popleft()
-            request.admitted_at = next(self._clock)
-            self.running.append(request)
-            budget -= taken
+        at = 0
+        for slot, start, rows, samples, from_device in table[:count].tolist():
+            request = self._requests[slot]
+            entries.append(ScheduledEntry(request, tokens[at:at + rows].tolist(), bool(samples), bool(from_device),
+                                          record=(slot, start, rows, samples, from_device)))
+            at += rows
+        self._sync_touched()
+        for entry in entries:
+            self._sync(entry.request)
         return entries
+
+    def _sync_touched(self) -> None:
+        """Whoever was admitted, preempted or finished since the last call shows it."""
+        out = np.empty(len(self._requests) + 1, dtype=np.int32)
+        count = self._lib.hs_touched(self._pointer, ctypes.c_void_p(out.ctypes.data), len(out))
+        for slot in out[:max(count, 0)].tolist():
+            request = self._requests.get(slot)
+            if request is not None:
+                self._sync(request)
 
     def _is_decoding(self, request: Request) -> bool:
-        return (request.handle is not None and bool(request.output_ids or request.pending)
-                and request.computed == request.num_tokens - 1)
-
-    def _ends_whatever_comes(self, request: Request) -> bool:
-        """True if the token still on the device is the request's last, whichever it is."""
-        return request.pending > 0 and (
-            len(request.output_ids) + request.pending >= request.sampling.max_new_tokens
-            or request.num_tokens >= self.config.max_positions)
-
-    def _schedule_portion(self, request: Request, budget: int, entries: List[ScheduledEntry]) -> int:
-        total = request.num_tokens
-        start = request.computed
-        count = min(budget, total - start)
-        # cut the portion down to the pages that are free
-        while count > 0 and not self.cache.can_reserve(request.handle, count):
-            free = min(self.cache.free_pages().values(), default=0)
-            room = self.cache.capacity(request.handle) - start + free * self.cache.page_size
-            count = min(count - 1, max(room, 0))
-        if count <= 0:
-            return 0
-        self.cache.reserve(request.handle, count)
-        entries.append(ScheduledEntry(request, request.tokens_from(start, count), start + count == total))
-        return count
-
-    def _can_never_fit(self, request: Request) -> bool:
-        # prompt (and what was generated before a preemption) plus the token to be sampled next
-        need = -(-(request.num_tokens + 1) // self.cache.page_size)
-        return any(need > allocator.num_pages for key, allocator in self.cache.allocators.items()
-                   if self.cache.windows[key] is None)
-
-    def _youngest_running(self) -> Request:
-        return max(self.running, key=lambda r: r.admitted_at)
-
-    def _preempt(self, victim: Request, entries: List[ScheduledEntry]) -> None:
-        entries[:] = [e for e in entries if e.request is not victim]
-        self.running.remove(victim)
-        self.cache.close(victim.handle)
-        victim.handle = None
-        victim.published_pages = 0
-        victim.preemptions += 1
-        self.stats["preemptions"] += 1
-        self.waiting.appendleft(victim)
+        if request.slot < 0:
+            return False
+        self._lib.hs_state(self._pointer, request.slot, ctypes.c_void_p(self._state.ctypes.data))
+        return bool(self._state[8])
 
     # ------------------------------------------------------------------ after the step
     def process_outputs(self, entries: Sequence[ScheduledEntry], sampled: Sequence[int]) -> List[StepOutput]:
         """``sampled``: one token per entry with ``samples`` set, in order.  The runner has
         committed the rows already."""
-        outputs: List[StepOutput] = list(self.finished_unreported)
-        self.finished_unreported.clear()
-        picks = iter(sampled)
-        tree = self.cache.prefix_tree
+        self._use_tree()
+        records = np.ascontiguousarray([e.record for e in entries] or [[0] * 5], dtype=np.int32)
+        picks = np.ascontiguousarray(list(sampled) or [0], dtype=np.int32)
+        out = np.empty((len(entries) + len(self._requests) + 1, 5), dtype=np.int32)
+        count = self._lib.hs_process(self._pointer, ctypes.c_void_p(records.ctypes.data), len(entries),
+                                     ctypes.c_void_p(picks.ctypes.data), len(sampled), ctypes.c_void_p(out.ctypes.data),
+                                     len(out))
+        if count < 0:
+            raise RuntimeError(self._lib.srb_last_error().decode())
+        self._handle_events()
+        self._sync_touched()
+        outputs: List[StepOutput] = []
+        for slot, token, cached, finished, reason in out[:count].tolist():
+            request = self._requests[slot]
+            self._sync(request)
+            if finished:
+                request.reported = True
+                self._ended.add(slot)
+            outputs.append(StepOutput(request.request_id, [token] if token >= 0 else [], cached, bool(finished),
+                                      REASONS[reason]))
         for entry in entries:
-            request = entry.request
-            if tree is not None and request.handle is not None:
-                # full pages of prompt tokens become known as soon as they are computed
-                full = min(request.handle.length, len(request.prompt)) // self.cache.page_size
-                if full > request.published_pages:
-                    tree.insert(request.prompt[:full * self.cache.page_size], request.handle.table(("kv", None))[:full])
-                    request.published_pages = full
-            if not entry.samples:
-                continue
-            token = int(next(picks))
-            request.pending = max(0, request.pending - 1)
-            if request.finished:
-                continue                     # it ended (stop token, abort) while this step was already running
-            request.output_ids.append(token)
-            stops = set(request.sampling.stop_token_ids) | set(self.config.default_stop_token_ids)
-            reason = None
-            if token in stops and not request.sampling.ignore_eos:
-                reason = "stop"
-            elif len(request.output_ids) >= request.sampling.max_new_tokens:
-                reason = "length"
-            elif request.num_tokens >= self.config.max_positions:
-                reason = "context"
-            if reason:
-                self.running.remove(request)
-                self._finish(request, reason, report=False)
-            outputs.append(StepOutput(request.request_id, [token], request.cached_tokens, request.finished, reason))
+            self._sync(entry.request)
+        self._forget_finished()
         return outputs
 
     def step_failed(self, entries: Sequence[ScheduledEntry]) -> None:
         """The step raised: every request of the batch is failed and gives its pages back."""
+        records = np.ascontiguousarray([e.record for e in entries] or [[0] * 5], dtype=np.int32)
+        self._lib.hs_step_failed(self._pointer, ctypes.c_void_p(records.ctypes.data), len(entries))
+        self._handle_events()
+        self._sync_touched()
         for entry in entries:
-            if entry.request in self.running:
-                self.running.remove(entry.request)
-                self._finish(entry.request, "abort")
-
-    def _finish(self, request: Request, reason: str, report: bool = True) -> None:
-        if request.handle is not None:
-            self.cache.close(request.handle)
-            request.handle = None
-        request.finished, request.finish_reason = True, reason
-        if report:
-            self.finished_unreported.append(
-                StepOutput(request.request_id, [], request.cached_tokens, True, reason))
+            self._sync(entry.request)

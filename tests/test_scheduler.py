@@ -156,9 +156,7 @@ def test_running_requests_that_all_starve_are_resolved_by_preemption():
     a.handle, b.handle = cache.open("a"), cache.open("b")
     for r, stamp in ((a, -3), (b, -2)):
         cache.reserve(r.handle, 16); cache.commit(r.handle, 16)
-        r.admitted_at = stamp
-        scheduler.waiting.remove(r)
-        scheduler.running.append(r)
+        scheduler._force_running(r, r.handle, stamp)
     assert cache.free_pages()[FULL] == 0
     drain(scheduler, cache)
     assert b.preemptions >= 1 and a.preemptions == 0
@@ -268,7 +266,7 @@ class FakeOverlappedEngine:
             tokens.append(next_token(known) if entry.samples else None)
         for entry in entries:
             if entry.samples:
-                entry.request.pending += 1
+                self.scheduler.mark_pending(entry.request)
         return list(zip(entries, tokens))
 
     def step(self):
