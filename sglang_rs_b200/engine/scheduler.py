@@ -309,9 +309,7 @@ class Scheduler:
             entries.append(ScheduledEntry(request, tokens[at:at + rows].tolist(), bool(samples), bool(from_device),
                                           record=(slot, start, rows, samples, from_device)))
             at += rows
-        self._sync_touched()
-        for entry in entries:
-            self._sync(entry.request)
+        self._sync_touched()          # entries alone change nothing that a Request shows
         return entries
 
     def _sync_touched(self) -> None:
@@ -344,17 +342,20 @@ class Scheduler:
             raise RuntimeError(self._lib.srb_last_error().decode())
         self._handle_events()
         self._sync_touched()
+        for entry in entries:
+            if entry.samples and entry.request.pending:
+                entry.request.pending -= 1               # the token has arrived (or its row was in vain)
         outputs: List[StepOutput] = []
         for slot, token, cached, finished, reason in out[:count].tolist():
             request = self._requests[slot]
-            self._sync(request)
+            if token >= 0 and not finished:
+                request.output_ids.append(token)         # a request that ended was brought up to date above
+            request.cached_tokens = cached
             if finished:
                 request.reported = True
                 self._ended.add(slot)
             outputs.append(StepOutput(request.request_id, [token] if token >= 0 else [], cached, bool(finished),
                                       REASONS[reason]))
-        for entry in entries:
-            self._sync(entry.request)
         self._forget_finished()
         return outputs
 
