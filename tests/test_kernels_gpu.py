@@ -47,6 +47,31 @@ def test_embedding_and_bad_token(dtype):
     ops.raise_on_error_word(word)                         # reading it cleared it
 
 
+def test_tokens_taken_from_the_step_before():
+    """Rows whose token was chosen on the device by the step before take it from there; the others
+    keep what the host wrote; an index outside the source is flagged and the row left alone."""
+    g = torch.Generator().manual_seed(1)
+    rows = 300
+    tokens = torch.randint(0, 1000, (rows,), generator=g, dtype=torch.int32)
+    source = torch.randint(1000, 2000, (77,), generator=g, dtype=torch.int32)
+    index = torch.full((rows,), -1, dtype=torch.int32)
+    chosen = torch.randperm(rows, generator=g)[:120]
+    index[chosen] = torch.randint(0, 77, (120,), generator=g, dtype=torch.int32)
+    want = tokens.clone()
+    want[chosen] = source[index[chosen].long()]
+    word = ops.new_error_word(DEV)
+    got = tokens.to(DEV)
+    ops.take_tokens(got, source.to(DEV), index.to(DEV), word)
+    ops.raise_on_error_word(word)
+    assert torch.equal(got.cpu(), want)
+    index[5] = 77
+    got = tokens.to(DEV)
+    ops.take_tokens(got, source.to(DEV), index.to(DEV), word)
+    assert int(got[5]) == int(tokens[5])
+    with pytest.raises(ops.KernelError, match="token id outside"):
+        ops.raise_on_error_word(word)
+
+
 @pytest.mark.parametrize("dtype", DTYPES)
 @pytest.mark.parametrize("width", [72, 100, 1023, 5120, 16400])
 def test_add_rmsnorm(dtype, width):
