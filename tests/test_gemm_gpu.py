@@ -103,3 +103,29 @@ def test_sizes_tma_cannot_take_are_refused():
     with pytest.raises(ops.KernelError, match="multiples of 8"):
         ops.gemm_bf16(x.to(DEV), w.to(DEV), ops.new_error_word(DEV))
     assert not ops.gemm_bf16_takes(68) and ops.gemm_bf16_takes(72)
+
+
+@pytest.mark.parametrize("tokens,features,k", [(256, 256, 64), (300, 640, 328), (2048, 512, 1024), (513, 257, 136),
+                                               (130, 1000, 200), (1100, 96, 4096)])
+def test_product_on_pairs_of_ctas(tokens, features, k):
+    """The persistent kernel for many tokens: 256 x 256 tiles on CTA pairs (cta_group::2), two
+    accumulators in tensor memory; sizes that are no multiple of a tile, several tiles per pair."""
+    x, w = operands(tokens, features, k, seed=tokens + features)
+    word = ops.new_error_word(DEV)
+    want = pm.plain_linear(x.double(), w.double())
+    got = ops.gemm_bf16_pair(x.to(DEV), w.to(DEV), word, mode="bf16")
+    ops.raise_on_error_word(word)
+    assert got.shape == (tokens, features) and relative_error(got, want) < 5e-3
+    again = ops.gemm_bf16_pair(x.to(DEV), w.to(DEV), word, mode="bf16")
+    assert torch.equal(again, got)
+
+
+@pytest.mark.parametrize("tokens,inner,k", [(256, 128, 64), (700, 200, 72), (1030, 256, 512), (300, 130, 200)])
+def test_gate_up_with_silu_on_pairs_of_ctas(tokens, inner, k):
+    x, w = operands(tokens, 2 * inner, k, seed=5 + inner)
+    word = ops.new_error_word(DEV)
+    got = ops.gemm_bf16_pair(x.to(DEV), w.to(DEV), word, mode="silu", features=inner, up_row_offset=inner)
+    ops.raise_on_error_word(word)
+    gate_up = pm.plain_linear(x.double(), w.double())
+    want = pm.plain_silu_mul(gate_up[:, :inner], gate_up[:, inner:])
+    assert got.shape == (tokens, inner) and relative_error(got, want) < 1e-2
