@@ -31,10 +31,15 @@ def build_parser() -> argparse.ArgumentParser:
     gen.add_argument("--random-weights", action="store_true", help="ignore the folder's weights; draw them from --seed")
     gen.add_argument("--seed", type=int, default=0)
     gen.add_argument("--page-size", type=int, default=16)
-    gen.add_argument("--max-total-tokens", type=int, default=None)
+    gen.add_argument("--max-total-tokens", "--num-reserved-decode-tokens", dest="max_total_tokens", type=int, default=None,
+                     help="tokens the live requests may hold together (the reference counts token slots under the "
+                          "second name)")
     gen.add_argument("--mem-fraction-static", type=float, default=0.85)
     gen.add_argument("--max-running-requests", type=int, default=256)
-    gen.add_argument("--chunked-prefill-size", type=int, default=2048)
+    gen.add_argument("--chunked-prefill-size", "--max-prefill-tokens", dest="chunked_prefill_size", type=int, default=2048,
+                     help="token budget of one step: decoded tokens first, prompt portions fill the rest")
+    gen.add_argument("--kv-cache-dtype", default="auto", choices=("auto",),
+                     help="the cache has the model's dtype; quantized caches are not built")
     gen.add_argument("--disable-cuda-graph", action="store_true")
     gen.add_argument("--disable-radix-cache", action="store_true")
     gen.add_argument("--disable-overlap-schedule", action="store_true",
