@@ -51,6 +51,18 @@ def check(rows, expected, tolerance, requests, what):
     assert bad is None, f"{what}: first wrong row: request {bad[0]} position {bad[1]} error {bad[2]:.3e} (tolerance {tolerance})"
 
 
+@pytest.mark.parametrize("page", [8, 64, 128])
+def test_other_page_sizes_of_the_tensor_core_kernels(prepared, page):
+    """Head_dim 128 in bfloat16 with pages of 8 and 64 tokens (several pages, or one, per 64-key block
+    of the tcgen05 attention) and of 128 (which that kernel refuses: the mma.sync kernel takes the
+    portions), portions mixed with decoded tokens."""
+    folder, requests, expected, _ = prepared("D", "bfloat16")
+    trace = rh.trace_mixed(requests, seed=4)
+    rows, session = rh.run_in_process(folder, "bfloat16", trace, max_tokens=rh.max_tokens_of(trace, max(64, page)),
+                                      page_size=page)           # pages larger than 64 round a request up to their own size
+    check(rows, expected, rh.BF16_TOLERANCE, requests, f"D/bfloat16/mixed/page {page}")
+
+
 @pytest.mark.parametrize("dtype_name", list(DTYPES))
 @pytest.mark.parametrize("case", list(CASES))
 @pytest.mark.parametrize("mode", ["whole", "tail", "portions", "mixed"])
