@@ -343,20 +343,39 @@ decode_attention_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16
     if (lane == 0) weights[head * (count + 1) + count] = 1.0f / l;
   }
   __syncthreads();
-  for (int i = threadIdx.x; i < groups * D; i += blockDim.x) {
-    const int head = i / D, e = i % D;
-    const size_t first = ((size_t)row * p.n_q + (size_t)kv_head * groups + head) * p.max_splits;
-    const float* w = weights + head * (count + 1);
-    float acc = 0.f;
-    for (int base = 0; base < count; base += 8) {          // eight loads in flight, added in split order
-      float v[8];
+  // four (head, element) pairs per thread and eight splits at a time: 32 loads in flight, added in split order
+  const int total = groups * D;
+  for (int i0 = threadIdx.x; i0 < total; i0 += 4 * blockDim.x) {
+    const float* src[4];
+    const float* w[4];
+    float acc[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
-      for (int j = 0; j < 8; ++j) v[j] = base + j < count ? __ldcg(part_acc + (first + base + j) * D + e) : 0.f;
-#pragma unroll
-      for (int j = 0; j < 8; ++j)
-        if (base + j < count) acc += v[j] * w[base + j];
+    for (int q = 0; q < 4; ++q) {
+      const int i = min(i0 + q * (int)blockDim.x, total - 1);
+      const int head = i / D, e = i % D;
+      src[q] = part_acc + ((size_t)row * p.n_q + (size_t)kv_head * groups + head) * p.max_splits * D + e;
+      w[q] = weights + head * (count + 1);
     }
-    out[((size_t)row * p.n_q + (size_t)kv_head * groups + head) * D + e] = __float2bfloat16_rn(acc * w[count]);
+    for (int base = 0; base < count; base += 8) {
+      float v[4][8];
+#pragma unroll
+      for (int q = 0; q < 4; ++q)
+#pragma unroll
+        for (int j = 0; j < 8; ++j) v[q][j] = base + j < count ? __ldcg(src[q] + (size_t)(base + j) * D) : 0.f;
+#pragma unroll
+      for (int q = 0; q < 4; ++q)
+#pragma unroll
+        for (int j = 0; j < 8; ++j)
+          if (base + j < count) acc[q] += v[q][j] * w[q][base + j];
+    }
+#pragma unroll
+    for (int q = 0; q < 4; ++q) {
+      const int i = i0 + q * (int)blockDim.x;
+      if (i < total) {
+        const int head = i / D, e = i % D;
+        out[((size_t)row * p.n_q + (size_t)kv_head * groups + head) * D + e] = __float2bfloat16_rn(acc[q] * w[q][count]);
+      }
+    }
   }
 }
 
