@@ -30,7 +30,7 @@ class PrefixTree:
         self.page_size, self.allocator = int(page_size), allocator
         self._lib = _core_library()
         for name in ("hc_tree_match", "hc_tree_insert", "hc_tree_evictable", "hc_tree_evict", "hc_tree_pages_held",
-                     "hc_tree_pages", "hc_tree_clear"):
+                     "hc_tree_pages", "hc_tree_clear", "hc_tree_counters"):
             getattr(self._lib, name).restype = ctypes.c_int
         self._lib.hc_tree_create.restype = ctypes.c_void_p
         self._lib.hc_tree_create.argtypes = [ctypes.c_void_p, ctypes.c_int, ctypes.c_int]
@@ -40,7 +40,6 @@ class PrefixTree:
         if not pointer:
             raise ValueError("the prefix tree could not be made for this group of pages")
         self._pointer = ctypes.c_void_p(pointer)
-        self.hits = self.lookups = 0
 
     def __del__(self):
         try:
@@ -49,19 +48,31 @@ class PrefixTree:
         except Exception:
             pass
 
+    def _counters(self):
+        out = np.zeros(2, dtype=np.int64)
+        self._lib.hc_tree_counters(self._pointer, _pointer(out))
+        return int(out[0]), int(out[1])
+
+    @property
+    def lookups(self) -> int:
+        """Prefix look-ups so far, the scheduler's among them."""
+        return self._counters()[0]
+
+    @property
+    def hits(self) -> int:
+        return self._counters()[1]
+
     @property
     def pages_held(self) -> int:
         return self._lib.hc_tree_pages_held(self._pointer)
 
     def match(self, tokens: Sequence[int]) -> List[int]:
         """Page ids of the longest known prefix of ``tokens``, leaving at least one token out."""
-        self.lookups += 1
         array = np.ascontiguousarray(tokens, dtype=np.int32)
         out = np.empty(max(len(array) // self.page_size, 1), dtype=np.int32)
         found = self._lib.hc_tree_match(self._pointer, _pointer(array), len(array), _pointer(out))
         if found < 0:
             raise RuntimeError(_message(self._lib))
-        self.hits += bool(found)
         return out[:found].tolist()
 
     def insert(self, tokens: Sequence[int], pages: Sequence[int]) -> int:

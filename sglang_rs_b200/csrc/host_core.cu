@@ -474,6 +474,7 @@ struct Tree {
   TreeNode root;
   long long clock = 0;
   int pages_held = 0;
+  long long lookups = 0, hits = 0;
 };
 
 void collect_leaves(TreeNode* node, std::vector<TreeNode*>& out) {
@@ -542,6 +543,8 @@ int hc_tree_match(void* handle, const int* tokens, int count, int* pages_out) {
     node->stamp = stamp;
     pages_out[found++] = node->page;
   }
+  ++tree->lookups;
+  tree->hits += found > 0 ? 1 : 0;
   return found;
 }
 
@@ -613,6 +616,15 @@ int hc_tree_evict(void* handle, int pages) {
     }
   }
   return freed;
+}
+
+// look-ups of prefixes so far (by the scheduler or through the Python face) and how many found something
+int hc_tree_counters(void* handle, long long* out) {
+  Tree* tree = static_cast<Tree*>(handle);
+  if (!tree) return fail(-1, "no tree");
+  out[0] = tree->lookups;
+  out[1] = tree->hits;
+  return 0;
 }
 
 int hc_tree_pages_held(void* handle) { return handle ? static_cast<Tree*>(handle)->pages_held : fail(-1, "no tree"); }
