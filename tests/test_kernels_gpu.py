@@ -355,18 +355,18 @@ def run_attention(case, scale, split_size):
     return out
 
 
-def run_decode(case, scale, counters):
+def run_decode(case, scale, counters, max_keys=None):
     q = case["q"]
     rows, n_q, d = q.shape
     n_kv = case["k_pool"].shape[1]
-    splits = ops.decode_splits(rows, n_kv)
+    splits = ops.decode_splits(rows, n_kv, max_keys)
     out = torch.full_like(q, float("nan"))
     word = ops.new_error_word(DEV)
     acc = torch.full((rows * n_q * splits * d,), float("nan"), device=DEV)
     ml = torch.full((rows * n_q * splits * 2,), float("nan"), device=DEV)
     ops.decode_attention(q, case["k_pool"], case["v_pool"], out, case["positions"], case["row_request"], case["table"],
                          scale=scale, window=case["window"] or 0, scratch_acc=acc, scratch_ml=ml, counters=counters,
-                         error_word=word)
+                         error_word=word, max_keys=max_keys)
     ops.raise_on_error_word(word)
     return out
 
@@ -391,6 +391,27 @@ def test_decode_attention_of_single_tokens(n_q, n_kv, d, page, window, lengths):
     assert int(counters.abs().sum()) == 0
     assert torch.equal(first, second)
     close(first, want, torch.bfloat16, "decode attention")
+
+
+@pytest.mark.parametrize("n_q,n_kv,d,page,window", [(32, 8, 128, 16, None), (12, 6, 64, 8, 500), (16, 1, 128, 32, None)])
+@pytest.mark.parametrize("splits", [1, 2, 5, 13])
+def test_decode_attention_with_more_blocks_than_run_at_once(n_q, n_kv, d, page, window, splits, monkeypatch):
+    """Many rows of very different lengths, cut into several times more blocks than run at once: the
+    same result whatever the number of blocks per row, twice in a row with the same counters, which
+    are zero again afterwards."""
+    rows = 1400 // (n_kv * splits) + 7
+    lengths = tuple(1 + (37 * i * i + 11 * i) % 1500 for i in range(rows))
+    assert rows * n_kv * splits > 3 * 148
+    case = paged_case(torch.bfloat16, n_q, n_kv, d, page, lengths, (1,) * rows, window, seed=rows)
+    scale = 1.0 / math.sqrt(d)
+    monkeypatch.setattr(ops, "decode_splits", lambda *a, **k: splits)
+    counters = torch.zeros(rows * n_kv, dtype=torch.int32, device=DEV)
+    first = run_decode(case, scale, counters, max_keys=max(lengths))
+    assert int(counters.abs().sum()) == 0
+    second = run_decode(case, scale, counters, max_keys=max(lengths))
+    assert int(counters.abs().sum()) == 0
+    assert torch.equal(first, second)
+    close(first, expected_attention(case, scale), torch.bfloat16, "decode attention, several waves of blocks")
 
 
 def test_decode_attention_finds_a_far_key_and_respects_the_window_edge():
