@@ -97,6 +97,36 @@ def test_add_rmsnorm(dtype, width):
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("width,parts,rows", [(4096, 9, 3), (4096, 9, 320), (2560, 16, 8), (2560, 17, 8), (264, 1, 64),
+                                              (5128, 0, 37), (8192, 3, 2)])
+def test_add_rmsnorm_of_few_and_of_many_rows(dtype, width, parts, rows):
+    """Residual, pending sum and up to 17 partial sums are added in that order, for few rows and for many,
+    at widths that take the vector kernel and widths that do not."""
+    g = torch.Generator().manual_seed(width + parts + rows)
+    residual = torch.randn(rows, width, generator=g) * 2
+    weight = 1 + 0.1 * torch.randn(width, generator=g)
+    eps = 1e-6
+    res_d = residual.to(DEV)
+    out = torch.full((rows, width), float("nan"), device=DEV, dtype=dtype)
+    if parts:
+        pieces = torch.randn(parts, rows, width, generator=g)
+        ops.add_rmsnorm(res_d, pieces.to(DEV), weight.to(DEV), eps, out)
+        summed = residual.double() + pieces.double().sum(0)
+    else:
+        delta = torch.randn(rows, width, generator=g)
+        ops.add_rmsnorm(res_d, delta.to(DEV, dtype), weight.to(DEV), eps, out)
+        summed = residual.double() + rounded(delta, dtype)
+    assert torch.allclose(res_d.cpu().double(), summed, atol=1e-5)
+    close(out, pm.plain_rms_norm(summed, weight.double(), eps), dtype, "add+norm")
+    pick = torch.tensor([rows - 1, 0], dtype=torch.int32, device=DEV)
+    out2 = torch.full((2, width), float("nan"), device=DEV, dtype=dtype)
+    before = res_d.clone()
+    ops.add_rmsnorm(res_d, None, weight.to(DEV), eps, out2, row_index=pick, write_residual=False)
+    assert torch.equal(res_d, before)
+    close(out2, pm.plain_rms_norm(summed[pick.cpu().long()], weight.double(), eps), dtype, "picked rows")
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
 def test_norm_and_rope_take_partial_sums(dtype):
     """A product cut along K hands its consumer float partial sums; they are added in order."""
     g = torch.Generator().manual_seed(2)
