@@ -35,6 +35,20 @@ def main():
     e0, e1 = math.exp(scale * 1.0 - scale), math.exp(0.0 - scale)
     anchors["attention"] = {"q": q, "k": [k0, k1], "v": [v0, v1], "scale": scale,
                             "y_last": [(e0 * v0[i] + e1 * v1[i]) / (e0 + e1) for i in range(2)], "y_first": v0}
+    # literal vectors of the reference's own tests, copied as data:
+    # grouped-query attention of one token, four query heads on two kv heads, scale 1
+    # (crates/sglang-kernel/tests/cpu_kernels.rs:174-190)
+    anchors["gqa_one_token"] = {"q": [1.0, 0.0, 0.0, 1.0, 1.0, 0.0, 0.0, 1.0], "k": [1.0, 0.0, 0.0, 1.0],
+                                "v": [2.0, 3.0, 5.0, 7.0], "query_heads": 4, "kv_heads": 2, "head_dim": 2,
+                                "scale": 1.0, "y": [2.0, 3.0, 2.0, 3.0, 5.0, 7.0, 5.0, 7.0]}
+    # the k largest probabilities of a row, renormalised (cpu_kernels.rs:200-238)
+    anchors["top_k_renorm"] = {"probs": [[0.1, 0.2, 0.7, 0.4], [0.3, 0.2, 0.1, 0.0]],
+                               "fixed_k": 2, "fixed_y": [[0.0, 0.0, 7.0 / 11.0, 4.0 / 11.0], [3.0 / 5.0, 2.0 / 5.0, 0.0, 0.0]],
+                               "per_row_k": [1, 3],
+                               "per_row_y": [[0.0, 0.0, 1.0, 0.0], [3.0 / 6.0, 2.0 / 6.0, 1.0 / 6.0, 0.0]]}
+    # rotation of the first four of six values only (cpu_kernels.rs:63-80)
+    anchors["rope_partial"] = {"x": [1.0, 2.0, 3.0, 4.0, 5.0, 6.0], "rotary_dim": 4, "position": 1, "theta": 1.0,
+                               "y": [1 * cos - 3 * sin, 2 * cos - 4 * sin, 3 * cos + 1 * sin, 4 * cos + 2 * sin, 5.0, 6.0]}
     path = os.path.join(os.path.dirname(os.path.abspath(__file__)), "plain_anchors.json")
     with open(path, "w") as handle:
         json.dump(anchors, handle, indent=1)

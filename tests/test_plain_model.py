@@ -1,4 +1,5 @@
-"""The plain implementation against hand-derived anchors and its own invariants (no GPU)."""
+"""The plain implementation against hand-derived anchors, vectors of the reference's own tests and its own
+invariants (no GPU)."""
 import json
 import os
 
@@ -52,6 +53,27 @@ def test_attention_anchor_and_grouping():
     windowed = pm.plain_attention(q, k, v, 0.3, window=2)
     tail = pm.plain_attention(q[2:3], k[1:3], v[1:3], 0.3, first_position=1)
     assert torch.allclose(windowed[2], tail[0]) and torch.allclose(windowed[:2], out[:2])
+
+
+def test_vectors_of_the_reference_tests():
+    """Inputs and expected outputs copied as data from the reference's own kernel tests
+    (crates/sglang-kernel/tests/cpu_kernels.rs:63-80, :174-190, :200-238)."""
+    a = ANCHORS["gqa_one_token"]
+    q = T(a["q"]).view(1, a["query_heads"], a["head_dim"])
+    k, v = T(a["k"]).view(1, a["kv_heads"], a["head_dim"]), T(a["v"]).view(1, a["kv_heads"], a["head_dim"])
+    assert torch.equal(pm.plain_attention(q, k, v, a["scale"]).reshape(-1), T(a["y"]))
+    a = ANCHORS["rope_partial"]
+    x = T(a["x"]).view(1, 1, 6)
+    got = pm.plain_rope_neox(x, torch.tensor([a["position"]]), pm.plain_inverse_frequencies(a["theta"], a["rotary_dim"]))
+    assert torch.allclose(got.reshape(-1), T(a["y"]), atol=1e-7)
+    a = ANCHORS["top_k_renorm"]
+    for row, (probs, fixed, k_row, per_row) in enumerate(zip(a["probs"], a["fixed_y"], a["per_row_k"], a["per_row_y"])):
+        logits = torch.log(T(probs))
+        for k, want in ((a["fixed_k"], fixed), (k_row, per_row)):
+            kept = pm.plain_filtered_distribution(logits, 1.0, top_k=k, top_p=None, min_p=None)
+            total = sum(kept.values())
+            got = [kept.get(i, 0.0) / total for i in range(len(probs))]
+            assert max(abs(g - w) for g, w in zip(got, want)) < 1e-12, (row, k, got, want)
 
 
 def one_hot_model():
