@@ -440,6 +440,15 @@ class CacheManager:
         """Pages that can be had now: free ones and those only the prefix tree holds."""
         return {key: allocator.free_count + self._reclaimable(key) for key, allocator in self.allocators.items()}
 
+    def can_take(self, count: int) -> bool:
+        """True if every group could hand out ``count`` pages now.  The prefix tree is only searched
+        for pages it could give up when the free ones do not do."""
+        for key, allocator in self.allocators.items():
+            free = allocator.free_count
+            if free < count and free + self._reclaimable(key) < count:
+                return False
+        return True
+
     def layer_cache(self, call_index: int):
         return self.layer_caches[call_index]
 

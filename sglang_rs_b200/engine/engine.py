@@ -159,8 +159,7 @@ class Engine:
         needs no token history, and every running request can get a page without preemption."""
         if self._host_only_sampling:
             return False
-        running = len(self.scheduler.running)
-        return all(free >= running for free in self.cache.free_pages().values())
+        return self.cache.can_take(len(self.scheduler.running))
 
     def _launch(self, before: Optional[_StepInFlight]) -> Optional[_StepInFlight]:
         entries = self.scheduler.schedule(ahead=before is not None)

@@ -89,6 +89,9 @@ def test_scheduler_reuses_prefixes_counts_them_and_keeps_the_tokens_right():
         assert r.output_ids == expected_output(r.prompt, 4)
     cache.check_invariants()
     assert cache.prefix_tree.pages_held == 5 + 0 and cache.free_pages()[FULL] == 32
+    # 27 pages are free and the tree could give up its 5: 32 can be taken, 33 cannot
+    assert cache.allocators[FULL].free_count == 27
+    assert cache.can_take(27) and cache.can_take(32) and not cache.can_take(33)
 
 
 @pytest.mark.parametrize("seed", range(4))
