@@ -51,11 +51,11 @@ def check(rows, expected, tolerance, requests, what):
     assert bad is None, f"{what}: first wrong row: request {bad[0]} position {bad[1]} error {bad[2]:.3e} (tolerance {tolerance})"
 
 
-@pytest.mark.parametrize("page", [8, 64, 128])
+@pytest.mark.parametrize("page", [1, 8, 64, 128, 256])
 def test_other_page_sizes_of_the_tensor_core_kernels(prepared, page):
-    """Head_dim 128 in bfloat16 with pages of 8 and 64 tokens (several pages, or one, per 64-key block
-    of the tcgen05 attention) and of 128 (which that kernel refuses: the mma.sync kernel takes the
-    portions), portions mixed with decoded tokens."""
+    """Head_dim 128 in bfloat16 with pages of 1 (the reference's default), 8 and 64 tokens (many pages,
+    several, or one per 64-key block of the tcgen05 attention) and of 128 and 256 (which that kernel
+    refuses: the mma.sync kernel takes the portions), portions mixed with decoded tokens."""
     folder, requests, expected, _ = prepared("D", "bfloat16")
     trace = rh.trace_mixed(requests, seed=4)
     rows, session = rh.run_in_process(folder, "bfloat16", trace, max_tokens=rh.max_tokens_of(trace, max(64, page)),
