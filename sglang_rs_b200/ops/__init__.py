@@ -416,10 +416,12 @@ def tiled_attention_tc(q: torch.Tensor, k_pool: torch.Tensor, v_pool: torch.Tens
 #: decode step at batch 128 takes 3.80 ms instead of 4.48 ms)
 OWN_GEMM_MAX_TOKENS = 64
 #: from this many rows on the gate/up product runs on the persistent CTA-pair kernel, which takes SiLU(gate) * up
-#: into its epilogue (measured at 2,048 rows of Qwen3-8B on B200: 274 us against 276 us + 24 us for the
-#: library's product and the SiLU kernel).  The plain products stay with the library: the pair kernel reaches
-#: 0.92 to 1.0 of it alone, and whole prefill steps measured no gain from switching them.
-PAIR_GEMM_MIN_TOKENS = 256
+#: into its epilogue.  Measured at Qwen3-8B sizes on B200, chained in a graph, against the library's product
+#: followed by the SiLU kernel: 64.8 against 53.7 us at 256 rows (96 tiles of 256 tokens leave the second
+#: round of the 74 pairs mostly empty), 155 against 155 us at 1,024, 214 against 219 us at 1,536, 280 against
+#: 301 us at 2,048.  The plain products stay with the library at every size: the pair kernel reaches 0.92 to
+#: 1.0 of it alone, and whole prefill steps measured no gain from switching them.
+PAIR_GEMM_MIN_TOKENS = 1280
 #: the SMs a product cut along K should fill
 SM_COUNT = 148
 

@@ -129,3 +129,17 @@ def test_gate_up_with_silu_on_pairs_of_ctas(tokens, inner, k):
     gate_up = pm.plain_linear(x.double(), w.double())
     want = pm.plain_silu_mul(gate_up[:, :inner], gate_up[:, inner:])
     assert got.shape == (tokens, inner) and relative_error(got, want) < 1e-2
+
+
+@pytest.mark.parametrize("tokens", [3, 64, 65, 300, 1279, 1280, 1400])
+def test_gate_up_takes_the_kernel_of_its_row_count(tokens):
+    """`gate_up_silu` runs the few-token kernel, the library's product with the SiLU kernel, or the
+    CTA-pair kernel, by the number of rows: the same result from each."""
+    inner, k = 264, 200
+    x, w = operands(tokens, 2 * inner, k, seed=tokens)
+    word = ops.new_error_word(DEV)
+    got = ops.gate_up_silu(x.to(DEV), w.to(DEV), inner, word)
+    ops.raise_on_error_word(word)
+    gate_up = pm.plain_linear(x.double(), w.double())
+    want = pm.plain_silu_mul(gate_up[:, :inner], gate_up[:, inner:])
+    assert got.shape == (tokens, inner) and relative_error(got, want) < 1e-2
