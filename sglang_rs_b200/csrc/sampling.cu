@@ -168,6 +168,387 @@ sample_pick_kernel(const float* __restrict__ logits, int vocab, int stride, cons
   out[row] = pick;
 }
 
+// ---------------------------------------------------------------------------------------------
+// Sampling with top-k, top-p and min-p (the reference's rule, model_executor.rs:471-555): the
+// probabilities p_i = exp(l_i / T - max_j l_j / T) are sorted descending (equal ones in index
+// order); the first k are kept; an item is kept while the mass before it, as a fraction of the
+// mass of those k, is below top_p, and while p_i >= p_0 * min_p; u * (kept mass) picks the first
+// kept item whose running mass exceeds it.
+//
+// Nothing is sorted here.  Every cut keeps a prefix of the sorted order, and a prefix is named by
+// a probability tau and a number n: all items above tau and the first n, in index order, of
+// those equal to tau.  The item at which a running count or a running mass crosses a threshold
+// is found by a radix search over the bits of p (11 + 11 + 10 bits): the histogram of the first
+// 11 bits (counts and masses per bin) is built once per row, together with the p themselves,
+// which go to scratch memory; each search then refines inside one bin with two light passes
+// over the stored p.  The position among equal items follows by division.  Masses are integers
+// (p * 2^40, rounded), so sums do not depend on the order in which threads add them and a row's
+// token does not depend on timing.  One block per row.
+#define FS_THREADS 1024
+#define FS_BINS 2048
+#define FS_BATCH 8          // loads of a thread in flight at once
+#define FS_QUADS 4          // the same for 16-byte loads of the stored probabilities
+typedef unsigned long long u64;
+
+__device__ __forceinline__ u64 fs_mass(float p) { return __float2ull_rn(p * 1099511627776.0f); }   // p * 2^40
+
+struct FsShared {
+  u64 first_mass[FS_BINS];        // histogram of the first 11 bits of p: mass and count per bin
+  u64 mass[FS_BINS + 1];          // histogram of the level being refined; the last entry is a mailbox
+  u64 totals[99];
+  unsigned first_count[FS_BINS];
+  unsigned count[FS_BINS];
+  unsigned found[4];
+  float warp_max[FS_THREADS / 32];
+  int index;
+};
+
+// sum over the block; every thread gets it
+__device__ __forceinline__ u64 fs_block_sum(u64 v, u64* scratch /* 33 */) {
+#pragma unroll
+  for (int offset = 16; offset > 0; offset >>= 1) v += __shfl_xor_sync(0xffffffffu, v, offset);
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  __syncthreads();
+  if (lane == 0) scratch[warp] = v;
+  __syncthreads();
+  if (warp == 0) {
+    u64 t = lane < FS_THREADS / 32 ? scratch[lane] : 0ull;
+#pragma unroll
+    for (int offset = 16; offset > 0; offset >>= 1) t += __shfl_xor_sync(0xffffffffu, t, offset);
+    if (lane == 0) scratch[32] = t;
+  }
+  __syncthreads();
+  return scratch[32];
+}
+
+// One item per lane (or none) into a histogram.  Called by whole warps.  Lanes that fall into the same
+// bin as the first lane still waiting add once, through that lane (up to three such groups: a flat row
+// puts a whole warp into one or two bins, and thirty-two additions to one address would queue up);
+// the lanes left after that add for themselves (a peaked row spreads a warp over many bins).
+__device__ __forceinline__ void fs_add(unsigned* count, u64* mass, bool mine, unsigned bin, u64 w) {
+  unsigned waiting = __ballot_sync(0xffffffffu, mine);
+  const int lane = threadIdx.x & 31;
+#pragma unroll
+  for (int round = 0; round < 3; ++round) {
+    if (waiting == 0) return;
+    const int leader = __ffs(waiting) - 1;
+    const unsigned lead_bin = __shfl_sync(0xffffffffu, bin, leader);
+    const bool in_group = ((waiting >> lane) & 1u) && bin == lead_bin;
+    const unsigned group = __ballot_sync(0xffffffffu, in_group);
+    if (__popc(group) >= 4) {
+      const unsigned lo = __reduce_add_sync(0xffffffffu, in_group ? (unsigned)(w & 0xFFFFFu) : 0u);
+      const unsigned mid = __reduce_add_sync(0xffffffffu, in_group ? (unsigned)((w >> 20) & 0xFFFFFu) : 0u);
+      const unsigned hi = __reduce_add_sync(0xffffffffu, in_group ? (unsigned)(w >> 40) : 0u);
+      if (lane == leader) {
+        atomicAdd(&count[lead_bin], (unsigned)__popc(group));
+        atomicAdd(&mass[lead_bin], (u64)lo + ((u64)mid << 20) + ((u64)hi << 40));
+      }
+    } else if (in_group) {
+      atomicAdd(&count[bin], 1u);
+      atomicAdd(&mass[bin], w);
+    }
+    waiting &= ~group;
+  }
+  if ((waiting >> lane) & 1u) {
+    atomicAdd(&count[bin], 1u);
+    atomicAdd(&mass[bin], w);
+  }
+}
+
+#define FS_BY_COUNT 0
+#define FS_BY_MASS 1
+#define FS_BY_KEY 2
+
+// Walks a histogram from its top bin down.  BY_COUNT / BY_MASS: the bin in which the running count or
+// mass (starting at `base`, what lies above the histogram's range) first exceeds `want`.  BY_KEY: the
+// bin `want`.  Leaves the bin in found[0], the count of the bins above it in found[1] and their mass
+// in the mailbox; every thread reads them after the call.
+template <int MODE>
+__device__ void fs_scan(const unsigned* count, const u64* mass, int nbins, u64 want, u64 base, FsShared& sh) {
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  if (threadIdx.x == 0) {                        // what holds if no bin is found (a row of NaN)
+    sh.found[0] = 0;
+    sh.found[1] = 0;
+    sh.mass[FS_BINS] = 0;
+  }
+  // thread t owns bins nbins - 1 - 2t and nbins - 2 - 2t; an inclusive scan over the threads, in the order
+  // of falling bins, tells each what lies above its bins
+  const int b0 = nbins - 1 - 2 * (int)threadIdx.x, b1 = b0 - 1;
+  const u64 c0 = b0 >= 0 ? (u64)count[b0] : 0ull, c1 = b1 >= 0 ? (u64)count[b1] : 0ull;
+  const u64 m0 = b0 >= 0 ? mass[b0] : 0ull, m1 = b1 >= 0 ? mass[b1] : 0ull;
+  u64 run_c = c0 + c1, run_m = m0 + m1;
+#pragma unroll
+  for (int offset = 1; offset < 32; offset <<= 1) {
+    const u64 tc = __shfl_up_sync(0xffffffffu, run_c, offset), tm = __shfl_up_sync(0xffffffffu, run_m, offset);
+    if (lane >= offset) {
+      run_c += tc;
+      run_m += tm;
+    }
+  }
+  __syncthreads();
+  if (lane == 31) {
+    sh.totals[33 + warp] = run_c;
+    sh.totals[66 + warp] = run_m;
+  }
+  __syncthreads();
+  u64 start_c = run_c - (c0 + c1), start_m = run_m - (m0 + m1);       // above this thread's bins, inside the range
+  for (int w = 0; w < warp; ++w) {
+    start_c += sh.totals[33 + w];
+    start_m += sh.totals[66 + w];
+  }
+  bool first = false, second = false;
+  if (MODE == FS_BY_KEY) {
+    first = b0 >= 0 && (u64)b0 == want;
+    second = b1 >= 0 && (u64)b1 == want;
+  } else {
+    const u64 v0 = MODE == FS_BY_COUNT ? c0 : m0, v1 = MODE == FS_BY_COUNT ? c1 : m1;
+    const u64 start_v = base + (MODE == FS_BY_COUNT ? start_c : start_m);
+    first = b0 >= 0 && start_v <= want && want < start_v + v0;
+    second = b1 >= 0 && start_v + v0 <= want && want < start_v + v0 + v1;
+  }
+  if (first) {
+    sh.found[0] = (unsigned)b0;
+    sh.found[1] = (unsigned)start_c;
+    sh.mass[FS_BINS] = start_m;
+  } else if (second) {
+    sh.found[0] = (unsigned)b1;
+    sh.found[1] = (unsigned)(start_c + c0);
+    sh.mass[FS_BINS] = start_m + m0;
+  }
+  __syncthreads();
+}
+
+struct FsCrossing {
+  unsigned key;      // bits of the probability at which the threshold is crossed
+  u64 above;         // items with a larger probability
+  u64 mass_above;    // their mass
+  u64 equal;         // items with exactly this probability
+};
+
+// BY_COUNT / BY_MASS: the item, in descending order of p, at which the running count or the running
+// mass first exceeds `want` (before <= want < before + own); the caller guarantees that it exists.
+// BY_KEY: the probability with the bits `want`.  `p` is the row of stored probabilities.
+template <int MODE>
+__device__ FsCrossing fs_search(const float* __restrict__ p, int vocab, u64 want, FsShared& sh) {
+  FsCrossing c;
+  c.above = 0;
+  c.mass_above = 0;
+  unsigned prefix = 0;
+  int fixed_bits = 0;
+#pragma unroll 1
+  for (int level = 0; level < 3; ++level) {
+    const int bits = level < 2 ? 11 : 10;
+    const int shift = 32 - fixed_bits - bits;
+    const u64 target = MODE == FS_BY_KEY ? (u64)(((unsigned)want >> shift) & ((1u << bits) - 1)) : want;
+    const u64 base = MODE == FS_BY_COUNT ? c.above : c.mass_above;
+    if (level == 0) {
+      fs_scan<MODE>(sh.first_count, sh.first_mass, 1 << bits, target, base, sh);
+    } else {
+      for (int b = threadIdx.x; b < FS_BINS; b += FS_THREADS) {
+        sh.count[b] = 0;
+        sh.mass[b] = 0;
+      }
+      __syncthreads();
+      // the stored row is padded to a multiple of four with values that match no prefix
+      const float4* p4 = reinterpret_cast<const float4*>(p);
+      const int quads = (vocab + 3) >> 2;
+      for (int start = 0; start < quads; start += FS_THREADS * FS_QUADS) {
+        float4 value[FS_QUADS];
+#pragma unroll
+        for (int j = 0; j < FS_QUADS; ++j) {
+          const int i = start + j * FS_THREADS + (int)threadIdx.x;
+          value[j] = i < quads ? p4[i] : make_float4(-1.f, -1.f, -1.f, -1.f);     // the sign bit never matches a prefix
+        }
+#pragma unroll
+        for (int j = 0; j < FS_QUADS; ++j) {
+          const float four[4] = {value[j].x, value[j].y, value[j].z, value[j].w};
+#pragma unroll
+          for (int e = 0; e < 4; ++e) {
+            const unsigned key = __float_as_uint(four[e]);
+            const bool mine = (key >> (32 - fixed_bits)) == prefix;
+            fs_add(sh.count, sh.mass, mine, (key >> shift) & ((1u << bits) - 1), fs_mass(four[e]));
+          }
+        }
+      }
+      __syncthreads();
+      fs_scan<MODE>(sh.count, sh.mass, 1 << bits, target, base, sh);
+    }
+    const unsigned bin = sh.found[0];
+    c.above += sh.found[1];
+    c.mass_above += sh.mass[FS_BINS];
+    prefix = (prefix << bits) | bin;
+    fixed_bits += bits;
+    if (level == 2) c.equal = sh.count[bin];
+    __syncthreads();
+  }
+  c.key = prefix;
+  return c;
+}
+
+// rows_index (or null: row b is block b) picks the rows of `logits` that are sampled here; the
+// per-row options are indexed by the row.  top_k <= 0 or >= vocab, top_p >= 1 and min_p <= 0
+// switch the cut off.  `stored` holds one row of `vocab` floats per block.
+__global__ void __launch_bounds__(FS_THREADS)
+sample_filtered_kernel(const float* __restrict__ logits, int vocab, long long stride, const int* __restrict__ rows_index,
+                       const float* __restrict__ temperature, const int* __restrict__ top_k,
+                       const float* __restrict__ top_p, const float* __restrict__ min_p,
+                       const float* __restrict__ uniform, float* __restrict__ stored, int* __restrict__ out) {
+  extern __shared__ __align__(16) unsigned char fs_raw[];
+  FsShared& sh = *reinterpret_cast<FsShared*>(fs_raw);
+  const int r = rows_index ? rows_index[blockIdx.x] : blockIdx.x;
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const float* l = logits + (size_t)r * stride;
+  const int pitch = (vocab + 3) & ~3;                 // rows of `stored` start on 16-byte boundaries
+  float* p = stored + (size_t)blockIdx.x * pitch;
+  const float t = temperature[r];
+  // the largest scaled logit
+  float best = -INFINITY;
+#pragma unroll 8
+  for (int i = threadIdx.x; i < vocab; i += FS_THREADS) best = fmaxf(best, __fdiv_rn(l[i], t));
+#pragma unroll
+  for (int offset = 16; offset > 0; offset >>= 1) best = fmaxf(best, __shfl_xor_sync(0xffffffffu, best, offset));
+  if (lane == 0) sh.warp_max[warp] = best;
+  for (int b = threadIdx.x; b < FS_BINS; b += FS_THREADS) {
+    sh.first_count[b] = 0;
+    sh.first_mass[b] = 0;
+  }
+  __syncthreads();
+  best = sh.warp_max[0];
+  for (int w = 1; w < FS_THREADS / 32; ++w) best = fmaxf(best, sh.warp_max[w]);
+  // the probabilities, stored for the passes to come, and the histogram of their first 11 bits
+  for (int start = 0; start < vocab; start += FS_THREADS * FS_BATCH) {
+    float raw[FS_BATCH];
+#pragma unroll
+    for (int j = 0; j < FS_BATCH; ++j) {
+      const int i = start + j * FS_THREADS + (int)threadIdx.x;
+      raw[j] = i < vocab ? l[i] : 0.f;
+    }
+#pragma unroll
+    for (int j = 0; j < FS_BATCH; ++j) {
+      const int i = start + j * FS_THREADS + (int)threadIdx.x;
+      const bool live = i < vocab;
+      const float value = expf(__fdiv_rn(raw[j], t) - best);
+      if (i < pitch) p[i] = live ? value : -1.f;
+      fs_add(sh.first_count, sh.first_mass, live, __float_as_uint(value) >> 21, fs_mass(value));
+    }
+  }
+  __syncthreads();                                   // the block reads what it wrote to `stored`
+
+  // a prefix of the sorted order: everything above `key`, and the first `n` of those equal to it
+  FsCrossing cut;
+  cut.key = 0;
+  u64 n = ~0ull;
+  bool any_cut = false;
+  auto tighten = [&](const FsCrossing& c, u64 ties) {
+    if (!any_cut || c.key > cut.key || (c.key == cut.key && ties < n)) {
+      cut = c;
+      n = ties;
+      any_cut = true;
+    }
+  };
+  // top-k, and the mass that top-p is a fraction of
+  const int k = top_k[r];
+  u64 total;
+  if (k > 0 && k < vocab) {
+    const FsCrossing c = fs_search<FS_BY_COUNT>(p, vocab, (u64)(k - 1), sh);
+    const u64 ties = (u64)k - c.above;               // of the items equal to the k-th, those that make k full
+    tighten(c, ties);
+    total = c.mass_above + ties * fs_mass(__uint_as_float(c.key));
+  } else {
+    u64 mine = 0;
+    for (int b = threadIdx.x; b < FS_BINS; b += FS_THREADS) mine += sh.first_mass[b];
+    total = fs_block_sum(mine, sh.totals);
+  }
+  // top-p.  Kept: mass before the item < top_p * total.  The last kept item is the one that holds the
+  // mass position limit - 1; of the items equal to it, those that start below the limit are kept.
+  const float tp = top_p[r];
+  if (tp < 1.0f && total > 0) {
+    u64 limit = (u64)ceil((double)tp * (double)total);
+    if (limit < 1) limit = 1;
+    if (limit > total) limit = total;
+    const FsCrossing c = fs_search<FS_BY_MASS>(p, vocab, limit - 1, sh);
+    const u64 w = fs_mass(__uint_as_float(c.key));
+    if (w > 0) tighten(c, (limit - c.mass_above + w - 1) / w);
+  }
+  // min-p: p_i >= p_0 * min_p, and p_0 = 1
+  const float mp = min_p[r];
+  if (mp > 0.f) tighten(fs_search<FS_BY_KEY>(p, vocab, (u64)__float_as_uint(1.0f * mp), sh), ~0ull);
+
+  // mass of what is kept, and the pick: the first kept item whose running mass exceeds u * kept
+  u64 kept = total;
+  if (any_cut) {
+    if (n > cut.equal) n = cut.equal;
+    kept = cut.mass_above + n * fs_mass(__uint_as_float(cut.key));
+  }
+  int answer = 0;
+  if (kept > 0) {
+    u64 target = (u64)((double)uniform[r] * (double)kept);
+    if (target >= kept) target = kept - 1;
+    const FsCrossing c = fs_search<FS_BY_MASS>(p, vocab, target, sh);
+    const u64 w = fs_mass(__uint_as_float(c.key));
+    u64 which = w > 0 ? (target - c.mass_above) / w : 0;       // among the items equal to it, in index order
+    if (c.equal > 0 && which >= c.equal) which = c.equal - 1;
+    // Its index: thread t owns the items t * per .. (t + 1) * per - 1, a scan over the threads' counts of
+    // matches finds the thread that holds the wanted one, and it walks its items again.
+    if (threadIdx.x == 0) sh.index = 0;
+    const int per = ((pitch / 4 + FS_THREADS - 1) / FS_THREADS) * 4;      // a multiple of four: 16-byte loads
+    const int begin = min(pitch, (int)threadIdx.x * per), end = min(pitch, begin + per);
+    unsigned mine = 0;
+#pragma unroll 4
+    for (int i = begin; i < end; i += 4) {
+      const float4 v = *reinterpret_cast<const float4*>(p + i);
+      mine += (__float_as_uint(v.x) == c.key) + (__float_as_uint(v.y) == c.key) + (__float_as_uint(v.z) == c.key) +
+              (__float_as_uint(v.w) == c.key);
+    }
+    unsigned run = mine;
+#pragma unroll
+    for (int offset = 1; offset < 32; offset <<= 1) {
+      const unsigned other = __shfl_up_sync(0xffffffffu, run, offset);
+      if (lane >= offset) run += other;
+    }
+    __syncthreads();
+    if (lane == 31) sh.count[warp] = run;
+    __syncthreads();
+    unsigned before = run - mine;
+    for (int w2 = 0; w2 < warp; ++w2) before += sh.count[w2];
+    if (mine > 0 && before <= (unsigned)which && (unsigned)which < before + mine) {
+      unsigned rank = before;
+      for (int i = begin; i < end; ++i) {
+        if (__float_as_uint(p[i]) == c.key) {
+          if (rank == (unsigned)which) sh.index = i;
+          ++rank;
+        }
+      }
+    }
+    __syncthreads();
+    answer = sh.index;
+  }
+  if (threadIdx.x == 0) out[r] = answer;
+}
+
+// One token for each of the `count` rows named in rows_index (null: rows 0 .. count - 1), into out[row].
+// Per-row options are indexed by the row: temperature (> 0), top_k (<= 0: off), top_p (>= 1: off),
+// min_p (<= 0: off), uniform in [0, 1).  `scratch` holds count rows of vocab floats, each rounded up to a
+// multiple of four.
+extern "C" int srb_sample_filtered(const float* logits, int vocab, long long stride, const int* rows_index, int count,
+                                   const float* temperature, const int* top_k, const float* top_p, const float* min_p,
+                                   const float* uniform, float* scratch, int* out, void* stream) {
+  if (count <= 0) return SRB_OK;
+  if (vocab <= 0 || stride < vocab) SRB_FAIL("sample_filtered: vocabulary %d and stride %lld do not fit", vocab, stride);
+  if (!temperature || !top_k || !top_p || !min_p || !uniform || !out || !scratch)
+    SRB_FAIL("sample_filtered: an option array, the scratch memory or the output is missing");
+  static bool configured = false;
+  if (!configured) {
+    SRB_CUDA_CALL(cudaFuncSetAttribute(sample_filtered_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                       (int)sizeof(FsShared)));
+    configured = true;
+  }
+  sample_filtered_kernel<<<count, FS_THREADS, sizeof(FsShared), (cudaStream_t)stream>>>(
+      logits, vocab, stride, rows_index, temperature, top_k, top_p, min_p, uniform, scratch, out);
+  SRB_LAUNCH_CHECK("sample_filtered");
+  return SRB_OK;
+}
+
 extern "C" int srb_sample_scratch_floats(int rows) { return rows * SAMPLE_CHUNKS * 3; }
 
 // logits [rows, stride] with `vocab` valid columns; temperature and uniform are [rows] or

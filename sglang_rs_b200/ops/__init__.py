@@ -596,3 +596,31 @@ def sample(logits: torch.Tensor, temperature: Optional[torch.Tensor], uniform: O
     _check(lib, lib.srb_sample(_ptr(logits), rows, vocab, logits.stride(0), _ptr(temperature), _ptr(uniform),
                                _ptr(out), _ptr(scratch), _stream()), launches=2)
     return out
+
+
+def sample_filtered(logits: torch.Tensor, rows_index: Optional[torch.Tensor], temperature: torch.Tensor,
+                    top_k: torch.Tensor, top_p: torch.Tensor, min_p: torch.Tensor, uniform: torch.Tensor,
+                    out: torch.Tensor) -> None:
+    """Sampling with top-k, top-p and min-p for the rows named in ``rows_index`` (int32; None: all rows),
+    into ``out[row]``.  The option tensors hold one entry per row of ``logits``: temperature > 0, top_k
+    (int32; <= 0: off), top_p (>= 1: off), min_p (<= 0: off), uniform in [0, 1)."""
+    _need(logits, "logits", torch.float32); _need(out, "out", torch.int32)
+    _need(temperature, "temperature", torch.float32); _need(top_k, "top_k", torch.int32)
+    _need(top_p, "top_p", torch.float32); _need(min_p, "min_p", torch.float32); _need(uniform, "uniform", torch.float32)
+    rows, vocab = logits.shape
+    for name, tensor in (("temperature", temperature), ("top_k", top_k), ("top_p", top_p), ("min_p", min_p),
+                         ("uniform", uniform), ("out", out)):
+        if tensor.numel() < rows:
+            raise KernelError(f"sample_filtered: {name} needs one entry per row")
+    count = rows
+    if rows_index is not None:
+        _need(rows_index, "rows_index", torch.int32)
+        count = rows_index.numel()
+    if count == 0:
+        return
+    lib = load_library("sampling")
+    # the rows' probabilities, each row padded to a multiple of four
+    scratch = torch.empty(count * ((vocab + 3) & ~3), dtype=torch.float32, device=logits.device)
+    _check(lib, lib.srb_sample_filtered(_ptr(logits), vocab, ctypes.c_longlong(logits.stride(0)), _ptr(rows_index), count,
+                                        _ptr(temperature), _ptr(top_k), _ptr(top_p), _ptr(min_p), _ptr(uniform),
+                                        _ptr(scratch), _ptr(out), _stream()))

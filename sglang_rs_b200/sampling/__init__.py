@@ -1,4 +1,4 @@
 from .params import SamplingParams
-from .sampler import RequestRandom, Sampler, apply_penalties, sample_filtered
+from .sampler import RequestRandom, Sampler, apply_penalties
 
-__all__ = ["SamplingParams", "RequestRandom", "Sampler", "apply_penalties", "sample_filtered"]
+__all__ = ["SamplingParams", "RequestRandom", "Sampler", "apply_penalties"]

@@ -647,3 +647,74 @@ def test_sampling_kernel():
     assert int(ends[0]) == 0
     last = ops.sample(logits[:1].to(DEV), torch.tensor([1.0], device=DEV), torch.tensor([0.99999994], device=DEV))
     assert int(last[0]) >= vocab - 50
+
+
+def plain_filtered_pick(kept, u):
+    """The reference's walk over the kept items in sorted order (model_executor.rs:532-555), in 64-bit;
+    also how far u * mass lies from the nearest edge between two items, as a fraction of the mass."""
+    tokens, masses = list(kept), list(kept.values())
+    total = sum(masses)
+    target, running, pick, gap = u * total, 0.0, tokens[-1], 1.0
+    found = False
+    for token, mass in zip(tokens, masses):
+        running += mass
+        gap = min(gap, abs(running - target) / total)
+        if not found and running > target:
+            pick, found = token, True
+    return pick, tokens, gap
+
+
+@pytest.mark.parametrize("vocab", [1531, 20011])
+def test_sampling_with_top_k_top_p_and_min_p(vocab):
+    """The kernel that samples with cuts against the reference's algorithm: peaked and flat rows, equal
+    logits at the edge of a cut (index order decides), cuts alone and together, u at both ends."""
+    g = torch.Generator().manual_seed(vocab)
+    rows = 8
+    logits = torch.randn(rows, vocab, generator=g) * 4
+    logits[1] = torch.randn(vocab, generator=g) * 0.01                     # nearly flat
+    logits[2] = 0.0                                                        # all equal: index order only
+    logits[3, [5, 77, 300, 900]] = 9.0                                     # four equal maxima
+    logits[4, [10, 20, 30]] = logits[4].max() - 1.0                        # equal values below the maximum
+    logits[5] = torch.round(logits[5])                                     # many ties everywhere
+    cases = [dict(top_k=1), dict(top_k=3), dict(top_k=50), dict(top_p=0.9), dict(top_p=1e-6), dict(top_p=0.3),
+             dict(min_p=0.5), dict(min_p=0.01), dict(top_k=40, top_p=0.83, min_p=0.02), dict(top_k=vocab - 1),
+             dict(top_k=2, top_p=0.999)]
+    temperature = torch.tensor([0.7, 1.0, 1.0, 0.5, 1.3, 2.0, 0.9, 1.0])
+    logits_d = logits.to(DEV)
+    out = torch.full((rows,), -1, dtype=torch.int32, device=DEV)
+    for case in cases:
+        k = torch.full((rows,), case.get("top_k", 0), dtype=torch.int32)
+        tp = torch.full((rows,), case.get("top_p", 1.0))
+        mp = torch.full((rows,), case.get("min_p", 0.0))
+        kept_of = [pm.plain_filtered_distribution(logits[r], float(temperature[r]), case.get("top_k"), case.get("top_p"),
+                                                  case.get("min_p")) for r in range(rows)]
+        for trial in range(6 if vocab < 5000 else 3):
+            u = torch.rand(rows, generator=g)
+            if trial == 0:
+                u[:] = 0.0
+            if trial == 1:
+                u[:] = 0.99999994
+            out.fill_(-1)
+            ops.sample_filtered(logits_d, None, temperature.to(DEV), k.to(DEV), tp.to(DEV), mp.to(DEV), u.to(DEV), out)
+            got = out.cpu().tolist()
+            for r in range(rows):
+                want, kept, gap = plain_filtered_pick(kept_of[r], float(u[r]))
+                if got[r] != want:
+                    # The kernel has 32-bit exponentials, the oracle 64-bit ones.  That may move a u within
+                    # rounding of an edge between two items to the other item, and it may order two items
+                    # of nearly equal probability the other way round; nothing else.
+                    scaled = logits[r].double() / float(temperature[r])
+                    p_got, p_want = math.exp(float(scaled[got[r]] - scaled.max())), math.exp(float(scaled[want] - scaled.max()))
+                    nearly_equal = abs(p_got - p_want) <= 1e-5 * p_want
+                    assert gap < 1e-5 or float(u[r]) > 0.9999 or nearly_equal, (case, r, got[r], want, gap)
+                    p_last = math.exp(float(scaled[kept[-1]] - scaled.max()))
+                    assert got[r] in kept or abs(p_got - p_last) <= 1e-5 * p_last, (case, r, got[r])
+    # only the rows that are named are written
+    out.fill_(-1)
+    index = torch.tensor([6, 2], dtype=torch.int32, device=DEV)
+    ones = torch.ones(rows)
+    ops.sample_filtered(logits_d, index, temperature.to(DEV), torch.full((rows,), 5, dtype=torch.int32, device=DEV),
+                        ones.to(DEV), torch.zeros(rows, device=DEV), torch.full((rows,), 0.5, device=DEV), out)
+    got = out.cpu().tolist()
+    assert [i for i, t in enumerate(got) if t >= 0] == [2, 6]
+    assert got[2] == 2                                                     # five equal items, u = 0.5: the third by index
