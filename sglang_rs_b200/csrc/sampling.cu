@@ -549,6 +549,78 @@ extern "C" int srb_sample_filtered(const float* logits, int vocab, long long str
   return SRB_OK;
 }
 
+// ---------------------------------------------------------------------------------------------
+// Penalties (model_executor.rs:558-590): a token seen c > 0 times in the request's prompt and output
+// has its logit divided by the repetition penalty if positive, multiplied if negative, and then
+// lowered by presence + frequency * c.  How often each token was seen is kept on the device, one row
+// of `vocab` counts per request with penalties: the prompt is counted once, every sampled token as
+// it is chosen, so no token has to come back to the host before the next step is sampled.
+__global__ void count_tokens_kernel(int* __restrict__ counts_row, const int* __restrict__ tokens, int n, int vocab) {
+  for (int i = blockIdx.x * blockDim.x + threadIdx.x; i < n; i += gridDim.x * blockDim.x) {
+    const int token = tokens[i];
+    if (token >= 0 && token < vocab) atomicAdd(&counts_row[token], 1);
+  }
+}
+
+// grid (blocks over the vocabulary, rows); index[r] < 0: the row has no penalties
+__global__ void apply_penalties_kernel(float* __restrict__ logits, long long stride, int vocab,
+                                       const int* __restrict__ counts, const int* __restrict__ index,
+                                       const float* __restrict__ presence, const float* __restrict__ frequency,
+                                       const float* __restrict__ repetition) {
+  const int r = blockIdx.y;
+  const int table_row = index[r];
+  if (table_row < 0) return;
+  const int* seen = counts + (size_t)table_row * vocab;
+  float* l = logits + (size_t)r * stride;
+  const float rep = repetition[r], pres = presence[r], freq = frequency[r];
+  for (int i = blockIdx.x * blockDim.x + threadIdx.x; i < vocab; i += gridDim.x * blockDim.x) {
+    const int c = seen[i];
+    if (c > 0) {
+      float v = l[i];
+      if (rep != 1.0f) v = v < 0.f ? v * rep : v / rep;
+      l[i] = v - pres - freq * (float)c;
+    }
+  }
+}
+
+__global__ void count_picked_kernel(int* __restrict__ counts, int vocab, const int* __restrict__ index,
+                                    const int* __restrict__ picked, int rows) {
+  const int r = blockIdx.x * blockDim.x + threadIdx.x;
+  if (r >= rows) return;
+  const int table_row = index[r], token = picked[r];
+  if (table_row >= 0 && token >= 0 && token < vocab) atomicAdd(&counts[(size_t)table_row * vocab + token], 1);
+}
+
+// counts_row: one row of `vocab` ints; tokens: n token ids on the device
+extern "C" int srb_count_tokens(int* counts_row, const int* tokens, int n, int vocab, void* stream) {
+  if (n <= 0) return SRB_OK;
+  const int blocks = (n + 255) / 256;
+  count_tokens_kernel<<<blocks > 64 ? 64 : blocks, 256, 0, (cudaStream_t)stream>>>(counts_row, tokens, n, vocab);
+  SRB_LAUNCH_CHECK("count_tokens");
+  return SRB_OK;
+}
+
+// logits [rows, stride] float, changed in place; counts [table rows, vocab]; index, presence, frequency,
+// repetition: one entry per row of logits
+extern "C" int srb_apply_penalties(float* logits, int rows, int vocab, long long stride, const int* counts,
+                                   const int* index, const float* presence, const float* frequency,
+                                   const float* repetition, void* stream) {
+  if (rows <= 0) return SRB_OK;
+  if (vocab <= 0 || stride < vocab) SRB_FAIL("apply_penalties: vocabulary %d and stride %lld do not fit", vocab, stride);
+  if (rows > 65535) SRB_FAIL("apply_penalties: %d rows exceed one launch", rows);
+  apply_penalties_kernel<<<dim3(16, rows), 256, 0, (cudaStream_t)stream>>>(logits, stride, vocab, counts, index, presence,
+                                                                           frequency, repetition);
+  SRB_LAUNCH_CHECK("apply_penalties");
+  return SRB_OK;
+}
+
+extern "C" int srb_count_picked(int* counts, int vocab, const int* index, const int* picked, int rows, void* stream) {
+  if (rows <= 0) return SRB_OK;
+  count_picked_kernel<<<(rows + 255) / 256, 256, 0, (cudaStream_t)stream>>>(counts, vocab, index, picked, rows);
+  SRB_LAUNCH_CHECK("count_picked");
+  return SRB_OK;
+}
+
 extern "C" int srb_sample_scratch_floats(int rows) { return rows * SAMPLE_CHUNKS * 3; }
 
 // logits [rows, stride] with `vocab` valid columns; temperature and uniform are [rows] or

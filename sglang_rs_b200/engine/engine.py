@@ -74,12 +74,11 @@ class Engine:
         self.scheduler = Scheduler(self.cache, SchedulerConfig(
             max_running_requests=max_running_requests, chunked_prefill_size=chunked_prefill_size,
             max_positions=self.model.max_positions, default_stop_token_ids=stops))
-        self.sampler = Sampler(self.device)
+        self.sampler = Sampler(self.device, self.model.vocab_size)
         self._randoms: Dict[Hashable, RequestRandom] = {}
         self._requests: Dict[Hashable, Request] = {}
         self._ids = itertools.count()
         self._in_flight: Optional[_StepInFlight] = None
-        self._host_only_sampling = 0            # live requests whose sampling needs their tokens on the host
 
     # ------------------------------------------------------------------ low level
     def add_request(self, input_ids: Sequence[int], sampling_params: Union[SamplingParams, Mapping, None] = None,
@@ -98,8 +97,8 @@ class Engine:
         self.scheduler.add_request(request)
         self._requests[request_id] = request
         self._randoms[request_id] = RequestRandom(request_id, params.seed)
-        if not Sampler.stays_on_device(params):
-            self._host_only_sampling += 1
+        if params.has_penalties:
+            self.sampler.seen.open(request_id, ids)          # the prompt's tokens count as seen
         return request_id
 
     def step(self, overlap: bool = False) -> List[StepOutput]:
@@ -126,7 +125,7 @@ class Engine:
                 sampling = [e.request for e in entries if e.samples]
                 sampled = self.sampler.sample(
                     logits, [r.sampling for r in sampling], [self._randoms[r.request_id] for r in sampling],
-                    [r.tokens if r.sampling.has_penalties else () for r in sampling])
+                    [r.request_id for r in sampling])
             self.runner.check_device_errors()
         except Exception:
             self.scheduler.step_failed(entries)
@@ -138,9 +137,7 @@ class Engine:
     def _forget_finished(self, outputs: Sequence[StepOutput]) -> None:
         for output in outputs:
             if output.finished and self._randoms.pop(output.request_id, None) is not None:
-                request = self._requests.get(output.request_id)
-                if request is not None and not Sampler.stays_on_device(request.sampling):
-                    self._host_only_sampling -= 1
+                self.sampler.seen.close(output.request_id)
 
     # ------------------------------------------------------------------ steps that overlap the host's work
     def _step_overlapped(self) -> List[StepOutput]:
@@ -156,9 +153,8 @@ class Engine:
 
     def _may_run_ahead(self) -> bool:
         """The next step can be chosen before the tokens of the one in flight are known: sampling
-        needs no token history, and every running request can get a page without preemption."""
-        if self._host_only_sampling:
-            return False
+        needs no token on the host (the counts for penalties live on the device), so what is left to
+        ask is whether every running request can get a page without preemption."""
         return self.cache.can_take(len(self.scheduler.running))
 
     def _launch(self, before: Optional[_StepInFlight]) -> Optional[_StepInFlight]:
@@ -166,7 +162,6 @@ class Engine:
         if not entries:
             return None
         sampling = [e.request for e in entries if e.samples]
-        on_device = all(Sampler.stays_on_device(r.sampling) for r in sampling)
         source_row = {}
         if before is not None:
             rows = [e.request for e in before.entries if e.samples]
@@ -176,22 +171,16 @@ class Engine:
                                   token_from=source_row[id(e.request)] if e.from_device else -1) for e in entries]
         try:
             logits = self.runner.step(step_entries, before.picked if before is not None else None)
-            if logits is None or not on_device:
-                # nothing to sample, or sampling that needs the host: finish the step here
-                sampled: List[int] = []
-                if logits is not None:
-                    sampled = self.sampler.sample(
-                        logits, [r.sampling for r in sampling], [self._randoms[r.request_id] for r in sampling],
-                        [r.tokens if r.sampling.has_penalties else () for r in sampling])
+            if logits is None:
+                # nothing to sample: the step is finished here
                 self.runner.check_device_errors()
-                picked = torch.tensor(sampled + [0], dtype=torch.int32).pin_memory()
+                picked = torch.zeros(1, dtype=torch.int32).pin_memory()
                 done = torch.cuda.Event()
                 done.record()
-                for request in sampling:
-                    self.scheduler.mark_pending(request)
-                return _StepInFlight(entries, picked[:len(sampled)].to(self.device, non_blocking=True), picked, done)
+                return _StepInFlight(entries, picked[:0].to(self.device, non_blocking=True), picked, done)
             picked = self.sampler.pick_on_device(logits, [r.sampling for r in sampling],
-                                                 [self._randoms[r.request_id] for r in sampling])
+                                                 [self._randoms[r.request_id] for r in sampling],
+                                                 [r.request_id for r in sampling])
             host = torch.empty(picked.numel() + 1, dtype=torch.int32, pin_memory=True)
             host[:-1].copy_(picked, non_blocking=True)
             host[-1:].copy_(self.runner.error_word, non_blocking=True)
@@ -221,6 +210,7 @@ class Engine:
         return outputs
 
     def abort(self, request_id: Hashable) -> bool:
+        self.sampler.seen.close(request_id)
         return self.scheduler.abort(request_id)
 
     def flush_cache(self) -> bool:

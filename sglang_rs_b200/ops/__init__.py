@@ -624,3 +624,33 @@ def sample_filtered(logits: torch.Tensor, rows_index: Optional[torch.Tensor], te
     _check(lib, lib.srb_sample_filtered(_ptr(logits), vocab, ctypes.c_longlong(logits.stride(0)), _ptr(rows_index), count,
                                         _ptr(temperature), _ptr(top_k), _ptr(top_p), _ptr(min_p), _ptr(uniform),
                                         _ptr(scratch), _ptr(out), _stream()))
+
+
+def count_tokens(counts_row: torch.Tensor, tokens: torch.Tensor) -> None:
+    """``counts_row[t] += 1`` for every token id in ``tokens`` (int32, on the device)."""
+    _need(counts_row, "counts_row", torch.int32); _need(tokens, "tokens", torch.int32)
+    lib = load_library("sampling")
+    _check(lib, lib.srb_count_tokens(_ptr(counts_row), _ptr(tokens), tokens.numel(), counts_row.numel(), _stream()))
+
+
+def apply_penalties(logits: torch.Tensor, counts: torch.Tensor, index: torch.Tensor, presence: torch.Tensor,
+                    frequency: torch.Tensor, repetition: torch.Tensor) -> None:
+    """Penalises ``logits`` in place: row r uses the counts of ``counts[index[r]]`` (``index[r] < 0``: none).
+    A token seen c > 0 times: divided by ``repetition[r]`` if positive, multiplied if negative, then
+    lowered by ``presence[r] + frequency[r] * c``."""
+    _need(logits, "logits", torch.float32); _need(counts, "counts", torch.int32); _need(index, "index", torch.int32)
+    _need(presence, "presence", torch.float32); _need(frequency, "frequency", torch.float32)
+    _need(repetition, "repetition", torch.float32)
+    rows, vocab = logits.shape
+    if counts.dim() != 2 or counts.shape[1] != vocab:
+        raise KernelError("apply_penalties: counts must be [table rows, vocab]")
+    lib = load_library("sampling")
+    _check(lib, lib.srb_apply_penalties(_ptr(logits), rows, vocab, ctypes.c_longlong(logits.stride(0)), _ptr(counts),
+                                        _ptr(index), _ptr(presence), _ptr(frequency), _ptr(repetition), _stream()))
+
+
+def count_picked(counts: torch.Tensor, index: torch.Tensor, picked: torch.Tensor) -> None:
+    """``counts[index[r], picked[r]] += 1`` for every row with ``index[r] >= 0``."""
+    _need(counts, "counts", torch.int32); _need(index, "index", torch.int32); _need(picked, "picked", torch.int32)
+    lib = load_library("sampling")
+    _check(lib, lib.srb_count_picked(_ptr(counts), counts.shape[1], _ptr(index), _ptr(picked), picked.numel(), _stream()))

@@ -1,4 +1,4 @@
 from .params import SamplingParams
-from .sampler import RequestRandom, Sampler, apply_penalties
+from .sampler import RequestRandom, Sampler, SeenCounts
 
-__all__ = ["SamplingParams", "RequestRandom", "Sampler", "apply_penalties"]
+__all__ = ["SamplingParams", "RequestRandom", "Sampler", "SeenCounts"]

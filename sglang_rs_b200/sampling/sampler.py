@@ -5,9 +5,9 @@ l / T and an inverse-CDF walk in vocabulary order with the request's own uniform
 top-k / top-p / min-p cuts in another that follows the reference's algorithm
 (crates/sglang-srt/src/model_executor.rs:471-555): sort descending; keep k; keep an item while
 the mass before it is below top_p; drop items below max_p * min_p; walk the kept items in
-sorted order with target = u * kept mass.  Neither needs the request's tokens on the host, so
-steps with such requests still overlap the host.  Penalties (model_executor.rs:558-590) change
-the logits of tokens seen in prompt and output with tensor operations first.
+sorted order with target = u * kept mass.  Penalties (model_executor.rs:558-590) change the logits of tokens
+seen in prompt and output first, from counts kept on the device.  None of this needs a request's
+tokens on the host, so steps overlap the host whatever the sampling options.
 
 Each request draws from its own generator, seeded by its ``seed`` (or by its id), so its
 tokens do not depend on what else is in the batch.
@@ -37,32 +37,64 @@ class RequestRandom:
         return min(max(self._generator.random(), 0.0), ONE_BELOW)
 
 
-def apply_penalties(row: torch.Tensor, seen: Sequence[int], params: SamplingParams) -> torch.Tensor:
-    """Penalised copy of a logits row (model_executor.rs:558-590)."""
-    out = row.clone()
-    if not seen:
-        return out
-    tokens = torch.as_tensor(list(seen), dtype=torch.long, device=row.device)
-    tokens = tokens[tokens < row.numel()]
-    unique, counts = torch.unique(tokens, return_counts=True)
-    values = out[unique]
-    repetition = params.repetition_penalty if params.repetition_penalty is not None else 1.0
-    if repetition != 1.0:
-        values = torch.where(values < 0, values * repetition, values / repetition)
-    values = values - (params.presence_penalty or 0.0) - (params.frequency_penalty or 0.0) * counts.to(values.dtype)
-    out[unique] = values
-    return out
+class SeenCounts:
+    """How often each token occurred in the prompt and output of the requests that have penalties:
+    one row of ``vocab`` counts per such request, on the device.  The prompt is counted when the
+    request arrives, every sampled token by the sampler as it is chosen; the row goes back when the
+    request ends."""
+
+    def __init__(self, vocab: int, device):
+        self.vocab, self.device = int(vocab), device
+        self.table = None                       # int32 [capacity, vocab]
+        self.rows = {}                          # request id -> row
+        self.free = []
+
+    def open(self, request_id, prompt: Sequence[int]) -> None:
+        if not self.free:
+            old = 0 if self.table is None else self.table.shape[0]
+            grown = torch.zeros((max(4, 2 * old), self.vocab), dtype=torch.int32, device=self.device)
+            if old:
+                grown[:old].copy_(self.table)
+            self.table = grown
+            self.free = list(range(grown.shape[0] - 1, old - 1, -1))
+        row = self.free.pop()
+        self.rows[request_id] = row
+        self.table[row].zero_()
+        if len(prompt):
+            tokens = torch.tensor(list(prompt), dtype=torch.int32).pin_memory().to(self.device, non_blocking=True)
+            ops.count_tokens(self.table[row], tokens)
+
+    def close(self, request_id) -> None:
+        row = self.rows.pop(request_id, None)
+        if row is not None:
+            self.free.append(row)
+
+    def row_of(self, request_id) -> int:
+        return self.rows.get(request_id, -1)
 
 
 class Sampler:
-    def __init__(self, device):
+    def __init__(self, device, vocab: int = 0):
         self.device = device
+        self.seen = SeenCounts(vocab, device)
 
     def pick_on_device(self, logits: torch.Tensor, params: Sequence[SamplingParams],
-                       randoms: Sequence[RequestRandom]) -> torch.Tensor:
-        """One token per row (penalties apart): the chosen ids stay on the device (int32 [rows]);
-        nothing waits for the GPU."""
+                       randoms: Sequence[RequestRandom], request_ids: Sequence = ()) -> torch.Tensor:
+        """One token per row: the chosen ids stay on the device (int32 [rows]); nothing waits for the
+        GPU.  ``request_ids`` name the rows' requests, for those with penalties (``logits`` is then
+        changed in place, and the chosen tokens are counted as seen)."""
         rows = logits.shape[0]
+        seen_rows = None
+        if any(p.has_penalties for p in params):
+            index = [self.seen.row_of(request_ids[r]) if params[r].has_penalties else -1 for r in range(rows)]
+            if any(i < 0 and params[r].has_penalties for r, i in enumerate(index)):
+                raise RuntimeError("a request with penalties has no row of counts; SeenCounts.open was not called")
+            seen_rows = torch.tensor(index, dtype=torch.int32).pin_memory().to(self.device, non_blocking=True)
+            options = torch.tensor(
+                [[p.presence_penalty or 0.0 for p in params], [p.frequency_penalty or 0.0 for p in params],
+                 [p.repetition_penalty if p.repetition_penalty is not None else 1.0 for p in params]],
+                dtype=torch.float32).pin_memory().to(self.device, non_blocking=True)
+            ops.apply_penalties(logits, self.seen.table, seen_rows, options[0], options[1], options[2])
         temperature = [0.0] * rows
         uniform = [0.0] * rows
         cut = []                                   # rows with top-k / top-p / min-p
@@ -92,20 +124,11 @@ class Sampler:
                                  cut + [0] * (rows - len(cut))], dtype=torch.int32).pin_memory().to(self.device,
                                                                                                   non_blocking=True)
             ops.sample_filtered(logits, ints[1, :len(cut)], staged[2], ints[0], staged[3], staged[4], staged[1], picked)
+        if seen_rows is not None:
+            ops.count_picked(self.seen.table, seen_rows, picked)
         return picked
 
-    @staticmethod
-    def stays_on_device(params: SamplingParams) -> bool:
-        """True if :meth:`pick_on_device` samples this request exactly as :meth:`sample` does."""
-        return not params.has_penalties
-
     def sample(self, logits: torch.Tensor, params: Sequence[SamplingParams], randoms: Sequence[RequestRandom],
-               seen_tokens: Sequence[Sequence[int]]) -> List[int]:
-        """``logits`` [rows, vocab] float32 on the device; one entry of the other arguments
-        per row.  Returns the chosen token ids on the host."""
-        if any(p.has_penalties for p in params):
-            logits = logits.clone()
-            for r, p in enumerate(params):
-                if p.has_penalties:
-                    logits[r] = apply_penalties(logits[r], seen_tokens[r], p)
-        return self.pick_on_device(logits, params, randoms).cpu().tolist()
+               request_ids: Sequence = ()) -> List[int]:
+        """The same with the chosen token ids brought to the host."""
+        return self.pick_on_device(logits, params, randoms, request_ids).cpu().tolist()

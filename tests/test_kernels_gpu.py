@@ -718,3 +718,37 @@ def test_sampling_with_top_k_top_p_and_min_p(vocab):
     got = out.cpu().tolist()
     assert [i for i, t in enumerate(got) if t >= 0] == [2, 6]
     assert got[2] == 2                                                     # five equal items, u = 0.5: the third by index
+
+
+def test_penalties_from_counts_on_the_device():
+    """Counts of seen tokens per request (prompt counted once, sampled tokens as they are chosen) and the
+    reference's penalties applied from them, against the plain implementation."""
+    g = torch.Generator().manual_seed(5)
+    vocab, rows = 777, 4
+    counts = torch.zeros(3, vocab, dtype=torch.int32, device=DEV)
+    prompts = {0: [5, 5, 9, 700, 5], 2: [1, 2, 3, 2]}
+    for table_row, prompt in prompts.items():
+        ops.count_tokens(counts[table_row], torch.tensor(prompt, dtype=torch.int32, device=DEV))
+    index = torch.tensor([2, -1, 0, -1], dtype=torch.int32, device=DEV)       # logits row -> row of counts
+    picked = torch.tensor([3, 8, 776, 5], dtype=torch.int32, device=DEV)
+    ops.count_picked(counts, index, picked)
+    seen = {0: prompts[2] + [3], 2: prompts[0] + [776]}                       # by logits row
+    want_counts = torch.zeros(3, vocab, dtype=torch.int32)
+    for t in prompts[0] + [776]:
+        want_counts[0, t] += 1
+    for t in prompts[2] + [3]:
+        want_counts[2, t] += 1
+    assert torch.equal(counts.cpu(), want_counts)
+    logits = torch.randn(rows, vocab, generator=g) * 3
+    presence = torch.tensor([0.25, 9.0, -0.5, 9.0])
+    frequency = torch.tensor([0.5, 9.0, 0.3, 9.0])
+    repetition = torch.tensor([2.0, 9.0, 1.0, 9.0])
+    got = logits.to(DEV)
+    ops.apply_penalties(got, counts, index, presence.to(DEV), frequency.to(DEV), repetition.to(DEV))
+    for r in range(rows):
+        if r in seen:
+            want = pm.plain_apply_penalties(logits[r], seen[r], frequency=float(frequency[r]), presence=float(presence[r]),
+                                            repetition=float(repetition[r]))
+        else:
+            want = logits[r]
+        assert torch.allclose(got[r].cpu().double(), want.double(), atol=1e-6), r
