@@ -200,8 +200,24 @@ struct FsShared {
   unsigned count[FS_BINS];
   unsigned found[4];
   float warp_max[FS_THREADS / 32];
+  float slice_max;
   int index;
 };
+
+// loads from the shared memory of another block of the cluster
+__device__ __forceinline__ unsigned fs_peer_u32(const unsigned* mine, unsigned rank) {
+  unsigned local = (unsigned)__cvta_generic_to_shared(mine), remote, v;
+  asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(remote) : "r"(local), "r"(rank));
+  asm volatile("ld.shared::cluster.u32 %0, [%1];" : "=r"(v) : "r"(remote) : "memory");
+  return v;
+}
+__device__ __forceinline__ u64 fs_peer_u64(const u64* mine, unsigned rank) {
+  unsigned local = (unsigned)__cvta_generic_to_shared(mine), remote;
+  u64 v;
+  asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(remote) : "r"(local), "r"(rank));
+  asm volatile("ld.shared::cluster.u64 %0, [%1];" : "=l"(v) : "r"(remote) : "memory");
+  return v;
+}
 
 // sum over the block; every thread gets it
 __device__ __forceinline__ u64 fs_block_sum(u64 v, u64* scratch /* 33 */) {
@@ -395,16 +411,22 @@ sample_filtered_kernel(const float* __restrict__ logits, int vocab, long long st
                        const float* __restrict__ uniform, float* __restrict__ stored, int* __restrict__ out) {
   extern __shared__ __align__(16) unsigned char fs_raw[];
   FsShared& sh = *reinterpret_cast<FsShared*>(fs_raw);
-  const int r = rows_index ? rows_index[blockIdx.x] : blockIdx.x;
+  // grid (blocks per row, rows): the blocks of a row form a thread-block cluster.  Each takes a slice of
+  // the vocabulary through the two heavy passes (the maximum; the probabilities and the histogram of
+  // their first bits), block 0 adds the histograms up through the cluster's shared memory and goes on alone.
+  const int r = rows_index ? rows_index[blockIdx.y] : blockIdx.y;
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int blocks = gridDim.x, rank = blockIdx.x;
   const float* l = logits + (size_t)r * stride;
   const int pitch = (vocab + 3) & ~3;                 // rows of `stored` start on 16-byte boundaries
-  float* p = stored + (size_t)blockIdx.x * pitch;
+  float* p = stored + (size_t)blockIdx.y * pitch;
   const float t = temperature[r];
+  const int slice = (pitch + blocks - 1) / blocks;
+  const int slice_begin = min(pitch, rank * slice), slice_end = min(pitch, slice_begin + slice);
   // the largest scaled logit
   float best = -INFINITY;
 #pragma unroll 8
-  for (int i = threadIdx.x; i < vocab; i += FS_THREADS) best = fmaxf(best, __fdiv_rn(l[i], t));
+  for (int i = slice_begin + threadIdx.x; i < min(slice_end, vocab); i += FS_THREADS) best = fmaxf(best, __fdiv_rn(l[i], t));
 #pragma unroll
   for (int offset = 16; offset > 0; offset >>= 1) best = fmaxf(best, __shfl_xor_sync(0xffffffffu, best, offset));
   if (lane == 0) sh.warp_max[warp] = best;
@@ -415,24 +437,47 @@ sample_filtered_kernel(const float* __restrict__ logits, int vocab, long long st
   __syncthreads();
   best = sh.warp_max[0];
   for (int w = 1; w < FS_THREADS / 32; ++w) best = fmaxf(best, sh.warp_max[w]);
+  if (blocks > 1) {
+    __syncthreads();
+    if (threadIdx.x == 0) sh.slice_max = best;
+    srb_cluster_sync();
+    for (int b = 0; b < blocks; ++b) best = fmaxf(best, srb_load_peer_shared(&sh.slice_max, b));
+  }
   // the probabilities, stored for the passes to come, and the histogram of their first 11 bits
-  for (int start = 0; start < vocab; start += FS_THREADS * FS_BATCH) {
+  for (int start = slice_begin; start < slice_end; start += FS_THREADS * FS_BATCH) {
     float raw[FS_BATCH];
 #pragma unroll
     for (int j = 0; j < FS_BATCH; ++j) {
       const int i = start + j * FS_THREADS + (int)threadIdx.x;
-      raw[j] = i < vocab ? l[i] : 0.f;
+      raw[j] = i < slice_end && i < vocab ? l[i] : 0.f;
     }
 #pragma unroll
     for (int j = 0; j < FS_BATCH; ++j) {
       const int i = start + j * FS_THREADS + (int)threadIdx.x;
-      const bool live = i < vocab;
+      const bool live = i < slice_end && i < vocab;
       const float value = expf(__fdiv_rn(raw[j], t) - best);
-      if (i < pitch) p[i] = live ? value : -1.f;
+      if (i < slice_end) p[i] = live ? value : -1.f;
       fs_add(sh.first_count, sh.first_mass, live, __float_as_uint(value) >> 21, fs_mass(value));
     }
   }
-  __syncthreads();                                   // the block reads what it wrote to `stored`
+  if (blocks > 1) {
+    srb_cluster_sync();                              // every block's histogram and slice of `stored` are complete
+    if (rank == 0) {
+      for (int b = threadIdx.x; b < FS_BINS; b += FS_THREADS) {
+        unsigned c = sh.first_count[b];
+        u64 m = sh.first_mass[b];
+        for (int other = 1; other < blocks; ++other) {
+          c += fs_peer_u32(&sh.first_count[b], other);
+          m += fs_peer_u64(&sh.first_mass[b], other);
+        }
+        sh.first_count[b] = c;
+        sh.first_mass[b] = m;
+      }
+    }
+    srb_cluster_sync();                              // nobody leaves while its histogram may still be read
+    if (rank != 0) return;
+  }
+  __syncthreads();                                   // the block reads what was written to `stored`
 
   // a prefix of the sorted order: everything above `key`, and the first `n` of those equal to it
   FsCrossing cut;
@@ -543,8 +588,13 @@ extern "C" int srb_sample_filtered(const float* logits, int vocab, long long str
                                        (int)sizeof(FsShared)));
     configured = true;
   }
-  sample_filtered_kernel<<<count, FS_THREADS, sizeof(FsShared), (cudaStream_t)stream>>>(
-      logits, vocab, stride, rows_index, temperature, top_k, top_p, min_p, uniform, scratch, out);
+  // blocks per row: as many (a power of two, 8 at most) as keep all of them resident at once
+  int blocks = 1;
+  while (blocks < 8 && count * blocks * 2 <= 148) blocks *= 2;
+  if (count > 65535) SRB_FAIL("sample_filtered: %d rows exceed one launch", count);
+  SRB_CUDA_CALL(srb_launch_clustered(sample_filtered_kernel, dim3(blocks, count), dim3(FS_THREADS), sizeof(FsShared),
+                                     (cudaStream_t)stream, dim3(blocks, 1, 1), logits, vocab, stride, rows_index,
+                                     temperature, top_k, top_p, min_p, uniform, scratch, out));
   SRB_LAUNCH_CHECK("sample_filtered");
   return SRB_OK;
 }
