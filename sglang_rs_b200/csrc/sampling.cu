@@ -183,7 +183,8 @@ sample_pick_kernel(const float* __restrict__ logits, int vocab, int stride, cons
 // which go to scratch memory; each search then refines inside one bin with two light passes
 // over the stored p.  The position among equal items follows by division.  Masses are integers
 // (p * 2^40, rounded), so sums do not depend on the order in which threads add them and a row's
-// token does not depend on timing.  One block per row.
+// token does not depend on timing.  Up to eight blocks per row (a thread-block cluster) share the
+// passes that build the first histogram; one of them does the searches.
 #define FS_THREADS 1024
 #define FS_BINS 2048
 #define FS_BATCH 8          // loads of a thread in flight at once
