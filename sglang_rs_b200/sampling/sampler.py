@@ -84,48 +84,51 @@ class Sampler:
         GPU.  ``request_ids`` name the rows' requests, for those with penalties (``logits`` is then
         changed in place, and the chosen tokens are counted as seen)."""
         rows = logits.shape[0]
-        seen_rows = None
-        if any(p.has_penalties for p in params):
-            index = [self.seen.row_of(request_ids[r]) if params[r].has_penalties else -1 for r in range(rows)]
-            if any(i < 0 and params[r].has_penalties for r, i in enumerate(index)):
-                raise RuntimeError("a request with penalties has no row of counts; SeenCounts.open was not called")
-            seen_rows = torch.tensor(index, dtype=torch.int32).pin_memory().to(self.device, non_blocking=True)
-            options = torch.tensor(
-                [[p.presence_penalty or 0.0 for p in params], [p.frequency_penalty or 0.0 for p in params],
-                 [p.repetition_penalty if p.repetition_penalty is not None else 1.0 for p in params]],
-                dtype=torch.float32).pin_memory().to(self.device, non_blocking=True)
-            ops.apply_penalties(logits, self.seen.table, seen_rows, options[0], options[1], options[2])
-        temperature = [0.0] * rows
-        uniform = [0.0] * rows
-        cut = []                                   # rows with top-k / top-p / min-p
+        penalised = [r for r in range(rows) if params[r].has_penalties]
+        # what the kernels need per row, in one tensor of floats and one of ints: two copies per step at most
+        temperature, uniform = [0.0] * rows, [0.0] * rows          # of the rows sampled without cuts
+        cut_temperature, top_p, min_p = [1.0] * rows, [1.0] * rows, [0.0] * rows
+        presence, frequency, repetition = [0.0] * rows, [0.0] * rows, [1.0] * rows
+        top_k, seen_row = [0] * rows, [-1] * rows
+        cut = []                                                   # rows with top-k / top-p / min-p
         for r, p in enumerate(params):
+            if p.has_penalties:
+                seen_row[r] = self.seen.row_of(request_ids[r]) if r < len(request_ids) else -1
+                if seen_row[r] < 0:
+                    raise RuntimeError("a request with penalties has no row of counts; SeenCounts.open was not called")
+                presence[r], frequency[r] = p.presence_penalty or 0.0, p.frequency_penalty or 0.0
+                repetition[r] = p.repetition_penalty if p.repetition_penalty is not None else 1.0
             if p.is_greedy:
                 continue
             uniform[r] = randoms[r].next_unit()
             if p.filters:
                 cut.append(r)
+                cut_temperature[r] = p.effective_temperature
+                top_k[r] = int(p.top_k) if p.top_k is not None else 0
+                top_p[r] = float(p.top_p) if p.top_p is not None else 1.0
+                min_p[r] = float(p.min_p) if p.min_p is not None else 0.0
             else:
                 temperature[r] = p.effective_temperature
-        staged = None
-        if cut or any(t > 0 for t in temperature):
-            floats = [temperature, uniform]
-            if cut:
-                floats += [[params[r].effective_temperature if params[r].filters and not params[r].is_greedy else 1.0
-                            for r in range(rows)],
-                           [float(params[r].top_p) if params[r].top_p is not None else 1.0 for r in range(rows)],
-                           [float(params[r].min_p) if params[r].min_p is not None else 0.0 for r in range(rows)]]
-            staged = torch.tensor(floats, dtype=torch.float32).pin_memory().to(self.device, non_blocking=True)
-        if staged is not None and any(t > 0 for t in temperature):
-            picked = ops.sample(logits, staged[0], staged[1])
+        plain = any(t > 0 for t in temperature)
+        floats = ints = None
+        if plain or cut or penalised:
+            floats = torch.tensor([temperature, uniform, cut_temperature, top_p, min_p, presence, frequency, repetition],
+                                  dtype=torch.float32).pin_memory().to(self.device, non_blocking=True)
+        if cut or penalised:
+            ints = torch.tensor([top_k, seen_row, cut + [0] * (rows - len(cut))],
+                                dtype=torch.int32).pin_memory().to(self.device, non_blocking=True)
+        if penalised:
+            ops.apply_penalties(logits, self.seen.table, ints[1], floats[5], floats[6], floats[7])
+        if len(cut) == rows:
+            picked = torch.empty(rows, dtype=torch.int32, device=logits.device)      # every row is written below
+        elif plain:
+            picked = ops.sample(logits, floats[0], floats[1])
         else:
             picked = ops.sample(logits, None, None)
         if cut:
-            ints = torch.tensor([[int(params[r].top_k) if params[r].top_k is not None else 0 for r in range(rows)],
-                                 cut + [0] * (rows - len(cut))], dtype=torch.int32).pin_memory().to(self.device,
-                                                                                                  non_blocking=True)
-            ops.sample_filtered(logits, ints[1, :len(cut)], staged[2], ints[0], staged[3], staged[4], staged[1], picked)
-        if seen_rows is not None:
-            ops.count_picked(self.seen.table, seen_rows, picked)
+            ops.sample_filtered(logits, ints[2, :len(cut)], floats[2], ints[0], floats[3], floats[4], floats[1], picked)
+        if penalised:
+            ops.count_picked(self.seen.table, ints[1], picked)
         return picked
 
     def sample(self, logits: torch.Tensor, params: Sequence[SamplingParams], randoms: Sequence[RequestRandom],
