@@ -311,8 +311,8 @@ class CacheManager:
 
     def _reclaim(self, key: GroupKey, shortfall: int) -> None:
         if self.prefix_tree is not None and key == ("kv", None) and shortfall > 0:
-            # a search of the tree costs as much for one page as for many: take some ahead
-            self.prefix_tree.evict(max(shortfall, self.EVICT_AHEAD))
+            # a search of the tree costs as much for one page as for many: take some ahead, more from a large tree
+            self.prefix_tree.evict(max(shortfall, self.EVICT_AHEAD, self.prefix_tree.pages_held // 256))
 
     def _reclaimable(self, key: GroupKey) -> int:
         return self.prefix_tree.evictable() if self.prefix_tree is not None and key == ("kv", None) else 0
@@ -465,6 +465,8 @@ class CacheManager:
         array = _ints(pairs if pairs else [0])
         if self._lib.hc_check(self._pointer, _pointer(array), len(pairs) // 2) < 0:
             raise AssertionError(_message(self._lib))
+        if self.prefix_tree is not None:
+            self.prefix_tree.check()
         if len(self.live) != self._lib.hc_live_count(self._pointer):
             raise AssertionError("the live requests of the books and of the manager differ")
 

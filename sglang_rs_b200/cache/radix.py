@@ -30,7 +30,7 @@ class PrefixTree:
         self.page_size, self.allocator = int(page_size), allocator
         self._lib = _core_library()
         for name in ("hc_tree_match", "hc_tree_insert", "hc_tree_evictable", "hc_tree_evict", "hc_tree_pages_held",
-                     "hc_tree_pages", "hc_tree_clear", "hc_tree_counters"):
+                     "hc_tree_pages", "hc_tree_clear", "hc_tree_counters", "hc_tree_check"):
             getattr(self._lib, name).restype = ctypes.c_int
         self._lib.hc_tree_create.restype = ctypes.c_void_p
         self._lib.hc_tree_create.argtypes = [ctypes.c_void_p, ctypes.c_int, ctypes.c_int]
@@ -88,8 +88,14 @@ class PrefixTree:
         return adopted
 
     def evictable(self) -> int:
-        """Pages that only the tree holds and that could be freed (leaves first, then their parents)."""
+        """Pages that only the tree holds and that could be freed (leaves first, then their parents).  The
+        tree keeps the count up to date as holders of its pages come and go; asking costs nothing."""
         return self._lib.hc_tree_evictable(self._pointer)
+
+    def check(self) -> None:
+        """The count of evictable pages that the tree keeps up to date equals a walk over the whole tree."""
+        if self._lib.hc_tree_check(self._pointer) < 0:
+            raise AssertionError(_message(self._lib))
 
     def evict(self, pages: int) -> int:
         """Frees up to ``pages`` pages that nobody but the tree holds, least recently used leaves first."""

@@ -37,7 +37,16 @@ struct Group {
   int num_pages = 0;
   std::vector<int> refs;
   std::vector<int> free_stack;     // back() is handed out next
+  // The prefix tree over this group's pages, if there is one, hears when a page goes from one holder
+  // to two or back: it keeps count of the pages that nobody but itself holds.
+  void* watcher = nullptr;
+  void (*shared_changed)(void* watcher, int page, bool shared) = nullptr;
 };
+
+inline void note_holders(Group& group, int page, int before, int after) {
+  if (group.shared_changed && ((before == 1 && after == 2) || (before == 2 && after == 1)))
+    group.shared_changed(group.watcher, page, after == 2);
+}
 
 struct Request {
   bool live = false;
@@ -62,10 +71,12 @@ bool good_group(const Core* core, int g) { return core && g >= 0 && g < (int)cor
 int release_page(Group& group, int page) {
   if (page < 0 || page >= group.num_pages || group.refs[page] <= 0)
     return fail(-4, "page %d is freed twice or was never handed out", page);
-  if (--group.refs[page] == 0) {
+  const int after = --group.refs[page];
+  if (after == 0) {
     group.free_stack.push_back(page);
     return 1;
   }
+  note_holders(group, page, after + 1, after);
   return 0;
 }
 
@@ -133,7 +144,9 @@ int hc_retain(void* handle, int g, int page) {
   Group& group = core->groups[g];
   if (page < 0 || page >= group.num_pages || group.refs[page] <= 0)
     return fail(-4, "page %d is free and cannot be shared", page);
-  return ++group.refs[page];
+  const int after = ++group.refs[page];
+  note_holders(group, page, after - 1, after);
+  return after;
 }
 
 int hc_release(void* handle, int g, int page) {   // 1 if the page went back to the free stack
@@ -320,7 +333,8 @@ int hc_adopt_prefix(void* handle, int r, int g, const int* pages, int count) {
     if (pages[i] < 0 || pages[i] >= group.num_pages || group.refs[pages[i]] <= 0)
       return fail(-4, "page %d is free and cannot be shared", pages[i]);
   for (int i = 0; i < count; ++i) {
-    ++group.refs[pages[i]];
+    const int after = ++group.refs[pages[i]];
+    note_holders(group, pages[i], after - 1, after);
     request.tables[g].push_back(pages[i]);
   }
   request.length = count * core->page_size;
@@ -464,6 +478,7 @@ struct TreeNode {
   int page = -1;
   TreeNode* parent = nullptr;
   long long stamp = 0;
+  int busy = 0;                    // nodes of this subtree, itself included, whose page someone else holds too
   std::map<std::vector<int>, std::unique_ptr<TreeNode>> children;
 };
 
@@ -475,7 +490,24 @@ struct Tree {
   long long clock = 0;
   int pages_held = 0;
   long long lookups = 0, hits = 0;
+  // Pages that eviction could free: nodes with nothing busy below them.  Kept up to date as holders
+  // come and go (a walk from the node to the root each time), so asking costs nothing.
+  int evictable = 0;
+  std::vector<TreeNode*> node_of_page;
 };
+
+// a page of the tree got a second holder, or lost it
+void tree_shared_changed(void* watcher, int page, bool shared) {
+  Tree* tree = static_cast<Tree*>(watcher);
+  if (page < 0 || page >= (int)tree->node_of_page.size()) return;
+  for (TreeNode* node = tree->node_of_page[page]; node && node != &tree->root; node = node->parent) {
+    if (shared) {
+      if (node->busy++ == 0) --tree->evictable;
+    } else {
+      if (--node->busy == 0) ++tree->evictable;
+    }
+  }
+}
 
 void collect_leaves(TreeNode* node, std::vector<TreeNode*>& out) {
   for (auto& entry : node->children) {
@@ -502,6 +534,31 @@ int count_evictable(const Tree* tree, const TreeNode* node, bool is_root, bool* 
   return total + (mine ? 1 : 0);
 }
 
+// frees up to `pages` pages that nobody but the tree holds, least recently used leaves first
+int evict_pages(Tree* tree, int pages) {
+  Group& group = tree->core->groups[tree->group];
+  int freed = 0;
+  while (freed < pages) {
+    std::vector<TreeNode*> leaves;
+    collect_leaves(&tree->root, leaves);
+    leaves.erase(std::remove_if(leaves.begin(), leaves.end(), [&](TreeNode* n) { return group.refs[n->page] != 1; }),
+                 leaves.end());
+    if (leaves.empty()) break;
+    std::stable_sort(leaves.begin(), leaves.end(), [](TreeNode* a, TreeNode* b) { return a->stamp < b->stamp; });
+    for (TreeNode* leaf : leaves) {
+      tree->node_of_page[leaf->page] = nullptr;       // a leaf that only the tree holds was counted as evictable
+      --tree->evictable;
+      if (release_page(group, leaf->page) < 0) return -4;
+      --tree->pages_held;
+      ++freed;
+      const std::vector<int> key = leaf->key;        // the node, and its key with it, goes with the erase
+      leaf->parent->children.erase(key);
+      if (freed >= pages) break;
+    }
+  }
+  return freed;
+}
+
 void collect_pages(const TreeNode* node, std::vector<int>& out) {
   for (const auto& entry : node->children) {
     out.push_back(entry.second->page);
@@ -520,10 +577,22 @@ void* hc_tree_create(void* handle, int g, int page_size) {
   tree->core = core;
   tree->group = g;
   tree->page_size = page_size;
+  tree->node_of_page.assign(core->groups[g].num_pages, nullptr);
+  core->groups[g].watcher = tree;
+  core->groups[g].shared_changed = tree_shared_changed;
   return tree;
 }
 
-void hc_tree_destroy(void* handle) { delete static_cast<Tree*>(handle); }
+void hc_tree_destroy(void* handle) {
+  Tree* tree = static_cast<Tree*>(handle);
+  if (!tree) return;
+  Group& group = tree->core->groups[tree->group];
+  if (group.watcher == tree) {
+    group.watcher = nullptr;
+    group.shared_changed = nullptr;
+  }
+  delete tree;
+}
 
 // page ids of the longest known prefix of tokens[0..count), leaving at least one token out
 int hc_tree_match(void* handle, const int* tokens, int count, int* pages_out) {
@@ -568,15 +637,19 @@ int hc_tree_insert(void* handle, const int* tokens, int token_count, const int* 
       if (pages[i] < 0) break;
       if (pages[i] >= group.num_pages || group.refs[pages[i]] <= 0)
         return fail(-4, "page %d is free and cannot be shared", pages[i]);
+      if (tree->node_of_page[pages[i]]) return fail(-4, "page %d is in the tree already", pages[i]);
       std::unique_ptr<TreeNode> fresh(new TreeNode());
       fresh->key = key;
       fresh->page = pages[i];
       fresh->parent = node;
       child = fresh.get();
       node->children.emplace(key, std::move(fresh));
-      ++group.refs[pages[i]];
+      ++group.refs[pages[i]];                         // the tree's own hold; who gave the page holds it too
       ++tree->pages_held;
       ++adopted;
+      tree->node_of_page[pages[i]] = child;
+      ++tree->evictable;                              // as if nobody else held it, then corrected
+      if (group.refs[pages[i]] > 1) tree_shared_changed(tree, pages[i], true);
     } else {
       child = it->second.get();
     }
@@ -589,33 +662,30 @@ int hc_tree_insert(void* handle, const int* tokens, int token_count, const int* 
 int hc_tree_evictable(void* handle) {
   Tree* tree = static_cast<Tree*>(handle);
   if (!tree) return fail(-1, "no tree");
-  bool unused = false;
-  return count_evictable(tree, &tree->root, true, &unused);
+  return tree->evictable;
 }
 
-// frees up to `pages` pages that nobody but the tree holds, least recently used leaves first
 int hc_tree_evict(void* handle, int pages) {
   Tree* tree = static_cast<Tree*>(handle);
   if (!tree) return fail(-1, "no tree");
-  Group& group = tree->core->groups[tree->group];
-  int freed = 0;
-  while (freed < pages) {
-    std::vector<TreeNode*> leaves;
-    collect_leaves(&tree->root, leaves);
-    leaves.erase(std::remove_if(leaves.begin(), leaves.end(), [&](TreeNode* n) { return group.refs[n->page] != 1; }),
-                 leaves.end());
-    if (leaves.empty()) break;
-    std::stable_sort(leaves.begin(), leaves.end(), [](TreeNode* a, TreeNode* b) { return a->stamp < b->stamp; });
-    for (TreeNode* leaf : leaves) {
-      if (release_page(group, leaf->page) < 0) return -4;
-      --tree->pages_held;
-      ++freed;
-      const std::vector<int> key = leaf->key;        // the node, and its key with it, goes with the erase
-      leaf->parent->children.erase(key);
-      if (freed >= pages) break;
-    }
-  }
-  return freed;
+  return evict_pages(tree, pages);
+}
+
+// the count that is kept up to date against a walk over the whole tree
+int hc_tree_check(void* handle) {
+  Tree* tree = static_cast<Tree*>(handle);
+  if (!tree) return fail(-1, "no tree");
+  bool unused = false;
+  const int walked = count_evictable(tree, &tree->root, true, &unused);
+  if (walked != tree->evictable)
+    return fail(-4, "the tree counts %d pages that eviction could free, a walk finds %d", tree->evictable, walked);
+  std::vector<int> pages;
+  collect_pages(&tree->root, pages);
+  if ((int)pages.size() != tree->pages_held) return fail(-4, "the tree holds %d pages, counted %d", (int)pages.size(), tree->pages_held);
+  for (int page : pages)
+    if (!tree->node_of_page[page] || tree->node_of_page[page]->page != page)
+      return fail(-4, "page %d of the tree has no node", page);
+  return 0;
 }
 
 // look-ups of prefixes so far (by the scheduler or through the Python face) and how many found something
@@ -643,6 +713,8 @@ int hc_tree_clear(void* handle) {
   if (!tree) return fail(-1, "no tree");
   std::vector<int> pages;
   collect_pages(&tree->root, pages);
+  for (int page : pages) tree->node_of_page[page] = nullptr;      // no node hears of the releases below
+  tree->evictable = 0;
   for (int page : pages)
     if (release_page(tree->core->groups[tree->group], page) < 0) return -4;
   tree->root.children.clear();
@@ -724,40 +796,17 @@ int token_at(const SchedRequest& r, int position) {
   return -1;                                   // still on the device
 }
 
-int reclaimable(const Sched* s, int g) {
-  if (!s->tree || s->tree->group != g) return 0;
-  bool unused = false;
-  return count_evictable(s->tree, &s->tree->root, true, &unused);
-}
+int reclaimable(const Sched* s, int g) { return s->tree && s->tree->group == g ? s->tree->evictable : 0; }
 
-int evict(Sched* s, int pages) {
-  Group& group = s->core->groups[s->tree->group];
-  int freed = 0;
-  while (freed < pages) {
-    std::vector<TreeNode*> leaves;
-    collect_leaves(&s->tree->root, leaves);
-    leaves.erase(std::remove_if(leaves.begin(), leaves.end(), [&](TreeNode* n) { return group.refs[n->page] != 1; }),
-                 leaves.end());
-    if (leaves.empty()) break;
-    std::stable_sort(leaves.begin(), leaves.end(), [](TreeNode* a, TreeNode* b) { return a->stamp < b->stamp; });
-    for (TreeNode* leaf : leaves) {
-      release_page(group, leaf->page);
-      --s->tree->pages_held;
-      ++freed;
-      const std::vector<int> key = leaf->key;
-      leaf->parent->children.erase(key);
-      if (freed >= pages) break;
-    }
-  }
-  return freed;
-}
+int evict(Sched* s, int pages) { return evict_pages(s->tree, pages); }
 
 // room for `tokens` more tokens, evicting cached prefixes if that helps; false: nothing changed
 bool reserve(Sched* s, int handle, int tokens) {
   int short_group = 0, shortfall = 0;
   int status = hc_reserve(s->core, handle, tokens, &short_group, &shortfall);
   if (status == -2 && s->tree && s->tree->group == short_group) {
-    evict(s, std::max(shortfall, s->evict_ahead));
+    // a search for leaves walks the whole tree, whatever it frees: a large tree gives more at once
+    evict(s, std::max(std::max(shortfall, s->evict_ahead), s->tree->pages_held / 256));
     status = hc_reserve(s->core, handle, tokens, &short_group, &shortfall);
   }
   return status == 0;

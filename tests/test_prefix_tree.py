@@ -119,3 +119,36 @@ def test_random_workloads_with_shared_prefixes_and_a_small_pool(seed):
     assert any(r.cached_tokens for r in requests)
     cache.prefix_tree.clear()
     assert cache.allocators[FULL].free_count == cache.allocators[FULL].num_pages
+
+
+def test_evictable_count_is_kept_without_a_walk():
+    """Two requests compute the same prompt at the same time; the second publishes a page below nodes that
+    hold the first one's pages.  When the first ends, its pages have no other holder but cannot be freed
+    while the page below them is in use: the count that the tree keeps says so, and a walk agrees."""
+    cache = CacheManager([PagedKV(2, 16)], page_size=4, max_tokens=64, max_requests=4, device=None)
+    tree = cache.enable_prefix_reuse()
+    tokens = list(range(16))
+    a, b = cache.open("a"), cache.open("b")
+    for handle, count in ((a, 12), (b, 16)):
+        cache.reserve(handle, count); cache.commit(handle, count)
+    assert tree.insert(tokens[:12], a.tables[FULL]) == 3
+    assert tree.insert(tokens, b.tables[FULL]) == 1                  # three nodes exist already, one is new
+    assert tree.evictable() == 0
+    cache.check_invariants()
+    cache.close(a)
+    assert tree.evictable() == 0                                      # b's page below keeps a's three from eviction
+    cache.check_invariants()
+    c = cache.open("c")
+    cache.adopt_prefix(c, FULL, tree.match(tokens + [99]))
+    assert c.length == 16
+    cache.close(b)
+    assert tree.evictable() == 0                                      # c holds the whole path now
+    cache.check_invariants()
+    cache.close(c)
+    assert tree.evictable() == 4
+    cache.check_invariants()
+    assert tree.evict(1) == 1 and tree.evictable() == 3
+    cache.check_invariants()
+    tree.clear()
+    assert tree.evictable() == 0 and cache.allocators[FULL].free_count == 16
+    cache.check_invariants()
