@@ -311,8 +311,8 @@ class CacheManager:
 
     def _reclaim(self, key: GroupKey, shortfall: int) -> None:
         if self.prefix_tree is not None and key == ("kv", None) and shortfall > 0:
-            # a search of the tree costs as much for one page as for many: take some ahead, more from a large tree
-            self.prefix_tree.evict(max(shortfall, self.EVICT_AHEAD, self.prefix_tree.pages_held // 256))
+            # some ahead, so that the next pages are there without another call
+            self.prefix_tree.evict(max(shortfall, self.EVICT_AHEAD))
 
     def _reclaimable(self, key: GroupKey) -> int:
         return self.prefix_tree.evictable() if self.prefix_tree is not None and key == ("kv", None) else 0

@@ -479,6 +479,9 @@ struct TreeNode {
   TreeNode* parent = nullptr;
   long long stamp = 0;
   int busy = 0;                    // nodes of this subtree, itself included, whose page someone else holds too
+  long long serial = 0;            // order of creation: decides between equal stamps
+  bool listed = false;             // among the tree's idle leaves, under `listed_stamp`
+  long long listed_stamp = 0;
   std::map<std::vector<int>, std::unique_ptr<TreeNode>> children;
 };
 
@@ -494,7 +497,32 @@ struct Tree {
   // come and go (a walk from the node to the root each time), so asking costs nothing.
   int evictable = 0;
   std::vector<TreeNode*> node_of_page;
+  // Leaves that only the tree holds, least recently used first: what eviction takes next, without a
+  // search.  A node enters when it is a leaf and idle, and leaves when it gets a child, a second holder
+  // or a new stamp (it enters again under the new one).
+  std::map<std::pair<long long, long long>, TreeNode*> idle_leaves;
+  long long serials = 0;
 };
+
+void unlist(Tree* tree, TreeNode* node) {
+  if (!node->listed) return;
+  tree->idle_leaves.erase(std::make_pair(node->listed_stamp, node->serial));
+  node->listed = false;
+}
+
+void list_if_idle_leaf(Tree* tree, TreeNode* node) {
+  if (node == &tree->root || node->listed || node->busy != 0 || !node->children.empty()) return;
+  node->listed_stamp = node->stamp;
+  node->listed = true;
+  tree->idle_leaves[std::make_pair(node->stamp, node->serial)] = node;
+}
+
+void touch(Tree* tree, TreeNode* node, long long stamp) {
+  const bool was = node->listed;
+  unlist(tree, node);
+  node->stamp = stamp;
+  if (was) list_if_idle_leaf(tree, node);
+}
 
 // a page of the tree got a second holder, or lost it
 void tree_shared_changed(void* watcher, int page, bool shared) {
@@ -502,9 +530,15 @@ void tree_shared_changed(void* watcher, int page, bool shared) {
   if (page < 0 || page >= (int)tree->node_of_page.size()) return;
   for (TreeNode* node = tree->node_of_page[page]; node && node != &tree->root; node = node->parent) {
     if (shared) {
-      if (node->busy++ == 0) --tree->evictable;
+      if (node->busy++ == 0) {
+        --tree->evictable;
+        unlist(tree, node);
+      }
     } else {
-      if (--node->busy == 0) ++tree->evictable;
+      if (--node->busy == 0) {
+        ++tree->evictable;
+        list_if_idle_leaf(tree, node);
+      }
     }
   }
 }
@@ -538,23 +572,18 @@ int count_evictable(const Tree* tree, const TreeNode* node, bool is_root, bool* 
 int evict_pages(Tree* tree, int pages) {
   Group& group = tree->core->groups[tree->group];
   int freed = 0;
-  while (freed < pages) {
-    std::vector<TreeNode*> leaves;
-    collect_leaves(&tree->root, leaves);
-    leaves.erase(std::remove_if(leaves.begin(), leaves.end(), [&](TreeNode* n) { return group.refs[n->page] != 1; }),
-                 leaves.end());
-    if (leaves.empty()) break;
-    std::stable_sort(leaves.begin(), leaves.end(), [](TreeNode* a, TreeNode* b) { return a->stamp < b->stamp; });
-    for (TreeNode* leaf : leaves) {
-      tree->node_of_page[leaf->page] = nullptr;       // a leaf that only the tree holds was counted as evictable
-      --tree->evictable;
-      if (release_page(group, leaf->page) < 0) return -4;
-      --tree->pages_held;
-      ++freed;
-      const std::vector<int> key = leaf->key;        // the node, and its key with it, goes with the erase
-      leaf->parent->children.erase(key);
-      if (freed >= pages) break;
-    }
+  while (freed < pages && !tree->idle_leaves.empty()) {
+    TreeNode* leaf = tree->idle_leaves.begin()->second;
+    unlist(tree, leaf);
+    tree->node_of_page[leaf->page] = nullptr;
+    --tree->evictable;
+    if (release_page(group, leaf->page) < 0) return -4;
+    --tree->pages_held;
+    ++freed;
+    TreeNode* parent = leaf->parent;
+    const std::vector<int> key = leaf->key;          // the node, and its key with it, goes with the erase
+    parent->children.erase(key);
+    list_if_idle_leaf(tree, parent);                 // it may be a leaf now, and the next to go
   }
   return freed;
 }
@@ -609,7 +638,7 @@ int hc_tree_match(void* handle, const int* tokens, int count, int* pages_out) {
     auto it = node->children.find(key);
     if (it == node->children.end()) break;
     node = it->second.get();
-    node->stamp = stamp;
+    touch(tree, node, stamp);
     pages_out[found++] = node->page;
   }
   ++tree->lookups;
@@ -642,7 +671,9 @@ int hc_tree_insert(void* handle, const int* tokens, int token_count, const int* 
       fresh->key = key;
       fresh->page = pages[i];
       fresh->parent = node;
+      fresh->serial = ++tree->serials;
       child = fresh.get();
+      if (node != &tree->root) unlist(tree, node);   // no leaf any more
       node->children.emplace(key, std::move(fresh));
       ++group.refs[pages[i]];                         // the tree's own hold; who gave the page holds it too
       ++tree->pages_held;
@@ -650,10 +681,11 @@ int hc_tree_insert(void* handle, const int* tokens, int token_count, const int* 
       tree->node_of_page[pages[i]] = child;
       ++tree->evictable;                              // as if nobody else held it, then corrected
       if (group.refs[pages[i]] > 1) tree_shared_changed(tree, pages[i], true);
+      else list_if_idle_leaf(tree, child);
     } else {
       child = it->second.get();
     }
-    child->stamp = stamp;
+    touch(tree, child, stamp);
     node = child;
   }
   return adopted;
@@ -685,6 +717,17 @@ int hc_tree_check(void* handle) {
   for (int page : pages)
     if (!tree->node_of_page[page] || tree->node_of_page[page]->page != page)
       return fail(-4, "page %d of the tree has no node", page);
+  // the list of idle leaves against a walk
+  std::vector<TreeNode*> leaves;
+  collect_leaves(&tree->root, leaves);
+  size_t idle = 0;
+  for (TreeNode* leaf : leaves) {
+    const bool wanted = tree->core->groups[tree->group].refs[leaf->page] == 1;
+    if (wanted != leaf->listed) return fail(-4, "the leaf of page %d is %s the list of idle leaves", leaf->page, leaf->listed ? "wrongly in" : "missing from");
+    if (leaf->listed && leaf->listed_stamp != leaf->stamp) return fail(-4, "the leaf of page %d is listed under an old stamp", leaf->page);
+    idle += wanted ? 1 : 0;
+  }
+  if (idle != tree->idle_leaves.size()) return fail(-4, "%d idle leaves are listed, a walk finds %d", (int)tree->idle_leaves.size(), (int)idle);
   return 0;
 }
 
@@ -715,6 +758,7 @@ int hc_tree_clear(void* handle) {
   collect_pages(&tree->root, pages);
   for (int page : pages) tree->node_of_page[page] = nullptr;      // no node hears of the releases below
   tree->evictable = 0;
+  tree->idle_leaves.clear();
   for (int page : pages)
     if (release_page(tree->core->groups[tree->group], page) < 0) return -4;
   tree->root.children.clear();
@@ -805,8 +849,7 @@ bool reserve(Sched* s, int handle, int tokens) {
   int short_group = 0, shortfall = 0;
   int status = hc_reserve(s->core, handle, tokens, &short_group, &shortfall);
   if (status == -2 && s->tree && s->tree->group == short_group) {
-    // a search for leaves walks the whole tree, whatever it frees: a large tree gives more at once
-    evict(s, std::max(std::max(shortfall, s->evict_ahead), s->tree->pages_held / 256));
+    evict(s, std::max(shortfall, s->evict_ahead));
     status = hc_reserve(s->core, handle, tokens, &short_group, &shortfall);
   }
   return status == 0;
