@@ -6,7 +6,7 @@ them (crates/sglang-srt/src/cli.rs:196-462, defaults :651-718): ``--model-path``
 ``--max-running-requests``, ``--chunked-prefill-size``; ``--flag=value`` is accepted
 (:720-723) and unknown flags are kept, not rejected (:575-582).  The reference's only command
 starts a server; here the commands are ``generate`` (tokens in, tokens out),
-``random-model`` (write a model folder from a config and a seed) and ``replay``.
+``random-model`` (write a model folder from a config and a seed), ``replay`` and ``bench``.
 """
 from __future__ import annotations
 
@@ -67,6 +67,7 @@ def build_parser() -> argparse.ArgumentParser:
     rnd.add_argument("--dtype", default="bfloat16", choices=("bfloat16", "float32"))
 
     commands.add_parser("replay", help="trace replay; same options as bin/trace_run", add_help=False)
+    commands.add_parser("bench", help="the benchmark of the repository; same options as bench.py", add_help=False)
     return parser
 
 
@@ -75,6 +76,23 @@ def main(argv: Optional[List[str]] = None) -> int:
     if argv and argv[0] == "replay":
         from .engine.replay import main as replay_main
         return replay_main(argv[1:])
+    if argv and argv[0] == "bench":
+        # bench.py lies beside the package, at the root of the repository
+        import os
+        import runpy
+        script = os.path.join(os.path.dirname(os.path.dirname(os.path.realpath(__file__))), "bench.py")
+        if not os.path.exists(script):
+            print(f"[sglang-rs] {script} does not exist: the benchmark comes with the repository, not with the package",
+                  file=sys.stderr)
+            return 2
+        saved, sys.argv = sys.argv, [script] + argv[1:]
+        try:
+            runpy.run_path(script, run_name="__main__")
+        except SystemExit as done:
+            return int(done.code or 0)
+        finally:
+            sys.argv = saved
+        return 0
     args, extra = build_parser().parse_known_args(argv)
     if extra:
         print(f"[sglang-rs] ignoring unknown arguments: {extra}", file=sys.stderr)

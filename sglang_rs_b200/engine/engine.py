@@ -213,6 +213,17 @@ class Engine:
         self.sampler.seen.close(request_id)
         return self.scheduler.abort(request_id)
 
+    def forward_logits(self, record: Mapping):
+        """One step record of trace replay (``{"entries": [{"id", "tokens", "want"}], "end": [...]}``) through
+        this engine's model, cache and step function; the wanted logits as a host float32 array, or None.
+        For tests: the requests of a trace hold pages of the engine's pool until their ``end``, beside the
+        scheduler's requests."""
+        from .replay import ReplaySession
+        if getattr(self, "_replay", None) is None:
+            self._replay = ReplaySession.over(self.model, self.cache, self.runner)
+        self.drain()
+        return self._replay.run(dict(record))
+
     def flush_cache(self) -> bool:
         """Possible only while nothing is queued or running, as in the reference
         (crates/sglang-srt/src/scheduler.rs:442-454)."""

@@ -42,6 +42,13 @@ class ReplaySession:
         self.runner = ModelRunner(self.model, self.cache, use_cuda_graphs=use_cuda_graphs)
         self.handles = {}
 
+    @classmethod
+    def over(cls, model, cache, runner) -> "ReplaySession":
+        """A session that drives a model, cache and runner that exist already (an engine's)."""
+        session = cls.__new__(cls)
+        session.dtype, session.model, session.cache, session.runner, session.handles = runner.dtype, model, cache, runner, {}
+        return session
+
     def run(self, record: dict):
         """One step record; returns the wanted logits as a host float32 array, or None."""
         from .runner import StepEntry

@@ -40,3 +40,10 @@ def test_sampling_options_and_prompts():
 def test_random_model_command():
     args, _ = parse("random-model", "--config", "c.json", "--out", "/o", "--seed", "5", "--dtype", "float32")
     assert (args.command, args.config, args.out, args.seed, args.dtype) == ("random-model", "c.json", "/o", 5, "float32")
+
+
+def test_bench_command_runs_the_benchmark_of_the_repository(capsys):
+    from sglang_rs_b200.cli import main
+    assert main(["bench", "--impl", "reference"]) == 0
+    assert '"impl": "reference"' in capsys.readouterr().out
+    assert main(["bench", "--gpus", "2"]) == 2

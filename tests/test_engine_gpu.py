@@ -57,6 +57,25 @@ def test_greedy_generation_through_the_entry_point(tmp_path, config, page, chunk
     assert all(a.free_count == a.num_pages for a in engine.cache.allocators.values())
 
 
+def test_logits_of_a_trace_through_the_engine(tmp_path):
+    """`Engine.forward_logits` takes the step records of trace replay: the engine's own model, cache and
+    step function, beside its scheduler."""
+    from sglang_rs_b200 import Engine
+    folder = rh.make_folder(tmp_path, "m", pm.TINY_A, seed=4, dtype=torch.float32)
+    cfg, weights = pm.load_folder(folder)
+    engine = Engine(model_path=folder, dtype="float32", max_total_tokens=256)
+    tokens = rh.random_requests(pm.TINY_A, (40,), seed=1)["r0"]
+    want = pm.plain_forward(cfg, weights, tokens).numpy()
+    first = engine.forward_logits({"entries": [{"id": "t", "tokens": tokens[:33], "want": [0, 32]}], "end": []})
+    assert engine.forward_logits({"entries": [{"id": "t", "tokens": tokens[33:39], "want": []}]}) is None
+    last = engine.forward_logits({"entries": [{"id": "t", "tokens": tokens[39:], "want": [0]}], "end": ["t"]})
+    scale = abs(want).max()
+    for got, position in ((first[0], 0), (first[1], 32), (last[0], 39)):
+        assert abs(got - want[position]).max() / scale < rh.FP32_TOLERANCE
+    assert engine.generate(tokens[:5], {"max_new_tokens": 4})["output_ids"] == pm.plain_greedy(cfg, weights, tokens[:5], 4)
+    engine.cache.check_invariants()
+
+
 def test_preemption_on_a_small_pool_gives_the_same_tokens(tmp_path):
     from sglang_rs_b200 import Engine
     folder = rh.make_folder(tmp_path, "m", pm.TINY_A, seed=4, dtype=torch.float32)
