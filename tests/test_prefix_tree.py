@@ -152,3 +152,51 @@ def test_evictable_count_is_kept_without_a_walk():
     tree.clear()
     assert tree.evictable() == 0 and cache.allocators[FULL].free_count == 16
     cache.check_invariants()
+
+
+@pytest.mark.parametrize("seed", range(6))
+def test_tree_books_under_random_orders_of_holders(seed):
+    """Requests publish, adopt, end and come back in random order, eviction takes pages in between: after
+    every move the count of evictable pages and the list of idle leaves equal a walk over the tree, and no
+    page is lost or held by a node that is gone."""
+    rng = random.Random(seed)
+    page_size, num_pages = 2, 48
+    cache = CacheManager([PagedKV(2, 16)], page_size=page_size, max_tokens=num_pages * page_size, max_requests=8, device=None)
+    tree = cache.enable_prefix_reuse()
+    stems = [[rng.randrange(5) for _ in range(rng.randrange(2, 9))] for _ in range(3)]
+    live = {}
+    for move in range(300):
+        kind = rng.random()
+        if kind < 0.45 and len(live) < 8:
+            tokens = rng.choice(stems) + [rng.randrange(5) for _ in range(rng.randrange(0, 9))]
+            handle = cache.open(f"r{move}")
+            matched = tree.match(tokens)
+            if matched:
+                cache.adopt_prefix(handle, FULL, matched)
+            rest = len(tokens) - handle.length
+            if not cache.can_reserve(handle, rest):
+                cache.close(handle)
+                continue
+            cache.reserve(handle, rest); cache.commit(handle, rest)
+            live[handle.request_id] = (handle, tokens)
+            if rng.random() < 0.8:
+                tree.insert(tokens, handle.tables[FULL])
+        elif kind < 0.8 and live:
+            handle, _ = live.pop(rng.choice(sorted(live)))
+            cache.close(handle)
+        elif kind < 0.95:
+            before = tree.evictable()
+            freed = tree.evict(rng.randrange(1, 6))
+            assert freed <= before and tree.evictable() == before - freed
+        else:
+            tree.match(rng.choice(stems) + [0, 1])                    # a look-up alone moves stamps
+        cache.check_invariants()
+    for handle, _ in live.values():
+        cache.close(handle)
+    cache.check_invariants()
+    assert tree.evictable() == tree.pages_held
+    held = tree.pages_held
+    assert tree.evict(10 ** 6) == held and tree.pages_held == 0 and tree.evictable() == 0
+    tree.clear()
+    cache.check_invariants()
+    assert cache.allocators[FULL].free_count == num_pages
