@@ -25,10 +25,13 @@ class LayerCall:
 
 class DecoderModel(Part):
     def __init__(self, embedding, layers: Sequence, final_norm, head, *, vocab_size: int, max_positions: int,
-                 program: Optional[Sequence[LayerCall]] = None, eos_token_ids: Sequence[int] = ()):
+                 program: Optional[Sequence[LayerCall]] = None, eos_token_ids: Sequence[int] = (),
+                 ignored_tensors: Sequence[str] = ()):
         self.embedding, self.layers, self.final_norm, self.head = embedding, list(layers), final_norm, head
         self.vocab_size, self.max_positions = int(vocab_size), int(max_positions)
         self.eos_token_ids = tuple(eos_token_ids)
+        #: shell-style patterns of checkpoint tensors that may be present and that nothing reads
+        self.ignored_tensors = tuple(ignored_tensors)
         self.program: List[LayerCall] = list(program) if program is not None else [
             LayerCall(i) for i in range(len(self.layers))]
         for index, call in enumerate(self.program):

@@ -53,7 +53,8 @@ def load_model(model_path: Optional[str] = None, *, device="cuda", dtype="bfloat
     else:
         if model_path is None:
             raise ValueError("a model folder is needed unless random_weights is set")
-        tensors = load_checkpoint(model_path, {name: spec.shape for name, spec in specs.items()})
+        tensors = load_checkpoint(model_path, {name: spec.shape for name, spec in specs.items()},
+                                  tuple(getattr(model, "ignored_tensors", ())))
     model.load(tensors, device, dtype)
     model.config = typed
     return model

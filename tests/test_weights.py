@@ -32,7 +32,8 @@ def test_round_trip_all_dtypes(tmp_path):
 
 
 def test_stored_form_rule():
-    assert stored_form(torch.zeros(2, dtype=torch.float16)).dtype == torch.bfloat16
+    # float16 is kept as stored: the 32-bit path widens it exactly, the bfloat16 path rounds it once
+    assert stored_form(torch.zeros(2, dtype=torch.float16)).dtype == torch.float16
     assert stored_form(torch.zeros(2, dtype=torch.bfloat16)).dtype == torch.bfloat16
     assert stored_form(torch.zeros(2, dtype=torch.float32)).dtype == torch.float32      # 32-bit stays 32-bit
     assert stored_form(torch.zeros(2, dtype=torch.int64)).dtype == torch.int32          # integer tables
@@ -79,17 +80,56 @@ def test_model_folder_and_one_error_for_everything(tmp_path):
     tensors["model.layers.0.self_attn.q_norm.weight"] = torch.ones(5)
     tensors["model.layers.2.self_attn.k_proj.weight"] = torch.ones(4, 4)
     tensors["model.layers.0.self_attn.rotary_emb.inv_freq"] = torch.ones(16)
+    tensors["model.layers.0.self_attn.extra.weight"] = torch.ones(16)
     write_file(os.path.join(folder, "model.safetensors"), tensors)
     with pytest.raises(WeightLoadError) as error:
         load_checkpoint(folder, expected)
     e = error.value
     assert e.missing == ["lm_head.weight", "model.layers.1.mlp.down_proj.weight"]
-    assert e.unexpected == ["model.layers.0.self_attn.rotary_emb.inv_freq"]
+    assert e.unexpected == ["model.layers.0.self_attn.extra.weight", "model.layers.0.self_attn.rotary_emb.inv_freq"]
     assert [name for name, _, _ in e.wrong_shape] == ["model.layers.0.self_attn.q_norm.weight",
                                                       "model.layers.2.self_attn.k_proj.weight"]
     text = str(e)
-    for fragment in ("missing tensors (2)", "unexpected tensors (1)", "wrong shapes (2)", "expected [32] found [5]"):
+    for fragment in ("missing tensors (2)", "unexpected tensors (2)", "wrong shapes (2)", "expected [32] found [5]"):
         assert fragment in text
+
+
+def test_buffers_that_exporters_write_are_not_an_error(tmp_path):
+    """A tied model whose file also holds ``lm_head.weight``, and rotary frequency buffers: the model names
+    them as ignorable, so they load (the reference binds by name and never reads them); any other
+    unexpected tensor is still an error."""
+    folder = write_model_folder(str(tmp_path / "tied"), TINY_A, seed=5, dtype=torch.float32)
+    model, _ = build_model(folder)
+    expected = {name: spec.shape for name, spec in model.tensor_specs().items()}
+    tensors = dict(read_model_dir(folder))
+    tensors["lm_head.weight"] = tensors["model.embed_tokens.weight"].clone()
+    tensors["model.layers.1.self_attn.rotary_emb.inv_freq"] = torch.ones(8)
+    write_file(os.path.join(folder, "model.safetensors"), tensors)
+    good = load_checkpoint(folder, expected, model.ignored_tensors)
+    assert set(good) == set(expected) and "lm_head.weight" not in good
+    with pytest.raises(WeightLoadError) as error:
+        load_checkpoint(folder, expected)                    # without the model's list both are unexpected
+    assert error.value.unexpected == ["lm_head.weight", "model.layers.1.self_attn.rotary_emb.inv_freq"]
+    # an untied model does not ignore a head: there it is expected, and a second one under another name is not
+    untied, _ = build_model(write_model_folder(str(tmp_path / "untied"), TINY_B, seed=5, dtype=torch.float32))
+    assert "lm_head.weight" not in untied.ignored_tensors and "lm_head.weight" in untied.tensor_specs()
+
+
+def test_float16_checkpoint_is_widened_exactly_for_the_32_bit_path(tmp_path):
+    """The host side of the rule: a float16 tensor reaches the part unrounded, and the part's cast to
+    float32 is exact (the reference widens every stored float type, model_artifacts.rs:850-860)."""
+    from sglang_rs_b200.parts.base import matrix_to, scale_to
+    folder = write_model_folder(str(tmp_path / "h"), TINY_A, seed=9, dtype=torch.float16)
+    model, _ = build_model(folder)
+    loaded = load_checkpoint(folder, {name: spec.shape for name, spec in model.tensor_specs().items()},
+                             model.ignored_tensors)
+    _, plain = load_folder(folder)                           # the plain reader widens float16 exactly
+    for name, tensor in loaded.items():
+        assert tensor.dtype == torch.float16
+        assert torch.equal(matrix_to(tensor, "cpu", torch.float32), plain[name])
+        assert torch.equal(scale_to(tensor, "cpu"), plain[name])
+    # values that bfloat16 cannot hold survive
+    assert any(not torch.equal(t.float(), t.to(torch.bfloat16).float()) for t in loaded.values())
 
 
 def test_sharded_folder_with_index(tmp_path):
