@@ -1,8 +1,10 @@
-from .model_config import ConfigError, Qwen3Config, RawConfig
+from .model_config import (ConfigError, RawConfig, missing_field, optional_bool, optional_float,
+                           optional_positive_int, required_positive_int)
 from .registry import (ArchitectureEntry, register_architecture, registered_architectures,
                        resolve_architecture, unregister_architecture)
 
 __all__ = [
-    "ConfigError", "Qwen3Config", "RawConfig", "ArchitectureEntry", "register_architecture",
-    "registered_architectures", "resolve_architecture", "unregister_architecture",
+    "ConfigError", "RawConfig", "ArchitectureEntry", "register_architecture", "registered_architectures",
+    "resolve_architecture", "unregister_architecture", "missing_field", "optional_bool", "optional_float",
+    "optional_positive_int", "required_positive_int",
 ]

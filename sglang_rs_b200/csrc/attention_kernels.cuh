@@ -1,5 +1,5 @@
-// Attention over the paged cache, generic form: any head_dim that is a multiple of 16
-// (up to 512), any number of query heads per kv head up to 32, any page size, optional
+// Attention over the paged cache, generic form: any head_dim up to 512, any number of
+// query heads per kv head up to 32, any page size, optional
 // window, 32-bit arithmetic throughout.  T is the storage type of q, the pages and the
 // output.  It is the whole attention of the 32-bit path and the fallback of the bfloat16
 // path for sizes its tensor-core kernels refuse.
@@ -160,7 +160,14 @@ template <typename T>
 __global__ void attention_combine_kernel(const float* __restrict__ part_acc, const float* __restrict__ part_ml,
                                          T* __restrict__ out, AttnParams p) {
   const int row = blockIdx.x, q_head = blockIdx.y;
-  const int count = min(row_split_count(p, p.positions[row]), p.max_splits);
+  const int pos = p.positions[row];
+  if (pos < 0) return;                                   // a padding row: no block wrote partials for it
+  const int wanted = row_split_count(p, pos);
+  if (wanted > p.max_splits) {
+    // the launch has too few blocks along the splits for this row: its newest keys were left out
+    if (q_head == 0 && threadIdx.x == 0 && p.error_word) atomicOr(p.error_word, SRB_FLAG_TOO_FEW_SPLITS);
+  }
+  const int count = min(wanted, p.max_splits);
   const size_t first = ((size_t)row * p.n_q + q_head) * p.max_splits;
   float m = -INFINITY;
   for (int s = 0; s < count; ++s) m = fmaxf(m, part_ml[(first + s) * 2]);
@@ -209,8 +216,7 @@ static int paged_attention_dispatch(const void* q, const void* k_pool, const voi
   if (n_q <= 0 || n_kv <= 0 || n_q % n_kv != 0)
     SRB_FAIL("paged_attention: %d query heads are not a multiple of %d kv heads", n_q, n_kv);
   if (n_q / n_kv > 32) SRB_FAIL("paged_attention: %d query heads per kv head exceed 32", n_q / n_kv);
-  if (head_dim <= 0 || head_dim % 16 != 0 || head_dim > 512)
-    SRB_FAIL("paged_attention: head_dim %d must be a multiple of 16, at most 512", head_dim);
+  if (head_dim <= 0 || head_dim > 512) SRB_FAIL("paged_attention: head_dim %d must be positive, at most 512", head_dim);
   if (page_size <= 0 || num_pages <= 0 || table_stride <= 0)
     SRB_FAIL("paged_attention: page size, page count and table stride must be positive");
   if (window < 0 || split_size < 0) SRB_FAIL("paged_attention: window and split size must be non-negative");

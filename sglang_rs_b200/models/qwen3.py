@@ -12,14 +12,29 @@ from __future__ import annotations
 
 import math
 
-from ..config.model_config import Qwen3Config
+from ..config.model_config import ConfigError
 from ..config.registry import register_architecture
 from ..parts import (AttentionNames, GatedMlp, GatedMlpNames, GroupedQueryAttention, OutputHead, PreNormBlock,
                      RmsNorm, RotaryEncoding, TokenEmbedding)
 from .decoder import DecoderModel
+from .qwen3_config import Qwen3Config
 
 
 def build_qwen3(config: Qwen3Config) -> DecoderModel:
+    """Sizes that config.json may hold and that a part refuses (a head wider than the attention kernels
+    take, too many query heads per kv head) are reported here, at load, under the architecture's name."""
+    try:
+        return _build(config)
+    except ValueError as error:
+        if isinstance(error, ConfigError):
+            raise
+        raise ConfigError(
+            Qwen3Config.ARCHITECTURE,
+            f"{error} (head_dim={config.head_dim}, num_attention_heads={config.num_attention_heads}, "
+            f"num_key_value_heads={config.num_key_value_heads})") from None
+
+
+def _build(config: Qwen3Config) -> DecoderModel:
     embedding = TokenEmbedding(config.vocab_size, config.hidden_size, "model.embed_tokens.weight")
     layers = []
     for index in range(config.num_hidden_layers):
@@ -46,8 +61,12 @@ def build_qwen3(config: Qwen3Config) -> DecoderModel:
     final_norm = RmsNorm(config.hidden_size, config.rms_norm_eps, "model.norm.weight")
     head = OutputHead(config.vocab_size, config.hidden_size,
                       None if config.tie_word_embeddings else "lm_head.weight", embedding)
+    # exporters of this architecture may store the rotation's frequency table, and a head beside a tied
+    # embedding; the reference binds by name and reads neither (crates/sglang-srt/src/models/qwen.rs:321-353)
+    ignored = ["*.rotary_emb.inv_freq"] + (["lm_head.weight"] if config.tie_word_embeddings else [])
     return DecoderModel(embedding, layers, final_norm, head, vocab_size=config.vocab_size,
-                        max_positions=config.max_position_embeddings, eos_token_ids=config.eos_token_ids)
+                        max_positions=config.max_position_embeddings, eos_token_ids=config.eos_token_ids,
+                        ignored_tensors=ignored)
 
 
 register_architecture(Qwen3Config.ARCHITECTURE, Qwen3Config.from_raw, build_qwen3, replace=True)

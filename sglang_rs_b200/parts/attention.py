@@ -35,12 +35,21 @@ class AttentionNames:
 
 class GroupedQueryAttention(Mixer):
     graph_safe = True
+    #: what the attention kernels take: the generic one gives a warp to each query head of a kv head (at most
+    #: 32 warps a block) and keeps up to 16 values of a head per lane
+    MAX_HEAD_DIM = 512
+    MAX_HEADS_PER_KV_HEAD = 32
 
     def __init__(self, hidden: int, num_heads: int, num_kv_heads: int, head_dim: int, scale: float,
                  position: PositionEncoding, names: AttentionNames, *, qk_norm_eps: Optional[float] = None,
                  window: Optional[int] = None):
         if num_heads % num_kv_heads:
             raise ValueError(f"{num_heads} query heads are not a multiple of {num_kv_heads} kv heads")
+        if not 0 < head_dim <= self.MAX_HEAD_DIM:
+            raise ValueError(f"head_dim {head_dim} is outside what the attention kernels take (1 to {self.MAX_HEAD_DIM})")
+        if num_heads // num_kv_heads > self.MAX_HEADS_PER_KV_HEAD:
+            raise ValueError(f"{num_heads // num_kv_heads} query heads per kv head exceed the "
+                             f"{self.MAX_HEADS_PER_KV_HEAD} that the attention kernels take")
         self.hidden, self.n_q, self.n_kv, self.d = int(hidden), int(num_heads), int(num_kv_heads), int(head_dim)
         self.scale, self.position, self.names = float(scale), position, names
         self.qk_norm_eps, self.window = qk_norm_eps, window

@@ -4,9 +4,10 @@ import json
 import pytest
 
 from plain_model import TINY_A, TINY_B, TINY_C
-from sglang_rs_b200.config import (ConfigError, Qwen3Config, RawConfig, register_architecture,
+from sglang_rs_b200.config import (ConfigError, RawConfig, register_architecture,
                                    registered_architectures, resolve_architecture, unregister_architecture)
 from sglang_rs_b200 import models  # noqa: F401
+from sglang_rs_b200.models.qwen3_config import Qwen3Config
 
 
 def parse(document):
@@ -67,6 +68,22 @@ def test_rejections(change, fragment):
     with pytest.raises(ConfigError) as error:
         parse(doc)
     assert fragment in str(error.value)
+
+
+@pytest.mark.parametrize("change, fragment", [
+    ({"head_dim": 520}, "head_dim 520 is outside what the attention kernels take"),
+    ({"num_attention_heads": 66, "num_key_value_heads": 2, "head_dim": 16}, "33 query heads per kv head exceed"),
+])
+def test_sizes_that_the_kernels_refuse_are_refused_when_the_model_is_built(change, fragment):
+    """config.json may hold them (the reference asks only for an even head_dim, models/qwen.rs:129-157); the
+    kernels do not take them, and the error comes at load with the keys' names, not at the first step."""
+    from sglang_rs_b200.weights import build_model
+    with pytest.raises(ConfigError) as error:
+        build_model(dict(TINY_A, **change))
+    assert fragment in str(error.value) and "head_dim=" in str(error.value) and "Qwen3ForCausalLM" in str(error.value)
+    # an even head_dim that is no multiple of 16 is taken
+    model, config = build_model(dict(TINY_A, head_dim=18))
+    assert config.head_dim == 18
 
 
 def test_head_dim_must_divide_when_derived():
