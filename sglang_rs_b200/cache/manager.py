@@ -136,33 +136,6 @@ class PageAllocator:
         return out[:count].tolist()
 
 
-class StateSlotPool:
-    """Slots for per-request state of fixed size; capacity = the most requests that run.
-    (A cache manager's slots live in its C++ books; this class stands alone.)"""
-
-    def __init__(self, capacity: int):
-        self.capacity = int(capacity)
-        self._free: List[int] = list(range(self.capacity - 1, -1, -1))
-        self._used: set = set()
-
-    @property
-    def free_count(self) -> int:
-        return len(self._free)
-
-    def assign(self) -> int:
-        if not self._free:
-            raise OutOfStateSlots(f"all {self.capacity} state slots are in use")
-        slot = self._free.pop()
-        self._used.add(slot)
-        return slot
-
-    def release(self, slot: int) -> None:
-        if slot not in self._used:
-            raise RuntimeError(f"state slot {slot} is freed twice or was never assigned")
-        self._used.remove(slot)
-        self._free.append(slot)
-
-
 class _StateSlots:
     """What ``CacheManager.state_pool`` shows of the slots in the C++ books."""
 

@@ -388,7 +388,7 @@ static int launch_decode(const void* q, const void* k_pool, const void* v_pool, 
   // merge is the tail of the kernel; with several waves of blocks the placement of whole clusters costs
   // more than it saves); the merge needs room for one more [head][D + 2]
   const bool cluster = dp.a.max_splits > 1 && dp.a.max_splits <= 8 &&
-                       (long long)rows * dp.a.n_kv * dp.a.max_splits <= 3 * 148;
+                       (long long)rows * dp.a.n_kv * dp.a.max_splits <= 3 * srb_sm_count();
   const size_t merge = (size_t)(DEC_WARPS + 1) * groups * (D + 2) * sizeof(float);
   const size_t smem = cluster && merge > keys ? merge : keys;
   auto kernel = cluster ? decode_attention_kernel<D, true> : decode_attention_kernel<D, false>;

@@ -20,6 +20,10 @@
 //    has to start at zero: each call writes every partial it later reads.  Two calls whose
 //    kernels may run at the same time (different streams, different threads) race on it;
 //    keep calls to this entry point ordered on the device.
+//  * max_splits must cover the row with the most keys: positions[r] / split_size + 1 (fewer with a
+//    window).  The host cannot see positions that live on the device, so a row that needs more is
+//    reported from the device instead: bit SRB_FLAG_TOO_FEW_SPLITS (16) is set in *error_word and the
+//    row's output lacks its newest keys.  Rows with a negative position are padding and are left alone.
 //  * It calls no cudaMalloc, cudaFree or other allocating routine, of CUDA or of any library.
 //
 // Arguments are those of srb_paged_attention without the two scratch pointers; split_size

@@ -24,6 +24,7 @@
 #define SRB_FLAG_BAD_SLOT 2
 #define SRB_FLAG_BAD_PAGE 4
 #define SRB_FLAG_WAIT_TIMEOUT 8
+#define SRB_FLAG_TOO_FEW_SPLITS 16   // a row of a split attention run has more key splits than the launch was given
 
 static thread_local char srb_error_buffer[512] = "";
 
@@ -93,6 +94,19 @@ __device__ __forceinline__ float srb_block_sum(float v, float* scratch /* >= 33 
   }
   __syncthreads();
   return scratch[32];
+}
+
+// The number of SMs of the current device, asked once per device: launch heuristics size their grids by it.
+static inline int srb_sm_count() {
+  static int cached[64] = {};
+  int device = 0;
+  if (cudaGetDevice(&device) != cudaSuccess || device < 0 || device >= 64) return 1;
+  if (cached[device] == 0) {
+    int count = 0;
+    if (cudaDeviceGetAttribute(&count, cudaDevAttrMultiProcessorCount, device) != cudaSuccess || count <= 0) return 1;
+    cached[device] = count;
+  }
+  return cached[device];
 }
 
 // ---- programmatic dependent launch ------------------------------------------------------

@@ -185,7 +185,7 @@ __global__ void add_bias_kernel(T* __restrict__ values, const float* __restrict_
 
 static int elementwise_grid(size_t total, int block) {
   size_t blocks = (total + block - 1) / block;
-  const size_t cap = 148 * 16;
+  const size_t cap = (size_t)srb_sm_count() * 16;
   return (int)(blocks < 1 ? 1 : (blocks > cap ? cap : blocks));
 }
 
@@ -267,7 +267,7 @@ extern "C" int srb_silu_mul(const void* gate_up, void* out, int rows, int inner,
     silu_mul_kernel<float><<<grid, 256, 0, s>>>((const float*)gate_up, (float*)out, rows, inner);
   else if (dtype == SRB_DTYPE_BF16 && inner % 8 == 0 && (((uintptr_t)gate_up | (uintptr_t)out) & 15) == 0) {
     size_t blocks = ((size_t)rows * (inner / 8) + 255) / 256;
-    if (blocks > 148 * 64) blocks = 148 * 64;
+    if (blocks > srb_sm_count() * 64) blocks = srb_sm_count() * 64;
     silu_mul_bf16x8_kernel<<<(int)blocks, 256, 0, s>>>((const __nv_bfloat16*)gate_up, (__nv_bfloat16*)out, rows, inner);
   } else if (dtype == SRB_DTYPE_BF16)
     silu_mul_kernel<__nv_bfloat16><<<grid, 256, 0, s>>>((const __nv_bfloat16*)gate_up, (__nv_bfloat16*)out, rows,

@@ -591,7 +591,7 @@ extern "C" int srb_sample_filtered(const float* logits, int vocab, long long str
   }
   // blocks per row: as many (a power of two, 8 at most) as keep all of them resident at once
   int blocks = 1;
-  while (blocks < 8 && count * blocks * 2 <= 148) blocks *= 2;
+  while (blocks < 8 && count * blocks * 2 <= srb_sm_count()) blocks *= 2;
   if (count > 65535) SRB_FAIL("sample_filtered: %d rows exceed one launch", count);
   SRB_CUDA_CALL(srb_launch_clustered(sample_filtered_kernel, dim3(blocks, count), dim3(FS_THREADS), sizeof(FsShared),
                                      (cudaStream_t)stream, dim3(blocks, 1, 1), logits, vocab, stride, rows_index,

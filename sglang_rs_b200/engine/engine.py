@@ -14,6 +14,7 @@ from typing import Any, Dict, Hashable, List, Mapping, Optional, Sequence, Union
 
 import torch
 
+from .. import ops
 from ..cache.manager import CacheManager
 from ..sampling import RequestRandom, Sampler, SamplingParams
 from ..weights import load_model, parse_dtype
@@ -57,6 +58,7 @@ class Engine:
             raise RuntimeError("no CUDA device is visible; this engine has no host path")
         self.dtype = parse_dtype(dtype)
         self.device = torch.device(device)
+        ops.require_supported_device(self.device)            # before any weight is read
         self.disable_overlap_schedule = disable_overlap_schedule
         self.model = load_model(model_path, device=self.device, dtype=self.dtype, random_weights=random_weights,
                                 seed=seed, config=config)
@@ -145,7 +147,15 @@ class Engine:
         launched = None
         if before is not None and self._may_run_ahead():
             launched = self._launch(before)                  # the GPU has its next step before this one is read
-        outputs = self.drain()
+        try:
+            outputs = self.drain()
+        except Exception:
+            # the step before failed on the device: the step that ran ahead of it was computed from its
+            # tokens, so its requests fail with it (and give their pages back) instead of staying
+            # running with a token that never arrives
+            if launched is not None:
+                self.scheduler.step_failed(launched.entries)
+            raise
         if launched is None:
             launched = self._launch(None)
         self._in_flight = launched

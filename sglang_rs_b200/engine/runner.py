@@ -245,6 +245,7 @@ class ModelRunner:
             raise RuntimeError("the model has no weights yet")
         if model.device.type != "cuda":
             raise RuntimeError("the engine runs on a CUDA device only; there is no host path")
+        ops.require_supported_device(model.device)
         self.model, self.cache = model, cache
         self.device, self.dtype = model.device, model.dtype
         widths = [layer.split_scratch() for layer in model.layers if hasattr(layer, "split_scratch")]

@@ -16,6 +16,11 @@ from ..csrc.build import load_library
 
 F32, BF16 = 0, 1
 
+# Products of more than a few rows go to cuBLAS through torch.  Its bfloat16 products may add the partial
+# sums of a split along K in bfloat16 unless told otherwise; every product of this engine accumulates in
+# 32 bits to the end, so that is switched off once, here.
+torch.backends.cuda.matmul.allow_bf16_reduced_precision_reduction = False
+
 
 class KernelError(RuntimeError):
     pass
@@ -78,13 +83,45 @@ def _check(library, status: int, launches: int = 1) -> None:
         raise KernelError(library.srb_last_error().decode("utf-8", "replace") or f"kernel status {status}")
 
 
+#: the compute capability the kernels are compiled for (sm_100a: tcgen05, tensor memory, TMA)
+REQUIRED_CAPABILITY = (10, 0)
+_sm_counts: dict = {}
+
+
+def require_supported_device(device) -> None:
+    """Fails at start-up, with the device's name, on a GPU that the kernels are not built for (the
+    reference decides the same from the SM version, crates/sglang-srt/src/backend.rs:355-366); without
+    this check the first tcgen05 launch would fail with a bare CUDA error."""
+    if not torch.cuda.is_available():
+        raise KernelError("no CUDA device is visible; this engine has no host path")
+    index = torch.device(device).index
+    index = torch.cuda.current_device() if index is None else index
+    capability = torch.cuda.get_device_capability(index)
+    if tuple(capability) != REQUIRED_CAPABILITY:
+        raise KernelError(
+            f"device cuda:{index} ({torch.cuda.get_device_name(index)}) has compute capability "
+            f"{capability[0]}.{capability[1]}; the kernels of this engine are built for sm_100a "
+            f"({REQUIRED_CAPABILITY[0]}.{REQUIRED_CAPABILITY[1]}, B200) only")
+
+
+def sm_count(device=None) -> int:
+    """SMs of ``device`` (default: the current one), asked once."""
+    index = torch.cuda.current_device() if device is None or torch.device(device).index is None \
+        else torch.device(device).index
+    count = _sm_counts.get(index)
+    if count is None:
+        count = _sm_counts[index] = torch.cuda.get_device_properties(index).multi_processor_count
+    return count
+
+
 def new_error_word(device) -> torch.Tensor:
     """Device-side word that kernels OR fault bits into (bad token, slot or page)."""
     return torch.zeros(1, dtype=torch.int32, device=device)
 
 
 ERROR_BITS = {1: "token id outside the vocabulary", 2: "cache slot outside the pool",
-              4: "page id outside the pool", 8: "a device-side wait ran out"}
+              4: "page id outside the pool", 8: "a device-side wait ran out",
+              16: "a row of a split attention run has more key splits than the launch was given"}
 
 
 def raise_on_error_word(word: torch.Tensor) -> None:
@@ -269,8 +306,8 @@ def paged_attention(q: torch.Tensor, k_pool: torch.Tensor, v_pool: torch.Tensor,
 
 
 
-#: blocks the decode attention aims at: three per SM
-DECODE_TARGET_BLOCKS = 3 * 148
+#: blocks per SM that the decode attention aims at
+DECODE_BLOCKS_PER_SM = 3
 DECODE_MAX_SPLITS = 64
 
 
@@ -291,8 +328,9 @@ DECODE_GLOBAL_MERGE_UNITS = 3
 DECODE_CLUSTER_SPLITS = 8
 
 
-def decode_splits(rows: int, n_kv: int, max_keys: Optional[int] = None) -> int:
-    """Blocks per (row, kv head).  A function of the shape only.
+def decode_splits(rows: int, n_kv: int, max_keys: Optional[int] = None, sms: Optional[int] = None) -> int:
+    """Blocks per (row, kv head).  A function of the shape and of the device's SM count (``sms``;
+    default: the current device's) only.
 
     Without ``max_keys`` (the most keys any row sees): as many as make about three blocks per SM.
     With it, the count that makes the step shortest under a simple model: the blocks run in waves
@@ -300,13 +338,14 @@ def decode_splits(rows: int, n_kv: int, max_keys: Optional[int] = None) -> int:
     Many rows then still get their keys cut (512 blocks are 1.15 waves: nearly half the second
     wave's time is lost), and no block walks fewer than ``DECODE_MIN_UNITS`` units."""
     base = max(rows * n_kv, 1)
+    target = DECODE_BLOCKS_PER_SM * (sms if sms is not None else sm_count())
     if max_keys is None:
-        return max(1, min(DECODE_MAX_SPLITS, DECODE_TARGET_BLOCKS // base))
+        return max(1, min(DECODE_MAX_SPLITS, target // base))
     units = max(1, -(-max_keys // 64))
     cap = max(1, min(DECODE_MAX_SPLITS, units // DECODE_MIN_UNITS))
     best, best_cost = 1, None
     for splits in range(1, cap + 1):
-        waves = -(-base * splits // DECODE_TARGET_BLOCKS)
+        waves = -(-base * splits // target)
         cost = waves * (-(-units // splits) + DECODE_BLOCK_OVERHEAD_UNITS) + (
             DECODE_GLOBAL_MERGE_UNITS if splits > DECODE_CLUSTER_SPLITS else 0)
         if best_cost is None or cost < best_cost:
@@ -422,20 +461,18 @@ OWN_GEMM_MAX_TOKENS = 64
 #: 301 us at 2,048.  The plain products stay with the library at every size: the pair kernel reaches 0.92 to
 #: 1.0 of it alone, and whole prefill steps measured no gain from switching them.
 PAIR_GEMM_MIN_TOKENS = 1280
-#: the SMs a product cut along K should fill
-SM_COUNT = 148
 
 
-def gemm_splits(tokens: int, features: int, k: int) -> int:
+def gemm_splits(tokens: int, features: int, k: int, sms: Optional[int] = None) -> int:
     """Into how many partial sums a small-batch product is cut along K.  A function of the
-    shape only: blocks of 128 weight rows alone cannot occupy the SMs when there are few of
+    shape and of the device's SM count only: blocks of 128 weight rows alone cannot occupy the SMs when there are few of
     them, so K is cut until about two blocks per SM exist (two fit), each with at least 8 K
     blocks."""
     if tokens > 64:
         return 1
     tiles = -(-features // 128)
     k_blocks = -(-k // 64)
-    splits = max(1, min(2 * SM_COUNT // tiles, k_blocks // 8))
+    splits = max(1, min(2 * (sms if sms is not None else sm_count()) // tiles, k_blocks // 8))
     if splits <= 1:
         return 1
     per_split = -(-k_blocks // splits)

@@ -3,7 +3,7 @@ import random
 
 import pytest
 
-from sglang_rs_b200.cache import CacheManager, OutOfPages, OutOfStateSlots, PageAllocator, StateSlotPool
+from sglang_rs_b200.cache import CacheManager, OutOfPages, OutOfStateSlots, PageAllocator
 from sglang_rs_b200.parts import PagedKV, RequestState
 
 FULL = ("kv", None)
@@ -95,14 +95,9 @@ def test_window_group_has_its_own_pages_and_gives_them_back_as_the_window_passes
 
 
 def test_state_slots_and_live_limit():
-    pool = StateSlotPool(2)
-    s0, s1 = pool.assign(), pool.assign()
-    with pytest.raises(OutOfStateSlots):
-        pool.assign()
-    pool.release(s0)
-    with pytest.raises(RuntimeError, match="freed twice"):
-        pool.release(s0)
-    assert pool.assign() == s0
+    """The slots of the cache manager's own books (C++), through the manager: one per live request, the one
+    given back last is handed out next, a request cannot end twice, and under random openings and
+    closings no slot is ever held by two live requests or lost."""
     cache = manager([RequestState((3, 5)), PagedKV(2, 16)], max_requests=2)
     a, b = cache.open("a"), cache.open("b")
     assert {a.state_slot, b.state_slot} == {0, 1}
@@ -111,8 +106,28 @@ def test_state_slots_and_live_limit():
     with pytest.raises(ValueError, match="already live"):
         cache.open("a")
     cache.close(a)
+    with pytest.raises(RuntimeError, match="ended twice"):
+        cache.close(a)
+    assert cache.state_pool.free_count == 1
     c = cache.open("c")
     assert c.state_slot == a.state_slot
+    cache.check_invariants()
+    cache.close(b); cache.close(c)
+    assert cache.state_pool.free_count == cache.state_pool.capacity == 2
+
+    import random
+    rng = random.Random(4)
+    cache = manager([RequestState((2,)), PagedKV(2, 16)], max_requests=5)
+    live = {}
+    for step in range(400):
+        if live and (len(live) == 5 or rng.random() < 0.45):
+            name = rng.choice(sorted(live))
+            cache.close(live.pop(name))
+        else:
+            live[f"r{step}"] = cache.open(f"r{step}")
+        slots = [handle.state_slot for handle in live.values()]
+        assert len(set(slots)) == len(slots) and all(0 <= slot < 5 for slot in slots)
+        assert cache.state_pool.free_count == 5 - len(live)
     cache.check_invariants()
 
 

@@ -341,17 +341,63 @@ def test_a_request_whose_pending_token_is_its_last_is_not_scheduled_ahead():
     assert engine.rows_in_vain == 0
 
 
+def test_a_failed_drain_after_a_run_ahead_launch_fails_both_steps():
+    """The engine's own overlapped loop (``Engine._step_overlapped``) with launch and drain faked: the
+    step before fails on the device after the next step was launched from its tokens.  The requests of
+    both steps end as failed, nothing stays running or pending, no page is lost, and the loop of
+    ``generate`` would stop."""
+    from types import SimpleNamespace
+    from sglang_rs_b200.engine.engine import Engine
+    scheduler, cache = make(max_tokens=128)
+    fake = FakeOverlappedEngine(scheduler, cache)
+    engine = Engine.__new__(Engine)
+    engine.scheduler, engine.cache, engine._in_flight = scheduler, cache, None
+    engine._may_run_ahead = lambda: True
+
+    def launch(before):
+        fake.in_flight = None if before is None else before.pairs
+        pairs = fake.launch(ahead=before is not None)
+        return None if pairs is None else SimpleNamespace(entries=[e for e, _ in pairs], pairs=pairs)
+
+    def drain():
+        flight, engine._in_flight = engine._in_flight, None
+        if flight is None:
+            return []
+        if fail["now"]:
+            scheduler.step_failed(flight.entries)
+            raise RuntimeError("device-side check failed")
+        return scheduler.process_outputs(flight.entries, [t for _, t in flight.pairs if t is not None])
+    engine._launch, engine.drain = launch, drain
+    fail = {"now": False}
+    a, b = request("a", range(6), max_new_tokens=8), request("b", range(9), max_new_tokens=8)
+    scheduler.add_request(a)
+    scheduler.add_request(b)
+    engine._step_overlapped()                                # prompts launched
+    engine._step_overlapped()                                # a step runs ahead, the prompts' tokens arrive
+    assert a.pending == 1 and len(a.output_ids) == 1
+    c = request("c", range(5), max_new_tokens=8)             # arrives now: only the step that runs ahead holds it
+    scheduler.add_request(c)
+    fail["now"] = True
+    with pytest.raises(RuntimeError, match="device-side"):
+        engine._step_overlapped()                            # launches ahead, then the step before fails
+    assert engine._in_flight is None and not scheduler.has_work
+    assert a.finished and b.finished and c.finished
+    assert a.finish_reason == b.finish_reason == c.finish_reason == "abort"
+    assert all(alloc.free_count == alloc.num_pages for alloc in cache.allocators.values())
+    cache.check_invariants()
+
+
 def test_decode_split_counts_follow_the_shape_only():
     """How many blocks share the keys of a (row, kv head) in the decode attention: a function of
     rows, kv heads and the longest row; within the bound that sizes the scratch memory."""
     from sglang_rs_b200 import ops
-    assert ops.decode_splits(64, 8, 2100) == 3           # 512 blocks would be 1.15 waves of 444
-    assert ops.decode_splits(8, 8, 2100) == 6            # 384 blocks: one wave
-    assert ops.decode_splits(1, 8, 2100) == 7            # five units each, merged inside a cluster
-    assert ops.decode_splits(1, 8, 40) == 1
+    assert ops.decode_splits(64, 8, 2100, sms=148) == 3           # 512 blocks would be 1.15 waves of 444
+    assert ops.decode_splits(8, 8, 2100, sms=148) == 6            # 384 blocks: one wave
+    assert ops.decode_splits(1, 8, 2100, sms=148) == 7            # five units each, merged inside a cluster
+    assert ops.decode_splits(1, 8, 40, sms=148) == 1
     for rows in (1, 3, 8, 64, 200):
         for n_kv in (1, 2, 8, 32):
             for keys in (1, 64, 65, 1000, 5000, 40000):
-                splits = ops.decode_splits(rows, n_kv, keys)
+                splits = ops.decode_splits(rows, n_kv, keys, sms=148)
                 assert 1 <= splits <= ops.decode_splits_bound(keys) <= ops.DECODE_MAX_SPLITS
-                assert splits == ops.decode_splits(rows, n_kv, keys)
+                assert splits == ops.decode_splits(rows, n_kv, keys, sms=148)
