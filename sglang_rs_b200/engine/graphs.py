@@ -1,8 +1,8 @@
 """CUDA graphs for steps that hold decoded tokens only.
 
 A decode step is a few hundred small launches; replayed from a graph it costs one launch
-on the host.  A graph is captured per (row bucket, block-table width, key-split count and
-split length per group) with every index array in one static device buffer that is refilled by one copy
+on the host.  A graph is captured per (row bucket, block-table width, key-split count per
+group) with every index array in one static device buffer that is refilled by one copy
 before each replay.  Rows beyond the live ones are padding: token 0 at position 0 whose
 key and value go to the pool's spare page (the page after the last one the allocator
 owns), so they touch nothing that lives.
@@ -42,11 +42,15 @@ class CapturedStep:
 
 class DecodeGraphs:
     MAX_ROWS = 256
-    #: floats of split scratch that all captured steps share (they replay one after another); keys are cut
-    #: into longer pieces, or into fewer blocks, until a step's partial results fit
+    #: floats of split scratch that all captured steps share (they replay one after another); a step whose
+    #: partial results do not fit runs its rows in several launches over it (the keys of a row are always
+    #: cut at the same positions, whatever the batch)
     SCRATCH_FLOATS = 16 << 20
     #: captured steps kept; the one unused for longest goes first
     MAX_CAPTURED = 48
+    #: bytes of logits that the kept steps may hold together (each owns [bucket, vocab] floats in the graphs'
+    #: pool: 155 MB at 256 rows and a vocabulary of 152 k); beyond it the steps unused for longest go as well
+    MAX_LOGIT_BYTES = 2 << 30
 
     def __init__(self, model, cache, planner: StepPlanner):
         self.model, self.cache, self.planner = model, cache, planner
@@ -58,8 +62,12 @@ class DecodeGraphs:
         self.kernels_per_replay: Dict[Hashable, int] = {}
 
     def eligible(self, entries: Sequence[StepEntry]) -> bool:
-        return (0 < len(entries) <= self.MAX_ROWS
-                and all(len(e.tokens) == 1 and list(e.want) in ([], [0]) for e in entries))
+        if not (0 < len(entries) <= self.MAX_ROWS
+                and all(len(e.tokens) == 1 and list(e.want) in ([], [0]) for e in entries)):
+            return False
+        # even one row's partial results must fit the shared scratch (else the step runs uncaptured)
+        most = bucket_of(max(e.handle.length for e in entries) // StepPlanner.SPLIT_SIZE + 1)
+        return most * max(self.planner._scratch_acc_width, 1) <= self.SCRATCH_FLOATS
 
     # ------------------------------------------------------------------ one step
     def run(self, entries: Sequence[StepEntry], token_source: Optional[torch.Tensor] = None) -> Optional[torch.Tensor]:
@@ -71,23 +79,19 @@ class DecodeGraphs:
         page_size = self.cache.page_size
         stride = bucket_of(max([e.handle.table_length(key) for e in entries for key in groups] + [1]), 8)
         positions = np.fromiter((e.handle.length for e in entries), dtype=np.int64, count=rows)
-        splits, sizes = [], []
+        splits = []
+        size = StepPlanner.SPLIT_SIZE
         for key in groups:
             window = self.cache.windows[key]
             begin = np.maximum(0, positions + 1 - window) if window else np.zeros_like(positions)
-            size = StepPlanner.SPLIT_SIZE
-            while True:
-                count = bucket_of(int((positions // size - begin // size + 1).max()))
-                if count == 1 or bucket * count * max(self.planner._scratch_acc_width, 1) <= self.SCRATCH_FLOATS:
-                    break
-                size *= 2
-            splits.append(count)
-            sizes.append(size)
-        key = (bucket, stride, tuple(splits), tuple(sizes))
+            splits.append(bucket_of(int((positions // size - begin // size + 1).max())))
+        key = (bucket, stride, tuple(splits))
         step = self.captured.get(key)
         if step is None:
             step = self._prepare(key, groups)
             while len(self.captured) > self.MAX_CAPTURED:
+                self.captured.popitem(last=False)
+            while len(self.captured) > 1 and self._logit_bytes() > self.MAX_LOGIT_BYTES:
                 self.captured.popitem(last=False)
         self.captured.move_to_end(key)
         if step.copied is not None:
@@ -103,7 +107,7 @@ class DecodeGraphs:
             step.copied = torch.cuda.Event()
         step.copied.record()
         if step.graph is None:
-            self._capture(key, step, groups, bucket, stride, splits, sizes)
+            self._capture(key, step, groups, bucket, stride, splits)
         step.graph.replay()
         self.replays += 1
         ops.launch_count += self.kernels_per_replay[key]
@@ -113,6 +117,9 @@ class DecodeGraphs:
         if len(wanted) == rows:
             return step.logits[:rows]
         return step.logits[torch.tensor(wanted, device=self.device)]
+
+    def _logit_bytes(self) -> int:
+        return sum(step.logits.numel() * 4 for step in self.captured.values() if step.logits is not None)
 
     # ------------------------------------------------------------------ buffers
     def _prepare(self, key, groups) -> CapturedStep:
@@ -143,7 +150,7 @@ class DecodeGraphs:
                                [e.token_from for e in entries], bucket, stride, offsets, step.staging.numpy())
 
     # ------------------------------------------------------------------ capture
-    def _context(self, step: CapturedStep, groups, bucket, stride, splits, sizes) -> Tuple[StepContext, torch.Tensor, list]:
+    def _context(self, step: CapturedStep, groups, bucket, stride, splits) -> Tuple[StepContext, torch.Tensor, list]:
         def part(name):
             begin, size = step.layout[name]
             return step.static[begin:begin + size]
@@ -158,14 +165,20 @@ class DecodeGraphs:
                              torch.empty(ml, dtype=torch.float32, device=self.device))
         acc, ml = self._scratch
         keep = [acc, ml]
+        size = StepPlanner.SPLIT_SIZE
         for g, key in enumerate(groups):
-            ctx.paged[key] = PagedBatch(part(f"table{g}").view(bucket, stride), part(f"slots{g}"),
-                                        [AttentionLaunch(0, bucket, sizes[g], splits[g], None, None,
-                                                         splits[g] * sizes[g])], acc, ml, self.planner.counters)
+            # as many rows per launch as the scratch holds partial results for (bucket and count are powers of two)
+            per_launch = bucket
+            while per_launch > 1 and per_launch * splits[g] * max(self.planner._scratch_acc_width, 1) > self.SCRATCH_FLOATS:
+                per_launch //= 2
+            launches = [AttentionLaunch(first, first + per_launch, size, splits[g], None, None, splits[g] * size)
+                        for first in range(0, bucket, per_launch)]
+            ctx.paged[key] = PagedBatch(part(f"table{g}").view(bucket, stride), part(f"slots{g}"), launches, acc, ml,
+                                        self.planner.counters)
         return ctx, part("logit_rows"), keep
 
-    def _capture(self, key, step: CapturedStep, groups, bucket, stride, splits, sizes) -> None:
-        ctx, logit_rows, keep = self._context(step, groups, bucket, stride, splits, sizes)
+    def _capture(self, key, step: CapturedStep, groups, bucket, stride, splits) -> None:
+        ctx, logit_rows, keep = self._context(step, groups, bucket, stride, splits)
         caches = [self.cache.layer_cache(i) for i in range(len(self.model.program))]
         current = torch.cuda.current_stream()
         side = torch.cuda.Stream()

@@ -18,7 +18,8 @@ import os
 import sys
 
 PAGE_SIZE = 16
-MAX_LIVE = 4
+#: requests that may be live at a time unless ``--max-live`` says otherwise
+DEFAULT_MAX_LIVE = 4
 
 
 class ReplaySession:
@@ -26,7 +27,7 @@ class ReplaySession:
     step records.  Used by the command line below and by tests."""
 
     def __init__(self, model_dir: str, dtype: str, max_tokens: int, page_size: int = PAGE_SIZE,
-                 device: str = "cuda", use_cuda_graphs: bool = True):
+                 device: str = "cuda", use_cuda_graphs: bool = True, max_live: int = DEFAULT_MAX_LIVE):
         import torch
         from ..cache import CacheManager
         from ..weights import load_model, parse_dtype
@@ -38,7 +39,7 @@ class ReplaySession:
         # The caller counts each live request's tokens rounded up to 64, a multiple of the page
         # size, so ceil(max_tokens / page_size) pages hold whatever is live at any time.
         self.cache = CacheManager(self.model.cache_needs(), page_size=page_size, max_tokens=max(max_tokens, 1),
-                                  max_requests=MAX_LIVE, device=device, dtype=self.dtype)
+                                  max_requests=max(int(max_live), 1), device=device, dtype=self.dtype)
         self.runner = ModelRunner(self.model, self.cache, use_cuda_graphs=use_cuda_graphs)
         self.handles = {}
 
@@ -78,11 +79,13 @@ def main(argv=None) -> int:
     parser.add_argument("--max-tokens", type=int, required=True,
                         help="most tokens that live requests hold at any time (each rounded up to 64)")
     parser.add_argument("--page-size", type=int, default=PAGE_SIZE)
+    parser.add_argument("--max-live", type=int, default=DEFAULT_MAX_LIVE,
+                        help="most requests that are live at a time (each holds a slot of per-request state)")
     args = parser.parse_args(argv)
 
     print(f"[trace_run] loading {args.model} as {args.dtype}", file=sys.stderr, flush=True)
     try:
-        session = ReplaySession(args.model, args.dtype, args.max_tokens, args.page_size)
+        session = ReplaySession(args.model, args.dtype, args.max_tokens, args.page_size, max_live=args.max_live)
     except RuntimeError as error:
         print(f"trace_run: {error}", file=sys.stderr)
         return 3

@@ -95,7 +95,7 @@ class StepPlanner:
     #: rows of one request that the tiled attention kernel takes per block
     TILE_ROWS = 64
     WIDE_TILE_ROWS = 128
-    #: floats of attention scratch above which the split is made coarser
+    #: floats of attention scratch above which the decoded rows of a step go in several launches
     SCRATCH_LIMIT = 64 << 20
 
     def __init__(self, cache: CacheManager, device, dtype: torch.dtype, scratch_widths: Sequence = ()):
@@ -212,19 +212,25 @@ class StepPlanner:
             pos = positions[:split_rows]
             begin = np.maximum(0, pos + 1 - window) if window else np.zeros_like(pos)
             split_size = self.SPLIT_SIZE
-            visible = int((pos + 1 - begin).max())
-            while True:
-                max_splits = int((pos // split_size - begin // split_size + 1).max())
+            per_row = pos // split_size - begin // split_size + 1
+            visible_per_row = pos + 1 - begin
+            # The keys are always cut every SPLIT_SIZE positions, so a row's arithmetic is a function of its
+            # own position.  When the partial results of all rows do not fit the scratch memory, the rows go
+            # in several launches, one after another over the same scratch, never in longer pieces.
+            width = max(self._scratch_acc_width, 1)
+            rows_per_launch = max(1, self.SCRATCH_LIMIT // (int(per_row.max()) * width))
+            need_acc = need_ml = 0
+            for first in range(0, split_rows, rows_per_launch):
+                last = min(split_rows, first + rows_per_launch)
+                max_splits = int(per_row[first:last].max())
+                visible = int(visible_per_row[first:last].max())
                 # the split count of the generic kernel, or that of the tensor-core decode kernel if larger
                 # (as far as the scratch limit lets it go)
-                fit = max(1, self.SCRATCH_LIMIT // max(split_rows * self._scratch_acc_width, 1))
+                fit = max(1, self.SCRATCH_LIMIT // ((last - first) * width))
                 widest = max(max_splits, min(ops.decode_splits_bound(visible), fit))
-                need_acc = split_rows * widest * self._scratch_acc_width
-                need_ml = split_rows * widest * self._scratch_ml_width
-                if need_acc <= self.SCRATCH_LIMIT or max_splits == 1:
-                    break
-                split_size *= 2
-            launches.append(AttentionLaunch(0, split_rows, split_size, max_splits, None, None, visible))
+                need_acc = max(need_acc, (last - first) * widest * self._scratch_acc_width)
+                need_ml = max(need_ml, (last - first) * widest * self._scratch_ml_width)
+                launches.append(AttentionLaunch(first, last, split_size, max_splits, None, None, visible))
             scratch_acc = self._scratch_tensor("acc", need_acc)
             scratch_ml = self._scratch_tensor("ml", need_ml)
         if rows > split_rows:

@@ -75,7 +75,7 @@ def trace_portions(requests, sizes=(7, 2, 16, 3, 2, 31, 1, 17, 5, 2, 64, 9)):
 
 
 def trace_mixed(requests, seed: int, max_live: int = 4, decode_tail: int = 32,
-                portion_sizes=(2, 3, 5, 16, 17, 31, 40)):
+                portion_sizes=(2, 3, 5, 16, 17, 31, 40), admit: float = 0.6):
     """Up to ``max_live`` live requests; every step mixes portions of some with single
     tokens of others; a request may sit a step out; finished requests end and the next one
     is admitted, so its pages are taken from those just given back."""
@@ -84,7 +84,7 @@ def trace_mixed(requests, seed: int, max_live: int = 4, decode_tail: int = 32,
     live: Dict[str, int] = {}
     steps = []
     while waiting or live:
-        while waiting and len(live) < max_live and (not live or rng.random() < 0.6):
+        while waiting and len(live) < max_live and (not live or rng.random() < admit):
             live[waiting.pop(0)] = 0
         entries, end = [], []
         for rid in list(live):
@@ -101,6 +101,31 @@ def trace_mixed(requests, seed: int, max_live: int = 4, decode_tail: int = 32,
         if entries:
             rng.shuffle(entries)
             steps.append({"entries": entries, "end": end})
+    for i, s in enumerate(steps):
+        s["step"] = i
+    return steps
+
+
+def trace_decode_together(requests, tail: int = 8, prompts_per_step: int = 16):
+    """Many requests live at once: their prompts (all but the last ``tail`` tokens) go in steps of
+    ``prompts_per_step`` whole prompts, then every step holds one token of every request, so a decode step has
+    as many rows as there are requests."""
+    steps = []
+    names = list(requests)
+    for first in range(0, len(names), prompts_per_step):
+        steps.append({"entries": [{"id": rid, "tokens": requests[rid][:max(1, len(requests[rid]) - tail)],
+                                   "want": [max(1, len(requests[rid]) - tail) - 1]}
+                                  for rid in names[first:first + prompts_per_step]], "end": []})
+    fed = {rid: max(1, len(requests[rid]) - tail) for rid in names}
+    while any(fed[rid] < len(requests[rid]) for rid in names):
+        entries, end = [], []
+        for rid in names:
+            if fed[rid] < len(requests[rid]):
+                entries.append({"id": rid, "tokens": [requests[rid][fed[rid]]], "want": [0]})
+                fed[rid] += 1
+                if fed[rid] == len(requests[rid]):
+                    end.append(rid)
+        steps.append({"entries": entries, "end": end})
     for i, s in enumerate(steps):
         s["step"] = i
     return steps
@@ -135,10 +160,19 @@ def collect(trace, outputs) -> Dict[str, Dict[int, np.ndarray]]:
     return rows
 
 
+def max_live_of(trace) -> int:
+    live, most = set(), 0
+    for step in trace:
+        live |= {entry["id"] for entry in step["entries"]}
+        most = max(most, len(live))
+        live -= set(step["end"])
+    return most
+
+
 def run_in_process(folder: str, dtype: str, trace, max_tokens=None, page_size: int = 16, graphs: bool = True):
     from sglang_rs_b200.engine.replay import ReplaySession
     session = ReplaySession(folder, dtype, max_tokens if max_tokens is not None else max_tokens_of(trace), page_size,
-                            use_cuda_graphs=graphs)
+                            use_cuda_graphs=graphs, max_live=max(4, max_live_of(trace)))
     outputs = []
     session.page_owners = {}                 # (group, page id) -> requests that held it at some time
     for step in trace:

@@ -1,0 +1,151 @@
+"""Replay with many live requests, against the plain implementation.
+
+The engine changes its path with the number of rows of a step: the tcgen05 product of this package takes
+up to 64 rows and is compiled for 16, 32 and 64 of them, the library's product takes more (inside captured
+graphs too, whose row buckets 128 and 256 hold padding rows), decode attention merges its key splits
+inside a cluster or through global memory depending on how many blocks there are, and the CTA-pair product
+takes the gate/up product of portions of 1,280 rows and more.  Each of these schedules is compared here
+with the oracle at model level: ~20, ~40, ~70 and ~150 live requests, all decoding together (captured and
+uncaptured) and mixed with prompt portions on a pool so small that pages are used again.
+"""
+import numpy as np
+import pytest
+import torch
+
+import plain_model as pm
+import replay_helpers as rh
+
+pytestmark = pytest.mark.gpu
+
+DTYPES = {"float32": (torch.float32, rh.FP32_TOLERANCE), "bfloat16": (torch.bfloat16, rh.BF16_TOLERANCE)}
+CONFIGS = {"A": (pm.TINY_A, 16), "D": (pm.TINY_D, 16)}
+LIVE = (20, 40, 70, 150)
+
+
+@pytest.fixture(scope="module")
+def prepared(tmp_path_factory):
+    cache = {}
+
+    def get(case, dtype_name, count):
+        key = (case, dtype_name)
+        if key not in cache:
+            config, page = CONFIGS[case]
+            folder = rh.make_folder(tmp_path_factory.mktemp(f"many_{case}_{dtype_name}"), "model", config, seed=13,
+                                    dtype=DTYPES[dtype_name][0])
+            rng = np.random.RandomState(5)
+            lengths = [int(n) for n in rng.randint(9, 120, size=200)]
+            requests = rh.random_requests(config, lengths, seed=17)
+            cache[key] = (folder, requests, {}, page)
+        folder, requests, expected, page = cache[key]
+        chosen = dict(list(requests.items())[:count])
+        missing = {rid: toks for rid, toks in chosen.items() if rid not in expected}
+        expected.update(rh.oracle(folder, missing))
+        return folder, chosen, expected, page
+    return get
+
+
+def check_rows(rows, expected, tolerance, what):
+    """Every row that the trace asked for is within ``tolerance`` of the oracle's row at that position."""
+    assert rows, what
+    bad = rh.first_bad(rows, expected, tolerance)
+    worst, where = rh.worst_error(rows, expected)
+    print(f"{what}: {sum(len(v) for v in rows.values())} rows, worst error {worst:.3e} of scale at {where}")
+    assert bad is None, f"{what}: first wrong row: request {bad[0]} position {bad[1]} error {bad[2]:.3e}"
+
+
+@pytest.mark.parametrize("live", LIVE)
+@pytest.mark.parametrize("case,dtype_name", [("D", "bfloat16"), ("D", "float32"), ("A", "float32")])
+def test_many_requests_decode_together(prepared, case, dtype_name, live):
+    """All requests live at once; after the prompts every step is one decoded token of each, so steps of
+    ``live`` rows run captured (padded to a bucket) and uncaptured.  In 32-bit the two are equal bit for bit."""
+    folder, requests, expected, page = prepared(case, dtype_name, live)
+    trace = rh.trace_decode_together(requests, tail=6)
+    assert max(len(s["entries"]) for s in trace) == live
+    captured, session = rh.run_in_process(folder, dtype_name, trace, page_size=page, graphs=True)
+    assert session.runner.graphs is not None and session.runner.graphs.replays >= 6
+    eager, _ = rh.run_in_process(folder, dtype_name, trace, page_size=page, graphs=False)
+    tolerance = DTYPES[dtype_name][1]
+    check_rows(captured, expected, tolerance, f"{case}/{dtype_name}/{live} live/captured")
+    check_rows(eager, expected, tolerance, f"{case}/{dtype_name}/{live} live/eager")
+    as_expected = {rid: {p: row.astype(np.float64) for p, row in by_pos.items()} for rid, by_pos in eager.items()}
+    worst = max(float(np.abs(captured[rid][p] - as_expected[rid][p]).max()) for rid in eager for p in eager[rid])
+    scale = max(float(np.abs(expected[rid]).max()) for rid in eager)
+    print(f"{case}/{dtype_name}/{live} live: captured against eager {worst / scale:.3e}")
+    assert worst == 0.0 if dtype_name == "float32" else worst / scale <= 1e-2
+
+
+@pytest.mark.parametrize("live", LIVE)
+@pytest.mark.parametrize("case,dtype_name", [("D", "bfloat16"), ("D", "float32"), ("A", "float32")])
+def test_many_requests_mixed_on_few_pages(prepared, case, dtype_name, live):
+    """Up to ``live`` live requests out of more: every step mixes portions of some with decoded tokens of the
+    others, requests end and later ones take over their pages."""
+    folder, requests, expected, page = prepared(case, dtype_name, live + live // 3)
+    trace = rh.trace_mixed(requests, seed=live, max_live=live, decode_tail=10, portion_sizes=(2, 3, 16, 17, 40),
+                           admit=0.98)
+    assert rh.max_live_of(trace) > live * 0.8
+    rows, session = rh.run_in_process(folder, dtype_name, trace, page_size=page)
+    assert {rid: len(v) for rid, v in rows.items()} == {rid: len(t) for rid, t in requests.items()}
+    check_rows(rows, expected, DTYPES[dtype_name][1], f"{case}/{dtype_name}/{live} live/mixed")
+    shared = [owners for owners in session.page_owners.values() if len(owners) > 1]
+    assert len(shared) >= 3, "no page was used again"
+    decode_rows = [sum(len(e["tokens"]) == 1 for e in s["entries"]) for s in trace]
+    print(f"most decoded rows in a step: {max(decode_rows)}, steps: {len(trace)}")
+    assert max(decode_rows) > live // 2
+
+
+def test_a_portion_of_more_than_1280_rows_inside_a_model(tmp_path):
+    """A prompt of 1,500 tokens in one step: in bfloat16 its gate/up product runs on the CTA-pair kernel
+    (SiLU in the epilogue), its attention on the tcgen05 kernel with many tiles; then tokens one by one."""
+    from sglang_rs_b200 import ops
+    config = dict(pm.TINY_D, max_position_embeddings=2048)
+    folder = rh.make_folder(tmp_path, "long", config, seed=23, dtype=torch.bfloat16)
+    requests = rh.random_requests(config, (1540, 1300), seed=29)
+    assert ops.pair_gemm_takes(1500, config["intermediate_size"], config["hidden_size"])
+    expected = rh.oracle(folder, requests)
+    trace = rh.trace_tail_by_one(requests, tail=12)
+    rows, _ = rh.run_in_process(folder, "bfloat16", trace)
+    assert {rid: len(v) for rid, v in rows.items()} == {rid: len(t) for rid, t in requests.items()}
+    check_rows(rows, expected, rh.BF16_TOLERANCE, "D/bfloat16/portion of 1,528 rows")
+
+
+@pytest.mark.parametrize("case,dtype_name", [("A", "float32"), ("D", "bfloat16")])
+def test_rows_go_in_several_launches_when_the_scratch_is_short(prepared, monkeypatch, case, dtype_name):
+    """With little scratch memory for the partial results of split keys, the decoded rows of a step run in
+    several launches; the keys of a row are still cut at the same positions, so in 32-bit nothing changes
+    at all, captured or not."""
+    from sglang_rs_b200.engine.graphs import DecodeGraphs
+    from sglang_rs_b200.engine.runner import StepPlanner
+    folder, _, _, page = prepared(case, dtype_name, 1)
+    config = CONFIGS[case][0]
+    rng = np.random.RandomState(41)
+    requests = rh.random_requests(config, [int(n) for n in rng.randint(100, 250, size=20)], seed=43)   # one or two splits
+    expected = rh.oracle(folder, requests)
+    trace = rh.trace_decode_together(requests, tail=5)
+    roomy, _ = rh.run_in_process(folder, dtype_name, trace, page_size=page, graphs=False)
+    width = config["num_attention_heads"] * config["head_dim"]
+    monkeypatch.setattr(StepPlanner, "SCRATCH_LIMIT", 6 * width)          # three rows of two splits per launch
+    monkeypatch.setattr(DecodeGraphs, "SCRATCH_FLOATS", 8 * width)
+    launches = []
+    for graphs in (False, True):
+        tight, session = rh.run_in_process(folder, dtype_name, trace, page_size=page, graphs=graphs)
+        check_rows(tight, expected, DTYPES[dtype_name][1], f"{case}/{dtype_name}/short scratch/graphs {graphs}")
+        worst = max(float(np.abs(tight[rid][p].astype(np.float64) - roomy[rid][p]).max()) for rid in roomy for p in roomy[rid])
+        scale = max(float(np.abs(expected[rid]).max()) for rid in roomy)
+        assert worst == 0.0 if dtype_name == "float32" else worst / scale <= 1e-2
+        launches.append(session)
+    # the plan of a step of 20 decoded rows really has several launches
+    planner = launches[0].runner.planner
+    positions = np.full(20, 200, dtype=np.int64)
+    plan = planner._plan(("kv", None), None, None, positions, 20, 20)
+    assert len(plan.launches) > 3 and all(l.split_size == StepPlanner.SPLIT_SIZE for l in plan.launches)
+    assert sorted((l.begin, l.end) for l in plan.launches)[0][0] == 0 and max(l.end for l in plan.launches) == 20
+
+
+def test_a_float16_checkpoint_in_the_32_bit_path(tmp_path):
+    """Weights stored as float16 are widened exactly for ``--dtype float32`` (the plain reader does the
+    same), so the logits agree at the 32-bit tolerance; rounded to bfloat16 first they would not."""
+    folder = rh.make_folder(tmp_path, "half", pm.TINY_A, seed=31, dtype=torch.float16)
+    requests = rh.random_requests(pm.TINY_A, (33, 64, 120), seed=37)
+    expected = rh.oracle(folder, requests)
+    rows, _ = rh.run_in_process(folder, "float32", rh.trace_portions(requests))
+    check_rows(rows, expected, rh.FP32_TOLERANCE, "A/float16 checkpoint/float32")
