@@ -6,6 +6,7 @@
 // (crates/sglang-kernel/src/cpu.rs:26-34), SiLU*mul g / (1 + exp(-g)) * u (cpu.rs:119-123),
 // embedding row copy with out-of-range ids flagged (cuda_bf16_kernels.rs:14-37).
 #include "common.cuh"
+#include "activations.cuh"
 
 SRB_DEFINE_LAST_ERROR()
 SRB_DEFINE_PDL_SWITCH()
@@ -138,22 +139,22 @@ add_rmsnorm_vec_kernel(float* __restrict__ residual, const T* __restrict__ delta
   }
 }
 
-// out[row, j] = silu(gate_up[row, j]) * gate_up[row, inner + j]
+// out[row, j] = act(gate_up[row, j]) * gate_up[row, inner + j], act being SRB_ACT_* `activation`
 template <typename T>
-__global__ void silu_mul_kernel(const T* __restrict__ gate_up, T* __restrict__ out, int rows, int inner) {
+__global__ void silu_mul_kernel(const T* __restrict__ gate_up, T* __restrict__ out, int rows, int inner, int activation) {
   const size_t total = (size_t)rows * inner;
   for (size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x; idx < total;
        idx += (size_t)gridDim.x * blockDim.x) {
     const size_t row = idx / inner, col = idx % inner;
     const float g = srb_to_float(gate_up[row * 2 * inner + col]);
     const float u = srb_to_float(gate_up[row * 2 * inner + inner + col]);
-    out[idx] = srb_from_float<T>(g / (1.0f + expf(-g)) * u);
+    out[idx] = srb_from_float<T>(srb_gated<true>(activation, g, u));
   }
 }
 
 // The same with eight bfloat16 values (16 bytes) per thread and access; `inner` a multiple of 8.
 __global__ void silu_mul_bf16x8_kernel(const __nv_bfloat16* __restrict__ gate_up, __nv_bfloat16* __restrict__ out,
-                                       int rows, int inner) {
+                                       int rows, int inner, int activation) {
   const int per_row = inner / 8;
   const size_t total = (size_t)rows * per_row;
   for (size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x; idx < total;
@@ -169,7 +170,7 @@ __global__ void silu_mul_bf16x8_kernel(const __nv_bfloat16* __restrict__ gate_up
     for (int j = 0; j < 4; ++j) {
       const float2 g = __bfloat1622float2(g2[j]), u = __bfloat1622float2(u2[j]);
       // the result is rounded to bfloat16 (8 bits): the hardware's exponential and division are exact enough
-      o2[j] = __floats2bfloat162_rn(__fdividef(g.x, 1.0f + __expf(-g.x)) * u.x, __fdividef(g.y, 1.0f + __expf(-g.y)) * u.y);
+      o2[j] = __floats2bfloat162_rn(srb_gated<false>(activation, g.x, u.x), srb_gated<false>(activation, g.y, u.y));
     }
     *reinterpret_cast<uint4*>(out + row * inner + col) = o4;
   }
@@ -258,23 +259,25 @@ extern "C" int srb_add_rmsnorm(float* residual, const void* delta, const float* 
   SRB_FAIL("add_rmsnorm: unknown dtype %d", dtype);
 }
 
-extern "C" int srb_silu_mul(const void* gate_up, void* out, int rows, int inner, int dtype, void* stream) {
+extern "C" int srb_gated_mul(const void* gate_up, void* out, int rows, int inner, int activation, int dtype,
+                             void* stream) {
   if (rows <= 0) return SRB_OK;
-  if (inner <= 0) SRB_FAIL("silu_mul: inner width %d must be positive", inner);
+  if (inner <= 0) SRB_FAIL("gated_mul: inner width %d must be positive", inner);
+  if (activation < 0 || activation >= SRB_ACT_COUNT) SRB_FAIL("gated_mul: unknown activation %d", activation);
   cudaStream_t s = (cudaStream_t)stream;
   const int grid = elementwise_grid((size_t)rows * inner, 256);
   if (dtype == SRB_DTYPE_F32)
-    silu_mul_kernel<float><<<grid, 256, 0, s>>>((const float*)gate_up, (float*)out, rows, inner);
+    silu_mul_kernel<float><<<grid, 256, 0, s>>>((const float*)gate_up, (float*)out, rows, inner, activation);
   else if (dtype == SRB_DTYPE_BF16 && inner % 8 == 0 && (((uintptr_t)gate_up | (uintptr_t)out) & 15) == 0) {
     size_t blocks = ((size_t)rows * (inner / 8) + 255) / 256;
     if (blocks > srb_sm_count() * 64) blocks = srb_sm_count() * 64;
-    silu_mul_bf16x8_kernel<<<(int)blocks, 256, 0, s>>>((const __nv_bfloat16*)gate_up, (__nv_bfloat16*)out, rows, inner);
+    silu_mul_bf16x8_kernel<<<(int)blocks, 256, 0, s>>>((const __nv_bfloat16*)gate_up, (__nv_bfloat16*)out, rows, inner, activation);
   } else if (dtype == SRB_DTYPE_BF16)
     silu_mul_kernel<__nv_bfloat16><<<grid, 256, 0, s>>>((const __nv_bfloat16*)gate_up, (__nv_bfloat16*)out, rows,
-                                                        inner);
+                                                        inner, activation);
   else
-    SRB_FAIL("silu_mul: unknown dtype %d", dtype);
-  SRB_LAUNCH_CHECK("silu_mul");
+    SRB_FAIL("gated_mul: unknown dtype %d", dtype);
+  SRB_LAUNCH_CHECK("gated_mul");
   return SRB_OK;
 }
 

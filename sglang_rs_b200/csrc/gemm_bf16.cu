@@ -30,6 +30,7 @@
 // No TMA load uses cluster multicast.
 #include "common.cuh"
 #include "tcgen05_helpers.cuh"
+#include "activations.cuh"
 #include <mutex>
 
 SRB_DEFINE_LAST_ERROR()
@@ -56,6 +57,7 @@ struct GemmArgs {
   int tokens, features, k;   // problem
   int ldo;                   // row pitch of out, in elements
   int up_row_offset;         // EPI_SILU: rows of the up matrix start here in W
+  int activation;            // EPI_SILU: which SRB_ACT_* is applied to the gate half
   int k_blocks_per_split;
   int* error_word;
 };
@@ -216,7 +218,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constan
             if (token >= args.tokens) break;
             const float g = acc[j], u = exchange[((quarter & 1) * 32 + lane) * 16 + j];
             reinterpret_cast<__nv_bfloat16*>(args.out)[(size_t)token * args.ldo + feature] =
-                __float2bfloat16_rn(g / (1.0f + expf(-g)) * u);
+                __float2bfloat16_rn(srb_gated<true>(args.activation, g, u));
           }
         }
         asm volatile("bar.sync 1, 128;" ::: "memory");       // the buffer is reused by the next 16 tokens
@@ -348,19 +350,21 @@ extern "C" int srb_gemm_bf16_block_tokens(int tokens, int mode) {
 // mode 0: out bf16 [tokens, ldo] = x w^T over `features` rows of w.
 // mode 1: the same as float.
 // mode 2: w stacks gate rows [0, features) and up rows [up_row_offset, up_row_offset + features);
-//         out bf16 [tokens, ldo] = silu(x gate^T) * (x up^T).
+//         out bf16 [tokens, ldo] = act(x gate^T) * (x up^T), act being SRB_ACT_* `activation` (activations.cuh).
 // mode 3: `splits` partial sums over K as float [splits, tokens, ldo]; the caller adds them in order.
 // mode 4: out float [tokens, ldo] += x w^T, K cut into `splits` (at most 8) blocks that form a cluster and add
 //         their sums in block order.
 extern "C" int srb_gemm_bf16(const void* x, const void* w, void* out, int tokens, int features, int k, int ldx,
                              int ldw, int ldo, int rows_of_w, int up_row_offset, int mode, int splits,
-                             int* error_word, void* stream) {
+                             int activation, int* error_word, void* stream) {
   if (tokens <= 0 || features <= 0) return SRB_OK;
   if (k <= 0 || k % 8 != 0 || ldx % 8 != 0 || ldw % 8 != 0)
     SRB_FAIL("gemm_bf16: inner size %d and the row pitches %d, %d must be positive multiples of 8 (16-byte rows "
              "for TMA)", k, ldx, ldw);
   if (((uintptr_t)x | (uintptr_t)w) & 15) SRB_FAIL("gemm_bf16: operands must be 16-byte aligned");
   if (mode < 0 || mode > 4) SRB_FAIL("gemm_bf16: unknown mode %d", mode);
+  if (mode == EPI_SILU && (activation < 0 || activation >= SRB_ACT_COUNT))
+    SRB_FAIL("gemm_bf16: unknown activation %d", activation);
   if (ldo < features) SRB_FAIL("gemm_bf16: output pitch %d is smaller than %d features", ldo, features);
   if (mode == EPI_SILU && up_row_offset + features > rows_of_w)
     SRB_FAIL("gemm_bf16: the up rows %d..%d lie outside the %d rows of w", up_row_offset, up_row_offset + features,
@@ -380,7 +384,7 @@ extern "C" int srb_gemm_bf16(const void* x, const void* w, void* out, int tokens
 
   GemmArgs args;
   args.out = out; args.tokens = tokens; args.features = features; args.k = k; args.ldo = ldo;
-  args.up_row_offset = up_row_offset; args.error_word = error_word;
+  args.up_row_offset = up_row_offset; args.activation = activation; args.error_word = error_word;
   args.k_blocks_per_split = (total_k_blocks + splits - 1) / splits;
   const int used_splits = (total_k_blocks + args.k_blocks_per_split - 1) / args.k_blocks_per_split;
   if (used_splits != splits) SRB_FAIL("gemm_bf16: %d splits leave one without work for %d blocks of K", splits, total_k_blocks);

@@ -22,6 +22,7 @@
 // rows of the same features (as in gemm_bf16.cu).
 #include "common.cuh"
 #include "tcgen05_helpers.cuh"
+#include "activations.cuh"
 #include <algorithm>
 #include <mutex>
 
@@ -39,6 +40,7 @@ SRB_DEFINE_LAST_ERROR()
 struct PairArgs {
   __nv_bfloat16* out;
   int tokens, features, k, ldo, up_row_offset;
+  int activation;            // which SRB_ACT_* the gated mode applies to the gate half
   int tiles_t, tiles_f, num_tiles;
   int* error_word;
 };
@@ -225,7 +227,7 @@ gemm_bf16_pair_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_co
 #pragma unroll
               for (int j = 0; j < 32; ++j) {
                 const float g = acc[j], u = buffer[j * 64 + (quarter & 1) * 32 + lane];
-                staged[(c + j) * FEATURES_PER_CTA + row_in_cta] = __float2bfloat16_rn(__fdividef(g, 1.0f + __expf(-g)) * u);
+                staged[(c + j) * FEATURES_PER_CTA + row_in_cta] = __float2bfloat16_rn(srb_gated<false>(args.activation, g, u));
               }
             }
           }
@@ -308,16 +310,18 @@ static int make_map(CUtensorMap* map, const void* base, long long rows, long lon
 
 // x [tokens, k] (row pitch ldx), w [rows_of_w, k] (row pitch ldw), out [tokens, ldo], all bfloat16; k and the
 // pitches multiples of 8.  mode 0: out = x w^T over `features` rows of w.  mode 2: w stacks gate rows
-// [0, features) and up rows [up_row_offset, up_row_offset + features); out = silu(x gate^T) * (x up^T).
+// [0, features) and up rows [up_row_offset, up_row_offset + features); out = act(x gate^T) * (x up^T), act being SRB_ACT_* `activation` (activations.cuh).
 extern "C" int srb_gemm_bf16_pair(const void* x, const void* w, void* out, int tokens, int features, int k, int ldx,
-                                  int ldw, int ldo, int rows_of_w, int up_row_offset, int mode, int* error_word,
-                                  void* stream) {
+                                  int ldw, int ldo, int rows_of_w, int up_row_offset, int mode, int activation,
+                                  int* error_word, void* stream) {
   if (tokens <= 0 || features <= 0) return SRB_OK;
   if (k <= 0 || k % 8 != 0 || ldx % 8 != 0 || ldw % 8 != 0 || ldo % 8 != 0)
     SRB_FAIL("gemm_bf16_pair: inner size %d and the row pitches %d, %d, %d must be positive multiples of 8", k, ldx, ldw,
              ldo);
   if (((uintptr_t)x | (uintptr_t)w | (uintptr_t)out) & 15) SRB_FAIL("gemm_bf16_pair: operands must be 16-byte aligned");
   if (mode != PAIR_EPI_BF16 && mode != PAIR_EPI_SILU) SRB_FAIL("gemm_bf16_pair: unknown mode %d", mode);
+  if (mode == PAIR_EPI_SILU && (activation < 0 || activation >= SRB_ACT_COUNT))
+    SRB_FAIL("gemm_bf16_pair: unknown activation %d", activation);
   if (mode == PAIR_EPI_SILU && up_row_offset + features > rows_of_w)
     SRB_FAIL("gemm_bf16_pair: the up rows lie outside the %d rows of w", rows_of_w);
   if (mode == PAIR_EPI_BF16 && features > rows_of_w) SRB_FAIL("gemm_bf16_pair: %d features exceed %d rows of w", features, rows_of_w);
@@ -327,7 +331,7 @@ extern "C" int srb_gemm_bf16_pair(const void* x, const void* w, void* out, int t
   const int features_per_pair = mode == PAIR_EPI_SILU ? PAIR_F : 2 * PAIR_F;
   PairArgs args;
   args.out = (__nv_bfloat16*)out; args.tokens = tokens; args.features = features; args.k = k; args.ldo = ldo;
-  args.up_row_offset = up_row_offset; args.error_word = error_word;
+  args.up_row_offset = up_row_offset; args.activation = activation; args.error_word = error_word;
   args.tiles_t = (tokens + PAIR_T - 1) / PAIR_T;
   args.tiles_f = (features + features_per_pair - 1) / features_per_pair;
   args.num_tiles = args.tiles_t * args.tiles_f;

@@ -196,14 +196,26 @@ def add_rmsnorm(residual: torch.Tensor, delta: Optional[torch.Tensor], weight: t
                                     int(write_residual), dtype_code(out.dtype), _stream()))
 
 
-def silu_mul(gate_up: torch.Tensor, out: torch.Tensor) -> None:
-    """out[r, j] = silu(gate_up[r, j]) * gate_up[r, inner + j]"""
+#: activations of a gated feed-forward, act(gate) * up, by the numbers of csrc/activations.cuh
+ACTIVATIONS = {"silu": 0, "gelu_tanh": 1}
+
+
+def activation_code(name: str) -> int:
+    try:
+        return ACTIVATIONS[name]
+    except KeyError:
+        raise KernelError(f"unknown activation {name!r}; the kernels have {sorted(ACTIVATIONS)}") from None
+
+
+def gated_mul(gate_up: torch.Tensor, out: torch.Tensor, activation: str = "silu") -> None:
+    """out[r, j] = act(gate_up[r, j]) * gate_up[r, inner + j]"""
     _need(gate_up, "gate_up"); _need(out, "out", gate_up.dtype)
     rows, inner = out.shape
     if gate_up.shape != (rows, 2 * inner):
-        raise KernelError("silu_mul: gate_up must be [rows, 2 * inner]")
+        raise KernelError("gated_mul: gate_up must be [rows, 2 * inner]")
     lib = load_library("elementwise")
-    _check(lib, lib.srb_silu_mul(_ptr(gate_up), _ptr(out), rows, inner, dtype_code(out.dtype), _stream()))
+    _check(lib, lib.srb_gated_mul(_ptr(gate_up), _ptr(out), rows, inner, activation_code(activation),
+                                  dtype_code(out.dtype), _stream()))
 
 
 def add_bias(values: torch.Tensor, bias: torch.Tensor) -> None:
@@ -521,38 +533,40 @@ def linear(x: torch.Tensor, weight: torch.Tensor, bias: Optional[torch.Tensor] =
     return out
 
 
-def gate_up_silu(x: torch.Tensor, weight: torch.Tensor, inner: int,
-                 error_word: Optional[torch.Tensor] = None) -> torch.Tensor:
-    """silu(x gate^T) * (x up^T) for ``weight`` = gate rows stacked over up rows [2 inner, in].
+def gated_product(x: torch.Tensor, weight: torch.Tensor, inner: int, error_word: Optional[torch.Tensor] = None,
+                  activation: str = "silu") -> torch.Tensor:
+    """act(x gate^T) * (x up^T) for ``weight`` = gate rows stacked over up rows [2 inner, in].
 
     bfloat16 with few rows: one tcgen05 kernel whose epilogue takes the product of its two
-    accumulators, so the [rows, 2 inner] intermediate never exists.  Otherwise the product
-    (``linear``) followed by the SiLU kernel."""
+    accumulators, so the [rows, 2 inner] intermediate never exists; with many rows the CTA-pair
+    kernel does the same.  Otherwise the product (``linear``) followed by the activation kernel."""
     if (x.dtype == torch.bfloat16 and x.shape[0] <= OWN_GEMM_MAX_TOKENS and error_word is not None
             and gemm_bf16_takes(x.shape[1])):
-        return gemm_bf16(x, weight, error_word, mode="silu", features=inner, up_row_offset=inner)
+        return gemm_bf16(x, weight, error_word, mode="gated", features=inner, up_row_offset=inner, activation=activation)
     if (x.dtype == torch.bfloat16 and error_word is not None and weight.shape[0] == 2 * inner
             and pair_gemm_takes(x.shape[0], inner, x.shape[1])):
-        return gemm_bf16_pair(x, weight, error_word, mode="silu", features=inner, up_row_offset=inner)
+        return gemm_bf16_pair(x, weight, error_word, mode="gated", features=inner, up_row_offset=inner,
+                              activation=activation)
     gate_up = linear(x, weight, error_word=error_word)
     act = torch.empty((x.shape[0], inner), dtype=x.dtype, device=x.device)
-    silu_mul(gate_up, act)
+    gated_mul(gate_up, act, activation)
     return act
 
 
-GEMM_MODES = {"bf16": 0, "f32": 1, "silu": 2, "partial": 3, "add": 4}
+GEMM_MODES = {"bf16": 0, "f32": 1, "gated": 2, "partial": 3, "add": 4}
 #: the blocks of a thread-block cluster: at most this many K splits add their sums inside the kernel
 GEMM_CLUSTER_SPLITS = 8
 
 
 def gemm_bf16(x: torch.Tensor, w: torch.Tensor, error_word: torch.Tensor, *, mode: str = "bf16",
               features: Optional[int] = None, up_row_offset: int = 0, splits: int = 1,
-              out: Optional[torch.Tensor] = None) -> torch.Tensor:
+              out: Optional[torch.Tensor] = None, activation: str = "silu") -> torch.Tensor:
     """y = x @ w^T on tcgen05 tensor cores (bfloat16 in, 32-bit accumulation).
 
     x [tokens, k], w [rows, k], k a multiple of 8.  ``mode``: ``bf16`` / ``f32`` store
-    [tokens, features]; ``silu`` treats w as gate rows [0, features) stacked over up rows
-    [up_row_offset, up_row_offset + features) and stores silu(gate) * up; ``partial`` stores
+    [tokens, features]; ``gated`` treats w as gate rows [0, features) stacked over up rows
+    [up_row_offset, up_row_offset + features) and stores act(gate) * up (``activation``: a name of
+    ``ACTIVATIONS``); ``partial`` stores
     ``splits`` float partial sums [splits, tokens, features] that the consumer adds in order;
     ``add`` adds the product to ``out`` (float32 [tokens, features], e.g. the residual stream) in
     place, K cut into at most ``GEMM_CLUSTER_SPLITS`` blocks that sum inside the kernel in block order.
@@ -582,18 +596,19 @@ def gemm_bf16(x: torch.Tensor, w: torch.Tensor, error_word: torch.Tensor, *, mod
         out = torch.empty((tokens, features), dtype=torch.float32 if mode == "f32" else torch.bfloat16, device=x.device)
     lib = load_library("gemm_bf16")
     _check(lib, lib.srb_gemm_bf16(_ptr(x), _ptr(w), _ptr(out), tokens, features, k, x.stride(0), w.stride(0), pitch,
-                                  rows, int(up_row_offset), code, int(splits), _ptr(error_word), _stream()))
+                                  rows, int(up_row_offset), code, int(splits), activation_code(activation),
+                                  _ptr(error_word), _stream()))
     return out
 
 
 def gemm_bf16_pair(x: torch.Tensor, w: torch.Tensor, error_word: torch.Tensor, *, mode: str = "bf16",
-                   features: Optional[int] = None, up_row_offset: int = 0) -> torch.Tensor:
+                   features: Optional[int] = None, up_row_offset: int = 0, activation: str = "silu") -> torch.Tensor:
     """y = x @ w^T for many tokens: 256 x 256 tiles on pairs of CTAs (``tcgen05.mma.cta_group::2``) in a
-    persistent kernel.  ``mode`` ``bf16`` or ``silu`` as in :func:`gemm_bf16`; the result is bfloat16."""
+    persistent kernel.  ``mode`` ``bf16`` or ``gated`` as in :func:`gemm_bf16`; the result is bfloat16."""
     _need(x, "x", torch.bfloat16); _need(w, "w", torch.bfloat16)
     tokens, k = x.shape
     rows = w.shape[0]
-    if w.shape[1] != k or mode not in ("bf16", "silu"):
+    if w.shape[1] != k or mode not in ("bf16", "gated"):
         raise KernelError(f"gemm_bf16_pair: x {tuple(x.shape)}, w {tuple(w.shape)} or mode {mode!r} do not fit")
     if features is None:
         features = rows
@@ -601,7 +616,8 @@ def gemm_bf16_pair(x: torch.Tensor, w: torch.Tensor, error_word: torch.Tensor, *
     out = torch.empty((tokens, pitch), dtype=torch.bfloat16, device=x.device)
     lib = load_library("gemm_bf16_pair")
     _check(lib, lib.srb_gemm_bf16_pair(_ptr(x), _ptr(w), _ptr(out), tokens, features, k, x.stride(0), w.stride(0), pitch,
-                                       rows, int(up_row_offset), GEMM_MODES[mode], _ptr(error_word), _stream()))
+                                       rows, int(up_row_offset), GEMM_MODES[mode], activation_code(activation),
+                                       _ptr(error_word), _stream()))
     return out if pitch == features else out[:, :features]
 
 

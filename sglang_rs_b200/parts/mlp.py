@@ -1,8 +1,11 @@
-"""Gated feed-forward: down( silu(gate(x)) * up(x) ).
+"""Gated feed-forward: down( act(gate(x)) * up(x) ).
 
-act_j = g_j / (1 + exp(-g_j)) * u_j (reference: crates/sglang-kernel/src/cpu.rs:119-123;
+With SiLU, act_j = g_j / (1 + exp(-g_j)) * u_j (reference: crates/sglang-kernel/src/cpu.rs:119-123;
 order of products crates/sglang-srt/src/cpu_reference.rs:585-603).  gate and up come from
-one product with the two matrices stacked (gate rows first), made at load time.
+one product with the two matrices stacked (gate rows first), made at load time.  The
+activation is a name that the kernels know (``ops.ACTIVATIONS``); it travels to the epilogue of
+the gate/up product as a number, so another activation is a case in csrc/activations.cuh and
+a name there, not a change to a product kernel.
 """
 from __future__ import annotations
 
@@ -25,11 +28,9 @@ class GatedMlpNames:
 class GatedMlp(FeedForward):
     graph_safe = True
 
-    ACTIVATIONS = ("silu",)
-
     def __init__(self, hidden: int, inner: int, activation: str, names: GatedMlpNames):
-        if activation not in self.ACTIVATIONS:
-            raise ValueError(f"unsupported activation {activation}; available: {self.ACTIVATIONS}")
+        if activation not in ops.ACTIVATIONS:
+            raise ValueError(f"unsupported activation {activation}; available: {sorted(ops.ACTIVATIONS)}")
         self.hidden, self.inner, self.activation, self.names = int(hidden), int(inner), activation, names
         self.w_gate_up = self.w_down = None
 
@@ -45,5 +46,5 @@ class GatedMlp(FeedForward):
 
     def forward(self, ctx, x: torch.Tensor) -> torch.Tensor:
         error_word = ctx.error_word if ctx is not None else None
-        act = ops.gate_up_silu(x, self.w_gate_up, self.inner, error_word)
+        act = ops.gated_product(x, self.w_gate_up, self.inner, error_word, self.activation)
         return ops.linear(act, self.w_down, error_word=error_word, partial_ok=True)

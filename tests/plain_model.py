@@ -275,6 +275,13 @@ TINY_E = {
     "vocab_size": 777, "rope_theta": 20000.0, "rms_norm_eps": 2e-5, "tie_word_embeddings": True,
     "max_position_embeddings": 512, "hidden_act": "silu", "attention_bias": True,
 }
+# an even head_dim that is no multiple of 16 (the reference asks only for an even one, models/qwen.rs:129-157)
+TINY_F = {
+    "architectures": ["Qwen3ForCausalLM"], "model_type": "qwen3", "num_hidden_layers": 2, "hidden_size": 88,
+    "num_attention_heads": 4, "num_key_value_heads": 2, "head_dim": 18, "intermediate_size": 136,
+    "vocab_size": 300, "rope_theta": 30000.0, "rms_norm_eps": 1e-5, "tie_word_embeddings": True,
+    "max_position_embeddings": 320, "hidden_act": "silu", "attention_bias": False,
+}
 
 
 def plain_random_weights(config: dict, seed: int) -> Dict[str, torch.Tensor]:

@@ -169,10 +169,11 @@ def max_live_of(trace) -> int:
     return most
 
 
-def run_in_process(folder: str, dtype: str, trace, max_tokens=None, page_size: int = 16, graphs: bool = True):
+def run_in_process(folder: str, dtype: str, trace, max_tokens=None, page_size: int = 16, graphs: bool = True,
+                   radix: bool = False):
     from sglang_rs_b200.engine.replay import ReplaySession
     session = ReplaySession(folder, dtype, max_tokens if max_tokens is not None else max_tokens_of(trace), page_size,
-                            use_cuda_graphs=graphs, max_live=max(4, max_live_of(trace)))
+                            use_cuda_graphs=graphs, max_live=max(4, max_live_of(trace)), radix=radix)
     outputs = []
     session.page_owners = {}                 # (group, page id) -> requests that held it at some time
     for step in trace:
@@ -183,7 +184,8 @@ def run_in_process(folder: str, dtype: str, trace, max_tokens=None, page_size: i
                     if page >= 0:
                         session.page_owners.setdefault((key, page), set()).add(rid)
         session.cache.check_invariants()
-    assert all(a.free_count == a.num_pages for a in session.cache.allocators.values()), "pages leaked"
+    held = session.cache.prefix_tree.pages_held if session.cache.prefix_tree is not None else 0
+    assert all(a.free_count + held == a.num_pages for a in session.cache.allocators.values()), "pages leaked"
     return collect(trace, outputs), session
 
 

@@ -1,5 +1,7 @@
 """The tcgen05 / TMEM / TMA matrix product alone, against a 64-bit product of the same
 bfloat16 values, at sizes that are no multiple of any tile."""
+import math
+
 import pytest
 import torch
 
@@ -79,15 +81,29 @@ def test_product_added_to_a_float_tensor_inside_a_cluster(tokens, features, k, s
         ops.gemm_bf16(x.to(DEV), w.to(DEV), word, mode="add", splits=9, out=into)
 
 
+def gelu_tanh_mul(gate, up):
+    """The second activation of the kernels, written out: g/2 (1 + tanh(sqrt(2/pi) (g + 0.044715 g^3))) * u.
+    No model of this package uses it; it shows that the activation is an argument, not a kernel."""
+    return 0.5 * gate * (1.0 + torch.tanh(math.sqrt(2.0 / math.pi) * (gate + 0.044715 * gate ** 3))) * up
+
+
+GATED = {"silu": pm.plain_silu_mul, "gelu_tanh": gelu_tanh_mul}
+
+
+@pytest.mark.parametrize("activation", list(GATED))
 @pytest.mark.parametrize("tokens,inner,k", [(1, 128, 64), (8, 200, 72), (70, 256, 512), (129, 130, 200)])
-def test_gate_up_with_silu_epilogue(tokens, inner, k):
+def test_gate_up_with_the_activation_in_the_epilogue(tokens, inner, k, activation):
     x, w = operands(tokens, inner, k, seed=11, rows=2 * inner)
+    x = x * 3                                                 # gate values where the activations differ
     word = ops.new_error_word(DEV)
-    got = ops.gemm_bf16(x.to(DEV), w.to(DEV), word, mode="silu", features=inner, up_row_offset=inner)
+    got = ops.gemm_bf16(x.to(DEV), w.to(DEV), word, mode="gated", features=inner, up_row_offset=inner,
+                        activation=activation)
     ops.raise_on_error_word(word)
     both = pm.plain_linear(x.double(), w.double())
-    want = pm.plain_silu_mul(both[:, :inner], both[:, inner:])
+    want = GATED[activation](both[:, :inner], both[:, inner:])
     assert got.shape == (tokens, inner) and relative_error(got, want) < 5e-3
+    with pytest.raises(ops.KernelError, match="unknown activation"):
+        ops.gemm_bf16(x.to(DEV), w.to(DEV), word, mode="gated", features=inner, up_row_offset=inner, activation="relu6")
 
 
 def test_a_rows_result_does_not_depend_on_the_rows_beside_it():
@@ -120,26 +136,30 @@ def test_product_on_pairs_of_ctas(tokens, features, k):
     assert torch.equal(again, got)
 
 
+@pytest.mark.parametrize("activation", list(GATED))
 @pytest.mark.parametrize("tokens,inner,k", [(256, 128, 64), (700, 200, 72), (1030, 256, 512), (300, 130, 200)])
-def test_gate_up_with_silu_on_pairs_of_ctas(tokens, inner, k):
+def test_gate_up_with_the_activation_on_pairs_of_ctas(tokens, inner, k, activation):
     x, w = operands(tokens, 2 * inner, k, seed=5 + inner)
+    x = x * 3
     word = ops.new_error_word(DEV)
-    got = ops.gemm_bf16_pair(x.to(DEV), w.to(DEV), word, mode="silu", features=inner, up_row_offset=inner)
+    got = ops.gemm_bf16_pair(x.to(DEV), w.to(DEV), word, mode="gated", features=inner, up_row_offset=inner,
+                             activation=activation)
     ops.raise_on_error_word(word)
     gate_up = pm.plain_linear(x.double(), w.double())
-    want = pm.plain_silu_mul(gate_up[:, :inner], gate_up[:, inner:])
+    want = GATED[activation](gate_up[:, :inner], gate_up[:, inner:])
     assert got.shape == (tokens, inner) and relative_error(got, want) < 1e-2
 
 
+@pytest.mark.parametrize("activation", list(GATED))
 @pytest.mark.parametrize("tokens", [3, 64, 65, 300, 1279, 1280, 1400])
-def test_gate_up_takes_the_kernel_of_its_row_count(tokens):
-    """`gate_up_silu` runs the few-token kernel, the library's product with the SiLU kernel, or the
+def test_gate_up_takes_the_kernel_of_its_row_count(tokens, activation):
+    """`gated_product` runs the few-token kernel, the library's product with the activation kernel, or the
     CTA-pair kernel, by the number of rows: the same result from each."""
     inner, k = 264, 200
     x, w = operands(tokens, 2 * inner, k, seed=tokens)
     word = ops.new_error_word(DEV)
-    got = ops.gate_up_silu(x.to(DEV), w.to(DEV), inner, word)
+    got = ops.gated_product(x.to(DEV), w.to(DEV), inner, word, activation)
     ops.raise_on_error_word(word)
     gate_up = pm.plain_linear(x.double(), w.double())
-    want = pm.plain_silu_mul(gate_up[:, :inner], gate_up[:, inner:])
+    want = GATED[activation](gate_up[:, :inner], gate_up[:, inner:])
     assert got.shape == (tokens, inner) and relative_error(got, want) < 1e-2

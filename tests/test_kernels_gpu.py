@@ -160,9 +160,12 @@ def test_silu_mul_and_bias(dtype):
     g = torch.Generator().manual_seed(1)
     gate_up = torch.randn(5, 2 * 200, generator=g) * 4
     out = torch.empty(5, 200, device=DEV, dtype=dtype)
-    ops.silu_mul(gate_up.to(DEV, dtype), out)
+    ops.gated_mul(gate_up.to(DEV, dtype), out)
     seen = rounded(gate_up, dtype)
     close(out, pm.plain_silu_mul(seen[:, :200], seen[:, 200:]), dtype, "silu*mul")
+    ops.gated_mul(gate_up.to(DEV, dtype), out, "gelu_tanh")
+    g_, u_ = seen[:, :200], seen[:, 200:]
+    close(out, 0.5 * g_ * (1.0 + torch.tanh(math.sqrt(2.0 / math.pi) * (g_ + 0.044715 * g_ ** 3))) * u_, dtype, "gelu*mul")
     values = torch.randn(4, 77, generator=g)
     bias = torch.randn(77, generator=g)
     v = values.to(DEV, dtype)
@@ -464,7 +467,8 @@ def test_decode_attention_finds_a_far_key_and_respects_the_window_edge():
 
 @pytest.mark.parametrize("dtype", DTYPES)
 @pytest.mark.parametrize("n_q,n_kv,d,page,window", [(4, 2, 16, 16, None), (6, 3, 32, 8, None), (5, 1, 48, 16, 37),
-                                                    (8, 8, 64, 4, None), (16, 2, 128, 32, 100), (3, 1, 272, 16, None)])
+                                                    (8, 8, 64, 4, None), (16, 2, 128, 32, 100), (3, 1, 272, 16, None),
+                                                    (6, 2, 40, 16, None), (3, 3, 18, 8, 50), (2, 1, 510, 16, None)])
 @pytest.mark.parametrize("split", [0, 32, 128, 256])
 def test_paged_attention(dtype, n_q, n_kv, d, page, window, split):
     lengths, rows = (1, 33, 300, 64, 257), (1, 5, 2, 64, 1)
@@ -606,9 +610,9 @@ def test_attention_refuses_sizes_it_cannot_take():
         ops.paged_attention(bad_q, case["k_pool"], case["v_pool"], torch.empty_like(bad_q), case["positions"],
                             case["row_request"], case["table"], scale=1.0, window=0, split_size=0, max_splits=1,
                             scratch_acc=None, scratch_ml=None, error_word=ops.new_error_word(DEV))
-    pool = torch.zeros(4, 1, 16, 40, device=DEV)
-    q = torch.zeros(1, 2, 40, device=DEV)
-    with pytest.raises(ops.KernelError, match="multiple of 16"):
+    pool = torch.zeros(4, 1, 16, 520, device=DEV)
+    q = torch.zeros(1, 2, 520, device=DEV)
+    with pytest.raises(ops.KernelError, match="at most 512"):
         ops.paged_attention(q, pool, pool, torch.empty_like(q), case["positions"], case["row_request"], case["table"],
                             scale=1.0, window=0, split_size=0, max_splits=1, scratch_acc=None, scratch_ml=None,
                             error_word=ops.new_error_word(DEV))

@@ -23,6 +23,8 @@ CASES = {
     # head_dim 128 / 64: in bfloat16 these run the tensor-core attention kernels and the tcgen05 product
     "D": (pm.TINY_D, (2, 129, 700, 64, 385, 257), 16),
     "E": (pm.TINY_E, (65, 130, 31, 400, 5, 90, 200, 33), 32),
+    # head_dim 18: even, no multiple of 16 (scalar paths of the rope kernel, a ragged last lane of the attention)
+    "F": (pm.TINY_F, (4, 150, 61, 300, 97), 4),
 }
 DTYPES = {"float32": (torch.float32, rh.FP32_TOLERANCE), "bfloat16": (torch.bfloat16, rh.BF16_TOLERANCE)}
 
@@ -107,6 +109,61 @@ def test_captured_decode_steps_equal_eager_ones(prepared, case, dtype_name):
         print(f"{case}/{dtype_name}: captured against eager: {worst:.3e} at {where}")
         assert worst <= (0.0 if dtype_name == "float32" else 1e-2)
         check(captured, expected, DTYPES[dtype_name][1], requests, f"{case}/{dtype_name}/captured")
+
+
+@pytest.mark.parametrize("dtype_name", list(DTYPES))
+def test_replay_with_the_prefix_tree(tmp_path, dtype_name):
+    """Tiny B, pages of 8: a second prompt shares 24 tokens with the first and is fed whole; it starts at
+    position 24 on the first one's three pages, and its rows from 24 on equal the oracle's rows of the whole
+    prompt.  A prompt that is known entirely still computes what lies behind its last whole page but one token
+    (40 known tokens: 4 pages taken).  A third kind arrives in two portions: only the first is matched."""
+    stored, tolerance = DTYPES[dtype_name]
+    folder = rh.make_folder(tmp_path, "radix", pm.TINY_B, seed=41, dtype=stored)
+    base = list(rh.random_requests(pm.TINY_B, (40,), seed=12).values())[0]
+    requests = {"a": base,
+                "b": base[:24] + list(rh.random_requests(pm.TINY_B, (16,), seed=13).values())[0],
+                "c": list(base),
+                "d": base[:24] + list(rh.random_requests(pm.TINY_B, (30,), seed=14).values())[0]}
+    expected = rh.oracle(folder, requests)
+    whole = lambda rid: {"id": rid, "tokens": requests[rid], "want": list(range(len(requests[rid])))}  # noqa: E731
+    trace = [{"step": 0, "entries": [whole("a")], "end": []},
+             {"step": 1, "entries": [whole("b")], "end": []},
+             {"step": 2, "entries": [whole("c"), {"id": "d", "tokens": requests["d"][:30], "want": list(range(30))}],
+              "end": ["a"]},
+             {"step": 3, "entries": [{"id": "d", "tokens": requests["d"][30:], "want": list(range(24))}],
+              "end": ["b", "c", "d"]}]
+    from sglang_rs_b200.engine.replay import ReplaySession
+    session = ReplaySession(folder, dtype_name, 512, page_size=8, radix=True)
+    outputs, tables = [], {}
+    for step in trace:
+        outputs.append(session.run(step))
+        for rid, handle in session.handles.items():
+            tables[rid] = handle.table(("kv", None))
+        session.cache.check_invariants()
+    assert session.cached_tokens == {"a": 0, "b": 24, "c": 32, "d": 24}
+    assert tables["b"][:3] == tables["a"][:3] and tables["b"][3] != tables["a"][3]     # the same physical pages
+    assert tables["c"][:4] == tables["a"][:4] and tables["d"][:3] == tables["a"][:3]
+    rows = rh.collect(trace, outputs)
+    computed = {}
+    for rid, by_pos in rows.items():
+        skipped = session.cached_tokens[rid]
+        assert all(np.isnan(by_pos[p]).all() for p in range(skipped)), "rows inside the cached prefix are not computed"
+        computed[rid] = {p: row for p, row in by_pos.items() if p >= skipped}
+        assert len(computed[rid]) == len(requests[rid]) - skipped
+    bad = rh.first_bad(computed, expected, tolerance)
+    worst, where = rh.worst_error(computed, expected)
+    print(f"B/{dtype_name}/prefix tree: worst error {worst:.3e} at {where}")
+    assert bad is None, f"first wrong row: request {bad[0]} position {bad[1]} error {bad[2]:.3e}"
+    tree = session.cache.prefix_tree
+    assert tree.hits == 3 and not session.handles
+    allocator = session.cache.allocators[("kv", None)]
+    assert allocator.free_count + tree.pages_held == allocator.num_pages
+    # without the tree the same trace computes every row, and the rows behind the prefix agree with those above
+    plain_rows, _ = rh.run_in_process(folder, dtype_name, trace, max_tokens=512, page_size=8)
+    for rid in computed:
+        for p, row in computed[rid].items():
+            err = float(np.abs(row.astype(np.float64) - plain_rows[rid][p]).max()) / float(np.abs(expected[rid]).max())
+            assert err <= (2e-5 if dtype_name == "float32" else 2e-2), (rid, p, err)
 
 
 def test_trace_run_program(prepared, tmp_path):
