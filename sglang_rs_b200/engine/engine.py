@@ -18,6 +18,7 @@ from .. import ops
 from ..cache.manager import CacheManager
 from ..sampling import RequestRandom, Sampler, SamplingParams
 from ..weights import load_model, parse_dtype
+from .metrics import EngineMetrics
 from .runner import ModelRunner, StepEntry
 from .scheduler import Request, Scheduler, SchedulerConfig, StepOutput
 
@@ -81,6 +82,8 @@ class Engine:
         self._requests: Dict[Hashable, Request] = {}
         self._ids = itertools.count()
         self._in_flight: Optional[_StepInFlight] = None
+        #: totals over the requests (the reference's serving counters); ``metrics.render()`` gives them as text
+        self.metrics = EngineMetrics()
 
     # ------------------------------------------------------------------ low level
     def add_request(self, input_ids: Sequence[int], sampling_params: Union[SamplingParams, Mapping, None] = None,
@@ -98,6 +101,7 @@ class Engine:
         request = Request(request_id, ids, params)
         self.scheduler.add_request(request)
         self._requests[request_id] = request
+        self.metrics.arrived(request_id, len(ids))
         self._randoms[request_id] = RequestRandom(request_id, params.seed)
         if params.has_penalties:
             self.sampler.seen.open(request_id, ids)          # the prompt's tokens count as seen
@@ -117,7 +121,9 @@ class Engine:
         outputs = self.drain()
         entries = self.scheduler.schedule()
         if not entries:
-            return outputs + self.scheduler.process_outputs([], [])
+            fresh = self.scheduler.process_outputs([], [])
+            self._forget_finished(fresh)
+            return outputs + fresh
         step_entries = [StepEntry(e.request.handle, e.tokens, [len(e.tokens) - 1] if e.samples else [])
                         for e in entries]
         try:
@@ -132,12 +138,15 @@ class Engine:
         except Exception:
             self.scheduler.step_failed(entries)
             raise
-        outputs += self.scheduler.process_outputs(entries, sampled)
-        self._forget_finished(outputs)
-        return outputs
+        fresh = self.scheduler.process_outputs(entries, sampled)
+        self._forget_finished(fresh)
+        return outputs + fresh
 
     def _forget_finished(self, outputs: Sequence[StepOutput]) -> None:
         for output in outputs:
+            self.metrics.produced(output.request_id, len(output.token_ids), output.finished,
+                                  failed=output.finish_reason in ("abort", "cache_full"),
+                                  cached_tokens=output.cached_tokens if output.finished else 0)
             if output.finished and self._randoms.pop(output.request_id, None) is not None:
                 self.sampler.seen.close(output.request_id)
 

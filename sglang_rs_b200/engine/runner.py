@@ -11,6 +11,7 @@ Both generation (the scheduler) and trace replay call :meth:`ModelRunner.step`.
 """
 from __future__ import annotations
 
+import time
 from dataclasses import dataclass, field
 from typing import Dict, Hashable, List, Optional, Sequence
 
@@ -19,6 +20,8 @@ import torch
 
 from .. import ops
 from ..cache.manager import CacheManager, OutOfPages, RequestCache
+from ..ops import trace
+from .metrics import StepLog, StepStats, step_log_target
 
 
 class StepInputError(ValueError):
@@ -258,6 +261,9 @@ class ModelRunner:
         self.planner = StepPlanner(cache, self.device, self.dtype, widths)
         self.error_word = self.planner.error_word
         self.steps_run = 0
+        #: the record of the last step, and the log that keeps (and, if asked by SRB_STEP_LOG, writes) them all
+        self.last_stats: Optional[StepStats] = None
+        self.step_log = StepLog(step_log_target())
         self.graphs = None
         if use_cuda_graphs and all(getattr(layer, "graph_safe", False) for layer in model.layers):
             from .graphs import DecodeGraphs
@@ -271,6 +277,12 @@ class ModelRunner:
         entries = [entry for entry in entries]
         if not entries:
             return None
+        started = time.perf_counter()
+        timers = trace.active
+        begin = end = None
+        if self.step_log.time_device or (timers is not None and timers.events):
+            begin, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            begin.record()
         self._validate(entries, token_source)
         reserved: List[StepEntry] = []
         try:
@@ -281,9 +293,11 @@ class ModelRunner:
             for entry in reserved:
                 self.cache.trim_reservation(entry.handle)
             raise
+        captured = False
         try:
             if self.graphs is not None and self.graphs.eligible(entries):
                 logits = self.graphs.run(entries, token_source)
+                captured = True
             else:
                 ctx, logit_rows = self.planner.flatten(entries, token_source)
                 caches = [self.cache.layer_cache(i) for i in range(len(self.model.program))]
@@ -296,6 +310,20 @@ class ModelRunner:
         for entry in entries:
             self.cache.commit(entry.handle, len(entry.tokens))
         self.steps_run += 1
+        if end is not None:
+            end.record()
+        counts = [len(entry.tokens) for entry in entries]
+        decode_rows = sum(1 for count in counts if count == 1)
+        stats = StepStats(
+            step=self.steps_run, rows=sum(counts), requests=len(entries), decode_rows=decode_rows,
+            prompt_rows=sum(counts) - decode_rows, wanted=sum(len(entry.want) for entry in entries), captured=captured,
+            pages_free={":".join(str(part) for part in key) if isinstance(key, tuple) else str(key): free
+                        for key, free in self.cache.free_pages().items()},
+            host_ms=(time.perf_counter() - started) * 1e3)
+        if timers is not None and timers.events:
+            stats.kernels = {kind: round(ms, 4) for kind, ms in timers.collect().items()}    # waits for the step
+        self.step_log.add(stats, begin, end)
+        self.last_stats = stats
         return logits
 
     def check_device_errors(self) -> None:

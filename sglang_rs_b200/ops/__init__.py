@@ -13,6 +13,8 @@ from typing import Optional
 import torch
 
 from ..csrc.build import load_library
+from . import trace
+from .trace import traced
 
 F32, BF16 = 0, 1
 
@@ -138,6 +140,7 @@ def raise_on_error_value(value: int, word: torch.Tensor) -> None:
 
 # --------------------------------------------------------------------------- rows
 
+@traced("embedding")
 def embedding(ids: torch.Tensor, table: torch.Tensor, residual: torch.Tensor, error_word: torch.Tensor) -> None:
     """residual[r, :] = float(table[ids[r], :])"""
     _need(ids, "ids", torch.int32); _need(table, "table"); _need(residual, "residual", torch.float32)
@@ -149,6 +152,7 @@ def embedding(ids: torch.Tensor, table: torch.Tensor, residual: torch.Tensor, er
                                   _ptr(error_word), dtype_code(table.dtype), _stream()))
 
 
+@traced("embedding")
 def take_tokens(tokens: torch.Tensor, source: torch.Tensor, index: torch.Tensor, error_word: torch.Tensor) -> None:
     """tokens[i] = source[index[i]] where index[i] >= 0 (int32, on the device): the token ids that the
     step before chose and that have not been to the host yet."""
@@ -160,6 +164,7 @@ def take_tokens(tokens: torch.Tensor, source: torch.Tensor, index: torch.Tensor,
                                     _ptr(error_word), _stream()))
 
 
+@traced("norm")
 def add_rmsnorm(residual: torch.Tensor, delta: Optional[torch.Tensor], weight: torch.Tensor, eps: float,
                 out: torch.Tensor, row_index: Optional[torch.Tensor] = None, write_residual: bool = True) -> None:
     """x = residual (+ delta); residual = x if asked; out = x / sqrt(mean(x^2) + eps) * weight.
@@ -207,6 +212,7 @@ def activation_code(name: str) -> int:
         raise KernelError(f"unknown activation {name!r}; the kernels have {sorted(ACTIVATIONS)}") from None
 
 
+@traced("activation")
 def gated_mul(gate_up: torch.Tensor, out: torch.Tensor, activation: str = "silu") -> None:
     """out[r, j] = act(gate_up[r, j]) * gate_up[r, inner + j]"""
     _need(gate_up, "gate_up"); _need(out, "out", gate_up.dtype)
@@ -218,6 +224,7 @@ def gated_mul(gate_up: torch.Tensor, out: torch.Tensor, activation: str = "silu"
                                   dtype_code(out.dtype), _stream()))
 
 
+@traced("bias")
 def add_bias(values: torch.Tensor, bias: torch.Tensor) -> None:
     _need(values, "values"); _need(bias, "bias", torch.float32)
     rows, width = values.shape
@@ -229,6 +236,7 @@ def add_bias(values: torch.Tensor, bias: torch.Tensor) -> None:
 
 # --------------------------------------------------------------------------- attention
 
+@traced("rope_kv")
 def qk_norm_rope_kv(qkv: torch.Tensor, q_out: torch.Tensor, k_pool: Optional[torch.Tensor],
                     v_pool: Optional[torch.Tensor], positions: torch.Tensor, slots: Optional[torch.Tensor],
                     q_norm: Optional[torch.Tensor], k_norm: Optional[torch.Tensor], eps: float,
@@ -286,6 +294,7 @@ def attention_scratch_sizes(rows: int, n_q: int, head_dim: int, max_splits: int)
     return rows * n_q * max_splits * head_dim, rows * n_q * max_splits * 2
 
 
+@traced("attention_generic")
 def paged_attention(q: torch.Tensor, k_pool: torch.Tensor, v_pool: torch.Tensor, out: torch.Tensor,
                     positions: torch.Tensor, row_request: torch.Tensor, block_table: torch.Tensor, *,
                     scale: float, window: int, split_size: int, max_splits: int,
@@ -370,6 +379,7 @@ def decode_splits_bound(max_keys: int) -> int:
     return max(1, min(DECODE_MAX_SPLITS, -(-max_keys // 64) // DECODE_MIN_UNITS))
 
 
+@traced("attention_decode")
 def decode_attention(q: torch.Tensor, k_pool: torch.Tensor, v_pool: torch.Tensor, out: torch.Tensor,
                      positions: torch.Tensor, row_request: torch.Tensor, block_table: torch.Tensor, *,
                      scale: float, window: int, scratch_acc: torch.Tensor, scratch_ml: torch.Tensor,
@@ -410,6 +420,7 @@ def tiled_attention_takes(dtype: torch.dtype, n_q: int, n_kv: int, head_dim: int
     return dtype == torch.bfloat16 and head_dim in (64, 128) and n_kv > 0 and n_q % n_kv == 0
 
 
+@traced("attention_prefill")
 def tiled_attention(q: torch.Tensor, k_pool: torch.Tensor, v_pool: torch.Tensor, out: torch.Tensor,
                     tiles: torch.Tensor, block_table: torch.Tensor, *, scale: float, window: int,
                     error_word: torch.Tensor) -> None:
@@ -440,6 +451,7 @@ def tiled_attention_tc_takes(dtype: torch.dtype, n_q: int, n_kv: int, head_dim: 
             and page_size >= 8 and page_size % 8 == 0 and 64 % page_size == 0)
 
 
+@traced("attention_prefill")
 def tiled_attention_tc(q: torch.Tensor, k_pool: torch.Tensor, v_pool: torch.Tensor, out: torch.Tensor,
                        tiles: torch.Tensor, block_table: torch.Tensor, *, scale: float, window: int,
                        error_word: torch.Tensor) -> None:
@@ -491,6 +503,7 @@ def gemm_splits(tokens: int, features: int, k: int, sms: Optional[int] = None) -
     return -(-k_blocks // per_split)
 
 
+@traced("gemm")
 def linear(x: torch.Tensor, weight: torch.Tensor, bias: Optional[torch.Tensor] = None,
            out_dtype: Optional[torch.dtype] = None, error_word: Optional[torch.Tensor] = None,
            partial_ok: bool = False) -> torch.Tensor:
@@ -533,6 +546,7 @@ def linear(x: torch.Tensor, weight: torch.Tensor, bias: Optional[torch.Tensor] =
     return out
 
 
+@traced("gemm")
 def gated_product(x: torch.Tensor, weight: torch.Tensor, inner: int, error_word: Optional[torch.Tensor] = None,
                   activation: str = "silu") -> torch.Tensor:
     """act(x gate^T) * (x up^T) for ``weight`` = gate rows stacked over up rows [2 inner, in].
@@ -558,6 +572,7 @@ GEMM_MODES = {"bf16": 0, "f32": 1, "gated": 2, "partial": 3, "add": 4}
 GEMM_CLUSTER_SPLITS = 8
 
 
+@traced("gemm")
 def gemm_bf16(x: torch.Tensor, w: torch.Tensor, error_word: torch.Tensor, *, mode: str = "bf16",
               features: Optional[int] = None, up_row_offset: int = 0, splits: int = 1,
               out: Optional[torch.Tensor] = None, activation: str = "silu") -> torch.Tensor:
@@ -601,6 +616,7 @@ def gemm_bf16(x: torch.Tensor, w: torch.Tensor, error_word: torch.Tensor, *, mod
     return out
 
 
+@traced("gemm")
 def gemm_bf16_pair(x: torch.Tensor, w: torch.Tensor, error_word: torch.Tensor, *, mode: str = "bf16",
                    features: Optional[int] = None, up_row_offset: int = 0, activation: str = "silu") -> torch.Tensor:
     """y = x @ w^T for many tokens: 256 x 256 tiles on pairs of CTAs (``tcgen05.mma.cta_group::2``) in a
@@ -633,6 +649,7 @@ def gemm_bf16_takes(k: int) -> bool:
 
 # --------------------------------------------------------------------------- sampling
 
+@traced("sampling")
 def sample(logits: torch.Tensor, temperature: Optional[torch.Tensor], uniform: Optional[torch.Tensor],
            out: Optional[torch.Tensor] = None) -> torch.Tensor:
     """One token per row of 32-bit logits: argmax where temperature is None or <= 0, else
@@ -651,6 +668,7 @@ def sample(logits: torch.Tensor, temperature: Optional[torch.Tensor], uniform: O
     return out
 
 
+@traced("sampling")
 def sample_filtered(logits: torch.Tensor, rows_index: Optional[torch.Tensor], temperature: torch.Tensor,
                     top_k: torch.Tensor, top_p: torch.Tensor, min_p: torch.Tensor, uniform: torch.Tensor,
                     out: torch.Tensor) -> None:
@@ -679,6 +697,7 @@ def sample_filtered(logits: torch.Tensor, rows_index: Optional[torch.Tensor], te
                                         _ptr(scratch), _ptr(out), _stream()))
 
 
+@traced("sampling")
 def count_tokens(counts_row: torch.Tensor, tokens: torch.Tensor) -> None:
     """``counts_row[t] += 1`` for every token id in ``tokens`` (int32, on the device)."""
     _need(counts_row, "counts_row", torch.int32); _need(tokens, "tokens", torch.int32)
@@ -686,6 +705,7 @@ def count_tokens(counts_row: torch.Tensor, tokens: torch.Tensor) -> None:
     _check(lib, lib.srb_count_tokens(_ptr(counts_row), _ptr(tokens), tokens.numel(), counts_row.numel(), _stream()))
 
 
+@traced("sampling")
 def apply_penalties(logits: torch.Tensor, counts: torch.Tensor, index: torch.Tensor, presence: torch.Tensor,
                     frequency: torch.Tensor, repetition: torch.Tensor) -> None:
     """Penalises ``logits`` in place: row r uses the counts of ``counts[index[r]]`` (``index[r] < 0``: none).
@@ -702,6 +722,7 @@ def apply_penalties(logits: torch.Tensor, counts: torch.Tensor, index: torch.Ten
                                         _ptr(index), _ptr(presence), _ptr(frequency), _ptr(repetition), _stream()))
 
 
+@traced("sampling")
 def count_picked(counts: torch.Tensor, index: torch.Tensor, picked: torch.Tensor) -> None:
     """``counts[index[r], picked[r]] += 1`` for every row with ``index[r] >= 0``."""
     _need(counts, "counts", torch.int32); _need(index, "index", torch.int32); _need(picked, "picked", torch.int32)

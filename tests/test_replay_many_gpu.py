@@ -7,6 +7,13 @@ inside a cluster or through global memory depending on how many blocks there are
 takes the gate/up product of portions of 1,280 rows and more.  Each of these schedules is compared here
 with the oracle at model level: ~20, ~40, ~70 and ~150 live requests, all decoding together (captured and
 uncaptured) and mixed with prompt portions on a pool so small that pages are used again.
+
+These tests compare six times as many logits as the other replay tests, so the largest bfloat16 error
+among them lies further out in the tail of rounding noise: with the q-norm scales sharpened by 3, as the
+other tests have them, whole prompts alone already reach 3.3e-2 of the scale in the worst of 12,000 rows
+(median 0.9e-2, 99.9th percentile 2.3e-2, the same figures for every way of cutting).  The models here
+are sharpened by 2 (worst 2.0e-2, whole or cut), which leaves the bound of 3e-2 able to tell a fault from
+noise; the bound itself is the one of the other tests.
 """
 import numpy as np
 import pytest
@@ -20,6 +27,7 @@ pytestmark = pytest.mark.gpu
 DTYPES = {"float32": (torch.float32, rh.FP32_TOLERANCE), "bfloat16": (torch.bfloat16, rh.BF16_TOLERANCE)}
 CONFIGS = {"A": (pm.TINY_A, 16), "D": (pm.TINY_D, 16)}
 LIVE = (20, 40, 70, 150)
+SHARPEN = 2.0
 
 
 @pytest.fixture(scope="module")
@@ -31,7 +39,7 @@ def prepared(tmp_path_factory):
         if key not in cache:
             config, page = CONFIGS[case]
             folder = rh.make_folder(tmp_path_factory.mktemp(f"many_{case}_{dtype_name}"), "model", config, seed=13,
-                                    dtype=DTYPES[dtype_name][0])
+                                    dtype=DTYPES[dtype_name][0], sharpen=SHARPEN)
             rng = np.random.RandomState(5)
             lengths = [int(n) for n in rng.randint(9, 120, size=200)]
             requests = rh.random_requests(config, lengths, seed=17)
@@ -91,6 +99,12 @@ def test_many_requests_mixed_on_few_pages(prepared, case, dtype_name, live):
     decode_rows = [sum(len(e["tokens"]) == 1 for e in s["entries"]) for s in trace]
     print(f"most decoded rows in a step: {max(decode_rows)}, steps: {len(trace)}")
     assert max(decode_rows) > live // 2
+    # against the same engine fed whole prompts, one at a time: the cut and the company add rounding only
+    whole, _ = rh.run_in_process(folder, dtype_name, rh.trace_whole(requests), max_tokens=4096, page_size=page)
+    worst = max(float(np.abs(rows[rid][p].astype(np.float64) - whole[rid][p]).max()) / float(np.abs(expected[rid]).max())
+                for rid in rows for p in rows[rid])
+    print(f"mixed against whole: {worst:.3e}")
+    assert worst <= (2e-5 if dtype_name == "float32" else 2e-2)
 
 
 def test_a_portion_of_more_than_1280_rows_inside_a_model(tmp_path):
@@ -98,7 +112,7 @@ def test_a_portion_of_more_than_1280_rows_inside_a_model(tmp_path):
     (SiLU in the epilogue), its attention on the tcgen05 kernel with many tiles; then tokens one by one."""
     from sglang_rs_b200 import ops
     config = dict(pm.TINY_D, max_position_embeddings=2048)
-    folder = rh.make_folder(tmp_path, "long", config, seed=23, dtype=torch.bfloat16)
+    folder = rh.make_folder(tmp_path, "long", config, seed=23, dtype=torch.bfloat16, sharpen=SHARPEN)
     requests = rh.random_requests(config, (1540, 1300), seed=29)
     assert ops.pair_gemm_takes(1500, config["intermediate_size"], config["hidden_size"])
     expected = rh.oracle(folder, requests)
