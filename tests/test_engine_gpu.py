@@ -725,3 +725,37 @@ def test_another_position_encoding_and_a_routed_feed_forward(tmp_path, experts, 
         assert (session.runner.graphs is not None) == (experts == 0)
     finally:
         unregister_architecture("ToyPartsForTests")
+
+
+def test_step_records_kernel_classes_and_request_totals(tmp_path):
+    """What the engine counts: a record per step (rows, kinds of rows, pages free, host and device time), the
+    device time per kernel class when tracing is on, and the totals over requests in the reference's names."""
+    from sglang_rs_b200 import Engine
+    from sglang_rs_b200.ops import trace
+    folder = rh.make_folder(tmp_path, "m", pm.TINY_D, seed=3, dtype=torch.bfloat16)
+    engine = Engine(model_path=folder, dtype="bfloat16", max_total_tokens=1024, chunked_prefill_size=32,
+                    disable_cuda_graph=True)
+    prompts = list(rh.random_requests(pm.TINY_D, (70, 9, 33), seed=8).values())
+    saved = trace.active
+    try:
+        trace.configure("events")
+        results = engine.generate(prompts, {"max_new_tokens": 5, "ignore_eos": True})
+    finally:
+        trace.active = saved
+    records = engine.runner.step_log.flush()
+    assert len(records) == engine.runner.steps_run and records[-1] is engine.runner.last_stats
+    assert sum(r.prompt_rows + r.decode_rows for r in records) == sum(r.rows for r in records)
+    assert sum(r.rows for r in records) == sum(len(p) for p in prompts) + 3 * 4      # the last token is never fed
+    assert all(r.rows <= 32 + 3 for r in records) and any(r.decode_rows and r.prompt_rows for r in records)
+    assert all(r.device_ms is not None and r.device_ms > 0 and r.host_ms > 0 for r in records)
+    kinds = set().union(*(r.kernels for r in records))
+    assert {"embedding", "norm", "gemm", "rope_kv"} <= kinds and any(k.startswith("attention") for k in kinds)
+    for r in records:
+        assert 0 < sum(r.kernels.values()) <= r.device_ms * 1.05 + 0.05
+    assert "kv:None" in records[0].pages_free
+    m = engine.metrics
+    assert (m.requests_total, m.requests_in_flight, m.requests_failed_total) == (3, 0, 0)
+    assert m.prompt_tokens_total == sum(len(p) for p in prompts) and m.generation_tokens_total == 15
+    assert m.time_to_first_token_seconds_count == 3 and m.request_duration_seconds_count == 3
+    assert all(len(r["output_ids"]) == 5 for r in results)
+    assert "sglang_generation_tokens_total 15" in m.render()
