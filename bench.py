@@ -196,14 +196,14 @@ def main() -> int:
     def decode_run(engine: Engine, batch: int, steps: int, context: int, sample_clocks: bool, entry_point: bool = True):
         """Prefill ``batch`` requests of ``context`` tokens, then time ``steps`` decode steps twice: the whole
         entry point, and the step function alone on the device."""
-        ids = [engine.add_request(p, {"max_new_tokens": 1 << 30, "ignore_eos": True}) for p in prompts(batch, context)]
-        while any(not engine.scheduler._is_decoding(engine._requests[i]) for i in ids):
-            engine.step()                                     # portions of prompts until every request decodes
-        requests = [engine._requests[i] for i in ids]
         begin, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         e2e_ms = h2d = None
         sampler = ClockSampler()
         if entry_point:
+            ids = [engine.add_request(p, {"max_new_tokens": 1 << 30, "ignore_eos": True}) for p in prompts(batch, context)]
+            while any(not engine.scheduler._is_decoding(engine._requests[i]) for i in ids):
+                engine.step()                                 # portions of prompts until every request decodes
+            requests = [engine._requests[i] for i in ids]
             # --- entry point, end to end: every step takes its rows' index arrays from pinned host memory and
             # hands the tokens of the step before back to the host (steps overlap the host's work)
             for _ in range(warmup):
@@ -224,13 +224,22 @@ def main() -> int:
             assert produced == steps * batch, (produced, steps, batch)
             e2e_ms = max(begin.elapsed_time(end), wall * 1e3) / steps
             h2d = engine.runner.planner.last_upload_bytes
-        elif sample_clocks:
-            sampler.start()
+            handles = [r.handle for r in requests]
+            tokens = [[r.tokens[-1]] for r in requests]
+            for r in requests:                                # the scheduler must not touch them meanwhile
+                engine.scheduler.release(r)
+        else:
+            # the prompts go through the step function directly, a portion at a time, so that every request
+            # holds exactly ``context`` tokens when the timed steps begin
+            names = iter(range(1 << 30))
+            handles = [engine.cache.open(f"direct-{batch}-{context}-{next(names)}") for _ in range(batch)]
+            for handle, prompt in zip(handles, prompts(batch, context)):
+                for first in range(0, context, 2048):
+                    engine.runner.step([StepEntry(handle, prompt[first:first + 2048], [])])
+            tokens = [[1] for _ in handles]
+            if sample_clocks:
+                sampler.start()
         # --- the step function alone: fixed token ids, logits stay on the device, greedy pick on the device
-        handles = [r.handle for r in requests]
-        tokens = [[r.tokens[-1]] for r in requests]
-        for r, h in zip(requests, handles):                   # the scheduler must not touch them meanwhile
-            engine.scheduler.release(r)
 
         def one_step():
             logits = engine.runner.step([StepEntry(h, t, [0]) for h, t in zip(handles, tokens)])
@@ -335,7 +344,7 @@ def main() -> int:
 
     short = min(args.steps, 32)
     end_context = SHAPES[args.shape]["context"] if args.shape == "qwen3-8b" else 4096
-    late = max(args.context, end_context - 2 * (short + warmup) - 16)       # the far end of the context sweep
+    late = max(args.context, end_context - (short + warmup) - 8)           # the far end of the context sweep
     engine = make_engine(max(args.batch, 1), args.steps, args.context if args.skip_points else late,
                          extra_tokens=max(4096, args.prefill_tokens))
     if args.only_prefill:
@@ -446,10 +455,27 @@ def compare_cublas(args, config, peak, shape_note) -> int:
                 torch.cuda.synchronize()
                 repeats = 20 if m <= 64 else 10
                 begin, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-                begin.record()
-                for i in range(repeats):
-                    call(weights[(i + 3) % copies])
-                end.record()
+                if m <= 64:
+                    # a few microseconds of kernel each: launched one by one the host would be what is timed, so
+                    # the calls are captured into one graph (as the engine's decode steps are) and replayed
+                    graph = torch.cuda.CUDAGraph()
+                    side = torch.cuda.Stream()
+                    side.wait_stream(torch.cuda.current_stream())
+                    with torch.cuda.stream(side):
+                        with torch.cuda.graph(graph, stream=side), ops.stream_scope():
+                            for i in range(repeats):
+                                call(weights[(i + 3) % copies])
+                    torch.cuda.current_stream().wait_stream(side)
+                    graph.replay()
+                    torch.cuda.synchronize()
+                    begin.record()
+                    graph.replay()
+                    end.record()
+                else:
+                    begin.record()
+                    for i in range(repeats):
+                        call(weights[(i + 3) % copies])
+                    end.record()
                 torch.cuda.synchronize()
                 return begin.elapsed_time(end) * 1e3 / repeats
             own_us, library_us = timed(own), timed(library)
@@ -467,7 +493,7 @@ def compare_cublas(args, config, peak, shape_note) -> int:
         torch.cuda.empty_cache()
     ops.raise_on_error_word(word)
     print(json.dumps({"mode": "compare-cublas", "config": shape_note, "timing": "CUDA events, weights rotate through copies "
-                      "larger than L2; gate_up includes the activation (own: in the epilogue; cuBLAS: a kernel after it)",
+                      "larger than L2; up to 64 rows the calls are replayed from one CUDA graph; gate_up includes the activation (own: in the epilogue; cuBLAS: a kernel after it)",
                       "products": results}))
     return 0
 

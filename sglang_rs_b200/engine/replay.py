@@ -35,7 +35,7 @@ class ReplaySession:
 
     def __init__(self, model_dir: str, dtype: str, max_tokens: int, page_size: int = PAGE_SIZE,
                  device: str = "cuda", use_cuda_graphs: bool = True, max_live: int = DEFAULT_MAX_LIVE,
-                 radix: bool = False):
+                 radix: bool = False, native_step=None):
         import torch
         from ..cache import CacheManager
         from ..weights import load_model, parse_dtype
@@ -52,7 +52,7 @@ class ReplaySession:
             if not self.cache.prefix_reuse_possible():
                 raise RuntimeError("this model's cache cannot share prefixes (a window or per-request state)")
             self.cache.enable_prefix_reuse()
-        self.runner = ModelRunner(self.model, self.cache, use_cuda_graphs=use_cuda_graphs)
+        self.runner = ModelRunner(self.model, self.cache, use_cuda_graphs=use_cuda_graphs, native_step=native_step)
         self.handles = {}
         self.history = {}            # request -> every token fed so far (kept only with a prefix tree)
         self.cached_tokens = {}      # request -> tokens its first entry took from the prefix tree

@@ -11,6 +11,7 @@ Both generation (the scheduler) and trace replay call :meth:`ModelRunner.step`.
 """
 from __future__ import annotations
 
+import os
 import time
 from dataclasses import dataclass, field
 from typing import Dict, Hashable, List, Optional, Sequence
@@ -249,7 +250,7 @@ class StepPlanner:
 
 
 class ModelRunner:
-    def __init__(self, model, cache: CacheManager, use_cuda_graphs: bool = True):
+    def __init__(self, model, cache: CacheManager, use_cuda_graphs: bool = True, native_step: Optional[bool] = None):
         if model.device is None:
             raise RuntimeError("the model has no weights yet")
         if model.device.type != "cuda":
@@ -264,6 +265,16 @@ class ModelRunner:
         #: the record of the last step, and the log that keeps (and, if asked by SRB_STEP_LOG, writes) them all
         self.last_stats: Optional[StepStats] = None
         self.step_log = StepLog(step_log_target())
+        # A model whose parts all have records for the step executor runs a step in one native call
+        # (``native_step`` False, or SRB_NATIVE_STEP=0, keeps the part-by-part launches).
+        if native_step is None:
+            native_step = os.environ.get("SRB_NATIVE_STEP", "1") not in ("0", "off", "false")
+        model.native = None
+        if native_step:
+            from .native import NativeModel, prepare
+            model.native = NativeModel.of(model)
+            if model.native is not None:
+                prepare(model.native, cache.page_size)
         self.graphs = None
         if use_cuda_graphs and all(getattr(layer, "graph_safe", False) for layer in model.layers):
             from .graphs import DecodeGraphs

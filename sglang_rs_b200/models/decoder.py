@@ -13,6 +13,7 @@ from typing import Dict, List, Mapping, Optional, Sequence
 
 import torch
 
+from ..ops import trace
 from ..parts.base import CacheNeed, Part, TensorSpec
 
 
@@ -45,6 +46,9 @@ class DecoderModel(Part):
                     raise ValueError(f"program entry {index} reads a cache of another shape than its own")
         self.dtype: Optional[torch.dtype] = None
         self.device = None
+        #: the model's records for the step executor (engine/native.py), set by the runner when every part has
+        #: one; ``forward`` then is one native call
+        self.native = None
 
     def all_parts(self):
         return [self.embedding, *self.layers, self.final_norm, self.head]
@@ -68,6 +72,9 @@ class DecoderModel(Part):
     def forward(self, ctx, caches: Sequence, logit_rows: Optional[torch.Tensor]) -> Optional[torch.Tensor]:
         """Runs the rows of ``ctx``; returns 32-bit logits of the rows in ``logit_rows``
         (None or empty: the pass only fills the caches)."""
+        if self.native is not None and trace.active is None and all(
+                cache is not None and hasattr(cache, "k_pool") for cache in caches):
+            return self.native.run(ctx, caches, logit_rows)
         residual = self.embedding.forward(ctx, ctx.token_ids)
         delta = None
         for index, call in enumerate(self.program):

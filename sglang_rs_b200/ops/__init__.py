@@ -13,14 +13,14 @@ from typing import Optional
 import torch
 
 from ..csrc.build import load_library
-from . import trace
+from . import records, trace
 from .trace import traced
 
 F32, BF16 = 0, 1
 
-# Products of more than a few rows go to cuBLAS through torch.  Its bfloat16 products may add the partial
-# sums of a split along K in bfloat16 unless told otherwise; every product of this engine accumulates in
-# 32 bits to the end, so that is switched off once, here.
+# Products of more than a few rows go to cuBLAS (``library_product``), on a handle whose math mode forbids
+# partial sums of a split along K in bfloat16: every product of this engine accumulates in 32 bits to the
+# end.  The same is asked of torch's own handle, for callers that mix torch's products with this package.
 torch.backends.cuda.matmul.allow_bf16_reduced_precision_reduction = False
 
 
@@ -327,8 +327,9 @@ def paged_attention(q: torch.Tensor, k_pool: torch.Tensor, v_pool: torch.Tensor,
 
 
 
-#: blocks per SM that the decode attention aims at
-DECODE_BLOCKS_PER_SM = 3
+
+
+#: the most blocks per (row, kv head) that :func:`decode_splits` ever returns
 DECODE_MAX_SPLITS = 64
 
 
@@ -338,45 +339,24 @@ def decode_attention_takes(dtype: torch.dtype, n_q: int, n_kv: int, head_dim: in
     return dtype == torch.bfloat16 and head_dim in (64, 128) and n_kv > 0 and n_q % n_kv == 0 and n_q // n_kv <= 16
 
 
-#: a block of the decode attention should walk at least this many 64-key units
-DECODE_MIN_UNITS = 2
-
-
-#: what a block costs beside its keys (set-up, the load of q, the merge), in 64-key units: up to
-#: DECODE_CLUSTER_SPLITS blocks merge inside a thread-block cluster, more go through global memory
-DECODE_BLOCK_OVERHEAD_UNITS = 3
-DECODE_GLOBAL_MERGE_UNITS = 3
-DECODE_CLUSTER_SPLITS = 8
 
 
 def decode_splits(rows: int, n_kv: int, max_keys: Optional[int] = None, sms: Optional[int] = None) -> int:
     """Blocks per (row, kv head).  A function of the shape and of the device's SM count (``sms``;
-    default: the current device's) only.
+    default: the current device's) only; defined in csrc/step_exec.cu, where the step executor uses it too.
 
     Without ``max_keys`` (the most keys any row sees): as many as make about three blocks per SM.
     With it, the count that makes the step shortest under a simple model: the blocks run in waves
     of three per SM, and a wave lasts as long as one block's share of the keys plus a fixed cost.
     Many rows then still get their keys cut (512 blocks are 1.15 waves: nearly half the second
-    wave's time is lost), and no block walks fewer than ``DECODE_MIN_UNITS`` units."""
-    base = max(rows * n_kv, 1)
-    target = DECODE_BLOCKS_PER_SM * (sms if sms is not None else sm_count())
-    if max_keys is None:
-        return max(1, min(DECODE_MAX_SPLITS, target // base))
-    units = max(1, -(-max_keys // 64))
-    cap = max(1, min(DECODE_MAX_SPLITS, units // DECODE_MIN_UNITS))
-    best, best_cost = 1, None
-    for splits in range(1, cap + 1):
-        waves = -(-base * splits // target)
-        cost = waves * (-(-units // splits) + DECODE_BLOCK_OVERHEAD_UNITS) + (
-            DECODE_GLOBAL_MERGE_UNITS if splits > DECODE_CLUSTER_SPLITS else 0)
-        if best_cost is None or cost < best_cost:
-            best, best_cost = splits, cost
-    return best
+    wave's time is lost), and no block walks fewer than two 64-key units."""
+    return records.library().sx_decode_splits(int(rows), int(n_kv), -1 if max_keys is None else int(max_keys),
+                                              int(sms if sms is not None else sm_count()))
 
 
 def decode_splits_bound(max_keys: int) -> int:
     """No call of :func:`decode_splits` with this ``max_keys`` returns more, whatever the rows and heads."""
-    return max(1, min(DECODE_MAX_SPLITS, -(-max_keys // 64) // DECODE_MIN_UNITS))
+    return records.library().sx_decode_splits_bound(int(max_keys))
 
 
 @traced("attention_decode")
@@ -489,18 +469,11 @@ PAIR_GEMM_MIN_TOKENS = 1280
 
 def gemm_splits(tokens: int, features: int, k: int, sms: Optional[int] = None) -> int:
     """Into how many partial sums a small-batch product is cut along K.  A function of the
-    shape and of the device's SM count only: blocks of 128 weight rows alone cannot occupy the SMs when there are few of
-    them, so K is cut until about two blocks per SM exist (two fit), each with at least 8 K
-    blocks."""
-    if tokens > 64:
-        return 1
-    tiles = -(-features // 128)
-    k_blocks = -(-k // 64)
-    splits = max(1, min(2 * (sms if sms is not None else sm_count()) // tiles, k_blocks // 8))
-    if splits <= 1:
-        return 1
-    per_split = -(-k_blocks // splits)
-    return -(-k_blocks // per_split)
+    shape and of the device's SM count only: blocks of 128 weight rows alone cannot occupy the SMs when
+    there are few of them, so K is cut until about two blocks per SM exist (two fit), each with at least
+    8 K blocks.  Defined in csrc/step_exec.cu, where the step executor uses it too."""
+    return records.library().sx_gemm_splits(int(tokens), int(features), int(k), int(sms if sms is not None else sm_count()),
+                                            OWN_GEMM_MAX_TOKENS)
 
 
 @traced("gemm")
@@ -510,8 +483,8 @@ def linear(x: torch.Tensor, weight: torch.Tensor, bias: Optional[torch.Tensor] =
     """y = x @ weight^T (+ bias); weight is [out, in], row-major.
 
     float32: the FFMA kernel of this package, true 32-bit.  bfloat16: up to
-    ``OWN_GEMM_MAX_TOKENS`` rows the tcgen05 kernel of this package, above that cuBLAS through
-    torch (what the reference's engine calls for every projection,
+    ``OWN_GEMM_MAX_TOKENS`` rows the tcgen05 kernel of this package, above that cuBLAS
+    (:func:`library_product`: what the reference's engine calls for every projection,
     crates/sglang-kernel/src/cublas.rs:383-410); both accumulate in 32-bit.  ``out_dtype``
     float32 keeps the accumulator's precision (used for the logits).  With ``partial_ok`` the
     result may be float32 [parts, rows, out]: partial sums over K that the consumer adds in
@@ -537,12 +510,25 @@ def linear(x: torch.Tensor, weight: torch.Tensor, bias: Optional[torch.Tensor] =
                 add_bias(out[0], bias)
             return out
         out = gemm_bf16(x, weight, error_word, mode="f32" if out_dtype == torch.float32 else "bf16")
-    elif out_dtype == torch.float32:
-        out = torch.mm(x, weight.t(), out_dtype=torch.float32)
     else:
-        out = torch.mm(x, weight.t())
+        out = library_product(x, weight, torch.float32 if out_dtype == torch.float32 else torch.bfloat16)
     if bias is not None:
         add_bias(out, bias)
+    return out
+
+
+def library_product(x: torch.Tensor, weight: torch.Tensor, out_dtype: torch.dtype) -> torch.Tensor:
+    """y = x @ weight^T by cuBLAS (``cublasGemmEx``, bfloat16 operands, 32-bit accumulation to the end), the
+    call the reference's engine makes for every projection (crates/sglang-kernel/src/cublas.rs:383-410).  The
+    same call, through the same handle and scratch memory, takes the products of many rows inside the step
+    executor."""
+    records.ensure_cublas(x.device)
+    m, k = x.shape
+    n = weight.shape[0]
+    out = torch.empty((m, n), dtype=out_dtype, device=x.device)
+    lib = records.library()
+    _check(lib, lib.sx_cublas_product(_ptr(x), _ptr(weight), _ptr(out), m, n, k, x.stride(0), weight.stride(0), out.stride(0),
+                                      int(out_dtype == torch.float32), _stream()))
     return out
 
 

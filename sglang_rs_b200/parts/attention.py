@@ -95,6 +95,24 @@ class GroupedQueryAttention(Mixer):
         self.b_o = scale_to(tensors[n.o_bias], device) if n.o_bias else None
         self.position.load(tensors, device, dtype)
 
+    def native_record(self):
+        """This mixer for the step executor, or None if its position encoding is not of the kind the fused
+        kernel applies from a frequency table (an encoding that computes its angles in Python keeps the
+        part-by-part path)."""
+        from ..ops.records import SxAttention, linear_record
+        if self.w_qkv is None or not self.position.fused:
+            return None
+        rotary = self.position.fused_rotary()
+        if rotary is not None and (rotary.angles is not None or rotary.inv_freq is None):
+            return None
+        return SxAttention(
+            linear_record(self.w_qkv, self.b_qkv), linear_record(self.w_o, self.b_o),
+            None if self.q_norm is None else self.q_norm.data_ptr(), None if self.k_norm is None else self.k_norm.data_ptr(),
+            None if rotary is None else rotary.inv_freq.data_ptr(),
+            self.qk_norm_eps if self.qk_norm_eps is not None else 0.0, self.scale,
+            rotary.rotary_dim if rotary is not None else 0, int(rotary.interleaved) if rotary is not None else 0,
+            self.n_q, self.n_kv, self.d, self.window or 0)
+
     def forward(self, ctx, cache, x: torch.Tensor) -> torch.Tensor:
         batch = ctx.paged[cache.group]
         rows = x.shape[0]

@@ -41,6 +41,16 @@ class PreNormBlock(Part):
         for part in self.parts():
             part.load(tensors, device, dtype)
 
+    def native_record(self):
+        """This block for the step executor, if each of its parts has a record of the kind the executor's
+        pre-norm block is made of; else None, and the block runs part by part."""
+        from ..ops.records import SxAttention, SxBlock, SxGatedMlp, SxNorm
+        found = [part.native_record() if hasattr(part, "native_record") else None for part in self.parts()]
+        kinds = (SxNorm, SxAttention, SxNorm, SxGatedMlp)
+        if not all(isinstance(record, kind) for record, kind in zip(found, kinds)):
+            return None
+        return SxBlock(*found)
+
     def forward(self, ctx, cache, residual: torch.Tensor,
                 delta: Optional[torch.Tensor]) -> Tuple[torch.Tensor, torch.Tensor]:
         normed = self.input_norm.add_norm(residual, delta, ctx.dtype)

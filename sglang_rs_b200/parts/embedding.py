@@ -27,6 +27,10 @@ class TokenEmbedding(Part):
     def load(self, tensors: Mapping[str, torch.Tensor], device, dtype: torch.dtype) -> None:
         self.table = matrix_to(tensors[self.weight_name], device, dtype)
 
+    def native_record(self):
+        """The step executor reads the table itself; the record says only that there is one."""
+        return None if self.table is None else True
+
     def forward(self, ctx, token_ids: torch.Tensor) -> torch.Tensor:
         residual = torch.empty((token_ids.numel(), self.width), dtype=torch.float32, device=token_ids.device)
         ops.embedding(token_ids, self.table, residual, ctx.error_word)
@@ -50,6 +54,10 @@ class OutputHead(Part):
     def load(self, tensors: Mapping[str, torch.Tensor], device, dtype: torch.dtype) -> None:
         if self.weight_name:
             self.weight = matrix_to(tensors[self.weight_name], device, dtype)
+
+    def native_record(self):
+        weight = self.weight if self.weight_name else self.embedding.table
+        return None if weight is None else True
 
     def forward(self, ctx, normed: torch.Tensor) -> torch.Tensor:
         weight = self.weight if self.weight_name else self.embedding.table

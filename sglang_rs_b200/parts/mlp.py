@@ -44,6 +44,14 @@ class GatedMlp(FeedForward):
         self.w_gate_up = matrix_to(torch.cat([tensors[n.gate], tensors[n.up]], dim=0), device, dtype)
         self.w_down = matrix_to(tensors[n.down], device, dtype)
 
+    def native_record(self):
+        """This feed-forward for the step executor: the two stacked matrices, the inner width, the activation."""
+        from ..ops.records import SxGatedMlp, linear_record
+        if self.w_gate_up is None:
+            return None
+        return SxGatedMlp(linear_record(self.w_gate_up, None), linear_record(self.w_down, None), self.inner,
+                          ops.activation_code(self.activation))
+
     def forward(self, ctx, x: torch.Tensor) -> torch.Tensor:
         error_word = ctx.error_word if ctx is not None else None
         act = ops.gated_product(x, self.w_gate_up, self.inner, error_word, self.activation)

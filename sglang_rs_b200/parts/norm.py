@@ -28,6 +28,11 @@ class RmsNorm(Norm):
     def load(self, tensors: Mapping[str, torch.Tensor], device, dtype: torch.dtype) -> None:
         self.weight = scale_to(tensors[self.weight_name], device)
 
+    def native_record(self):
+        """This norm for the step executor: its scale, eps and width."""
+        from ..ops.records import SxNorm
+        return None if self.weight is None else SxNorm(self.weight.data_ptr(), self.eps, self.width)
+
     def add_norm(self, residual: torch.Tensor, delta: Optional[torch.Tensor], out_dtype: torch.dtype,
                  row_index: Optional[torch.Tensor] = None) -> torch.Tensor:
         """residual += delta (in place, unless rows are picked); returns norm(residual).

@@ -170,10 +170,11 @@ def max_live_of(trace) -> int:
 
 
 def run_in_process(folder: str, dtype: str, trace, max_tokens=None, page_size: int = 16, graphs: bool = True,
-                   radix: bool = False):
+                   radix: bool = False, native_step=None):
     from sglang_rs_b200.engine.replay import ReplaySession
     session = ReplaySession(folder, dtype, max_tokens if max_tokens is not None else max_tokens_of(trace), page_size,
-                            use_cuda_graphs=graphs, max_live=max(4, max_live_of(trace)), radix=radix)
+                            use_cuda_graphs=graphs, max_live=max(4, max_live_of(trace)), radix=radix,
+                            native_step=native_step)
     outputs = []
     session.page_owners = {}                 # (group, page id) -> requests that held it at some time
     for step in trace:

@@ -166,6 +166,24 @@ def test_replay_with_the_prefix_tree(tmp_path, dtype_name):
             assert err <= (2e-5 if dtype_name == "float32" else 2e-2), (rid, p, err)
 
 
+@pytest.mark.parametrize("dtype_name", list(DTYPES))
+@pytest.mark.parametrize("case", ["A", "C", "D", "F"])
+def test_a_step_in_one_native_call_equals_the_step_part_by_part(prepared, case, dtype_name):
+    """The step executor launches what the parts would launch one by one: the same kernels with the same
+    arguments, so the logits are equal bit for bit, in both dtypes, captured or not, on a trace that mixes
+    portions with decoded tokens (C has biases and one kv head, D the tensor-core kernels, F head_dim 18)."""
+    folder, requests, expected, page = prepared(case, dtype_name)
+    for trace, graphs in ((rh.trace_mixed(requests, seed=31), False), (rh.trace_tail_by_one(requests), True)):
+        native, session = rh.run_in_process(folder, dtype_name, trace, page_size=page, graphs=graphs, native_step=True)
+        assert session.model.native is not None
+        by_parts, other = rh.run_in_process(folder, dtype_name, trace, page_size=page, graphs=graphs, native_step=False)
+        assert other.model.native is None
+        for rid in by_parts:
+            for p, row in by_parts[rid].items():
+                assert np.array_equal(row, native[rid][p]), (case, dtype_name, graphs, rid, p)
+        check(native, expected, DTYPES[dtype_name][1], requests, f"{case}/{dtype_name}/native step")
+
+
 def test_trace_run_program(prepared, tmp_path):
     """The program itself, as a user calls it: steps on standard input, files out."""
     folder, requests, expected, page = prepared("A", "float32")
