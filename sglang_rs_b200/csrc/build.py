@@ -160,9 +160,11 @@ def set_pdl(on: bool) -> None:
 
 
 def load_library(name: str) -> ctypes.CDLL:
+    """The library of ``<name>.cu``.  ``SRB_LIBRARY_<NAME>`` may name a build of the same source made another
+    way (the host code built with sanitizers, for instance); it is loaded in place of the one built here."""
     library = _loaded.get(name)
     if library is None:
-        library = ctypes.CDLL(compile_library(name))
+        library = ctypes.CDLL(os.environ.get(f"SRB_LIBRARY_{name.upper()}") or compile_library(name))
         library.srb_last_error.restype = ctypes.c_char_p
         if hasattr(library, "srb_set_pdl"):
             library.srb_set_pdl(int(_pdl))
