@@ -168,74 +168,108 @@ __global__ void qk_norm_rope_kv_kernel(const T* __restrict__ qkv, const float* _
 
 
 // Many rows (256 and more), head_dim 128, rotation of the whole head in half-split pairs, the
-// projection in one tensor: one block per row, every warp takes several heads of the row and keeps a
-// head in registers (lane l holds elements 4l..4l+3, its rotation partner sits in lane l ^ 16), so a
-// head costs one load, one exchange and one store; v heads are copied as they are.  Same arithmetic
-// as the kernel above.
+// projection in one tensor: one block per row.  Half a warp takes a head: lane l of the half holds the
+// eight elements 8l..8l+7 (one 16-byte access in bfloat16, two in 32-bit), its rotation partner sits eight
+// lanes away.  A block's sixteen half-warps take sixteen heads per pass, and a thread asks for the data of
+// all its passes (up to ROW_PASSES) before it touches any of them, so that each SM has some hundred KB in
+// flight; the table of angles is computed while those loads travel.  v heads are copied as they are.
+// Same arithmetic as the kernel above, bit for bit: the sum of squares is added up in the order of that
+// kernel's warp reduction (four elements per lane there: this lane's two halves stand for two of its lanes).
 #define ROW_WARPS 8
-template <typename T>
-__device__ __forceinline__ float4 load_head4(const T* p) {
-  if (sizeof(T) == 2) {
-    const uint2 raw = *reinterpret_cast<const uint2*>(p);
-    const float2 a = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&raw.x));
-    const float2 b = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&raw.y));
-    return make_float4(a.x, a.y, b.x, b.y);
-  }
-  return *reinterpret_cast<const float4*>(p);
+#define ROW_PASSES 4
+struct Head8 { float v[8]; };
+template <typename T> struct Raw8;
+template <> struct Raw8<__nv_bfloat16> { uint4 a; };
+template <> struct Raw8<float> { float4 a, b; };
+__device__ __forceinline__ Raw8<__nv_bfloat16> load_raw8(const __nv_bfloat16* p) {
+  Raw8<__nv_bfloat16> r;
+  r.a = *reinterpret_cast<const uint4*>(p);
+  return r;
 }
-template <typename T>
-__device__ __forceinline__ void store_head4(T* p, float4 x) {
-  if (sizeof(T) == 2) {
-    uint2 raw;
-    *reinterpret_cast<__nv_bfloat162*>(&raw.x) = __floats2bfloat162_rn(x.x, x.y);
-    *reinterpret_cast<__nv_bfloat162*>(&raw.y) = __floats2bfloat162_rn(x.z, x.w);
-    *reinterpret_cast<uint2*>(p) = raw;
-  } else {
-    *reinterpret_cast<float4*>(p) = x;
-  }
+__device__ __forceinline__ Raw8<float> load_raw8(const float* p) {
+  Raw8<float> r;
+  r.a = *reinterpret_cast<const float4*>(p);
+  r.b = *reinterpret_cast<const float4*>(p + 4);
+  return r;
 }
-// norm (if a weight is given) and rotation of the four values this lane holds of one head
-__device__ __forceinline__ float4 norm_and_rotate(float4 x, bool has_norm, float4 w, float eps, bool rotate, float4 cs,
-                                                  float4 sn, bool first_half) {
+__device__ __forceinline__ Head8 widen8(const Raw8<__nv_bfloat16>& r) {
+  Head8 h;
+  const __nv_bfloat162* pairs = reinterpret_cast<const __nv_bfloat162*>(&r.a);
+#pragma unroll
+  for (int j = 0; j < 4; ++j) {
+    const float2 f = __bfloat1622float2(pairs[j]);
+    h.v[2 * j] = f.x;
+    h.v[2 * j + 1] = f.y;
+  }
+  return h;
+}
+__device__ __forceinline__ Head8 widen8(const Raw8<float>& r) {
+  Head8 h;
+  h.v[0] = r.a.x; h.v[1] = r.a.y; h.v[2] = r.a.z; h.v[3] = r.a.w;
+  h.v[4] = r.b.x; h.v[5] = r.b.y; h.v[6] = r.b.z; h.v[7] = r.b.w;
+  return h;
+}
+__device__ __forceinline__ void store8(__nv_bfloat16* p, const Head8& h) {
+  uint4 raw;
+  __nv_bfloat162* pairs = reinterpret_cast<__nv_bfloat162*>(&raw);
+#pragma unroll
+  for (int j = 0; j < 4; ++j) pairs[j] = __floats2bfloat162_rn(h.v[2 * j], h.v[2 * j + 1]);
+  *reinterpret_cast<uint4*>(p) = raw;
+}
+__device__ __forceinline__ void store8(float* p, const Head8& h) {
+  *reinterpret_cast<float4*>(p) = make_float4(h.v[0], h.v[1], h.v[2], h.v[3]);
+  *reinterpret_cast<float4*>(p + 4) = make_float4(h.v[4], h.v[5], h.v[6], h.v[7]);
+}
+__device__ __forceinline__ void store_raw8(__nv_bfloat16* p, const Raw8<__nv_bfloat16>& r) { *reinterpret_cast<uint4*>(p) = r.a; }
+__device__ __forceinline__ void store_raw8(float* p, const Raw8<float>& r) {
+  *reinterpret_cast<float4*>(p) = r.a;
+  *reinterpret_cast<float4*>(p + 4) = r.b;
+}
+
+// norm (if a weight is given) and rotation of the eight values this lane holds of one head; the sixteen lanes
+// of a half-warp hold the head, `first_half` says on which side of the rotation pairs this lane's values lie
+__device__ __forceinline__ Head8 norm_and_rotate8(Head8 x, bool has_norm, const float* w, float eps, bool rotate,
+                                                  const float* cs, const float* sn, bool first_half) {
+  // The other kernel sums four elements per lane over 32 lanes by a butterfly (16, 8, 4, 2, 1); here a lane's
+  // two quadruples are that kernel's lanes 2l and 2l + 1, so its first four exchanges become 8, 4, 2, 1 within
+  // the half-warp for each quadruple, and its last one is the sum of the two quadruples.  (The exchanges run
+  // whether or not this half's head has a norm: the two halves of a warp may differ in that.)
+  float lo = sum_squares4(make_float4(x.v[0], x.v[1], x.v[2], x.v[3]));
+  float hi = sum_squares4(make_float4(x.v[4], x.v[5], x.v[6], x.v[7]));
+#pragma unroll
+  for (int offset = 8; offset > 0; offset >>= 1) {
+    lo += __shfl_xor_sync(0xffffffffu, lo, offset);
+    hi += __shfl_xor_sync(0xffffffffu, hi, offset);
+  }
   if (has_norm) {
-    const float total = srb_warp_sum(sum_squares4(x));
-    const float inv = __frsqrt_rn(total * (1.0f / 128.0f) + eps);
-    x = make_float4(normed(x.x, inv, w.x), normed(x.y, inv, w.y), normed(x.z, inv, w.z), normed(x.w, inv, w.w));
+    const float inv = __frsqrt_rn((lo + hi) * (1.0f / 128.0f) + eps);
+#pragma unroll
+    for (int j = 0; j < 8; ++j) x.v[j] = normed(x.v[j], inv, w[j]);
   }
   if (rotate) {
-    float4 other;
-    other.x = __shfl_xor_sync(0xffffffffu, x.x, 16); other.y = __shfl_xor_sync(0xffffffffu, x.y, 16);
-    other.z = __shfl_xor_sync(0xffffffffu, x.z, 16); other.w = __shfl_xor_sync(0xffffffffu, x.w, 16);
-    if (first_half)
-      x = make_float4(rotate_first(x.x, other.x, cs.x, sn.x), rotate_first(x.y, other.y, cs.y, sn.y),
-                      rotate_first(x.z, other.z, cs.z, sn.z), rotate_first(x.w, other.w, cs.w, sn.w));
-    else
-      x = make_float4(rotate_second(other.x, x.x, cs.x, sn.x), rotate_second(other.y, x.y, cs.y, sn.y),
-                      rotate_second(other.z, x.z, cs.z, sn.z), rotate_second(other.w, x.w, cs.w, sn.w));
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+      const float other = __shfl_xor_sync(0xffffffffu, x.v[j], 8);
+      x.v[j] = first_half ? rotate_first(x.v[j], other, cs[j], sn[j]) : rotate_second(other, x.v[j], cs[j], sn[j]);
+    }
   }
   return x;
 }
 
 template <typename T>
-__global__ void __launch_bounds__(ROW_WARPS * 32)
+__global__ void __launch_bounds__(ROW_WARPS * 32, 3)
 qk_norm_rope_kv_row_kernel(const T* __restrict__ qkv, int qkv_stride, T* __restrict__ q_out, T* __restrict__ k_pool,
                            T* __restrict__ v_pool, const int* __restrict__ positions, const int* __restrict__ slots,
                            const float* __restrict__ q_norm, const float* __restrict__ k_norm, float eps,
                            const float* __restrict__ inv_freq, const float* __restrict__ angles, int n_q, int n_kv,
                            int page_size, int num_pages, int* error_word) {
-  constexpr int D = 128, HALF = 64;
+  constexpr int D = 128, HALF = 64, HEADS_PER_PASS = ROW_WARPS * 2;
   __shared__ __align__(16) float cos_table[HALF], sin_table[HALF];
   srb_launch_dependents();
-  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int lane = threadIdx.x & 31;
+  const int half_warp = threadIdx.x >> 4, l = lane & 15;      // this thread's head of a pass, its place in the head
   const int row = blockIdx.x;
   const bool rotate = inv_freq || angles;
-  if (threadIdx.x < HALF) {
-    if (angles) {
-      sincosf(angles[(size_t)row * HALF + threadIdx.x], &sin_table[threadIdx.x], &cos_table[threadIdx.x]);
-    } else if (inv_freq) {
-      sincosf((float)positions[row] * inv_freq[threadIdx.x], &sin_table[threadIdx.x], &cos_table[threadIdx.x]);
-    }
-  }
   int slot = 0;
   bool slot_ok = true;
   if (slots) {
@@ -243,46 +277,72 @@ qk_norm_rope_kv_row_kernel(const T* __restrict__ qkv, int qkv_stride, T* __restr
     slot_ok = slot >= 0 && slot < num_pages * page_size;
     if (!slot_ok && threadIdx.x == 0) atomicOr(error_word, SRB_FLAG_BAD_SLOT);
   }
+  const int heads = (slots && slot_ok) ? n_q + 2 * n_kv : n_q;
+  const bool first_half = l < 8;
+  const int pair0 = (l & 7) * 8;                               // the eight pairs this lane takes part in
   srb_grid_dependency_wait();
-  __syncthreads();
-  const int pair0 = (lane & 15) * 4;                      // the four pairs this lane takes part in
-  float4 cs = make_float4(1.f, 1.f, 1.f, 1.f), sn = make_float4(0.f, 0.f, 0.f, 0.f);
-  if (rotate) {
-    cs = *reinterpret_cast<const float4*>(cos_table + pair0);
-    sn = *reinterpret_cast<const float4*>(sin_table + pair0);
-  }
-  const bool first_half = lane < 16;
-  const float4 one = make_float4(1.f, 1.f, 1.f, 1.f);
-  const T* src = qkv + (size_t)row * qkv_stride + lane * 4;
-  // q heads
-  {
-    const float4 w = q_norm ? *reinterpret_cast<const float4*>(q_norm + lane * 4) : one;
-    T* dst = q_out + (size_t)row * n_q * D + lane * 4;
-#pragma unroll 2
-    for (int head = warp; head < n_q; head += ROW_WARPS)
-      store_head4(dst + head * D, norm_and_rotate(load_head4(src + head * D), q_norm != nullptr, w, eps, rotate, cs, sn,
-                                                  first_half));
-  }
-  if (!slots || !slot_ok) return;
+  const T* src = qkv + (size_t)row * qkv_stride + l * 8;
   // where the row's k and v go: element offset of kv head 0, and the step from one kv head to the next
-  const size_t kv_base = ((size_t)(slot / page_size) * n_kv * page_size + (slot % page_size)) * D + lane * 4;
+  const size_t kv_base = ((size_t)(slot / page_size) * n_kv * page_size + (slot % page_size)) * D + l * 8;
   const size_t kv_step = (size_t)page_size * D;
-  {
-    const float4 w = k_norm ? *reinterpret_cast<const float4*>(k_norm + lane * 4) : one;
-#pragma unroll 2
-    for (int head = warp; head < n_kv; head += ROW_WARPS)
-      store_head4(k_pool + kv_base + head * kv_step,
-                  norm_and_rotate(load_head4(src + (n_q + head) * D), k_norm != nullptr, w, eps, rotate, cs, sn,
-                                  first_half));
-  }
-  // v heads: no arithmetic, the values go to the pages as they are
-  for (int head = warp; head < n_kv; head += ROW_WARPS) {
-    const T* from = src + (n_q + n_kv + head) * D;
-    T* to = v_pool + kv_base + head * kv_step;
-    if (sizeof(T) == 2)
-      *reinterpret_cast<uint2*>(to) = *reinterpret_cast<const uint2*>(from);
-    else
-      *reinterpret_cast<float4*>(to) = *reinterpret_cast<const float4*>(from);
+  bool table_ready = false;
+  for (int first = 0; first < heads; first += HEADS_PER_PASS * ROW_PASSES) {
+    Raw8<T> raw[ROW_PASSES];
+#pragma unroll
+    for (int p = 0; p < ROW_PASSES; ++p) {
+      const int head = first + p * HEADS_PER_PASS + half_warp;
+      if (head < heads) raw[p] = load_raw8(src + (size_t)head * D);
+    }
+    if (!table_ready) {
+      // the angles of the row, while the loads above are on their way
+      if (threadIdx.x < HALF) {
+        if (angles) {
+          sincosf(angles[(size_t)row * HALF + threadIdx.x], &sin_table[threadIdx.x], &cos_table[threadIdx.x]);
+        } else if (inv_freq) {
+          sincosf((float)positions[row] * inv_freq[threadIdx.x], &sin_table[threadIdx.x], &cos_table[threadIdx.x]);
+        }
+      }
+      __syncthreads();
+      table_ready = true;
+    }
+    float cs[8], sn[8];
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+      cs[j] = rotate ? cos_table[pair0 + j] : 1.f;
+      sn[j] = rotate ? sin_table[pair0 + j] : 0.f;
+    }
+#pragma unroll
+    for (int p = 0; p < ROW_PASSES; ++p) {
+      const int head = first + p * HEADS_PER_PASS + half_warp;
+      // both halves of a warp run the exchanges together; a half whose head lies beyond the last one idles
+      const bool live = head < heads;
+      const bool is_q = head < n_q, is_k = !is_q && head < n_q + n_kv;
+      if (!__any_sync(0xffffffffu, live)) continue;
+      if (live && !is_q && !is_k) {                            // a v head: no arithmetic
+        store_raw8(v_pool + kv_base + (size_t)(head - n_q - n_kv) * kv_step, raw[p]);
+      }
+      const bool work = live && (is_q || is_k);
+      if (!__any_sync(0xffffffffu, work)) continue;
+      Head8 x;
+      if (work) {
+        x = widen8(raw[p]);
+      } else {
+#pragma unroll
+        for (int j = 0; j < 8; ++j) x.v[j] = 0.f;
+      }
+      // the exchanges inside use the full mask, so every lane of the warp calls it; a half without work carries zeros
+      const float* weight = (is_q || !live) ? q_norm : k_norm;   // a few hundred bytes that stay in the first-level cache
+      float w[8];
+#pragma unroll
+      for (int j = 0; j < 8; ++j) w[j] = weight ? weight[l * 8 + j] : 1.f;
+      x = norm_and_rotate8(x, weight != nullptr, w, eps, rotate, cs, sn, first_half);
+      if (work) {
+        if (is_q)
+          store8(q_out + ((size_t)row * n_q + head) * D + l * 8, x);
+        else
+          store8(k_pool + kv_base + (size_t)(head - n_q) * kv_step, x);
+      }
+    }
   }
 }
 
@@ -312,8 +372,8 @@ extern "C" int srb_qk_norm_rope_kv(const void* qkv, const float* qkv_parts, int 
   cudaStream_t s = (cudaStream_t)stream;
   const bool whole_head_pairs = !(inv_freq || angles) || (rotary_dim == head_dim && !interleaved);
   // (with fewer rows than about two per SM the kernel below, which spreads a row over blocks, is quicker)
-  if (rows >= 256 && head_dim == 128 && vector_ok && whole_head_pairs && num_parts == 0 &&
-      (((uintptr_t)q_norm | (uintptr_t)k_norm) & 15) == 0) {
+  const int row_bytes_ok = dtype == SRB_DTYPE_F32 || qkv_stride % 8 == 0;      // 16-byte accesses of eight values
+  if (rows >= 256 && head_dim == 128 && vector_ok && whole_head_pairs && num_parts == 0 && row_bytes_ok) {
     if (dtype == SRB_DTYPE_F32)
       SRB_CUDA_CALL(srb_launch(qk_norm_rope_kv_row_kernel<float>, dim3(rows), dim3(ROW_WARPS * 32), 0, s,
                                (const float*)qkv, qkv_stride, (float*)q_out, (float*)k_pool, (float*)v_pool, positions,

@@ -65,6 +65,10 @@ class NativeModel:
         r.blocks = ctypes.cast(self._blocks, ctypes.POINTER(SxBlock))
         self._step = SxStep()
         self._lib = library()
+        #: scratch memory between the kernels of a step: kept from step to step and grown when a step needs more
+        #: (steps run one after another on one stream).  A step that is being captured into a CUDA graph takes
+        #: memory of its own from the graph's pool instead, which then belongs to that graph's replays.
+        self._workspace: Optional[torch.Tensor] = None
 
     @classmethod
     def of(cls, model) -> Optional["NativeModel"]:
@@ -143,7 +147,13 @@ class NativeModel:
             keep.append(launches)
         step.workspace, step.workspace_bytes = None, 0
         need = self._lib.sx_workspace_bytes(ctypes.byref(self._record), ctypes.byref(step))
-        workspace = torch.empty(need + 256, dtype=torch.uint8, device=self.device)
+        if torch.cuda.is_current_stream_capturing():
+            workspace = torch.empty(need + 256, dtype=torch.uint8, device=self.device)
+        else:
+            if self._workspace is None or self._workspace.numel() < need + 256:
+                self._workspace = None                          # the old one goes back before the new one is asked for
+                self._workspace = torch.empty(int((need + 256) * 1.25), dtype=torch.uint8, device=self.device)
+            workspace = self._workspace
         address = workspace.data_ptr()
         step.workspace = (address + 255) // 256 * 256
         step.workspace_bytes = need

@@ -241,14 +241,14 @@ def test_qk_norm_rope_kv(dtype, n_q, n_kv, d, rot, inter):
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
-@pytest.mark.parametrize("use_parts", [False, True])
-def test_qk_norm_rope_kv_many_rows_of_128(dtype, use_parts):
+@pytest.mark.parametrize("use_parts,n_q,n_kv", [(False, 6, 2), (True, 6, 2), (False, 32, 8), (False, 64, 8), (False, 5, 5)])
+def test_qk_norm_rope_kv_many_rows_of_128(dtype, use_parts, n_q, n_kv):
     """Portions of 256 rows and more with head_dim 128 take a kernel that keeps a head in
     registers: against the plain formulas, and bit for bit against the kernel that the same rows
     take when they come a few at a time (a token's cache entry must not depend on the step it
     came in)."""
     g = torch.Generator().manual_seed(5)
-    rows, n_q, n_kv, d, page = 291, 6, 2, 128, 16
+    rows, d, page = 291, 128, 16        # 10, 48, 80 or 15 heads a row: less than a pass of 16, three passes, five, one
     pages = -(-rows // page) + 2
     width = (n_q + 2 * n_kv) * d
     qkv = torch.randn(rows, width, generator=g)
