@@ -23,6 +23,7 @@ and of a decode step (uncaptured, so that each kernel can be bracketed by events
 from __future__ import annotations
 
 import argparse
+import gc
 import json
 import os
 import statistics
@@ -395,6 +396,7 @@ def main() -> int:
         points[f"decode_b{args.batch}_ctx{end_context}_hbm_frac"] = round(
             decode_bytes(config, args.batch, far["context"]) / (far["step_ms"] * 1e-3) / 1e9 / peak["hbm_gbs"], 4)
         del engine
+        gc.collect()                                          # a model and its records for the step executor refer to each other
         torch.cuda.empty_cache()
         big_batch = 64 if args.shape != "qwen3-32b" else 32
         big = make_engine(big_batch, short, late)

@@ -261,8 +261,11 @@ __global__ void __launch_bounds__(ROW_WARPS * 32, 3)
 qk_norm_rope_kv_row_kernel(const T* __restrict__ qkv, int qkv_stride, T* __restrict__ q_out, T* __restrict__ k_pool,
                            T* __restrict__ v_pool, const int* __restrict__ positions, const int* __restrict__ slots,
                            const float* __restrict__ q_norm, const float* __restrict__ k_norm, float eps,
-                           const float* __restrict__ inv_freq, const float* __restrict__ angles, int n_q, int n_kv,
-                           int page_size, int num_pages, int* error_word) {
+                           const float* __restrict__ inv_freq, const float* __restrict__ angles,
+                           const float* __restrict__ cos_sin, int n_q, int n_kv, int page_size, int num_pages,
+                           int* error_word) {
+  // cos_sin: the rows' cosines and sines [rows, 128] (64 cosines, then 64 sines) computed once for the step by
+  // rope_table_kernel, or null: then this block computes its row's own, with the same arithmetic
   constexpr int D = 128, HALF = 64, HEADS_PER_PASS = ROW_WARPS * 2;
   __shared__ __align__(16) float cos_table[HALF], sin_table[HALF];
   srb_launch_dependents();
@@ -285,7 +288,21 @@ qk_norm_rope_kv_row_kernel(const T* __restrict__ qkv, int qkv_stride, T* __restr
   // where the row's k and v go: element offset of kv head 0, and the step from one kv head to the next
   const size_t kv_base = ((size_t)(slot / page_size) * n_kv * page_size + (slot % page_size)) * D + l * 8;
   const size_t kv_step = (size_t)page_size * D;
-  bool table_ready = false;
+  bool table_ready = !rotate;
+  float cs[8], sn[8];
+#pragma unroll
+  for (int j = 0; j < 8; ++j) {
+    cs[j] = 1.f;
+    sn[j] = 0.f;
+  }
+  if (rotate && cos_sin) {                                     // these loads travel together with the first heads'
+    const float* mine = cos_sin + (size_t)row * D + pair0;
+    const float4 c0 = *reinterpret_cast<const float4*>(mine), c1 = *reinterpret_cast<const float4*>(mine + 4);
+    const float4 s0 = *reinterpret_cast<const float4*>(mine + HALF), s1 = *reinterpret_cast<const float4*>(mine + HALF + 4);
+    cs[0] = c0.x; cs[1] = c0.y; cs[2] = c0.z; cs[3] = c0.w; cs[4] = c1.x; cs[5] = c1.y; cs[6] = c1.z; cs[7] = c1.w;
+    sn[0] = s0.x; sn[1] = s0.y; sn[2] = s0.z; sn[3] = s0.w; sn[4] = s1.x; sn[5] = s1.y; sn[6] = s1.z; sn[7] = s1.w;
+    table_ready = true;
+  }
   for (int first = 0; first < heads; first += HEADS_PER_PASS * ROW_PASSES) {
     Raw8<T> raw[ROW_PASSES];
 #pragma unroll
@@ -304,12 +321,11 @@ qk_norm_rope_kv_row_kernel(const T* __restrict__ qkv, int qkv_stride, T* __restr
       }
       __syncthreads();
       table_ready = true;
-    }
-    float cs[8], sn[8];
 #pragma unroll
-    for (int j = 0; j < 8; ++j) {
-      cs[j] = rotate ? cos_table[pair0 + j] : 1.f;
-      sn[j] = rotate ? sin_table[pair0 + j] : 0.f;
+      for (int j = 0; j < 8; ++j) {
+        cs[j] = cos_table[pair0 + j];
+        sn[j] = sin_table[pair0 + j];
+      }
     }
 #pragma unroll
     for (int p = 0; p < ROW_PASSES; ++p) {
@@ -346,6 +362,41 @@ qk_norm_rope_kv_row_kernel(const T* __restrict__ qkv, int qkv_stride, T* __restr
   }
 }
 
+// The cosines and sines of every row's angles, once for a step: out[r, 0..half) = cos, out[r, half..2 half) = sin
+// of float(positions[r]) * inv_freq[i] (or of angles[r, i]), the arithmetic of the kernels above.
+__global__ void rope_table_kernel(const int* __restrict__ positions, const float* __restrict__ inv_freq,
+                                  const float* __restrict__ angles, int rows, int half, float* __restrict__ out) {
+  const int i = blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= rows * half) return;
+  const int row = i / half, pair = i - row * half;
+  float sn, cs;
+  sincosf(angles ? angles[i] : (float)positions[row] * inv_freq[pair], &sn, &cs);
+  out[(size_t)row * 2 * half + pair] = cs;
+  out[(size_t)row * 2 * half + half + pair] = sn;
+}
+
+extern "C" int srb_rope_table(const int* positions, const float* inv_freq, const float* angles, int rows, int rotary_dim,
+                              float* out, void* stream) {
+  if (rows <= 0) return SRB_OK;
+  if (rotary_dim <= 0 || (rotary_dim & 1) || (!inv_freq && !angles) || !out)
+    SRB_FAIL("rope_table: an even rotary width, frequencies or angles, and an output are needed");
+  const int total = rows * (rotary_dim >> 1);
+  rope_table_kernel<<<(total + 255) / 256, 256, 0, (cudaStream_t)stream>>>(positions, inv_freq, angles, rows, rotary_dim >> 1, out);
+  SRB_LAUNCH_CHECK("rope_table");
+  return SRB_OK;
+}
+
+// How many rows a step must have for the kernel that can take the table of srb_rope_table (fewer rows compute
+// their angles inside the kernel, under the tail of the kernel ahead).
+extern "C" int srb_rope_table_min_rows() { return 256; }
+
+extern "C" int srb_qk_norm_rope_kv_table(const void* qkv, const float* qkv_parts, int num_parts, long long part_stride,
+                                         int qkv_stride, void* q_out, void* k_pool, void* v_pool, const int* positions,
+                                         const int* slots, const float* q_norm, const float* k_norm, float eps,
+                                         const float* inv_freq, const float* angles, const float* cos_sin, int rotary_dim,
+                                         int interleaved, int rows, int n_q, int n_kv, int head_dim, int page_size,
+                                         int num_pages, int* error_word, int dtype, void* stream);
+
 // `slots` may be null: then only the q heads are processed (a layer that reads another
 // layer's cache writes nothing).
 extern "C" int srb_qk_norm_rope_kv(const void* qkv, const float* qkv_parts, int num_parts, long long part_stride,
@@ -355,6 +406,19 @@ extern "C" int srb_qk_norm_rope_kv(const void* qkv, const float* qkv_parts, int 
                                    int rotary_dim,
                                    int interleaved, int rows, int n_q, int n_kv, int head_dim, int page_size,
                                    int num_pages, int* error_word, int dtype, void* stream) {
+  return srb_qk_norm_rope_kv_table(qkv, qkv_parts, num_parts, part_stride, qkv_stride, q_out, k_pool, v_pool, positions,
+                                   slots, q_norm, k_norm, eps, inv_freq, angles, nullptr, rotary_dim, interleaved, rows, n_q,
+                                   n_kv, head_dim, page_size, num_pages, error_word, dtype, stream);
+}
+
+// The same with `cos_sin`: the table of srb_rope_table for these rows (float [rows, rotary_dim], 16-byte aligned),
+// or null.  Only the kernel for many rows reads it; the values are those the kernels compute themselves.
+extern "C" int srb_qk_norm_rope_kv_table(const void* qkv, const float* qkv_parts, int num_parts, long long part_stride,
+                                         int qkv_stride, void* q_out, void* k_pool, void* v_pool, const int* positions,
+                                         const int* slots, const float* q_norm, const float* k_norm, float eps,
+                                         const float* inv_freq, const float* angles, const float* cos_sin, int rotary_dim,
+                                         int interleaved, int rows, int n_q, int n_kv, int head_dim, int page_size,
+                                         int num_pages, int* error_word, int dtype, void* stream) {
   if (rows <= 0) return SRB_OK;
   if (n_q <= 0 || n_kv <= 0 || head_dim <= 0 || page_size <= 0)
     SRB_FAIL("qk_norm_rope_kv: head counts, head_dim and page size must be positive");
@@ -373,17 +437,18 @@ extern "C" int srb_qk_norm_rope_kv(const void* qkv, const float* qkv_parts, int 
   const bool whole_head_pairs = !(inv_freq || angles) || (rotary_dim == head_dim && !interleaved);
   // (with fewer rows than about two per SM the kernel below, which spreads a row over blocks, is quicker)
   const int row_bytes_ok = dtype == SRB_DTYPE_F32 || qkv_stride % 8 == 0;      // 16-byte accesses of eight values
-  if (rows >= 256 && head_dim == 128 && vector_ok && whole_head_pairs && num_parts == 0 && row_bytes_ok) {
+  if (rows >= srb_rope_table_min_rows() && head_dim == 128 && vector_ok && whole_head_pairs && num_parts == 0 && row_bytes_ok) {
+    const float* table = (cos_sin && (((uintptr_t)cos_sin) & 15) == 0) ? cos_sin : nullptr;
     if (dtype == SRB_DTYPE_F32)
       SRB_CUDA_CALL(srb_launch(qk_norm_rope_kv_row_kernel<float>, dim3(rows), dim3(ROW_WARPS * 32), 0, s,
                                (const float*)qkv, qkv_stride, (float*)q_out, (float*)k_pool, (float*)v_pool, positions,
-                               slots, q_norm, k_norm, eps, inv_freq, angles, n_q, n_kv, page_size, num_pages,
+                               slots, q_norm, k_norm, eps, inv_freq, angles, table, n_q, n_kv, page_size, num_pages,
                                error_word));
     else if (dtype == SRB_DTYPE_BF16)
       SRB_CUDA_CALL(srb_launch(qk_norm_rope_kv_row_kernel<__nv_bfloat16>, dim3(rows), dim3(ROW_WARPS * 32), 0, s,
                                (const __nv_bfloat16*)qkv, qkv_stride, (__nv_bfloat16*)q_out, (__nv_bfloat16*)k_pool,
-                               (__nv_bfloat16*)v_pool, positions, slots, q_norm, k_norm, eps, inv_freq, angles, n_q, n_kv,
-                               page_size, num_pages, error_word));
+                               (__nv_bfloat16*)v_pool, positions, slots, q_norm, k_norm, eps, inv_freq, angles, table, n_q,
+                               n_kv, page_size, num_pages, error_word));
     else
       SRB_FAIL("qk_norm_rope_kv: unknown dtype %d", dtype);
     SRB_LAUNCH_CHECK("qk_norm_rope_kv_row");

@@ -193,8 +193,13 @@ extern "C" int sx_cublas_product(const void* x, const void* w, void* y, int m, i
 static inline long long aligned(long long bytes) { return (bytes + 255) / 256 * 256; }
 
 struct Layout {
-  long long residual, normed, qkv, q, attended, delta, activation, gate_up, final_normed, total;
+  long long residual, normed, qkv, q, attended, delta, activation, gate_up, final_normed, rope_table, total;
 };
+
+// From this many rows on the rows' cosines and sines are computed once per step (and per table of frequencies)
+// and handed to the rope kernel for many rows; fewer rows compute them inside the kernel, under the tail of
+// the kernel ahead.
+#define SX_ROPE_TABLE_MIN_ROWS 256
 
 static long long product_bytes(const SxStep& step, const SxLinear& linear, int rows, int element, bool partial_ok) {
   long long bytes = (long long)rows * linear.out_features * element;
@@ -207,9 +212,11 @@ static long long product_bytes(const SxStep& step, const SxLinear& linear, int r
 
 static Layout layout_of(const SxModel& model, const SxStep& step) {
   const int rows = step.rows, element = model.dtype == SRB_DTYPE_F32 ? 4 : 2;
-  long long qkv = 0, q = 0, delta = 0, activation = 0, gate_up = 0;
+  long long qkv = 0, q = 0, delta = 0, activation = 0, gate_up = 0, rope_table = 0;
   for (int b = 0; b < model.num_blocks; ++b) {
     const SxBlock& block = model.blocks[b];
+    if (rows >= SX_ROPE_TABLE_MIN_ROWS && block.mixer.inv_freq)
+      rope_table = std::max(rope_table, (long long)rows * block.mixer.rotary_dim * 4);
     qkv = std::max(qkv, product_bytes(step, block.mixer.qkv, rows, element, true));
     q = std::max(q, (long long)rows * block.mixer.n_q * block.mixer.head_dim * element);
     delta = std::max(delta, product_bytes(step, block.mixer.o, rows, element, true));
@@ -229,6 +236,7 @@ static Layout layout_of(const SxModel& model, const SxStep& step) {
   l.activation = take(activation);
   l.gate_up = take(gate_up);
   l.final_normed = take((long long)std::max(step.num_wanted, 1) * model.hidden * element);
+  l.rope_table = take(rope_table);
   l.total = at;
   return l;
 }
@@ -248,6 +256,8 @@ struct Run {
   const SxStep& step;
   cudaStream_t stream;
   int launches = 0;
+  const float* table_of = nullptr;       // the frequencies whose table of cosines and sines the workspace holds
+  int table_width = 0;
   int element() const { return model.dtype == SRB_DTYPE_F32 ? 4 : 2; }
 
   // y = x w^T (+ bias) into `out` (room for partial sums included when partial_ok)
@@ -299,10 +309,20 @@ struct Run {
     void* q = base + l.q;
     void* out = base + l.attended;
     const long long width = (long long)a.qkv.out_features;
+    const float* table = nullptr;
+    if (rows >= SX_ROPE_TABLE_MIN_ROWS && a.inv_freq && kernels.rope_table) {
+      // every layer of a model usually turns by the same frequencies: the table is made for the first of them
+      table = (const float*)(base + l.rope_table);
+      if (table_of != a.inv_freq || table_width != a.rotary_dim) {
+        SX_KERNEL(rope_table, (step.positions, a.inv_freq, nullptr, rows, a.rotary_dim, (float*)(base + l.rope_table), stream));
+        table_of = a.inv_freq;
+        table_width = a.rotary_dim;
+      }
+    }
     SX_KERNEL(qk_norm_rope_kv,
               (qkv.whole, qkv.parts, qkv.num_parts, qkv.part_stride, (int)width, q, call.writable ? call.k_pool : nullptr,
                call.writable ? call.v_pool : nullptr, step.positions, call.writable ? group.slots : nullptr, a.q_norm, a.k_norm,
-               a.qk_eps, a.inv_freq, nullptr, a.inv_freq ? a.rotary_dim : 0, a.interleaved, rows, a.n_q, a.n_kv, a.head_dim,
+               a.qk_eps, a.inv_freq, nullptr, table, a.inv_freq ? a.rotary_dim : 0, a.interleaved, rows, a.n_q, a.n_kv, a.head_dim,
                call.writable ? call.page_size : 1, call.writable ? call.num_pages : 1, step.error_word, model.dtype, stream));
     const bool bf16 = model.dtype == SRB_DTYPE_BF16;
     const bool heads_ok = a.n_kv > 0 && a.n_q % a.n_kv == 0 && (a.head_dim == 64 || a.head_dim == 128);

@@ -122,9 +122,11 @@ typedef struct SxKernels {
   int (*gemm_bf16_pair)(const void*, const void*, void*, int, int, int, int, int, int, int, int, int, int, int*, void*);
   SxLastError gemm_bf16_pair_error;
   int (*qk_norm_rope_kv)(const void*, const float*, int, long long, int, void*, void*, void*, const int*, const int*,
-                         const float*, const float*, float, const float*, const float*, int, int, int, int, int, int, int, int,
-                         int*, int, void*);
+                         const float*, const float*, float, const float*, const float*, const float*, int, int, int, int, int,
+                         int, int, int, int*, int, void*);                    // srb_qk_norm_rope_kv_table
   SxLastError qk_norm_rope_kv_error;
+  int (*rope_table)(const int*, const float*, const float*, int, int, float*, void*);
+  SxLastError rope_table_error;
   int (*paged_attention)(const void*, const void*, const void*, void*, float*, float*, const int*, const int*, const int*, int,
                          int, int, int, int, int, int, int, int, int, float, int*, int, void*);
   SxLastError paged_attention_error;

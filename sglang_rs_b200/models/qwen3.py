@@ -36,6 +36,9 @@ def build_qwen3(config: Qwen3Config) -> DecoderModel:
 
 def _build(config: Qwen3Config) -> DecoderModel:
     embedding = TokenEmbedding(config.vocab_size, config.hidden_size, "model.embed_tokens.weight")
+    # one encoding for all layers: its table of frequencies is a constant of the model, and layers that share it
+    # share, within a step, the cosines and sines computed from it
+    rotary = RotaryEncoding(config.head_dim, config.rope_theta)
     layers = []
     for index in range(config.num_hidden_layers):
         prefix = f"model.layers.{index}"
@@ -48,7 +51,7 @@ def _build(config: Qwen3Config) -> DecoderModel:
         mixer = GroupedQueryAttention(
             config.hidden_size, config.num_attention_heads, config.num_key_value_heads, config.head_dim,
             scale=1.0 / math.sqrt(config.head_dim),
-            position=RotaryEncoding(config.head_dim, config.rope_theta),
+            position=rotary,
             names=names, qk_norm_eps=config.rms_norm_eps, window=None)
         feed_forward = GatedMlp(
             config.hidden_size, config.intermediate_size, config.hidden_act,

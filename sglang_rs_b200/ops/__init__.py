@@ -241,7 +241,8 @@ def qk_norm_rope_kv(qkv: torch.Tensor, q_out: torch.Tensor, k_pool: Optional[tor
                     v_pool: Optional[torch.Tensor], positions: torch.Tensor, slots: Optional[torch.Tensor],
                     q_norm: Optional[torch.Tensor], k_norm: Optional[torch.Tensor], eps: float,
                     inv_freq: Optional[torch.Tensor], rotary_dim: int, interleaved: bool, n_q: int, n_kv: int,
-                    head_dim: int, error_word: torch.Tensor, angles: Optional[torch.Tensor] = None) -> None:
+                    head_dim: int, error_word: torch.Tensor, angles: Optional[torch.Tensor] = None,
+                    cos_sin: Optional[torch.Tensor] = None) -> None:
     """Per-head norm of q and k, rotation of q and k, q to ``q_out``, k and v into the pages.
 
     ``qkv`` is [rows, >= (n_q + 2 n_kv) head_dim] with q heads, k heads, v heads in that order,
@@ -249,7 +250,8 @@ def qk_norm_rope_kv(qkv: torch.Tensor, q_out: torch.Tensor, k_pool: Optional[tor
     pools are [pages, n_kv, page_size, head_dim]; ``slots[r]`` = page * page_size + offset.
     With ``slots`` None nothing is written to the pages.  The rotation takes its angles as
     ``positions[r] * inv_freq[i]`` or, if ``angles`` (float32 [rows, rotary_dim / 2]) is given,
-    from there."""
+    from there.  ``cos_sin``: the table of :func:`rope_table` for these rows; the kernel for many rows
+    then reads the cosines and sines instead of computing them (the same values)."""
     _need(qkv, "qkv"); _need(q_out, "q_out"); _need(positions, "positions", torch.int32)
     if angles is not None:
         _need(angles, "angles", torch.float32)
@@ -281,12 +283,29 @@ def qk_norm_rope_kv(qkv: torch.Tensor, q_out: torch.Tensor, k_pool: Optional[tor
         _need(inv_freq, "inv_freq", torch.float32)
         if inv_freq.numel() != rotary_dim // 2:
             raise KernelError("qk_norm_rope_kv: inv_freq must have rotary_dim / 2 elements")
+    if cos_sin is not None:
+        _need(cos_sin, "cos_sin", torch.float32)
+        if cos_sin.shape != (rows, rotary_dim):
+            raise KernelError("qk_norm_rope_kv: cos_sin must be [rows, rotary_dim]")
     lib = load_library("rope_kv")
-    _check(lib, lib.srb_qk_norm_rope_kv(
+    _check(lib, lib.srb_qk_norm_rope_kv_table(
         _ptr(whole), _ptr(parts), num_parts, ctypes.c_longlong(part_stride), qkv.stride(-2), _ptr(q_out), _ptr(k_pool),
         _ptr(v_pool), _ptr(positions), _ptr(slots), _ptr(q_norm), _ptr(k_norm), ctypes.c_float(eps), _ptr(inv_freq),
-        _ptr(angles), rotary_dim, int(interleaved), rows, n_q, n_kv, head_dim, page_size, num_pages, _ptr(error_word),
-        dtype_code(q_out.dtype), _stream()))
+        _ptr(angles), _ptr(cos_sin), rotary_dim, int(interleaved), rows, n_q, n_kv, head_dim, page_size, num_pages,
+        _ptr(error_word), dtype_code(q_out.dtype), _stream()))
+
+
+@traced("rope_kv")
+def rope_table(positions: torch.Tensor, inv_freq: Optional[torch.Tensor], rotary_dim: int,
+               angles: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """float32 [rows, rotary_dim]: per row the cosines, then the sines, of ``positions[r] * inv_freq[i]`` (or of
+    ``angles[r, i]``), computed once for a step; the step executor hands it to the rope kernel of every layer."""
+    _need(positions, "positions", torch.int32)
+    rows = positions.numel()
+    out = torch.empty((rows, rotary_dim), dtype=torch.float32, device=positions.device)
+    lib = load_library("rope_kv")
+    _check(lib, lib.srb_rope_table(_ptr(positions), _ptr(inv_freq), _ptr(angles), rows, rotary_dim, _ptr(out), _stream()))
+    return out
 
 
 def attention_scratch_sizes(rows: int, n_q: int, head_dim: int, max_splits: int) -> tuple[int, int]:

@@ -84,7 +84,8 @@ KERNEL_SLOTS = (
     ("embedding", "elementwise", "srb_embedding"), ("add_rmsnorm", "elementwise", "srb_add_rmsnorm"),
     ("gated_mul", "elementwise", "srb_gated_mul"), ("add_bias", "elementwise", "srb_add_bias"),
     ("gemm_f32", "gemm_f32", "srb_gemm_f32"), ("gemm_bf16", "gemm_bf16", "srb_gemm_bf16"),
-    ("gemm_bf16_pair", "gemm_bf16_pair", "srb_gemm_bf16_pair"), ("qk_norm_rope_kv", "rope_kv", "srb_qk_norm_rope_kv"),
+    ("gemm_bf16_pair", "gemm_bf16_pair", "srb_gemm_bf16_pair"), ("qk_norm_rope_kv", "rope_kv", "srb_qk_norm_rope_kv_table"),
+    ("rope_table", "rope_kv", "srb_rope_table"),
     ("paged_attention", "attention", "srb_paged_attention"), ("decode_attention", "attention_decode", "srb_decode_attention"),
     ("prefill_attention", "attention_prefill", "srb_prefill_attention"),
     ("prefill_attention_tc", "attention_prefill_tc", "srb_prefill_attention_tc"),

@@ -49,7 +49,9 @@ class RotaryEncoding(PositionEncoding):
         return torch.pow(torch.tensor(self.theta, dtype=torch.float64), -2.0 * pair / self.rotary_dim).to(torch.float32)
 
     def load(self, tensors, device, dtype) -> None:
-        self._table = FusedRotary(self.inverse_frequencies().to(device), self.rotary_dim, self.interleaved)
+        # an encoding that several layers share is loaded once: they then share one table on the device
+        if self._table is None or self._table.inv_freq.device != torch.device(device):
+            self._table = FusedRotary(self.inverse_frequencies().to(device), self.rotary_dim, self.interleaved)
 
     def fused_rotary(self) -> FusedRotary:
         return self._table

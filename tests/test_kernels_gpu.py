@@ -263,13 +263,14 @@ def test_qk_norm_rope_kv_many_rows_of_128(dtype, use_parts, n_q, n_kv):
     else:
         source, seen = qkv.to(DEV, dtype), rounded(qkv, dtype)
 
-    def run(lo, hi):
+    def run(lo, hi, table=False):
         k_pool = torch.zeros(pages, n_kv, page, d, device=DEV, dtype=dtype)
         v_pool = torch.zeros_like(k_pool)
         q_out = torch.zeros(hi - lo, n_q, d, device=DEV, dtype=dtype)
         src = source[:, lo:hi].contiguous() if use_parts else source[lo:hi]
+        cos_sin = ops.rope_table(positions[lo:hi].to(DEV), inv.to(DEV), d) if table else None
         ops.qk_norm_rope_kv(src, q_out, k_pool, v_pool, positions[lo:hi].to(DEV), slots[lo:hi].to(DEV), qn.to(DEV),
-                            kn.to(DEV), 1e-6, inv.to(DEV), d, False, n_q, n_kv, d, word)
+                            kn.to(DEV), 1e-6, inv.to(DEV), d, False, n_q, n_kv, d, word, cos_sin=cos_sin)
         return q_out, k_pool, v_pool
 
     q_out, k_pool, v_pool = run(0, rows)
@@ -281,6 +282,12 @@ def test_qk_norm_rope_kv_many_rows_of_128(dtype, use_parts, n_q, n_kv):
     close(q_out, q, dtype, "q")
     close(k_pool.cpu()[slots.long() // page, :, slots.long() % page], k, dtype, "k")
     close(v_pool.cpu()[slots.long() // page, :, slots.long() % page], v, dtype, "v")
+    # with the cosines and sines computed once for all rows (as the step executor does): the same bits
+    q_table, k_table, v_table = run(0, rows, table=True)
+    assert torch.equal(q_table, q_out) and torch.equal(k_table, k_pool) and torch.equal(v_table, v_pool)
+    table = ops.rope_table(positions.to(DEV), inv.to(DEV), d).cpu().double()
+    angle = positions.double()[:, None] * inv.double()[None, :]
+    assert float((table[:, :d // 2] - torch.cos(angle)).abs().max()) < 1e-3      # float32 angles of up to 5,000
     # the same rows, 37 at a time, through the kernel for few rows
     for lo in range(0, rows, 37):
         hi = min(rows, lo + 37)
