@@ -227,9 +227,9 @@ __device__ __forceinline__ void store_raw8(float* p, const Raw8<float>& r) {
 }
 
 // norm (if a weight is given) and rotation of the eight values this lane holds of one head; the sixteen lanes
-// of a half-warp hold the head, `first_half` says on which side of the rotation pairs this lane's values lie
+// of a half-warp hold the head; `sn` holds the sines with the sign of this lane's side of the rotation pairs
 __device__ __forceinline__ Head8 norm_and_rotate8(Head8 x, bool has_norm, const float* w, float eps, bool rotate,
-                                                  const float* cs, const float* sn, bool first_half) {
+                                                  const float* cs, const float* sn) {
   // The other kernel sums four elements per lane over 32 lanes by a butterfly (16, 8, 4, 2, 1); here a lane's
   // two quadruples are that kernel's lanes 2l and 2l + 1, so its first four exchanges become 8, 4, 2, 1 within
   // the half-warp for each quadruple, and its last one is the sum of the two quadruples.  (The exchanges run
@@ -247,10 +247,12 @@ __device__ __forceinline__ Head8 norm_and_rotate8(Head8 x, bool has_norm, const 
     for (int j = 0; j < 8; ++j) x.v[j] = normed(x.v[j], inv, w[j]);
   }
   if (rotate) {
+    // rotate_first(a, b) = a cos - b sin for the first of a pair, rotate_second(a, b) = b cos + a sin for the second:
+    // with the partner's value in `other` both are own * cos + other * (-+ sin), and `sn` comes with that sign
 #pragma unroll
     for (int j = 0; j < 8; ++j) {
       const float other = __shfl_xor_sync(0xffffffffu, x.v[j], 8);
-      x.v[j] = first_half ? rotate_first(x.v[j], other, cs[j], sn[j]) : rotate_second(other, x.v[j], cs[j], sn[j]);
+      x.v[j] = __fmaf_rn(x.v[j], cs[j], __fmul_rn(other, sn[j]));
     }
   }
   return x;
@@ -268,7 +270,10 @@ qk_norm_rope_kv_row_kernel(const T* __restrict__ qkv, int qkv_stride, T* __restr
   // rope_table_kernel, or null: then this block computes its row's own, with the same arithmetic
   constexpr int D = 128, HALF = 64, HEADS_PER_PASS = ROW_WARPS * 2;
   __shared__ __align__(16) float cos_table[HALF], sin_table[HALF];
+  __shared__ __align__(16) float norm_weights[2][D];          // of q heads, of k heads (ones where there is no norm)
   srb_launch_dependents();
+  norm_weights[threadIdx.x >> 7][threadIdx.x & 127] =
+      (threadIdx.x < D ? q_norm : k_norm) ? (threadIdx.x < D ? q_norm : k_norm)[threadIdx.x & 127] : 1.f;
   const int lane = threadIdx.x & 31;
   const int half_warp = threadIdx.x >> 4, l = lane & 15;      // this thread's head of a pass, its place in the head
   const int row = blockIdx.x;
@@ -301,8 +306,13 @@ qk_norm_rope_kv_row_kernel(const T* __restrict__ qkv, int qkv_stride, T* __restr
     const float4 s0 = *reinterpret_cast<const float4*>(mine + HALF), s1 = *reinterpret_cast<const float4*>(mine + HALF + 4);
     cs[0] = c0.x; cs[1] = c0.y; cs[2] = c0.z; cs[3] = c0.w; cs[4] = c1.x; cs[5] = c1.y; cs[6] = c1.z; cs[7] = c1.w;
     sn[0] = s0.x; sn[1] = s0.y; sn[2] = s0.z; sn[3] = s0.w; sn[4] = s1.x; sn[5] = s1.y; sn[6] = s1.z; sn[7] = s1.w;
+    if (first_half) {
+#pragma unroll
+      for (int j = 0; j < 8; ++j) sn[j] = -sn[j];
+    }
     table_ready = true;
   }
+  bool synced = false;
   for (int first = 0; first < heads; first += HEADS_PER_PASS * ROW_PASSES) {
     Raw8<T> raw[ROW_PASSES];
 #pragma unroll
@@ -310,22 +320,25 @@ qk_norm_rope_kv_row_kernel(const T* __restrict__ qkv, int qkv_stride, T* __restr
       const int head = first + p * HEADS_PER_PASS + half_warp;
       if (head < heads) raw[p] = load_raw8(src + (size_t)head * D);
     }
-    if (!table_ready) {
-      // the angles of the row, while the loads above are on their way
-      if (threadIdx.x < HALF) {
+    if (!synced) {
+      // while the loads above are on their way: the angles of the row, unless the step brought their table
+      if (!table_ready && threadIdx.x < HALF) {
         if (angles) {
           sincosf(angles[(size_t)row * HALF + threadIdx.x], &sin_table[threadIdx.x], &cos_table[threadIdx.x]);
         } else if (inv_freq) {
           sincosf((float)positions[row] * inv_freq[threadIdx.x], &sin_table[threadIdx.x], &cos_table[threadIdx.x]);
         }
       }
-      __syncthreads();
-      table_ready = true;
+      __syncthreads();                                         // the norm weights and the angles are in shared memory
+      if (!table_ready) {
 #pragma unroll
-      for (int j = 0; j < 8; ++j) {
-        cs[j] = cos_table[pair0 + j];
-        sn[j] = sin_table[pair0 + j];
+        for (int j = 0; j < 8; ++j) {
+          cs[j] = cos_table[pair0 + j];
+          sn[j] = first_half ? -sin_table[pair0 + j] : sin_table[pair0 + j];
+        }
+        table_ready = true;
       }
+      synced = true;
     }
 #pragma unroll
     for (int p = 0; p < ROW_PASSES; ++p) {
@@ -347,11 +360,11 @@ qk_norm_rope_kv_row_kernel(const T* __restrict__ qkv, int qkv_stride, T* __restr
         for (int j = 0; j < 8; ++j) x.v[j] = 0.f;
       }
       // the exchanges inside use the full mask, so every lane of the warp calls it; a half without work carries zeros
-      const float* weight = (is_q || !live) ? q_norm : k_norm;   // a few hundred bytes that stay in the first-level cache
-      float w[8];
-#pragma unroll
-      for (int j = 0; j < 8; ++j) w[j] = weight ? weight[l * 8 + j] : 1.f;
-      x = norm_and_rotate8(x, weight != nullptr, w, eps, rotate, cs, sn, first_half);
+      const bool q_side = is_q || !live;
+      const float4 w0 = *reinterpret_cast<const float4*>(&norm_weights[q_side ? 0 : 1][l * 8]);
+      const float4 w1 = *reinterpret_cast<const float4*>(&norm_weights[q_side ? 0 : 1][l * 8 + 4]);
+      const float w[8] = {w0.x, w0.y, w0.z, w0.w, w1.x, w1.y, w1.z, w1.w};
+      x = norm_and_rotate8(x, (q_side ? q_norm : k_norm) != nullptr, w, eps, rotate, cs, sn);
       if (work) {
         if (is_q)
           store8(q_out + ((size_t)row * n_q + head) * D + l * 8, x);
