@@ -16,7 +16,9 @@ output lengths uniform in [16, 512], portions of 2,048 tokens) and prints total 
 second, the time to the first token and the rows per step.  ``--mode compare-cublas`` times every product
 of a layer and the logits product at 1, 8, 64 and 2,048 rows, the engine's own path beside ``torch.mm``
 (cuBLAS) of the same shape.  ``--mode kernels`` prints the device time per kernel class of a prefill step
-and of a decode step (uncaptured, so that each kernel can be bracketed by events).
+and of a decode step (uncaptured, so that each kernel can be bracketed by events).  ``--mode ablate`` times the
+captured decode step with one kind of kernel left out at a time (the step then computes nothing of use): what
+each kind costs inside the graph, where kernels overlap their neighbours.
 
 ``--shape`` picks the layer sizes (BASELINE.json configs[2], [3], [4]); every mode takes it.
 """
@@ -149,7 +151,7 @@ def main() -> int:
     parser.add_argument("--warmup", type=int, default=3)
     parser.add_argument("--impl", default="ours", choices=("ours", "reference"))
     parser.add_argument("--shape", default="qwen3-8b", choices=sorted(SHAPES))
-    parser.add_argument("--mode", default="decode", choices=("decode", "serve", "compare-cublas", "kernels"))
+    parser.add_argument("--mode", default="decode", choices=("decode", "serve", "compare-cublas", "kernels", "ablate"))
     parser.add_argument("--layers", type=int, default=None, help="fewer than the shape has, only where memory or time needs it")
     parser.add_argument("--batch", type=int, default=8)
     parser.add_argument("--context", type=int, default=2048, help="tokens each request holds when decoding starts")
@@ -342,6 +344,27 @@ def main() -> int:
         return serve(args, config, peak, shape_note, warmup)
     if args.mode == "kernels":
         return kernel_classes(args, config, make_engine, prompts, shape_note, warmup)
+    if args.mode == "ablate":
+        from sglang_rs_b200.ops import records
+        engine = make_engine(args.batch, args.steps, args.context)
+        steps = min(args.steps, 32)
+        times = {}
+        for name, bit in [("nothing", 0), *records.SKIP_BITS.items()]:
+            records.skip = bit
+            engine.runner.graphs.captured.clear()                # the choice is made when a step is captured
+            try:
+                times[name] = decode_run(engine, args.batch, steps, args.context, sample_clocks=False, entry_point=False)["step_ms"]
+            finally:
+                records.skip = 0
+            engine.runner.error_word.zero_()
+        whole = times.pop("nothing")
+        per_layer = {name: round((whole - ms) * 1e3 / (1 if name == "head" else layers), 2) for name, ms in times.items()}
+        print(json.dumps({"mode": "ablate", "config": {**shape_note, "global_batch": args.batch, "seq_len": args.context},
+                          "step_ms": round(whole, 4), "us_per_layer_with_all_kernels": round(whole * 1e3 / layers, 2),
+                          "us_saved_per_layer_by_leaving_out": per_layer,
+                          "note": "captured decode steps; 'head' is per step, not per layer; a kernel's saving is what it "
+                                  "costs beyond what its neighbours hide"}))
+        return 0
 
     short = min(args.steps, 32)
     end_context = SHAPES[args.shape]["context"] if args.shape == "qwen3-8b" else 4096

@@ -261,10 +261,14 @@ struct Run {
   int element() const { return model.dtype == SRB_DTYPE_F32 ? 4 : 2; }
 
   // y = x w^T (+ bias) into `out` (room for partial sums included when partial_ok)
-  int linear(const void* x, int rows, const SxLinear& l, void* out, bool out_float, bool partial_ok, Produced* produced) {
+  bool skipped(int bit) const { return (step.skip & bit) != 0; }
+
+  int linear(const void* x, int rows, const SxLinear& l, void* out, bool out_float, bool partial_ok, Produced* produced,
+             int skip_bit) {
     const int m = rows, n = l.out_features, k = l.in_features;
     *produced = Produced();
     produced->whole = out;
+    if (skipped(skip_bit)) return SRB_OK;                      // a measurement leaves this product out
     if (model.dtype == SRB_DTYPE_F32) {
       SX_KERNEL(gemm_f32, ((const float*)x, (const float*)l.weight, l.bias, (float*)out, m, n, k, k, k, n, stream));
       return SRB_OK;
@@ -293,6 +297,7 @@ struct Run {
 
   int add_norm(float* residual, const Produced* delta, const SxNorm& norm, void* out, const int* row_index, int rows,
                bool write_residual) {
+    if (skipped(SX_SKIP_NORM)) return SRB_OK;
     SX_KERNEL(add_rmsnorm, (residual, delta ? delta->whole : nullptr, delta ? delta->parts : nullptr,
                             delta ? delta->num_parts : 0, delta ? delta->part_stride : 0, norm.weight, out, row_index, rows,
                             norm.width, norm.eps, write_residual ? 1 : 0, model.dtype, stream));
@@ -304,7 +309,7 @@ struct Run {
     if (call.group < 0 || call.group >= step.num_groups) SRB_FAIL("step_exec: a layer call names cache group %d", call.group);
     const SxGroup& group = step.groups[call.group];
     Produced qkv;
-    int status = linear(x, rows, a.qkv, base + l.qkv, false, true, &qkv);
+    int status = linear(x, rows, a.qkv, base + l.qkv, false, true, &qkv, SX_SKIP_QKV);
     if (status != SRB_OK) return status;
     void* q = base + l.q;
     void* out = base + l.attended;
@@ -319,6 +324,7 @@ struct Run {
         table_width = a.rotary_dim;
       }
     }
+    if (!skipped(SX_SKIP_ROPE))
     SX_KERNEL(qk_norm_rope_kv,
               (qkv.whole, qkv.parts, qkv.num_parts, qkv.part_stride, (int)width, q, call.writable ? call.k_pool : nullptr,
                call.writable ? call.v_pool : nullptr, step.positions, call.writable ? group.slots : nullptr, a.q_norm, a.k_norm,
@@ -333,7 +339,7 @@ struct Run {
     for (int i = 0; i < group.num_launches; ++i) {
       const SxLaunch& launch = group.launches[i];
       const int count = launch.end - launch.begin;
-      if (count <= 0) continue;
+      if (count <= 0 || skipped(SX_SKIP_ATTENTION)) continue;
       if (launch.wide_tiles && tc_takes) {
         SX_KERNEL(prefill_attention_tc, (q, call.k_pool, call.v_pool, out, launch.wide_tiles, launch.num_wide_tiles, rows,
                                          group.block_table, group.table_stride, a.n_q, a.n_kv, a.head_dim, call.page_size,
@@ -371,14 +377,15 @@ struct Run {
                                   launch.split_size, launch.max_splits, a.scale, step.error_word, model.dtype, stream));
       if (launch.split_size) ++launches;                       // the merge of the splits is a launch of its own
     }
-    return linear(out, rows, a.o, base + l.delta, false, true, produced);
+    return linear(out, rows, a.o, base + l.delta, false, true, produced, SX_SKIP_O);
   }
 
   int gated_mlp(const SxGatedMlp& f, const void* x, char* base, const Layout& l, Produced* produced) {
     const int rows = step.rows, k = f.gate_up.in_features;
     void* act = base + l.activation;
     const bool bf16 = model.dtype == SRB_DTYPE_BF16;
-    if (bf16 && rows <= step.own_gemm_max_tokens && k % 8 == 0) {
+    if (skipped(SX_SKIP_GATE_UP)) {
+    } else if (bf16 && rows <= step.own_gemm_max_tokens && k % 8 == 0) {
       SX_KERNEL(gemm_bf16, (x, f.gate_up.weight, act, rows, f.inner, k, k, k, f.inner, f.gate_up.out_features, f.inner,
                             SX_GEMM_GATED, 1, f.activation, step.error_word, stream));
     } else if (bf16 && f.gate_up.out_features == 2 * f.inner && rows >= step.pair_gemm_min_tokens && f.inner % 8 == 0 && k % 8 == 0) {
@@ -386,11 +393,11 @@ struct Run {
                                  SX_GEMM_GATED, f.activation, step.error_word, stream));
     } else {
       Produced both;
-      const int status = linear(x, rows, f.gate_up, base + l.gate_up, false, false, &both);
+      const int status = linear(x, rows, f.gate_up, base + l.gate_up, false, false, &both, 0);
       if (status != SRB_OK) return status;
       SX_KERNEL(gated_mul, (both.whole, act, rows, f.inner, f.activation, model.dtype, stream));
     }
-    return linear(act, rows, f.down, base + l.delta, false, true, produced);
+    return linear(act, rows, f.down, base + l.delta, false, true, produced, SX_SKIP_DOWN);
   }
 };
 
@@ -436,7 +443,7 @@ extern "C" int sx_run(const SxModel* model_pointer, const SxStep* step_pointer) 
                               step.num_wanted, false);
     if (status != SRB_OK) return status;
     Produced logits;
-    status = run.linear(final_normed, step.num_wanted, model.head, step.logits, true, false, &logits);
+    status = run.linear(final_normed, step.num_wanted, model.head, step.logits, true, false, &logits, SX_SKIP_HEAD);
     if (status != SRB_OK) return status;
   }
   return run.launches;

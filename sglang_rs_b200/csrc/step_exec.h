@@ -89,8 +89,20 @@ typedef struct SxGroup {
 
 #define SX_MAX_GROUPS 4
 
+// Kernels of a step that a measurement may leave out (SxStep.skip): the step then computes nothing of use, but
+// its time shows what the kernels left in cost.  Used by `bench.py --mode ablate` only.
+#define SX_SKIP_NORM 1
+#define SX_SKIP_ROPE 2
+#define SX_SKIP_ATTENTION 4
+#define SX_SKIP_QKV 8
+#define SX_SKIP_O 16
+#define SX_SKIP_GATE_UP 32
+#define SX_SKIP_DOWN 64
+#define SX_SKIP_HEAD 128
+
 typedef struct SxStep {
   int rows, num_wanted, sms, own_gemm_max_tokens, pair_gemm_min_tokens, num_groups;
+  int skip, reserved;          // skip: SX_SKIP_* bits, 0 in every step that is meant to compute
   const int* token_ids;        // [rows]
   const int* positions;        // [rows]
   const int* row_request;      // [rows]

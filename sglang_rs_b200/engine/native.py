@@ -118,6 +118,7 @@ class NativeModel:
         step.sms = ops.sm_count(self.device)
         step.own_gemm_max_tokens, step.pair_gemm_min_tokens = ops.OWN_GEMM_MAX_TOKENS, ops.PAIR_GEMM_MIN_TOKENS
         step.num_groups = len(groups)
+        step.skip = records.skip
         step.token_ids, step.positions = ctx.token_ids.data_ptr(), ctx.positions.data_ptr()
         step.row_request = ctx.row_request.data_ptr()
         step.logit_rows = logit_rows.data_ptr() if wanted else None

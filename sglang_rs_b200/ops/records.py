@@ -68,11 +68,16 @@ class SxGroup(ctypes.Structure):
 
 
 SX_MAX_GROUPS = 4
+#: kernels of a step that a measurement may leave out (``skip`` below): the SX_SKIP_* bits of csrc/step_exec.h
+SKIP_BITS = {"norm": 1, "rope": 2, "attention": 4, "qkv": 8, "o": 16, "gate_up": 32, "down": 64, "head": 128}
+#: bits that every step run by the executor leaves out; 0 except inside ``bench.py --mode ablate``
+skip = 0
 
 
 class SxStep(ctypes.Structure):
     _fields_ = [("rows", ctypes.c_int), ("num_wanted", ctypes.c_int), ("sms", ctypes.c_int),
                 ("own_gemm_max_tokens", ctypes.c_int), ("pair_gemm_min_tokens", ctypes.c_int), ("num_groups", ctypes.c_int),
+                ("skip", ctypes.c_int), ("reserved", ctypes.c_int),
                 ("token_ids", ctypes.c_void_p), ("positions", ctypes.c_void_p), ("row_request", ctypes.c_void_p),
                 ("logit_rows", ctypes.c_void_p), ("error_word", ctypes.c_void_p), ("workspace", ctypes.c_void_p),
                 ("workspace_bytes", ctypes.c_longlong), ("logits", ctypes.c_void_p), ("stream", ctypes.c_void_p),
