@@ -113,7 +113,7 @@ class ReplaySession:
         return host
 
 
-def main(argv=None) -> int:
+def build_parser() -> argparse.ArgumentParser:
     parser = argparse.ArgumentParser(prog="trace_run", description=__doc__.split("\n\n")[0])
     parser.add_argument("--model", required=True, help="folder with config.json and model.safetensors")
     parser.add_argument("--dtype", required=True, choices=("bfloat16", "float32"))
@@ -125,7 +125,11 @@ def main(argv=None) -> int:
                         help="most requests that are live at a time (each holds a slot of per-request state)")
     parser.add_argument("--radix", action="store_true",
                         help="keep the prefix tree: a new request starts on the pages of its longest known prefix")
-    args = parser.parse_args(argv)
+    return parser
+
+
+def main(argv=None) -> int:
+    args = build_parser().parse_args(argv)
 
     print(f"[trace_run] loading {args.model} as {args.dtype}", file=sys.stderr, flush=True)
     try:

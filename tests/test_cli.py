@@ -47,3 +47,16 @@ def test_bench_command_runs_the_benchmark_of_the_repository(capsys):
     assert main(["bench", "--impl", "reference"]) == 0
     assert '"impl": "reference"' in capsys.readouterr().out
     assert main(["bench", "--gpus", "2"]) == 2
+
+
+def test_trace_replay_options():
+    """``bin/trace_run``: the four options of its contract, and the three beside them."""
+    from sglang_rs_b200.engine.replay import DEFAULT_MAX_LIVE, PAGE_SIZE, build_parser as replay_parser
+    args = replay_parser().parse_args(["--model", "/m", "--dtype", "float32", "--out", "/o", "--max-tokens", "640"])
+    assert (args.model, args.dtype, args.out, args.max_tokens) == ("/m", "float32", "/o", 640)
+    assert (args.page_size, args.max_live, args.radix) == (PAGE_SIZE, DEFAULT_MAX_LIVE, False) and DEFAULT_MAX_LIVE == 4
+    args = replay_parser().parse_args(["--model", "/m", "--dtype", "bfloat16", "--out", "/o", "--max-tokens", "64",
+                                       "--max-live", "150", "--radix", "--page-size", "8"])
+    assert (args.max_live, args.radix, args.page_size) == (150, True, 8)
+    with pytest.raises(SystemExit):
+        replay_parser().parse_args(["--model", "/m", "--dtype", "float16", "--out", "/o", "--max-tokens", "64"])
