@@ -32,7 +32,7 @@ NVCC_FLAGS: Sequence[str] = (
 #: every library of the package; ``build_all`` compiles each of them
 LIBRARIES: Sequence[str] = ("elementwise", "rope_kv", "attention", "gemm_f32", "sampling", "attention_noalloc",
                             "attention_decode", "attention_prefill", "gemm_bf16",
-                            "attention_prefill_tc", "host_core", "gemm_bf16_pair", "step_exec")
+                            "attention_prefill_tc", "host_core", "gemm_bf16_pair", "step_exec", "plain_reference")
 
 _loaded: Dict[str, ctypes.CDLL] = {}
 
