@@ -47,7 +47,9 @@ class NativeModel:
     """The records of one loaded model, and the call that runs a step through them."""
 
     def __init__(self, model, blocks: List[SxBlock], call_blocks: List[int]):
-        self.model = model
+        # what is needed of the model, not the model itself: the model refers to this object, and a cycle would keep
+        # the weights alive until a collection of garbage
+        self.program, self.vocab_size = list(model.program), model.vocab_size
         self.device, self.dtype = model.device, model.dtype
         self._blocks = (SxBlock * len(blocks))(*blocks)
         self._call_blocks = call_blocks
@@ -90,8 +92,8 @@ class NativeModel:
     def _bind_caches(self, ctx, caches: Sequence) -> None:
         """The program's calls with the pools they read and write (made once per set of caches)."""
         groups = list(ctx.paged)
-        calls = (SxCall * len(self.model.program))()
-        for index, call in enumerate(self.model.program):
+        calls = (SxCall * len(self.program))()
+        for index, call in enumerate(self.program):
             source = caches[index if call.cache_from is None else call.cache_from]
             record = calls[index]
             record.block = call.layer
@@ -160,7 +162,7 @@ class NativeModel:
         step.workspace_bytes = need
         logits = None
         if wanted:
-            logits = torch.empty((wanted, self.model.vocab_size), dtype=torch.float32, device=self.device)
+            logits = torch.empty((wanted, self.vocab_size), dtype=torch.float32, device=self.device)
             step.logits = logits.data_ptr()
         else:
             step.logits = None
