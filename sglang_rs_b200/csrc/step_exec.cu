@@ -147,7 +147,7 @@ extern "C" int sx_set_cublas_workspace(void* memory, long long bytes) {
   return SRB_OK;
 }
 
-static int blas_handle(cublasHandle_t* out) {
+static int blas_handle(cublasHandle_t* out, int* device_out) {
   int device = 0;
   SRB_CUDA_CALL(cudaGetDevice(&device));
   if (device < 0 || device >= 64) SRB_FAIL("step_exec: device index %d is outside 0..63", device);
@@ -164,6 +164,7 @@ static int blas_handle(cublasHandle_t* out) {
     }
   }
   *out = blas.handle[device];
+  *device_out = device;
   return SRB_OK;
 }
 
@@ -171,9 +172,14 @@ static int blas_handle(cublasHandle_t* out) {
 static int blas_product(const void* x, const void* w, void* y, int m, int n, int k, int ldx, int ldw, int ldy, bool y_float,
                         cudaStream_t stream) {
   cublasHandle_t handle;
-  const int status = blas_handle(&handle);
+  int device = 0;
+  const int status = blas_handle(&handle, &device);
   if (status != SRB_OK) return status;
   if (blas.set_stream(handle, stream) != CUBLAS_STATUS_SUCCESS) SRB_FAIL("step_exec: cublasSetStream failed");
+  // setting the stream puts the library back on its own workspace pool: this package's is given again
+  if (blas.workspace[device] &&
+      blas.set_workspace(handle, blas.workspace[device], blas.workspace_bytes[device]) != CUBLAS_STATUS_SUCCESS)
+    SRB_FAIL("step_exec: cuBLAS refused the workspace");
   const float one = 1.0f, zero = 0.0f;
   // row-major y = x w^T is column-major y^T = w x^T: A = w (k x n stored, transposed), B = x (k x m stored)
   const cublasStatus_t result =
