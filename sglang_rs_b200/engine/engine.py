@@ -66,7 +66,14 @@ class Engine:
         if max_total_tokens is None:
             free, _ = torch.cuda.mem_get_info(self.device)
             per_token = max(kv_bytes_per_token(self.model, self.dtype), 1)
-            max_total_tokens = int(free * mem_fraction_static) // per_token
+            # what the step function takes beside the pool, at its largest: the split scratch of captured and of
+            # uncaptured steps, the logits that captured steps keep, cuBLAS's workspace
+            from .graphs import DecodeGraphs
+            from .runner import StepPlanner
+            beside = 4 * (StepPlanner.SCRATCH_LIMIT + 2 * DecodeGraphs.SCRATCH_FLOATS) + (64 << 20)
+            if not disable_cuda_graph:
+                beside += DecodeGraphs.MAX_LOGIT_BYTES
+            max_total_tokens = int(max(free - beside, 0) * mem_fraction_static) // per_token
             max_total_tokens = max(page_size, min(max_total_tokens, max_running_requests * self.model.max_positions))
         self.cache = CacheManager(self.model.cache_needs(), page_size=page_size, max_tokens=max_total_tokens,
                                   max_requests=max_running_requests, device=self.device, dtype=self.dtype)
