@@ -1,7 +1,7 @@
 """Benchmarks of the engine on one B200, random weights, synthetic token ids.
 
     python bench.py [--gpus 1] [--steps K] [--warmup W] [--impl ours|reference]
-                    [--shape qwen3-8b|qwen3-1.7b|qwen3-32b] [--mode decode|serve|compare-cublas|kernels]
+                    [--shape qwen3-8b|qwen3-1.7b|qwen3-32b] [--mode decode|prefill|serve|compare-cublas|kernels|ablate]
 
 ``--mode decode`` (the default) prints the headline JSON line: ``value`` is decoded tokens per second of K
 decode steps at batch 8, timed on the device with CUDA events; ``e2e`` is the same through the Python entry
@@ -11,6 +11,7 @@ ends of the context sweep (2,048 and 4,096 tokens), and the host's share of a pr
 step (decoded rows beside a prompt portion); ``roofline`` divides the bytes a decode step has to read by
 its time.  Peaks come from MEASURED_PEAKS.json when present.
 
+``--mode prefill`` (or ``--only-prefill``) times one prompt of ``--prefill-tokens`` tokens alone.
 ``--mode serve`` runs the continuous-batching workload (128 requests, prompt lengths uniform in [64, 4096],
 output lengths uniform in [16, 512], portions of 2,048 tokens) and prints total and generated tokens per
 second, the time to the first token and the rows per step.  ``--mode compare-cublas`` times every product
@@ -151,7 +152,7 @@ def main() -> int:
     parser.add_argument("--warmup", type=int, default=3)
     parser.add_argument("--impl", default="ours", choices=("ours", "reference"))
     parser.add_argument("--shape", default="qwen3-8b", choices=sorted(SHAPES))
-    parser.add_argument("--mode", default="decode", choices=("decode", "serve", "compare-cublas", "kernels", "ablate"))
+    parser.add_argument("--mode", default="decode", choices=("decode", "prefill", "serve", "compare-cublas", "kernels", "ablate"))
     parser.add_argument("--layers", type=int, default=None, help="fewer than the shape has, only where memory or time needs it")
     parser.add_argument("--batch", type=int, default=8)
     parser.add_argument("--context", type=int, default=2048, help="tokens each request holds when decoding starts")
@@ -372,7 +373,7 @@ def main() -> int:
     late = max(args.context, end_context - (short + warmup) - 8)           # the far end of the context sweep
     engine = make_engine(max(args.batch, 1), args.steps, args.context if args.skip_points else late,
                          extra_tokens=max(4096, args.prefill_tokens))
-    if args.only_prefill:
+    if args.only_prefill or args.mode == "prefill":
         best, median, wall = prefill_run(engine, args.prefill_tokens, args.steps)
         flops = prefill_flops(config, args.prefill_tokens)
         print(json.dumps({"prefill_ms": round(best, 3), "median_ms": round(median, 3), "wall_ms_back_to_back": round(wall, 3),

@@ -59,6 +59,8 @@ def build_parser() -> argparse.ArgumentParser:
     gen.add_argument("--sampling-seed", type=int, default=None)
     gen.add_argument("--stop-token-ids", type=_ids, default=None)
     gen.add_argument("--ignore-eos", action="store_true")
+    gen.add_argument("--stream", action="store_true",
+                     help="print a JSON line for every step's tokens of every prompt as they reach the host")
 
     rnd = commands.add_parser("random-model", help="write config.json and model.safetensors from a config and a seed")
     rnd.add_argument("--config", required=True, help="a config.json (or a folder holding one)")
@@ -129,7 +131,12 @@ def main(argv: Optional[List[str]] = None) -> int:
             sampling[key] = value
     if args.sampling_seed is not None:
         sampling["seed"] = args.sampling_seed
-    results = engine.generate(prompts, sampling)
+    sink = None
+    if args.stream:
+        def sink(index, output):
+            print(json.dumps({"index": index, "token_ids": output.token_ids, "finished": output.finished,
+                              "finish_reason": output.finish_reason}), flush=True)
+    results = engine.generate(prompts, sampling, sink=sink)
     for prompt, result in zip(prompts, results):
         print(json.dumps({"input_ids": prompt, **result}))
     return 0

@@ -10,7 +10,7 @@ from __future__ import annotations
 
 import itertools
 from dataclasses import dataclass
-from typing import Any, Dict, Hashable, List, Mapping, Optional, Sequence, Union
+from typing import Any, Callable, Dict, Hashable, List, Mapping, Optional, Sequence, Union
 
 import torch
 
@@ -261,9 +261,15 @@ class Engine:
 
     # ------------------------------------------------------------------ the call a user makes
     def generate(self, input_ids: Union[Sequence[int], Sequence[Sequence[int]]],
-                 sampling_params: Union[Mapping, Sequence[Mapping], None] = None) -> Union[Dict, List[Dict]]:
+                 sampling_params: Union[Mapping, Sequence[Mapping], None] = None,
+                 sink: Optional[Callable[[int, StepOutput], Any]] = None) -> Union[Dict, List[Dict]]:
         """``input_ids``: one prompt or a list of prompts (token ids).  Returns, per prompt,
-        ``{"output_ids", "cached_tokens", "finished", "finish_reason"}``."""
+        ``{"output_ids", "cached_tokens", "finished", "finish_reason"}``.
+
+        ``sink``: called as ``sink(index of the prompt, output)`` for every step's output of every prompt as soon
+        as the step's tokens have reached the host (tokens stream out while generation goes on).  A sink that
+        returns ``False`` ends that request: it is aborted, its pages are given back, and what it had produced
+        stays in its result (the reference's stream sink has this rule, crates/sglang-srt/src/engine.rs:294-297)."""
         single = len(input_ids) > 0 and not isinstance(input_ids[0], (list, tuple))
         prompts = [input_ids] if single else list(input_ids)
         if isinstance(sampling_params, (list, tuple)):
@@ -273,8 +279,15 @@ class Engine:
         else:
             params = [sampling_params] * len(prompts)
         ids = [self.add_request(prompt, p) for prompt, p in zip(prompts, params)]
+        index_of = {request_id: index for index, request_id in enumerate(ids)}
         while self.scheduler.has_work or self._in_flight is not None:
-            self.step(overlap=not self.disable_overlap_schedule)
+            outputs = self.step(overlap=not self.disable_overlap_schedule)
+            if sink is None:
+                continue
+            for output in outputs:
+                index = index_of.get(output.request_id)
+                if index is not None and sink(index, output) is False and not output.finished:
+                    self.abort(output.request_id)
         results = []
         for request_id in ids:
             request = self._requests.pop(request_id)

@@ -28,7 +28,8 @@ def test_sampling_options_and_prompts():
                     "--top-p", "0.9", "--top-k", "40", "--min-p", "0.05", "--repetition-penalty", "1.1",
                     "--presence-penalty", "0.2", "--frequency-penalty", "-0.1", "--sampling-seed", "3",
                     "--stop-token-ids", "9,10", "--ignore-eos", "--max-new-tokens", "4")
-    assert args.input_ids == ["5 6", "7,8"] and args.stop_token_ids == [9, 10] and args.ignore_eos
+    assert args.input_ids == ["5 6", "7,8"] and args.stop_token_ids == [9, 10] and args.ignore_eos and not args.stream
+    assert parse("generate", "--model-path", "/m", "--input-ids", "1", "--stream")[0].stream
     assert (args.temperature, args.top_p, args.top_k, args.min_p) == (0.7, 0.9, 40, 0.05)
     assert (args.repetition_penalty, args.presence_penalty, args.frequency_penalty, args.sampling_seed) == (1.1, 0.2, -0.1, 3)
     with pytest.raises(SystemExit):                                   # one source of prompts, not two

@@ -759,3 +759,34 @@ def test_step_records_kernel_classes_and_request_totals(tmp_path):
     assert m.time_to_first_token_seconds_count == 3 and m.request_duration_seconds_count == 3
     assert all(len(r["output_ids"]) == 5 for r in results)
     assert "sglang_generation_tokens_total 15" in m.render()
+
+
+def test_tokens_stream_through_a_sink_and_a_sink_can_end_a_request(tmp_path):
+    """``generate(..., sink=...)``: every step's output reaches the sink as soon as it is on the host; a sink that
+    returns False ends that request alone (the reference's rule, crates/sglang-srt/src/engine.rs:294-297).  The other
+    requests produce what they produce without a sink, and the ended request's pages are given back."""
+    from sglang_rs_b200 import Engine
+    folder = rh.make_folder(tmp_path, "m", pm.TINY_A, seed=4, dtype=torch.float32)
+    prompts = list(rh.random_requests(pm.TINY_A, (21, 40, 9), seed=2).values())
+    params = {"max_new_tokens": 12, "ignore_eos": True}
+    plain = Engine(model_path=folder, dtype="float32", max_total_tokens=512, chunked_prefill_size=16).generate(prompts, params)
+    engine = Engine(model_path=folder, dtype="float32", max_total_tokens=512, chunked_prefill_size=16,
+                    disable_radix_cache=True)
+    seen = {0: [], 1: [], 2: []}
+    finished = {}
+
+    def sink(index, output):
+        seen[index].extend(output.token_ids)
+        if output.finished:
+            finished[index] = output.finish_reason
+        return not (index == 1 and len(seen[1]) >= 3)          # the second request is ended after three tokens
+
+    results = engine.generate(prompts, params, sink=sink)
+    assert [r["output_ids"] for r in results] == [seen[0], seen[1], seen[2]]
+    assert results[0]["output_ids"] == plain[0]["output_ids"] and results[2]["output_ids"] == plain[2]["output_ids"]
+    assert 3 <= len(seen[1]) <= 4 and seen[1] == plain[1]["output_ids"][:len(seen[1])]     # a step was in flight
+    assert results[1]["finish_reason"] == "abort" and finished == {0: "length", 1: "abort", 2: "length"}
+    assert not engine.scheduler.has_work and engine._in_flight is None
+    engine.cache.check_invariants()
+    assert all(a.free_count == a.num_pages for a in engine.cache.allocators.values())
+    assert engine.metrics.requests_failed_total == 1 and engine.metrics.requests_in_flight == 0
