@@ -8,6 +8,7 @@ and nothing falls back to another implementation.
 from __future__ import annotations
 
 import ctypes
+import os
 from typing import Optional
 
 import torch
@@ -472,18 +473,20 @@ def tiled_attention_tc(q: torch.Tensor, k_pool: torch.Tensor, v_pool: torch.Tens
 
 # --------------------------------------------------------------------------- matrix products
 
+#: The two thresholds below were measured at Qwen3-8B sizes on a B200; they are tunables (the environment
+#: variables SRB_OWN_GEMM_MAX_TOKENS and SRB_PAIR_GEMM_MIN_TOKENS set them), read at every step.
 #: up to this many rows a bfloat16 product runs on this package's tcgen05 kernel for few tokens.  With 65 to
 #: 128 rows the kernel has one block per SM and no cut along K, and the library is twice as fast
 #: (Qwen3-8B sizes on B200, chained in a graph: QKV 12 against 20 us, down 23 against 52 us; a 12-layer
 #: decode step at batch 128 takes 3.80 ms instead of 4.48 ms)
-OWN_GEMM_MAX_TOKENS = 64
+OWN_GEMM_MAX_TOKENS = int(os.environ.get("SRB_OWN_GEMM_MAX_TOKENS", "64"))
 #: from this many rows on the gate/up product runs on the persistent CTA-pair kernel, which takes SiLU(gate) * up
 #: into its epilogue.  Measured at Qwen3-8B sizes on B200, chained in a graph, against the library's product
 #: followed by the SiLU kernel: 64.8 against 53.7 us at 256 rows (96 tiles of 256 tokens leave the second
 #: round of the 74 pairs mostly empty), 155 against 155 us at 1,024, 214 against 219 us at 1,536, 280 against
 #: 301 us at 2,048.  The plain products stay with the library at every size: the pair kernel reaches 0.92 to
 #: 1.0 of it alone, and whole prefill steps measured no gain from switching them.
-PAIR_GEMM_MIN_TOKENS = 1280
+PAIR_GEMM_MIN_TOKENS = int(os.environ.get("SRB_PAIR_GEMM_MIN_TOKENS", "1280"))
 
 
 def gemm_splits(tokens: int, features: int, k: int, sms: Optional[int] = None) -> int:
