@@ -257,7 +257,8 @@ class CacheManager:
             elif isinstance(need, RequestState):
                 state = None
                 if device is not None:
-                    state = torch.zeros((self.max_requests, *need.shape), dtype=need.dtype or dtype, device=device)
+                    # one slot more than requests can hold: rows that pad a captured step use it
+                    state = torch.zeros((self.max_requests + 1, *need.shape), dtype=need.dtype or dtype, device=device)
                 self.layer_caches.append(StateLayerCache(state))
             elif need is None:
                 self.layer_caches.append(None)

@@ -414,7 +414,8 @@ int hc_fill_group(void* handle, int g, const int* requests, const int* counts, i
 
 // The whole static buffer of a captured decode step (one row per request, padded to `bucket` rows).
 // offsets: tokens, positions, row_request, cu_rows, state_slots, logit_rows, token_from, then per group
-// table and slots.  Padding rows: token 0 at position 0, writing to the pool's spare page.
+// table and slots.  Padding rows: token 0 at position 0, writing to the pool's spare page; their state slot is
+// the spare one behind the slots that requests can hold (index = number of state slots).
 int hc_fill_decode(void* handle, const int* requests, const int* tokens, const int* token_from, int rows, int bucket,
                    int stride, const int* spare_pages, const int* offsets, int* buffer) {
   Core* core = static_cast<Core*>(handle);
@@ -433,7 +434,7 @@ int hc_fill_decode(void* handle, const int* requests, const int* tokens, const i
     positions[i] = live ? core->requests[requests[i]].length : 0;
     row_request[i] = i;
     cu_rows[i] = i;
-    state_slots[i] = live ? core->requests[requests[i]].state_slot : 0;
+    state_slots[i] = live ? core->requests[requests[i]].state_slot : (int)core->state_used.size();
     logit_rows[i] = i;
     from[i] = live ? token_from[i] : -1;
   }

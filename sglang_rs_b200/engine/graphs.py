@@ -5,7 +5,9 @@ on the host.  A graph is captured per (row bucket, block-table width, key-split 
 group) with every index array in one static device buffer that is refilled by one copy
 before each replay.  Rows beyond the live ones are padding: token 0 at position 0 whose
 key and value go to the pool's spare page (the page after the last one the allocator
-owns), so they touch nothing that lives.
+owns) and whose per-request state is the spare slot behind those that requests hold, so
+they touch nothing that lives.  A mixer with state of its own may therefore be captured
+too, if its step for decoded tokens runs on the device from ``ctx.state_slots`` alone.
 
 The kernels, their arithmetic and the split of the keys are those of the eager path.
 """

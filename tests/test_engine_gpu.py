@@ -410,8 +410,10 @@ def register_toy(stateless=False):
     class DecayingSumMixer(Mixer):
         """s_t = decay * s_{t-1} + W x_t; y_t = s_t.  The state s lives in the request's slot."""
 
-        def __init__(self, hidden, decay, weight_name):
+        def __init__(self, hidden, decay, weight_name, on_device=False):
             self.hidden, self.decay, self.weight_name = hidden, decay, weight_name
+            # with its decode step on the device (below) the mixer may be captured into a CUDA graph
+            self.graph_safe = on_device
 
         def cache_need(self):
             return RequestState((self.hidden,), torch.float32)
@@ -424,6 +426,13 @@ def register_toy(stateless=False):
 
         def forward(self, ctx, cache, x):
             v = ops.linear(x, self.w).float()
+            if self.graph_safe and all(b - a == 1 for a, b in zip(ctx.host_cu_rows, ctx.host_cu_rows[1:])):
+                # one row per request (a decode step): the whole step from the device's own copy of the slots;
+                # rows that pad a captured step carry the spare slot, which no request holds
+                slots = ctx.state_slots.long()
+                s = self.decay * cache.state[slots] + v
+                cache.state[slots] = s
+                return s.to(x.dtype)
             out = torch.empty_like(v)
             for r in range(ctx.num_requests):
                 slot = ctx.host_state_slots[r]
@@ -449,7 +458,8 @@ def register_toy(stateless=False):
                                 GatedMlp(h, cfg["inner"], "silu", GatedMlpNames(f"{p}.gate", f"{p}.up", f"{p}.down")))
 
         rope = lambda: RotaryEncoding(cfg["head_dim"], cfg["theta"])  # noqa: E731
-        first = attn(0, cfg["window"] + 6, rope()) if cfg.get("stateless") else DecayingSumMixer(h, cfg["decay"], "layers.0.mix")
+        first = attn(0, cfg["window"] + 6, rope()) if cfg.get("stateless") else DecayingSumMixer(
+            h, cfg["decay"], "layers.0.mix", on_device=bool(cfg.get("state_on_device")))
         layers = [block(0, first), block(1, attn(1, None, rope())),
                   block(2, attn(2, cfg["window"], NoPositionEncoding())), block(3, attn(3, None, rope()))]
         # layer 1 runs twice (two caches, one set of weights); layer 3 reads the cache of the first call of layer 1
@@ -541,6 +551,37 @@ def test_an_architecture_defined_in_the_test(tmp_path, dtype_name, stored, toler
                 limit = (0.0 if dtype_name == "float32" else 3e-2) * float(logits.abs().max())
                 assert float(logits.max() - logits[token]) <= limit
                 tokens.append(token)
+    finally:
+        unregister_architecture("ToyHybridForTests")
+
+
+@pytest.mark.parametrize("dtype_name,stored,tolerance", [("float32", torch.float32, rh.FP32_TOLERANCE),
+                                                         ("bfloat16", torch.bfloat16, rh.BF16_TOLERANCE)])
+def test_a_mixer_with_state_of_its_own_decodes_from_captured_graphs(tmp_path, dtype_name, stored, tolerance):
+    """The toy's stateful mixer with its decode step on the device: decode steps are captured (rows that pad a
+    captured step use the spare state slot), give the oracle's logits, and in 32-bit the very bits of the
+    uncaptured run; portions of prompts still walk their rows in order on the host."""
+    from sglang_rs_b200.config import unregister_architecture
+    from sglang_rs_b200.weights import read_model_dir, write_model_folder
+    toy = dict(TOY, state_on_device=True)
+    register_toy()
+    try:
+        folder = write_model_folder(str(tmp_path / "toy3"), toy, seed=6, dtype=stored)
+        weights = {k: v.float() for k, v in read_model_dir(folder).items()}
+        requests = rh.random_requests({"vocab_size": TOY["vocab"]}, (70, 33, 150, 9, 41), seed=9)
+        expected = {rid: plain_toy_forward(toy, weights, toks).numpy() for rid, toks in requests.items()}
+        for trace in (rh.trace_tail_by_one(requests, tail=20), rh.trace_mixed(requests, seed=6, decode_tail=20),
+                      rh.trace_decode_together(requests, tail=9)):
+            captured, session = rh.run_in_process(folder, dtype_name, trace)
+            assert session.runner.graphs is not None and session.runner.graphs.replays >= 9
+            assert session.model.native is None                  # a part without a record: the part-by-part path
+            bad = rh.first_bad(captured, expected, tolerance)
+            assert bad is None, bad
+            eager, _ = rh.run_in_process(folder, dtype_name, trace, graphs=False)
+            for rid in eager:
+                for p, row in eager[rid].items():
+                    if dtype_name == "float32":
+                        assert np.array_equal(row, captured[rid][p]), (rid, p)
     finally:
         unregister_architecture("ToyHybridForTests")
 
