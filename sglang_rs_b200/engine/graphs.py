@@ -96,6 +96,13 @@ class DecodeGraphs:
             while len(self.captured) > 1 and self._logit_bytes() > self.MAX_LOGIT_BYTES:
                 self.captured.popitem(last=False)
         self.captured.move_to_end(key)
+        if step.graph is None:
+            # Captured, and run twice before that, on rows that are all padding: what those runs write goes to the
+            # spare page and the spare state slot, so a mixer whose step is not idempotent (a running state) is
+            # not stepped twice for the live requests.
+            self._fill(step, [], groups, bucket, stride, positions, page_size)
+            step.static.copy_(step.staging, non_blocking=True)
+            self._capture(key, step, groups, bucket, stride, splits)
         if step.copied is not None:
             step.copied.synchronize()        # the staging buffer is free again once its last copy has run
         self._fill(step, entries, groups, bucket, stride, positions, page_size)
@@ -108,8 +115,6 @@ class DecodeGraphs:
         if step.copied is None:
             step.copied = torch.cuda.Event()
         step.copied.record()
-        if step.graph is None:
-            self._capture(key, step, groups, bucket, stride, splits)
         step.graph.replay()
         self.replays += 1
         ops.launch_count += self.kernels_per_replay[key]
