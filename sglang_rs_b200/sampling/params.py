@@ -5,8 +5,8 @@ the thread's generator and has no seed option (crates/sglang-srt/src/model_execu
 """
 from __future__ import annotations
 
-from dataclasses import dataclass, field
-from typing import Any, Mapping, Optional, Sequence, Tuple
+from dataclasses import dataclass
+from typing import Any, Mapping, Optional, Tuple
 
 GREEDY_EPSILON = 1.1920929e-07       # f32::EPSILON: a temperature at or below it is greedy
 
