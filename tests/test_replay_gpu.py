@@ -213,10 +213,10 @@ def test_trace_run_program(prepared, tmp_path):
 
 @pytest.mark.parametrize("dtype_name", ["bfloat16", "float32"])
 def test_layer_sizes_of_the_8b_shape(tmp_path, dtype_name):
-    """One layer with the benchmark's layer sizes (hidden 4096, 32/8 heads of 128, inner 12288) and a
-    vocabulary of 32,000: the products are cut along K as in the benchmark and the attention kernels
-    see 4 query heads per kv head.  Prompt in one step, then tokens one by one across a key split."""
-    config = dict(pm.TINY_D, num_hidden_layers=1, hidden_size=4096, num_attention_heads=32, num_key_value_heads=8,
+    """Layers with the benchmark's layer sizes (hidden 4096, 32/8 heads of 128, inner 12288; two of them in
+    32-bit, one in bfloat16) and a vocabulary of 32,000: the products are cut along K as in the benchmark and the
+    attention kernels see 4 query heads per kv head.  Prompt in one step, then tokens one by one across a key split."""
+    config = dict(pm.TINY_D, num_hidden_layers=2 if dtype_name == "float32" else 1, hidden_size=4096, num_attention_heads=32, num_key_value_heads=8,
                   head_dim=128, intermediate_size=12288, vocab_size=32000, max_position_embeddings=512)
     stored = DTYPES[dtype_name][0]
     folder = rh.make_folder(tmp_path, "big", config, seed=5, dtype=stored)
