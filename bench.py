@@ -152,7 +152,8 @@ def main() -> int:
     parser.add_argument("--warmup", type=int, default=3)
     parser.add_argument("--impl", default="ours", choices=("ours", "reference"))
     parser.add_argument("--shape", default="qwen3-8b", choices=sorted(SHAPES))
-    parser.add_argument("--mode", default="decode", choices=("decode", "prefill", "serve", "compare-cublas", "kernels", "ablate"))
+    parser.add_argument("--mode", default="decode", choices=("decode", "prefill", "serve", "compare-cublas", "kernels", "ablate", "probe-overlap"))
+    parser.add_argument("--rows", default="1,8,64,2048", help="--mode compare-cublas: the row counts, comma-separated")
     parser.add_argument("--layers", type=int, default=None, help="fewer than the shape has, only where memory or time needs it")
     parser.add_argument("--batch", type=int, default=8)
     parser.add_argument("--context", type=int, default=2048, help="tokens each request holds when decoding starts")
@@ -345,6 +346,8 @@ def main() -> int:
         return serve(args, config, peak, shape_note, warmup)
     if args.mode == "kernels":
         return kernel_classes(args, config, make_engine, prompts, shape_note, warmup)
+    if args.mode == "probe-overlap":
+        return probe_overlap(args, config)
     if args.mode == "ablate":
         from sglang_rs_b200.ops import records
         engine = make_engine(args.batch, args.steps, args.context)
@@ -450,7 +453,7 @@ def compare_cublas(args, config, peak, shape_note) -> int:
     device = torch.device("cuda")
     word = ops.new_error_word(device)
     inner = config["intermediate_size"]
-    rows_list = (1, 8, 64, 2048)
+    rows_list = tuple(int(r) for r in args.rows.split(","))
     results = []
     generator = torch.Generator(device=device).manual_seed(args.seed)
     for name, (n, k) in layer_products(config).items():
@@ -508,6 +511,11 @@ def compare_cublas(args, config, peak, shape_note) -> int:
             own_us, library_us = timed(own), timed(library)
             entry = {"product": name, "rows": m, "weight": [n, k], "own_us": round(own_us, 2), "cublas_us": round(library_us, 2),
                      "own_over_cublas": round(library_us / own_us, 3)}
+            if m >= 256 and name not in ("gate_up", "lm_head"):
+                # the CTA-pair kernel on a plain product (the engine leaves these to the library)
+                pair_us = timed(lambda w: ops.gemm_bf16_pair(x, w, word, mode="bf16"))
+                entry["pair_kernel_us"] = round(pair_us, 2)
+                entry["pair_kernel_tflops"] = round(2.0 * m * n * k / (pair_us * 1e-6) / 1e12, 1)
             if m <= 64:
                 entry["own_hbm_frac"] = round(n * k * 2 / (own_us * 1e-6) / 1e9 / peak["hbm_gbs"], 3)
                 entry["cublas_hbm_frac"] = round(n * k * 2 / (library_us * 1e-6) / 1e9 / peak["hbm_gbs"], 3)
@@ -522,6 +530,59 @@ def compare_cublas(args, config, peak, shape_note) -> int:
     print(json.dumps({"mode": "compare-cublas", "config": shape_note, "timing": "CUDA events, weights rotate through copies "
                       "larger than L2; up to 64 rows the calls are replayed from one CUDA graph; gate_up includes the activation (own: in the epilogue; cuBLAS: a kernel after it)",
                       "products": results}))
+    return 0
+
+
+# ---------------------------------------------------------------------------------------- do kernels overlap?
+def probe_overlap(args, config) -> int:
+    """The library's gate/up and down products of ``--prefill-tokens`` rows on one stream and this package's norm
+    kernel on another: alone, and together.  (What two halves of a prompt on two streams could hide of the
+    memory-bound kernels under the products.)"""
+    import torch
+    from sglang_rs_b200 import ops
+    device = torch.device("cuda")
+    rows, hidden, inner = args.prefill_tokens, config["hidden_size"], config["intermediate_size"]
+    x = torch.randn(rows, hidden, device=device).bfloat16()
+    act = torch.randn(rows, inner, device=device).bfloat16()
+    w_gate_up = (torch.randn(2 * inner, hidden, device=device) * 0.02).bfloat16()
+    w_down = (torch.randn(hidden, inner, device=device) * 0.02).bfloat16()
+    residual, delta = torch.randn(rows, hidden, device=device), torch.randn(rows, hidden, device=device).bfloat16()
+    weight, out = torch.ones(hidden, device=device), torch.empty(rows, hidden, device=device, dtype=torch.bfloat16)
+    word = ops.new_error_word(device)
+
+    def products():
+        for _ in range(10):
+            ops.linear(x, w_gate_up, error_word=word)
+            ops.linear(act, w_down, error_word=word)
+
+    def norms():
+        for _ in range(40):
+            ops.add_rmsnorm(residual, delta, weight, 1e-6, out)
+
+    def timed(call):
+        call()
+        torch.cuda.synchronize()
+        begin, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        begin.record()
+        call()
+        end.record()
+        torch.cuda.synchronize()
+        return begin.elapsed_time(end)
+    one, two = torch.cuda.Stream(), torch.cuda.Stream()
+
+    def together():
+        current = torch.cuda.current_stream()
+        one.wait_stream(current)
+        two.wait_stream(current)
+        with torch.cuda.stream(one), ops.stream_scope():
+            products()
+        with torch.cuda.stream(two), ops.stream_scope():
+            norms()
+        current.wait_stream(one)
+        current.wait_stream(two)
+    print(json.dumps({"mode": "probe-overlap", "rows": rows, "products_alone_ms": round(timed(products), 3),
+                      "norms_alone_ms": round(timed(norms), 3), "together_on_two_streams_ms": round(timed(together), 3),
+                      "what": "10 x (gate/up + down) by the library on one stream, 40 add+norm kernels on another"}))
     return 0
 
 
@@ -596,11 +657,13 @@ def kernel_classes(args, config, make_engine, prompts, shape_note, warmup) -> in
     import torch
     from sglang_rs_b200.engine.runner import StepEntry
     from sglang_rs_b200.ops import trace
-    engine = make_engine(args.batch, 8, args.context, extra_tokens=4096)
+    length = args.prefill_tokens
+    engine = make_engine(args.batch, 8, args.context, extra_tokens=max(4096, length + 64))
     engine.runner.graphs = None                              # every kernel launched on its own
     out = {"mode": "kernels", "config": shape_note, "note": "CUDA events around every op of an uncaptured step; "
            "shares, not absolutes: a captured decode step is shorter than the sum"}
-    tokens = prompts(1, PREFILL_TOKENS)[0]
+    tokens = prompts(1, length)[0]
+    out["prefill_tokens"] = length
     handles = [engine.cache.open(f"d{i}") for i in range(args.batch)]
     for handle, prompt in zip(handles, prompts(args.batch, args.context)):
         engine.runner.step([StepEntry(handle, prompt, [])])
@@ -611,7 +674,7 @@ def kernel_classes(args, config, make_engine, prompts, shape_note, warmup) -> in
                 trace.configure("events")
             if name == "prefill":
                 handle = engine.cache.open(f"p{i}")
-                engine.runner.step([StepEntry(handle, tokens, [PREFILL_TOKENS - 1])])
+                engine.runner.step([StepEntry(handle, tokens, [length - 1])])
                 engine.cache.close(handle)
             else:
                 engine.runner.step([StepEntry(h, [1], [0]) for h in handles])
