@@ -46,13 +46,12 @@ def prepare(native: "NativeModel", page_size: int) -> None:
 class NativeModel:
     """The records of one loaded model, and the call that runs a step through them."""
 
-    def __init__(self, model, blocks: List[SxBlock], call_blocks: List[int]):
+    def __init__(self, model, blocks: List[SxBlock]):
         # what is needed of the model, not the model itself: the model refers to this object, and a cycle would keep
         # the weights alive until a collection of garbage
         self.program, self.vocab_size = list(model.program), model.vocab_size
         self.device, self.dtype = model.device, model.dtype
         self._blocks = (SxBlock * len(blocks))(*blocks)
-        self._call_blocks = call_blocks
         self._calls = None
         self._calls_of = None
         self._record = SxModel()
@@ -84,7 +83,7 @@ class NativeModel:
             if not isinstance(record, SxBlock):
                 return None
             blocks.append(record)
-        return cls(model, blocks, [call.layer for call in model.program])
+        return cls(model, blocks)
 
     def attention_shapes(self) -> List[tuple]:
         return [(b.mixer.n_q, b.mixer.n_kv, b.mixer.head_dim) for b in self._blocks]

@@ -16,8 +16,6 @@ import torch
 
 from ..csrc.build import load_library
 
-c_int_p = ctypes.POINTER(ctypes.c_int)
-
 
 class SxLinear(ctypes.Structure):
     _fields_ = [("weight", ctypes.c_void_p), ("bias", ctypes.c_void_p), ("out_features", ctypes.c_int),
