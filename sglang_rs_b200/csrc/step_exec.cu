@@ -221,7 +221,7 @@ static Layout layout_of(const SxModel& model, const SxStep& step) {
   long long qkv = 0, q = 0, delta = 0, activation = 0, gate_up = 0, rope_table = 0;
   for (int b = 0; b < model.num_blocks; ++b) {
     const SxBlock& block = model.blocks[b];
-    if (rows >= SX_ROPE_TABLE_MIN_ROWS && block.mixer.inv_freq)
+    if (rows >= SX_ROPE_TABLE_MIN_ROWS && block.mixer.inv_freq && block.mixer.head_dim == 128)
       rope_table = std::max(rope_table, (long long)rows * block.mixer.rotary_dim * 4);
     qkv = std::max(qkv, product_bytes(step, block.mixer.qkv, rows, element, true));
     q = std::max(q, (long long)rows * block.mixer.n_q * block.mixer.head_dim * element);
@@ -266,9 +266,9 @@ struct Run {
   int table_width = 0;
   int element() const { return model.dtype == SRB_DTYPE_F32 ? 4 : 2; }
 
-  // y = x w^T (+ bias) into `out` (room for partial sums included when partial_ok)
   bool skipped(int bit) const { return (step.skip & bit) != 0; }
 
+  // y = x w^T (+ bias) into `out` (room for partial sums included when partial_ok)
   int linear(const void* x, int rows, const SxLinear& l, void* out, bool out_float, bool partial_ok, Produced* produced,
              int skip_bit) {
     const int m = rows, n = l.out_features, k = l.in_features;
@@ -321,7 +321,9 @@ struct Run {
     void* out = base + l.attended;
     const long long width = (long long)a.qkv.out_features;
     const float* table = nullptr;
-    if (rows >= SX_ROPE_TABLE_MIN_ROWS && a.inv_freq && kernels.rope_table) {
+    // (only the kernel for many rows of 128-wide heads rotated whole, in half-split pairs, reads the table)
+    if (rows >= SX_ROPE_TABLE_MIN_ROWS && a.inv_freq && kernels.rope_table && a.head_dim == 128 && a.rotary_dim == 128 &&
+        !a.interleaved) {
       // every layer of a model usually turns by the same frequencies: the table is made for the first of them
       table = (const float*)(base + l.rope_table);
       if (table_of != a.inv_freq || table_width != a.rotary_dim) {
