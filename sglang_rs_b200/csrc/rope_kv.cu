@@ -12,6 +12,8 @@
 //
 // Page pool layout: [page, kv_head, slot_in_page, head_dim].
 #include "common.cuh"
+#include "mma_helpers.cuh"
+#include <algorithm>
 
 SRB_DEFINE_LAST_ERROR()
 SRB_DEFINE_PDL_SWITCH()
@@ -168,211 +170,271 @@ __global__ void qk_norm_rope_kv_kernel(const T* __restrict__ qkv, const float* _
 
 
 // Many rows (256 and more), head_dim 128, rotation of the whole head in half-split pairs, the
-// projection in one tensor: one block per row.  Half a warp takes a head: lane l of the half holds the
-// eight elements 8l..8l+7 (one 16-byte access in bfloat16, two in 32-bit), its rotation partner sits eight
-// lanes away.  A block's sixteen half-warps take sixteen heads per pass, and a thread asks for the data of
-// all its passes (up to ROW_PASSES) before it touches any of them, so that each SM has some hundred KB in
-// flight; the table of angles is computed while those loads travel.  v heads are copied as they are.
-// Same arithmetic as the kernel above, bit for bit: the sum of squares is added up in the order of that
-// kernel's warp reduction (four elements per lane there: this lane's two halves stand for two of its lanes).
-#define ROW_WARPS 8
-#define ROW_PASSES 4
-struct Head8 { float v[8]; };
-template <typename T> struct Raw8;
-template <> struct Raw8<__nv_bfloat16> { uint4 a; };
-template <> struct Raw8<float> { float4 a, b; };
-__device__ __forceinline__ Raw8<__nv_bfloat16> load_raw8(const __nv_bfloat16* p) {
-  Raw8<__nv_bfloat16> r;
+// projection in one tensor.  Blocks of four warps stay on their SM and walk the rows blockIdx.x, blockIdx.x +
+// gridDim.x, ...  A row's bytes come into a ring of ROW_STAGES buffers in shared memory by asynchronous 16-byte
+// copies (one group of copies per row), two rows ahead of the arithmetic, so that the copies of later rows
+// travel under the arithmetic of the current one and no register waits for them.  Eight lanes take a head:
+// lane l of the eight holds the elements 8l..8l+7 and 64+8l..64+8l+7, that is both members of its eight
+// rotation pairs, so the rotation needs no exchange between lanes and the sum of squares three.  A warp takes
+// four heads per pass, the block sixteen.  The angles come from the step's table (copied with the row), or are
+// computed when the row's copies are issued.  v heads are copied as they are.  Same arithmetic as the kernel
+// above, bit for bit: the sum of squares is added up in the order of that kernel's warp reduction (four
+// elements per lane there: this lane's four quadruples stand for its lanes 2l, 2l + 1, 2l + 16 and 2l + 17).
+#define ROW_THREADS 128
+#define ROW_STAGES 3
+#define ROW_BLOCKS_PER_SM 5
+struct Head16 { float a[8], b[8]; };             // the first and the second member of eight rotation pairs
+template <typename T> struct Raw16;
+template <> struct Raw16<__nv_bfloat16> { uint4 a, b; };
+template <> struct Raw16<float> { float4 a0, a1, b0, b1; };
+__device__ __forceinline__ Raw16<__nv_bfloat16> load_raw16(const __nv_bfloat16* p) {
+  Raw16<__nv_bfloat16> r;
   r.a = *reinterpret_cast<const uint4*>(p);
+  r.b = *reinterpret_cast<const uint4*>(p + 64);
   return r;
 }
-__device__ __forceinline__ Raw8<float> load_raw8(const float* p) {
-  Raw8<float> r;
-  r.a = *reinterpret_cast<const float4*>(p);
-  r.b = *reinterpret_cast<const float4*>(p + 4);
+__device__ __forceinline__ Raw16<float> load_raw16(const float* p) {
+  Raw16<float> r;
+  r.a0 = *reinterpret_cast<const float4*>(p);
+  r.a1 = *reinterpret_cast<const float4*>(p + 4);
+  r.b0 = *reinterpret_cast<const float4*>(p + 64);
+  r.b1 = *reinterpret_cast<const float4*>(p + 68);
   return r;
 }
-__device__ __forceinline__ Head8 widen8(const Raw8<__nv_bfloat16>& r) {
-  Head8 h;
-  const __nv_bfloat162* pairs = reinterpret_cast<const __nv_bfloat162*>(&r.a);
+__device__ __forceinline__ void widen8(const uint4& raw, float* out) {
+  const __nv_bfloat162* pairs = reinterpret_cast<const __nv_bfloat162*>(&raw);
 #pragma unroll
   for (int j = 0; j < 4; ++j) {
     const float2 f = __bfloat1622float2(pairs[j]);
-    h.v[2 * j] = f.x;
-    h.v[2 * j + 1] = f.y;
+    out[2 * j] = f.x;
+    out[2 * j + 1] = f.y;
   }
+}
+__device__ __forceinline__ Head16 widen16(const Raw16<__nv_bfloat16>& r) {
+  Head16 h;
+  widen8(r.a, h.a);
+  widen8(r.b, h.b);
   return h;
 }
-__device__ __forceinline__ Head8 widen8(const Raw8<float>& r) {
-  Head8 h;
-  h.v[0] = r.a.x; h.v[1] = r.a.y; h.v[2] = r.a.z; h.v[3] = r.a.w;
-  h.v[4] = r.b.x; h.v[5] = r.b.y; h.v[6] = r.b.z; h.v[7] = r.b.w;
+__device__ __forceinline__ Head16 widen16(const Raw16<float>& r) {
+  Head16 h;
+  h.a[0] = r.a0.x; h.a[1] = r.a0.y; h.a[2] = r.a0.z; h.a[3] = r.a0.w;
+  h.a[4] = r.a1.x; h.a[5] = r.a1.y; h.a[6] = r.a1.z; h.a[7] = r.a1.w;
+  h.b[0] = r.b0.x; h.b[1] = r.b0.y; h.b[2] = r.b0.z; h.b[3] = r.b0.w;
+  h.b[4] = r.b1.x; h.b[5] = r.b1.y; h.b[6] = r.b1.z; h.b[7] = r.b1.w;
   return h;
 }
-__device__ __forceinline__ void store8(__nv_bfloat16* p, const Head8& h) {
+__device__ __forceinline__ uint4 pack8(const float* v) {
   uint4 raw;
   __nv_bfloat162* pairs = reinterpret_cast<__nv_bfloat162*>(&raw);
 #pragma unroll
-  for (int j = 0; j < 4; ++j) pairs[j] = __floats2bfloat162_rn(h.v[2 * j], h.v[2 * j + 1]);
-  *reinterpret_cast<uint4*>(p) = raw;
+  for (int j = 0; j < 4; ++j) pairs[j] = __floats2bfloat162_rn(v[2 * j], v[2 * j + 1]);
+  return raw;
 }
-__device__ __forceinline__ void store8(float* p, const Head8& h) {
-  *reinterpret_cast<float4*>(p) = make_float4(h.v[0], h.v[1], h.v[2], h.v[3]);
-  *reinterpret_cast<float4*>(p + 4) = make_float4(h.v[4], h.v[5], h.v[6], h.v[7]);
+__device__ __forceinline__ void store16(__nv_bfloat16* p, const Head16& h) {
+  *reinterpret_cast<uint4*>(p) = pack8(h.a);
+  *reinterpret_cast<uint4*>(p + 64) = pack8(h.b);
 }
-__device__ __forceinline__ void store_raw8(__nv_bfloat16* p, const Raw8<__nv_bfloat16>& r) { *reinterpret_cast<uint4*>(p) = r.a; }
-__device__ __forceinline__ void store_raw8(float* p, const Raw8<float>& r) {
-  *reinterpret_cast<float4*>(p) = r.a;
-  *reinterpret_cast<float4*>(p + 4) = r.b;
+__device__ __forceinline__ void store16(float* p, const Head16& h) {
+  *reinterpret_cast<float4*>(p) = make_float4(h.a[0], h.a[1], h.a[2], h.a[3]);
+  *reinterpret_cast<float4*>(p + 4) = make_float4(h.a[4], h.a[5], h.a[6], h.a[7]);
+  *reinterpret_cast<float4*>(p + 64) = make_float4(h.b[0], h.b[1], h.b[2], h.b[3]);
+  *reinterpret_cast<float4*>(p + 68) = make_float4(h.b[4], h.b[5], h.b[6], h.b[7]);
+}
+__device__ __forceinline__ void store_raw16(__nv_bfloat16* p, const Raw16<__nv_bfloat16>& r) {
+  *reinterpret_cast<uint4*>(p) = r.a;
+  *reinterpret_cast<uint4*>(p + 64) = r.b;
+}
+__device__ __forceinline__ void store_raw16(float* p, const Raw16<float>& r) {
+  *reinterpret_cast<float4*>(p) = r.a0;
+  *reinterpret_cast<float4*>(p + 4) = r.a1;
+  *reinterpret_cast<float4*>(p + 64) = r.b0;
+  *reinterpret_cast<float4*>(p + 68) = r.b1;
 }
 
-// norm (if a weight is given) and rotation of the eight values this lane holds of one head; the sixteen lanes
-// of a half-warp hold the head; `sn` holds the sines with the sign of this lane's side of the rotation pairs
-__device__ __forceinline__ Head8 norm_and_rotate8(Head8 x, bool has_norm, const float* w, float eps, bool rotate,
-                                                  const float* cs, const float* sn) {
-  // The other kernel sums four elements per lane over 32 lanes by a butterfly (16, 8, 4, 2, 1); here a lane's
-  // two quadruples are that kernel's lanes 2l and 2l + 1, so its first four exchanges become 8, 4, 2, 1 within
-  // the half-warp for each quadruple, and its last one is the sum of the two quadruples.  (The exchanges run
-  // whether or not this half's head has a norm: the two halves of a warp may differ in that.)
-  float lo = sum_squares4(make_float4(x.v[0], x.v[1], x.v[2], x.v[3]));
-  float hi = sum_squares4(make_float4(x.v[4], x.v[5], x.v[6], x.v[7]));
+// Two 32-bit floats in one 64-bit register, for the instructions that work on both at once (each half is
+// rounded as the single instruction would round it).
+typedef unsigned long long Float2x;
+__device__ __forceinline__ Float2x pair_of(float lo, float hi) {
+  Float2x p;
+  asm("mov.b64 %0, {%1, %2};" : "=l"(p) : "f"(lo), "f"(hi));
+  return p;
+}
+__device__ __forceinline__ float low_of(Float2x p) {
+  float lo, hi;
+  asm("mov.b64 {%0, %1}, %2;" : "=f"(lo), "=f"(hi) : "l"(p));
+  return lo;
+}
+__device__ __forceinline__ float high_of(Float2x p) {
+  float lo, hi;
+  asm("mov.b64 {%0, %1}, %2;" : "=f"(lo), "=f"(hi) : "l"(p));
+  return hi;
+}
+__device__ __forceinline__ Float2x mul_pairs(Float2x a, Float2x b) {
+  Float2x d;
+  asm("mul.rn.f32x2 %0, %1, %2;" : "=l"(d) : "l"(a), "l"(b));
+  return d;
+}
+__device__ __forceinline__ Float2x fma_pairs(Float2x a, Float2x b, Float2x c) {
+  Float2x d;
+  asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(d) : "l"(a), "l"(b), "l"(c));
+  return d;
+}
+
+// norm (if the head has one) and rotation of the sixteen values this lane holds of one head; eight lanes hold
+// the head.  wa, wb: the norm's weights at this lane's elements; cs, sn: cosines and sines of its eight pairs.
+// The two members of a rotation pair travel in one 64-bit register.
+__device__ __forceinline__ Head16 norm_and_rotate16(const Head16& x, bool has_norm, const float* wa, const float* wb, float eps,
+                                                    bool rotate, const float* cs, const float* sn) {
+  Float2x p[8];
 #pragma unroll
-  for (int offset = 8; offset > 0; offset >>= 1) {
-    lo += __shfl_xor_sync(0xffffffffu, lo, offset);
-    hi += __shfl_xor_sync(0xffffffffu, hi, offset);
+  for (int j = 0; j < 8; ++j) p[j] = pair_of(x.a[j], x.b[j]);
+  // The other kernel sums four elements per lane (x^2, then y, z, w by fused multiply-adds) over 32 lanes by a
+  // butterfly (16, 8, 4, 2, 1).  This lane's four quadruples are that kernel's lanes 2l, 2l + 1 (first members) and
+  // 2l + 16, 2l + 17 (second members): its exchange over 16 is a sum inside this lane, those over 8, 4 and 2 are
+  // exchanges over 4, 2 and 1 among the eight lanes, and the last one is again a sum inside the lane.  (The
+  // exchanges run whether or not the head has a norm: the heads of a warp may differ in that.)
+  const Float2x lo = fma_pairs(p[3], p[3], fma_pairs(p[2], p[2], fma_pairs(p[1], p[1], mul_pairs(p[0], p[0]))));
+  const Float2x hi = fma_pairs(p[7], p[7], fma_pairs(p[6], p[6], fma_pairs(p[5], p[5], mul_pairs(p[4], p[4]))));
+  float even = __fadd_rn(low_of(lo), high_of(lo)), odd = __fadd_rn(low_of(hi), high_of(hi));
+#pragma unroll
+  for (int offset = 4; offset > 0; offset >>= 1) {
+    even += __shfl_xor_sync(0xffffffffu, even, offset);
+    odd += __shfl_xor_sync(0xffffffffu, odd, offset);
   }
   if (has_norm) {
-    const float inv = __frsqrt_rn((lo + hi) * (1.0f / 128.0f) + eps);
+    const float inv = __frsqrt_rn((even + odd) * (1.0f / 128.0f) + eps);
+    const Float2x inv2 = pair_of(inv, inv);
 #pragma unroll
-    for (int j = 0; j < 8; ++j) x.v[j] = normed(x.v[j], inv, w[j]);
+    for (int j = 0; j < 8; ++j) p[j] = mul_pairs(mul_pairs(p[j], inv2), pair_of(wa[j], wb[j]));      // (x inv) w, as normed()
   }
+  Head16 y;
   if (rotate) {
-    // rotate_first(a, b) = a cos - b sin for the first of a pair, rotate_second(a, b) = b cos + a sin for the second:
-    // with the partner's value in `other` both are own * cos + other * (-+ sin), and `sn` comes with that sign
 #pragma unroll
     for (int j = 0; j < 8; ++j) {
-      const float other = __shfl_xor_sync(0xffffffffu, x.v[j], 8);
-      x.v[j] = __fmaf_rn(x.v[j], cs[j], __fmul_rn(other, sn[j]));
+      // (a cos - b sin, b cos + a sin): the products with the sine are rounded first, as rotate_first/_second do
+      const float a = low_of(p[j]), b = high_of(p[j]);
+      const Float2x r = fma_pairs(p[j], pair_of(cs[j], cs[j]), pair_of(-__fmul_rn(b, sn[j]), __fmul_rn(a, sn[j])));
+      y.a[j] = low_of(r);
+      y.b[j] = high_of(r);
+    }
+  } else {
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+      y.a[j] = low_of(p[j]);
+      y.b[j] = high_of(p[j]);
     }
   }
-  return x;
+  return y;
 }
 
 template <typename T>
-__global__ void __launch_bounds__(ROW_WARPS * 32, 3)
+__global__ void __launch_bounds__(ROW_THREADS, ROW_BLOCKS_PER_SM)
 qk_norm_rope_kv_row_kernel(const T* __restrict__ qkv, int qkv_stride, T* __restrict__ q_out, T* __restrict__ k_pool,
                            T* __restrict__ v_pool, const int* __restrict__ positions, const int* __restrict__ slots,
                            const float* __restrict__ q_norm, const float* __restrict__ k_norm, float eps,
                            const float* __restrict__ inv_freq, const float* __restrict__ angles,
-                           const float* __restrict__ cos_sin, int n_q, int n_kv, int page_size, int num_pages,
+                           const float* __restrict__ cos_sin, int rows, int n_q, int n_kv, int page_size, int num_pages,
                            int* error_word) {
   // cos_sin: the rows' cosines and sines [rows, 128] (64 cosines, then 64 sines) computed once for the step by
-  // rope_table_kernel, or null: then this block computes its row's own, with the same arithmetic
-  constexpr int D = 128, HALF = 64, HEADS_PER_PASS = ROW_WARPS * 2;
-  __shared__ __align__(16) float cos_table[HALF], sin_table[HALF];
-  __shared__ __align__(16) float norm_weights[2][D];          // of q heads, of k heads (ones where there is no norm)
+  // rope_table_kernel, or null: then this block computes its rows' own, with the same arithmetic
+  constexpr int D = 128, HALF = 64, HEADS_PER_PASS = ROW_THREADS / 8, STAGES = ROW_STAGES;
+  extern __shared__ __align__(16) unsigned char staged_bytes[];       // [STAGES][heads of a row][128] of T
+  __shared__ __align__(16) float row_cos_sin[STAGES][D];              // per row: 64 cosines, then 64 sines
+  __shared__ __align__(16) float norm_weights[2][D];                  // of q heads, of k heads (ones where there is no norm)
+  __shared__ int row_slot[STAGES];                                    // -1: the row's k and v are not stored
   srb_launch_dependents();
-  norm_weights[threadIdx.x >> 7][threadIdx.x & 127] =
-      (threadIdx.x < D ? q_norm : k_norm) ? (threadIdx.x < D ? q_norm : k_norm)[threadIdx.x & 127] : 1.f;
-  const int lane = threadIdx.x & 31;
-  const int half_warp = threadIdx.x >> 4, l = lane & 15;      // this thread's head of a pass, its place in the head
-  const int row = blockIdx.x;
+  norm_weights[0][threadIdx.x] = q_norm ? q_norm[threadIdx.x] : 1.f;
+  norm_weights[1][threadIdx.x] = k_norm ? k_norm[threadIdx.x] : 1.f;
+  const int group = threadIdx.x >> 3, l = threadIdx.x & 7;     // this thread's head of a pass, its place in the head
   const bool rotate = inv_freq || angles;
-  int slot = 0;
-  bool slot_ok = true;
-  if (slots) {
-    slot = slots[row];
-    slot_ok = slot >= 0 && slot < num_pages * page_size;
-    if (!slot_ok && threadIdx.x == 0) atomicOr(error_word, SRB_FLAG_BAD_SLOT);
-  }
-  const int heads = (slots && slot_ok) ? n_q + 2 * n_kv : n_q;
-  const bool first_half = l < 8;
-  const int pair0 = (l & 7) * 8;                               // the eight pairs this lane takes part in
+  const int heads_stored = slots ? n_q + 2 * n_kv : n_q;       // heads of a row that are brought in
+  const size_t stage_bytes = (size_t)heads_stored * D * sizeof(T);
+  const int row_chunks = (int)(stage_bytes / 16);              // 16-byte pieces of a row
+  const int pair0 = l * 8;                                     // the eight pairs this lane holds
   srb_grid_dependency_wait();
-  const T* src = qkv + (size_t)row * qkv_stride + l * 8;
-  // where the row's k and v go: element offset of kv head 0, and the step from one kv head to the next
-  const size_t kv_base = ((size_t)(slot / page_size) * n_kv * page_size + (slot % page_size)) * D + l * 8;
-  const size_t kv_step = (size_t)page_size * D;
-  bool table_ready = !rotate;
-  float cs[8], sn[8];
-#pragma unroll
-  for (int j = 0; j < 8; ++j) {
-    cs[j] = 1.f;
-    sn[j] = 0.f;
-  }
-  if (rotate && cos_sin) {                                     // these loads travel together with the first heads'
-    const float* mine = cos_sin + (size_t)row * D + pair0;
-    const float4 c0 = *reinterpret_cast<const float4*>(mine), c1 = *reinterpret_cast<const float4*>(mine + 4);
-    const float4 s0 = *reinterpret_cast<const float4*>(mine + HALF), s1 = *reinterpret_cast<const float4*>(mine + HALF + 4);
-    cs[0] = c0.x; cs[1] = c0.y; cs[2] = c0.z; cs[3] = c0.w; cs[4] = c1.x; cs[5] = c1.y; cs[6] = c1.z; cs[7] = c1.w;
-    sn[0] = s0.x; sn[1] = s0.y; sn[2] = s0.z; sn[3] = s0.w; sn[4] = s1.x; sn[5] = s1.y; sn[6] = s1.z; sn[7] = s1.w;
-    if (first_half) {
-#pragma unroll
-      for (int j = 0; j < 8; ++j) sn[j] = -sn[j];
-    }
-    table_ready = true;
-  }
-  bool synced = false;
-  for (int first = 0; first < heads; first += HEADS_PER_PASS * ROW_PASSES) {
-    Raw8<T> raw[ROW_PASSES];
-#pragma unroll
-    for (int p = 0; p < ROW_PASSES; ++p) {
-      const int head = first + p * HEADS_PER_PASS + half_warp;
-      if (head < heads) raw[p] = load_raw8(src + (size_t)head * D);
-    }
-    if (!synced) {
-      // while the loads above are on their way: the angles of the row, unless the step brought their table
-      if (!table_ready && threadIdx.x < HALF) {
-        if (angles) {
-          sincosf(angles[(size_t)row * HALF + threadIdx.x], &sin_table[threadIdx.x], &cos_table[threadIdx.x]);
-        } else if (inv_freq) {
-          sincosf((float)positions[row] * inv_freq[threadIdx.x], &sin_table[threadIdx.x], &cos_table[threadIdx.x]);
+
+  // asks for row number `turn` of this block (if there is one) into the ring; one group of copies either way
+  auto request = [&](int turn) {
+    const int row = blockIdx.x + turn * gridDim.x, stage = turn % STAGES;
+    if (row < rows) {
+      const unsigned char* src = reinterpret_cast<const unsigned char*>(qkv + (size_t)row * qkv_stride);
+      unsigned char* dst = staged_bytes + stage * stage_bytes;
+      for (int c = threadIdx.x; c < row_chunks; c += ROW_THREADS) cp_async_16(dst + c * 16, src + (size_t)c * 16, 16);
+      if (rotate) {
+        if (cos_sin) {
+          if (threadIdx.x < D / 4)
+            cp_async_16(&row_cos_sin[stage][threadIdx.x * 4], cos_sin + (size_t)row * D + threadIdx.x * 4, 16);
+        } else if (threadIdx.x < HALF) {
+          const float angle = angles ? angles[(size_t)row * HALF + threadIdx.x] : (float)positions[row] * inv_freq[threadIdx.x];
+          sincosf(angle, &row_cos_sin[stage][HALF + threadIdx.x], &row_cos_sin[stage][threadIdx.x]);
         }
       }
-      __syncthreads();                                         // the norm weights and the angles are in shared memory
-      if (!table_ready) {
-#pragma unroll
-        for (int j = 0; j < 8; ++j) {
-          cs[j] = cos_table[pair0 + j];
-          sn[j] = first_half ? -sin_table[pair0 + j] : sin_table[pair0 + j];
+      if (threadIdx.x == ROW_THREADS - 1) {
+        int slot = -1;
+        if (slots) {
+          slot = slots[row];
+          if (slot < 0 || slot >= num_pages * page_size) {
+            atomicOr(error_word, SRB_FLAG_BAD_SLOT);
+            slot = -1;
+          }
         }
-        table_ready = true;
+        row_slot[stage] = slot;
       }
-      synced = true;
     }
+    cp_async_commit();
+  };
+
 #pragma unroll
-    for (int p = 0; p < ROW_PASSES; ++p) {
-      const int head = first + p * HEADS_PER_PASS + half_warp;
-      // both halves of a warp run the exchanges together; a half whose head lies beyond the last one idles
+  for (int turn = 0; turn < STAGES - 1; ++turn) request(turn);
+  for (int turn = 0;; ++turn) {
+    const int row = blockIdx.x + turn * gridDim.x, stage = turn % STAGES;
+    if (row >= rows) break;
+    cp_async_wait<STAGES - 2>();      // all groups but the newest STAGES - 2: this row's has landed
+    __syncthreads();                  // ... for every thread; and every thread has left the row before this one,
+    request(turn + STAGES - 1);       // whose buffer the row STAGES - 1 ahead takes
+    float cs[8] = {1.f, 1.f, 1.f, 1.f, 1.f, 1.f, 1.f, 1.f}, sn[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+    if (rotate) {
+      const float4* mine = reinterpret_cast<const float4*>(&row_cos_sin[stage][pair0]);
+      const float4 c0 = mine[0], c1 = mine[1], s0 = mine[HALF / 4], s1 = mine[HALF / 4 + 1];
+      cs[0] = c0.x; cs[1] = c0.y; cs[2] = c0.z; cs[3] = c0.w; cs[4] = c1.x; cs[5] = c1.y; cs[6] = c1.z; cs[7] = c1.w;
+      sn[0] = s0.x; sn[1] = s0.y; sn[2] = s0.z; sn[3] = s0.w; sn[4] = s1.x; sn[5] = s1.y; sn[6] = s1.z; sn[7] = s1.w;
+    }
+    const int slot = row_slot[stage];
+    const int heads = slot >= 0 ? heads_stored : n_q;
+    // where the row's k and v go: element offset of kv head 0, and the step from one kv head to the next
+    const size_t kv_base = slot >= 0 ? ((size_t)(slot / page_size) * n_kv * page_size + (slot % page_size)) * D + l * 8 : 0;
+    const size_t kv_step = (size_t)page_size * D;
+    const T* src = reinterpret_cast<const T*>(staged_bytes + stage * stage_bytes) + l * 8;
+    for (int first = 0; first < heads; first += HEADS_PER_PASS) {
+      const int head = first + group;
+      // The four heads of a warp run the exchanges together (they use the full mask, and stay inside a group of
+      // eight lanes); a group whose head lies beyond the last one, or is a v head, computes on the last head's
+      // values and stores nothing.
       const bool live = head < heads;
       const bool is_q = head < n_q, is_k = !is_q && head < n_q + n_kv;
-      if (!__any_sync(0xffffffffu, live)) continue;
+      const Raw16<T> raw = load_raw16(src + (size_t)min(head, heads - 1) * D);
       if (live && !is_q && !is_k) {                            // a v head: no arithmetic
-        store_raw8(v_pool + kv_base + (size_t)(head - n_q - n_kv) * kv_step, raw[p]);
+        store_raw16(v_pool + kv_base + (size_t)(head - n_q - n_kv) * kv_step, raw);
       }
       const bool work = live && (is_q || is_k);
       if (!__any_sync(0xffffffffu, work)) continue;
-      Head8 x;
-      if (work) {
-        x = widen8(raw[p]);
-      } else {
-#pragma unroll
-        for (int j = 0; j < 8; ++j) x.v[j] = 0.f;
-      }
-      // the exchanges inside use the full mask, so every lane of the warp calls it; a half without work carries zeros
-      const bool q_side = is_q || !live;
-      const float4 w0 = *reinterpret_cast<const float4*>(&norm_weights[q_side ? 0 : 1][l * 8]);
-      const float4 w1 = *reinterpret_cast<const float4*>(&norm_weights[q_side ? 0 : 1][l * 8 + 4]);
-      const float w[8] = {w0.x, w0.y, w0.z, w0.w, w1.x, w1.y, w1.z, w1.w};
-      x = norm_and_rotate8(x, (q_side ? q_norm : k_norm) != nullptr, w, eps, rotate, cs, sn);
+      const float* weights = norm_weights[is_q ? 0 : 1];
+      const float4 wa0 = *reinterpret_cast<const float4*>(weights + pair0), wa1 = *reinterpret_cast<const float4*>(weights + pair0 + 4);
+      const float4 wb0 = *reinterpret_cast<const float4*>(weights + HALF + pair0);
+      const float4 wb1 = *reinterpret_cast<const float4*>(weights + HALF + pair0 + 4);
+      const float wa[8] = {wa0.x, wa0.y, wa0.z, wa0.w, wa1.x, wa1.y, wa1.z, wa1.w};
+      const float wb[8] = {wb0.x, wb0.y, wb0.z, wb0.w, wb1.x, wb1.y, wb1.z, wb1.w};
+      const Head16 x = norm_and_rotate16(widen16(raw), (is_q ? q_norm : k_norm) != nullptr, wa, wb, eps, rotate, cs, sn);
       if (work) {
         if (is_q)
-          store8(q_out + ((size_t)row * n_q + head) * D + l * 8, x);
+          store16(q_out + ((size_t)row * n_q + head) * D + l * 8, x);
         else
-          store8(k_pool + kv_base + (size_t)(head - n_q) * kv_step, x);
+          store16(k_pool + kv_base + (size_t)(head - n_q) * kv_step, x);
       }
     }
   }
+  cp_async_wait<0>();                 // (groups without copies may still be counted)
 }
 
 // The cosines and sines of every row's angles, once for a step: out[r, 0..half) = cos, out[r, half..2 half) = sin
@@ -450,20 +512,32 @@ extern "C" int srb_qk_norm_rope_kv_table(const void* qkv, const float* qkv_parts
   const bool whole_head_pairs = !(inv_freq || angles) || (rotary_dim == head_dim && !interleaved);
   // (with fewer rows than about two per SM the kernel below, which spreads a row over blocks, is quicker)
   const int row_bytes_ok = dtype == SRB_DTYPE_F32 || qkv_stride % 8 == 0;      // 16-byte accesses of eight values
-  if (rows >= srb_rope_table_min_rows() && head_dim == 128 && vector_ok && whole_head_pairs && num_parts == 0 && row_bytes_ok) {
+  const size_t staged = (size_t)ROW_STAGES * heads * 128 * (dtype == SRB_DTYPE_F32 ? 4 : 2);     // the ring of rows
+  if (rows >= srb_rope_table_min_rows() && head_dim == 128 && vector_ok && whole_head_pairs && num_parts == 0 && row_bytes_ok &&
+      staged <= 200 * 1024) {
     const float* table = (cos_sin && (((uintptr_t)cos_sin) & 15) == 0) ? cos_sin : nullptr;
-    if (dtype == SRB_DTYPE_F32)
-      SRB_CUDA_CALL(srb_launch(qk_norm_rope_kv_row_kernel<float>, dim3(rows), dim3(ROW_WARPS * 32), 0, s,
+    // as many blocks as stay on the chip together (fewer where the ring is large), every block with the same number of
+    // rows, give or take one
+    const int per_sm = (int)std::max<size_t>(1, std::min<size_t>(ROW_BLOCKS_PER_SM, (220 * 1024) / (staged + 3 * 1024)));
+    const int resident = srb_sm_count() * per_sm;
+    const int rows_per_block = (rows + resident - 1) / resident;
+    const int blocks = (rows + rows_per_block - 1) / rows_per_block;
+    if (dtype == SRB_DTYPE_F32) {
+      SRB_CUDA_CALL(cudaFuncSetAttribute(qk_norm_rope_kv_row_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)staged));
+      SRB_CUDA_CALL(srb_launch(qk_norm_rope_kv_row_kernel<float>, dim3(blocks), dim3(ROW_THREADS), staged, s,
                                (const float*)qkv, qkv_stride, (float*)q_out, (float*)k_pool, (float*)v_pool, positions,
-                               slots, q_norm, k_norm, eps, inv_freq, angles, table, n_q, n_kv, page_size, num_pages,
+                               slots, q_norm, k_norm, eps, inv_freq, angles, table, rows, n_q, n_kv, page_size, num_pages,
                                error_word));
-    else if (dtype == SRB_DTYPE_BF16)
-      SRB_CUDA_CALL(srb_launch(qk_norm_rope_kv_row_kernel<__nv_bfloat16>, dim3(rows), dim3(ROW_WARPS * 32), 0, s,
+    } else if (dtype == SRB_DTYPE_BF16) {
+      SRB_CUDA_CALL(cudaFuncSetAttribute(qk_norm_rope_kv_row_kernel<__nv_bfloat16>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                         (int)staged));
+      SRB_CUDA_CALL(srb_launch(qk_norm_rope_kv_row_kernel<__nv_bfloat16>, dim3(blocks), dim3(ROW_THREADS), staged, s,
                                (const __nv_bfloat16*)qkv, qkv_stride, (__nv_bfloat16*)q_out, (__nv_bfloat16*)k_pool,
-                               (__nv_bfloat16*)v_pool, positions, slots, q_norm, k_norm, eps, inv_freq, angles, table, n_q,
+                               (__nv_bfloat16*)v_pool, positions, slots, q_norm, k_norm, eps, inv_freq, angles, table, rows, n_q,
                                n_kv, page_size, num_pages, error_word));
-    else
+    } else {
       SRB_FAIL("qk_norm_rope_kv: unknown dtype %d", dtype);
+    }
     SRB_LAUNCH_CHECK("qk_norm_rope_kv_row");
     return SRB_OK;
   }
