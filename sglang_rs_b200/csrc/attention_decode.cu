@@ -67,6 +67,7 @@ decode_attention_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16
   // after the dependency wait.  Keys before that position are from earlier steps (a row of this
   // launch is the only row of its request in the step), so a block whose first unit ends before
   // the row's position asks for it before the wait and overlaps the kernel ahead.
+  srb_mark(SRB_MARK_DECODE_ATTENTION, 0);
   srb_launch_dependents();
   const int pos = p.positions[row];
   int first_unit, units, lo, hi;
@@ -117,6 +118,7 @@ decode_attention_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16
   const bool first_unit_is_old = (unit_begin + 1) * DEC_UNIT <= pos;
   if (has_work && first_unit_is_old) issue(unit_begin, 0);
   srb_grid_dependency_wait();
+  srb_mark(SRB_MARK_DECODE_ATTENTION, 1);
   if (has_work && !first_unit_is_old) issue(unit_begin, 0);
 
   // Q fragments: rows of the tile are the query heads of this kv head; rows >= groups are zero
@@ -308,6 +310,7 @@ decode_attention_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16
           __float2bfloat16_rn(l > 0.f ? acc / l : 0.f);
     }
     srb_cluster_sync();                                    // nobody leaves while its memory may still be read
+    srb_mark(SRB_MARK_DECODE_ATTENTION, 2);
     return;
   }
 
@@ -323,7 +326,10 @@ decode_attention_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16
     if (is_last) *counter = 0;
   }
   __syncthreads();
-  if (!is_last) return;
+  if (!is_last) {
+    srb_mark(SRB_MARK_DECODE_ATTENTION, 2);
+    return;
+  }
   __threadfence();
   float* weights = stage_f;              // [groups][count + 1]: 2^(m_s - M) per split, then 1 / sum
   for (int head = warp; head < groups; head += DEC_WARPS) {
@@ -377,6 +383,7 @@ decode_attention_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16
       }
     }
   }
+  srb_mark(SRB_MARK_DECODE_ATTENTION, 2);
 }
 
 template <int D>

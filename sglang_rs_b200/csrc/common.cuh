@@ -118,8 +118,48 @@ static inline int srb_sm_count() {
 // are visible.  srb_launch_dependents() tells the device that the next kernel may be brought
 // in.  Without the launch attribute both calls do nothing.
 static int srb_pdl_enabled = 0;
+
+// ---- a timeline of blocks, for builds with -DSRB_TIMELINE only --------------------------------------
+// Every block of the kernels that make a decode step writes (time, kind, phase, SM, block) records into a
+// buffer that the caller hands to each library: phase 0 when the block starts, 1 when its wait for the kernels
+// ahead returns, 2 when it leaves.  From them one reads how far a kernel runs under the one before it.  Without
+// the flag the marks compile to nothing.
+#ifdef SRB_TIMELINE
+static __device__ unsigned long long* srb_timeline_buffer = nullptr;    // [0]: records written; then two words each
+static __device__ unsigned long long srb_timeline_capacity = 0;
+#define SRB_DEFINE_TIMELINE()                                                                             \
+  extern "C" int srb_set_timeline(void* buffer, long long records) {                                      \
+    unsigned long long capacity = (unsigned long long)records;                                            \
+    if (cudaMemcpyToSymbol(srb_timeline_buffer, &buffer, sizeof(buffer)) != cudaSuccess) return -1;       \
+    return cudaMemcpyToSymbol(srb_timeline_capacity, &capacity, sizeof(capacity)) == cudaSuccess ? 0 : -1; \
+  }
+__device__ __forceinline__ void srb_mark(unsigned kind, unsigned phase) {
+  if (threadIdx.x == 0 && srb_timeline_buffer) {
+    unsigned long long now;
+    unsigned sm;
+    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(now));
+    asm volatile("mov.u32 %0, %%smid;" : "=r"(sm));
+    const unsigned long long at = atomicAdd(srb_timeline_buffer, 1ULL);
+    if (at < srb_timeline_capacity) {
+      const unsigned block = blockIdx.x + gridDim.x * (blockIdx.y + gridDim.y * blockIdx.z);
+      srb_timeline_buffer[1 + 2 * at] = now;
+      srb_timeline_buffer[2 + 2 * at] = ((unsigned long long)kind << 56) | ((unsigned long long)phase << 48) |
+                                        ((unsigned long long)(sm & 0xffff) << 32) | block;
+    }
+  }
+}
+#else
+#define SRB_DEFINE_TIMELINE()
+__device__ __forceinline__ void srb_mark(unsigned, unsigned) {}
+#endif
+#define SRB_MARK_NORM 1
+#define SRB_MARK_PRODUCT 2
+#define SRB_MARK_ROPE 3
+#define SRB_MARK_DECODE_ATTENTION 4
+
 #define SRB_DEFINE_PDL_SWITCH() \
-  extern "C" void srb_set_pdl(int on) { srb_pdl_enabled = on; }
+  extern "C" void srb_set_pdl(int on) { srb_pdl_enabled = on; } \
+  SRB_DEFINE_TIMELINE()
 
 __device__ __forceinline__ void srb_grid_dependency_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
 __device__ __forceinline__ void srb_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }

@@ -100,9 +100,21 @@ add_rmsnorm_vec_kernel(float* __restrict__ residual, const T* __restrict__ delta
                        const float* __restrict__ delta_parts, int num_parts, size_t part_stride,
                        const float* __restrict__ weight, T* __restrict__ out, const int* __restrict__ row_index,
                        int width, float eps, int write_residual) {
+  // the partial sums of a thread's four columns are asked for eight at a time, so that a row of a decode step
+  // costs one or two trips to L2, not one per few parts (measured at Qwen3-8B sizes: 3 % at batch 1, 7 % at 16)
+  constexpr int PART_BATCH = ITER == 1 ? 8 : 4;
   __shared__ float scratch[33];
+  srb_mark(SRB_MARK_NORM, 0);
   srb_launch_dependents();
   srb_grid_dependency_wait();
+  srb_mark(SRB_MARK_NORM, 1);
+  // the norm's weight travels with the row's loads, not after the sum of squares
+  float4 w[ITER];
+#pragma unroll
+  for (int it = 0; it < ITER; ++it) {
+    const int i = (it * blockDim.x + threadIdx.x) * 4;
+    w[it] = i < width ? *reinterpret_cast<const float4*>(weight + i) : make_float4(0.f, 0.f, 0.f, 0.f);
+  }
   const int row = blockIdx.x;
   const size_t src = (size_t)(row_index ? row_index[row] : row) * width;
   float4 x[ITER];
@@ -113,14 +125,22 @@ add_rmsnorm_vec_kernel(float* __restrict__ residual, const T* __restrict__ delta
     x[it] = make_float4(0.f, 0.f, 0.f, 0.f);
     if (i < width) {
       x[it] = *reinterpret_cast<const float4*>(residual + src + i);
-      if (delta) {
-        const float4 d = load4(delta + src + i);
-        x[it].x += d.x; x[it].y += d.y; x[it].z += d.z; x[it].w += d.w;
-      }
-#pragma unroll 4
-      for (int part = 0; part < num_parts; ++part) {
-        const float4 d = *reinterpret_cast<const float4*>(delta_parts + part * part_stride + src + i);
-        x[it].x += d.x; x[it].y += d.y; x[it].z += d.z; x[it].w += d.w;
+      float4 whole = make_float4(0.f, 0.f, 0.f, 0.f);
+      if (delta) whole = load4(delta + src + i);
+      for (int first = 0; first < num_parts || first == 0; first += PART_BATCH) {
+        float4 d[PART_BATCH];
+#pragma unroll
+        for (int j = 0; j < PART_BATCH; ++j)
+          if (first + j < num_parts) d[j] = *reinterpret_cast<const float4*>(delta_parts + (first + j) * part_stride + src + i);
+        if (first == 0 && delta) {
+          x[it].x += whole.x; x[it].y += whole.y; x[it].z += whole.z; x[it].w += whole.w;
+        }
+#pragma unroll
+        for (int j = 0; j < PART_BATCH; ++j) {
+          if (first + j < num_parts) {
+            x[it].x += d[j].x; x[it].y += d[j].y; x[it].z += d[j].z; x[it].w += d[j].w;
+          }
+        }
       }
       if (write_residual) *reinterpret_cast<float4*>(residual + src + i) = x[it];
       partial += x[it].x * x[it].x + x[it].y * x[it].y + x[it].z * x[it].z + x[it].w * x[it].w;
@@ -132,11 +152,10 @@ add_rmsnorm_vec_kernel(float* __restrict__ residual, const T* __restrict__ delta
 #pragma unroll
   for (int it = 0; it < ITER; ++it) {
     const int i = (it * blockDim.x + threadIdx.x) * 4;
-    if (i < width) {
-      const float4 w = *reinterpret_cast<const float4*>(weight + i);
-      store4(dst + i, make_float4(x[it].x * inv * w.x, x[it].y * inv * w.y, x[it].z * inv * w.z, x[it].w * inv * w.w));
-    }
+    if (i < width)
+      store4(dst + i, make_float4(x[it].x * inv * w[it].x, x[it].y * inv * w[it].y, x[it].z * inv * w[it].z, x[it].w * inv * w[it].w));
   }
+  srb_mark(SRB_MARK_NORM, 2);
 }
 
 // out[row, j] = act(gate_up[row, j]) * gate_up[row, inner + j], act being SRB_ACT_* `activation`

@@ -104,6 +104,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constan
   tc_fence_after();
   const unsigned tmem_base = tmem_holder;
 
+  srb_mark(SRB_MARK_PRODUCT, 0);
   srb_launch_dependents();
   if (warp == 0) {
     // Copies, by the whole warp with one elected lane issuing: addresses and coordinates stay in
@@ -128,6 +129,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constan
       issued = i + 1;
     }
     srb_grid_dependency_wait();
+    srb_mark(SRB_MARK_PRODUCT, 1);
     for (int i = 0; i < issued; ++i) {
       if (elect_one())
         tma_load_2d(smem_base + i * STAGE_BYTES + A_BYTES, &map_x, smem_u32(&full_bar[i]), (kb_begin + i) * GEMM_BLOCK_K,
@@ -266,6 +268,7 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constan
     srb_cluster_sync();                                      // nobody leaves while its tile may still be read
   }
   __syncthreads();
+  srb_mark(SRB_MARK_PRODUCT, 2);
   if (threadIdx.x == 0 && abort_flag) atomicOr(args.error_word, SRB_FLAG_WAIT_TIMEOUT);
   if (warp == 1) {
     tc_fence_after();

@@ -50,6 +50,7 @@ __global__ void qk_norm_rope_kv_kernel(const T* __restrict__ qkv, const float* _
   extern __shared__ __align__(16) float staged_all[];  // ROPE_WARPS * head_dim floats
   // The table of angles needs only the step's index arrays and constants: it is computed before
   // the wait for the kernel ahead (whose product this kernel reads) and overlaps that kernel's end.
+  srb_mark(SRB_MARK_ROPE, 0);
   srb_launch_dependents();
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int row = blockIdx.x;
@@ -66,6 +67,7 @@ __global__ void qk_norm_rope_kv_kernel(const T* __restrict__ qkv, const float* _
     for (int i = threadIdx.x; i < (rotary_dim >> 1); i += blockDim.x) sincosf(pos * inv_freq[i], &sin_table[i], &cos_table[i]);
   }
   srb_grid_dependency_wait();
+  srb_mark(SRB_MARK_ROPE, 1);
   __syncthreads();
 #pragma unroll 1
   for (int round = 0; round < rounds; ++round) {
@@ -76,15 +78,33 @@ __global__ void qk_norm_rope_kv_kernel(const T* __restrict__ qkv, const float* _
   const bool is_q = head < n_q;
   const bool is_k = !is_q && head < n_q + n_kv;
   const float* norm_weight = is_q ? q_norm : (is_k ? k_norm : nullptr);
+  // the norm's weight (heads of up to 128 values) and the row's slot are asked for together with the head's
+  // values, not after the sum of squares and after the rotation: one trip to L2 instead of three
+  const bool weight_early = norm_weight && head_dim <= 128;
+  float early[4] = {0.f, 0.f, 0.f, 0.f};
+  if (weight_early) {
+#pragma unroll
+    for (int j = 0; j < 4; ++j)
+      if (lane + 32 * j < head_dim) early[j] = norm_weight[lane + 32 * j];
+  }
+  const int slot = is_q ? 0 : slots[row];
 
   float partial = 0.f;
   if (num_parts > 0 && vector_ok) {
     // four consecutive values per lane and part: all loads of a lane are in flight together
     for (int e = lane * 4; e < head_dim; e += 128) {
       float4 x = make_float4(0.f, 0.f, 0.f, 0.f);
-      for (int part = 0; part < num_parts; ++part) {
-        const float4 d = *reinterpret_cast<const float4*>(qkv_parts + part * part_stride + src_offset + e);
-        x.x += d.x; x.y += d.y; x.z += d.z; x.w += d.w;
+      for (int first = 0; first < num_parts; first += 8) {
+        float4 d[8];
+#pragma unroll
+        for (int j = 0; j < 8; ++j)
+          if (first + j < num_parts) d[j] = *reinterpret_cast<const float4*>(qkv_parts + (first + j) * part_stride + src_offset + e);
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+          if (first + j < num_parts) {
+            x.x += d[j].x; x.y += d[j].y; x.z += d[j].z; x.w += d[j].w;
+          }
+        }
       }
       *reinterpret_cast<float4*>(staged + e) = x;
       partial += sum_squares4(x);
@@ -118,7 +138,13 @@ __global__ void qk_norm_rope_kv_kernel(const T* __restrict__ qkv, const float* _
   if (norm_weight) {
     const float total = srb_warp_sum(partial);
     const float inv = __frsqrt_rn(total / (float)head_dim + eps);
-    for (int e = lane; e < head_dim; e += 32) staged[e] = normed(staged[e], inv, norm_weight[e]);
+    if (weight_early) {
+#pragma unroll
+      for (int j = 0; j < 4; ++j)
+        if (lane + 32 * j < head_dim) staged[lane + 32 * j] = normed(staged[lane + 32 * j], inv, early[j]);
+    } else {
+      for (int e = lane; e < head_dim; e += 32) staged[e] = normed(staged[e], inv, norm_weight[e]);
+    }
   }
   __syncwarp();
   if ((is_q || is_k) && rotate) {
@@ -138,7 +164,6 @@ __global__ void qk_norm_rope_kv_kernel(const T* __restrict__ qkv, const float* _
   if (is_q) {
     dst = q_out + ((size_t)row * n_q + head) * head_dim;
   } else {
-    const int slot = slots[row];
     if (slot < 0 || slot >= num_pages * page_size) {
       if (lane == 0) atomicOr(error_word, SRB_FLAG_BAD_SLOT);
       __syncwarp();
@@ -166,6 +191,7 @@ __global__ void qk_norm_rope_kv_kernel(const T* __restrict__ qkv, const float* _
   }
   __syncwarp();                            // the staging row is reused by the warp's next head
   }
+  srb_mark(SRB_MARK_ROPE, 2);
 }
 
 
