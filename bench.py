@@ -1,7 +1,7 @@
 """Benchmarks of the engine on one B200, random weights, synthetic token ids.
 
     python bench.py [--gpus 1] [--steps K] [--warmup W] [--impl ours|reference]
-                    [--shape qwen3-8b|qwen3-1.7b|qwen3-32b] [--mode decode|prefill|serve|compare-cublas|kernels|ablate]
+                    [--shape qwen3-8b|qwen3-1.7b|qwen3-32b] [--mode decode|prefill|serve|compare-cublas|kernels|ablate|timeline]
 
 ``--mode decode`` (the default) prints the headline JSON line: ``value`` is decoded tokens per second of K
 decode steps at batch 8, timed on the device with CUDA events; ``e2e`` is the same through the Python entry
@@ -19,7 +19,9 @@ of a layer and the logits product at 1, 8, 64 and 2,048 rows, the engine's own p
 (cuBLAS) of the same shape.  ``--mode kernels`` prints the device time per kernel class of a prefill step
 and of a decode step (uncaptured, so that each kernel can be bracketed by events).  ``--mode ablate`` times the
 captured decode step with one kind of kernel left out at a time (the step then computes nothing of use): what
-each kind costs inside the graph, where kernels overlap their neighbours.
+each kind costs inside the graph, where kernels overlap their neighbours.  ``--mode timeline`` runs one captured
+decode step with kernels built to record when every block starts, stops waiting for the kernels ahead and leaves,
+and prints these times launch by launch (use ``--layers 3`` or so).
 
 ``--shape`` picks the layer sizes (BASELINE.json configs[2], [3], [4]); every mode takes it.
 """
@@ -152,7 +154,7 @@ def main() -> int:
     parser.add_argument("--warmup", type=int, default=3)
     parser.add_argument("--impl", default="ours", choices=("ours", "reference"))
     parser.add_argument("--shape", default="qwen3-8b", choices=sorted(SHAPES))
-    parser.add_argument("--mode", default="decode", choices=("decode", "prefill", "serve", "compare-cublas", "kernels", "ablate", "probe-overlap"))
+    parser.add_argument("--mode", default="decode", choices=("decode", "prefill", "serve", "compare-cublas", "kernels", "ablate", "probe-overlap", "timeline"))
     parser.add_argument("--rows", default="1,8,64,2048", help="--mode compare-cublas: the row counts, comma-separated")
     parser.add_argument("--layers", type=int, default=None, help="fewer than the shape has, only where memory or time needs it")
     parser.add_argument("--batch", type=int, default=8)
@@ -175,6 +177,13 @@ def main() -> int:
         print(f"bench.py: this engine runs on one GPU; --gpus {args.gpus} is not supported")
         return 2
     warmup = max(args.warmup, 3)
+
+    if args.mode == "timeline":
+        # the kernels of a decode step, built with marks that record when each block starts, stops waiting for the
+        # kernels ahead and leaves; the variants are files of their own and are loaded in place of the plain builds
+        from sglang_rs_b200.csrc.build import compile_library
+        for name in TIMELINE_LIBRARIES:
+            os.environ[f"SRB_LIBRARY_{name.upper()}"] = compile_library(name, ("SRB_TIMELINE",))
 
     import torch
     from sglang_rs_b200 import ops
@@ -348,6 +357,8 @@ def main() -> int:
         return kernel_classes(args, config, make_engine, prompts, shape_note, warmup)
     if args.mode == "probe-overlap":
         return probe_overlap(args, config)
+    if args.mode == "timeline":
+        return timeline(args, make_engine, prompts, shape_note)
     if args.mode == "ablate":
         from sglang_rs_b200.ops import records
         engine = make_engine(args.batch, args.steps, args.context)
@@ -442,6 +453,79 @@ def main() -> int:
 
 
 # ---------------------------------------------------------------------------------------- products beside cuBLAS
+#: the libraries whose kernels make a decode step of few rows; each has srb_set_timeline when built with SRB_TIMELINE
+TIMELINE_LIBRARIES = ("elementwise", "rope_kv", "attention_decode", "gemm_bf16")
+TIMELINE_KINDS = {1: "add + norm", 2: "product", 3: "rope + page write", 4: "decode attention"}
+TIMELINE_PHASES = ("first block starts", "wait for the kernels ahead returns", "block leaves")
+
+
+def timeline(args, make_engine, prompts, shape_note) -> int:
+    """One captured decode step with kernels that record (time, kernel, phase, SM, block) for every block: prints,
+    launch by launch, when the blocks started, when their wait for the kernels ahead returned and when they left.
+    The marks cost each block some atomics, so a step is a few per cent longer than without them: read the table
+    for the order and the overlap of kernels, not for a step's length."""
+    import ctypes
+
+    import numpy as np
+    import torch
+    from sglang_rs_b200 import ops
+    from sglang_rs_b200.csrc.build import load_library
+    from sglang_rs_b200.engine.runner import StepEntry
+
+    engine = make_engine(args.batch, 16, args.context)
+    handles = [engine.cache.open(f"timeline-{i}") for i in range(args.batch)]
+    for handle, prompt in zip(handles, prompts(args.batch, args.context)):
+        for first in range(0, args.context, 2048):
+            engine.runner.step([StepEntry(handle, prompt[first:first + 2048], [])])
+
+    def one_step():
+        return ops.sample(engine.runner.step([StepEntry(h, [1], [0]) for h in handles]), None, None)
+    for _ in range(6):
+        one_step()
+    torch.cuda.synchronize()
+    records = 1 << 18
+    log = torch.zeros(1 + 2 * records, dtype=torch.int64, device="cuda")
+    for name in TIMELINE_LIBRARIES:
+        if load_library(name).srb_set_timeline(ctypes.c_void_p(log.data_ptr()), ctypes.c_longlong(records)) != 0:
+            raise RuntimeError(f"{name}: the timeline buffer was refused")
+    one_step()
+    torch.cuda.synchronize()
+    log.zero_()
+    begin, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    begin.record()
+    one_step()
+    end.record()
+    torch.cuda.synchronize()
+    for name in TIMELINE_LIBRARIES:
+        load_library(name).srb_set_timeline(None, ctypes.c_longlong(0))
+    host = log.cpu().numpy()
+    count = min(int(host[0]), records)
+    when = host[1:1 + 2 * count:2].astype(np.int64)
+    tag = host[2:2 + 2 * count:2].astype(np.uint64)
+    kind = (tag >> np.uint64(56)).astype(int)
+    phase = ((tag >> np.uint64(48)) & np.uint64(0xff)).astype(int)
+    when = (when - when.min()) / 1000.0
+    rows = []
+    for k in TIMELINE_KINDS:
+        for ph in range(len(TIMELINE_PHASES)):
+            chosen = np.sort(when[(kind == k) & (phase == ph)])
+            if not len(chosen):
+                continue
+            # the marks of one launch lie close together; a gap of more than 1.2 us starts the next launch
+            cuts = [0, *(np.nonzero(np.diff(chosen) > 1.2)[0] + 1).tolist(), len(chosen)]
+            for a, b in zip(cuts[:-1], cuts[1:]):
+                rows.append((float(chosen[a]), float(chosen[b - 1]), b - a, TIMELINE_KINDS[k], TIMELINE_PHASES[ph]))
+    rows.sort()
+    print(f"{'first us':>9} {'last us':>9} {'blocks':>6}  kernel, what its blocks did", file=sys.stderr)
+    for first, last, blocks, name, what in rows:
+        print(f"{first:9.2f} {last:9.2f} {blocks:6d}  {name}: {what}", file=sys.stderr)
+    print(json.dumps({"mode": "timeline", "config": {**shape_note, "global_batch": args.batch, "seq_len": args.context},
+                      "step_us_with_marks": round(begin.elapsed_time(end) * 1e3, 1), "records": count,
+                      "note": "the table is on stderr: per launch and phase the time of the first and the last block's "
+                              "mark, in us since the step's first mark"}))
+    return 0
+
+
 def compare_cublas(args, config, peak, shape_note) -> int:
     """Every product of a layer and the logits product at 1, 8, 64 and 2,048 rows: the path the engine takes
     (``ops.linear`` / ``ops.gated_product``: this package's tcgen05 kernels up to 64 rows and for gate/up of long

@@ -57,12 +57,12 @@ def _headers() -> list[str]:
     return sorted(os.path.join(SOURCE_DIR, n) for n in os.listdir(SOURCE_DIR) if n.endswith((".cuh", ".h")))
 
 
-def _digest(name: str) -> str:
+def _digest(name: str, defines: Sequence[str] = ()) -> str:
     h = hashlib.sha256()
     for path in [os.path.join(SOURCE_DIR, f"{name}.cu"), *_headers()]:
         with open(path, "rb") as handle:
             h.update(handle.read())
-    h.update(" ".join(NVCC_FLAGS).encode())
+    h.update(" ".join([*NVCC_FLAGS, *(f"-D{d}" for d in defines)]).encode())
     return h.hexdigest()[:16]
 
 
@@ -84,27 +84,37 @@ def build_dir() -> str:
     raise KernelBuildError(f"no writable build folder among {candidates}")
 
 
-def library_path(name: str) -> str:
-    return os.path.join(build_dir(), f"{name}-{_digest(name)}.so")
+def _file_name(name: str, defines: Sequence[str] = ()) -> str:
+    # a variant built with preprocessor definitions carries them in its name, apart from the plain build
+    stem = name if not defines else name + "+" + "+".join(defines)
+    return f"{stem}-{_digest(name, defines)}.so"
 
 
-def _find_built(name: str) -> str | None:
+def library_path(name: str, defines: Sequence[str] = ()) -> str:
+    return os.path.join(build_dir(), _file_name(name, defines))
+
+
+def _find_built(name: str, defines: Sequence[str] = ()) -> str | None:
     """A library built earlier for exactly these sources, wherever it may be read."""
-    file_name = f"{name}-{_digest(name)}.so"
+    file_name = _file_name(name, defines)
     for folder in (os.environ.get("SRB_BUILD_DIR"), os.path.join(SOURCE_DIR, "_build")):
         if folder and os.path.exists(os.path.join(folder, file_name)):
             return os.path.join(folder, file_name)
     return None
 
 
-def compile_library(name: str) -> str:
+def compile_library(name: str, defines: Sequence[str] = ()) -> str:
+    """The path of the library built from ``name``.cu, compiled now if no build of these sources exists.
+    ``defines``: preprocessor definitions of a variant (``SRB_TIMELINE``: blocks record when they start, stop
+    waiting and leave); a variant is a file of its own and is loaded only where its path is given
+    (``SRB_LIBRARY_<NAME>``)."""
     source = os.path.join(SOURCE_DIR, f"{name}.cu")
     if not os.path.exists(source):
         raise KernelBuildError(f"no such kernel source: {source}")
-    found = _find_built(name)
+    found = _find_built(name, defines)
     if found:
         return found
-    target = library_path(name)
+    target = library_path(name, defines)
     if os.path.exists(target):
         return target
     lock_path = target + ".lock"
@@ -116,7 +126,7 @@ def compile_library(name: str) -> str:
             _say(f"compiling {name}.cu for sm_100a ...")
             started = time.time()
             partial = f"{target}.{os.getpid()}.tmp"
-            command = [_nvcc(), *NVCC_FLAGS, "-I", SOURCE_DIR, "-o", partial, source]
+            command = [_nvcc(), *NVCC_FLAGS, *(f"-D{d}" for d in defines), "-I", SOURCE_DIR, "-o", partial, source]
             process = subprocess.Popen(command, stdout=subprocess.PIPE, stderr=subprocess.STDOUT, text=True)
             while True:
                 try:
@@ -129,8 +139,9 @@ def compile_library(name: str) -> str:
                     os.remove(partial)
                 raise KernelBuildError(f"nvcc failed for {name}.cu:\n{' '.join(command)}\n{output}")
             os.replace(partial, target)
+            stem = os.path.basename(target).rsplit("-", 1)[0]
             for stale in os.listdir(os.path.dirname(target)):        # builds of older sources of this library
-                if stale.startswith(f"{name}-") and stale.endswith(".so") and stale != os.path.basename(target):
+                if stale.startswith(f"{stem}-") and stale.endswith(".so") and stale != os.path.basename(target):
                     try:
                         os.remove(os.path.join(os.path.dirname(target), stale))
                     except OSError:

@@ -133,11 +133,16 @@ static __device__ unsigned long long srb_timeline_capacity = 0;
     if (cudaMemcpyToSymbol(srb_timeline_buffer, &buffer, sizeof(buffer)) != cudaSuccess) return -1;       \
     return cudaMemcpyToSymbol(srb_timeline_capacity, &capacity, sizeof(capacity)) == cudaSuccess ? 0 : -1; \
   }
-__device__ __forceinline__ void srb_mark(unsigned kind, unsigned phase) {
+__device__ __forceinline__ unsigned long long srb_now() {
+  unsigned long long now;
+  asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(now)::"memory");      // (not to be moved across a barrier)
+  return now;
+}
+// a record of a time taken earlier with srb_now() (a kernel that wants several marks close together takes the
+// times on the way and writes the records at its end, so that writing them delays nothing it measures)
+__device__ __forceinline__ void srb_mark_at(unsigned kind, unsigned phase, unsigned long long now) {
   if (threadIdx.x == 0 && srb_timeline_buffer) {
-    unsigned long long now;
     unsigned sm;
-    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(now));
     asm volatile("mov.u32 %0, %%smid;" : "=r"(sm));
     const unsigned long long at = atomicAdd(srb_timeline_buffer, 1ULL);
     if (at < srb_timeline_capacity) {
@@ -148,8 +153,11 @@ __device__ __forceinline__ void srb_mark(unsigned kind, unsigned phase) {
     }
   }
 }
+__device__ __forceinline__ void srb_mark(unsigned kind, unsigned phase) { srb_mark_at(kind, phase, srb_now()); }
 #else
 #define SRB_DEFINE_TIMELINE()
+__device__ __forceinline__ unsigned long long srb_now() { return 0; }
+__device__ __forceinline__ void srb_mark_at(unsigned, unsigned, unsigned long long) {}
 __device__ __forceinline__ void srb_mark(unsigned, unsigned) {}
 #endif
 #define SRB_MARK_NORM 1
