@@ -100,7 +100,8 @@ __device__ __forceinline__ unsigned long long add2(unsigned long long a, unsigne
 template <int D, int HEADS, int STAGES>
 __global__ void __launch_bounds__(64 + 160 * HEADS, HEADS == 1 ? 2 : 1)
 prefill_attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
-                            const __grid_constant__ CUtensorMap map_v, TcArgs args) {
+                            const __grid_constant__ CUtensorMap map_v, const __grid_constant__ CUtensorMap map_out,
+                            TcArgs args) {
   constexpr int HALVES = D / 64;                           // 64-element (128-byte) column blocks of a head
   constexpr int Q_HALF_BYTES = TC_ROWS * 128;              // [128 rows][64] bfloat16
   constexpr int HALF_BYTES = TC_KEYS * 128;                // [64 keys][64] bfloat16
@@ -370,26 +371,49 @@ prefill_attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
       mbar_arrive(smem_u32(&p_ready[t][i & 1]));
     }
     if (ok) ok = mbar_wait(smem_u32(&o_ready[t]), 0, &abort_flag);
+    // A whole tile leaves through shared memory and one bulk store per 64 columns: a thread's row lies 8 KB from its
+    // neighbour's in the output, so stores from registers touch 32 lines per instruction.  The head's Q tile is free
+    // (every S product has completed) and has the layout the store wants: [128 rows][128 bytes] per 64 columns,
+    // 16-byte pieces exchanged by the 128-byte swizzle.
+    const bool whole_tile = n_rows == TC_ROWS;
+    unsigned char* stage = q_smem + t * Q_BYTES;
     if (ok) {
       tc_fence_after();
       const float inv = row_live && l_run > 0.f ? 1.0f / l_run : 0.f;
       __nv_bfloat16* dst = args.out + ((size_t)(row_begin + r) * args.n_q + head) * D;
-#pragma unroll 1
+#pragma unroll 2
       for (int c = 0; c < D; c += 32) {
         float ov[32];
         tmem_load_32(lane_address + O_COL + c, ov);
-        if (row_live) {
 #pragma unroll
-          for (int j = 0; j < 32; j += 8) {
-            uint4 packed;
-            __nv_bfloat162* pair = reinterpret_cast<__nv_bfloat162*>(&packed);
-            pair[0] = __floats2bfloat162_rn(ov[j] * inv, ov[j + 1] * inv);
-            pair[1] = __floats2bfloat162_rn(ov[j + 2] * inv, ov[j + 3] * inv);
-            pair[2] = __floats2bfloat162_rn(ov[j + 4] * inv, ov[j + 5] * inv);
-            pair[3] = __floats2bfloat162_rn(ov[j + 6] * inv, ov[j + 7] * inv);
+        for (int j = 0; j < 32; j += 8) {
+          uint4 packed;
+          __nv_bfloat162* pair = reinterpret_cast<__nv_bfloat162*>(&packed);
+          pair[0] = __floats2bfloat162_rn(ov[j] * inv, ov[j + 1] * inv);
+          pair[1] = __floats2bfloat162_rn(ov[j + 2] * inv, ov[j + 3] * inv);
+          pair[2] = __floats2bfloat162_rn(ov[j + 4] * inv, ov[j + 5] * inv);
+          pair[3] = __floats2bfloat162_rn(ov[j + 6] * inv, ov[j + 7] * inv);
+          if (whole_tile) {
+            const int column = c + j, piece = (column & 63) >> 3;
+            *reinterpret_cast<uint4*>(stage + (column >> 6) * Q_HALF_BYTES + r * 128 + ((piece ^ (r & 7)) << 4)) = packed;
+          } else if (row_live) {
             *reinterpret_cast<uint4*>(dst + c + j) = packed;
           }
         }
+      }
+    }
+    if (whole_tile) {
+      // (every warp of the head comes here, also one whose wait gave up: the barrier below counts all four)
+      fence_proxy_async_shared();
+      if (t == 0)
+        asm volatile("bar.sync 1, 128;" ::: "memory");
+      else
+        asm volatile("bar.sync 2, 128;" ::: "memory");
+      if (quarter == 0 && lane == 0 && !abort_flag) {
+#pragma unroll
+        for (int h = 0; h < HALVES; ++h)
+          tma_store_3d(&map_out, smem_u32(stage + h * Q_HALF_BYTES), h * 64, head, row_begin);
+        tma_store_commit_and_wait_read();
       }
     }
     tc_fence_before();
@@ -429,14 +453,14 @@ extern "C" int srb_prefill_tc_supports(int n_q, int n_kv, int head_dim, int page
 extern "C" int srb_prefill_tc_tile_rows() { return TC_ROWS; }
 
 template <int D, int HEADS, int STAGES>
-static int launch_tc(const CUtensorMap& map_q, const CUtensorMap& map_k, const CUtensorMap& map_v, const TcArgs& args,
-                     int num_tiles, cudaStream_t s) {
+static int launch_tc(const CUtensorMap& map_q, const CUtensorMap& map_k, const CUtensorMap& map_v, const CUtensorMap& map_out,
+                     const TcArgs& args, int num_tiles, cudaStream_t s) {
   const size_t smem = (size_t)(D / 64) * 128 * (HEADS * TC_ROWS + 2 * STAGES * TC_KEYS) + 1024;
   auto kernel = prefill_attention_tc_kernel<D, HEADS, STAGES>;
   SRB_CUDA_CALL(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
   dim3 grid(args.n_q / HEADS, num_tiles);
   if (num_tiles > 65535) SRB_FAIL("prefill_attention_tc: %d tiles exceed one launch", num_tiles);
-  kernel<<<grid, 64 + 160 * HEADS, smem, s>>>(map_q, map_k, map_v, args);
+  kernel<<<grid, 64 + 160 * HEADS, smem, s>>>(map_q, map_k, map_v, map_out, args);
   SRB_LAUNCH_CHECK("prefill_attention_tc");
   return SRB_OK;
 }
@@ -453,20 +477,21 @@ extern "C" int srb_prefill_attention_tc(const void* q, const void* k_pool, const
              "head counts are not taken by this kernel", head_dim, page_size);
   if (num_pages <= 0 || table_stride <= 0 || window < 0 || rows <= 0)
     SRB_FAIL("prefill_attention_tc: page count, table stride and rows must be positive");
-  if ((((uintptr_t)q | (uintptr_t)k_pool | (uintptr_t)v_pool) & 15) != 0)
+  if ((((uintptr_t)q | (uintptr_t)k_pool | (uintptr_t)v_pool | (uintptr_t)out) & 15) != 0)
     SRB_FAIL("prefill_attention_tc: operands must be 16-byte aligned");
   EncodeTiledFn encode = encode_tiled();
   if (!encode) SRB_FAIL("prefill_attention_tc: the driver does not offer cuTensorMapEncodeTiled");
-  CUtensorMap map_q, map_k, map_v;
-  {
+  CUtensorMap map_q, map_k, map_v, map_out;
+  for (int pass = 0; pass < 2; ++pass) {                     // q, and the output of the same shape
     const cuuint64_t dims[3] = {(cuuint64_t)head_dim, (cuuint64_t)n_q, (cuuint64_t)rows};
     const cuuint64_t strides[2] = {(cuuint64_t)head_dim * 2, (cuuint64_t)n_q * head_dim * 2};
     const cuuint32_t box[3] = {64, 1, TC_ROWS};
     const cuuint32_t elem[3] = {1, 1, 1};
-    const CUresult status = encode(&map_q, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3, const_cast<void*>(q), dims, strides,
+    const CUresult status = encode(pass == 0 ? &map_q : &map_out, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3,
+                                   pass == 0 ? const_cast<void*>(q) : out, dims, strides,
                                    box, elem, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
                                    CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
-    if (status != CUDA_SUCCESS) SRB_FAIL("prefill_attention_tc: tensor map of q failed with %d", (int)status);
+    if (status != CUDA_SUCCESS) SRB_FAIL("prefill_attention_tc: tensor map of %s failed with %d", pass == 0 ? "q" : "the output", (int)status);
   }
   const long long pool_rows = (long long)num_pages * n_kv * page_size;
   if (pool_rows > 0x7fffffffll) SRB_FAIL("prefill_attention_tc: the pool has too many rows for one tensor map");
@@ -489,8 +514,8 @@ extern "C" int srb_prefill_attention_tc(const void* q, const void* k_pool, const
   // two query heads per block when the heads of a kv head pair up
   const bool pairs = (n_q / n_kv) % 2 == 0;
   if (head_dim == 64)
-    return pairs ? launch_tc<64, 2, 4>(map_q, map_k, map_v, args, num_tiles, s)
-                 : launch_tc<64, 1, 2>(map_q, map_k, map_v, args, num_tiles, s);
-  return pairs ? launch_tc<128, 2, 4>(map_q, map_k, map_v, args, num_tiles, s)
-               : launch_tc<128, 1, 2>(map_q, map_k, map_v, args, num_tiles, s);
+    return pairs ? launch_tc<64, 2, 4>(map_q, map_k, map_v, map_out, args, num_tiles, s)
+                 : launch_tc<64, 1, 2>(map_q, map_k, map_v, map_out, args, num_tiles, s);
+  return pairs ? launch_tc<128, 2, 4>(map_q, map_k, map_v, map_out, args, num_tiles, s)
+               : launch_tc<128, 1, 2>(map_q, map_k, map_v, map_out, args, num_tiles, s);
 }
