@@ -30,6 +30,7 @@
 #include "tcgen05_helpers.cuh"
 
 SRB_DEFINE_LAST_ERROR()
+SRB_DEFINE_TIMELINE()
 
 #define TC_ROWS 128
 #define TC_KEYS 64
@@ -121,6 +122,7 @@ prefill_attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
   __shared__ unsigned tmem_holder;
   __shared__ int abort_flag;
 
+  srb_mark(SRB_MARK_PREFILL_ATTENTION, 0);
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   // heads are the fast grid dimension: tiles arrive sorted by falling work, so the long ones start first
   const int tile = blockIdx.y, head0 = blockIdx.x * HEADS;
@@ -157,6 +159,7 @@ prefill_attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
   __syncthreads();
   tc_fence_after();
   const unsigned tmem_base = tmem_holder;
+  srb_mark(SRB_MARK_PREFILL_ATTENTION, 1);                 // (no wait for the kernels ahead here: set-up is complete)
 
   constexpr int V_WARP = 1 + 5 * HEADS;                    // the last warp
   if (warp == 0 || warp == V_WARP) {
@@ -424,6 +427,12 @@ prefill_attention_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
     tc_fence_after();
     tmem_dealloc(tmem_base, TMEM_COLUMNS);
   }
+#ifdef SRB_TIMELINE
+  // (thread 0 is in the K copy warp, which reaches the barrier above long before the softmax warps: its clock is read
+  // only after a second barrier, which the warp that freed the tensor memory reaches last)
+  __syncthreads();
+  srb_mark(SRB_MARK_PREFILL_ATTENTION, 2);
+#endif
 }
 
 // ------------------------------------------------------------------------------- host side

@@ -133,9 +133,16 @@ static __device__ unsigned long long srb_timeline_capacity = 0;
     if (cudaMemcpyToSymbol(srb_timeline_buffer, &buffer, sizeof(buffer)) != cudaSuccess) return -1;       \
     return cudaMemcpyToSymbol(srb_timeline_capacity, &capacity, sizeof(capacity)) == cudaSuccess ? 0 : -1; \
   }
+// The timer is read under a predicate computed from a volatile load of shared memory: the assembler is free to move a
+// plain read of the timer up across a barrier or a wait that comes before it (a block's last barrier, measured: every
+// warp's "time after the barrier" was the time it had arrived), but not a load of shared memory, nor what depends on it.
 __device__ __forceinline__ unsigned long long srb_now() {
+  __shared__ unsigned srb_timer_anchor;                    // never written: any value will do
+  const unsigned anchor = *reinterpret_cast<volatile unsigned*>(&srb_timer_anchor);
   unsigned long long now;
-  asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(now)::"memory");      // (not to be moved across a barrier)
+  asm volatile(
+      "{\n.reg .pred p;\nsetp.ne.u32 p, %1, 0x9e3779b9;\nmov.u64 %0, 0;\n@p mov.u64 %0, %%globaltimer;\n}\n"
+      : "=l"(now) : "r"(anchor) : "memory");
   return now;
 }
 // a record of a time taken earlier with srb_now() (a kernel that wants several marks close together takes the
@@ -164,6 +171,7 @@ __device__ __forceinline__ void srb_mark(unsigned, unsigned) {}
 #define SRB_MARK_PRODUCT 2
 #define SRB_MARK_ROPE 3
 #define SRB_MARK_DECODE_ATTENTION 4
+#define SRB_MARK_PREFILL_ATTENTION 5
 
 #define SRB_DEFINE_PDL_SWITCH() \
   extern "C" void srb_set_pdl(int on) { srb_pdl_enabled = on; } \
