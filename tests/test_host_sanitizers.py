@@ -27,8 +27,10 @@ def test_host_books_under_address_and_undefined_behaviour_sanitizers(tmp_path):
     library = str(tmp_path / "host_core_sanitized.so")
     subprocess.check_call(["g++", "-x", "c++", "-std=c++17", "-O1", "-g", "-fsanitize=address,undefined",
                            "-fno-sanitize-recover=undefined", "-shared", "-fPIC", "-o", library, SOURCE])
-    env = dict(os.environ, SRB_LIBRARY_HOST_CORE=library, LD_PRELOAD=runtime("libasan.so"),
-               ASAN_OPTIONS="detect_leaks=0:abort_on_error=1", UBSAN_OPTIONS="print_stacktrace=1:halt_on_error=1")
+    # (the child sees no GPU: the CUDA driver does not start under AddressSanitizer, and the host books need none)
+    env = dict(os.environ, SRB_LIBRARY_HOST_CORE=library, LD_PRELOAD=runtime("libasan.so"), CUDA_VISIBLE_DEVICES="",
+               ASAN_OPTIONS="detect_leaks=0:abort_on_error=1:protect_shadow_gap=0",
+               UBSAN_OPTIONS="print_stacktrace=1:halt_on_error=1")
     tests = [os.path.join(ROOT, "tests", name) for name in ("test_cache_manager.py", "test_prefix_tree.py", "test_scheduler.py")]
     process = subprocess.run([sys.executable, "-m", "pytest", "-q", "-x", "-m", "not gpu", "-p", "no:cacheprovider", *tests],
                              env=env, capture_output=True, text=True, timeout=900, cwd=ROOT)
