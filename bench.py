@@ -21,7 +21,8 @@ and of a decode step (uncaptured, so that each kernel can be bracketed by events
 captured decode step with one kind of kernel left out at a time (the step then computes nothing of use): what
 each kind costs inside the graph, where kernels overlap their neighbours.  ``--mode timeline`` runs one captured
 decode step with kernels built to record when every block starts, stops waiting for the kernels ahead and leaves,
-and prints these times launch by launch (use ``--layers 3`` or so).
+and prints these times launch by launch (use ``--layers 3`` or so); with ``--only-prefill`` the step is one prompt of
+``--prefill-tokens`` and the table shows the blocks of the prefill attention tile by tile.
 
 ``--shape`` picks the layer sizes (BASELINE.json configs[2], [3], [4]); every mode takes it.
 """
@@ -454,8 +455,8 @@ def main() -> int:
 
 # ---------------------------------------------------------------------------------------- products beside cuBLAS
 #: the libraries whose kernels make a decode step of few rows; each has srb_set_timeline when built with SRB_TIMELINE
-TIMELINE_LIBRARIES = ("elementwise", "rope_kv", "attention_decode", "gemm_bf16")
-TIMELINE_KINDS = {1: "add + norm", 2: "product", 3: "rope + page write", 4: "decode attention"}
+TIMELINE_LIBRARIES = ("elementwise", "rope_kv", "attention_decode", "gemm_bf16", "attention_prefill_tc")
+TIMELINE_KINDS = {1: "add + norm", 2: "product", 3: "rope + page write", 4: "decode attention", 5: "prefill attention"}
 TIMELINE_PHASES = ("first block starts", "wait for the kernels ahead returns", "block leaves")
 
 
@@ -472,15 +473,27 @@ def timeline(args, make_engine, prompts, shape_note) -> int:
     from sglang_rs_b200.csrc.build import load_library
     from sglang_rs_b200.engine.runner import StepEntry
 
-    engine = make_engine(args.batch, 16, args.context)
-    handles = [engine.cache.open(f"timeline-{i}") for i in range(args.batch)]
-    for handle, prompt in zip(handles, prompts(args.batch, args.context)):
-        for first in range(0, args.context, 2048):
-            engine.runner.step([StepEntry(handle, prompt[first:first + 2048], [])])
+    if args.only_prefill:
+        # a prompt of --prefill-tokens in one step: only the tcgen05 attention carries marks among its kernels
+        # (phase 1 there: set-up complete); the table below is per tile of 128 rows instead of per launch
+        engine = make_engine(1, 16, args.prefill_tokens)
+        prompt = prompts(1, args.prefill_tokens)[0]
+        turn = iter(range(1 << 30))
 
-    def one_step():
-        return ops.sample(engine.runner.step([StepEntry(h, [1], [0]) for h in handles]), None, None)
-    for _ in range(6):
+        def one_step():
+            handle = engine.cache.open(f"timeline-prefill-{next(turn)}")
+            engine.runner.step([StepEntry(handle, prompt, [args.prefill_tokens - 1])])
+            engine.cache.close(handle)
+    else:
+        engine = make_engine(args.batch, 16, args.context)
+        handles = [engine.cache.open(f"timeline-{i}") for i in range(args.batch)]
+        for handle, prompt in zip(handles, prompts(args.batch, args.context)):
+            for first in range(0, args.context, 2048):
+                engine.runner.step([StepEntry(handle, prompt[first:first + 2048], [])])
+
+        def one_step():
+            return ops.sample(engine.runner.step([StepEntry(h, [1], [0]) for h in handles]), None, None)
+    for _ in range(3 if args.only_prefill else 6):
         one_step()
     torch.cuda.synchronize()
     records = 1 << 18
@@ -505,6 +518,8 @@ def timeline(args, make_engine, prompts, shape_note) -> int:
     kind = (tag >> np.uint64(56)).astype(int)
     phase = ((tag >> np.uint64(48)) & np.uint64(0xff)).astype(int)
     when = (when - when.min()) / 1000.0
+    if args.only_prefill:
+        return prefill_attention_table(args, shape_note, when, tag, kind, phase, count, begin.elapsed_time(end))
     rows = []
     for k in TIMELINE_KINDS:
         for ph in range(len(TIMELINE_PHASES)):
@@ -523,6 +538,45 @@ def timeline(args, make_engine, prompts, shape_note) -> int:
                       "step_us_with_marks": round(begin.elapsed_time(end) * 1e3, 1), "records": count,
                       "note": "the table is on stderr: per launch and phase the time of the first and the last block's "
                               "mark, in us since the step's first mark"}))
+    return 0
+
+
+def prefill_attention_table(args, shape_note, when, tag, kind, phase, count, step_ms) -> int:
+    """The blocks of the last layer's prefill attention, tile by tile (a tile: 128 rows of the prompt against the keys
+    before and beside them; the grid holds one block per tile and pair of query heads, longest tiles first): when
+    they started, how long they stayed, and which SMs took a second block."""
+    import numpy as np
+    block = (tag & np.uint64(0xffffffff)).astype(int)
+    sm = ((tag >> np.uint64(32)) & np.uint64(0xffff)).astype(int)
+    mine = kind == 5
+    last = {}                                     # (block, phase) -> (time, sm) of the last layer's launch
+    for i in np.argsort(when):
+        if mine[i]:
+            last[(int(block[i]), int(phase[i]))] = (float(when[i]), int(sm[i]))
+    blocks = sorted({b for b, _ in last})
+    if not blocks:
+        print("no marks of the prefill attention: the step did not run the tcgen05 kernel", file=sys.stderr)
+        return 1
+    head_blocks = shape_note["num_attention_heads"] // 2 if (shape_note["num_attention_heads"] //
+                                                           shape_note["num_key_value_heads"]) % 2 == 0 else shape_note["num_attention_heads"]
+    base = min(last[(b, 0)][0] for b in blocks)
+    print(f"{'tile':>4} {'blocks':>6} {'start us':>17} {'set-up us':>9} {'stay us':>15} {'leave us':>9}", file=sys.stderr)
+    for tile in range((len(blocks) + head_blocks - 1) // head_blocks):
+        ids = [b for b in blocks if b // head_blocks == tile]
+        start = np.array([last[(b, 0)][0] - base for b in ids])
+        ready = np.array([last[(b, 1)][0] - last[(b, 0)][0] for b in ids])
+        leave = np.array([last[(b, 2)][0] - base for b in ids])
+        print(f"{tile:4d} {len(ids):6d} {start.min():7.1f} ..{start.max():7.1f} {ready.mean():9.1f} "
+              f"{(leave - start).min():6.1f} ..{(leave - start).max():6.1f} {leave.max():9.1f}", file=sys.stderr)
+    per_sm = {}
+    for b in blocks:
+        per_sm.setdefault(last[(b, 0)][1], []).append(b)
+    print(f"{len(blocks)} blocks on {len(per_sm)} SMs; SMs with two or more blocks: {sum(len(v) > 1 for v in per_sm.values())}",
+          file=sys.stderr)
+    print(json.dumps({"mode": "timeline", "config": {**shape_note, "prefill_tokens": args.prefill_tokens},
+                      "step_ms_with_marks": round(step_ms, 3), "records": count,
+                      "attention_us_last_layer": round(max(last[(b, 2)][0] for b in blocks) - base, 1),
+                      "note": "the table is on stderr: the last layer's prefill attention, per tile of 128 rows"}))
     return 0
 
 
