@@ -622,10 +622,12 @@ def compare_cublas(args, config, peak, shape_note) -> int:
                     call(weights[i % copies])
                 torch.cuda.synchronize()
                 repeats = 20 if m <= 64 else 10
+                replayed = m <= 1024
                 begin, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-                if m <= 64:
-                    # a few microseconds of kernel each: launched one by one the host would be what is timed, so
-                    # the calls are captured into one graph (as the engine's decode steps are) and replayed
+                if replayed:
+                    # some tens of microseconds of kernel each: launched one by one the host would be what is timed
+                    # (this package's call goes through Python), so the calls are captured into one graph (as the
+                    # engine's decode steps are) and replayed
                     graph = torch.cuda.CUDAGraph()
                     side = torch.cuda.Stream()
                     side.wait_stream(torch.cuda.current_stream())
@@ -654,10 +656,10 @@ def compare_cublas(args, config, peak, shape_note) -> int:
                 pair_us = timed(lambda w: ops.gemm_bf16_pair(x, w, word, mode="bf16"))
                 entry["pair_kernel_us"] = round(pair_us, 2)
                 entry["pair_kernel_tflops"] = round(2.0 * m * n * k / (pair_us * 1e-6) / 1e12, 1)
-            if m <= 64:
+            if m <= 512:
                 entry["own_hbm_frac"] = round(n * k * 2 / (own_us * 1e-6) / 1e9 / peak["hbm_gbs"], 3)
                 entry["cublas_hbm_frac"] = round(n * k * 2 / (library_us * 1e-6) / 1e9 / peak["hbm_gbs"], 3)
-            else:
+            if m > 64:
                 entry["own_tflops"] = round(2.0 * m * n * k / (own_us * 1e-6) / 1e12, 1)
                 entry["cublas_tflops"] = round(2.0 * m * n * k / (library_us * 1e-6) / 1e12, 1)
             results.append(entry)
@@ -666,7 +668,7 @@ def compare_cublas(args, config, peak, shape_note) -> int:
         torch.cuda.empty_cache()
     ops.raise_on_error_word(word)
     print(json.dumps({"mode": "compare-cublas", "config": shape_note, "timing": "CUDA events, weights rotate through copies "
-                      "larger than L2; up to 64 rows the calls are replayed from one CUDA graph; gate_up includes the activation (own: in the epilogue; cuBLAS: a kernel after it)",
+                      "larger than L2; up to 1,024 rows the calls are replayed from one CUDA graph; gate_up includes the activation (own: in the epilogue; cuBLAS: a kernel after it)",
                       "products": results}))
     return 0
 
