@@ -39,3 +39,17 @@ def test_the_timeline_of_a_prefill_step_lists_the_attention_tile_by_tile():
                             "--layers", "2")
     assert line["mode"] == "timeline" and line["attention_us_last_layer"] > 0
     assert "blocks on" in table and table.count("\n") >= 5          # a header, four tiles of 128 rows, the summary
+
+
+def test_kernel_classes_ablation_serving_and_the_comparison_with_cublas_on_a_small_case():
+    line, _ = run_bench("--mode", "kernels", "--shape", "qwen3-1.7b", "--layers", "2", "--prefill-tokens", "256", "--batch", "2",
+                        "--context", "128")
+    assert line["mode"] == "kernels" and line["prefill"]["gemm"] > 0 and line["decode"]["attention_decode"] > 0
+    line, _ = run_bench("--mode", "ablate", "--shape", "qwen3-1.7b", "--layers", "2", "--batch", "2", "--context", "128", "--steps", "4")
+    assert line["mode"] == "ablate" and set(line["us_saved_per_layer_by_leaving_out"]) >= {"norm", "rope", "attention", "qkv"}
+    line, _ = run_bench("--mode", "serve", "--shape", "qwen3-1.7b", "--layers", "2", "--requests", "6")
+    assert line["mode"] == "serve" and line["requests"] == 6 and line["value"] > 0 and line["preemptions"] >= 0
+    line, _ = run_bench("--mode", "compare-cublas", "--shape", "qwen3-1.7b", "--rows", "8,128")
+    assert line["mode"] == "compare-cublas"
+    by_key = {(entry["product"], entry["rows"]): entry for entry in line["products"]}
+    assert by_key[("qkv", 8)]["own_us"] > 0 and by_key[("down", 128)]["cublas_us"] > 0
