@@ -88,6 +88,42 @@ def test_preemption_on_a_small_pool_gives_the_same_tokens(tmp_path):
     assert [r["output_ids"] for r in results] == [pm.plain_greedy(cfg, weights, p, 40) for p in prompts]
 
 
+@pytest.mark.parametrize("overlap", [True, False])
+def test_many_preemptions_with_long_prompts_change_no_token(overlap):
+    """Sixteen requests with prompts of up to 1,500 tokens on a pool that holds a fifth of them (layers of 1,024 wide,
+    heads of 128: portions of 512 rows go through the kernels for many rows): the requests are preempted dozens of
+    times, their prompts computed again in other portions and beside other rows, and in 32-bit every token must be
+    the one that a pool without pressure gives."""
+    import random
+    from sglang_rs_b200 import Engine
+    config = {"architectures": ["Qwen3ForCausalLM"], "model_type": "qwen3", "num_hidden_layers": 2, "hidden_size": 1024,
+              "num_attention_heads": 8, "num_key_value_heads": 4, "head_dim": 128, "intermediate_size": 1536,
+              "vocab_size": 3001, "rope_theta": 1e6, "rms_norm_eps": 1e-6, "tie_word_embeddings": False,
+              "max_position_embeddings": 4096, "hidden_act": "silu", "attention_bias": False}
+    rng = random.Random(5)
+    prompts = [[rng.randrange(config["vocab_size"]) for _ in range(rng.choice([17, 130, 300, 700, 1500]))] for _ in range(16)]
+    new_tokens = [rng.choice([8, 40, 90]) for _ in prompts]
+
+    def run(pool):
+        engine = Engine(config=config, random_weights=True, seed=1, dtype="float32", page_size=16, max_total_tokens=pool,
+                        max_running_requests=12, chunked_prefill_size=512, disable_overlap_schedule=not overlap)
+        ids = [engine.add_request(p, {"max_new_tokens": n, "ignore_eos": True}) for p, n in zip(prompts, new_tokens)]
+        tokens = {i: [] for i in ids}
+        while engine.scheduler.has_work or engine._in_flight is not None:
+            for output in engine.step(overlap=overlap):
+                tokens[output.request_id].extend(output.token_ids)
+        for output in engine.drain():
+            tokens[output.request_id].extend(output.token_ids)
+        engine.cache.check_invariants()
+        return [tokens[i] for i in ids], engine.scheduler.stats["preemptions"]
+
+    at_ease, none = run(40000)
+    pressed, preemptions = run(2400)
+    assert none == 0 and preemptions >= 10
+    assert [len(t) for t in pressed] == new_tokens
+    assert pressed == at_ease
+
+
 @pytest.mark.parametrize("dtype_name,stored,limit", [("float32", torch.float32, 0.0), ("bfloat16", torch.bfloat16, 3e-2)])
 def test_shared_prefix_is_reused_and_changes_nothing(tmp_path, dtype_name, stored, limit):
     """Two prompts share 24 tokens (3 pages of 8); the second starts from the first one's pages.
